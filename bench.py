@@ -1,0 +1,455 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode-time KV path: append of RoPE'd K/V + GQA flash-decode attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg2|cfg3]
+
+One "step" = one decode step of the whole model stack of the workload: every layer appends one token per sequence
+and runs attention over its cache.  Default workload (`cfg1`): 28-layer Qwen3-0.6B shape (16 q / 8 kv heads,
+head_dim 128), batch 1, fp16 cache, context 4096 growing by one token per step, synthetic seeded N(0,1) inputs.
+
+Prints ONE JSON line (rank 0).  `value` is device-timed throughput with inputs resident in HBM; `e2e` is the same
+metric through the host-buffer entry point (er_kv_decode_step_host) with H2D/D2H copies inside the timed region;
+`roofline` is the attention kernel's algorithmic bytes over its CUDA-event-timed duration against the measured
+copy bandwidth; `cpu_baseline` times the CPU restatement of the reference path on the host cores.
+
+Multi-GPU (`--gpus N`, launched by torchrun, one rank per GPU): the path shards by sequence with no data-path
+collective -- every rank advances its own sequence(s) -- so scaling is weak and `value` sums all ranks.
+
+`--impl reference` times the reference's own CPU implementation of the path (its Swift sources cannot be built
+here, so this is the C restatement under oracle/) with all host threads, on the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_kv_append_attention_tokens_per_s"
+WORKLOADS = {
+    # BASELINE.json configs[1]: the configuration the metric is quoted on
+    "cfg1": dict(name="cfg1: Qwen3-0.6B shape, 28 layers, batch 1, fp16 KV, context 4096, 1 token appended per step",
+                 layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="head_major", theta=1.0e6),
+    "cfg1_token_major": dict(name="cfg1 with the reference's token-major [slot][kvHead][dim] ring layout",
+                             layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="token_major",
+                             theta=1.0e6),
+    # BASELINE.json configs[2]
+    "cfg2": dict(name="cfg2: Qwen3-0.6B shape, 28 layers, batch 8, TurboQuant turbo4 K / turbo3 V, fp16 norms, context 32768",
+                 layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3, norm="float16",
+                 layout="head_major", theta=1.0e6, outliers=True),
+    # BASELINE.json configs[3] (single-GPU form: all kv heads on one GPU)
+    "cfg3": dict(name="cfg3: Llama-3.1-8B shape, 32 layers, batch 64, fp16 KV in 16-token pages, context U[1024,16384]",
+                 layers=32, batch=64, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
+                 page_size=16, theta=5.0e5),
+}
+D = 128
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            p = json.load(open(path))
+            return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def row_bytes(w):
+    """Algorithmic cache bytes per (token, kv head): K row + V row (+ stored norms)."""
+    if w["precision"] == "float16":
+        return 2 * D * 2
+    nb = 2 if w.get("norm", "float32") == "float16" else 4
+    return (D * w["kbits"] + 31) // 32 * 4 + (D * w["vbits"] + 31) // 32 * 4 + 2 * nb
+
+
+def sequence_lengths(w, seed=2):
+    if "ragged" in w:
+        lo, hi = w["ragged"]
+        rng = np.random.Generator(np.random.PCG64(seed))
+        return [int(x) for x in rng.integers(lo, hi + 1, size=w["batch"])]
+    return [w["ctx"]] * w["batch"]
+
+
+def step_bytes(w, lens, step_index):
+    """Algorithmic bytes of one decode step: every cache row read once per kv head, one row written per
+    (layer, sequence, kv head), Q read and O written."""
+    rb = row_bytes(w)
+    read = sum((n + step_index + 1) for n in lens) * w["kv_heads"] * rb * w["layers"]
+    write = len(lens) * w["kv_heads"] * rb * w["layers"]
+    qo = len(lens) * w["layers"] * w["heads"] * D * 4 * 2
+    return read + write + qo
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------- CPU legs
+
+def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
+    """Times the CPU restatement of the reference path (oracle/) with every host thread on a bounded sample of the
+    workload: `layers_sampled` of the model's layers per step, throughput scaled to the full layer count."""
+    from oracle import er_oracle as oracle
+    oracle.build()
+    threads = oracle.max_threads()
+    L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
+    rng = np.random.Generator(np.random.PCG64(7))
+    turbo = w["precision"] != "float16"
+    max_len = max(lens) + 64
+    # one layer's cache per sampled layer; lengths as in the workload
+    def make_layer():
+        if turbo:
+            kw, vw = (D * w["kbits"] + 31) // 32, (D * w["vbits"] + 31) // 32
+            return [dict(kc=rng.integers(0, 2 ** 32, size=(max_len * Hkv, kw), dtype=np.uint32),
+                         kn=np.abs(rng.standard_normal(max_len * Hkv).astype(np.float32)) + 10,
+                         vc=rng.integers(0, 2 ** 32, size=(max_len * Hkv, vw), dtype=np.uint32),
+                         vn=np.abs(rng.standard_normal(max_len * Hkv).astype(np.float32)) + 10) for _ in range(B)]
+        return [dict(k=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16),
+                     v=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16)) for _ in range(B)]
+
+    def one_layer_step(layer, s):
+        for b in range(B):
+            q = rng.standard_normal((H, D), dtype=np.float32)
+            k = rng.standard_normal((Hkv, D), dtype=np.float32)
+            v = rng.standard_normal((Hkv, D), dtype=np.float32)
+            c = layer[b]
+            if turbo:
+                oracle.decode_step_turboquant(q, k, v, c["kc"], c["kn"], w["kbits"], c["vc"], c["vn"], w["vbits"], lens[b] + s,
+                                              w["theta"], norm_fp16=w.get("norm") == "float16", threads=threads)
+            else:
+                oracle.decode_step_f16(q, k, v, c["k"], c["v"], lens[b] + s, w["theta"], threads=threads)
+
+    probe_layer = make_layer()
+    t0 = time.perf_counter()
+    one_layer_step(probe_layer, 0)
+    t_layer = time.perf_counter() - t0
+    if steps is None:
+        layers_sampled = max(1, min(L, int(budget_s / max(t_layer, 1e-6) / 4)))
+        steps = max(1, min(32, int(budget_s / (t_layer * layers_sampled))))
+    else:
+        total = steps + warmup
+        layers_sampled = max(1, min(L, int(150.0 / max(t_layer * total, 1e-6))))
+    layers = [probe_layer] + [make_layer() for _ in range(layers_sampled - 1)]
+    for s in range(warmup):
+        for layer in layers:
+            one_layer_step(layer, s)
+    t0 = time.perf_counter()
+    for s in range(steps):
+        for layer in layers:
+            one_layer_step(layer, warmup + s)
+    dt = time.perf_counter() - t0
+    per_step_full = dt / steps * (L / layers_sampled)
+    sample = "%d decode steps x %d of %d layers (batch %d, context %d), time scaled by %d/%d" % (
+        steps, layers_sampled, L, B, max(lens), L, layers_sampled)
+    return dict(value=B / per_step_full, unit="tokens/s", cores=threads, kind="port", sample=sample,
+                ms_per_step=per_step_full * 1e3, steps=steps)
+
+
+def run_reference_impl(args, w, lens):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_reference_leg(w, lens, args.cpu_seconds, steps=args.steps, warmup=max(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "implementation": "CPU restatement of the reference path (oracle/er_oracle.c), "
+                   "OpenMP over heads; the reference's Swift/Metal sources cannot be built in this environment"},
+        "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------- GPU leg
+
+def build_cache(er, torch, w, lens, extra_tokens):
+    B, L, Hkv = len(lens), w["layers"], w["kv_heads"]
+    cap = (max(lens) + extra_tokens + 15) // 16 * 16
+    layout = {"head_major": er.Layout.head_major, "token_major": er.Layout.token_major, "paged": er.Layout.paged}[w["layout"]]
+    kw = {}
+    if layout == er.Layout.paged:
+        ps = w["page_size"]
+        need = sum((n + extra_tokens + ps - 1) // ps for n in lens)
+        kw = dict(page_size=ps, num_pages=need)
+    if w["precision"] == "float16":
+        cache = er.KVCache(cap, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, **kw)
+    else:
+        nf = er.NormFormat.float16 if w.get("norm") == "float16" else er.NormFormat.float32
+        cache = er.KVCache(cap, L, Hkv, D, er.Precision.turboquantV2, key_type=w["kbits"], value_type=w["vbits"], norm_format=nf,
+                           max_batch=B, layout=layout, **kw)
+    if layout == er.Layout.paged:
+        rng = np.random.Generator(np.random.PCG64(2))
+        alloc = er.BlockTableAllocator(kw["num_pages"], w["page_size"], free_order=rng.permutation(kw["num_pages"]))
+        for b, n in enumerate(lens):
+            cache.set_block_table(b, alloc.ensure(b, n + extra_tokens))
+    return cache
+
+
+def fill_cache(er, torch, cache, w, lens, sp, seed):
+    """Pre-fills every (layer, sequence) with seeded N(0,1) rows (cast to fp16) through the bulk append entry point."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    Hkv = w["kv_heads"]
+    scale_k = scale_v = None
+    if w.get("outliers"):
+        rng = np.random.Generator(np.random.PCG64(seed))
+        scale_k = torch.as_tensor(np.where(rng.random((Hkv, D)) < 0.01, 20.0, 1.0).astype(np.float32)).cuda()
+        scale_v = torch.as_tensor(np.where(rng.random((Hkv, D)) < 0.01, 20.0, 1.0).astype(np.float32)).cuda()
+    chunk = 8192
+    for l in range(w["layers"]):
+        for b, n in enumerate(lens):
+            for s in range(0, n, chunk):
+                c = min(chunk, n - s)
+                k = torch.randn((c, Hkv, D), generator=g, device="cuda", dtype=torch.float32)
+                v = torch.randn((c, Hkv, D), generator=g, device="cuda", dtype=torch.float32)
+                if scale_k is not None:
+                    k, v = k * scale_k, v * scale_v
+                k, v = k.half().float(), v.half().float()
+                cache.write_rows(l, b, s, c, k, v, sp)
+    torch.cuda.synchronize()
+
+
+def run_ours(args, w, lens):
+    import torch
+    import torch.distributed as dist
+    import edgerunner_b200 as er
+    from edgerunner_b200.sharding import max_over_ranks
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit("--gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, world))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
+    K, W = args.steps, max(args.warmup, 0)
+    sp = er.step_params(rope_theta=w["theta"])
+    cache = build_cache(er, torch, w, lens, K + W + 8)
+    fill_cache(er, torch, cache, w, lens, sp, seed=1000 + rank)
+    base_positions = list(lens)
+
+    def set_start():
+        for b, n in enumerate(base_positions):
+            cache.set_position(n, seq=b)
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5 + rank)
+    pool = min(K + W, 64)      # distinct per-step inputs, cycled (a step's cost does not depend on their values)
+    qs = torch.randn((pool, L, B, H, D), generator=g, device="cuda").half().float()
+    ks = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
+    vs = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
+    out = torch.empty((L, B, H, D), device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- leg 1: device-resident inputs, whole step through er_kv_decode_step ----
+    set_start()
+    for s in range(W):
+        cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = er.lib().er_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for s in range(K):
+        i = (W + s) % pool
+        cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
+    e1.record(stream)
+    barrier()
+    launches = er.lib().er_kernel_launch_count() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1), device="cuda")
+    clocks = sampler.stop() if rank == 0 else None
+    assert cache.device_status() == 0, "device-side wait timed out"
+    for b, n in enumerate(base_positions):
+        assert cache.total_written(0, b) == n + W + K
+    tokens = B * K * world
+    value = tokens / (ms_total * 1e-3)
+    bytes_total = sum(step_bytes(w, lens, W + s) for s in range(K))
+    hbm_gbs = bytes_total / (ms_total * 1e-3) / 1e9       # per GPU
+
+    # ---- leg 2: per-kernel durations (append / attention) with CUDA events, same steps, split entry points ----
+    set_start()
+    for s in range(W):
+        cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+    torch.cuda.synchronize()
+    n_probe = min(K, 64)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_probe)]
+    for s in range(n_probe):
+        i = (W + s) % pool
+        evs[s][0].record(stream)
+        cache.append_rope_kv(ks[i], vs[i], sp, stream=stream)
+        evs[s][1].record(stream)
+        cache.attention_decode(qs[i], out, H, sp, pending=1, stream=stream)
+        evs[s][2].record(stream)
+        cache.advance(1, stream=stream)
+    torch.cuda.synchronize()
+    t_append = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    t_attn = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    attn_bytes = statistics.mean(step_bytes(w, lens, W + s) for s in range(n_probe)) - B * Hkv * row_bytes(w) * L
+    peak, peak_src = measured_peaks()
+    achieved = attn_bytes / (t_attn * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": int(attn_bytes), "launch_ms": round(t_attn, 5),
+                "append_kernel_ms": round(t_append, 5), "frac_of_8tbs": round(achieved / 8000.0, 4)}
+
+    # ---- leg 3: end to end through the host-buffer entry point (H2D q/k/v + D2H out every step) ----
+    hq = torch.empty((pool, L, B, H, D), dtype=torch.float32).pin_memory().copy_(qs.cpu())
+    hk = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(ks.cpu())
+    hv = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(vs.cpu())
+    hout = torch.empty((L, B, H, D), dtype=torch.float32).pin_memory()
+    set_start()
+    for s in range(W):
+        cache.decode_step_host(hq[s % pool], hk[s % pool], hv[s % pool], hout, H, sp, stream=stream)
+    barrier()
+    e0.record(stream)
+    t0 = time.perf_counter()
+    checksum = 0.0
+    for s in range(K):
+        i = (W + s) % pool
+        cache.decode_step_host(hq[i], hk[i], hv[i], hout, H, sp, stream=stream)
+        checksum += float(hout[0, 0, 0, 0])          # the host reads the step's result
+    e1.record(stream)
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms), device="cuda")
+    assert math.isfinite(checksum)
+    e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+           "h2d_bytes_per_step": int(hq[0].numel() + hk[0].numel() + hv[0].numel()) * 4, "d2h_bytes_per_step": int(hout.numel()) * 4,
+           "entry_point": "er_kv_decode_step_host"}
+
+    # ---- leg 4: one launch per layer (how a model that interleaves its own projections would call it) ----
+    set_start()
+    for s in range(min(W, 4)):
+        for l in range(L):
+            cache.decode_step(qs[s % pool, l], ks[s % pool, l], vs[s % pool, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=stream)
+    torch.cuda.synchronize()
+    n_pl = min(K, 32)
+    e0.record(stream)
+    for s in range(n_pl):
+        i = (W + s) % pool
+        for l in range(L):
+            cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    per_layer_tok_s = B * n_pl / (e0.elapsed_time(e1) * 1e-3)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_leg(w, lens, args.cpu_seconds)
+        cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "layers": L, "batch_per_gpu": B, "q_heads": H, "kv_heads": Hkv, "head_dim": D,
+                       "kv_storage": w["precision"], "layout": w["layout"],
+                       "launch": "layer-batched: one append + one persistent attention launch per step for all layers",
+                       "sharding": "by sequence, one replica of the workload per GPU, no collective" if world > 1 else "single GPU",
+                       "l2": "cache bytes read per step (%.0f MB) exceed the 126 MB L2; no flush needed" % (step_bytes(w, lens, W) / 1e6),
+                       "per_layer_launch_tokens_per_s": per_layer_tok_s},
+            "hbm_gbs_per_gpu": round(hbm_gbs, 1), "frac_of_8tbs": round(hbm_gbs / 8000.0, 4),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    w = WORKLOADS[args.workload]
+    lens = sequence_lengths(w)
+    if args.impl == "reference":
+        run_reference_impl(args, w, lens)
+    else:
+        run_ours(args, w, lens)
+
+
+if __name__ == "__main__":
+    main()

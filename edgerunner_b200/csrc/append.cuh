@@ -1,0 +1,169 @@
+// Row append / scatter / gather kernels for the dense (fp16 / fp32) KV cache.
+//
+// append_rope_dense_kernel fuses what the reference issues as separate dispatches per layer:
+//   rope_neox_f32_to_f16   K row -> NeoX RoPE -> half() -> cache slot   (Shaders/RoPE.metal:498-531)
+//   convert_f32_to_f16     V row -> half() -> cache slot                (LlamaLanguageModel.swift:3676-3684)
+// for every (layer, sequence) of a decode step in one launch.  Each thread converts 2 x 8 contiguous
+// elements (dims [8i,8i+8) and their RoPE partners [64+8i,64+8i+8)) and issues 16-byte stores.
+#pragma once
+
+#include "er_common.cuh"
+
+namespace er {
+
+struct AppendParams {
+    const float* k;               // [rows][num_kv_heads][128]
+    const float* v;
+    uint8_t* k_base;
+    uint8_t* v_base;
+    int64_t k_layer_stride_bytes;
+    int64_t v_layer_stride_bytes;
+    const int32_t* lengths;       // decode mode: row position = lengths[layer][seq]
+    int bulk;                     // 0: row r -> (layer_begin + r / batch, r % batch); 1: fixed (layer, seq), pos = start + r
+    int layer_begin;
+    int batch;
+    int fixed_layer;
+    int fixed_seq;
+    int start_pos;
+    int rows;
+    float rope_scaling;
+    int apply_rope;
+    KVAddressing addr;
+    InvFreqTable inv_freq;
+};
+
+__device__ __forceinline__ void append_locate(const AppendParams& p, int r, int& layer, int& seq, uint32_t& pos) {
+    if (p.bulk) {
+        layer = p.fixed_layer;
+        seq = p.fixed_seq;
+        pos = static_cast<uint32_t>(p.start_pos + r);
+    } else {
+        layer = p.layer_begin + r / p.batch;
+        seq = r % p.batch;
+        pos = static_cast<uint32_t>(p.lengths[layer * p.batch + seq]);
+    }
+}
+
+template <typename ELEM>
+__device__ __forceinline__ void store8(uint8_t* dst, const float* x);
+
+template <>
+__device__ __forceinline__ void store8<__half>(uint8_t* dst, const float* x) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __halves2half2(__float2half_rn(x[2 * i]), __float2half_rn(x[2 * i + 1]));
+    *reinterpret_cast<uint4*>(dst) = u;
+}
+
+template <>
+__device__ __forceinline__ void store8<float>(uint8_t* dst, const float* x) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(x[0], x[1], x[2], x[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+template <typename ELEM>
+__global__ void __launch_bounds__(128) append_rope_dense_kernel(const __grid_constant__ AppendParams p) {
+    __shared__ float2 cs[kHalfDim];
+    const int r = blockIdx.x;
+    int layer, seq;
+    uint32_t pos;
+    append_locate(p, r, layer, seq, pos);
+    if (p.apply_rope && threadIdx.x < kHalfDim)
+        cs[threadIdx.x] = rope_cos_sin(pos, p.inv_freq.f[threadIdx.x], p.rope_scaling);
+    __syncthreads();
+    const int slot = static_cast<int>(pos % static_cast<uint32_t>(p.addr.max_seq_len));
+    constexpr int kRowBytes = kHeadDim * sizeof(ELEM);
+    const int hkv = p.addr.num_kv_heads;
+    for (int w = threadIdx.x; w < hkv * 16; w += blockDim.x) {
+        const int h = w >> 4, part = w & 15, is_v = part >> 3, i = part & 7;
+        const float* src = (is_v ? p.v : p.k) + (static_cast<int64_t>(r) * hkv + h) * kHeadDim;
+        const float4 a0 = __ldg(reinterpret_cast<const float4*>(src + 8 * i));
+        const float4 a1 = __ldg(reinterpret_cast<const float4*>(src + 8 * i + 4));
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(src + 64 + 8 * i));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(src + 64 + 8 * i + 4));
+        float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        if (!is_v && p.apply_rope) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float y0, y1;
+                rope_rotate(xa[c], xb[c], cs[8 * i + c], y0, y1);
+                xa[c] = y0;
+                xb[c] = y1;
+            }
+        }
+        uint8_t* base = is_v ? p.v_base + layer * p.v_layer_stride_bytes : p.k_base + layer * p.k_layer_stride_bytes;
+        uint8_t* dst = base + row_index(p.addr, seq, h, slot) * kRowBytes;
+        store8<ELEM>(dst + 8 * i * sizeof(ELEM), xa);
+        store8<ELEM>(dst + (64 + 8 * i) * sizeof(ELEM), xb);
+    }
+}
+
+// Generic element scatter (any head_dim, no rotation): one token row [num_kv_heads][head_dim] of raw
+// elements into its cache slot.  Backs KVCache.append / appendF16 (KVCache.swift:410-476).
+__global__ void scatter_row_kernel(const uint8_t* src, uint8_t* base, KVAddressing addr, int seq, int slot,
+                                   int head_dim, int elem_bytes) {
+    const int row_bytes = head_dim * elem_bytes;
+    const int total = addr.num_kv_heads * row_bytes;
+    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < total; b += gridDim.x * blockDim.x) {
+        const int h = b / row_bytes, off = b % row_bytes;
+        base[row_index(addr, seq, h, slot) * row_bytes + off] = src[b];
+    }
+}
+
+// Generic gather in logical (oldest-first) order for KVCache.retrieve (KVCache.swift:478-522):
+// logical token i lives in slot (first_slot + i) % max_seq_len.
+__global__ void gather_rows_kernel(const uint8_t* base, uint8_t* dst, KVAddressing addr, int seq, int first_slot,
+                                   int tokens, int row_bytes) {
+    const int64_t per_token = static_cast<int64_t>(addr.num_kv_heads) * row_bytes;
+    const int64_t total = per_token * tokens;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < total;
+         b += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(b / per_token);
+        const int rem = static_cast<int>(b % per_token);
+        const int h = rem / row_bytes, off = rem % row_bytes;
+        const int slot = (first_slot + t) % addr.max_seq_len;
+        dst[b] = base[row_index(addr, seq, h, slot) * row_bytes + off];
+    }
+}
+
+// rope_neox_f32 / rope_neox_f32_to_f16 as stand-alone operators (Shaders/RoPE.metal:57-93, 498-531),
+// any even head_dim up to 512, partial rotary factor honoured.  inv_freq[pair] =
+// 1.0f / powr(theta, float(2*pair)/float(headDim)) is tabulated by the host.
+struct WideInvFreqTable {
+    float f[256];
+};
+
+template <typename OUT>
+__global__ void rope_neox_kernel(const float* in, OUT* out, uint32_t seq_len, uint32_t num_heads, uint32_t head_dim,
+                                 uint32_t start_pos, float scaling, float partial,
+                                 const __grid_constant__ WideInvFreqTable table) {
+    const uint32_t half = head_dim / 2;
+    const uint64_t total = static_cast<uint64_t>(seq_len) * num_heads * half;
+    const uint32_t rotated = static_cast<uint32_t>(static_cast<float>(half) * partial);
+    for (uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+         e += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t pair = static_cast<uint32_t>(e % half);
+        const uint64_t sh = e / half;
+        const uint32_t seq = static_cast<uint32_t>(sh / num_heads);
+        const uint64_t hb = sh * head_dim;
+        float x0 = in[hb + pair], x1 = in[hb + pair + half];
+        if (pair < rotated) {
+            const float2 cs = rope_cos_sin(seq + start_pos, table.f[pair], scaling);
+            float y0, y1;
+            rope_rotate(x0, x1, cs, y0, y1);
+            x0 = y0;
+            x1 = y1;
+        }
+        out[hb + pair] = static_cast<OUT>(x0);
+        out[hb + pair + half] = static_cast<OUT>(x1);
+    }
+}
+
+__global__ void add_lengths_kernel(int32_t* lengths, int begin, int count, int delta) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x)
+        lengths[begin + e] += delta;
+}
+
+}  // namespace er

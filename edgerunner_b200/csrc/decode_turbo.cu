@@ -1,0 +1,26 @@
+// Instantiations of the persistent flash-decode kernel for TurboQuant rows: key/value presets turbo3 and
+// turbo4 in every combination, GQA group sizes 1, 2, 4.
+#include "flash_decode_turbo.cuh"
+#include "launchers.h"
+
+namespace er {
+
+template <int KB, int VB>
+static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
+    switch (group) {
+        case 1: return launch_decode_policy<TurboPolicy<1, KB, VB>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboPolicy<4, KB, VB>>(p, grid, stream);
+        default: return kNotBuilt;
+    }
+}
+
+int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream) {
+    if (kbits == 4 && vbits == 4) return launch_group<4, 4>(group, p, grid, stream);
+    if (kbits == 4 && vbits == 3) return launch_group<4, 3>(group, p, grid, stream);
+    if (kbits == 3 && vbits == 3) return launch_group<3, 3>(group, p, grid, stream);
+    if (kbits == 3 && vbits == 4) return launch_group<3, 4>(group, p, grid, stream);
+    return kNotBuilt;
+}
+
+}  // namespace er

@@ -1,0 +1,888 @@
+// Host side of the C ABI declared in include/er_kv.h: the KV cache object (device slabs, ring /
+// block-table bookkeeping, scratch) and the launch code of every kernel.  The cache mirrors the public
+// surface of the reference's KVCache (Sources/EdgeRunnerMetal/KVCache.swift:12-1138); storage layout and
+// kernels are this library's own.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/er_kv.h"
+#include "append.cuh"
+#include "er_common.cuh"
+#include "launchers.h"
+#include "turboquant.cuh"
+
+using namespace er;
+
+namespace {
+
+thread_local std::string g_last_error;
+std::atomic<uint64_t> g_launches{0};
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define ER_CUDA(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess) return fail(ER_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+inline int32_t check_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ER_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return ER_OK;
+}
+
+// inv_freq[pair] = 1.0f / powr(theta, float(2*pair)/float(headDim))   (Shaders/RoPE.metal:83-84),
+// powr evaluated through double and rounded once.
+template <typename TABLE>
+void fill_inv_freq(TABLE& t, int capacity, float theta, uint32_t head_dim) {
+    const uint32_t half = head_dim / 2;
+    for (uint32_t d = 0; d < static_cast<uint32_t>(capacity); ++d) {
+        if (d < half) {
+            const float exponent = static_cast<float>(2u * d) / static_cast<float>(head_dim);
+            const float pw = static_cast<float>(std::pow(static_cast<double>(theta), static_cast<double>(exponent)));
+            t.f[d] = 1.0f / pw;
+        } else {
+            t.f[d] = 0.f;
+        }
+    }
+}
+
+// Scratch shared by the raw-buffer operators (no cache object): one per device, created on first use.
+struct Workspace {
+    int device = -1;
+    int num_sms = 0;
+    float* scratch = nullptr;
+    int* counters = nullptr;   // [0] done counter, [1] status, [16..] item counters
+    size_t counter_ints = 0;
+};
+
+std::mutex g_ws_mu;
+std::vector<Workspace> g_ws;
+
+constexpr size_t kScratchFloatsPerCta = 2 * 8 * 130;   // two slots, up to 8 q heads per kv head
+
+int32_t make_workspace(Workspace& w, int device, size_t item_counters) {
+    w.device = device;
+    ER_CUDA(cudaDeviceGetAttribute(&w.num_sms, cudaDevAttrMultiProcessorCount, device));
+    ER_CUDA(cudaMalloc(&w.scratch, sizeof(float) * kScratchFloatsPerCta * w.num_sms));
+    w.counter_ints = 16 + item_counters;
+    ER_CUDA(cudaMalloc(&w.counters, sizeof(int) * w.counter_ints));
+    ER_CUDA(cudaMemset(w.counters, 0, sizeof(int) * w.counter_ints));
+    return ER_OK;
+}
+
+int32_t get_workspace(Workspace** out) {
+    int device = 0;
+    ER_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_ws_mu);
+    for (auto& w : g_ws)
+        if (w.device == device) { *out = &w; return ER_OK; }
+    g_ws.reserve(16);
+    g_ws.emplace_back();
+    int32_t rc = make_workspace(g_ws.back(), device, static_cast<size_t>(kMaxPairs) * 16);
+    if (rc != ER_OK) { g_ws.pop_back(); return rc; }
+    *out = &g_ws.back();
+    return ER_OK;
+}
+
+int32_t decode_status(int rc, int group, int kbits, int vbits) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rc == 0) return ER_OK;
+    if (rc == kNotBuilt)
+        return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4 and presets turbo3/turbo4 are",
+                    group, kbits, vbits);
+    return fail(ER_ERR_CUDA, "flash_decode_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+}
+
+int32_t dispatch_decode_f16(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
+    return decode_status(launch_decode_dense(group, p, grid, stream), group, 16, 16);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------ cache object
+
+struct er_kv {
+    er_kv_config cfg{};
+    int device = 0;
+    int num_sms = 0;
+    bool turbo = false;
+    int elem_bytes = 0;           // dense element size
+    int k_row_bytes = 0;          // bytes of one (token, kv head) row
+    int v_row_bytes = 0;
+    int norm_bytes = 0;           // TurboQuant: bytes of one stored norm
+    int page_tokens = 0;          // tokens per page (HEAD_MAJOR: padded ring length)
+    int pool_pages = 0;           // pages per layer
+    int pages_per_seq = 0;        // block-table stride (0 = identity addressing)
+    bool token_major = false;
+    uint8_t* k_slab = nullptr;
+    uint8_t* v_slab = nullptr;
+    uint8_t* kn_slab = nullptr;
+    uint8_t* vn_slab = nullptr;
+    int64_t k_layer_stride = 0, v_layer_stride = 0, n_layer_stride = 0;
+    int32_t* d_lengths = nullptr;          // [layers][batch] tokens written (device copy is authoritative)
+    std::vector<int32_t> h_lengths;
+    int32_t* d_block_table = nullptr;
+    std::vector<int32_t> h_block_table;    // [batch][pages_per_seq], -1 = unassigned
+    std::vector<uint32_t> h_block_count;
+    float* d_scratch = nullptr;
+    int* d_counters = nullptr;             // [0] done, [1] status, [16..] item counters
+    uint8_t* d_stage = nullptr;            // staging for host-facing calls
+    size_t stage_bytes = 0;
+    float cached_theta = 0.f;
+    InvFreqTable inv_freq{};
+    std::mutex mu;
+
+    KVAddressing addressing() const {
+        KVAddressing a;
+        a.token_major = token_major ? 1 : 0;
+        a.num_kv_heads = static_cast<int>(cfg.num_kv_heads);
+        a.max_seq_len = static_cast<int>(cfg.max_seq_len);
+        a.page_size = page_tokens;
+        a.pages_per_seq = pages_per_seq;
+        a.block_table = d_block_table;
+        return a;
+    }
+    const InvFreqTable& freq(float theta) {
+        if (theta != cached_theta) {
+            fill_inv_freq(inv_freq, kHalfDim, theta, cfg.head_dim);
+            cached_theta = theta;
+        }
+        return inv_freq;
+    }
+};
+
+namespace {
+
+int32_t ensure_stage(er_kv* kv, size_t bytes) {
+    if (kv->stage_bytes >= bytes) return ER_OK;
+    if (kv->d_stage) cudaFree(kv->d_stage);
+    kv->d_stage = nullptr;
+    kv->stage_bytes = 0;
+    size_t want = std::max<size_t>(bytes, 1 << 20);
+    if (cudaMalloc(&kv->d_stage, want) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ER_ERR_ALLOCATION_FAILED, "staging buffer of %zu bytes", want);
+    }
+    kv->stage_bytes = want;
+    return ER_OK;
+}
+
+int32_t pull_lengths(er_kv* kv) {
+    ER_CUDA(cudaMemcpy(kv->h_lengths.data(), kv->d_lengths, kv->h_lengths.size() * sizeof(int32_t),
+                       cudaMemcpyDeviceToHost));
+    return ER_OK;
+}
+int32_t push_lengths(er_kv* kv) {
+    ER_CUDA(cudaMemcpy(kv->d_lengths, kv->h_lengths.data(), kv->h_lengths.size() * sizeof(int32_t),
+                       cudaMemcpyHostToDevice));
+    return ER_OK;
+}
+
+int32_t check_layers(const er_kv* kv, uint32_t b, uint32_t e) {
+    if (b >= e || e > kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer range [%u, %u) of %u", b, e, kv->cfg.num_layers);
+    return ER_OK;
+}
+
+bool is_dense(const er_kv* kv) { return kv->cfg.precision == ER_KV_FLOAT32 || kv->cfg.precision == ER_KV_FLOAT16; }
+
+int32_t step_defaults(const er_kv* kv, const er_step_params* in, er_step_params& out) {
+    if (in) out = *in; else { std::memset(&out, 0, sizeof(out)); out.rope_theta = 10000.f; }
+    if (out.rope_scaling == 0.f) out.rope_scaling = 1.f;
+    if (out.softmax_scale == 0.f) out.softmax_scale = 1.0f / std::sqrt(static_cast<float>(kv->cfg.head_dim));
+    if (out.apply_rope && !(out.rope_theta > 0.f)) return fail(ER_ERR_INVALID_ARGUMENT, "rope_theta must be > 0");
+    return ER_OK;
+}
+
+int32_t launch_append(er_kv* kv, AppendParams& ap, cudaStream_t stream) {
+    ap.k_base = kv->k_slab;
+    ap.v_base = kv->v_slab;
+    ap.k_layer_stride_bytes = kv->k_layer_stride;
+    ap.v_layer_stride_bytes = kv->v_layer_stride;
+    ap.addr = kv->addressing();
+    if (ap.rows <= 0) return ER_OK;
+    if (kv->turbo) {
+        TurboAppendParams tp;
+        tp.base = ap;
+        tp.kn_base = kv->kn_slab;
+        tp.vn_base = kv->vn_slab;
+        tp.n_layer_stride_bytes = kv->n_layer_stride;
+        tp.norm_fp16 = kv->cfg.norm_format == ER_TQ_NORM_FLOAT16;
+        return launch_turbo_append(tp, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), stream,
+                                   check_launch);
+    }
+    if (kv->cfg.precision == ER_KV_FLOAT16)
+        append_rope_dense_kernel<__half><<<ap.rows, 128, 0, stream>>>(ap);
+    else
+        append_rope_dense_kernel<float><<<ap.rows, 128, 0, stream>>>(ap);
+    return check_launch("append_rope_dense_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* er_status_string(int32_t s) {
+    switch (s) {
+        case ER_OK: return "ok";
+        case ER_ERR_ALLOCATION_FAILED: return "allocationFailed";
+        case ER_ERR_INVALID_LAYER: return "invalidLayer";
+        case ER_ERR_PRECISION_MISMATCH: return "precisionMismatch";
+        case ER_ERR_UNSUPPORTED_STORAGE: return "unsupportedStorage";
+        case ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API: return "compressedRetrieveRequiresDecodedAPI";
+        case ER_ERR_COMPRESSED_BUFFER_ACCESS_REQUIRES_TURBOQUANT_API: return "compressedBufferAccessRequiresTurboQuantAPI";
+        case ER_ERR_SHAPE: return "shape";
+        case ER_ERR_CUDA: return "cuda";
+        case ER_ERR_INVALID_ARGUMENT: return "invalidArgument";
+        case ER_ERR_OUT_OF_PAGES: return "outOfPages";
+        case ER_ERR_UNSUPPORTED: return "unsupported";
+        case ER_ERR_DEVICE_TIMEOUT: return "deviceTimeout";
+        default: return "unknown";
+    }
+}
+
+const char* er_last_error_string(void) { return g_last_error.c_str(); }
+
+int32_t er_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+uint64_t er_kernel_launch_count(void) { return g_launches.load(); }
+
+int32_t er_host_alloc(void** out, size_t bytes) {
+    if (!out) return fail(ER_ERR_INVALID_ARGUMENT, "null out");
+    ER_CUDA(cudaHostAlloc(out, bytes, cudaHostAllocDefault));
+    return ER_OK;
+}
+int32_t er_host_free(void* ptr) {
+    ER_CUDA(cudaFreeHost(ptr));
+    return ER_OK;
+}
+
+int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
+    if (!c || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (c->max_seq_len == 0 || c->num_layers == 0 || c->num_kv_heads == 0 || c->head_dim == 0)
+        return fail(ER_ERR_SHAPE, "zero-sized cache dimension");
+    switch (c->precision) {
+        case ER_KV_FLOAT32: case ER_KV_FLOAT16: case ER_KV_TURBOQUANT_V2: break;
+        case ER_KV_FLOAT8: case ER_KV_Q8_0: case ER_KV_TURBOQUANT_BALANCED: case ER_KV_TURBOQUANT_AGGRESSIVE:
+            return fail(ER_ERR_UNSUPPORTED_STORAGE, "precision %u is outside this backend's scope", c->precision);
+        default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
+    }
+    if (er_device_count() <= 0) return fail(ER_ERR_CUDA, "no CUDA device: this backend has no CPU fallback");
+    er_kv* kv = new er_kv();
+    kv->cfg = *c;
+    if (kv->cfg.max_batch == 0) kv->cfg.max_batch = 1;
+    if (static_cast<uint64_t>(kv->cfg.num_layers) * kv->cfg.max_batch > 1u << 20) { delete kv; return fail(ER_ERR_SHAPE, "layers*batch too large"); }
+    kv->turbo = c->precision == ER_KV_TURBOQUANT_V2;
+    auto bail = [&](int32_t rc) { er_kv_destroy(kv); return rc; };
+    if (cudaGetDevice(&kv->device) != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cudaGetDevice"));
+    cudaDeviceGetAttribute(&kv->num_sms, cudaDevAttrMultiProcessorCount, kv->device);
+    if (kv->turbo) {
+        if (c->head_dim != kHeadDim) return bail(fail(ER_ERR_SHAPE, "TurboQuant storage needs head_dim 128 (TurboQuantLayout.supportedDimension)"));
+        for (uint32_t t : {c->key_type, c->value_type})
+            if (t != ER_TQ_TURBO2 && t != ER_TQ_TURBO3 && t != ER_TQ_TURBO4)
+                return bail(fail(ER_ERR_INVALID_ARGUMENT, "TurboQuant type %u (expected 2, 3 or 4 bits)", t));
+        kv->k_row_bytes = tq_code_words(static_cast<int>(c->key_type)) * 4;
+        kv->v_row_bytes = tq_code_words(static_cast<int>(c->value_type)) * 4;
+        kv->norm_bytes = c->norm_format == ER_TQ_NORM_FLOAT16 ? 2 : 4;
+        if (kv->cfg.layout == ER_KV_LAYOUT_TOKEN_MAJOR) kv->cfg.layout = ER_KV_LAYOUT_HEAD_MAJOR;
+    } else {
+        kv->elem_bytes = c->precision == ER_KV_FLOAT32 ? 4 : 2;
+        kv->k_row_bytes = kv->v_row_bytes = static_cast<int>(c->head_dim) * kv->elem_bytes;
+    }
+    const uint32_t B = kv->cfg.max_batch;
+    switch (kv->cfg.layout) {
+        case ER_KV_LAYOUT_TOKEN_MAJOR:
+            kv->token_major = true;
+            kv->page_tokens = static_cast<int>(c->max_seq_len);
+            kv->pool_pages = static_cast<int>(B);
+            kv->pages_per_seq = 0;
+            break;
+        case ER_KV_LAYOUT_HEAD_MAJOR:
+            kv->page_tokens = static_cast<int>((c->max_seq_len + 15u) & ~15u);
+            kv->pool_pages = static_cast<int>(B);
+            kv->pages_per_seq = 0;
+            break;
+        case ER_KV_LAYOUT_PAGED:
+            if (c->page_size == 0 || c->page_size % 16 != 0 || c->num_pages == 0)
+                return bail(fail(ER_ERR_INVALID_ARGUMENT, "paged layout needs page_size %% 16 == 0 and num_pages > 0"));
+            kv->page_tokens = static_cast<int>(c->page_size);
+            kv->pool_pages = static_cast<int>(c->num_pages);
+            kv->pages_per_seq = static_cast<int>((c->max_seq_len + c->page_size - 1) / c->page_size);
+            break;
+        default: return bail(fail(ER_ERR_INVALID_ARGUMENT, "unknown layout %u", kv->cfg.layout));
+    }
+    const int64_t rows_per_layer = static_cast<int64_t>(kv->pool_pages) * c->num_kv_heads * kv->page_tokens;
+    kv->k_layer_stride = rows_per_layer * kv->k_row_bytes;
+    kv->v_layer_stride = rows_per_layer * kv->v_row_bytes;
+    kv->n_layer_stride = rows_per_layer * kv->norm_bytes;
+    auto alloc = [&](uint8_t** p, int64_t bytes) -> bool {
+        if (bytes == 0) return true;
+        if (cudaMalloc(p, static_cast<size_t>(bytes)) != cudaSuccess) { cudaGetLastError(); *p = nullptr; return false; }
+        return cudaMemset(*p, 0, static_cast<size_t>(bytes)) == cudaSuccess;
+    };
+    if (!alloc(&kv->k_slab, kv->k_layer_stride * c->num_layers) || !alloc(&kv->v_slab, kv->v_layer_stride * c->num_layers) ||
+        !alloc(&kv->kn_slab, kv->n_layer_stride * c->num_layers) || !alloc(&kv->vn_slab, kv->n_layer_stride * c->num_layers))
+        return bail(fail(ER_ERR_ALLOCATION_FAILED, "KV slabs (%lld + %lld bytes per layer, %u layers)",
+                         static_cast<long long>(kv->k_layer_stride), static_cast<long long>(kv->v_layer_stride), c->num_layers));
+    kv->h_lengths.assign(static_cast<size_t>(c->num_layers) * B, 0);
+    if (cudaMalloc(&kv->d_lengths, kv->h_lengths.size() * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemset(kv->d_lengths, 0, kv->h_lengths.size() * sizeof(int32_t)) != cudaSuccess)
+        return bail(fail(ER_ERR_ALLOCATION_FAILED, "length table"));
+    if (kv->pages_per_seq > 0) {
+        kv->h_block_table.assign(static_cast<size_t>(B) * kv->pages_per_seq, 0);
+        kv->h_block_count.assign(B, 0);
+        if (cudaMalloc(&kv->d_block_table, kv->h_block_table.size() * sizeof(int32_t)) != cudaSuccess ||
+            cudaMemset(kv->d_block_table, 0, kv->h_block_table.size() * sizeof(int32_t)) != cudaSuccess)
+            return bail(fail(ER_ERR_ALLOCATION_FAILED, "block table"));
+    }
+    const size_t counters = 16 + static_cast<size_t>(c->num_layers) * B * c->num_kv_heads;
+    if (cudaMalloc(&kv->d_scratch, sizeof(float) * kScratchFloatsPerCta * std::max(kv->num_sms, 1)) != cudaSuccess ||
+        cudaMalloc(&kv->d_counters, sizeof(int) * counters) != cudaSuccess ||
+        cudaMemset(kv->d_counters, 0, sizeof(int) * counters) != cudaSuccess)
+        return bail(fail(ER_ERR_ALLOCATION_FAILED, "scratch"));
+    if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cache initialisation"));
+    *out = kv;
+    return ER_OK;
+}
+
+void er_kv_destroy(er_kv* kv) {
+    if (!kv) return;
+    cudaFree(kv->k_slab); cudaFree(kv->v_slab); cudaFree(kv->kn_slab); cudaFree(kv->vn_slab);
+    cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
+    cudaFree(kv->d_stage);
+    cudaGetLastError();
+    delete kv;
+}
+
+int32_t er_kv_get_config(const er_kv* kv, er_kv_config* out) {
+    if (!kv || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    *out = kv->cfg;
+    return ER_OK;
+}
+
+int32_t er_kv_current_length(er_kv* kv) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int32_t best = 0;
+    for (int32_t n : kv->h_lengths) best = std::max(best, std::min<int32_t>(n, static_cast<int32_t>(kv->cfg.max_seq_len)));
+    return best;
+}
+
+int64_t er_kv_total_written(er_kv* kv, uint32_t layer, uint32_t seq) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    return kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq];
+}
+
+int32_t er_kv_cache_params(er_kv* kv, uint32_t layer, uint32_t seq, ERKVCacheParams* out) {
+    if (!kv || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    const int32_t total = kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq];
+    out->maxSeqLen = kv->cfg.max_seq_len;
+    out->currentLen = static_cast<uint32_t>(std::min<int64_t>(total, kv->cfg.max_seq_len));
+    out->writePos = static_cast<uint32_t>(total % static_cast<int32_t>(kv->cfg.max_seq_len));
+    out->numKVHeads = kv->cfg.num_kv_heads;
+    out->headDim = kv->cfg.head_dim;
+    out->precision = kv->cfg.precision;
+    return ER_OK;
+}
+
+int32_t er_kv_reset(er_kv* kv) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    std::fill(kv->h_lengths.begin(), kv->h_lengths.end(), 0);
+    return push_lengths(kv);
+}
+
+int32_t er_kv_advance_write_position(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t count) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    for (uint32_t s = 0; s < kv->cfg.max_batch; ++s)
+        if (seq == UINT32_MAX || seq == s) kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + s] += static_cast<int32_t>(count);
+    return push_lengths(kv);
+}
+
+int32_t er_kv_set_position(er_kv* kv, uint32_t seq, uint32_t position) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    for (uint32_t l = 0; l < kv->cfg.num_layers; ++l)
+        for (uint32_t s = 0; s < kv->cfg.max_batch; ++s)
+            if (seq == UINT32_MAX || seq == s) kv->h_lengths[static_cast<size_t>(l) * kv->cfg.max_batch + s] = static_cast<int32_t>(position);
+    return push_lengths(kv);
+}
+
+int32_t er_kv_set_block_table(er_kv* kv, uint32_t seq, const int32_t* pages, uint32_t count) {
+    if (!kv || (!pages && count)) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (kv->pages_per_seq == 0) return fail(ER_ERR_UNSUPPORTED_STORAGE, "cache is not paged");
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (count > static_cast<uint32_t>(kv->pages_per_seq)) return fail(ER_ERR_SHAPE, "%u pages exceed the %d a sequence can hold", count, kv->pages_per_seq);
+    for (uint32_t i = 0; i < count; ++i)
+        if (pages[i] < 0 || pages[i] >= kv->pool_pages) return fail(ER_ERR_INVALID_ARGUMENT, "page id %d outside the pool of %d", pages[i], kv->pool_pages);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t* row = kv->h_block_table.data() + static_cast<size_t>(seq) * kv->pages_per_seq;
+    std::copy(pages, pages + count, row);
+    std::fill(row + count, row + kv->pages_per_seq, 0);
+    kv->h_block_count[seq] = count;
+    ER_CUDA(cudaMemcpy(kv->d_block_table + static_cast<size_t>(seq) * kv->pages_per_seq, row,
+                       sizeof(int32_t) * kv->pages_per_seq, cudaMemcpyHostToDevice));
+    return ER_OK;
+}
+
+int32_t er_kv_get_block_table(er_kv* kv, uint32_t seq, int32_t* pages, uint32_t capacity, uint32_t* count) {
+    if (!kv || !count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (kv->pages_per_seq == 0) return fail(ER_ERR_UNSUPPORTED_STORAGE, "cache is not paged");
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    *count = kv->h_block_count[seq];
+    for (uint32_t i = 0; i < std::min(capacity, *count); ++i) pages[i] = kv->h_block_table[static_cast<size_t>(seq) * kv->pages_per_seq + i];
+    return ER_OK;
+}
+
+int32_t er_kv_device_buffers(er_kv* kv, uint32_t layer, er_kv_buffers* out) {
+    if (!kv || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    out->keys = kv->k_slab + layer * kv->k_layer_stride;
+    out->values = kv->v_slab + layer * kv->v_layer_stride;
+    out->key_norms = kv->kn_slab ? kv->kn_slab + layer * kv->n_layer_stride : nullptr;
+    out->value_norms = kv->vn_slab ? kv->vn_slab + layer * kv->n_layer_stride : nullptr;
+    out->key_bytes = static_cast<uint64_t>(kv->k_layer_stride);
+    out->value_bytes = static_cast<uint64_t>(kv->v_layer_stride);
+    out->key_row_bytes = static_cast<uint32_t>(kv->k_row_bytes);
+    out->value_row_bytes = static_cast<uint32_t>(kv->v_row_bytes);
+    return ER_OK;
+}
+
+// ---- host-facing append / retrieve ----
+
+static int32_t host_append(er_kv* kv, uint32_t layer, uint32_t seq, const void* hk, const void* hv, size_t count,
+                           int src_elem_bytes) {
+    const size_t per_token = static_cast<size_t>(kv->cfg.num_kv_heads) * kv->cfg.head_dim;
+    if (count != per_token) return fail(ER_ERR_SHAPE, "expected %zu elements per token, got %zu", per_token, count);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int32_t& total = kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq];
+    const size_t bytes = per_token * src_elem_bytes;
+    rc = ensure_stage(kv, 2 * bytes);
+    if (rc != ER_OK) return rc;
+    ER_CUDA(cudaMemcpy(kv->d_stage, hk, bytes, cudaMemcpyHostToDevice));
+    ER_CUDA(cudaMemcpy(kv->d_stage + bytes, hv, bytes, cudaMemcpyHostToDevice));
+    if (kv->turbo) {
+        AppendParams ap{};
+        ap.k = reinterpret_cast<const float*>(kv->d_stage);
+        ap.v = reinterpret_cast<const float*>(kv->d_stage + bytes);
+        ap.bulk = 1; ap.fixed_layer = static_cast<int>(layer); ap.fixed_seq = static_cast<int>(seq);
+        ap.start_pos = total; ap.rows = 1; ap.batch = static_cast<int>(kv->cfg.max_batch);
+        ap.apply_rope = 0; ap.rope_scaling = 1.f;
+        rc = launch_append(kv, ap, nullptr);
+        if (rc != ER_OK) return rc;
+    } else {
+        const int slot = total % static_cast<int32_t>(kv->cfg.max_seq_len);
+        const KVAddressing a = kv->addressing();
+        scatter_row_kernel<<<4, 256>>>(kv->d_stage, kv->k_slab + layer * kv->k_layer_stride, a, static_cast<int>(seq), slot,
+                                       static_cast<int>(kv->cfg.head_dim), kv->elem_bytes);
+        if ((rc = check_launch("scatter_row_kernel")) != ER_OK) return rc;
+        scatter_row_kernel<<<4, 256>>>(kv->d_stage + bytes, kv->v_slab + layer * kv->v_layer_stride, a, static_cast<int>(seq), slot,
+                                       static_cast<int>(kv->cfg.head_dim), kv->elem_bytes);
+        if ((rc = check_launch("scatter_row_kernel")) != ER_OK) return rc;
+    }
+    total += 1;
+    rc = push_lengths(kv);
+    if (rc != ER_OK) return rc;
+    ER_CUDA(cudaDeviceSynchronize());
+    return ER_OK;
+}
+
+int32_t er_kv_append_f32(er_kv* kv, uint32_t layer, uint32_t seq, const float* hk, const float* hv, size_t count) {
+    if (!kv || !hk || !hv) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    // KVCache.append: float32 and TurboQuant precisions only; everything else is precisionMismatch (KVCache.swift:450-452).
+    if (kv->cfg.precision != ER_KV_FLOAT32 && !kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "append of Float rows into precision %u", kv->cfg.precision);
+    return host_append(kv, layer, seq, hk, hv, count, 4);
+}
+
+int32_t er_kv_append_f16(er_kv* kv, uint32_t layer, uint32_t seq, const uint16_t* hk, const uint16_t* hv, size_t count) {
+    if (!kv || !hk || !hv) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (kv->cfg.precision != ER_KV_FLOAT16) return fail(ER_ERR_PRECISION_MISMATCH, "appendF16 needs a float16 cache");
+    return host_append(kv, layer, seq, hk, hv, count, 2);
+}
+
+// Logical order of KVCache.orderedRowIndices (KVCache.swift:1130-1138).
+static void logical_window(const er_kv* kv, int32_t total, int& first_slot, int& tokens) {
+    const int32_t maxn = static_cast<int32_t>(kv->cfg.max_seq_len);
+    tokens = std::min(total, maxn);
+    first_slot = total <= maxn ? 0 : total % maxn;
+}
+
+int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element_bytes, void* hk, void* hv,
+                       size_t capacity, uint32_t* token_count) {
+    if (!kv || !token_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    // validateRequestedType (KVCache.swift:866-883)
+    if (kv->turbo) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "TurboQuant cache");
+    if (static_cast<int>(element_bytes) != kv->elem_bytes) return fail(ER_ERR_PRECISION_MISMATCH, "requested %u-byte elements from a %d-byte cache", element_bytes, kv->elem_bytes);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int first_slot, tokens;
+    logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
+    *token_count = static_cast<uint32_t>(tokens);
+    if (tokens == 0) return ER_OK;
+    const size_t elems = static_cast<size_t>(tokens) * kv->cfg.num_kv_heads * kv->cfg.head_dim;
+    if (!hk || !hv || capacity < elems) return fail(ER_ERR_SHAPE, "output capacity %zu < %zu elements", capacity, elems);
+    const size_t bytes = elems * kv->elem_bytes;
+    rc = ensure_stage(kv, 2 * bytes);
+    if (rc != ER_OK) return rc;
+    const KVAddressing a = kv->addressing();
+    const int blocks = static_cast<int>(std::min<size_t>((bytes + 255) / 256, 4096));
+    gather_rows_kernel<<<blocks, 256>>>(kv->k_slab + layer * kv->k_layer_stride, kv->d_stage, a, static_cast<int>(seq), first_slot, tokens, kv->k_row_bytes);
+    if ((rc = check_launch("gather_rows_kernel")) != ER_OK) return rc;
+    gather_rows_kernel<<<blocks, 256>>>(kv->v_slab + layer * kv->v_layer_stride, kv->d_stage + bytes, a, static_cast<int>(seq), first_slot, tokens, kv->v_row_bytes);
+    if ((rc = check_launch("gather_rows_kernel")) != ER_OK) return rc;
+    ER_CUDA(cudaMemcpy(hk, kv->d_stage, bytes, cudaMemcpyDeviceToHost));
+    ER_CUDA(cudaMemcpy(hv, kv->d_stage + bytes, bytes, cudaMemcpyDeviceToHost));
+    return ER_OK;
+}
+
+int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, int is_value, uint32_t* h_codes,
+                                       uint32_t* h_signs, uint32_t* h_mask, float* h_meta, size_t capacity_rows,
+                                       uint32_t* row_count) {
+    if (!kv || !row_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int first_slot, tokens;
+    logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
+    const size_t rows = static_cast<size_t>(tokens) * kv->cfg.num_kv_heads;
+    *row_count = static_cast<uint32_t>(rows);
+    if (rows == 0) return ER_OK;
+    if (capacity_rows < rows || !h_codes || !h_meta) return fail(ER_ERR_SHAPE, "output capacity %zu < %zu rows", capacity_rows, rows);
+    const int row_bytes = is_value ? kv->v_row_bytes : kv->k_row_bytes;
+    const size_t code_bytes = rows * row_bytes, norm_bytes = rows * kv->norm_bytes;
+    const size_t norm_off = (code_bytes + 255) & ~size_t(255);
+    const size_t meta_off = norm_off + ((norm_bytes + 255) & ~size_t(255));
+    rc = ensure_stage(kv, meta_off + rows * 8);
+    if (rc != ER_OK) return rc;
+    const KVAddressing a = kv->addressing();
+    const uint8_t* codes = (is_value ? kv->v_slab : kv->k_slab) + layer * (is_value ? kv->v_layer_stride : kv->k_layer_stride);
+    const uint8_t* norms = (is_value ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
+    const int blocks = static_cast<int>(std::min<size_t>((code_bytes + 255) / 256, 4096));
+    gather_rows_kernel<<<blocks, 256>>>(codes, kv->d_stage, a, static_cast<int>(seq), first_slot, tokens, row_bytes);
+    if ((rc = check_launch("gather_rows_kernel")) != ER_OK) return rc;
+    gather_rows_kernel<<<blocks, 256>>>(norms, kv->d_stage + norm_off, a, static_cast<int>(seq), first_slot, tokens, kv->norm_bytes);
+    if ((rc = check_launch("gather_rows_kernel")) != ER_OK) return rc;
+    float* d_meta = reinterpret_cast<float*>(kv->d_stage + meta_off);
+    widen_norms_kernel<<<static_cast<int>((rows + 255) / 256), 256>>>(kv->d_stage + norm_off, d_meta, static_cast<int>(rows), kv->norm_bytes == 2);
+    if ((rc = check_launch("widen_norms_kernel")) != ER_OK) return rc;
+    ER_CUDA(cudaMemcpy(h_codes, kv->d_stage, code_bytes, cudaMemcpyDeviceToHost));
+    ER_CUDA(cudaMemcpy(h_meta, d_meta, rows * 8, cudaMemcpyDeviceToHost));
+    if (h_signs) std::memset(h_signs, 0, rows * 16);
+    if (h_mask) std::memset(h_mask, 0, rows * 16);
+    return ER_OK;
+}
+
+int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t seq, float* hk, float* hv, size_t capacity,
+                                          uint32_t* token_count) {
+    if (!kv || !token_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int first_slot, tokens;
+    logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
+    *token_count = static_cast<uint32_t>(tokens);
+    if (tokens == 0) return ER_OK;
+    const size_t rows = static_cast<size_t>(tokens) * kv->cfg.num_kv_heads;
+    const size_t elems = rows * kHeadDim;
+    if (!hk || !hv || capacity < elems) return fail(ER_ERR_SHAPE, "output capacity %zu < %zu elements", capacity, elems);
+    rc = ensure_stage(kv, 2 * elems * 4);
+    if (rc != ER_OK) return rc;
+    TurboDecodeRowsParams dp;
+    dp.addr = kv->addressing();
+    dp.seq = static_cast<int>(seq); dp.first_slot = first_slot; dp.tokens = tokens;
+    dp.norm_fp16 = kv->norm_bytes == 2;
+    for (int is_v = 0; is_v < 2; ++is_v) {
+        dp.codes = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+        dp.norms = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
+        dp.out = reinterpret_cast<float*>(kv->d_stage) + is_v * elems;
+        rc = launch_turbo_decode_rows(dp, static_cast<int>(is_v ? kv->cfg.value_type : kv->cfg.key_type), nullptr, check_launch);
+        if (rc != ER_OK) return rc;
+    }
+    ER_CUDA(cudaMemcpy(hk, kv->d_stage, elems * 4, cudaMemcpyDeviceToHost));
+    ER_CUDA(cudaMemcpy(hv, kv->d_stage + elems * 4, elems * 4, cudaMemcpyDeviceToHost));
+    return ER_OK;
+}
+
+// ---- stand-alone operators ----
+
+static int32_t rope_common(const float* in, void* out, const ERRoPEParams* p, bool to_f16, void* stream) {
+    if (!in || !out || !p) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (p->headDim == 0 || p->headDim % 2 != 0 || p->headDim > 512) return fail(ER_ERR_SHAPE, "headDim %u (even, <= 512)", p->headDim);
+    if (!(p->theta > 0.f)) return fail(ER_ERR_INVALID_ARGUMENT, "theta must be > 0");
+    const uint64_t total = static_cast<uint64_t>(p->seqLen) * p->numHeads * (p->headDim / 2);
+    if (total == 0) return ER_OK;
+    WideInvFreqTable table;
+    fill_inv_freq(table, 256, p->theta, p->headDim);
+    const float scaling = p->scalingFactor == 0.f ? 1.f : p->scalingFactor;
+    const int blocks = static_cast<int>(std::min<uint64_t>((total + 255) / 256, 1u << 16));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (to_f16)
+        rope_neox_kernel<__half><<<blocks, 256, 0, s>>>(in, static_cast<__half*>(out), p->seqLen, p->numHeads, p->headDim, p->startPos, scaling, p->partialRotaryFactor, table);
+    else
+        rope_neox_kernel<float><<<blocks, 256, 0, s>>>(in, static_cast<float*>(out), p->seqLen, p->numHeads, p->headDim, p->startPos, scaling, p->partialRotaryFactor, table);
+    return check_launch("rope_neox_kernel");
+}
+
+int32_t er_rope_neox_f32(const float* in, float* out, const ERRoPEParams* p, void* stream) { return rope_common(in, out, p, false, stream); }
+int32_t er_rope_neox_f32_to_f16(const float* in, uint16_t* out, const ERRoPEParams* p, void* stream) { return rope_common(in, out, p, true, stream); }
+
+int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uint32_t source_row_stride, uint32_t dst_row_base,
+                                    uint32_t bits, uint32_t* out_codes, uint32_t* out_signs, uint32_t* out_mask, float* out_meta,
+                                    void* stream) {
+    if (!source || !out_codes || !out_meta) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (bits < 2 || bits > 4) return fail(ER_ERR_INVALID_ARGUMENT, "bits %u (fixed presets: 2, 3, 4)", bits);
+    if (source_row_stride < kHeadDim) return fail(ER_ERR_SHAPE, "source_row_stride %u < 128", source_row_stride);
+    if (row_count == 0) return ER_OK;
+    return launch_turbo_quantize_rows(source, row_count, source_row_stride, dst_row_base, static_cast<int>(bits), out_codes, out_signs,
+                                      out_mask, out_meta, static_cast<cudaStream_t>(stream), check_launch);
+}
+
+int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out, const ERGQAParams* gp, void* stream) {
+    if (!q || !k || !v || !out || !gp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (gp->headDim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "headDim %u: this backend's attention kernels are built for 128", gp->headDim);
+    if (gp->numKVHeads == 0 || gp->numHeads % gp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", gp->numHeads, gp->numKVHeads);
+    if (gp->numKVHeads > 16) return fail(ER_ERR_UNSUPPORTED, "numKVHeads %u > 16 for the raw-buffer operator", gp->numKVHeads);
+    const uint32_t kv_seq = gp->kvSeqLen > 0 ? gp->kvSeqLen : gp->seqLen;
+    if (gp->seqLen == 0 || kv_seq == 0) return ER_OK;
+    Workspace* ws = nullptr;
+    int32_t rc = get_workspace(&ws);
+    if (rc != ER_OK) return rc;
+    DecodeParams p{};
+    p.k_base = reinterpret_cast<const uint8_t*>(k);
+    p.v_base = reinterpret_cast<const uint8_t*>(v);
+    p.k_layer_stride_bytes = 0; p.v_layer_stride_bytes = 0;
+    p.lengths = nullptr;
+    p.layer_begin = 0; p.num_layers = 1; p.batch = 1;
+    p.num_q_heads = static_cast<int>(gp->numHeads);
+    p.pending = 0; p.advance = 0;
+    const float scale = gp->scale != 0.f ? gp->scale : 1.0f / std::sqrt(static_cast<float>(gp->headDim));
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.apply_rope = 0; p.rope_scaling = 1.f;
+    p.addr.token_major = 1; p.addr.num_kv_heads = static_cast<int>(gp->numKVHeads);
+    p.addr.max_seq_len = static_cast<int>(kv_seq); p.addr.page_size = static_cast<int>(kv_seq);
+    p.addr.pages_per_seq = 0; p.addr.block_table = nullptr;
+    p.scratch = ws->scratch; p.done_counter = ws->counters; p.status = ws->counters + 1; p.item_counters = ws->counters + 16;
+    const int group = static_cast<int>(gp->numHeads / gp->numKVHeads);
+    // One launch per query row: row r sees keys 0 .. r + qOffset (Shaders/GQA.metal:345).
+    for (uint32_t r = 0; r < gp->seqLen; ++r) {
+        uint64_t visible = gp->causal ? std::min<uint64_t>(kv_seq, static_cast<uint64_t>(r) + gp->qOffset + 1) : kv_seq;
+        p.fixed_kv_len = static_cast<int>(visible);
+        p.fixed_q_pos = 0;
+        p.q = q + static_cast<size_t>(r) * gp->numHeads * kHeadDim;
+        p.out = out + static_cast<size_t>(r) * gp->numHeads * kHeadDim;
+        rc = dispatch_decode_f16(group, p, ws->num_sms, static_cast<cudaStream_t>(stream));
+        if (rc != ER_OK) return rc;
+    }
+    return ER_OK;
+}
+
+// ---- cache-level device operators ----
+
+int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t lb, uint32_t le, const float* k, const float* v, const er_step_params* sp, void* stream) {
+    if (!kv || !k || !v) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rc = check_layers(kv, lb, le);
+    if (rc != ER_OK) return rc;
+    if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "device append is built for head_dim 128");
+    er_step_params s;
+    if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    AppendParams ap{};
+    ap.k = k; ap.v = v;
+    ap.lengths = kv->d_lengths;
+    ap.bulk = 0; ap.layer_begin = static_cast<int>(lb); ap.batch = static_cast<int>(kv->cfg.max_batch);
+    ap.rows = static_cast<int>((le - lb) * kv->cfg.max_batch);
+    ap.apply_rope = s.apply_rope ? 1 : 0; ap.rope_scaling = s.rope_scaling;
+    if (ap.apply_rope) ap.inv_freq = kv->freq(s.rope_theta);
+    return launch_append(kv, ap, static_cast<cudaStream_t>(stream));
+}
+
+int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start, uint32_t count, const float* k, const float* v,
+                         const er_step_params* sp, void* stream) {
+    if (!kv || !k || !v) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "device append is built for head_dim 128");
+    if (static_cast<uint64_t>(start) + count > kv->cfg.max_seq_len) return fail(ER_ERR_SHAPE, "rows [%u, %u) exceed max_seq_len %u", start, start + count, kv->cfg.max_seq_len);
+    er_step_params s;
+    int32_t rc = step_defaults(kv, sp, s);
+    if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    AppendParams ap{};
+    ap.k = k; ap.v = v;
+    ap.bulk = 1; ap.fixed_layer = static_cast<int>(layer); ap.fixed_seq = static_cast<int>(seq);
+    ap.start_pos = static_cast<int>(start); ap.rows = static_cast<int>(count); ap.batch = static_cast<int>(kv->cfg.max_batch);
+    ap.apply_rope = s.apply_rope ? 1 : 0; ap.rope_scaling = s.rope_scaling;
+    if (ap.apply_rope) ap.inv_freq = kv->freq(s.rope_theta);
+    rc = launch_append(kv, ap, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    set_min_length_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(kv->d_lengths + static_cast<size_t>(layer) * kv->cfg.max_batch + seq,
+                                                                          static_cast<int>(start + count));
+    return check_launch("set_min_length_kernel");
+}
+
+static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
+                                uint32_t advance, const er_step_params& s, cudaStream_t stream) {
+    if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "attention kernels are built for head_dim 128");
+    if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
+    if (kv->cfg.precision == ER_KV_FLOAT32) return fail(ER_ERR_UNSUPPORTED, "attention over a float32 cache is outside this backend's scope");
+    const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
+    // (layer, sequence) pairs are scheduled kMaxPairs at a time.
+    const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
+    if (kv->cfg.max_batch > static_cast<uint32_t>(kMaxPairs)) return fail(ER_ERR_UNSUPPORTED, "max_batch %u > %d", kv->cfg.max_batch, kMaxPairs);
+    for (uint32_t l0 = lb; l0 < le; l0 += layers_per_launch) {
+        const uint32_t l1 = std::min(le, l0 + layers_per_launch);
+        const size_t off = static_cast<size_t>(l0 - lb) * kv->cfg.max_batch * num_heads * kHeadDim;
+        int32_t rc;
+        DecodeParams p{};
+        p.q = q + off; p.out = out + off;
+        p.k_base = kv->k_slab; p.v_base = kv->v_slab;
+        p.k_layer_stride_bytes = kv->k_layer_stride; p.v_layer_stride_bytes = kv->v_layer_stride;
+        p.kn_base = kv->kn_slab; p.vn_base = kv->vn_slab; p.n_layer_stride_bytes = kv->n_layer_stride;
+        p.norm_fp16 = kv->norm_bytes == 2;
+        p.lengths = kv->d_lengths; p.layer_begin = static_cast<int>(l0); p.num_layers = static_cast<int>(l1 - l0);
+        p.batch = static_cast<int>(kv->cfg.max_batch); p.num_q_heads = static_cast<int>(num_heads);
+        p.pending = static_cast<int>(pending); p.advance = static_cast<int>(advance);
+        p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+        p.apply_rope = s.apply_rope ? 1 : 0; p.rope_scaling = s.rope_scaling;
+        if (p.apply_rope) p.inv_freq = kv->freq(s.rope_theta);
+        p.addr = kv->addressing();
+        p.scratch = kv->d_scratch; p.done_counter = kv->d_counters; p.status = kv->d_counters + 1; p.item_counters = kv->d_counters + 16;
+        if (kv->turbo)
+            rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
+                               group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type));
+        else
+            rc = dispatch_decode_f16(group, p, kv->num_sms, stream);
+        if (rc != ER_OK) return rc;
+    }
+    return ER_OK;
+}
+
+int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
+                               const er_step_params* sp, void* stream) {
+    if (!kv || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rc = check_layers(kv, lb, le);
+    if (rc != ER_OK) return rc;
+    er_step_params s;
+    if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    return attention_locked(kv, lb, le, q, out, num_heads, pending ? 1 : 0, 0, s, static_cast<cudaStream_t>(stream));
+}
+
+int32_t er_kv_advance(er_kv* kv, uint32_t lb, uint32_t le, uint32_t count, void* stream) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    int32_t rc = check_layers(kv, lb, le);
+    if (rc != ER_OK) return rc;
+    const int n = static_cast<int>((le - lb) * kv->cfg.max_batch);
+    add_lengths_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), n, static_cast<int>(count));
+    return check_launch("add_lengths_kernel");
+}
+
+int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, const float* k, const float* v, float* out,
+                          uint32_t num_heads, const er_step_params* sp, void* stream) {
+    if (!kv || !q || !k || !v || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rc = er_kv_append_rope_kv(kv, lb, le, k, v, sp, stream);
+    if (rc != ER_OK) return rc;
+    er_step_params s;
+    if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    // The attention launch of the last layer chunk commits the appended row (lengths += 1) when it drains.
+    const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
+    if (le - lb <= layers_per_launch)
+        return attention_locked(kv, lb, le, q, out, num_heads, 1, 1, s, static_cast<cudaStream_t>(stream));
+    rc = attention_locked(kv, lb, le, q, out, num_heads, 1, 0, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    const int n = static_cast<int>((le - lb) * kv->cfg.max_batch);
+    add_lengths_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), n, 1);
+    return check_launch("add_lengths_kernel");
+}
+
+int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float* hq, const float* hk, const float* hv, float* hout,
+                               uint32_t num_heads, const er_step_params* sp, void* stream) {
+    if (!kv || !hq || !hk || !hv || !hout) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rc = check_layers(kv, lb, le);
+    if (rc != ER_OK) return rc;
+    const size_t rows = static_cast<size_t>(le - lb) * kv->cfg.max_batch;
+    const size_t q_bytes = rows * num_heads * kv->cfg.head_dim * 4, kv_bytes = rows * kv->cfg.num_kv_heads * kv->cfg.head_dim * 4;
+    {
+        std::lock_guard<std::mutex> lock(kv->mu);
+        rc = ensure_stage(kv, 2 * q_bytes + 2 * kv_bytes);
+        if (rc != ER_OK) return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint8_t* dq = kv->d_stage; uint8_t* dk = dq + q_bytes; uint8_t* dv = dk + kv_bytes; uint8_t* dout = dv + kv_bytes;
+    ER_CUDA(cudaMemcpyAsync(dq, hq, q_bytes, cudaMemcpyHostToDevice, s));
+    ER_CUDA(cudaMemcpyAsync(dk, hk, kv_bytes, cudaMemcpyHostToDevice, s));
+    ER_CUDA(cudaMemcpyAsync(dv, hv, kv_bytes, cudaMemcpyHostToDevice, s));
+    rc = er_kv_decode_step(kv, lb, le, reinterpret_cast<const float*>(dq), reinterpret_cast<const float*>(dk), reinterpret_cast<const float*>(dv),
+                           reinterpret_cast<float*>(dout), num_heads, sp, stream);
+    if (rc != ER_OK) return rc;
+    ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
+    ER_CUDA(cudaStreamSynchronize(s));
+    return ER_OK;
+}
+
+int32_t er_kv_device_status(er_kv* kv) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    int status = 0;
+    ER_CUDA(cudaMemcpy(&status, kv->d_counters + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    return status;
+}
+
+}  // extern "C"

@@ -1,0 +1,513 @@
+// Persistent split-K GQA flash-decode over the KV cache (fp16 rows or TurboQuant codes).
+//
+// Replaces the decode use (seqLen == 1) of gqa_attention_f16kv (Shaders/GQA.metal:278-387), the attention
+// phase of fused_qk_norm_rope_gqa (Shaders/RoPE.metal:395-494) and gqa_attention_turboquant_decode
+// (Shaders/TurboQuant.metal:1794-2001); the split/merge arithmetic is the log-sum-exp merge of
+// gqa_decode_attention_packed_f16kv_reduce (Shaders/GQA.metal:753-776).
+//
+// Work decomposition.  An *item* is one (layer, sequence, kv head); its rows are cut into *units* of 16
+// tokens.  All units of the launch form one flat list that is divided evenly among the CTAs (one CTA per
+// SM), so every SM streams the same number of bytes however the sequence lengths are distributed.  A CTA
+// walks its contiguous unit range; when the range covers an item only partly the CTA writes an
+// un-normalised partial (max, sum, acc[128]) per q head to global scratch and the last CTA to arrive at
+// the item (an atomic counter, nobody waits) merges the partials and writes the output.
+//
+// Inside a CTA one producer warp stages tiles of up to 128 tokens (the rows of one kv head) into a
+// shared-memory ring with bulk asynchronous copies completing on mbarriers; 8 consumer warps each take one
+// 16-token unit of the tile, keep their own online-softmax state and are merged once per item.  All q
+// heads of the kv head (GROUP of them) share every staged byte, so each cache byte is read once.
+//
+// The storage format is a policy (DensePolicy below, TurboPolicy in flash_decode_turbo.cuh) providing the
+// stage layout, the copy issue, the Q register preparation and the per-unit arithmetic.
+#pragma once
+
+#include "er_common.cuh"
+
+namespace er {
+
+constexpr int kRowBytesF16 = kHeadDim * 2;                  // 256
+constexpr int kTileBytesF16 = kTileTokens * kRowBytesF16;   // 32 KiB per K or V tile
+
+struct DecodeParams {
+    const float* q;               // [layers][batch][num_q_heads][128]
+    float* out;                   // same shape
+    const uint8_t* k_base;        // first row of layer 0 (fp16 rows or packed codes)
+    const uint8_t* v_base;
+    int64_t k_layer_stride_bytes;
+    int64_t v_layer_stride_bytes;
+    const uint8_t* kn_base;       // TurboQuant: stored norms
+    const uint8_t* vn_base;
+    int64_t n_layer_stride_bytes;
+    int norm_fp16;
+    int32_t* lengths;             // device [total_layers][batch] tokens written; nullptr -> fixed_* below
+    int fixed_kv_len;
+    int fixed_q_pos;
+    int layer_begin;
+    int num_layers;               // layers covered by this launch
+    int batch;
+    int num_q_heads;
+    int pending;                  // rows appended but not yet committed to `lengths`
+    int advance;                  // added to lengths[...] by the last CTA to finish
+    float scale_log2;             // softmax scale * log2(e)
+    float rope_scaling;
+    int apply_rope;
+    KVAddressing addr;
+    float* scratch;               // [gridDim.x][2][GROUP][130]
+    int* item_counters;           // [pairs * kv heads], zero between launches
+    int* done_counter;            // zero between launches
+    int* status;
+    InvFreqTable inv_freq;
+};
+
+template <class POL>
+struct DecodeSmem {
+    static constexpr int G = POL::kGroup;
+    static constexpr int kOffPrefix = POL::kStages * POL::kStageBytes;
+    static constexpr int kOffMergeAcc = kOffPrefix + (kMaxPairs + 4) * 4;
+    static constexpr int kOffMergeML = kOffMergeAcc + kConsumerWarps * G * kHeadDim * 4;
+    static constexpr int kOffProb = kOffMergeML + kConsumerWarps * G * 2 * 4;
+    static constexpr int kOffCosSin = kOffProb + kConsumerWarps * G * kUnitTokens * 4;
+    static constexpr int kOffBars = kOffCosSin + 2 * kHalfDim * 8;
+    static constexpr int kOffFlags = kOffBars + 2 * POL::kStages * 8;
+    static constexpr int kOffExtra = (kOffFlags + 32 + 127) & ~127;
+    static constexpr int kTotal = kOffExtra + POL::kExtraBytes;
+};
+
+__device__ __forceinline__ int64_t cta_range_start(int cta, int64_t total_units, int active) {
+    return static_cast<int64_t>(cta) * total_units / active;
+}
+__device__ __forceinline__ int cta_of_unit(int64_t unit, int64_t total_units, int active) {
+    return static_cast<int>(((unit + 1) * active - 1) / total_units);
+}
+
+// One (possibly partial) item visit of a CTA: units [u0, u1) of an item that has `units` units.
+struct Segment {
+    int pair, head, u0, u1, units;
+    int64_t item_unit0;   // global index of the item's first unit
+};
+
+__device__ __forceinline__ Segment locate_segment(const int* prefix, int num_pairs, int hkv, int64_t cur,
+                                                  int64_t range_end) {
+    int lo = 0, hi = num_pairs;   // find the pair j with prefix[j]*hkv <= cur < prefix[j+1]*hkv
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (static_cast<int64_t>(prefix[mid]) * hkv <= cur) lo = mid; else hi = mid;
+    }
+    Segment s;
+    s.pair = lo;
+    s.units = prefix[lo + 1] - prefix[lo];
+    const int64_t rel = cur - static_cast<int64_t>(prefix[lo]) * hkv;
+    s.head = static_cast<int>(rel / s.units);
+    s.u0 = static_cast<int>(rel % s.units);
+    s.item_unit0 = cur - s.u0;
+    const int64_t left = range_end - cur;
+    s.u1 = (s.units - s.u0 <= left) ? s.units : s.u0 + static_cast<int>(left);
+    return s;
+}
+
+__device__ __forceinline__ int kv_length(const DecodeParams& p, int pair) {
+    if (p.lengths == nullptr) return p.fixed_kv_len;
+    const int layer = p.layer_begin + pair / p.batch, seq = pair % p.batch;
+    const int n = p.lengths[layer * p.batch + seq] + p.pending;
+    return n < p.addr.max_seq_len ? n : p.addr.max_seq_len;
+}
+
+// ------------------------------------------------------------------------------------------ dense fp16 policy
+
+template <int GROUP>
+struct DensePolicy {
+    static constexpr int kGroup = GROUP;
+    static constexpr int kStages = 3;
+    static constexpr int kStageBytes = 2 * kTileBytesF16;
+    static constexpr int kExtraBytes = 0;
+    static constexpr int kOffFin = 0;
+    static constexpr bool kRotated = false;
+    static constexpr int kQRegs = 16;   // per head: dims [8i,8i+8) then [64+8i,64+8i+8), i = lane % 8
+
+    __device__ static void init_extra(uint8_t*, int) {}
+
+    // Producer: K and V rows [t0, t0+ntok) of (layer, seq, head) -> stage.  Token-major storage needs one
+    // 256-byte copy per row; page-major storage one copy per touched page.
+    __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq,
+                                      int head, int t0, int ntok, int lane) {
+        const uint8_t* kl = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
+        const uint8_t* vl = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
+        __syncwarp();
+        if (p.addr.token_major) {
+            for (int c = lane; c < 2 * ntok; c += 32) {
+                const int is_v = c >= ntok;
+                const int r = is_v ? c - ntok : c;
+                const int64_t row = row_index(p.addr, seq, head, t0 + r);
+                bulk_g2s(stage + is_v * kTileBytesF16 + r * kRowBytesF16, (is_v ? vl : kl) + row * kRowBytesF16,
+                         kRowBytesF16, bar);
+            }
+        } else {
+            const int ps = p.addr.page_size;
+            const int first_page = t0 / ps;
+            const int nseg = (t0 + ntok - 1) / ps - first_page + 1;
+            for (int c = lane; c < 2 * nseg; c += 32) {
+                const int is_v = c & 1, sgi = c >> 1;
+                const int tb = max(t0, (first_page + sgi) * ps);
+                const int te = min(t0 + ntok, (first_page + sgi + 1) * ps);
+                const int64_t row = row_index(p.addr, seq, head, tb);
+                bulk_g2s(stage + is_v * kTileBytesF16 + (tb - t0) * kRowBytesF16, (is_v ? vl : kl) + row * kRowBytesF16,
+                         static_cast<uint32_t>(te - tb) * kRowBytesF16, bar);
+            }
+        }
+    }
+
+    // Consumers: per-lane Q registers, NeoX-rotated in registers when asked.
+    __device__ static void load_q(const DecodeParams& p, float (&q)[GROUP][kQRegs], const float* qrow, const float2* cs,
+                                  uint8_t*, int, int lane) {
+        const int i = lane & 7;
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            const float4* src = reinterpret_cast<const float4*>(qrow + g * kHeadDim + 8 * i);
+            const float4 a0 = __ldg(src), a1 = __ldg(src + 1), b0 = __ldg(src + 16), b1 = __ldg(src + 17);
+            const float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (p.apply_rope) {
+                    rope_rotate(xa[c], xb[c], cs[8 * i + c], q[g][c], q[g][8 + c]);
+                } else {
+                    q[g][c] = xa[c];
+                    q[g][8 + c] = xb[c];
+                }
+            }
+        }
+    }
+
+    // Scores, online softmax and P.V of one 16-token unit held in shared memory.
+    //   QK: lane (j = lane/8, i = lane%8) visits rows 4r+j, r = 0..3 -> two conflict-free 16-byte reads per
+    //       row; an 8-lane butterfly finishes the dot product.
+    //   PV: lane owns output dims [4*lane, 4*lane+4) and walks the 16 rows (one 8-byte read each).
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid,
+                                        const float (&q)[GROUP][kQRegs], float (&m)[GROUP], float (&l)[GROUP],
+                                        float (&acc)[GROUP][4], float* prob, const uint8_t*, int lane) {
+        const uint8_t* ks = stage + unit * kUnitTokens * kRowBytesF16;
+        const uint8_t* vs = stage + kTileBytesF16 + unit * kUnitTokens * kRowBytesF16;
+        const int j = lane >> 3, i = lane & 7;
+        float s[4][GROUP];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int row = 4 * r + j;
+            const uint4 ka = *reinterpret_cast<const uint4*>(ks + row * kRowBytesF16 + i * 16);
+            const uint4 kb = *reinterpret_cast<const uint4*>(ks + row * kRowBytesF16 + 128 + i * 16);
+            float fa[8], fb[8];
+            unpack8(ka, fa);
+            unpack8(kb, fb);
+#pragma unroll
+            for (int g = 0; g < GROUP; ++g) {
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    d0 = fmaf(q[g][c], fa[c], d0);
+                    d1 = fmaf(q[g][8 + c], fb[c], d1);
+                }
+                s[r][g] = d0 + d1;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int g = 0; g < GROUP; ++g) {
+                float v = s[r][g];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                s[r][g] = (4 * r + j < nvalid) ? v * p.scale_log2 : -INFINITY;
+            }
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            float mx = fmaxf(fmaxf(s[0][g], s[1][g]), fmaxf(s[2][g], s[3][g]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[g], mx);               // finite: the unit has at least one valid row
+            const float corr = fast_exp2(m[g] - m_new);        // m == -inf -> 0
+            float psum = 0.f;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float pr = fast_exp2(s[r][g] - m_new);   // masked rows -> 0
+                psum += pr;
+                if (i == 0) prob[g * kUnitTokens + 4 * r + j] = pr;
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+            l[g] = fmaf(l[g], corr, psum);
+            m[g] = m_new;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] *= corr;
+        }
+        __syncwarp();
+        const uint8_t* vrow = vs + lane * 8;
+        if (nvalid == kUnitTokens) {
+#pragma unroll
+            for (int t4 = 0; t4 < kUnitTokens; t4 += 4) {
+                float4 pg[GROUP];
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) pg[g] = *reinterpret_cast<const float4*>(prob + g * kUnitTokens + t4);
+#pragma unroll
+                for (int tt = 0; tt < 4; ++tt) {
+                    float vf[4];
+                    unpack4(*reinterpret_cast<const uint2*>(vrow + (t4 + tt) * kRowBytesF16), vf);
+#pragma unroll
+                    for (int g = 0; g < GROUP; ++g) {
+                        const float w = tt == 0 ? pg[g].x : tt == 1 ? pg[g].y : tt == 2 ? pg[g].z : pg[g].w;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[g][c] = fmaf(w, vf[c], acc[g][c]);
+                    }
+                }
+            }
+        } else {
+            for (int t = 0; t < nvalid; ++t) {   // rows past nvalid were never copied: do not touch them
+                float vf[4];
+                unpack4(*reinterpret_cast<const uint2*>(vrow + t * kRowBytesF16), vf);
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) {
+                    const float w = prob[g * kUnitTokens + t];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[g][c] = fmaf(w, vf[c], acc[g][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
+};
+
+// ------------------------------------------------------------------------------------------ the kernel
+
+template <class POL>
+__global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const __grid_constant__ DecodeParams p) {
+    using L = DecodeSmem<POL>;
+    constexpr int GROUP = POL::kGroup;
+    constexpr int kStages = POL::kStages;
+    extern __shared__ __align__(128) uint8_t smem[];
+    int* prefix = reinterpret_cast<int*>(smem + L::kOffPrefix);
+    float* merge_acc = reinterpret_cast<float*>(smem + L::kOffMergeAcc);
+    float* merge_ml = reinterpret_cast<float*>(smem + L::kOffMergeML);
+    float* prob_all = reinterpret_cast<float*>(smem + L::kOffProb);
+    float2* cos_sin = reinterpret_cast<float2*>(smem + L::kOffCosSin);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+    uint64_t* empty_bar = full_bar + kStages;
+    volatile int* flags = reinterpret_cast<volatile int*>(smem + L::kOffFlags);   // [0] abort [1] item-last [2] grid-last
+    uint8_t* extra = smem + L::kOffExtra;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hkv = p.addr.num_kv_heads;
+    const int num_pairs = p.num_layers * p.batch;
+
+    if (tid == 0) {
+        flags[0] = 0; flags[1] = 0; flags[2] = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kConsumerWarps);
+        }
+        mbar_init_fence();
+    }
+    POL::init_extra(extra, tid);
+    // ---- unit prefix over (layer, sequence) pairs, built by warp 0 ----
+    if (warp == 0) {
+        const int per_lane = (num_pairs + 31) / 32;
+        const int begin = lane * per_lane;
+        int sum = 0;
+        for (int k = 0; k < per_lane; ++k) {
+            const int j = begin + k;
+            if (j < num_pairs) sum += (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+        }
+        int incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        int run = incl - sum;
+        for (int k = 0; k < per_lane; ++k) {
+            const int j = begin + k;
+            if (j < num_pairs) {
+                prefix[j] = run;
+                run += (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+            }
+        }
+        if (lane == 31) prefix[num_pairs] = incl;
+    }
+    __syncthreads();
+
+    const int64_t total_units = static_cast<int64_t>(prefix[num_pairs]) * hkv;
+    int active = static_cast<int>(min(static_cast<int64_t>(gridDim.x), (total_units + kConsumerWarps - 1) / kConsumerWarps));
+    const int cta = blockIdx.x;
+
+    // Sequences without any row produce a zero output row (invSum = 0 rule, Shaders/GQA.metal:379).
+    for (int j = cta; j < num_pairs; j += gridDim.x) {
+        if (prefix[j + 1] == prefix[j]) {
+            float* o = p.out + static_cast<int64_t>(j) * p.num_q_heads * kHeadDim;
+            for (int e = tid; e < p.num_q_heads * kHeadDim; e += blockDim.x) o[e] = 0.f;
+        }
+    }
+
+    if (cta < active && total_units > 0) {
+        const int64_t range_begin = cta_range_start(cta, total_units, active);
+        const int64_t range_end = cta_range_start(cta + 1, total_units, active);
+
+        if (warp == kConsumerWarps) {
+            // ================= producer warp =================
+            int k = 0;
+            int64_t cur = range_begin;
+            while (cur < range_end) {
+                const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
+                const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
+                const int kv_len = kv_length(p, sg.pair);
+                for (int tu = sg.u0; tu < sg.u1; tu += kConsumerWarps, ++k) {
+                    const int nun = min(kConsumerWarps, sg.u1 - tu);
+                    const int t0 = tu * kUnitTokens;
+                    const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
+                    const int s = k % kStages;
+                    if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status);
+                    POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane);
+                }
+                cur += sg.u1 - sg.u0;
+            }
+        } else {
+            // ================= consumer warps =================
+            float* prob = prob_all + warp * GROUP * kUnitTokens;
+            int k = 0, item_visit = 0;
+            int64_t cur = range_begin;
+            while (cur < range_end) {
+                const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
+                const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
+                const int kv_len = kv_length(p, sg.pair);
+                const int q_pos = (p.lengths == nullptr) ? p.fixed_q_pos : p.lengths[layer * p.batch + seq] + p.pending - 1;
+                float2* cs = cos_sin + (item_visit & 1) * kHalfDim;
+                ++item_visit;
+                if (p.apply_rope && tid < kHalfDim)
+                    cs[tid] = rope_cos_sin(static_cast<uint32_t>(q_pos), p.inv_freq.f[tid], p.rope_scaling);
+                consumer_sync();
+
+                float q[GROUP][POL::kQRegs], m[GROUP], l[GROUP], acc[GROUP][4];
+                const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
+                POL::load_q(p, q, qrow, cs, extra, warp, lane);
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) {
+                    m[g] = -INFINITY;
+                    l[g] = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
+                }
+
+                for (int tu = sg.u0; tu < sg.u1; tu += kConsumerWarps, ++k) {
+                    const int nun = min(kConsumerWarps, sg.u1 - tu);
+                    const int t0 = tu * kUnitTokens;
+                    const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
+                    const int s = k % kStages;
+                    mbar_wait(&full_bar[s], (k / kStages) & 1, &flags[0], p.status);
+                    if (warp < nun && !flags[0]) {
+                        const int nvalid = min(kUnitTokens, ntok - warp * kUnitTokens);
+                        POL::process_unit(p, smem + s * POL::kStageBytes, warp, nvalid, q, m, l, acc, prob, extra, lane);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                }
+
+                // ---- merge the 8 warps of this CTA ----
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) {
+                    if (lane == 0) {
+                        merge_ml[(warp * GROUP + g) * 2] = m[g];
+                        merge_ml[(warp * GROUP + g) * 2 + 1] = l[g];
+                    }
+                    *reinterpret_cast<float4*>(merge_acc + (warp * GROUP + g) * kHeadDim + 4 * lane) =
+                        make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+                }
+                consumer_sync();
+                const bool sole = (sg.u0 == 0 && sg.u1 == sg.units);
+                const int item = sg.pair * hkv + sg.head;
+                float* out_item = p.out + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
+                // Outputs of the rotated (TurboQuant) space pass through shared memory for the inverse transform.
+                float* fin = POL::kRotated ? reinterpret_cast<float*>(extra + POL::kOffFin) : out_item;
+                const int slot = (range_begin > sg.item_unit0) ? 0 : 1;
+                float* my_scratch = p.scratch + (static_cast<int64_t>(cta) * 2 + slot) * GROUP * 130;
+                for (int idx = tid; idx < GROUP * kHeadDim; idx += kConsumerWarps * 32) {
+                    const int g = idx >> 7, d = idx & 127;
+                    float M = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, merge_ml[(w * GROUP + g) * 2]);
+                    float Lsum = 0.f, A = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; ++w) {
+                        const float wgt = fast_exp2(merge_ml[(w * GROUP + g) * 2] - M);
+                        Lsum = fmaf(merge_ml[(w * GROUP + g) * 2 + 1], wgt, Lsum);
+                        A = fmaf(merge_acc[(w * GROUP + g) * kHeadDim + d], wgt, A);
+                    }
+                    if (sole) {
+                        fin[idx] = Lsum > 0.f ? A / Lsum : 0.f;
+                    } else {
+                        if (d == 0) {
+                            my_scratch[g * 130] = M;
+                            my_scratch[g * 130 + 1] = Lsum;
+                        }
+                        my_scratch[g * 130 + 2 + d] = A;
+                    }
+                }
+                bool wrote = sole;
+                if (!sole) {
+                    const int64_t item_end = sg.item_unit0 + sg.units;
+                    const int c_first = cta_of_unit(sg.item_unit0, total_units, active);
+                    const int c_last = cta_of_unit(item_end - 1, total_units, active);
+                    __threadfence();
+                    consumer_sync();
+                    if (tid == 0) {
+                        const int prev = atomicAdd(p.item_counters + item, 1);
+                        flags[1] = (prev == c_last - c_first) ? 1 : 0;
+                    }
+                    consumer_sync();
+                    if (flags[1]) {
+                        wrote = true;
+                        __threadfence();
+                        for (int idx = tid; idx < GROUP * kHeadDim; idx += kConsumerWarps * 32) {
+                            const int g = idx >> 7, d = idx & 127;
+                            float M = -INFINITY;
+                            for (int c = c_first; c <= c_last; ++c) {
+                                const int sl = (cta_range_start(c, total_units, active) > sg.item_unit0) ? 0 : 1;
+                                M = fmaxf(M, __ldcg(p.scratch + (static_cast<int64_t>(c) * 2 + sl) * GROUP * 130 + g * 130));
+                            }
+                            float Lsum = 0.f, A = 0.f;
+                            for (int c = c_first; c <= c_last; ++c) {
+                                const int sl = (cta_range_start(c, total_units, active) > sg.item_unit0) ? 0 : 1;
+                                const float* sc = p.scratch + (static_cast<int64_t>(c) * 2 + sl) * GROUP * 130 + g * 130;
+                                const float wgt = fast_exp2(__ldcg(sc) - M);
+                                Lsum = fmaf(__ldcg(sc + 1), wgt, Lsum);
+                                A = fmaf(__ldcg(sc + 2 + d), wgt, A);
+                            }
+                            fin[idx] = Lsum > 0.f ? A / Lsum : 0.f;
+                        }
+                        if (tid == 0) p.item_counters[item] = 0;
+                    }
+                }
+                if (POL::kRotated && wrote) {   // CTA-uniform condition
+                    consumer_sync();
+                    POL::store_out(out_item, fin, warp, lane);
+                }
+                cur += sg.u1 - sg.u0;
+            }
+        }
+    }
+
+    // ---- the last CTA to finish commits the new row: lengths += advance ----
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const int prev = atomicAdd(p.done_counter, 1);
+        flags[2] = (prev == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (flags[2]) {
+        if (p.advance != 0 && p.lengths != nullptr)
+            for (int e = tid; e < num_pairs; e += blockDim.x) p.lengths[p.layer_begin * p.batch + e] += p.advance;
+        if (tid == 0) *p.done_counter = 0;
+    }
+}
+
+}  // namespace er

@@ -1,0 +1,27 @@
+// Launch entry points of the decode kernels, one translation unit per storage format so they compile in
+// parallel.  Return value: cudaSuccess (0), a cudaError_t from configuration or launch, or -1 when the
+// requested template combination is not built.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "flash_decode.cuh"
+
+namespace er {
+
+constexpr int kNotBuilt = -1;
+
+int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t stream);
+int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
+
+template <class POL>
+inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
+    constexpr int kSmem = DecodeSmem<POL>::kTotal;
+    static_assert(kSmem <= 232448, "decode kernel exceeds the 227 KiB shared-memory limit of an sm_100 CTA");
+    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<POL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    flash_decode_kernel<POL><<<grid, kDecodeThreads, kSmem, stream>>>(p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace er

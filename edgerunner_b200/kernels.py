@@ -1,0 +1,86 @@
+"""Stand-alone operator wrappers named after the reference's kernel holders:
+
+    RoPEKernel        Sources/EdgeRunnerMetal/RoPEKernel.swift:4-307     (execute / encodeNeoX)
+    GQAKernel         Sources/EdgeRunnerMetal/GQAKernel.swift:4-187      (execute / encode on fp16 K/V)
+    TurboQuantKernel  Sources/EdgeRunnerMetal/TurboQuantKernel.swift:13-112 (quantize rows)
+
+`encode*` methods enqueue on a stream with device buffers (the command-buffer style of the reference);
+`execute*` methods are the array-in / array-out convenience forms used by the reference's tests.
+"""
+import ctypes as C
+import math
+
+import numpy as np
+
+from ._lib import ERGQAParams, ERRoPEParams, check, lib, ptr, stream_ptr
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("edgerunner_b200 operators need a CUDA device (no CPU fallback)")
+    return torch
+
+
+class RoPEKernel:
+    def encode_neox(self, input_buffer, output_buffer, seq_len, num_heads, head_dim, start_pos=0, theta=10000.0,
+                    scaling_factor=1.0, partial_rotary_factor=1.0, to_f16=False, stream=None):
+        p = ERRoPEParams(seq_len, num_heads, head_dim, start_pos, theta, scaling_factor, partial_rotary_factor)
+        fn = lib().er_rope_neox_f32_to_f16 if to_f16 else lib().er_rope_neox_f32
+        check(fn(ptr(input_buffer), ptr(output_buffer), C.byref(p), stream_ptr(stream)))
+
+    def execute_neox(self, input, seq_len, num_heads, head_dim, start_pos=0, theta=10000.0, scaling_factor=1.0,
+                     partial_rotary_factor=1.0, to_f16=False):
+        torch = _torch()
+        x = torch.as_tensor(np.ascontiguousarray(input, dtype=np.float32)).cuda()
+        out = torch.empty(x.shape, dtype=torch.float16 if to_f16 else torch.float32, device="cuda")
+        self.encode_neox(x, out, seq_len, num_heads, head_dim, start_pos, theta, scaling_factor, partial_rotary_factor, to_f16)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
+
+class GQAKernel:
+    block_size = 16                 # GQAKernel.blockSize
+    max_optimized_head_dim = 128    # GQAKernel.maxOptimizedHeadDim
+
+    def encode(self, q_buffer, k_buffer, v_buffer, output_buffer, seq_len, head_dim, num_heads, num_kv_heads, causal,
+               kv_seq_len=0, q_offset=0, scale=None, stream=None):
+        """fp16 K/V variant (pipelineF16KV): q/out float32 [S,H,D], k/v float16 [T,Hkv,D] device buffers."""
+        p = ERGQAParams(seq_len, head_dim, num_heads, num_kv_heads, num_heads // num_kv_heads,
+                        (1.0 / math.sqrt(head_dim)) if scale is None else scale, int(bool(causal)), self.block_size,
+                        self.block_size, kv_seq_len, q_offset)
+        check(lib().er_gqa_attention_f16kv(ptr(q_buffer), ptr(k_buffer), ptr(v_buffer), ptr(output_buffer), C.byref(p),
+                                           stream_ptr(stream)))
+
+    def execute_f16kv(self, q, k, v, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len=0, q_offset=0):
+        torch = _torch()
+        qd = torch.as_tensor(np.ascontiguousarray(q, dtype=np.float32)).cuda()
+        kd = torch.as_tensor(np.ascontiguousarray(k, dtype=np.float16)).cuda()
+        vd = torch.as_tensor(np.ascontiguousarray(v, dtype=np.float16)).cuda()
+        out = torch.empty_like(qd)
+        self.encode(qd, kd, vd, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len, q_offset)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
+
+class TurboQuantKernel:
+    def encode_quantize_rows(self, source, row_count, source_row_stride, destination_row_base, bits, out_codes,
+                             out_residual_signs, out_outlier_mask, out_metadata, stream=None):
+        check(lib().er_turboquant_quantize_rows(ptr(source), row_count, source_row_stride, destination_row_base, bits,
+                                                ptr(out_codes), ptr(out_residual_signs), ptr(out_outlier_mask),
+                                                ptr(out_metadata), stream_ptr(stream)))
+
+    def execute_quantize_rows(self, rows, bits):
+        """rows: [n, >=128] float32 -> (codes [n,w] u32, signs [n,4], mask [n,4], meta [n,2])."""
+        torch = _torch()
+        x = torch.as_tensor(np.ascontiguousarray(rows, dtype=np.float32)).cuda()
+        n, stride = x.shape
+        w = (128 * bits + 31) // 32
+        codes = torch.full((n, w), -1, dtype=torch.int32, device="cuda")
+        signs = torch.full((n, 4), -1, dtype=torch.int32, device="cuda")
+        mask = torch.full((n, 4), -1, dtype=torch.int32, device="cuda")
+        meta = torch.full((n, 2), float("nan"), dtype=torch.float32, device="cuda")
+        self.encode_quantize_rows(x, n, stride, 0, bits, codes, signs, mask, meta)
+        torch.cuda.synchronize()
+        return (codes.cpu().numpy().view(np.uint32), signs.cpu().numpy().view(np.uint32),
+                mask.cpu().numpy().view(np.uint32), meta.cpu().numpy())

@@ -1,0 +1,276 @@
+/*
+ * er_kv.h -- C ABI of the B200 (sm_100a) backend for EdgeRunner's decode-time KV-cache path:
+ * append of RoPE'd K / V rows, optional TurboQuant compression, GQA flash-decode attention.
+ *
+ * This is the surface an `EdgeRunnerCUDA` Swift target binds through a module map in place of
+ * the EdgeRunnerMetal kernels.  Every entry point names the reference interface it replaces
+ * (paths relative to the reference checkout).  Plain C: opaque handle, pointers, sizes, status
+ * codes.  Unless stated otherwise `const float* ... /+device+/` arguments are device pointers and
+ * work is enqueued on the given `cudaStream_t` (passed as `void*`, NULL = legacy default stream)
+ * and returns without waiting; `host` arguments are ordinary host pointers and the call
+ * synchronises before returning.
+ *
+ * There is no CPU fallback anywhere behind this header: every compute entry point launches
+ * hand-written CUDA kernels and reports ER_ERR_CUDA if no device is usable.
+ */
+#ifndef ER_KV_H
+#define ER_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library itself is built with -fvisibility=hidden */
+#endif
+
+/* ---- parameter structs shared verbatim with the reference (field names and order are the interface) ---- */
+
+/* Sources/EdgeRunnerSharedTypes/include/KVCacheParams.h:12-19 */
+typedef struct {
+    uint32_t maxSeqLen;
+    uint32_t currentLen;
+    uint32_t writePos;
+    uint32_t numKVHeads;
+    uint32_t headDim;
+    uint32_t precision;
+} ERKVCacheParams;
+
+/* Sources/EdgeRunnerSharedTypes/include/AttentionParams.h:15-27 */
+typedef struct {
+    uint32_t seqLen;
+    uint32_t headDim;
+    uint32_t numHeads;
+    uint32_t numKVHeads;
+    uint32_t groupSize;
+    float scale;
+    uint32_t causal;
+    uint32_t kvBlockSize;
+    uint32_t qBlockSize;
+    uint32_t kvSeqLen; /* 0 = same as seqLen */
+    uint32_t qOffset;  /* key k is visible to query row r iff k <= r + qOffset */
+} ERGQAParams;
+
+/* Sources/EdgeRunnerSharedTypes/include/RoPEParams.h:6-21 */
+typedef struct {
+    uint32_t seqLen;
+    uint32_t numHeads;
+    uint32_t headDim;
+    uint32_t startPos;
+    float theta;
+    float scalingFactor;
+    float partialRotaryFactor;
+} ERRoPEParams;
+
+/* ---- status codes: 0 ok, negatives 1:1 with KVCacheError (Sources/EdgeRunnerMetal/KVCache.swift:1141-1148);
+ * shape preconditions that trap in the reference (KVCache.swift:413-414) are reported as ER_ERR_SHAPE. ---- */
+enum {
+    ER_OK = 0,
+    ER_ERR_ALLOCATION_FAILED = -1,
+    ER_ERR_INVALID_LAYER = -2,
+    ER_ERR_PRECISION_MISMATCH = -3,
+    ER_ERR_UNSUPPORTED_STORAGE = -4,
+    ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API = -5,
+    ER_ERR_COMPRESSED_BUFFER_ACCESS_REQUIRES_TURBOQUANT_API = -6,
+    ER_ERR_SHAPE = -7,
+    ER_ERR_CUDA = -8,
+    ER_ERR_INVALID_ARGUMENT = -9,
+    ER_ERR_OUT_OF_PAGES = -10,
+    ER_ERR_UNSUPPORTED = -11,
+    ER_ERR_DEVICE_TIMEOUT = -12 /* a bounded device-side wait gave up; see er_kv_device_status */
+};
+
+/* KVCache.Precision raw values (KVCache.swift:39-49). float8 / q8_0 / balanced / aggressive are accepted
+ * by er_kv_create only to report ER_ERR_UNSUPPORTED_STORAGE. */
+enum {
+    ER_KV_FLOAT32 = 0,
+    ER_KV_FLOAT16 = 1,
+    ER_KV_FLOAT8 = 2,
+    ER_KV_Q8_0 = 3,
+    ER_KV_TURBOQUANT_V2 = 4,
+    ER_KV_TURBOQUANT_BALANCED = 5,
+    ER_KV_TURBOQUANT_AGGRESSIVE = 6
+};
+
+/* TurboQuantFixedType (TurboQuant.swift:172-190): the value is the bit width of the preset. */
+enum { ER_TQ_TURBO2 = 2, ER_TQ_TURBO3 = 3, ER_TQ_TURBO4 = 4 };
+
+/* Storage layouts.  The reference has exactly one: a token-major ring per layer
+ * ([slot][kvHead][dim], KVCache.swift:357-370).  HEAD_MAJOR keeps each kv head's tokens contiguous
+ * ([seq][kvHead][slot][dim]) so a tile of tokens is one bulk copy; PAGED stores fixed-size pages
+ * ([page][kvHead][slotInPage][dim]) addressed through a per-sequence block table. */
+enum { ER_KV_LAYOUT_TOKEN_MAJOR = 0, ER_KV_LAYOUT_HEAD_MAJOR = 1, ER_KV_LAYOUT_PAGED = 2 };
+
+/* Stored per-row TurboQuant norm: the reference keeps two floats (rowNorm, residualNorm;
+ * KVCache.swift:1095-1096); the compact format keeps rowNorm as fp16 and drops the always-zero rest. */
+enum { ER_TQ_NORM_FLOAT32 = 0, ER_TQ_NORM_FLOAT16 = 1 };
+
+typedef struct {
+    uint32_t max_seq_len;   /* ring length per sequence (tokens) */
+    uint32_t num_layers;
+    uint32_t num_kv_heads;  /* heads held by THIS cache (a kv-head shard holds its slice only) */
+    uint32_t head_dim;
+    uint32_t precision;     /* ER_KV_* */
+    uint32_t key_type;      /* ER_TQ_* when precision == ER_KV_TURBOQUANT_V2 */
+    uint32_t value_type;
+    uint32_t norm_format;   /* ER_TQ_NORM_* */
+    uint32_t max_batch;     /* sequences held (the reference's cache is the max_batch == 1 case) */
+    uint32_t layout;        /* ER_KV_LAYOUT_* (TurboQuant storage ignores TOKEN_MAJOR and uses HEAD_MAJOR) */
+    uint32_t page_size;     /* tokens per page, multiple of 16 (PAGED only) */
+    uint32_t num_pages;     /* pages in the shared pool (PAGED only) */
+    uint32_t reserved[4];
+} er_kv_config;
+
+typedef struct er_kv er_kv;
+
+/* Raw device buffers of one layer; replaces KVCache.metalBuffers / turboQuantMetalBuffers
+ * (KVCache.swift:631-667).  Borrowed: valid until er_kv_destroy. */
+typedef struct {
+    void* keys;          /* dense: fp16/fp32 elements; TurboQuant: packed code words */
+    void* values;
+    void* key_norms;     /* TurboQuant only: one norm per row (format per config.norm_format) */
+    void* value_norms;
+    uint64_t key_bytes;
+    uint64_t value_bytes;
+    uint32_t key_row_bytes;   /* bytes of one (token, kv head) row */
+    uint32_t value_row_bytes;
+} er_kv_buffers;
+
+/* Decode-step controls. */
+typedef struct {
+    float rope_theta;      /* ERRoPEParams.theta */
+    float rope_scaling;    /* ERRoPEParams.scalingFactor (1.0 = none) */
+    float softmax_scale;   /* 0 -> 1/sqrt(head_dim) (GQAKernel.encode, GQAKernel.swift:134) */
+    uint32_t apply_rope;   /* 1: NeoX-rotate Q and K at the row's position inside the call */
+    uint32_t reserved[4];
+} er_step_params;
+
+const char* er_status_string(int32_t status);
+const char* er_last_error_string(void);              /* thread-local detail for the last failing call */
+int32_t er_device_count(void);
+
+/* ---- cache object: KVCache.init / deinit (KVCache.swift:192-275) ---- */
+int32_t er_kv_create(const er_kv_config* config, er_kv** out);
+void er_kv_destroy(er_kv* kv);
+int32_t er_kv_get_config(const er_kv* kv, er_kv_config* out);
+
+/* KVCache.currentLength (KVCache.swift:184-188): max over layers (and sequences) of min(totalWritten, maxSeqLen). */
+int32_t er_kv_current_length(er_kv* kv);
+/* Tokens written so far to (layer, seq), not clamped. */
+int64_t er_kv_total_written(er_kv* kv, uint32_t layer, uint32_t seq);
+
+/* KVCache.append(layer:keys:values:) (KVCache.swift:410-453): host float rows of numKVHeads*headDim elements,
+ * stored as float32, or TurboQuant-encoded on the device; advances the ring.  ER_ERR_PRECISION_MISMATCH for a
+ * float16 cache, exactly like the reference. */
+int32_t er_kv_append_f32(er_kv* kv, uint32_t layer, uint32_t seq, const float* host_keys, const float* host_values,
+                         size_t element_count);
+/* KVCache.appendF16 (KVCache.swift:455-476): fp16 bit patterns. */
+int32_t er_kv_append_f16(er_kv* kv, uint32_t layer, uint32_t seq, const uint16_t* host_keys,
+                         const uint16_t* host_values, size_t element_count);
+
+/* KVCache.retrieve(layer:asType:) (KVCache.swift:478-522): logical (oldest-first) order, [token][kvHead][dim].
+ * element_bytes is the requested element size (4 = Float, 2 = Float16); capacity_elements bounds the copy.
+ * *token_count receives the number of tokens returned. */
+int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element_bytes, void* host_keys,
+                       void* host_values, size_t capacity_elements, uint32_t* token_count);
+/* KVCache.retrieveDecodedTurboQuant (KVCache.swift:524-586): rows dequantised on the device. */
+int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t seq, float* host_keys,
+                                          float* host_values, size_t capacity_elements, uint32_t* token_count);
+/* KVCache.retrieveTurboQuantRuntimeRows (KVCache.swift:588-629) in the reference's split-buffer row format:
+ * codes [rows][words], residual signs [rows][4] (zero), outlier mask [rows][4] (zero), metadata [rows][2]
+ * (rowNorm, 0).  rows = tokens*numKVHeads in logical order, row = token*numKVHeads + kvHead. */
+int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, int is_value, uint32_t* host_codes,
+                                       uint32_t* host_residual_signs, uint32_t* host_outlier_mask,
+                                       float* host_metadata, size_t capacity_rows, uint32_t* row_count);
+
+/* KVCache.metalBuffers / turboQuantMetalBuffers (KVCache.swift:631-667). */
+int32_t er_kv_device_buffers(er_kv* kv, uint32_t layer, er_kv_buffers* out);
+/* KVCache.cacheParams (KVCache.swift:691-703). */
+int32_t er_kv_cache_params(er_kv* kv, uint32_t layer, uint32_t seq, ERKVCacheParams* out);
+/* KVCache.reset / advanceWritePosition / setPosition (KVCache.swift:705-729). seq == UINT32_MAX: all sequences. */
+int32_t er_kv_reset(er_kv* kv);
+int32_t er_kv_advance_write_position(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t count);
+int32_t er_kv_set_position(er_kv* kv, uint32_t seq, uint32_t position);
+
+/* Paged layout: install the block table of one sequence (page ids into the shared pool, one per page_size
+ * tokens).  The allocator that hands out page ids lives above this ABI (host side). */
+int32_t er_kv_set_block_table(er_kv* kv, uint32_t seq, const int32_t* host_page_ids, uint32_t page_count);
+int32_t er_kv_get_block_table(er_kv* kv, uint32_t seq, int32_t* host_page_ids, uint32_t capacity, uint32_t* page_count);
+
+/* ---- device-side operators ---- */
+
+/* RoPEKernel.encodeNeoX -> rope_neox_f32 (RoPEKernel.swift:240-260, Shaders/RoPE.metal:57-93).
+ * in/out: device [seqLen][numHeads][headDim] float; may alias. */
+int32_t er_rope_neox_f32(const float* in, float* out, const ERRoPEParams* params, void* stream);
+/* rope_neox_f32_to_f16 (Shaders/RoPE.metal:498-531): out is device fp16. */
+int32_t er_rope_neox_f32_to_f16(const float* in, uint16_t* out, const ERRoPEParams* params, void* stream);
+
+/* turboquant_quantize_rows for the fixed presets (Shaders/TurboQuant.metal:562-709; dispatched by
+ * encodeTurboQuantRows, Sources/EdgeRunner/Models/LlamaLanguageModel.swift:1754-1818).  source: device
+ * [row_count][source_row_stride] float (first 128 of each row are used); outputs are the reference's four
+ * split device buffers written at rows destination_row_base + i. */
+int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uint32_t source_row_stride,
+                                    uint32_t destination_row_base, uint32_t bits, uint32_t* out_codes,
+                                    uint32_t* out_residual_signs, uint32_t* out_outlier_mask, float* out_metadata,
+                                    void* stream);
+
+/* GQAKernel.encode on an fp16 K/V pair -> gqa_attention_f16kv (GQAKernel.swift:113-172, Shaders/GQA.metal:278-387).
+ * q/out: device [seqLen][numHeads][headDim] float; k/v: device [kvSeqLen][numKVHeads][headDim] fp16. */
+int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out,
+                               const ERGQAParams* params, void* stream);
+
+/* Append one new token per sequence to layers [layer_begin, layer_end): the three per-layer dispatches of the
+ * decode pass -- V row convert/quantise, K NeoX RoPE + convert/quantise -- at row position totalWritten
+ * (LlamaLanguageModel.swift:3649-3684, 3757-3825).  k, v: device [layers][max_batch][numKVHeads][headDim] float.
+ * Does not advance the write position. */
+int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* k, const float* v,
+                             const er_step_params* params, void* stream);
+
+/* Decode attention of one query row per sequence over rows [0, min(totalWritten + pending, maxSeqLen)) of each
+ * layer in [layer_begin, layer_end) -- gqa_attention_f16kv / gqa_attention_turboquant_decode with seqLen 1
+ * (LlamaLanguageModel.swift:3867-3881, 3924-3938; Shaders/TurboQuant.metal:1794-2001).  `pending` is 1 when the
+ * row just written by er_kv_append_rope_kv has not been committed by an advance yet, else 0.
+ * q, out: device [layers][max_batch][num_heads][headDim] float.  With params->apply_rope, Q is rotated at
+ * position totalWritten + pending - 1. */
+int32_t er_kv_attention_decode(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* q, float* out,
+                               uint32_t num_heads, uint32_t pending, const er_step_params* params, void* stream);
+
+/* Whole decode step for layers [layer_begin, layer_end): append + attention + advance of the write position by
+ * one, enqueued back to back (the body of fusedDecodePass steps 2-5, LlamaLanguageModel.swift:3649-3941).
+ * Positions live on the device, so a captured CUDA graph of this call can be replayed step after step. */
+int32_t er_kv_decode_step(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* q, const float* k,
+                          const float* v, float* out, uint32_t num_heads, const er_step_params* params, void* stream);
+
+/* Same step with HOST buffers (pinned or pageable): copies q/k/v in, runs the step, copies `out` back and
+ * waits.  This is the call a host-side model loop makes when its activations live in host memory. */
+int32_t er_kv_decode_step_host(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* host_q,
+                               const float* host_k, const float* host_v, float* host_out, uint32_t num_heads,
+                               const er_step_params* params, void* stream);
+
+/* Device advance of the write position of every sequence of layers [layer_begin, layer_end) by `count`. */
+int32_t er_kv_advance(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, uint32_t count, void* stream);
+
+/* Bulk load of already-positioned rows (prefill / test set-up): rows [start, start+count) of (layer, seq) from
+ * device float [count][numKVHeads][headDim]; K is NeoX-rotated at its row position when params->apply_rope.
+ * Sets totalWritten of (layer, seq) to max(totalWritten, start + count). */
+int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start, uint32_t count, const float* k,
+                         const float* v, const er_step_params* params, void* stream);
+
+/* Number of kernels this library has launched since load (all caches, this process). */
+uint64_t er_kernel_launch_count(void);
+/* Device status word of the cache: 0, or ER_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel expired. */
+int32_t er_kv_device_status(er_kv* kv);
+
+/* Pinned host memory helpers for callers without a CUDA runtime binding of their own. */
+int32_t er_host_alloc(void** out, size_t bytes);
+int32_t er_host_free(void* ptr);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ER_KV_H */

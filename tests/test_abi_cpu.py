@@ -1,0 +1,151 @@
+"""CPU-side checks of the product: the C-ABI library builds/loads and exports every symbol include/er_kv.h
+declares, error paths that need no device, the host-side block-table allocator and sharding arithmetic.
+No compute entry point is called here (there is no GPU in this environment and no CPU fallback in the library)."""
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def er():
+    import edgerunner_b200 as er
+    from edgerunner_b200 import build
+    build.build()
+    return er
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "er_kv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(er_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(er):
+    from edgerunner_b200 import _lib
+    declared = _declared_functions()
+    assert len(declared) >= 30
+    L = er.lib()
+    for name in declared:
+        assert hasattr(L, name), name
+    assert sorted(_lib.SYMBOLS) == declared          # the Python binding covers the whole header
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    exported = set(re.findall(r" T (er_[a-z0-9_]+)", out))
+    assert exported == set(declared)                 # and nothing else leaks out of the library
+
+
+def test_param_struct_layouts_match_reference_headers(er):
+    import ctypes as C
+    from edgerunner_b200 import _lib
+    # Sources/EdgeRunnerSharedTypes/include/{KVCacheParams,AttentionParams,RoPEParams}.h: plain uint32/float fields
+    assert C.sizeof(_lib.ERKVCacheParams) == 24 and C.sizeof(_lib.ERGQAParams) == 44 and C.sizeof(_lib.ERRoPEParams) == 28
+    assert [f[0] for f in _lib.ERGQAParams._fields_] == ["seqLen", "headDim", "numHeads", "numKVHeads", "groupSize", "scale",
+                                                         "causal", "kvBlockSize", "qBlockSize", "kvSeqLen", "qOffset"]
+    assert C.sizeof(_lib.er_kv_config) == 64
+
+
+def test_no_device_fails_loudly(er):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    assert er.lib().er_device_count() == 0
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        er.KVCache(16, 1, 2, 4, er.Precision.float32)
+    assert e.value.name == "cuda" and "no CPU fallback" in str(e.value)
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        er.KVCache(16, 1, 2, 128, er.Precision.q8_0)
+    assert e.value.name == "unsupportedStorage"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        er.KVCache(0, 1, 2, 128, er.Precision.float16)
+    assert e.value.name == "shape"
+    assert er.lib().er_status_string(-6) == b"compressedBufferAccessRequiresTurboQuantAPI"
+
+
+def test_tables_identical_in_oracle_and_product():
+    a = open(os.path.join(ROOT, "oracle", "er_tq_tables.h")).read().replace("ER_ORACLE_TQ_TABLES_H", "X")
+    b = open(os.path.join(ROOT, "edgerunner_b200", "csrc", "tq_tables.h")).read().replace("ER_CSRC_TQ_TABLES_H", "X")
+    assert a == b
+
+
+def test_product_never_touches_the_oracle():
+    pkg = os.path.join(ROOT, "edgerunner_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "er_oracle" not in text and "liber_oracle" not in text, f
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f
+
+
+def test_block_table_allocator(er):
+    a = er.BlockTableAllocator(10, 16, free_order=[3, 1, 4, 0, 5, 9, 2, 6, 8, 7])
+    assert a.pages_for(0) == 0 and a.pages_for(1) == 1 and a.pages_for(16) == 1 and a.pages_for(17) == 2
+    assert a.ensure("s0", 33) == [3, 1, 4]
+    assert a.ensure("s1", 16) == [0]
+    assert a.ensure("s0", 40) == [3, 1, 4] and a.ensure("s0", 49) == [3, 1, 4, 5]
+    assert a.free_pages == 5
+    with pytest.raises(er.OutOfPages):
+        a.ensure("s2", 16 * 6)
+    assert a.free_pages == 5 and a.block_table("s2") == []
+    a.release("s0")
+    assert a.free_pages == 9 and a.ensure("s2", 16 * 6) == [3, 1, 4, 5, 9, 2]
+    with pytest.raises(ValueError):
+        er.BlockTableAllocator(4, 24)
+    with pytest.raises(ValueError):
+        er.BlockTableAllocator(4, 16, free_order=[0, 1, 1, 2])
+
+
+def test_head_and_sequence_shards():
+    from edgerunner_b200.sharding import HeadShard, split_range
+    covered = []
+    for r in range(4):
+        s = HeadShard(32, 8, 4, r)
+        assert s.group == 4 and s.local_kv_heads == 2 and s.local_heads == 8
+        covered += list(range(s.q_begin, s.q_end))
+        assert s.q_begin == s.kv_begin * 4
+    assert covered == list(range(32))
+    with pytest.raises(ValueError):
+        HeadShard(32, 8, 3, 0)
+    parts = [split_range(10, 4, r) for r in range(4)]
+    assert parts == [(0, 3), (3, 6), (6, 8), (8, 10)]
+
+
+_GLOO_WORKER = r'''
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+from edgerunner_b200.sharding import HeadShard, all_gather_heads, max_over_ranks, split_range
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % sys.argv[2], rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+B, H, Hkv, D = 3, 8, 4, 128
+shard = HeadShard(H, Hkv, 2, rank)
+full = torch.arange(B * H * D, dtype=torch.float32).reshape(B, H, D)
+local = shard.slice_q(full).clone()              # stands in for this rank's attention output slice
+out = all_gather_heads(local)
+assert out.shape == full.shape and torch.equal(out, full), "gathered heads differ"
+assert max_over_ranks(1.0 + rank) == 2.0
+b0, b1 = split_range(5, 2, rank)                 # sequence sharding: disjoint cover, no exchange
+cover = [torch.zeros(5) for _ in range(2)]
+mine = torch.zeros(5); mine[b0:b1] = 1
+dist.all_gather(cover, mine)
+assert torch.equal(cover[0] + cover[1], torch.ones(5))
+dist.destroy_process_group()
+print("rank", rank, "ok")
+'''
+
+
+def test_all_gather_of_head_slices_gloo_world2(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_GLOO_WORKER)
+    port = str(29500 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True) for r in range(2)]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, o
+        assert "rank %d ok" % r in o

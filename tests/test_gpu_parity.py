@@ -1,0 +1,518 @@
+"""GPU parity tests: every check drives the CUDA kernels through the C ABI (edgerunner_b200 -> liber_kv.so) and
+compares with the CPU oracle on the same seeded inputs.
+
+Bars: bit-exact for cache contents, packed TurboQuant codes, norms stored as float32 and block-table gathers;
+2e-3 max relative error for attention outputs (fp32 accumulate), the bound named by the benchmark contract and
+by the reference's own fp16-KV test (Tests/EdgeRunnerMetalTests/GQATests.swift:431-433).
+"""
+import ctypes as C
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+
+from helpers import THETA_QWEN3, attention_err, max_rel_err, normal_f16, outlier_channels, rng_for
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_literals.json")))
+
+
+@pytest.fixture(scope="module")
+def er():
+    import edgerunner_b200 as er
+    assert er.lib().er_device_count() > 0
+    return er
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    return torch
+
+
+def dev(torch, a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+# --------------------------------------------------------------------------------------------- KVCache host surface
+
+def test_kvcache_literals_through_abi(er):
+    g = GOLD["kv_append_single_step"]
+    c = er.KVCache(g["max_seq_len"], g["num_layers"], g["num_kv_heads"], g["head_dim"], er.Precision.float32)
+    c.append(0, g["keys"], g["values"])
+    assert c.current_length == 1
+    k, v = c.retrieve(0, np.float32)
+    assert k.tolist() == g["keys"] and v.tolist() == g["values"]
+
+    g = GOLD["kv_wrap_around"]
+    for layout in (er.Layout.token_major, er.Layout.head_major):
+        c = er.KVCache(g["max_seq_len"], 1, g["num_kv_heads"], g["head_dim"], er.Precision.float32, layout=layout)
+        for i in range(4):
+            c.append(0, [i, i + 0.5], [i * 10, i * 10 + 5])
+        c.append(0, *g["final_append"])
+        assert c.current_length == 4
+        k, v = c.retrieve(0, np.float32)
+        for idx, val in g["keys_expect"].items():
+            assert k[int(idx)] == val
+        assert v.tolist() == [10, 15, 20, 25, 30, 35, 990, 995]
+        p = c.cache_params(0)
+        assert (p.maxSeqLen, p.currentLen, p.writePos, p.numKVHeads, p.headDim, p.precision) == (4, 4, 1, 1, 2, 0)
+
+    g = GOLD["kv_multi_layer"]
+    c = er.KVCache(g["max_seq_len"], g["num_layers"], g["num_kv_heads"], g["head_dim"], er.Precision.float32)
+    for layer, (k, v) in enumerate(g["appends"]):
+        c.append(layer, k, v)
+    assert c.retrieve(0, np.float32)[0].tolist() == g["keys0"] and c.retrieve(1, np.float32)[0].tolist() == g["keys1"]
+    c.reset()
+    assert c.current_length == 0
+
+    g = GOLD["kv_float16"]
+    c = er.KVCache(g["max_seq_len"], 1, g["num_kv_heads"], g["head_dim"], er.Precision.float16)
+    c.append_f16(0, g["keys"], g["values"])
+    k, v = c.retrieve(0, np.float16)
+    assert k.tolist() == g["keys"] and v.tolist() == g["values"]
+
+
+def test_kvcache_error_cases(er):
+    c = er.KVCache(8, 1, 1, 4, er.Precision.float16)
+    c.append_f16(0, [1, 2, 3, 4], [5, 6, 7, 8])
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # KVCacheTests.swift:177-197
+        c.retrieve(0, np.float32)
+    assert e.value.name == "precisionMismatch"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # KVCacheTests.swift:199-219
+        c.device_buffers(1)
+    assert e.value.name == "invalidLayer"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # Float rows into a float16 cache (KVCache.swift:450-452)
+        c.append(0, [1, 2, 3, 4], [5, 6, 7, 8])
+    assert e.value.name == "precisionMismatch"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # precondition(keys.count == layerElements) -> status, not a trap
+        c.append_f16(0, [1, 2, 3], [5, 6, 7])
+    assert e.value.name == "shape"
+    t = er.KVCache(8, 1, 1, 128, er.Precision.turboquantV2)
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # KVCacheTests.swift:242-265
+        t.metal_buffers(0)
+    assert e.value.name == "compressedBufferAccessRequiresTurboQuantAPI"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        t.retrieve(0, np.float32)
+    assert e.value.name == "compressedRetrieveRequiresDecodedAPI"
+    assert t.turboquant_buffers(0).key_row_bytes == 48
+    for prec in (er.Precision.float8, er.Precision.q8_0, er.Precision.turboQuantAggressive):
+        with pytest.raises(er.EdgeRunnerCUDAError) as e:
+            er.KVCache(8, 1, 1, 128, prec)
+        assert e.value.name == "unsupportedStorage"
+
+
+def test_set_position_and_advance(er):
+    c = er.KVCache(16, 3, 1, 2, er.Precision.float32, max_batch=2)
+    c.set_position(5)
+    assert c.current_length == 5 and c.cache_params(2, 1).writePos == 5
+    c.advance_write_position(1, 13, seq=0)
+    assert c.total_written(1, 0) == 18 and c.total_written(1, 1) == 5
+    p = c.cache_params(1, 0)
+    assert (p.currentLen, p.writePos) == (16, 2)
+    c.reset()
+    assert c.current_length == 0
+
+
+# --------------------------------------------------------------------------------------------- RoPE
+
+def test_rope_known_values_and_oracle(er, oracle):
+    g = GOLD["rope_known_values"]
+    rk = er.RoPEKernel()
+    out = rk.execute_neox(np.array(g["input"], dtype=np.float32), g["seq_len"], g["num_heads"], g["head_dim"],
+                          start_pos=0, theta=g["theta"]).ravel()
+    assert abs(out[0]) < 1e-5 and abs(out[1]) < 1e-5
+    assert abs(out[2] - math.cos(1.0)) < 1e-5 and abs(out[3] - math.sin(1.0)) < 1e-5
+
+    rng = rng_for(11)
+    x = rng.standard_normal((7, 5, 128), dtype=np.float32)
+    for theta, start, scaling, partial in ((1e6, 4090, 1.0, 1.0), (1e4, 0, 2.0, 0.25), (5e5, 131000, 1.0, 1.0)):
+        want = oracle.rope_neox(x, start, theta, scaling, partial)
+        got = rk.execute_neox(x, 7, 5, 128, start, theta, scaling, partial)
+        assert np.array_equal(got.reshape(want.shape), want), (theta, start)
+        want16 = oracle.rope_neox_to_f16(x, start, theta, scaling, partial)
+        got16 = rk.execute_neox(x, 7, 5, 128, start, theta, scaling, partial, to_f16=True)
+        assert np.array_equal(got16.view(np.uint16).reshape(want16.shape), want16)
+    x = rng.standard_normal((3, 2, 64), dtype=np.float32)       # another head_dim
+    assert np.array_equal(rk.execute_neox(x, 3, 2, 64, 17, 1e4).reshape(x.shape), oracle.rope_neox(x, 17, 1e4))
+
+
+# --------------------------------------------------------------------------------------------- TurboQuant quantiser
+
+def _signal(phase):
+    # TurboQuantAttentionTests.swift:1472-1477
+    x = np.arange(128, dtype=np.float32)
+    return (np.sin(x * np.float32(0.15) + np.float32(phase)) + np.float32(0.35) * np.cos(x * np.float32(0.05) - np.float32(phase))).astype(np.float32)
+
+
+def _quantizer_inputs():
+    rng = rng_for(21)
+    rows = [rng.standard_normal((600, 128), dtype=np.float32)]
+    rows.append(normal_f16(rng, (300, 128)) * outlier_channels(rng, 128, 0.05))
+    rows.append(np.stack([_signal(0.1 * i) for i in range(64)]))
+    special = np.zeros((8, 128), dtype=np.float32)
+    special[1, 5] = 3.0
+    special[2] = 1e-20
+    special[3] = 1e18
+    special[4, :] = -2.5
+    special[5, ::2] = 1.0
+    special[6] = np.float32(np.nan)
+    special[7, 0] = np.float32(np.inf)
+    rows.append(special)
+    return np.concatenate(rows).astype(np.float32)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_quantize_rows_bit_exact(er, oracle, bits):
+    x = _quantizer_inputs()
+    codes, signs, mask, meta = er.TurboQuantKernel().execute_quantize_rows(x, bits)
+    want_codes, want_norm = oracle.tq_encode_rows(x, bits)
+    assert np.array_equal(codes, want_codes)                       # codes ==   (TurboQuantAttentionTests.swift:760)
+    assert not signs.any() and not mask.any()                      # mask / signs ==
+    finite = np.isfinite(want_norm)
+    assert np.array_equal(meta[finite, 0].view(np.uint32), want_norm[finite].view(np.uint32))   # rowNorm (< 1e-5 there)
+    assert np.array_equal(np.isnan(meta[:, 0]), np.isnan(want_norm))
+    assert not meta[:, 1].any()                                    # residualNorm == 0
+
+
+def test_quantize_rows_stride_and_base(er, oracle, torch):
+    rng = rng_for(22)
+    x = rng.standard_normal((37, 160), dtype=np.float32)           # source_row_stride 160 > 128
+    base = 5
+    codes = torch.zeros((64, 16), dtype=torch.int32, device="cuda")
+    meta = torch.zeros((64, 2), dtype=torch.float32, device="cuda")
+    signs = torch.ones((64, 4), dtype=torch.int32, device="cuda")
+    mask = torch.ones((64, 4), dtype=torch.int32, device="cuda")
+    er.TurboQuantKernel().encode_quantize_rows(dev(torch, x), 37, 160, base, 4, codes, signs, mask, meta)
+    torch.cuda.synchronize()
+    want_codes, want_norm = oracle.tq_encode_rows(x[:, :128], 4)
+    got = codes.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got[base:base + 37], want_codes) and not got[:base].any() and not got[base + 37:].any()
+    assert np.array_equal(meta.cpu().numpy()[base:base + 37, 0], want_norm)
+    assert not signs.cpu().numpy()[base:base + 37].any() and signs.cpu().numpy()[:base].all()
+
+
+# --------------------------------------------------------------------------------------------- dense decode
+
+def _oracle_dense_cache(oracle, K, V, theta):
+    """K, V: [T, Hkv, D] float32 -> fp16 caches [T, Hkv, D] with K NeoX-rotated at its row position."""
+    T = K.shape[0]
+    kc = np.empty(K.shape, dtype=np.uint16)
+    for t in range(T):
+        kc[t] = oracle.rope_neox_to_f16(K[t:t + 1], t, theta)[0]
+    return kc, oracle.f32_to_f16_bits(V)
+
+
+def _run_dense_config(er, oracle, torch, layout, L, B, Hq, Hkv, ctx, steps, seed, theta=THETA_QWEN3, page_size=0,
+                      ragged=False, max_seq_len=None):
+    D = 128
+    rng = rng_for(seed)
+    lens = [ctx] * B if not ragged else [int(x) for x in rng.integers(max(1, ctx // 8), ctx + 1, size=B)]
+    max_len = max(lens) + steps
+    T = max_seq_len or ((max_len + 15) // 16 * 16)
+    kw = {}
+    alloc = None
+    if layout == er.Layout.paged:
+        pages_per_seq = (T + page_size - 1) // page_size
+        num_pages = pages_per_seq * B + 3
+        kw = dict(page_size=page_size, num_pages=num_pages)
+        alloc = er.BlockTableAllocator(num_pages, page_size, free_order=rng.permutation(num_pages))
+    cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, **kw)
+    if alloc:
+        for b in range(B):
+            cache.set_block_table(b, alloc.ensure(b, lens[b] + steps))
+            assert cache.get_block_table(b) == alloc.block_table(b)
+    sp = er.step_params(rope_theta=theta)
+    okc = [[None] * B for _ in range(L)]
+    ovc = [[None] * B for _ in range(L)]
+    for l in range(L):
+        for b in range(B):
+            K = normal_f16(rng, (lens[b], Hkv, D))
+            V = normal_f16(rng, (lens[b], Hkv, D))
+            cache.write_rows(l, b, 0, lens[b], dev(torch, K), dev(torch, V), sp)
+            kc, vc = _oracle_dense_cache(oracle, K, V, theta)
+            okc[l][b] = np.concatenate([kc, np.zeros((steps, Hkv, D), np.uint16)])
+            ovc[l][b] = np.concatenate([vc, np.zeros((steps, Hkv, D), np.uint16)])
+    torch.cuda.synchronize()
+    worst = 0.0
+    for s in range(steps):
+        q = normal_f16(rng, (L, B, Hq, D))
+        k = normal_f16(rng, (L, B, Hkv, D))
+        v = normal_f16(rng, (L, B, Hkv, D))
+        out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        got = out.cpu().numpy()
+        for l in range(L):
+            for b in range(B):
+                want, _ = oracle.decode_step_f16(q[l, b], k[l, b], v[l, b], okc[l][b], ovc[l][b], lens[b] + s, theta, threads=8)
+                worst = max(worst, max_rel_err(got[l, b], want))
+                assert attention_err(got[l, b], want) < TOL
+    assert worst < TOL, worst
+    # cache contents, read back in logical order through the ABI, are bit-identical to the oracle's
+    for l in range(L):
+        for b in range(B):
+            n = lens[b] + steps
+            assert cache.total_written(l, b) == n
+            gk, gv = cache.retrieve(l, np.float16, seq=b)
+            assert np.array_equal(gk.view(np.uint16), okc[l][b][:n].ravel())
+            assert np.array_equal(gv.view(np.uint16), ovc[l][b][:n].ravel())
+    return worst
+
+
+def test_config0_single_layer_decode(er, oracle, torch):
+    """Configuration 0: Qwen3-0.6B-shaped layer, 16 q heads / 8 kv heads / head_dim 128, fp16 cache pre-filled with
+    512 tokens, append 1 token, RoPE theta 1e6 at positions 0..512, output fp32 [16,128]."""
+    for layout in (er.Layout.head_major, er.Layout.token_major):
+        worst = _run_dense_config(er, oracle, torch, layout, L=1, B=1, Hq=16, Hkv=8, ctx=512, steps=1, seed=0)
+        print("config0 %s max rel err %.3e" % (layout.name, worst))
+
+
+def test_config0_against_committed_golden(er, oracle, torch):
+    """Same configuration against the committed fixture (tests/golden/config0_expected.npz, generated by
+    tests/golden/make_config0.py from the oracle)."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "config0_expected.npz")
+    gold = np.load(path)
+    from golden.make_config0 import config0_inputs
+    Q, K, V = config0_inputs()
+    cache = er.KVCache(1024, 1, 8, 128, er.Precision.float16)
+    sp = er.step_params(rope_theta=THETA_QWEN3)
+    cache.write_rows(0, 0, 0, 512, dev(torch, K[:512]), dev(torch, V[:512]), sp)
+    out = torch.empty((16, 128), dtype=torch.float32, device="cuda")
+    cache.decode_step(dev(torch, Q), dev(torch, K[512]), dev(torch, V[512]), out, 16, sp)
+    torch.cuda.synchronize()
+    assert max_rel_err(out.cpu().numpy(), gold["out"]) < TOL
+    gk, gv = cache.retrieve(0, np.float16)
+    assert np.array_equal(gk.view(np.uint16).reshape(513, 8, 128)[[0, 1, 255, 511, 512]], gold["k_rows"])
+    assert np.array_equal(gv.view(np.uint16).reshape(513, 8, 128)[[0, 1, 255, 511, 512]], gold["v_rows"])
+
+
+def test_multilayer_steps_all_layouts(er, oracle, torch):
+    """Configuration-1-shaped (several independent layers, consecutive decode steps) at a size the oracle finishes
+    quickly, in every storage layout; odd context so tiles end ragged."""
+    for layout, ps in ((er.Layout.head_major, 0), (er.Layout.token_major, 0), (er.Layout.paged, 16), (er.Layout.paged, 64)):
+        _run_dense_config(er, oracle, torch, layout, L=3, B=1, Hq=16, Hkv=8, ctx=777, steps=3, seed=3, page_size=ps)
+
+
+def test_batched_ragged_paged_llama_shape(er, oracle, torch):
+    """Configuration-3-shaped: 32 q heads / 8 kv heads (group 4), 16-token pages, block tables a seeded random
+    permutation of a shared pool, ragged context lengths."""
+    _run_dense_config(er, oracle, torch, er.Layout.paged, L=2, B=5, Hq=32, Hkv=8, ctx=1500, steps=2, seed=2,
+                      theta=5e5, page_size=16, ragged=True)
+
+
+def test_group1_and_tiny_contexts(er, oracle, torch):
+    _run_dense_config(er, oracle, torch, er.Layout.head_major, L=1, B=3, Hq=4, Hkv=4, ctx=40, steps=2, seed=5, ragged=True)
+    _run_dense_config(er, oracle, torch, er.Layout.token_major, L=2, B=2, Hq=8, Hkv=2, ctx=1, steps=18, seed=6)
+
+
+def test_ring_wrap_decode(er, oracle, torch):
+    """More decode steps than ring slots: new rows overwrite the oldest slots and attention covers the whole ring
+    (reads ignore the wrap: softmax is order-independent and K carries its absolute RoPE position)."""
+    D, Hq, Hkv, T = 128, 4, 2, 32
+    rng = rng_for(9)
+    cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16)
+    sp = er.step_params(rope_theta=1e4)
+    kc = np.zeros((T, Hkv, D), np.uint16)
+    vc = np.zeros((T, Hkv, D), np.uint16)
+    for s in range(T + 9):
+        q, k, v = normal_f16(rng, (Hq, D)), normal_f16(rng, (Hkv, D)), normal_f16(rng, (Hkv, D))
+        out = torch.empty((Hq, D), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        slot = s % T
+        q_rot = oracle.rope_neox(q[None], s, 1e4)[0]
+        kc[slot] = oracle.rope_neox_to_f16(k[None], s, 1e4)[0]
+        vc[slot] = oracle.f32_to_f16_bits(v)
+        n = min(s + 1, T)
+        want = oracle.gqa_f16kv(q_rot[None], kc[:n], vc[:n], causal=False)[0]
+        assert max_rel_err(out.cpu().numpy(), want) < TOL
+    p = cache.cache_params(0)
+    assert (p.currentLen, p.writePos) == (T, 9)
+    gk, _ = cache.retrieve(0, np.float16)          # logical order: oldest first
+    order = [(9 + i) % T for i in range(T)]
+    assert np.array_equal(gk.view(np.uint16).reshape(T, Hkv, D), kc[order])
+
+
+def test_append_then_attention_split_calls(er, oracle, torch):
+    """er_kv_append_rope_kv + er_kv_attention_decode(pending=1) + er_kv_advance == er_kv_decode_step."""
+    rng = rng_for(12)
+    L, B, Hq, Hkv, D, ctx = 2, 2, 8, 4, 128, 300
+    caches = [er.KVCache(512, L, Hkv, D, er.Precision.float16, max_batch=B) for _ in range(2)]
+    sp = er.step_params(rope_theta=1e6)
+    for l in range(L):
+        for b in range(B):
+            K, V = normal_f16(rng, (ctx, Hkv, D)), normal_f16(rng, (ctx, Hkv, D))
+            for c in caches:
+                c.write_rows(l, b, 0, ctx, dev(torch, K), dev(torch, V), sp)
+    q, k, v = (dev(torch, normal_f16(rng, (L, B, h, D))) for h in (Hq, Hkv, Hkv))
+    o1 = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
+    o2 = torch.empty_like(o1)
+    caches[0].decode_step(q, k, v, o1, Hq, sp)
+    caches[1].append_rope_kv(k, v, sp)
+    caches[1].attention_decode(q, o2, Hq, sp, pending=1)
+    caches[1].advance(1)
+    torch.cuda.synchronize()
+    assert torch.equal(o1, o2)
+    assert caches[0].total_written(1, 1) == caches[1].total_written(1, 1) == ctx + 1
+
+
+def test_decode_step_host_buffers(er, oracle, torch):
+    rng = rng_for(13)
+    L, B, Hq, Hkv, D, ctx = 2, 1, 16, 8, 128, 200
+    c1 = er.KVCache(256, L, Hkv, D, er.Precision.float16)
+    c2 = er.KVCache(256, L, Hkv, D, er.Precision.float16)
+    sp = er.step_params(rope_theta=1e6)
+    for l in range(L):
+        K, V = normal_f16(rng, (ctx, Hkv, D)), normal_f16(rng, (ctx, Hkv, D))
+        for c in (c1, c2):
+            c.write_rows(l, 0, 0, ctx, dev(torch, K), dev(torch, V), sp)
+    q, k, v = (normal_f16(rng, (L, B, h, D)) for h in (Hq, Hkv, Hkv))
+    out_d = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
+    c1.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out_d, Hq, sp)
+    hq, hk, hv = (torch.as_tensor(a).pin_memory() for a in (q, k, v))
+    hout = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
+    c2.decode_step_host(hq, hk, hv, hout, Hq, sp)
+    torch.cuda.synchronize()
+    assert torch.equal(out_d.cpu(), hout)
+
+
+def test_gqa_kernel_operator_matches_cpu_gqa(er, oracle):
+    """GQAKernel on raw fp16 K/V buffers (pipelineF16KV), prefill semantics: the reference's own test shape
+    (GQATests.swift:365-434: S=16, D=128, 8 q / 2 kv heads, causal, inputs in [-0.25, 0.25], |err| < 2e-3) plus
+    kvSeqLen != seqLen with a query offset (GQATests.swift:277-324)."""
+    rng = rng_for(31)
+    gk = er.GQAKernel()
+    S, D, H, Hkv = 16, 128, 8, 2
+    q = rng.uniform(-0.25, 0.25, (S, H, D)).astype(np.float32)
+    k = rng.uniform(-0.25, 0.25, (S, Hkv, D)).astype(np.float32)
+    v = rng.uniform(-0.25, 0.25, (S, Hkv, D)).astype(np.float32)
+    got = gk.execute_f16kv(q, k, v, S, D, H, Hkv, causal=True)
+    assert np.max(np.abs(got - oracle.gqa_f32(q, k, v, causal=True))) < GOLD["gqa_f16kv_tolerance"]["abs_tolerance"]
+    k16, v16 = k.astype(np.float16), v.astype(np.float16)
+    assert max_rel_err(got, oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=True)) < TOL
+    S, T, off = 3, 150, 147
+    q = normal_f16(rng, (S, H, D))
+    k16, v16 = normal_f16(rng, (T, Hkv, D)).astype(np.float16), normal_f16(rng, (T, Hkv, D)).astype(np.float16)
+    got = gk.execute_f16kv(q, k16, v16, S, D, H, Hkv, causal=True, kv_seq_len=T, q_offset=off)
+    want = oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=True, q_offset=off)
+    assert max_rel_err(got, want) < TOL
+    got = gk.execute_f16kv(q, k16, v16, S, D, H, Hkv, causal=False, kv_seq_len=T)
+    assert max_rel_err(got, oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=False)) < TOL
+
+
+# --------------------------------------------------------------------------------------------- TurboQuant cache + decode
+
+def _run_turbo_config(er, oracle, torch, L, B, Hq, Hkv, ctx, steps, seed, kbits, vbits, norm_format, layout, page_size=0,
+                      ragged=False, outliers=False, theta=THETA_QWEN3):
+    D = 128
+    rng = rng_for(seed)
+    lens = [ctx] * B if not ragged else [int(x) for x in rng.integers(max(1, ctx // 8), ctx + 1, size=B)]
+    T = (max(lens) + steps + 15) // 16 * 16
+    kw = {}
+    if layout == er.Layout.paged:
+        pages_per_seq = (T + page_size - 1) // page_size
+        num_pages = pages_per_seq * B + 2
+        kw = dict(page_size=page_size, num_pages=num_pages)
+        alloc = er.BlockTableAllocator(num_pages, page_size, free_order=rng.permutation(num_pages))
+    fp16_norm = norm_format == er.NormFormat.float16
+    cache = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=kbits, value_type=vbits, norm_format=norm_format,
+                       max_batch=B, layout=layout, **kw)
+    if layout == er.Layout.paged:
+        for b in range(B):
+            cache.set_block_table(b, alloc.ensure(b, lens[b] + steps))
+    sp = er.step_params(rope_theta=theta)
+    kscale = outlier_channels(rng, (Hkv, D)) if outliers else np.ones((Hkv, D), np.float32)
+    vscale = outlier_channels(rng, (Hkv, D)) if outliers else np.ones((Hkv, D), np.float32)
+    kwid, vwid = (128 * kbits + 31) // 32, (128 * vbits + 31) // 32
+    st = {}
+    round16 = (lambda a: a.astype(np.float16).astype(np.float32)) if fp16_norm else (lambda a: a)
+    for l in range(L):
+        for b in range(B):
+            n = lens[b]
+            K = (rng.standard_normal((n, Hkv, D), dtype=np.float32) * kscale).astype(np.float16).astype(np.float32)
+            V = (rng.standard_normal((n, Hkv, D), dtype=np.float32) * vscale).astype(np.float16).astype(np.float32)
+            cache.write_rows(l, b, 0, n, dev(torch, K), dev(torch, V), sp)
+            Kr = np.concatenate([oracle.rope_neox(K[t:t + 1], t, theta) for t in range(n)])
+            kc, kn = oracle.tq_encode_rows(Kr.reshape(-1, D), kbits)
+            vc, vn = oracle.tq_encode_rows(V.reshape(-1, D), vbits)
+            pad = steps * Hkv
+            st[l, b] = [np.concatenate([kc, np.zeros((pad, kwid), np.uint32)]), np.concatenate([round16(kn), np.zeros(pad, np.float32)]),
+                        np.concatenate([vc, np.zeros((pad, vwid), np.uint32)]), np.concatenate([round16(vn), np.zeros(pad, np.float32)])]
+    torch.cuda.synchronize()
+    worst = 0.0
+    for s in range(steps):
+        q = normal_f16(rng, (L, B, Hq, D))
+        k = (rng.standard_normal((L, B, Hkv, D), dtype=np.float32) * kscale).astype(np.float16).astype(np.float32)
+        v = (rng.standard_normal((L, B, Hkv, D), dtype=np.float32) * vscale).astype(np.float16).astype(np.float32)
+        out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        got = out.cpu().numpy()
+        for l in range(L):
+            for b in range(B):
+                kc, kn, vc, vn = st[l, b]
+                want = oracle.decode_step_turboquant(q[l, b], k[l, b], v[l, b], kc, kn, kbits, vc, vn, vbits, lens[b] + s,
+                                                     theta, norm_fp16=fp16_norm, threads=8)
+                worst = max(worst, max_rel_err(got[l, b], want))
+    assert worst < TOL, worst
+    # stored rows, exported in the reference's split-buffer format: codes and float32 norms bit-exact
+    for l in range(L):
+        for b in range(B):
+            n = (lens[b] + steps) * Hkv
+            (gkc, gks, gkm, gkmeta), (gvc, gvs, gvm, gvmeta) = cache.retrieve_turboquant_runtime_rows(l, seq=b)
+            kc, kn, vc, vn = st[l, b]
+            assert np.array_equal(gkc, kc[:n]) and np.array_equal(gvc, vc[:n])
+            assert np.array_equal(gkmeta[:, 0], kn[:n]) and np.array_equal(gvmeta[:, 0], vn[:n])
+            assert not gkmeta[:, 1].any() and not gks.any() and not gkm.any() and not gvs.any() and not gvm.any()
+    return worst
+
+
+@pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4)])
+def test_turboquant_decode_presets(er, oracle, torch, kbits, vbits):
+    w = _run_turbo_config(er, oracle, torch, L=2, B=1, Hq=16, Hkv=8, ctx=333, steps=2, seed=40 + kbits * 4 + vbits, kbits=kbits,
+                          vbits=vbits, norm_format=er.NormFormat.float32, layout=er.Layout.head_major)
+    print("turbo K%d/V%d max rel err %.3e" % (kbits, vbits, w))
+
+
+def test_turboquant_config2_shape_compact_norms(er, oracle, torch):
+    """Configuration-2-shaped: batch of sequences, turbo4 K / turbo3 V, fp16 norms, 1% outlier channels x20."""
+    _run_turbo_config(er, oracle, torch, L=2, B=3, Hq=16, Hkv=8, ctx=700, steps=2, seed=1, kbits=4, vbits=3,
+                      norm_format=er.NormFormat.float16, layout=er.Layout.head_major, ragged=True, outliers=True)
+
+
+def test_turboquant_config4_shape_paged(er, oracle, torch):
+    """Configuration-4-shaped: 32 q / 8 kv heads, turbo4 / turbo4, 64-token pages."""
+    _run_turbo_config(er, oracle, torch, L=1, B=3, Hq=32, Hkv=8, ctx=900, steps=2, seed=4, kbits=4, vbits=4,
+                      norm_format=er.NormFormat.float16, layout=er.Layout.paged, page_size=64, ragged=True)
+
+
+def test_turboquant_host_append_and_decoded_retrieve(er, oracle):
+    """KVCache.append on a TurboQuant cache + retrieveDecodedTurboQuant (KVCacheTests.swift:221-240) against the
+    oracle's cache; decoded rows equal up to the float rounding of the inverse transform's scale order."""
+    sig = lambda s: np.array([(math.sin(x * 0.17) + math.cos(x * 0.07) * 0.5) * s for x in range(128)], dtype=np.float32)
+    keys = np.concatenate([sig(1.0), sig(0.7)])
+    values = np.concatenate([sig(0.5), sig(1.2)])
+    c = er.KVCache(8, 1, 2, 128, er.Precision.turboquantV2, key_type=4, value_type=3)
+    o = oracle.OracleKVCache(8, 1, 2, 128, oracle.PREC_TURBO_V2, key_bits=4, value_bits=3)
+    for i in range(3):
+        c.append(0, keys * (i + 1), values - i)
+        o.append(0, keys * (i + 1), values - i)
+    assert c.current_length == 3
+    (kc, _, _, kmeta), (vc, _, _, vmeta) = c.retrieve_turboquant_runtime_rows(0)
+    okc, okm = o.turbo_rows(0, False)
+    ovc, ovm = o.turbo_rows(0, True)
+    assert np.array_equal(kc, okc[:6]) and np.array_equal(vc, ovc[:6])
+    assert np.array_equal(kmeta, okm[:6]) and np.array_equal(vmeta, ovm[:6])
+    dk, dv = c.retrieve_decoded_turboquant(0)
+    wk, wv = o.retrieve_decoded_turboquant(0)
+    assert dk.size == 3 * 256 and np.isfinite(dk).all()
+    assert np.array_equal(dk, wk) and np.array_equal(dv, wv)
