@@ -41,6 +41,8 @@ WORKLOADS = {
     "cfg1_token_major": dict(name="cfg1 with the reference's token-major [slot][kvHead][dim] ring layout",
                              layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="token_major",
                              theta=1.0e6),
+    "cfg1_long": dict(name="cfg1 shape at context 32768 (asymptotic kernel bandwidth; not a BASELINE configuration)",
+                      layers=28, batch=1, heads=16, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=1.0e6),
     # BASELINE.json configs[2]
     "cfg2": dict(name="cfg2: Qwen3-0.6B shape, 28 layers, batch 8, TurboQuant turbo4 K / turbo3 V, fp16 norms, context 32768",
                  layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3, norm="float16",
@@ -61,6 +63,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-device-leg", action="store_true",
+                    help="run only the device-resident timed leg (short runs under a profiler)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
     return ap.parse_args()
 
@@ -349,6 +353,15 @@ def run_ours(args, w, lens):
     value = tokens / (ms_total * 1e-3)
     bytes_total = sum(step_bytes(w, lens, W + s) for s in range(K))
     hbm_gbs = bytes_total / (ms_total * 1e-3) / 1e9       # per GPU
+
+    if args.only_device_leg:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                              "ms_per_step": ms_total / K, "hbm_gbs_per_gpu": round(hbm_gbs, 1), "gpu_launches": int(launches),
+                              "config": {"workload": w["name"]}, "note": "device leg only"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- leg 2: per-kernel durations (append / attention) with CUDA events, same steps, split entry points ----
     set_start()

@@ -85,6 +85,7 @@ SYMBOLS = {
     "er_kv_write_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _stp, _vp]),
     "er_kernel_launch_count": (C.c_uint64, []),
     "er_kv_device_status": (_i32, [_vp]),
+    "er_kv_set_trace": (_i32, [_vp, _vp, _u32]),
     "er_host_alloc": (_i32, [C.POINTER(_vp), _sz]),
     "er_host_free": (_i32, [_vp]),
 }

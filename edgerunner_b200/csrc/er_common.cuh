@@ -11,9 +11,6 @@ namespace er {
 constexpr int kHeadDim = 128;          // the attention / TurboQuant kernels are specialised for head_dim 128
 constexpr int kHalfDim = 64;
 constexpr int kUnitTokens = 16;        // scheduling quantum: 16 tokens of one kv head
-constexpr int kConsumerWarps = 8;
-constexpr int kTileTokens = kUnitTokens * kConsumerWarps;   // 128 tokens staged per pipeline stage
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;   // + one producer warp
 constexpr int kMaxPairs = 2048;        // (layer, sequence) pairs one launch can schedule
 
 // Device status codes mirrored to the host as ER_ERR_DEVICE_TIMEOUT.
@@ -89,8 +86,9 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 }
 
 // Named barrier among the consumer warps only (the producer warp never joins it).
+template <int THREADS>
 __device__ __forceinline__ void consumer_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

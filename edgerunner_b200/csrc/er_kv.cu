@@ -150,6 +150,8 @@ struct er_kv {
     size_t stage_bytes = 0;
     float cached_theta = 0.f;
     InvFreqTable inv_freq{};
+    unsigned long long* d_trace = nullptr;   // caller-owned diagnostics buffer (er_kv_set_trace)
+    uint32_t trace_ctas = 0;
     std::mutex mu;
 
     KVAddressing addressing() const {
@@ -778,7 +780,8 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
 }
 
 static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
-                                uint32_t advance, const er_step_params& s, cudaStream_t stream) {
+                                uint32_t advance, const er_step_params& s, cudaStream_t stream, const float* k_new = nullptr,
+                                const float* v_new = nullptr) {
     if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "attention kernels are built for head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
     if (kv->cfg.precision == ER_KV_FLOAT32) return fail(ER_ERR_UNSUPPORTED, "attention over a float32 cache is outside this backend's scope");
@@ -799,6 +802,11 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         p.lengths = kv->d_lengths; p.layer_begin = static_cast<int>(l0); p.num_layers = static_cast<int>(l1 - l0);
         p.batch = static_cast<int>(kv->cfg.max_batch); p.num_q_heads = static_cast<int>(num_heads);
         p.pending = static_cast<int>(pending); p.advance = static_cast<int>(advance);
+        if (k_new != nullptr) {
+            const size_t kv_off = static_cast<size_t>(l0 - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kHeadDim;
+            p.k_new = k_new + kv_off; p.v_new = v_new + kv_off; p.fused_append = 1;
+        }
+        p.trace = (kv->d_trace != nullptr && kv->trace_ctas >= static_cast<uint32_t>(kv->num_sms)) ? kv->d_trace : nullptr;
         p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
         p.apply_rope = s.apply_rope ? 1 : 0; p.rope_scaling = s.rope_scaling;
         if (p.apply_rope) p.inv_freq = kv->freq(s.rope_theta);
@@ -837,17 +845,24 @@ int32_t er_kv_advance(er_kv* kv, uint32_t lb, uint32_t le, uint32_t count, void*
 int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, const float* k, const float* v, float* out,
                           uint32_t num_heads, const er_step_params* sp, void* stream) {
     if (!kv || !q || !k || !v || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
-    int32_t rc = er_kv_append_rope_kv(kv, lb, le, k, v, sp, stream);
+    int32_t rc = check_layers(kv, lb, le);
     if (rc != ER_OK) return rc;
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
-    std::lock_guard<std::mutex> lock(kv->mu);
-    // The attention launch of the last layer chunk commits the appended row (lengths += 1) when it drains.
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    if (le - lb <= layers_per_launch)
-        return attention_locked(kv, lb, le, q, out, num_heads, 1, 1, s, static_cast<cudaStream_t>(stream));
-    rc = attention_locked(kv, lb, le, q, out, num_heads, 1, 0, s, static_cast<cudaStream_t>(stream));
-    if (rc != ER_OK) return rc;
+    const bool one_launch = le - lb <= layers_per_launch;
+    // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
+    // quantised by the append kernel first.
+    const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;
+    if (!fused) {
+        rc = er_kv_append_rope_kv(kv, lb, le, k, v, sp, stream);
+        if (rc != ER_OK) return rc;
+    }
+    std::lock_guard<std::mutex> lock(kv->mu);
+    // The launch commits the appended row (lengths += 1) when its last CTA drains.
+    rc = attention_locked(kv, lb, le, q, out, num_heads, 1, one_launch ? 1 : 0, s, static_cast<cudaStream_t>(stream),
+                          fused ? k : nullptr, fused ? v : nullptr);
+    if (rc != ER_OK || one_launch) return rc;
     const int n = static_cast<int>((le - lb) * kv->cfg.max_batch);
     add_lengths_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), n, 1);
     return check_launch("add_lengths_kernel");
@@ -876,6 +891,14 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
     ER_CUDA(cudaStreamSynchronize(s));
     return ER_OK;
+}
+
+int32_t er_kv_set_trace(er_kv* kv, uint64_t* device_buffer, uint32_t capacity_ctas) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    kv->d_trace = reinterpret_cast<unsigned long long*>(device_buffer);
+    kv->trace_ctas = device_buffer ? capacity_ctas : 0;
+    return kv->num_sms;
 }
 
 int32_t er_kv_device_status(er_kv* kv) {

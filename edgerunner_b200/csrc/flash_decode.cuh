@@ -26,7 +26,6 @@
 namespace er {
 
 constexpr int kRowBytesF16 = kHeadDim * 2;                  // 256
-constexpr int kTileBytesF16 = kTileTokens * kRowBytesF16;   // 32 KiB per K or V tile
 
 struct DecodeParams {
     const float* q;               // [layers][batch][num_q_heads][128]
@@ -46,6 +45,10 @@ struct DecodeParams {
     int num_layers;               // layers covered by this launch
     int batch;
     int num_q_heads;
+    const float* k_new;           // fused append: this step's K / V rows, [layers][batch][kv_heads][128] float
+    const float* v_new;
+    int fused_append;             // 1: the warp that owns the new row's unit converts it, uses it and stores it
+    unsigned long long* trace;    // optional [gridDim.x][8] globaltimer stamps (diagnostics), else nullptr
     int pending;                  // rows appended but not yet committed to `lengths`
     int advance;                  // added to lengths[...] by the last CTA to finish
     float scale_log2;             // softmax scale * log2(e)
@@ -62,11 +65,12 @@ struct DecodeParams {
 template <class POL>
 struct DecodeSmem {
     static constexpr int G = POL::kGroup;
+    static constexpr int NW = POL::kUnitsPerTile * POL::kWarpGroups;   // consumer warps
     static constexpr int kOffPrefix = POL::kStages * POL::kStageBytes;
     static constexpr int kOffMergeAcc = kOffPrefix + (kMaxPairs + 4) * 4;
-    static constexpr int kOffMergeML = kOffMergeAcc + kConsumerWarps * G * kHeadDim * 4;
-    static constexpr int kOffProb = kOffMergeML + kConsumerWarps * G * 2 * 4;
-    static constexpr int kOffCosSin = kOffProb + kConsumerWarps * G * kUnitTokens * 4;
+    static constexpr int kOffMergeML = kOffMergeAcc + NW * G * kHeadDim * 4;
+    static constexpr int kOffProb = kOffMergeML + NW * G * 2 * 4;
+    static constexpr int kOffCosSin = kOffProb + NW * G * kUnitTokens * 4;
     static constexpr int kOffBars = kOffCosSin + 2 * kHalfDim * 8;
     static constexpr int kOffFlags = kOffBars + 2 * POL::kStages * 8;
     static constexpr int kOffExtra = (kOffFlags + 32 + 127) & ~127;
@@ -114,14 +118,20 @@ __device__ __forceinline__ int kv_length(const DecodeParams& p, int pair) {
 
 // ------------------------------------------------------------------------------------------ dense fp16 policy
 
-template <int GROUP>
+template <int GROUP, int UNITS_PER_TILE = 8, int WARP_GROUPS = 1, int STAGES = 3>
 struct DensePolicy {
     static constexpr int kGroup = GROUP;
-    static constexpr int kStages = 3;
+    static constexpr int kUnitsPerTile = UNITS_PER_TILE;   // 16-token units staged per tile, one consumer warp each
+    static constexpr int kWarpGroups = WARP_GROUPS;        // consumer warp groups taking tiles round-robin
+    static constexpr int kStages = STAGES;
+    static constexpr int kTileBytesF16 = UNITS_PER_TILE * kUnitTokens * kRowBytesF16;   // per K or V tile
     static constexpr int kStageBytes = 2 * kTileBytesF16;
     static constexpr int kExtraBytes = 0;
     static constexpr int kOffFin = 0;
     static constexpr bool kRotated = false;
+    static constexpr bool kFusedAppend = true;
+    // A warp group must meet consecutive phases of the stages it visits: tiles go to groups round-robin.
+    static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
     static constexpr int kQRegs = 16;   // per head: dims [8i,8i+8) then [64+8i,64+8i+8), i = lane % 8
 
     __device__ static void init_extra(uint8_t*, int) {}
@@ -275,16 +285,58 @@ struct DensePolicy {
         __syncwarp();
     }
 
+    // Fused append (rope_neox_f32_to_f16 + convert_f32_to_f16 of the decode pass, Shaders/RoPE.metal:498-531,
+    // LlamaLanguageModel.swift:3676-3684): the warp whose unit holds the new token's slot converts the new K/V
+    // row into the staged tile (so attention sees it) and stores both rows to the cache with 16-byte stores.
+    __device__ static void patch_new_row(const DecodeParams& p, uint8_t* stage, int unit, int r, int layer, int seq,
+                                         int head, int slot, const float* k_src, const float* v_src, const float2* cs,
+                                         int lane) {
+        uint8_t* krow = stage + (unit * kUnitTokens + r) * kRowBytesF16;
+        uint8_t* vrow = stage + kTileBytesF16 + (unit * kUnitTokens + r) * kRowBytesF16;
+        __half* kh = reinterpret_cast<__half*>(krow);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+            const int d = lane + 32 * part;
+            float x0 = __ldg(k_src + d), x1 = __ldg(k_src + d + kHalfDim);
+            if (p.apply_rope) {
+                float y0, y1;
+                rope_rotate(x0, x1, cs[d], y0, y1);
+                x0 = y0;
+                x1 = y1;
+            }
+            kh[d] = __float2half_rn(x0);
+            kh[d + kHalfDim] = __float2half_rn(x1);
+        }
+        const float4 v4 = __ldg(reinterpret_cast<const float4*>(v_src) + lane);
+        uint2 vv;
+        reinterpret_cast<__half2*>(&vv)[0] = __halves2half2(__float2half_rn(v4.x), __float2half_rn(v4.y));
+        reinterpret_cast<__half2*>(&vv)[1] = __halves2half2(__float2half_rn(v4.z), __float2half_rn(v4.w));
+        reinterpret_cast<uint2*>(vrow)[lane] = vv;
+        __syncwarp();
+        const int64_t row = row_index(p.addr, seq, head, slot);
+        const bool is_v = lane >= 16;
+        const uint4 val = *reinterpret_cast<const uint4*>((is_v ? vrow : krow) + (lane & 15) * 16);
+        uint8_t* dst = const_cast<uint8_t*>(is_v ? p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes
+                                                 : p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes);
+        *reinterpret_cast<uint4*>(dst + row * kRowBytesF16 + (lane & 15) * 16) = val;
+        // generic-proxy writes to the stage precede its next refill by the async proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+
     __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
 };
 
 // ------------------------------------------------------------------------------------------ the kernel
 
 template <class POL>
-__global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const __grid_constant__ DecodeParams p) {
+__global__ void __launch_bounds__((POL::kUnitsPerTile * POL::kWarpGroups + 1) * 32, 1)
+flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     using L = DecodeSmem<POL>;
     constexpr int GROUP = POL::kGroup;
     constexpr int kStages = POL::kStages;
+    constexpr int UPT = POL::kUnitsPerTile;          // units (= consumer warps of one group) per tile
+    constexpr int NG = POL::kWarpGroups;
+    constexpr int NW = UPT * NG;                     // consumer warps; warp NW is the producer
     extern __shared__ __align__(128) uint8_t smem[];
     int* prefix = reinterpret_cast<int*>(smem + L::kOffPrefix);
     float* merge_acc = reinterpret_cast<float*>(smem + L::kOffMergeAcc);
@@ -298,13 +350,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hkv = p.addr.num_kv_heads;
+    auto stamp = [&](int slot) {   // diagnostics: per-CTA phase times
+        if (p.trace != nullptr) p.trace[blockIdx.x * 8 + slot] = global_timer_ns();
+    };
+    if (tid == 0) stamp(0);
     const int num_pairs = p.num_layers * p.batch;
 
     if (tid == 0) {
         flags[0] = 0; flags[1] = 0; flags[2] = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kConsumerWarps);
+            mbar_init(&empty_bar[s], UPT);
         }
         mbar_init_fence();
     }
@@ -335,9 +391,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
         if (lane == 31) prefix[num_pairs] = incl;
     }
     __syncthreads();
+    if (tid == 0) stamp(1);
 
     const int64_t total_units = static_cast<int64_t>(prefix[num_pairs]) * hkv;
-    int active = static_cast<int>(min(static_cast<int64_t>(gridDim.x), (total_units + kConsumerWarps - 1) / kConsumerWarps));
+    int active = static_cast<int>(min(static_cast<int64_t>(gridDim.x), (total_units + UPT - 1) / UPT));
     const int cta = blockIdx.x;
 
     // Sequences without any row produce a zero output row (invSum = 0 rule, Shaders/GQA.metal:379).
@@ -352,7 +409,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
         const int64_t range_begin = cta_range_start(cta, total_units, active);
         const int64_t range_end = cta_range_start(cta + 1, total_units, active);
 
-        if (warp == kConsumerWarps) {
+        if (warp == NW) {
             // ================= producer warp =================
             int k = 0;
             int64_t cur = range_begin;
@@ -360,8 +417,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
-                for (int tu = sg.u0; tu < sg.u1; tu += kConsumerWarps, ++k) {
-                    const int nun = min(kConsumerWarps, sg.u1 - tu);
+                for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
+                    const int nun = min(UPT, sg.u1 - tu);
                     const int t0 = tu * kUnitTokens;
                     const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
                     const int s = k % kStages;
@@ -373,6 +430,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
         } else {
             // ================= consumer warps =================
             float* prob = prob_all + warp * GROUP * kUnitTokens;
+            const int wgroup = warp / UPT, wunit = warp % UPT;   // tiles k with k % NG == wgroup are this warp's
             int k = 0, item_visit = 0;
             int64_t cur = range_begin;
             while (cur < range_end) {
@@ -384,7 +442,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                 ++item_visit;
                 if (p.apply_rope && tid < kHalfDim)
                     cs[tid] = rope_cos_sin(static_cast<uint32_t>(q_pos), p.inv_freq.f[tid], p.rope_scaling);
-                consumer_sync();
+                consumer_sync<NW * 32>();
 
                 float q[GROUP][POL::kQRegs], m[GROUP], l[GROUP], acc[GROUP][4];
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
@@ -397,21 +455,31 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                     for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
                 }
 
-                for (int tu = sg.u0; tu < sg.u1; tu += kConsumerWarps, ++k) {
-                    const int nun = min(kConsumerWarps, sg.u1 - tu);
+                for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
+                    if (NG > 1 && k % NG != wgroup) continue;
+                    const int nun = min(UPT, sg.u1 - tu);
                     const int t0 = tu * kUnitTokens;
                     const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
                     const int s = k % kStages;
                     mbar_wait(&full_bar[s], (k / kStages) & 1, &flags[0], p.status);
-                    if (warp < nun && !flags[0]) {
-                        const int nvalid = min(kUnitTokens, ntok - warp * kUnitTokens);
-                        POL::process_unit(p, smem + s * POL::kStageBytes, warp, nvalid, q, m, l, acc, prob, extra, lane);
+                    if (k == 0 && tid == 0) stamp(2);
+                    if (POL::kFusedAppend && p.fused_append && !flags[0]) {
+                        const int slot_new = q_pos % p.addr.max_seq_len;
+                        if (wunit < nun && tu + wunit == (slot_new >> 4))
+                            POL::patch_new_row(p, smem + s * POL::kStageBytes, wunit, slot_new & 15, layer, seq, sg.head, slot_new,
+                                               p.k_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim,
+                                               p.v_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim, cs, lane);
+                    }
+                    if (wunit < nun && !flags[0]) {
+                        const int nvalid = min(kUnitTokens, ntok - wunit * kUnitTokens);
+                        POL::process_unit(p, smem + s * POL::kStageBytes, wunit, nvalid, q, m, l, acc, prob, extra, lane);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty_bar[s]);
                 }
 
-                // ---- merge the 8 warps of this CTA ----
+                if (tid == 0) stamp(3);   // last write wins: end of this CTA's streaming
+                // ---- merge the consumer warps of this CTA ----
 #pragma unroll
                 for (int g = 0; g < GROUP; ++g) {
                     if (lane == 0) {
@@ -421,7 +489,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                     *reinterpret_cast<float4*>(merge_acc + (warp * GROUP + g) * kHeadDim + 4 * lane) =
                         make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
                 }
-                consumer_sync();
+                consumer_sync<NW * 32>();
                 const bool sole = (sg.u0 == 0 && sg.u1 == sg.units);
                 const int item = sg.pair * hkv + sg.head;
                 float* out_item = p.out + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
@@ -429,14 +497,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                 float* fin = POL::kRotated ? reinterpret_cast<float*>(extra + POL::kOffFin) : out_item;
                 const int slot = (range_begin > sg.item_unit0) ? 0 : 1;
                 float* my_scratch = p.scratch + (static_cast<int64_t>(cta) * 2 + slot) * GROUP * 130;
-                for (int idx = tid; idx < GROUP * kHeadDim; idx += kConsumerWarps * 32) {
+                for (int idx = tid; idx < GROUP * kHeadDim; idx += NW * 32) {
                     const int g = idx >> 7, d = idx & 127;
                     float M = -INFINITY;
 #pragma unroll
-                    for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, merge_ml[(w * GROUP + g) * 2]);
+                    for (int w = 0; w < NW; ++w) M = fmaxf(M, merge_ml[(w * GROUP + g) * 2]);
                     float Lsum = 0.f, A = 0.f;
 #pragma unroll
-                    for (int w = 0; w < kConsumerWarps; ++w) {
+                    for (int w = 0; w < NW; ++w) {
                         const float wgt = fast_exp2(merge_ml[(w * GROUP + g) * 2] - M);
                         Lsum = fmaf(merge_ml[(w * GROUP + g) * 2 + 1], wgt, Lsum);
                         A = fmaf(merge_acc[(w * GROUP + g) * kHeadDim + d], wgt, A);
@@ -457,16 +525,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                     const int c_first = cta_of_unit(sg.item_unit0, total_units, active);
                     const int c_last = cta_of_unit(item_end - 1, total_units, active);
                     __threadfence();
-                    consumer_sync();
+                    consumer_sync<NW * 32>();
                     if (tid == 0) {
                         const int prev = atomicAdd(p.item_counters + item, 1);
                         flags[1] = (prev == c_last - c_first) ? 1 : 0;
                     }
-                    consumer_sync();
+                    consumer_sync<NW * 32>();
                     if (flags[1]) {
                         wrote = true;
                         __threadfence();
-                        for (int idx = tid; idx < GROUP * kHeadDim; idx += kConsumerWarps * 32) {
+                        for (int idx = tid; idx < GROUP * kHeadDim; idx += NW * 32) {
                             const int g = idx >> 7, d = idx & 127;
                             float M = -INFINITY;
                             for (int c = c_first; c <= c_last; ++c) {
@@ -487,7 +555,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
                     }
                 }
                 if (POL::kRotated && wrote) {   // CTA-uniform condition
-                    consumer_sync();
+                    consumer_sync<NW * 32>();
                     POL::store_out(out_item, fin, warp, lane);
                 }
                 cur += sg.u1 - sg.u0;
@@ -496,7 +564,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
     }
 
     // ---- the last CTA to finish commits the new row: lengths += advance ----
+    if (tid == 0) stamp(4);
     __syncthreads();
+    if (tid == 0) stamp(5);
     if (tid == 0) {
         __threadfence();
         const int prev = atomicAdd(p.done_counter, 1);
@@ -508,6 +578,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) flash_decode_kernel(const _
             for (int e = tid; e < num_pairs; e += blockDim.x) p.lengths[p.layer_begin * p.batch + e] += p.advance;
         if (tid == 0) *p.done_counter = 0;
     }
+    if (tid == 0) stamp(6);
 }
 
 }  // namespace er

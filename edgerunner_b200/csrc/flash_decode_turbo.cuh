@@ -16,10 +16,14 @@
 
 namespace er {
 
-template <int GROUP, int KBITS, int VBITS>
+template <int GROUP, int KBITS, int VBITS, int UNITS_PER_TILE = 8, int WARP_GROUPS = 1, int STAGES = 4>
 struct TurboPolicy {
     static constexpr int kGroup = GROUP;
-    static constexpr int kStages = 4;
+    static constexpr int kUnitsPerTile = UNITS_PER_TILE;
+    static constexpr int kWarpGroups = WARP_GROUPS;
+    static constexpr int kStages = STAGES;
+    static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
+    static constexpr int kThreads = (UNITS_PER_TILE * WARP_GROUPS + 1) * 32;
     static constexpr int kKW = tq_code_words(KBITS);
     static constexpr int kVW = tq_code_words(VBITS);
     static constexpr int kKcBytes = kTileTokens * kKW * 4;
@@ -33,13 +37,17 @@ struct TurboPolicy {
     static constexpr int kOffFin = kOffQrot + GROUP * kHeadDim * 4;
     static constexpr int kExtraBytes = kOffFin + GROUP * kHeadDim * 4;
     static constexpr bool kRotated = true;
+    static constexpr bool kFusedAppend = false;   // rows are quantised by the separate append kernel
+    static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
+    __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
+                                         const float2*, int) {}
     static constexpr int kQRegs = 16;                        // per head: rotated dims [16i, 16i+16), i = lane % 8
 
     __device__ static void init_extra(uint8_t* extra, int tid) {
         float* lk = reinterpret_cast<float*>(extra + kOffLutK);
         float* lv = reinterpret_cast<float*>(extra + kOffLutV);
-        for (int e = tid; e < (1 << KBITS) * 32; e += kDecodeThreads) lk[e] = tq_centroids<KBITS>()[e >> 5];
-        for (int e = tid; e < (1 << VBITS) * 32; e += kDecodeThreads) lv[e] = tq_centroids<VBITS>()[e >> 5];
+        for (int e = tid; e < (1 << KBITS) * 32; e += kThreads) lk[e] = tq_centroids<KBITS>()[e >> 5];
+        for (int e = tid; e < (1 << VBITS) * 32; e += kThreads) lv[e] = tq_centroids<VBITS>()[e >> 5];
     }
 
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
@@ -89,7 +97,7 @@ struct TurboPolicy {
             warp_tq_forward(a, lane);
             *reinterpret_cast<float4*>(qrot + warp * kHeadDim + 4 * lane) = make_float4(a[0], a[1], a[2], a[3]);
         }
-        consumer_sync();
+        consumer_sync<UNITS_PER_TILE * WARP_GROUPS * 32>();
         const int i = lane & 7;
 #pragma unroll
         for (int g = 0; g < GROUP; ++g)

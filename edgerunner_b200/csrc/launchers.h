@@ -18,9 +18,16 @@ template <class POL>
 inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
     constexpr int kSmem = DecodeSmem<POL>::kTotal;
     static_assert(kSmem <= 232448, "decode kernel exceeds the 227 KiB shared-memory limit of an sm_100 CTA");
-    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<POL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    static int configured_device = -1;   // the attribute is per device and sticky: set it once
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return static_cast<int>(e);
-    flash_decode_kernel<POL><<<grid, kDecodeThreads, kSmem, stream>>>(p);
+    if (configured_device != device) {
+        e = cudaFuncSetAttribute(flash_decode_kernel<POL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured_device = device;
+    }
+    flash_decode_kernel<POL><<<grid, (POL::kUnitsPerTile * POL::kWarpGroups + 1) * 32, kSmem, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -221,5 +221,9 @@ class KVCache:
     def write_rows(self, layer, seq, start, count, k, v, params, stream=None):
         check(lib().er_kv_write_rows(self._h, layer, seq, start, count, ptr(k), ptr(v), C.byref(params), stream_ptr(stream)))
 
+    def set_trace(self, buffer, capacity_ctas):
+        """Install (or, with None, remove) a device int64 buffer [capacity_ctas, 8] for per-CTA phase timestamps."""
+        return check(lib().er_kv_set_trace(self._h, ptr(buffer), capacity_ctas))
+
     def device_status(self):
         return lib().er_kv_device_status(self._h)

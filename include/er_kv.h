@@ -263,6 +263,13 @@ uint64_t er_kernel_launch_count(void);
 /* Device status word of the cache: 0, or ER_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel expired. */
 int32_t er_kv_device_status(er_kv* kv);
 
+/* Diagnostics (the counterpart of the reference's per-phase trace collectors,
+ * Sources/EdgeRunner/Models/LlamaLanguageModel.swift:6322-6558): while a buffer is installed every CTA of a decode
+ * launch writes 8 nanosecond timestamps (start, scheduled, first tile landed, streaming done, pre-exit barrier, ...)
+ * to device_buffer[cta*8 ..].  Returns the number of CTAs a launch uses; a smaller capacity disables tracing.
+ * NULL uninstalls. */
+int32_t er_kv_set_trace(er_kv* kv, uint64_t* device_buffer, uint32_t capacity_ctas);
+
 /* Pinned host memory helpers for callers without a CUDA runtime binding of their own. */
 int32_t er_host_alloc(void** out, size_t bytes);
 int32_t er_host_free(void* ptr);
