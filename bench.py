@@ -107,7 +107,10 @@ def step_bytes(w, lens, step_index):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 20 ms.  The sampler is started before the warm-up and
+    stopped after a load window (the timed steps repeated for ~1.5 s right after the timed region, which by itself
+    lasts only tens of milliseconds); samples taken while the GPU was idle (before the first launch) are dropped by
+    keeping only those with power draw above half the maximum seen."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -119,7 +122,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -138,23 +141,24 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons, power = [], [], set(), []
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-                power.append(float(f[3]))
+                rows.append((float(f[1]), float(f[2]), float(f[3]), [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": []}
+        pmax = max(r[2] for r in rows)
+        load = [r for r in rows if r[2] >= 0.5 * pmax] or rows
+        reasons = sorted({n for r in load for n in r[3]})
+        return {"sm_mhz": statistics.median(r[0] for r in load), "sm_max_mhz": max(r[1] for r in rows), "power_w_max": pmax,
+                "samples": len(load), "reasons": reasons,
+                "window": "warm-up + timed steps + the same steps repeated for ~1.5 s, sampled every 20 ms"}
 
 
 # ------------------------------------------------------------------------------------------------- CPU legs
@@ -328,13 +332,13 @@ def run_ours(args, w, lens):
         torch.cuda.synchronize()
 
     # ---- leg 1: device-resident inputs, whole step through er_kv_decode_step ----
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     set_start()
     for s in range(W):
         cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = er.lib().er_kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -345,7 +349,16 @@ def run_ours(args, w, lens):
     barrier()
     launches = er.lib().er_kernel_launch_count() - launches0
     ms_total = max_over_ranks(e0.elapsed_time(e1), device="cuda")
+    # load window for the clock samples: the same steps again (positions rewound so the cache capacity holds)
+    t_load = time.perf_counter()
+    while rank == 0 and time.perf_counter() - t_load < 1.5:
+        set_start()
+        for s in range(min(K + W, 128)):
+            cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    for b, n in enumerate(base_positions):      # restore the post-run state the checks below expect
+        cache.set_position(n + W + K, seq=b)
     assert cache.device_status() == 0, "device-side wait timed out"
     for b, n in enumerate(base_positions):
         assert cache.total_written(0, b) == n + W + K

@@ -161,6 +161,18 @@ __global__ void rope_neox_kernel(const float* in, OUT* out, uint32_t seq_len, ui
     }
 }
 
+// Host-buffer entry point: pulls this step's q / k / v rows out of pinned (device-mapped) host memory into the
+// device staging area with plain 16-byte loads -- one launch instead of three copy-engine transfers.
+__global__ void gather_host_inputs_kernel(const float4* q, const float4* k, const float4* v, float4* dq, float4* dk,
+                                          float4* dv, int nq4, int nkv4) {
+    const int total = nq4 + 2 * nkv4;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        if (e < nq4) dq[e] = q[e];
+        else if (e < nq4 + nkv4) dk[e - nq4] = k[e - nq4];
+        else dv[e - nq4 - nkv4] = v[e - nq4 - nkv4];
+    }
+}
+
 __global__ void add_lengths_kernel(int32_t* lengths, int begin, int count, int delta) {
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x)
         lengths[begin + e] += delta;

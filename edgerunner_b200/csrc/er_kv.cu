@@ -868,6 +868,15 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     return check_launch("add_lengths_kernel");
 }
 
+// Device alias of a host pointer when the memory is pinned and mapped (cudaHostAlloc / cudaHostRegister under
+// unified addressing), else nullptr.
+static void* mapped_device_pointer(const void* host) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (attr.type != cudaMemoryTypeHost) return nullptr;
+    return attr.devicePointer;
+}
+
 int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float* hq, const float* hk, const float* hv, float* hout,
                                uint32_t num_heads, const er_step_params* sp, void* stream) {
     if (!kv || !hq || !hk || !hv || !hout) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
@@ -882,13 +891,29 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* dq = kv->d_stage; uint8_t* dk = dq + q_bytes; uint8_t* dv = dk + kv_bytes; uint8_t* dout = dv + kv_bytes;
-    ER_CUDA(cudaMemcpyAsync(dq, hq, q_bytes, cudaMemcpyHostToDevice, s));
-    ER_CUDA(cudaMemcpyAsync(dk, hk, kv_bytes, cudaMemcpyHostToDevice, s));
-    ER_CUDA(cudaMemcpyAsync(dv, hv, kv_bytes, cudaMemcpyHostToDevice, s));
+    const void* mq = mapped_device_pointer(hq);
+    const void* mk = mapped_device_pointer(hk);
+    const void* mv = mapped_device_pointer(hv);
+    void* mout = mapped_device_pointer(hout);
+    if (mq && mk && mv && q_bytes % 16 == 0 && kv_bytes % 16 == 0) {
+        // pinned inputs: one gather launch reads them over the bus
+        const int nq4 = static_cast<int>(q_bytes / 16), nkv4 = static_cast<int>(kv_bytes / 16);
+        const int blocks = std::min(2 * std::max(kv->num_sms, 1), (nq4 + 2 * nkv4 + 255) / 256);
+        gather_host_inputs_kernel<<<blocks, 256, 0, s>>>(static_cast<const float4*>(mq), static_cast<const float4*>(mk),
+                                                         static_cast<const float4*>(mv), reinterpret_cast<float4*>(dq),
+                                                         reinterpret_cast<float4*>(dk), reinterpret_cast<float4*>(dv), nq4, nkv4);
+        if ((rc = check_launch("gather_host_inputs_kernel")) != ER_OK) return rc;
+    } else {
+        ER_CUDA(cudaMemcpyAsync(dq, hq, q_bytes, cudaMemcpyHostToDevice, s));
+        ER_CUDA(cudaMemcpyAsync(dk, hk, kv_bytes, cudaMemcpyHostToDevice, s));
+        ER_CUDA(cudaMemcpyAsync(dv, hv, kv_bytes, cudaMemcpyHostToDevice, s));
+    }
+    // pinned output: the merging warps store the rows straight into host memory
+    float* step_out = mout ? static_cast<float*>(mout) : reinterpret_cast<float*>(dout);
     rc = er_kv_decode_step(kv, lb, le, reinterpret_cast<const float*>(dq), reinterpret_cast<const float*>(dk), reinterpret_cast<const float*>(dv),
-                           reinterpret_cast<float*>(dout), num_heads, sp, stream);
+                           step_out, num_heads, sp, stream);
     if (rc != ER_OK) return rc;
-    ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
+    if (!mout) ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
     ER_CUDA(cudaStreamSynchronize(s));
     return ER_OK;
 }
