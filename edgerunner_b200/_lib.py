@@ -77,6 +77,7 @@ SYMBOLS = {
     "er_rope_neox_f32_to_f16": (_i32, [_vp, _vp, C.POINTER(ERRoPEParams), _vp]),
     "er_turboquant_quantize_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "er_gqa_attention_f16kv": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
+    "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_kv_append_rope_kv": (_i32, [_vp, _u32, _u32, _vp, _vp, _stp, _vp]),
     "er_kv_attention_decode": (_i32, [_vp, _u32, _u32, _vp, _vp, _u32, _u32, _stp, _vp]),
     "er_kv_decode_step": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _stp, _vp]),

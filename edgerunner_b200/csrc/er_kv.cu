@@ -119,6 +119,12 @@ int32_t dispatch_decode_f16(int group, const DecodeParams& p, int grid, cudaStre
 
 }  // namespace
 
+namespace er {
+// Hooks for the library's other translation units.
+int32_t report_error(int32_t code, const char* message) { return fail(code, "%s", message); }
+void count_kernel_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace er
+
 // ------------------------------------------------------------------------------------------------ cache object
 
 struct er_kv {

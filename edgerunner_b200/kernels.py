@@ -52,6 +52,16 @@ class GQAKernel:
         check(lib().er_gqa_attention_f16kv(ptr(q_buffer), ptr(k_buffer), ptr(v_buffer), ptr(output_buffer), C.byref(p),
                                            stream_ptr(stream)))
 
+    def encode_static_workspace(self, q_buffer, k_buffer, v_buffer, output_buffer, seq_len, head_dim, num_heads, num_kv_heads,
+                                causal, kv_seq_len=0, q_offset=0, scale=None, stream=None):
+        """Same operator through er_gqa_attention_f16kv_static: for hosts where the library must not allocate device
+        memory (the workspace is a ~1 MiB array inside the library; at most 16 kv heads, group size 1/2/4)."""
+        p = ERGQAParams(seq_len, head_dim, num_heads, num_kv_heads, num_heads // num_kv_heads,
+                        (1.0 / math.sqrt(head_dim)) if scale is None else scale, int(bool(causal)), self.block_size,
+                        self.block_size, kv_seq_len, q_offset)
+        check(lib().er_gqa_attention_f16kv_static(ptr(q_buffer), ptr(k_buffer), ptr(v_buffer), ptr(output_buffer), C.byref(p),
+                                                  stream_ptr(stream)))
+
     def execute_f16kv(self, q, k, v, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len=0, q_offset=0):
         torch = _torch()
         qd = torch.as_tensor(np.ascontiguousarray(q, dtype=np.float32)).cuda()

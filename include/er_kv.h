@@ -221,6 +221,18 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
 int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out,
                                const ERGQAParams* params, void* stream);
 
+/* No counterpart in the reference.  Same operator and arguments as er_gqa_attention_f16kv, for hosts that cannot
+ * let the library allocate: a server whose own pool already owns all free device memory, or a latency-critical
+ * thread that must not take the driver's allocation path.  The split-K workspace is a ~1 MiB array compiled into
+ * the library (every GPU that loads the library holds it until the process exits), so the call performs no
+ * cudaMalloc / cudaFree of any kind.  Limits: numKVHeads <= 16, numHeads / numKVHeads in {1, 2, 4}, at most 256 SMs;
+ * anything larger is rejected with ER_ERR_UNSUPPORTED.  The first call on a device looks up the array's device
+ * address (make that call before starting a stream capture).  All calls share the one array: it keeps the last
+ * call's contents (the counters are re-zeroed on the stream at every call) and two calls that overlap on the GPU
+ * race -- keep them on one stream or order them yourself. */
+int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t* k, const uint16_t* v, float* out,
+                                      const ERGQAParams* params, void* stream);
+
 /* Append one new token per sequence to layers [layer_begin, layer_end): the three per-layer dispatches of the
  * decode pass -- V row convert/quantise, K NeoX RoPE + convert/quantise -- at row position totalWritten
  * (LlamaLanguageModel.swift:3649-3684, 3757-3825).  k, v: device [layers][max_batch][numKVHeads][headDim] float.
