@@ -427,21 +427,49 @@ def run_ours(args, w, lens):
            "h2d_bytes_per_step": int(hq[0].numel() + hk[0].numel() + hv[0].numel()) * 4, "d2h_bytes_per_step": int(hout.numel()) * 4,
            "entry_point": "er_kv_decode_step_host"}
 
-    # ---- leg 4: one launch per layer (how a model that interleaves its own projections would call it) ----
+    # ---- leg 4: one launch per layer (how a model that interleaves its own projections would call it), plain
+    #      launches and replayed as a CUDA graph of the 28 launches (positions live on the device, so one captured
+    #      step can be replayed for every following step) ----
+    def per_layer_step(i):
+        for l in range(L):
+            cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=torch.cuda.current_stream())
+
     set_start()
     for s in range(min(W, 4)):
-        for l in range(L):
-            cache.decode_step(qs[s % pool, l], ks[s % pool, l], vs[s % pool, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=stream)
+        per_layer_step(s % pool)
     torch.cuda.synchronize()
     n_pl = min(K, 32)
     e0.record(stream)
     for s in range(n_pl):
-        i = (W + s) % pool
-        for l in range(L):
-            cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=stream)
+        per_layer_step((W + s) % pool)
     e1.record(stream)
     torch.cuda.synchronize()
     per_layer_tok_s = B * n_pl / (e0.elapsed_time(e1) * 1e-3)
+    per_layer_graph_tok_s = None
+    try:
+        set_start()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            per_layer_step(0)                      # warm the capture stream
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            per_layer_step(0)
+        set_start()
+        for _ in range(4):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n_pl):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        per_layer_graph_tok_s = B * n_pl / (e0.elapsed_time(e1) * 1e-3)
+        assert cache.total_written(0, 0) == base_positions[0] + 4 + n_pl
+    except Exception as exc:   # graph capture is an optional extra figure
+        per_layer_graph_tok_s = "unavailable: %s" % (str(exc).splitlines()[0][:120] if str(exc) else type(exc).__name__)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -458,7 +486,8 @@ def run_ours(args, w, lens):
                        "launch": "layer-batched: one append + one persistent attention launch per step for all layers",
                        "sharding": "by sequence, one replica of the workload per GPU, no collective" if world > 1 else "single GPU",
                        "l2": "cache bytes read per step (%.0f MB) exceed the 126 MB L2; no flush needed" % (step_bytes(w, lens, W) / 1e6),
-                       "per_layer_launch_tokens_per_s": per_layer_tok_s},
+                       "per_layer_launch_tokens_per_s": per_layer_tok_s,
+                       "per_layer_launch_cuda_graph_tokens_per_s": per_layer_graph_tok_s},
             "hbm_gbs_per_gpu": round(hbm_gbs, 1), "frac_of_8tbs": round(hbm_gbs / 8000.0, 4),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }

@@ -534,18 +534,24 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     if (flags[1]) {
                         wrote = true;
                         __threadfence();
+                        // Only the first contributor can have started at or before the item: every later one
+                        // begins inside it and therefore used slot 0.
+                        const int first_slot = (cta_range_start(c_first, total_units, active) > sg.item_unit0) ? 0 : 1;
+                        const float* first_partial = p.scratch + (static_cast<int64_t>(c_first) * 2 + first_slot) * GROUP * 130;
+                        const int ncontrib = c_last - c_first + 1;
                         for (int idx = tid; idx < GROUP * kHeadDim; idx += NW * 32) {
                             const int g = idx >> 7, d = idx & 127;
-                            float M = -INFINITY;
-                            for (int c = c_first; c <= c_last; ++c) {
-                                const int sl = (cta_range_start(c, total_units, active) > sg.item_unit0) ? 0 : 1;
-                                M = fmaxf(M, __ldcg(p.scratch + (static_cast<int64_t>(c) * 2 + sl) * GROUP * 130 + g * 130));
-                            }
-                            float Lsum = 0.f, A = 0.f;
-                            for (int c = c_first; c <= c_last; ++c) {
-                                const int sl = (cta_range_start(c, total_units, active) > sg.item_unit0) ? 0 : 1;
-                                const float* sc = p.scratch + (static_cast<int64_t>(c) * 2 + sl) * GROUP * 130 + g * 130;
-                                const float wgt = fast_exp2(__ldcg(sc) - M);
+                            float M = __ldcg(first_partial + g * 130);
+#pragma unroll 4
+                            for (int c = 1; c < ncontrib; ++c)
+                                M = fmaxf(M, __ldcg(p.scratch + static_cast<int64_t>(c_first + c) * 2 * GROUP * 130 + g * 130));
+                            float wgt = fast_exp2(__ldcg(first_partial + g * 130) - M);
+                            float Lsum = __ldcg(first_partial + g * 130 + 1) * wgt;
+                            float A = __ldcg(first_partial + g * 130 + 2 + d) * wgt;
+#pragma unroll 4
+                            for (int c = 1; c < ncontrib; ++c) {
+                                const float* sc = p.scratch + static_cast<int64_t>(c_first + c) * 2 * GROUP * 130 + g * 130;
+                                wgt = fast_exp2(__ldcg(sc) - M);
                                 Lsum = fmaf(__ldcg(sc + 1), wgt, Lsum);
                                 A = fmaf(__ldcg(sc + 2 + d), wgt, A);
                             }

@@ -516,3 +516,80 @@ def test_turboquant_host_append_and_decoded_retrieve(er, oracle):
     wk, wv = o.retrieve_decoded_turboquant(0)
     assert dk.size == 3 * 256 and np.isfinite(dk).all()
     assert np.array_equal(dk, wk) and np.array_equal(dv, wv)
+
+
+# --------------------------------------------------------------------------------------------- full BASELINE sizes
+
+def test_config1_full_size_first_and_last_layers(er, oracle, torch):
+    """Configuration 1 at its full size (28 independent layers, context 4096, 16 q / 8 kv heads): two consecutive
+    decode steps through the layer-batched entry point; layers 0, 13 and 27 are checked against the oracle, every
+    layer through a size-independent property: the output row of a head is a convex combination of V rows, so each
+    coordinate lies inside the [min, max] of the cached V column (plus the appended row)."""
+    L, Hq, Hkv, D, ctx, theta = 28, 16, 8, 128, 4096, THETA_QWEN3
+    rng = rng_for(100)
+    cache = er.KVCache(ctx + 16, L, Hkv, D, er.Precision.float16)
+    sp = er.step_params(rope_theta=theta)
+    check_layers = (0, 13, 27)
+    ok, ov, vmin, vmax = {}, {}, [], []
+    for l in range(L):
+        K, V = normal_f16(rng, (ctx, Hkv, D)), normal_f16(rng, (ctx, Hkv, D))
+        cache.write_rows(l, 0, 0, ctx, dev(torch, K), dev(torch, V), sp)
+        vmin.append(V.min(axis=0))
+        vmax.append(V.max(axis=0))
+        if l in check_layers:
+            kc = np.concatenate([oracle.rope_neox_to_f16(K[t:t + 1], t, theta) for t in range(ctx)])
+            ok[l] = np.concatenate([kc, np.zeros((2, Hkv, D), np.uint16)])
+            ov[l] = np.concatenate([oracle.f32_to_f16_bits(V), np.zeros((2, Hkv, D), np.uint16)])
+    for s in range(2):
+        q, k, v = normal_f16(rng, (L, 1, Hq, D)), normal_f16(rng, (L, 1, Hkv, D)), normal_f16(rng, (L, 1, Hkv, D))
+        out = torch.full((L, 1, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        for l in range(L):
+            lo = np.minimum(vmin[l], v[l, 0]) - 1e-3
+            hi = np.maximum(vmax[l], v[l, 0]) + 1e-3
+            vmin[l], vmax[l] = np.minimum(vmin[l], v[l, 0]), np.maximum(vmax[l], v[l, 0])
+            o = got[l, 0].reshape(Hkv, Hq // Hkv, D)
+            assert (o >= lo[:, None, :]).all() and (o <= hi[:, None, :]).all(), l
+        for l in check_layers:
+            want, _ = oracle.decode_step_f16(q[l, 0], k[l, 0], v[l, 0], ok[l], ov[l], ctx + s, theta, threads=8)
+            assert max_rel_err(got[l, 0], want) < TOL, l
+    assert cache.total_written(27, 0) == ctx + 2
+
+
+def test_config2_shape_long_context_sampled(er, oracle, torch):
+    """Configuration 2's per-sequence shape (TurboQuant turbo4 K / turbo3 V, fp16 norms, context 32768, outlier channels)
+    on one layer and two sequences: appended rows' codes bit-exact, attention against the oracle over the same codes."""
+    L, B, Hq, Hkv, D, ctx, theta = 1, 2, 16, 8, 128, 32768, THETA_QWEN3
+    rng = rng_for(101)
+    cache = er.KVCache(ctx + 16, L, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=3, norm_format=er.NormFormat.float16,
+                       max_batch=B)
+    sp = er.step_params(rope_theta=theta)
+    ks, vs = outlier_channels(rng, (Hkv, D)), outlier_channels(rng, (Hkv, D))
+    for b in range(B):
+        for s0 in range(0, ctx, 8192):
+            K = (rng.standard_normal((8192, Hkv, D), dtype=np.float32) * ks).astype(np.float16).astype(np.float32)
+            V = (rng.standard_normal((8192, Hkv, D), dtype=np.float32) * vs).astype(np.float16).astype(np.float32)
+            cache.write_rows(0, b, s0, 8192, dev(torch, K), dev(torch, V), sp)
+    q = normal_f16(rng, (L, B, Hq, D))
+    k = (rng.standard_normal((L, B, Hkv, D), dtype=np.float32) * ks).astype(np.float16).astype(np.float32)
+    v = (rng.standard_normal((L, B, Hkv, D), dtype=np.float32) * vs).astype(np.float16).astype(np.float32)
+    out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for b in range(B):
+        (kc, _, _, kmeta), (vc, _, _, vmeta) = cache.retrieve_turboquant_runtime_rows(0, seq=b)
+        assert kc.shape[0] == (ctx + 1) * Hkv
+        # the appended row: codes equal the oracle's encoding of the RoPE'd row
+        kr = oracle.rope_neox(k[0, b][None], ctx, theta)[0]
+        wkc, wkn = oracle.tq_encode_rows(kr, 4)
+        wvc, wvn = oracle.tq_encode_rows(v[0, b], 3)
+        assert np.array_equal(kc[-Hkv:], wkc) and np.array_equal(vc[-Hkv:], wvc)
+        assert np.array_equal(kmeta[-Hkv:, 0], wkn.astype(np.float16).astype(np.float32))
+        # attention over the codes the cache holds
+        q_rot = oracle.rope_neox(q[0, b][None], ctx, theta)[0]
+        want = oracle.tq_attention_decode(q_rot, kc, kmeta[:, 0], 4, vc, vmeta[:, 0], 3, Hkv, ctx + 1, threads=8)
+        assert max_rel_err(got[0, b], want) < TOL
