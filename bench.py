@@ -80,6 +80,11 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch from the committed ncu capture of the same
+# workload (profiles/flash_decode_dense_g2_cfg1.md); None where no capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"cfg1": 471218688 + 4663040}
+
+
 def row_bytes(w):
     """Algorithmic cache bytes per (token, kv head): K row + V row (+ stored norms)."""
     if w["precision"] == "float16":
@@ -398,7 +403,9 @@ def run_ours(args, w, lens):
     peak, peak_src = measured_peaks()
     achieved = attn_bytes / (t_attn * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
+                "traffic_source": "ncu capture summarised in profiles/flash_decode_dense_g2_cfg1.md" if args.workload == "cfg1" else None,
+                "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": int(attn_bytes), "launch_ms": round(t_attn, 5),
                 "append_kernel_ms": round(t_append, 5), "frac_of_8tbs": round(achieved / 8000.0, 4)}
 

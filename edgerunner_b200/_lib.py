@@ -80,6 +80,7 @@ SYMBOLS = {
     "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_kv_append_rope_kv": (_i32, [_vp, _u32, _u32, _vp, _vp, _stp, _vp]),
     "er_kv_attention_decode": (_i32, [_vp, _u32, _u32, _vp, _vp, _u32, _u32, _stp, _vp]),
+    "er_kv_attention_prefill": (_i32, [_vp, _u32, _u32, _vp, _vp, _u32, _u32, _u32, _stp, _vp]),
     "er_kv_decode_step": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _stp, _vp]),
     "er_kv_decode_step_host": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _stp, _vp]),
     "er_kv_advance": (_i32, [_vp, _u32, _u32, _u32, _vp]),

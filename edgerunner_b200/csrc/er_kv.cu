@@ -18,6 +18,7 @@
 #include "append.cuh"
 #include "er_common.cuh"
 #include "launchers.h"
+#include "prefill.cuh"
 #include "turboquant.cuh"
 
 using namespace er;
@@ -709,6 +710,26 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
     if (gp->numKVHeads > 16) return fail(ER_ERR_UNSUPPORTED, "numKVHeads %u > 16 for the raw-buffer operator", gp->numKVHeads);
     const uint32_t kv_seq = gp->kvSeqLen > 0 ? gp->kvSeqLen : gp->seqLen;
     if (gp->seqLen == 0 || kv_seq == 0) return ER_OK;
+    if (gp->seqLen > 1) {   // prompt / chunk: tensor-core kernel
+        PrefillParams pp{};
+        pp.q = q; pp.out = out;
+        pp.k_layer = reinterpret_cast<const uint8_t*>(k);
+        pp.v_layer = reinterpret_cast<const uint8_t*>(v);
+        pp.addr.token_major = 1; pp.addr.num_kv_heads = static_cast<int>(gp->numKVHeads);
+        pp.addr.max_seq_len = static_cast<int>(kv_seq); pp.addr.page_size = static_cast<int>(kv_seq);
+        pp.seq = 0; pp.seq_len = static_cast<int>(gp->seqLen); pp.kv_len = static_cast<int>(kv_seq);
+        pp.q_offset = static_cast<int>(gp->qOffset); pp.causal = gp->causal ? 1 : 0;
+        pp.num_q_heads = static_cast<int>(gp->numHeads);
+        const float sc = gp->scale != 0.f ? gp->scale : 1.0f / std::sqrt(static_cast<float>(gp->headDim));
+        pp.scale_log2 = sc * 1.4426950408889634f;
+        pp.rope_scaling = 1.f;
+        const int rcl = launch_prefill_f16(static_cast<int>(gp->numHeads / gp->numKVHeads), pp, static_cast<int>(gp->numKVHeads),
+                                           static_cast<cudaStream_t>(stream));
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
+        if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
+        return ER_OK;
+    }
     Workspace* ws = nullptr;
     int32_t rc = get_workspace(&ws);
     if (rc != ER_OK) return rc;
@@ -837,6 +858,41 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float*
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
     return attention_locked(kv, lb, le, q, out, num_heads, pending ? 1 : 0, 0, s, static_cast<cudaStream_t>(stream));
+}
+
+int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
+                                uint32_t seq_len, uint32_t q_offset, const er_step_params* sp, void* stream) {
+    if (!kv || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (kv->cfg.precision != ER_KV_FLOAT16 || kv->cfg.head_dim != kHeadDim)
+        return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16 caches with head_dim 128");
+    if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
+    if (seq_len == 0) return ER_OK;
+    er_step_params s;
+    int32_t rc = step_defaults(kv, sp, s);
+    if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    PrefillParams pp{};
+    pp.q = q; pp.out = out;
+    pp.k_layer = kv->k_slab + layer * kv->k_layer_stride;
+    pp.v_layer = kv->v_slab + layer * kv->v_layer_stride;
+    pp.addr = kv->addressing();
+    pp.seq = static_cast<int>(seq); pp.seq_len = static_cast<int>(seq_len);
+    pp.kv_len_ptr = kv->d_lengths + static_cast<size_t>(layer) * kv->cfg.max_batch + seq;
+    pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
+    pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);
+    pp.causal = 1;
+    pp.num_q_heads = static_cast<int>(num_heads);
+    pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+    pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;
+    if (pp.apply_rope) pp.inv_freq = kv->freq(s.rope_theta);
+    const int rcl = launch_prefill_f16(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, static_cast<int>(kv->cfg.num_kv_heads),
+                                       static_cast<cudaStream_t>(stream));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
+    if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
+    return ER_OK;
 }
 
 int32_t er_kv_advance(er_kv* kv, uint32_t lb, uint32_t le, uint32_t count, void* stream) {

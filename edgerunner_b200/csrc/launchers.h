@@ -13,6 +13,8 @@ constexpr int kNotBuilt = -1;
 
 int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t stream);
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
+struct PrefillParams;
+int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cudaStream_t stream);
 
 template <class POL>
 inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {

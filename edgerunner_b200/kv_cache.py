@@ -203,6 +203,13 @@ class KVCache:
         check(lib().er_kv_attention_decode(self._h, layer_begin, le, ptr(q), ptr(out), num_heads, pending, C.byref(params),
                                            stream_ptr(stream)))
 
+    def attention_prefill(self, layer, seq, q, out, num_heads, seq_len, params, q_offset=None, stream=None):
+        """Causal attention of `seq_len` query rows over the cache rows of (layer, seq); q_offset None = the queries are
+        the newest rows."""
+        off = 0xFFFFFFFF if q_offset is None else q_offset
+        check(lib().er_kv_attention_prefill(self._h, layer, seq, ptr(q), ptr(out), num_heads, seq_len, off, C.byref(params),
+                                            stream_ptr(stream)))
+
     def decode_step(self, q, k, v, out, num_heads, params, layer_begin=0, layer_end=None, stream=None):
         le = self.num_layers if layer_end is None else layer_end
         check(lib().er_kv_decode_step(self._h, layer_begin, le, ptr(q), ptr(k), ptr(v), ptr(out), num_heads,

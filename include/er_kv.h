@@ -249,6 +249,15 @@ int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t layer_begin, uint32_t layer_end
 int32_t er_kv_attention_decode(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* q, float* out,
                                uint32_t num_heads, uint32_t pending, const er_step_params* params, void* stream);
 
+/* Chunked-prefill attention of `seq_len` query rows of (layer, seq) over the rows already in the cache -- the
+ * seqLen > 1 dispatch of gqa_attention_f16kv / flash_attention_gqa_simd_qf32_kvf16 in fusedPrefillPass
+ * (LlamaLanguageModel.swift:2940-2957; Shaders/GQA.metal:278-387, Shaders/FlashAttention.metal:194-264), on the tensor
+ * cores.  Write the chunk's K/V rows first (er_kv_write_rows), then call this: query row r has absolute position
+ * q_offset + r and sees keys 0 .. q_offset + r.  q_offset == UINT32_MAX means "the query rows are the newest seq_len
+ * rows of the cache".  q, out: device [seq_len][num_heads][headDim] float.  float16 caches only. */
+int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
+                                uint32_t seq_len, uint32_t q_offset, const er_step_params* params, void* stream);
+
 /* Whole decode step for layers [layer_begin, layer_end): append + attention + advance of the write position by
  * one, enqueued back to back (the body of fusedDecodePass steps 2-5, LlamaLanguageModel.swift:3649-3941).
  * Positions live on the device, so a captured CUDA graph of this call can be replayed step after step. */

@@ -593,3 +593,72 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
         q_rot = oracle.rope_neox(q[0, b][None], ctx, theta)[0]
         want = oracle.tq_attention_decode(q_rot, kc, kmeta[:, 0], 4, vc, vmeta[:, 0], 3, Hkv, ctx + 1, threads=8)
         assert max_rel_err(got[0, b], want) < TOL
+
+
+# --------------------------------------------------------------------------------------------- chunked prefill (tensor cores)
+
+@pytest.mark.parametrize("layout,page_size,Hq,Hkv,ctx,S", [
+    ("head_major", 0, 16, 8, 300, 77),        # Qwen3-0.6B heads, ragged sizes (partial tiles on both axes)
+    ("paged", 64, 32, 8, 1000, 130),          # configuration-4-shaped: 32 q / 8 kv heads, 64-token pages
+    ("token_major", 0, 8, 8, 0, 64),          # group 1, prompt from an empty cache
+    ("paged", 16, 16, 2, 129, 5),             # group 8
+])
+def test_chunked_prefill_attention(er, oracle, torch, layout, page_size, Hq, Hkv, ctx, S):
+    """er_kv_attention_prefill: a chunk of S new tokens appended after `ctx` cached tokens; query row r (position ctx + r)
+    sees keys 0 .. ctx + r.  Oracle: cpuGQA over the fp16 cache contents with kvSeqLen = ctx + S, qOffset = ctx."""
+    D, theta = 128, 1.0e6
+    rng = rng_for(200 + S)
+    T = (ctx + S + 15) // 16 * 16
+    kw = {}
+    lay = getattr(er.Layout, layout)
+    if lay == er.Layout.paged:
+        n_pages = (T + page_size - 1) // page_size + 3
+        kw = dict(page_size=page_size, num_pages=n_pages)
+    cache = er.KVCache(T, 2, Hkv, D, er.Precision.float16, layout=lay, **kw)
+    if lay == er.Layout.paged:
+        alloc = er.BlockTableAllocator(n_pages, page_size, free_order=rng.permutation(n_pages))
+        cache.set_block_table(0, alloc.ensure(0, ctx + S))
+    sp = er.step_params(rope_theta=theta)
+    layer = 1
+    K, V = normal_f16(rng, (ctx + S, Hkv, D)), normal_f16(rng, (ctx + S, Hkv, D))
+    if ctx:
+        cache.write_rows(layer, 0, 0, ctx, dev(torch, K[:ctx]), dev(torch, V[:ctx]), sp)
+    cache.write_rows(layer, 0, ctx, S, dev(torch, K[ctx:]), dev(torch, V[ctx:]), sp)
+    q = normal_f16(rng, (S, Hq, D))
+    out = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(layer, 0, dev(torch, q), out, Hq, S, sp)
+    torch.cuda.synchronize()
+    kc = np.concatenate([oracle.rope_neox_to_f16(K[t:t + 1], t, theta) for t in range(ctx + S)])
+    vc = oracle.f32_to_f16_bits(V)
+    q_rot = oracle.rope_neox(q, ctx, theta)
+    want = oracle.gqa_f16kv(q_rot, kc, vc, causal=True, q_offset=ctx, threads=8)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert max_rel_err(got, want) < TOL
+    # explicit offset form gives the same rows
+    out2 = torch.empty_like(out)
+    cache.attention_prefill(layer, 0, dev(torch, q), out2, Hq, S, sp, q_offset=ctx)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+def test_prefill_then_decode_consistency(er, oracle, torch):
+    """The last row of a prefill chunk equals a decode step that appends the same token."""
+    D, Hq, Hkv, ctx, theta = 128, 16, 8, 200, 1.0e6
+    rng = rng_for(300)
+    K, V = normal_f16(rng, (ctx + 1, Hkv, D)), normal_f16(rng, (ctx + 1, Hkv, D))
+    q = normal_f16(rng, (1, Hq, D))
+    sp = er.step_params(rope_theta=theta)
+    a = er.KVCache(256, 1, Hkv, D, er.Precision.float16)
+    b = er.KVCache(256, 1, Hkv, D, er.Precision.float16)
+    for c in (a, b):
+        c.write_rows(0, 0, 0, ctx, dev(torch, K[:ctx]), dev(torch, V[:ctx]), sp)
+    o_dec = torch.empty((1, 1, Hq, D), dtype=torch.float32, device="cuda")
+    a.decode_step(dev(torch, q[None]), dev(torch, K[ctx][None, None]), dev(torch, V[ctx][None, None]), o_dec, Hq, sp)
+    b.write_rows(0, 0, ctx, 1, dev(torch, K[ctx:]), dev(torch, V[ctx:]), sp)
+    # two query rows so the tensor-core kernel is the one that runs: rows at positions ctx-1 and ctx
+    q2 = np.concatenate([normal_f16(rng, (1, Hq, D)), q])
+    o_pf = torch.empty((2, Hq, D), dtype=torch.float32, device="cuda")
+    b.attention_prefill(0, 0, dev(torch, q2), o_pf, Hq, 2, sp)
+    torch.cuda.synchronize()
+    assert max_rel_err(o_pf[1].cpu().numpy(), o_dec[0, 0].cpu().numpy()) < TOL

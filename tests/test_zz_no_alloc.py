@@ -4,7 +4,8 @@ Some hosts of this library may not let it allocate device memory (a serving proc
 free HBM, or a thread that must stay off the driver's allocation path), so this operator keeps its split-K workspace
 in an array built into the library.  The test drives both entry points through the C ABI on the same inputs, twice
 in a row (the second call finds the first call's leftovers in the shared workspace), and expects outputs within the
-attention tolerance of the other GPU tests -- in fact bit-identical, the kernel being the same."""
+attention tolerance of the other GPU tests -- bit-identical for single query rows, where both run the same kernel
+(multi-row calls of the regular entry point use the tensor-core prefill kernel instead)."""
 import numpy as np
 import pytest
 
@@ -41,7 +42,8 @@ def test_static_workspace_entry_point_matches_regular_one():
             w, g = want.cpu().numpy(), got.cpu().numpy()
             assert np.isfinite(g).all()
             assert _rel(g, w) < TOL, (call, S, T, H, Hkv)
-            assert np.array_equal(g, w)
+            if S == 1:
+                assert np.array_equal(g, w)
 
 
 def test_static_workspace_rejects_shapes_beyond_its_limits():
