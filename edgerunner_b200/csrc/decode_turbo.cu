@@ -8,9 +8,10 @@ namespace er {
 template <int KB, int VB>
 static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
     switch (group) {
-        case 1: return launch_decode_policy<TurboPolicy<1, KB, VB>>(p, grid, stream);
-        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB>>(p, grid, stream);
-        case 4: return launch_decode_policy<TurboPolicy<4, KB, VB>>(p, grid, stream);
+        // the 4-bit/4-bit pair tables take 128 KiB of shared memory: three stages instead of four
+        case 1: return launch_decode_policy<TurboPolicy<1, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboPolicy<4, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
         default: return kNotBuilt;
     }
 }

@@ -31,9 +31,12 @@ struct TurboPolicy {
     static constexpr int kOffKn = kKcBytes + kVcBytes;
     static constexpr int kOffVn = kOffKn + kTileTokens * 4;
     static constexpr int kStageBytes = kOffVn + kTileTokens * 4;
-    static constexpr int kOffLutK = 0;                       // [2^KBITS][32] floats, one column per lane
-    static constexpr int kOffLutV = 2048;
-    static constexpr int kOffQrot = 4096;                    // [GROUP][128] rotated queries
+    // Pair tables: entry (code of dim d) | (code of dim d+1) << bits -> (centroid, centroid), one column per lane so
+    // that 32 lanes looking up 32 different pairs never collide on a bank.
+    static constexpr int kKPairs = 1 << (2 * KBITS), kVPairs = 1 << (2 * VBITS);
+    static constexpr int kOffLutK = 0;                       // float2 [kKPairs][32]
+    static constexpr int kOffLutV = kKPairs * 32 * 8;        // float2 [kVPairs][32]
+    static constexpr int kOffQrot = kOffLutV + kVPairs * 32 * 8;   // [GROUP][128] rotated queries
     static constexpr int kOffFin = kOffQrot + GROUP * kHeadDim * 4;
     static constexpr int kExtraBytes = kOffFin + GROUP * kHeadDim * 4;
     static constexpr bool kRotated = true;
@@ -44,10 +47,16 @@ struct TurboPolicy {
     static constexpr int kQRegs = 16;                        // per head: rotated dims [16i, 16i+16), i = lane % 8
 
     __device__ static void init_extra(uint8_t* extra, int tid) {
-        float* lk = reinterpret_cast<float*>(extra + kOffLutK);
-        float* lv = reinterpret_cast<float*>(extra + kOffLutV);
-        for (int e = tid; e < (1 << KBITS) * 32; e += kThreads) lk[e] = tq_centroids<KBITS>()[e >> 5];
-        for (int e = tid; e < (1 << VBITS) * 32; e += kThreads) lv[e] = tq_centroids<VBITS>()[e >> 5];
+        float2* lk = reinterpret_cast<float2*>(extra + kOffLutK);
+        float2* lv = reinterpret_cast<float2*>(extra + kOffLutV);
+        for (int e = tid; e < kKPairs * 32; e += kThreads) {
+            const int pv = e >> 5;
+            lk[e] = make_float2(tq_centroids<KBITS>()[pv & ((1 << KBITS) - 1)], tq_centroids<KBITS>()[pv >> KBITS]);
+        }
+        for (int e = tid; e < kVPairs * 32; e += kThreads) {
+            const int pv = e >> 5;
+            lv[e] = make_float2(tq_centroids<VBITS>()[pv & ((1 << VBITS) - 1)], tq_centroids<VBITS>()[pv >> VBITS]);
+        }
     }
 
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
@@ -115,8 +124,8 @@ struct TurboPolicy {
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid,
                                         const float (&q)[GROUP][kQRegs], float (&m)[GROUP], float (&l)[GROUP],
                                         float (&acc)[GROUP][4], float* prob, const uint8_t* extra, int lane) {
-        const float* lutk = reinterpret_cast<const float*>(extra + kOffLutK) + lane;
-        const float* lutv = reinterpret_cast<const float*>(extra + kOffLutV) + lane;
+        const float2* lutk = reinterpret_cast<const float2*>(extra + kOffLutK) + lane;
+        const float2* lutv = reinterpret_cast<const float2*>(extra + kOffLutV) + lane;
         const uint32_t* kc = reinterpret_cast<const uint32_t*>(stage) + unit * kUnitTokens * kKW;
         const uint32_t* vc = reinterpret_cast<const uint32_t*>(stage + kKcBytes) + unit * kUnitTokens * kVW;
         const uint8_t* kn = stage + kOffKn;
@@ -136,7 +145,18 @@ struct TurboPolicy {
             }
             float cv[16];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) cv[c] = lutk[((static_cast<uint32_t>(bits >> (KBITS * c))) & ((1u << KBITS) - 1u)) * 32];
+            for (int c2 = 0; c2 < 8; ++c2) {
+                uint32_t pv;
+                if (KBITS == 4) {      // byte c2 of the two words
+                    const uint32_t w = c2 < 4 ? static_cast<uint32_t>(bits) : static_cast<uint32_t>(bits >> 32);
+                    pv = (w >> (8 * (c2 & 3))) & 0xFFu;
+                } else {
+                    pv = static_cast<uint32_t>(bits >> (2 * KBITS * c2)) & (kKPairs - 1);
+                }
+                const float2 t = lutk[pv * 32];
+                cv[2 * c2] = t.x;
+                cv[2 * c2 + 1] = t.y;
+            }
 #pragma unroll
             for (int g = 0; g < GROUP; ++g) {
                 float d0 = 0.f, d1 = 0.f;
@@ -192,9 +212,9 @@ struct TurboPolicy {
             const uint32_t* words = vc + t * kVW;
             uint32_t bits = words[vw0] >> vsh;
             if (VBITS == 3 && vsh > 20) bits |= words[vw0 + 1] << (32 - vsh);
-            float cv[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) cv[c] = lutv[((bits >> (VBITS * c)) & ((1u << VBITS) - 1u)) * 32];
+            const float2 v01 = lutv[(bits & (kVPairs - 1)) * 32];
+            const float2 v23 = lutv[((bits >> (2 * VBITS)) & (kVPairs - 1)) * 32];
+            const float cv[4] = {v01.x, v01.y, v23.x, v23.y};
 #pragma unroll
             for (int g = 0; g < GROUP; ++g) {
                 const float w = prob[g * kUnitTokens + t];
