@@ -10,7 +10,8 @@ static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t
     switch (group) {
         // the 4-bit/4-bit pair tables take 128 KiB of shared memory: three stages instead of four
         case 1: return launch_decode_policy<TurboPolicy<1, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
-        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
+        // group 2: 12 consumer warps in two groups (96-token tiles) hide the lookup latency best of the measured shapes
+        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB, 6, 2, 4>>(p, grid, stream);
         case 4: return launch_decode_policy<TurboPolicy<4, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
         default: return kNotBuilt;
     }

@@ -865,8 +865,8 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (!kv || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
-    if (kv->cfg.precision != ER_KV_FLOAT16 || kv->cfg.head_dim != kHeadDim)
-        return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16 caches with head_dim 128");
+    if ((kv->cfg.precision != ER_KV_FLOAT16 && !kv->turbo) || kv->cfg.head_dim != kHeadDim)
+        return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16 and TurboQuant caches with head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
     if (seq_len == 0) return ER_OK;
     er_step_params s;
@@ -880,6 +880,46 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.addr = kv->addressing();
     pp.seq = static_cast<int>(seq); pp.seq_len = static_cast<int>(seq_len);
     pp.kv_len_ptr = kv->d_lengths + static_cast<size_t>(layer) * kv->cfg.max_batch + seq;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    const int n_qrows = static_cast<int>(seq_len * num_heads);
+    if (kv->turbo) {
+        // Rotated-space formulation: expand the sequence's codes to fp16 rows norm*centroid, rotate the queries, run the
+        // same tensor-core kernel, rotate the outputs back.
+        const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
+        const size_t rows_bytes = static_cast<size_t>(kv->cfg.num_kv_heads) * tpad * kHeadDim * 2;
+        const size_t q_bytes = static_cast<size_t>(n_qrows) * kHeadDim * 4;
+        rc = ensure_stage(kv, 2 * rows_bytes + q_bytes + 256);
+        if (rc != ER_OK) return rc;
+        __half* ek = reinterpret_cast<__half*>(kv->d_stage);
+        __half* ev = reinterpret_cast<__half*>(kv->d_stage + rows_bytes);
+        float* qrot = reinterpret_cast<float*>(kv->d_stage + 2 * rows_bytes);
+        for (int is_v = 0; is_v < 2; ++is_v) {
+            TurboExpandParams ep{};
+            ep.codes = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+            ep.norms = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
+            ep.out = is_v ? ev : ek;
+            ep.addr = kv->addressing();
+            ep.len_ptr = pp.kv_len_ptr;
+            ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad; ep.norm_fp16 = kv->norm_bytes == 2;
+            rc = launch_turbo_expand_rows(ep, static_cast<int>(is_v ? kv->cfg.value_type : kv->cfg.key_type),
+                                          static_cast<int>(kv->cfg.max_seq_len * kv->cfg.num_kv_heads), cs, check_launch);
+            if (rc != ER_OK) return rc;
+        }
+        TurboRotateParams rp{};
+        rp.in = q; rp.out = qrot; rp.rows = n_qrows; rp.heads = static_cast<int>(num_heads); rp.inverse = 0;
+        rp.apply_rope = s.apply_rope ? 1 : 0; rp.rope_scaling = s.rope_scaling;
+        if (rp.apply_rope) rp.inv_freq = kv->freq(s.rope_theta);
+        rp.pos_from_len = q_offset == UINT32_MAX ? 1 : 0; rp.pos0 = q_offset == UINT32_MAX ? 0u : q_offset;
+        rp.seq_len = static_cast<int>(seq_len); rp.len_ptr = pp.kv_len_ptr; rp.max_len = static_cast<int>(kv->cfg.max_seq_len);
+        tq_rotate_rows_kernel<<<std::min((n_qrows + 7) / 8, 4096), 256, 0, cs>>>(rp);
+        if ((rc = check_launch("tq_rotate_rows_kernel")) != ER_OK) return rc;
+        pp.q = qrot;
+        pp.k_layer = reinterpret_cast<const uint8_t*>(ek);
+        pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
+        pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
+        pp.seq = 0;
+        s.apply_rope = 0;
+    }
     pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
     pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);
     pp.causal = 1;
@@ -892,6 +932,12 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
     if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
+    if (kv->turbo) {
+        TurboRotateParams rp{};
+        rp.in = out; rp.out = out; rp.rows = n_qrows; rp.heads = static_cast<int>(num_heads); rp.inverse = 1;
+        tq_rotate_rows_kernel<<<std::min((n_qrows + 7) / 8, 4096), 256, 0, cs>>>(rp);
+        if ((rc = check_launch("tq_rotate_rows_kernel")) != ER_OK) return rc;
+    }
     return ER_OK;
 }
 

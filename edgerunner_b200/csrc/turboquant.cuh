@@ -235,6 +235,92 @@ __global__ void tq_decode_rows_kernel(const __grid_constant__ TurboDecodeRowsPar
     }
 }
 
+// ---- pieces of the TurboQuant chunked-prefill path (gqa_attention_turboquant, Shaders/TurboQuant.metal:1454-1649) ----
+// The contraction runs on the fp16 tensor-core prefill kernel in the *rotated* space:
+//   score = <fwd(q), kNorm * centroids(K codes)> * scale ,  out = inverse( sum_t p_t * vNorm_t * centroids(V codes) ).
+
+// Rows [0, *len) of (seq, every kv head): norm * centroid(code) as fp16, head-major [kv head][slot][128].
+struct TurboExpandParams {
+    const uint8_t* codes;
+    const uint8_t* norms;
+    __half* out;
+    KVAddressing addr;
+    const int32_t* len_ptr;
+    int seq, out_stride_rows, norm_fp16;
+};
+
+template <int BITS>
+__global__ void tq_expand_rows_f16_kernel(const __grid_constant__ TurboExpandParams p) {
+    constexpr int kWords = tq_code_words(BITS);
+    const float* cent = tq_centroids<BITS>();
+    const int lane = threadIdx.x & 31;
+    int len = *p.len_ptr;
+    len = len < p.addr.max_seq_len ? len : p.addr.max_seq_len;
+    const int64_t total = static_cast<int64_t>(len) * p.addr.num_kv_heads;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < total;
+         row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+        const int h = static_cast<int>(row / len), t = static_cast<int>(row % len);
+        const int64_t ridx = row_index(p.addr, p.seq, h, t);
+        const uint32_t* words = reinterpret_cast<const uint32_t*>(p.codes + ridx * (kWords * 4));
+        const float norm = p.norm_fp16 ? __half2float(reinterpret_cast<const __half*>(p.norms)[ridx])
+                                       : reinterpret_cast<const float*>(p.norms)[ridx];
+        const int off = 4 * BITS * lane, w0 = off >> 5, sh = off & 31;
+        uint32_t bits = words[w0] >> sh;
+        if (sh + 4 * BITS > 32) bits |= words[w0 + 1] << (32 - sh);
+        float a[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) a[c] = norm * cent[(bits >> (BITS * c)) & ((1u << BITS) - 1u)];
+        uint2 o;
+        reinterpret_cast<__half2*>(&o)[0] = __floats2half2_rn(a[0], a[1]);
+        reinterpret_cast<__half2*>(&o)[1] = __floats2half2_rn(a[2], a[3]);
+        reinterpret_cast<uint2*>(p.out + (static_cast<int64_t>(h) * p.out_stride_rows + t) * kHeadDim)[lane] = o;
+    }
+}
+
+// rows [n][128] float: forward ([NeoX RoPE at position pos0 + row / heads ->] randomizedHadamard) or inverse transform,
+// one warp per row; in == out allowed.
+struct TurboRotateParams {
+    const float* in;
+    float* out;
+    int rows, heads, inverse, apply_rope, pos_from_len, seq_len;
+    uint32_t pos0;
+    const int32_t* len_ptr;   // pos_from_len: pos0 = min(*len_ptr, max_len) - seq_len
+    int max_len;
+    float rope_scaling;
+    InvFreqTable inv_freq;
+};
+
+__global__ void tq_rotate_rows_kernel(const __grid_constant__ TurboRotateParams p) {
+    const int lane = threadIdx.x & 31;
+    uint32_t pos0 = p.pos0;
+    if (p.pos_from_len) {
+        int len = *p.len_ptr;
+        len = len < p.max_len ? len : p.max_len;
+        pos0 = static_cast<uint32_t>(len - p.seq_len);
+    }
+    for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += gridDim.x * (blockDim.x >> 5)) {
+        const float4 x = *reinterpret_cast<const float4*>(p.in + static_cast<int64_t>(row) * kHeadDim + 4 * lane);
+        float a[4] = {x.x, x.y, x.z, x.w};
+        if (p.inverse) {
+            warp_tq_inverse(a, lane);
+        } else {
+            if (p.apply_rope) {
+                const uint32_t pos = pos0 + static_cast<uint32_t>(row / p.heads);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float other = __shfl_xor_sync(0xffffffffu, a[c], 16);
+                    const float2 cs = rope_cos_sin_fast(pos, p.inv_freq.f[(4 * lane + c) & 63], p.rope_scaling);
+                    float y0, y1;
+                    if (lane < 16) { rope_rotate(a[c], other, cs, y0, y1); a[c] = y0; }
+                    else           { rope_rotate(other, a[c], cs, y0, y1); a[c] = y1; }
+                }
+            }
+            warp_tq_forward(a, lane);
+        }
+        *reinterpret_cast<float4*>(p.out + static_cast<int64_t>(row) * kHeadDim + 4 * lane) = make_float4(a[0], a[1], a[2], a[3]);
+    }
+}
+
 // Stored norms -> the reference's metadata pairs (rowNorm, residualNorm = 0).
 __global__ void widen_norms_kernel(const uint8_t* norms, float* meta, int rows, int norm_fp16) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -290,6 +376,16 @@ inline int32_t launch_turbo_append(const TurboAppendParams& tp, int kbits, int v
     ER_TQ_APPEND_CASE(2, 2) ER_TQ_APPEND_CASE(4, 2) ER_TQ_APPEND_CASE(3, 2) ER_TQ_APPEND_CASE(2, 3) ER_TQ_APPEND_CASE(2, 4)
 #undef ER_TQ_APPEND_CASE
     return -9;
+}
+
+inline int32_t launch_turbo_expand_rows(const TurboExpandParams& p, int bits, int max_rows, cudaStream_t stream, LaunchCheck check) {
+    const int blocks = static_cast<int>((static_cast<int64_t>(max_rows) + 7) / 8 < 16384 ? (static_cast<int64_t>(max_rows) + 7) / 8 : 16384);
+    switch (bits) {
+        case 2: tq_expand_rows_f16_kernel<2><<<blocks, 256, 0, stream>>>(p); break;
+        case 3: tq_expand_rows_f16_kernel<3><<<blocks, 256, 0, stream>>>(p); break;
+        default: tq_expand_rows_f16_kernel<4><<<blocks, 256, 0, stream>>>(p); break;
+    }
+    return check("tq_expand_rows_f16_kernel");
 }
 
 inline int32_t launch_turbo_decode_rows(const TurboDecodeRowsParams& p, int bits, cudaStream_t stream, LaunchCheck check) {

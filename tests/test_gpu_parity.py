@@ -642,6 +642,59 @@ def test_chunked_prefill_attention(er, oracle, torch, layout, page_size, Hq, Hkv
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("layout,page_size,Hq,Hkv,kbits,vbits,ctx,S,fp16_norm", [
+    ("head_major", 0, 16, 8, 4, 3, 300, 70, True),
+    ("paged", 64, 32, 8, 4, 4, 515, 130, True),       # configuration-4-shaped: 64-token pages, turbo4 / turbo4
+    ("head_major", 0, 8, 8, 3, 3, 0, 37, False),
+    ("token_major", 0, 16, 8, 3, 4, 90, 2, False),
+])
+def test_chunked_prefill_attention_turboquant(er, oracle, torch, layout, page_size, Hq, Hkv, kbits, vbits, ctx, S, fp16_norm):
+    """er_kv_attention_prefill on a TurboQuant cache (gqa_attention_turboquant with qSeqLen > 1,
+    Shaders/TurboQuant.metal:1454-1649): row r at position ctx + r sees codes 0 .. ctx + r.  The tensor-core path rounds
+    norm*centroid to fp16 (2^-12 relative), so the bound is the 2e-3 attention metric (error relative to the row's
+    largest output), not the element-wise one."""
+    D, theta = 128, 1.0e6
+    rng = rng_for(400 + S)
+    T = (ctx + S + 15) // 16 * 16
+    kw = {}
+    lay = getattr(er.Layout, layout)
+    if lay == er.Layout.paged:
+        n_pages = (T + page_size - 1) // page_size + 3
+        kw = dict(page_size=page_size, num_pages=n_pages)
+    cache = er.KVCache(T, 2, Hkv, D, er.Precision.turboquantV2, key_type=kbits, value_type=vbits, layout=lay,
+                       norm_format=er.NormFormat.float16 if fp16_norm else er.NormFormat.float32, **kw)
+    if lay == er.Layout.paged:
+        alloc = er.BlockTableAllocator(n_pages, page_size, free_order=rng.permutation(n_pages))
+        cache.set_block_table(0, alloc.ensure(0, ctx + S))
+    sp = er.step_params(rope_theta=theta)
+    layer = 1
+    n = ctx + S
+    K, V = normal_f16(rng, (n, Hkv, D)), normal_f16(rng, (n, Hkv, D))
+    cache.write_rows(layer, 0, 0, n, dev(torch, K), dev(torch, V), sp)
+    q = normal_f16(rng, (S, Hq, D))
+    out = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(layer, 0, dev(torch, q), out, Hq, S, sp)
+    torch.cuda.synchronize()
+    Kr = np.concatenate([oracle.rope_neox(K[t:t + 1], t, theta) for t in range(n)])
+    kc, kn = oracle.tq_encode_rows(Kr.reshape(-1, D), kbits)
+    vc, vn = oracle.tq_encode_rows(V.reshape(-1, D), vbits)
+    if fp16_norm:
+        kn, vn = kn.astype(np.float16).astype(np.float32), vn.astype(np.float16).astype(np.float32)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    worst = 0.0
+    for r in range(S):
+        qr = oracle.rope_neox(q[r:r + 1], ctx + r, theta)[0]
+        want = oracle.tq_attention_decode(qr, kc, kn, kbits, vc, vn, vbits, Hkv, ctx + r + 1, threads=8)
+        worst = max(worst, attention_err(got[r], want))
+    print("turbo prefill K%d/V%d worst attention err %.3e" % (kbits, vbits, worst))
+    assert worst < TOL
+    out2 = torch.empty_like(out)
+    cache.attention_prefill(layer, 0, dev(torch, q), out2, Hq, S, sp, q_offset=ctx)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
 def test_prefill_then_decode_consistency(er, oracle, torch):
     """The last row of a prefill chunk equals a decode step that appends the same token."""
     D, Hq, Hkv, ctx, theta = 128, 16, 8, 200, 1.0e6
