@@ -1,18 +1,18 @@
 // Instantiations of the persistent flash-decode kernel for TurboQuant rows: key/value presets turbo3 and
 // turbo4 in every combination, GQA group sizes 1, 2, 4.
-#include "flash_decode_turbo.cuh"
+#include "flash_decode_turbo_mma.cuh"
 #include "launchers.h"
 
 namespace er {
 
 template <int KB, int VB>
 static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
+    // 16 consumer warps in two groups (128-token tiles, 4 stages): the fastest of the measured shapes; more warps or more
+    // groups lose to register spills and to thinner tiles.
     switch (group) {
-        // the 4-bit/4-bit pair tables take 128 KiB of shared memory: three stages instead of four
-        case 1: return launch_decode_policy<TurboPolicy<1, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
-        // group 2: 12 consumer warps in two groups (96-token tiles) hide the lookup latency best of the measured shapes
-        case 2: return launch_decode_policy<TurboPolicy<2, KB, VB, 6, 2, 4>>(p, grid, stream);
-        case 4: return launch_decode_policy<TurboPolicy<4, KB, VB, 8, 1, (KB + VB == 8 ? 3 : 4)>>(p, grid, stream);
+        case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 8, 2, 4>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 8, 2, 4>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 8, 2, 4>>(p, grid, stream);
         default: return kNotBuilt;
     }
 }

@@ -17,7 +17,7 @@
 // 16-token unit of the tile, keep their own online-softmax state and are merged once per item.  All q
 // heads of the kv head (GROUP of them) share every staged byte, so each cache byte is read once.
 //
-// The storage format is a policy (DensePolicy below, TurboPolicy in flash_decode_turbo.cuh) providing the
+// The storage format is a policy (DensePolicy below, TurboMmaPolicy in flash_decode_turbo_mma.cuh) providing the
 // stage layout, the copy issue, the Q register preparation and the per-unit arithmetic.
 #pragma once
 
@@ -118,6 +118,33 @@ __device__ __forceinline__ int kv_length(const DecodeParams& p, int pair) {
 
 // ------------------------------------------------------------------------------------------ dense fp16 policy
 
+// Per-warp running state of one item in the lane-owns-dims form: lane holds output dims [4*lane, 4*lane+4) of every
+// q head of the group, the running maximum / denominator (replicated over lanes) and its slice of the queries.
+template <int GROUP, int QREGS>
+struct LaneState {
+    float q[GROUP][QREGS], m[GROUP], l[GROUP], acc[GROUP][4];
+    __device__ __forceinline__ void reset() {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            m[g] = -INFINITY;
+            l[g] = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
+        }
+    }
+    // ml: [GROUP][2] (max, denominator); accs: [GROUP][128] un-normalised outputs of this warp
+    __device__ __forceinline__ void publish(float* ml, float* accs, int lane) const {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            if (lane == 0) {
+                ml[g * 2] = m[g];
+                ml[g * 2 + 1] = l[g];
+            }
+            *reinterpret_cast<float4*>(accs + g * kHeadDim + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        }
+    }
+};
+
 template <int GROUP, int UNITS_PER_TILE = 8, int WARP_GROUPS = 1, int STAGES = 3>
 struct DensePolicy {
     static constexpr int kGroup = GROUP;
@@ -133,8 +160,18 @@ struct DensePolicy {
     // A warp group must meet consecutive phases of the stages it visits: tiles go to groups round-robin.
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
     static constexpr int kQRegs = 16;   // per head: dims [8i,8i+8) then [64+8i,64+8i+8), i = lane % 8
+    using State = LaneState<GROUP, kQRegs>;
 
     __device__ static void init_extra(uint8_t*, int) {}
+    __device__ __forceinline__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs,
+                                                  uint8_t* extra, int warp, int lane) {
+        load_q(p, st.q, qrow, cs, extra, warp, lane);
+        st.reset();
+    }
+    __device__ __forceinline__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid,
+                                                        State& st, float* prob, const uint8_t* extra, int lane) {
+        process_unit(p, stage, unit, nvalid, st.q, st.m, st.l, st.acc, prob, extra, lane);
+    }
 
     // Producer: K and V rows [t0, t0+ntok) of (layer, seq, head) -> stage.  Token-major storage needs one
     // 256-byte copy per row; page-major storage one copy per touched page.
@@ -444,16 +481,9 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     cs[tid] = rope_cos_sin(static_cast<uint32_t>(q_pos), p.inv_freq.f[tid], p.rope_scaling);
                 consumer_sync<NW * 32>();
 
-                float q[GROUP][POL::kQRegs], m[GROUP], l[GROUP], acc[GROUP][4];
+                typename POL::State st;
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
-                POL::load_q(p, q, qrow, cs, extra, warp, lane);
-#pragma unroll
-                for (int g = 0; g < GROUP; ++g) {
-                    m[g] = -INFINITY;
-                    l[g] = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[g][c] = 0.f;
-                }
+                POL::load_q(p, st, qrow, cs, extra, warp, lane);
 
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     if (NG > 1 && k % NG != wgroup) continue;
@@ -472,7 +502,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     }
                     if (wunit < nun && !flags[0]) {
                         const int nvalid = min(kUnitTokens, ntok - wunit * kUnitTokens);
-                        POL::process_unit(p, smem + s * POL::kStageBytes, wunit, nvalid, q, m, l, acc, prob, extra, lane);
+                        POL::process_unit(p, smem + s * POL::kStageBytes, wunit, nvalid, st, prob, extra, lane);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -480,15 +510,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
 
                 if (tid == 0) stamp(3);   // last write wins: end of this CTA's streaming
                 // ---- merge the consumer warps of this CTA ----
-#pragma unroll
-                for (int g = 0; g < GROUP; ++g) {
-                    if (lane == 0) {
-                        merge_ml[(warp * GROUP + g) * 2] = m[g];
-                        merge_ml[(warp * GROUP + g) * 2 + 1] = l[g];
-                    }
-                    *reinterpret_cast<float4*>(merge_acc + (warp * GROUP + g) * kHeadDim + 4 * lane) =
-                        make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-                }
+                st.publish(merge_ml + warp * GROUP * 2, merge_acc + warp * GROUP * kHeadDim, lane);
                 consumer_sync<NW * 32>();
                 const bool sole = (sg.u0 == 0 && sg.u1 == sg.units);
                 const int item = sg.pair * hkv + sg.head;

@@ -412,6 +412,9 @@ def test_gqa_kernel_operator_matches_cpu_gqa(er, oracle):
 
 def _run_turbo_config(er, oracle, torch, L, B, Hq, Hkv, ctx, steps, seed, kbits, vbits, norm_format, layout, page_size=0,
                       ragged=False, outliers=False, theta=THETA_QWEN3):
+    """Cache bytes (codes, norms) are compared bit for bit.  Attention outputs are bounded by 2e-3 of the head row's
+    largest output (helpers.attention_err): the decode kernel contracts fp16 copies of the centroids on the tensor
+    cores, which leaves errors of 1e-4 .. 1e-3 of that scale on outputs that cancel to near zero."""
     D = 128
     rng = rng_for(seed)
     lens = [ctx] * B if not ragged else [int(x) for x in rng.integers(max(1, ctx // 8), ctx + 1, size=B)]
@@ -462,7 +465,7 @@ def _run_turbo_config(er, oracle, torch, L, B, Hq, Hkv, ctx, steps, seed, kbits,
                 kc, kn, vc, vn = st[l, b]
                 want = oracle.decode_step_turboquant(q[l, b], k[l, b], v[l, b], kc, kn, kbits, vc, vn, vbits, lens[b] + s,
                                                      theta, norm_fp16=fp16_norm, threads=8)
-                worst = max(worst, max_rel_err(got[l, b], want))
+                worst = max(worst, attention_err(got[l, b], want))
     assert worst < TOL, worst
     # stored rows, exported in the reference's split-buffer format: codes and float32 norms bit-exact
     for l in range(L):
@@ -592,7 +595,7 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
         # attention over the codes the cache holds
         q_rot = oracle.rope_neox(q[0, b][None], ctx, theta)[0]
         want = oracle.tq_attention_decode(q_rot, kc, kmeta[:, 0], 4, vc, vmeta[:, 0], 3, Hkv, ctx + 1, threads=8)
-        assert max_rel_err(got[0, b], want) < TOL
+        assert attention_err(got[0, b], want) < TOL
 
 
 # --------------------------------------------------------------------------------------------- chunked prefill (tensor cores)
