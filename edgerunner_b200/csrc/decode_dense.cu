@@ -13,4 +13,59 @@ int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t
     }
 }
 
+int decode_dense_tile_tokens(int group) {
+    switch (group) {
+        case 1: return DensePolicy<1, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
+        case 2: return DensePolicy<2, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
+        case 4: return DensePolicy<4>::kUnitsPerTile * kUnitTokens;
+        default: return 0;
+    }
+}
+
+namespace {
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_entry() {
+    static EncodeTiledFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
+            status != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            ptr = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+bool encode_one(CUtensorMap* map, const uint8_t* base, int64_t layer_stride, int tile, uint64_t layers, uint64_t seqs, uint64_t slots,
+                uint64_t kv_heads) {
+    EncodeTiledFn fn = encode_tiled_entry();
+    if (fn == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) return false;
+    const cuuint64_t row = kRowBytesF16;
+    const cuuint64_t dims[5] = {kHeadDim, kv_heads, slots, seqs, layers};
+    const cuuint64_t seq_stride = slots * kv_heads * row;
+    // a stride of a dimension of extent 1 is never used to form an address but must still be a valid multiple of 16
+    const cuuint64_t strides[4] = {row, kv_heads * row, seq_stride, layers > 1 ? static_cast<cuuint64_t>(layer_stride) : seqs * seq_stride};
+    const cuuint32_t box[5] = {kHeadDim, 1, static_cast<cuuint32_t>(tile), 1, 1};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<uint8_t*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+int encode_token_major_maps(DecodeParams& p, int group, uint64_t layers, uint64_t seqs, uint64_t slots, uint64_t kv_heads) {
+    p.use_tmap = 0;
+    const int tile = decode_dense_tile_tokens(group);
+    if (tile == 0 || !p.addr.token_major) return -1;
+    if (!encode_one(&p.k_map, p.k_base, p.k_layer_stride_bytes, tile, layers, seqs, slots, kv_heads) ||
+        !encode_one(&p.v_map, p.v_base, p.v_layer_stride_bytes, tile, layers, seqs, slots, kv_heads))
+        return -1;
+    p.use_tmap = 1;
+    return 0;
+}
+
 }  // namespace er

@@ -7,12 +7,12 @@ namespace er {
 
 template <int KB, int VB>
 static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
-    // 16 consumer warps in two groups (128-token tiles, 4 stages): the fastest of the measured shapes; more warps or more
-    // groups lose to register spills and to thinner tiles.
+    // 14 consumer warps in two groups (112-token tiles, 4 stages, 136 registers): the fastest of the measured shapes; 16
+    // and 20 warps spill, 12 warps and thinner tiles hide less of the table-lookup latency.
     switch (group) {
-        case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 8, 2, 4>>(p, grid, stream);
-        case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 8, 2, 4>>(p, grid, stream);
-        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 8, 2, 4>>(p, grid, stream);
+        case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 7, 2, 4>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 7, 2, 4>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 7, 2, 4>>(p, grid, stream);
         default: return kNotBuilt;
     }
 }

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_fp16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -83,6 +84,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                      smem_u32(dst_smem)),
                  "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+
+// Tiled TMA load of a 5-D box (coordinates innermost first) global -> shared, completion on an mbarrier.  The
+// innermost coordinate times the element size must be a multiple of 16 bytes (always 0 here); destination 128-byte
+// aligned.  Out-of-range rows are filled with zeros and still count towards the box's bytes.
+__device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // Named barrier among the consumer warps only (the producer warp never joins it).

@@ -749,6 +749,7 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
     p.addr.pages_per_seq = 0; p.addr.block_table = nullptr;
     p.scratch = ws->scratch; p.done_counter = ws->counters; p.status = ws->counters + 1; p.item_counters = ws->counters + 16;
     const int group = static_cast<int>(gp->numHeads / gp->numKVHeads);
+    encode_token_major_maps(p, group, 1, 1, kv_seq, gp->numKVHeads);
     // One launch per query row: row r sees keys 0 .. r + qOffset (Shaders/GQA.metal:345).
     for (uint32_t r = 0; r < gp->seqLen; ++r) {
         uint64_t visible = gp->causal ? std::min<uint64_t>(kv_seq, static_cast<uint64_t>(r) + gp->qOffset + 1) : kv_seq;
@@ -842,8 +843,11 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         if (kv->turbo)
             rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
                                group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type));
-        else
+        else {
+            if (kv->token_major)
+                encode_token_major_maps(p, group, kv->cfg.num_layers, kv->cfg.max_batch, kv->cfg.max_seq_len, kv->cfg.num_kv_heads);
             rc = dispatch_decode_f16(group, p, kv->num_sms, stream);
+        }
         if (rc != ER_OK) return rc;
     }
     return ER_OK;
@@ -888,16 +892,18 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
         const size_t rows_bytes = static_cast<size_t>(kv->cfg.num_kv_heads) * tpad * kHeadDim * 2;
         const size_t q_bytes = static_cast<size_t>(n_qrows) * kHeadDim * 4;
-        rc = ensure_stage(kv, 2 * rows_bytes + q_bytes + 256);
+        rc = ensure_stage(kv, 3 * rows_bytes + q_bytes + 256);
         if (rc != ER_OK) return rc;
         __half* ek = reinterpret_cast<__half*>(kv->d_stage);
         __half* ev = reinterpret_cast<__half*>(kv->d_stage + rows_bytes);
-        float* qrot = reinterpret_cast<float*>(kv->d_stage + 2 * rows_bytes);
+        __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);   // the keys keep their fp16 rounding residue
+        float* qrot = reinterpret_cast<float*>(kv->d_stage + 3 * rows_bytes);
         for (int is_v = 0; is_v < 2; ++is_v) {
             TurboExpandParams ep{};
             ep.codes = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
             ep.norms = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
             ep.out = is_v ? ev : ek;
+            ep.out_lo = is_v ? nullptr : ekl;
             ep.addr = kv->addressing();
             ep.len_ptr = pp.kv_len_ptr;
             ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad; ep.norm_fp16 = kv->norm_bytes == 2;
@@ -916,6 +922,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         pp.q = qrot;
         pp.k_layer = reinterpret_cast<const uint8_t*>(ek);
         pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
+        pp.k_lo_layer = reinterpret_cast<const uint8_t*>(ekl);
         pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
         pp.seq = 0;
         s.apply_rope = 0;

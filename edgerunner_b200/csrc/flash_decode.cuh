@@ -28,6 +28,10 @@ namespace er {
 constexpr int kRowBytesF16 = kHeadDim * 2;                  // 256
 
 struct DecodeParams {
+    // Token-major fp16 rows only (use_tmap): tensor maps over [layer][seq][slot][kv head][128 halves] of K and V with a
+    // box of one kv head x the policy's tile of slots, so a tile is one TMA load per tensor instead of a copy per row.
+    CUtensorMap k_map, v_map;
+    int use_tmap;
     const float* q;               // [layers][batch][num_q_heads][128]
     float* out;                   // same shape
     const uint8_t* k_base;        // first row of layer 0 (fp16 rows or packed codes)
@@ -179,6 +183,15 @@ struct DensePolicy {
                                       int head, int t0, int ntok, int lane) {
         const uint8_t* kl = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vl = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        if (p.use_tmap) {
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, 2u * kTileBytesF16);
+                tma_load_5d(stage, &p.k_map, 0, head, t0, seq, layer, bar);
+                tma_load_5d(stage + kTileBytesF16, &p.v_map, 0, head, t0, seq, layer, bar);
+            }
+            __syncwarp();
+            return;
+        }
         if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
         __syncwarp();
         if (p.addr.token_major) {

@@ -12,6 +12,12 @@ namespace er {
 constexpr int kNotBuilt = -1;
 
 int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t stream);
+// Slots per staged tile of the fp16 kernel built for `group` (the tensor maps' box height), 0 when not built.
+int decode_dense_tile_tokens(int group);
+// Fills p.k_map / p.v_map / p.use_tmap for token-major fp16 rows [layers][seqs][slots][kv_heads][128]; layer strides
+// in bytes (0 with one layer).  Returns 0, or -1 when the driver entry point is missing or refuses the layout
+// (p.use_tmap stays 0 and the kernel copies row by row).
+int encode_token_major_maps(DecodeParams& p, int group, uint64_t layers, uint64_t seqs, uint64_t slots, uint64_t kv_heads);
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 struct PrefillParams;
 int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cudaStream_t stream);

@@ -244,6 +244,7 @@ struct TurboExpandParams {
     const uint8_t* codes;
     const uint8_t* norms;
     __half* out;
+    __half* out_lo;   // optional: fp16 of (value - fp16(value)), same shape
     KVAddressing addr;
     const int32_t* len_ptr;
     int seq, out_stride_rows, norm_fp16;
@@ -271,9 +272,16 @@ __global__ void tq_expand_rows_f16_kernel(const __grid_constant__ TurboExpandPar
 #pragma unroll
         for (int c = 0; c < 4; ++c) a[c] = norm * cent[(bits >> (BITS * c)) & ((1u << BITS) - 1u)];
         uint2 o;
-        reinterpret_cast<__half2*>(&o)[0] = __floats2half2_rn(a[0], a[1]);
-        reinterpret_cast<__half2*>(&o)[1] = __floats2half2_rn(a[2], a[3]);
+        const __half2 h01 = __floats2half2_rn(a[0], a[1]), h23 = __floats2half2_rn(a[2], a[3]);
+        reinterpret_cast<__half2*>(&o)[0] = h01;
+        reinterpret_cast<__half2*>(&o)[1] = h23;
         reinterpret_cast<uint2*>(p.out + (static_cast<int64_t>(h) * p.out_stride_rows + t) * kHeadDim)[lane] = o;
+        if (p.out_lo != nullptr) {
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            reinterpret_cast<__half2*>(&o)[0] = __floats2half2_rn(a[0] - f01.x, a[1] - f01.y);
+            reinterpret_cast<__half2*>(&o)[1] = __floats2half2_rn(a[2] - f23.x, a[3] - f23.y);
+            reinterpret_cast<uint2*>(p.out_lo + (static_cast<int64_t>(h) * p.out_stride_rows + t) * kHeadDim)[lane] = o;
+        }
     }
 }
 

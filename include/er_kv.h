@@ -254,7 +254,9 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t layer_begin, uint32_t layer_e
  * (LlamaLanguageModel.swift:2940-2957; Shaders/GQA.metal:278-387, Shaders/FlashAttention.metal:194-264), on the tensor
  * cores.  Write the chunk's K/V rows first (er_kv_write_rows), then call this: query row r has absolute position
  * q_offset + r and sees keys 0 .. q_offset + r.  q_offset == UINT32_MAX means "the query rows are the newest seq_len
- * rows of the cache".  q, out: device [seq_len][num_heads][headDim] float.  float16 caches only. */
+ * rows of the cache".  q, out: device [seq_len][num_heads][headDim] float.  float16 caches, and TurboQuant caches
+ * (gqa_attention_turboquant, Shaders/TurboQuant.metal:1454-1649: the sequence's codes are expanded to fp16 rows in
+ * a scratch buffer of the cache, so calls on one cache must not overlap). */
 int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
                                 uint32_t seq_len, uint32_t q_offset, const er_step_params* params, void* stream);
 
