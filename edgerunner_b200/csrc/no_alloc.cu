@@ -106,6 +106,7 @@ extern "C" int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t*
     p.addr.max_seq_len = static_cast<int>(kv_seq); p.addr.page_size = static_cast<int>(kv_seq);
     p.scratch = reinterpret_cast<float*>(scratch + kStaticCounterBytes);
     p.done_counter = counters; p.status = counters + 1; p.item_counters = counters + 16;
+    encode_token_major_maps(p, group, 1, 1, kv_seq, gp->numKVHeads);   // host-side descriptor encoding: no device allocation
     for (uint32_t r = 0; r < gp->seqLen; ++r) {   // row r sees keys 0 .. r + qOffset (Shaders/GQA.metal:345)
         const uint64_t visible = gp->causal ? (static_cast<uint64_t>(r) + gp->qOffset + 1 < kv_seq ? static_cast<uint64_t>(r) + gp->qOffset + 1 : kv_seq) : kv_seq;
         p.fixed_kv_len = static_cast<int>(visible);
