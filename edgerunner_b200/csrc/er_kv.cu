@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -112,6 +113,20 @@ int32_t decode_status(int rc, int group, int kbits, int vbits) {
         return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4 and presets turbo3/turbo4 are",
                     group, kbits, vbits);
     return fail(ER_ERR_CUDA, "flash_decode_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+}
+
+// Chunked prefill: the tcgen05 kernel when the chunk fills at least one 128-row CTA tile and the layout is covered, else
+// the mma.sync kernel.  ER_PREFILL_KERNEL=mma_sync in the environment forces the latter (A/B measurements).
+int launch_prefill(int group, const PrefillParams& pp, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream) {
+    static const bool force_legacy = [] {
+        const char* e = std::getenv("ER_PREFILL_KERNEL");
+        return e != nullptr && std::strcmp(e, "mma_sync") == 0;
+    }();
+    if (!force_legacy && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
+        const int rc = launch_prefill_umma(group, pp, outer_extent, num_kv_heads, status, stream);
+        if (rc != kNotBuilt) return rc;
+    }
+    return launch_prefill_f16(group, pp, num_kv_heads, stream);
 }
 
 int32_t dispatch_decode_f16(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
@@ -723,8 +738,11 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
         const float sc = gp->scale != 0.f ? gp->scale : 1.0f / std::sqrt(static_cast<float>(gp->headDim));
         pp.scale_log2 = sc * 1.4426950408889634f;
         pp.rope_scaling = 1.f;
-        const int rcl = launch_prefill_f16(static_cast<int>(gp->numHeads / gp->numKVHeads), pp, static_cast<int>(gp->numKVHeads),
-                                           static_cast<cudaStream_t>(stream));
+        Workspace* pws = nullptr;
+        int32_t prc = get_workspace(&pws);
+        if (prc != ER_OK) return prc;
+        const int rcl = launch_prefill(static_cast<int>(gp->numHeads / gp->numKVHeads), pp, 1, static_cast<int>(gp->numKVHeads),
+                                       pws->counters + 1, static_cast<cudaStream_t>(stream));
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
         if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
@@ -934,8 +952,9 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;
     if (pp.apply_rope) pp.inv_freq = kv->freq(s.rope_theta);
-    const int rcl = launch_prefill_f16(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, static_cast<int>(kv->cfg.num_kv_heads),
-                                       static_cast<cudaStream_t>(stream));
+    const uint64_t outer_extent = kv->turbo ? 1u : static_cast<uint64_t>(kv->pool_pages);
+    const int rcl = launch_prefill(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, outer_extent, static_cast<int>(kv->cfg.num_kv_heads),
+                                   kv->d_counters + 1, static_cast<cudaStream_t>(stream));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
     if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));

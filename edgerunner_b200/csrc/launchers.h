@@ -21,6 +21,10 @@ int encode_token_major_maps(DecodeParams& p, int group, uint64_t layers, uint64_
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 struct PrefillParams;
 int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cudaStream_t stream);
+// tcgen05 version of the same kernel.  outer_extent: pages in the pool (page-major rows) or sequences (token-major rows)
+// behind p.k_layer; status: device word that receives kStatusTimeout if a bounded wait gives up.  kNotBuilt when the
+// shape or the layout is not covered (the caller then uses launch_prefill_f16).
+int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream);
 
 template <class POL>
 inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {

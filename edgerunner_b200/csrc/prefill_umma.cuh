@@ -1,0 +1,389 @@
+// Chunked-prefill GQA attention on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory,
+// operands staged by TMA).  Same contract as prefill_f16_kernel (prefill.cuh): query row r at absolute position
+// r + qOffset attends to keys 0 .. r + qOffset (Shaders/GQA.metal:278-387, Shaders/FlashAttention.metal:194-264).
+//
+// One CTA owns 128 "M rows" of one kv head: 128 / GROUP consecutive query rows x the GROUP query heads that share it.
+//   warps 0-3 (128 threads)  thread t owns M row t: prepares its Q row, does the softmax of its row of S straight out of
+//                            tensor memory (no shuffles), writes its row of P, rescales its row of O when its maximum moved
+//   warp 4, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of STAGES) and every tcgen05.mma
+// Per 64-token tile:  S[128x64]  = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims each, S double-buffered in TMEM
+//                     O[128x128] += Phi.V + Plo.V                    4 k-steps of 16 tokens, O stays in TMEM
+// Q (pre-multiplied by scale*log2 e) and P enter as fp16 hi + lo pairs so that, with K and V exact in fp16, the result
+// keeps fp32 accuracy; the optional second K operand serves caches whose rows are expanded from fp32 (TurboQuant).
+// Shared-memory operand tiles use the 128-byte swizzle (what TMA writes with SWIZZLE_128B and what the matrix descriptors
+// name): rows of 64 halves at a 128-byte pitch, 16-byte chunk c of row r stored at chunk c ^ (r & 7); K and Q/P are
+// K-major operands (8-row group stride 1024 B), V is an MN-major B operand (the contraction runs over its rows): leading
+// offset = distance between its two 64-dim column blocks, stride offset = 1024 B between 8-token groups.
+// Every wait is bounded (2 s); on a timeout the CTA raises its abort flag and the status word, skips the remaining
+// waits, frees its tensor memory and returns.
+#pragma once
+
+#include "prefill.cuh"
+
+namespace er {
+
+constexpr int kUmRows = 128;          // M rows per CTA
+constexpr int kUmTile = 64;           // tokens per K/V tile
+constexpr int kUmThreads = 160;
+constexpr int kUmRegion = kUmRows * 128;            // 16 KiB: 128 rows x 64 halves
+constexpr int kUmKvRegion = kUmTile * 128;          // 8 KiB: 64 tokens x 64 halves
+constexpr int kUmOffQhi = 0, kUmOffQlo = 2 * kUmRegion, kUmOffPhi = 4 * kUmRegion, kUmOffPlo = 5 * kUmRegion;
+constexpr int kUmOffStages = 6 * kUmRegion;         // 96 KiB
+__host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * kUmKvRegion; }   // K [Klo] V
+__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 2 : 3; }
+__host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
+    return kUmOffStages + um_stages(ksplit) * um_stage_bytes(ksplit) + 256 + 1024;   // + barriers, + alignment slack
+}
+
+struct UmmaPrefillParams {
+    CUtensorMap k_map, v_map, klo_map;   // 5-D, box {64 dims, ...}: see encode_prefill_maps
+    PrefillParams base;
+    int box_rows;                        // tokens per TMA box (64 / box_rows boxes per region and tile)
+    int layer;                           // coordinate of the maps' outermost dimension
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_5d_sw(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, fp16 A and B, A K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem), "l"(adesc),
+                 "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 16-byte chunk `chunk` (0..7) of row `row` in a 128-byte-swizzled region
+__device__ __forceinline__ uint32_t um_swz(int row, int chunk) { return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+template <int GROUP, bool KSPLIT>
+__global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __grid_constant__ UmmaPrefillParams up) {
+    constexpr int kStages = um_stages(KSPLIT);
+    constexpr int kStageBytes = um_stage_bytes(KSPLIT);
+    constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
+    constexpr int kOffKlo = 2 * kUmKvRegion;
+    extern __shared__ uint8_t um_smem_raw[];
+    const PrefillParams& p = up.base;
+    const uint32_t sbase = (smem_u32(um_smem_raw) + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
+    uint8_t* sgen = um_smem_raw + (sbase - smem_u32(um_smem_raw));
+    const uint32_t bars = sbase + kUmOffStages + kStages * kStageBytes;
+    // barriers: kv_full[s] 0..2, kv_empty[s] 3..5, s_full[2] 6..7, p_full 8, o_full 9
+    auto bar = [&](int i) { return bars + 8u * i; };
+    uint64_t* bar_gen = reinterpret_cast<uint64_t*>(sgen + kUmOffStages + kStages * kStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 13);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kv_head = blockIdx.y;
+    constexpr int kQRowsPerCta = kUmRows / GROUP;
+    const int q0 = blockIdx.x * kQRowsPerCta;
+
+    int kv_len = p.kv_len;
+    if (p.kv_len_ptr != nullptr) {
+        const int n = *p.kv_len_ptr;
+        kv_len = n < p.addr.max_seq_len ? n : p.addr.max_seq_len;
+    }
+    const int q_offset = p.q_offset_from_end ? kv_len - p.seq_len : p.q_offset;
+    const int q_last = min(q0 + kQRowsPerCta, p.seq_len) - 1;
+    const int kv_hi = p.causal ? min(kv_len, q_last + q_offset + 1) : kv_len;
+    const int num_tiles = (kv_hi + kUmTile - 1) / kUmTile;
+
+    if (tid == 0) {
+        for (int i = 0; i < 10; ++i) mbar_init(bar_gen + i, i == 8 ? 128u : 1u);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;   // S buffers at columns 0 and 64, O at 128..255
+
+    if (warp == 4) {
+        // ================= producer: TMA + MMA issue (one lane) =================
+        if (lane == 0 && num_tiles > 0) {
+            const int boxes = kUmTile / up.box_rows;
+            auto load_tile = [&](int tile) {
+                const int st = tile % kStages;
+                const int t0 = tile * kUmTile;
+                const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
+                // rows past the cache length are not fetched (their pages may not exist); the consumers clear V there
+                int nbox = 0;
+                for (int b = 0; b < boxes; ++b) nbox += (t0 + b * up.box_rows < kv_len) ? 1 : 0;
+                const uint32_t box_bytes = static_cast<uint32_t>(up.box_rows) * 128u;
+                mbar_arrive_expect_tx(bar_gen + st, nbox * box_bytes * (KSPLIT ? 6u : 4u));
+                for (int b = 0; b < nbox; ++b) {
+                    const int slot = t0 + b * up.box_rows;
+                    int c1, c2, c3;
+                    if (p.addr.token_major) {
+                        c1 = kv_head; c2 = slot; c3 = p.seq;
+                    } else {
+                        const int page_local = slot / p.addr.page_size;
+                        c1 = slot - page_local * p.addr.page_size;
+                        c2 = kv_head;
+                        c3 = p.addr.pages_per_seq > 0 ? p.addr.block_table[p.seq * p.addr.pages_per_seq + page_local] : p.seq;
+                    }
+                    const uint32_t off = static_cast<uint32_t>(b) * box_bytes;
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        tma_load_5d_sw(stage + r * kUmKvRegion + off, &up.k_map, 64 * r, c1, c2, c3, up.layer, bar(st));
+                        tma_load_5d_sw(stage + kOffV + r * kUmKvRegion + off, &up.v_map, 64 * r, c1, c2, c3, up.layer, bar(st));
+                        if (KSPLIT) tma_load_5d_sw(stage + kOffKlo + r * kUmKvRegion + off, &up.klo_map, 64 * r, c1, c2, c3, up.layer, bar(st));
+                    }
+                }
+            };
+            constexpr uint32_t idesc_qk = umma_idesc(kUmRows, kUmTile, false);
+            constexpr uint32_t idesc_pv = umma_idesc(kUmRows, kHeadDim, true);
+            auto issue_qk = [&](int tile) {
+                const int st = tile % kStages;
+                const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
+                const uint32_t d = tmem_s0 + 64u * (tile & 1);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t koff = (kk >> 2) * kUmKvRegion + (kk & 3) * 32, qoff = (kk >> 2) * kUmRegion + (kk & 3) * 32;
+                    const uint64_t kd = umma_desc(stage + koff, 16, 1024);
+                    umma_f16(d, umma_desc(sbase + kUmOffQhi + qoff, 16, 1024), kd, idesc_qk, kk > 0);
+                    umma_f16(d, umma_desc(sbase + kUmOffQlo + qoff, 16, 1024), kd, idesc_qk, 1);
+                    if (KSPLIT)
+                        umma_f16(d, umma_desc(sbase + kUmOffQhi + qoff, 16, 1024), umma_desc(stage + kOffKlo + koff, 16, 1024), idesc_qk, 1);
+                }
+                umma_commit(bar(6 + (tile & 1)));
+            };
+            for (int t = 0; t < min(kStages, num_tiles); ++t) load_tile(t);
+            // Q is written by the consumer warps: wait for their first p_full-style handshake (phase 0 of barrier 8)
+            mbar_wait(bar_gen + 8, 0, abort_flag, up.status);
+            tc_fence_after();
+            mbar_wait(bar_gen + 0, 0, abort_flag, up.status);
+            if (!*abort_flag) issue_qk(0);
+            for (int j = 0; j < num_tiles; ++j) {
+                const int st = j % kStages;
+                if (j + 1 < num_tiles) {
+                    mbar_wait(bar_gen + (j + 1) % kStages, ((j + 1) / kStages) & 1, abort_flag, up.status);
+                    tc_fence_after();
+                    if (!*abort_flag) issue_qk(j + 1);
+                }
+                mbar_wait(bar_gen + 8, (j + 1) & 1, abort_flag, up.status);   // P(j) written (phase 0 was the Q handshake)
+                tc_fence_after();
+                if (!*abort_flag) {
+                    const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
+#pragma unroll
+                    for (int kt = 0; kt < 4; ++kt) {
+                        const uint64_t vd = umma_desc(stage + kOffV + kt * 2048, kUmKvRegion, 1024);
+                        umma_f16(tmem_o, umma_desc(sbase + kUmOffPhi + kt * 32, 16, 1024), vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
+                        umma_f16(tmem_o, umma_desc(sbase + kUmOffPlo + kt * 32, 16, 1024), vd, idesc_pv, 1u);
+                    }
+                    umma_commit(bar(9));           // O(j) complete, P and S(j) free
+                    umma_commit(bar(3 + st));      // stage free
+                }
+                if (j + kStages < num_tiles) {
+                    mbar_wait(bar_gen + 3 + st, (j / kStages) & 1, abort_flag, up.status);
+                    if (!*abort_flag) load_tile(j + kStages);
+                }
+            }
+        }
+    } else {
+        // ================= consumers: thread = M row =================
+        const int m = tid;
+        const int qi = q0 + m / GROUP, head = kv_head * GROUP + m % GROUP;
+        const bool row_ok = qi < p.seq_len;
+        const int qpos = q_offset + qi;
+        // ---- Q row: fp32 -> [RoPE] -> * scale*log2e -> fp16 hi + lo, swizzled K-major ----
+        {
+            const float* src = p.q + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
+#pragma unroll 1
+            for (int c8 = 0; c8 < 8; ++c8) {          // dims [8 c8, 8 c8 + 8) and their partners + 64
+                float a[8], b[8];
+#pragma unroll
+                for (int h4 = 0; h4 < 2; ++h4) {
+                    const float4 x = row_ok ? *reinterpret_cast<const float4*>(src + 8 * c8 + 4 * h4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 y = row_ok ? *reinterpret_cast<const float4*>(src + 64 + 8 * c8 + 4 * h4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    a[4 * h4] = x.x; a[4 * h4 + 1] = x.y; a[4 * h4 + 2] = x.z; a[4 * h4 + 3] = x.w;
+                    b[4 * h4] = y.x; b[4 * h4 + 1] = y.y; b[4 * h4 + 2] = y.z; b[4 * h4 + 3] = y.w;
+                }
+                uint32_t ah[4], al[4], bh[4], bl[4];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    if (p.apply_rope) {
+                        const float2 cs = rope_cos_sin_fast(static_cast<uint32_t>(qpos), p.inv_freq.f[8 * c8 + e], p.rope_scaling);
+                        float y0, y1;
+                        rope_rotate(a[e], b[e], cs, y0, y1);
+                        a[e] = y0; b[e] = y1;
+                    }
+                    a[e] *= p.scale_log2;
+                    b[e] *= p.scale_log2;
+                }
+#pragma unroll
+                for (int e2 = 0; e2 < 4; ++e2) {
+                    ah[e2] = pack_half2(a[2 * e2], a[2 * e2 + 1]);
+                    bh[e2] = pack_half2(b[2 * e2], b[2 * e2 + 1]);
+                    const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&ah[e2]));
+                    const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&bh[e2]));
+                    al[e2] = pack_half2(a[2 * e2] - af.x, a[2 * e2 + 1] - af.y);
+                    bl[e2] = pack_half2(b[2 * e2] - bf.x, b[2 * e2 + 1] - bf.y);
+                }
+                const uint32_t off = um_swz(m, c8);
+                *reinterpret_cast<uint4*>(sgen + kUmOffQhi + off) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
+                *reinterpret_cast<uint4*>(sgen + kUmOffQlo + off) = make_uint4(al[0], al[1], al[2], al[3]);
+                *reinterpret_cast<uint4*>(sgen + kUmOffQhi + kUmRegion + off) = make_uint4(bh[0], bh[1], bh[2], bh[3]);
+                *reinterpret_cast<uint4*>(sgen + kUmOffQlo + kUmRegion + off) = make_uint4(bl[0], bl[1], bl[2], bl[3]);
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_gen + 8);     // phase 0 of p_full: "Q is in place"
+        }
+
+        float m_run = -INFINITY, l_run = 0.f;
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        for (int j = 0; j < num_tiles; ++j) {
+            const int t0 = j * kUmTile;
+            mbar_wait(bar_gen + 6 + (j & 1), (j >> 1) & 1, abort_flag, up.status);
+            tc_fence_after();
+            float s[64];
+            {
+                float lo[32], hi[32];
+                tmem_ld32(tmem_s0 + lane_base + 64u * (j & 1), lo);
+                tmem_ld32(tmem_s0 + lane_base + 64u * (j & 1) + 32u, hi);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) { s[c] = lo[c]; s[32 + c] = hi[c]; }
+            }
+            const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
+            if (t0 + kUmTile - 1 > limit) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int c = 1; c < 64; ++c) mx = fmaxf(mx, s[c]);
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = fast_exp2(m_run - m_use);
+            m_run = m_new;
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                s[c] = fast_exp2(s[c] - m_use);
+                psum += s[c];
+            }
+            l_run = fmaf(l_run, corr, psum);
+            // O(j-1) must be complete before O is rescaled and before P is overwritten
+            if (j > 0) {
+                mbar_wait(bar_gen + 9, (j - 1) & 1, abort_flag, up.status);
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f) && !*abort_flag) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_base + c0, o);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] *= corr;
+                        tmem_st32(tmem_o + lane_base + c0, o);
+                    }
+                }
+            }
+            // the last tile: V rows past the cache length were not fetched; clear them (0 * stale bits must not be NaN)
+            if (t0 + kUmTile > kv_len) {
+                mbar_wait(bar_gen + j % kStages, (j / kStages) & 1, abort_flag, up.status);
+                uint8_t* vst = sgen + kUmOffStages + (j % kStages) * kStageBytes + kOffV;
+                const int first = kv_len - t0;
+                for (int idx = tid; idx < (kUmTile - first) * 16; idx += 128) {
+                    const int row = first + idx / 16, part = idx % 16;    // 2 regions x 8 chunks
+                    *reinterpret_cast<uint4*>(vst + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                uint32_t ph[4], pl[4];
+#pragma unroll
+                for (int e2 = 0; e2 < 4; ++e2) {
+                    const float x0 = s[8 * c8 + 2 * e2], x1 = s[8 * c8 + 2 * e2 + 1];
+                    ph[e2] = pack_half2(x0, x1);
+                    const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&ph[e2]));
+                    pl[e2] = pack_half2(x0 - hf.x, x1 - hf.y);
+                }
+                const uint32_t off = um_swz(m, c8);
+                *reinterpret_cast<uint4*>(sgen + kUmOffPhi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(sgen + kUmOffPlo + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_gen + 8);
+        }
+        // ---- epilogue: O / l ----
+        if (num_tiles > 0) {
+            mbar_wait(bar_gen + 9, (num_tiles - 1) & 1, abort_flag, up.status);
+            tc_fence_after();
+        }
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        float* dst = p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+            float o[32];
+            if (num_tiles > 0 && !*abort_flag) {
+                tmem_ld32(tmem_o + lane_base + c0, o);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = 0.f;
+            }
+            if (row_ok) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c] * inv, o[c + 1] * inv, o[c + 2] * inv, o[c + 3] * inv);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+}
+
+}  // namespace er
