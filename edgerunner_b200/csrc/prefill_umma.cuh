@@ -3,11 +3,15 @@
 // r + qOffset attends to keys 0 .. r + qOffset (Shaders/GQA.metal:278-387, Shaders/FlashAttention.metal:194-264).
 //
 // One CTA owns 128 "M rows" of one kv head: 128 / GROUP consecutive query rows x the GROUP query heads that share it.
-//   warps 0-3 (128 threads)  thread t owns M row t: prepares its Q row, does the softmax of its row of S straight out of
-//                            tensor memory (no shuffles), writes its row of P, rescales its row of O when its maximum moved
-//   warp 4, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of STAGES) and every tcgen05.mma
-// Per 64-token tile:  S[128x64]  = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims each, S double-buffered in TMEM
-//                     O[128x128] += Phi.V + Plo.V                    4 k-steps of 16 tokens, O stays in TMEM
+//   warps 0-3 and 4-7        two softmax groups of 128 threads; group g takes the tiles j with j % 2 == g and keeps its own
+//                            running maximum, denominator and O accumulator, so that one group's softmax overlaps the other
+//                            group's matrix products.  Thread t of a group owns M row t: it reads its row of S straight out
+//                            of tensor memory (no shuffles), writes its row of P and rescales its row of O when its maximum
+//                            moved.  The two partial results are merged once at the end.
+//   warp 8, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of 3 or 2 stages) and every tcgen05.mma
+// Per 64-token tile j, g = j % 2:  S_g[128x64]   = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims
+//                                  O_g[128x128] += Phi_g.V + Plo_g.V                   4 k-steps of 16 tokens
+// Tensor memory: S_0, S_1 at columns 0 and 64, O_0, O_1 at columns 128 and 256 (512 columns allocated).
 // Q (pre-multiplied by scale*log2 e) and P enter as fp16 hi + lo pairs so that, with K and V exact in fp16, the result
 // keeps fp32 accuracy; the optional second K operand serves caches whose rows are expanded from fp32 (TurboQuant).
 // Shared-memory operand tiles use the 128-byte swizzle (what TMA writes with SWIZZLE_128B and what the matrix descriptors
@@ -24,15 +28,16 @@ namespace er {
 
 constexpr int kUmRows = 128;          // M rows per CTA
 constexpr int kUmTile = 64;           // tokens per K/V tile
-constexpr int kUmThreads = 160;
+constexpr int kUmThreads = 288;
 constexpr int kUmRegion = kUmRows * 128;            // 16 KiB: 128 rows x 64 halves
 constexpr int kUmKvRegion = kUmTile * 128;          // 8 KiB: 64 tokens x 64 halves
-constexpr int kUmOffQhi = 0, kUmOffQlo = 2 * kUmRegion, kUmOffPhi = 4 * kUmRegion, kUmOffPlo = 5 * kUmRegion;
-constexpr int kUmOffStages = 6 * kUmRegion;         // 96 KiB
+constexpr int kUmOffQhi = 0, kUmOffQlo = 2 * kUmRegion;
+constexpr int kUmOffP = 4 * kUmRegion;              // per softmax group: P hi, P lo (2 regions)
+constexpr int kUmOffStages = 8 * kUmRegion;         // 128 KiB
 __host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * kUmKvRegion; }   // K [Klo] V
 __host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 2 : 3; }
 __host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
-    return kUmOffStages + um_stages(ksplit) * um_stage_bytes(ksplit) + 256 + 1024;   // + barriers, + alignment slack
+    return kUmOffStages + um_stages(ksplit) * um_stage_bytes(ksplit) + 128 + 1024;   // + barriers, alignment slack
 }
 
 struct UmmaPrefillParams {
@@ -50,10 +55,17 @@ __device__ __forceinline__ void tma_load_5d_sw(uint32_t dst, const CUtensorMap* 
         : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
-           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.  The issuing thread keeps the
+// constant high word in a register and forms the low word (start address >> 4 | leading offset >> 4 << 16) with one add
+// per instruction: the scalar code between two tcgen05.mma is what bounds their issue rate.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ uint64_t umma_desc_pack(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
 }
 // Instruction descriptor of kind::f16: fp32 accumulate, fp16 A and B, A K-major.
 __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major) {
@@ -67,6 +79,18 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// 32 consecutive columns of this thread's lane; the caller issues tmem_ld_wait() before using them
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
     asm volatile(
@@ -109,16 +133,17 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     constexpr int kStageBytes = um_stage_bytes(KSPLIT);
     constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
     constexpr int kOffKlo = 2 * kUmKvRegion;
+    // barriers: kv_full[s] 0..2, kv_empty[s] 3..5, s_full[g] 6..7, p_full[g] 8..9, o_full[g] 10..11, q_full 12
+    constexpr int kBarKvFull = 0, kBarKvEmpty = 3, kBarSFull = 6, kBarPFull = 8, kBarOFull = 10, kBarQFull = 12, kNumBars = 13;
     extern __shared__ uint8_t um_smem_raw[];
     const PrefillParams& p = up.base;
     const uint32_t sbase = (smem_u32(um_smem_raw) + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
     uint8_t* sgen = um_smem_raw + (sbase - smem_u32(um_smem_raw));
-    const uint32_t bars = sbase + kUmOffStages + kStages * kStageBytes;
-    // barriers: kv_full[s] 0..2, kv_empty[s] 3..5, s_full[2] 6..7, p_full 8, o_full 9
-    auto bar = [&](int i) { return bars + 8u * i; };
     uint64_t* bar_gen = reinterpret_cast<uint64_t*>(sgen + kUmOffStages + kStages * kStageBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + 12);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 13);
+    const uint32_t bars = smem_u32(bar_gen);
+    auto bar = [&](int i) { return bars + 8u * i; };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + kNumBars + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = blockIdx.y;
     constexpr int kQRowsPerCta = kUmRows / GROUP;
@@ -135,21 +160,22 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     const int num_tiles = (kv_hi + kUmTile - 1) / kUmTile;
 
     if (tid == 0) {
-        for (int i = 0; i < 10; ++i) mbar_init(bar_gen + i, i == 8 ? 128u : 1u);
+        for (int i = 0; i < kNumBars; ++i)
+            mbar_init(bar_gen + i, (i == kBarPFull || i == kBarPFull + 1) ? 128u : i == kBarQFull ? 256u : 1u);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;   // S buffers at columns 0 and 64, O at 128..255
+    // S_g at columns 64 g, O_g at columns 128 + 128 g
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================= producer: TMA + MMA issue (one lane) =================
         if (lane == 0 && num_tiles > 0) {
             const int boxes = kUmTile / up.box_rows;
@@ -161,7 +187,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 int nbox = 0;
                 for (int b = 0; b < boxes; ++b) nbox += (t0 + b * up.box_rows < kv_len) ? 1 : 0;
                 const uint32_t box_bytes = static_cast<uint32_t>(up.box_rows) * 128u;
-                mbar_arrive_expect_tx(bar_gen + st, nbox * box_bytes * (KSPLIT ? 6u : 4u));
+                mbar_arrive_expect_tx(bar_gen + kBarKvFull + st, nbox * box_bytes * (KSPLIT ? 6u : 4u));
                 for (int b = 0; b < nbox; ++b) {
                     const int slot = t0 + b * up.box_rows;
                     int c1, c2, c3;
@@ -176,72 +202,82 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     const uint32_t off = static_cast<uint32_t>(b) * box_bytes;
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
-                        tma_load_5d_sw(stage + r * kUmKvRegion + off, &up.k_map, 64 * r, c1, c2, c3, up.layer, bar(st));
-                        tma_load_5d_sw(stage + kOffV + r * kUmKvRegion + off, &up.v_map, 64 * r, c1, c2, c3, up.layer, bar(st));
-                        if (KSPLIT) tma_load_5d_sw(stage + kOffKlo + r * kUmKvRegion + off, &up.klo_map, 64 * r, c1, c2, c3, up.layer, bar(st));
+                        tma_load_5d_sw(stage + r * kUmKvRegion + off, &up.k_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
+                        tma_load_5d_sw(stage + kOffV + r * kUmKvRegion + off, &up.v_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
+                        if (KSPLIT)
+                            tma_load_5d_sw(stage + kOffKlo + r * kUmKvRegion + off, &up.klo_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
                     }
                 }
             };
             constexpr uint32_t idesc_qk = umma_idesc(kUmRows, kUmTile, false);
             constexpr uint32_t idesc_pv = umma_idesc(kUmRows, kHeadDim, true);
-            auto issue_qk = [&](int tile) {
-                const int st = tile % kStages;
-                const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
-                const uint32_t d = tmem_s0 + 64u * (tile & 1);
+            // descriptor low words of the operands at k-step 0 (stage 0 for K / V); every other one is a constant away
+            constexpr uint32_t kHi = umma_desc_hi(1024);
+            const uint32_t qhi_lo = umma_desc_lo(sbase + kUmOffQhi, 16), qlo_lo = umma_desc_lo(sbase + kUmOffQlo, 16);
+            const uint32_t k_lo = umma_desc_lo(sbase + kUmOffStages, 16), klo_lo = umma_desc_lo(sbase + kUmOffStages + kOffKlo, 16);
+            const uint32_t v_lo = umma_desc_lo(sbase + kUmOffStages + kOffV, kUmKvRegion);
+            const uint32_t p_lo = umma_desc_lo(sbase + kUmOffP, 16);
+            auto issue_qk = [&](int tile) {   // waits for the tile's K, then S_g = Q K^T
+                const int st = tile % kStages, g = tile & 1;
+                mbar_wait(bar_gen + kBarKvFull + st, (tile / kStages) & 1, abort_flag, up.status);
+                tc_fence_after();
+                if (*abort_flag) return;
+                const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
+                const uint32_t d = tmem + 64u * g;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t koff = (kk >> 2) * kUmKvRegion + (kk & 3) * 32, qoff = (kk >> 2) * kUmRegion + (kk & 3) * 32;
-                    const uint64_t kd = umma_desc(stage + koff, 16, 1024);
-                    umma_f16(d, umma_desc(sbase + kUmOffQhi + qoff, 16, 1024), kd, idesc_qk, kk > 0);
-                    umma_f16(d, umma_desc(sbase + kUmOffQlo + qoff, 16, 1024), kd, idesc_qk, 1);
-                    if (KSPLIT)
-                        umma_f16(d, umma_desc(sbase + kUmOffQhi + qoff, 16, 1024), umma_desc(stage + kOffKlo + koff, 16, 1024), idesc_qk, 1);
+                    constexpr int dummy = 0; (void)dummy;
+                    const uint32_t koff = ((kk >> 2) * kUmKvRegion + (kk & 3) * 32) >> 4, qoff = ((kk >> 2) * kUmRegion + (kk & 3) * 32) >> 4;
+                    const uint64_t kd = umma_desc_pack(k_lo + st_off + koff, kHi);
+                    const uint64_t qh = umma_desc_pack(qhi_lo + qoff, kHi);
+                    umma_f16(d, qh, kd, idesc_qk, kk > 0);
+                    umma_f16(d, umma_desc_pack(qlo_lo + qoff, kHi), kd, idesc_qk, 1);
+                    if (KSPLIT) umma_f16(d, qh, umma_desc_pack(klo_lo + st_off + koff, kHi), idesc_qk, 1);
                 }
-                umma_commit(bar(6 + (tile & 1)));
+                umma_commit(bar(kBarSFull + g));
             };
             for (int t = 0; t < min(kStages, num_tiles); ++t) load_tile(t);
-            // Q is written by the consumer warps: wait for their first p_full-style handshake (phase 0 of barrier 8)
-            mbar_wait(bar_gen + 8, 0, abort_flag, up.status);
+            mbar_wait(bar_gen + kBarQFull, 0, abort_flag, up.status);   // Q rows are in shared memory
             tc_fence_after();
-            mbar_wait(bar_gen + 0, 0, abort_flag, up.status);
-            if (!*abort_flag) issue_qk(0);
+            issue_qk(0);
+            if (num_tiles > 1) issue_qk(1);
             for (int j = 0; j < num_tiles; ++j) {
-                const int st = j % kStages;
-                if (j + 1 < num_tiles) {
-                    mbar_wait(bar_gen + (j + 1) % kStages, ((j + 1) / kStages) & 1, abort_flag, up.status);
-                    tc_fence_after();
-                    if (!*abort_flag) issue_qk(j + 1);
-                }
-                mbar_wait(bar_gen + 8, (j + 1) & 1, abort_flag, up.status);   // P(j) written (phase 0 was the Q handshake)
+                const int st = j % kStages, g = j & 1;
+                mbar_wait(bar_gen + kBarPFull + g, (j >> 1) & 1, abort_flag, up.status);   // P_g of tile j written, S_g read
                 tc_fence_after();
                 if (!*abort_flag) {
-                    const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
+                    const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4), pg_lo = p_lo + g * ((2 * kUmRegion) >> 4);
+                    const uint32_t d = tmem + 128u + 128u * g;
 #pragma unroll
                     for (int kt = 0; kt < 4; ++kt) {
-                        const uint64_t vd = umma_desc(stage + kOffV + kt * 2048, kUmKvRegion, 1024);
-                        umma_f16(tmem_o, umma_desc(sbase + kUmOffPhi + kt * 32, 16, 1024), vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
-                        umma_f16(tmem_o, umma_desc(sbase + kUmOffPlo + kt * 32, 16, 1024), vd, idesc_pv, 1u);
+                        const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
+                        umma_f16(d, umma_desc_pack(pg_lo + ((kt * 32) >> 4), kHi), vd, idesc_pv, (j > 1 || kt > 0) ? 1u : 0u);
+                        umma_f16(d, umma_desc_pack(pg_lo + ((kUmRegion + kt * 32) >> 4), kHi), vd, idesc_pv, 1u);
                     }
-                    umma_commit(bar(9));           // O(j) complete, P and S(j) free
-                    umma_commit(bar(3 + st));      // stage free
+                    umma_commit(bar(kBarOFull + g));       // O_g includes tile j; P_g free
+                    umma_commit(bar(kBarKvEmpty + st));    // stage free
                 }
+                // with three stages tile j + 2 is already in flight and its scores are queued first; with two, tile j + 2
+                // reuses this stage and can only be fetched once the product above has drained
+                if (kStages >= 3 && j + 2 < num_tiles) issue_qk(j + 2);
                 if (j + kStages < num_tiles) {
-                    mbar_wait(bar_gen + 3 + st, (j / kStages) & 1, abort_flag, up.status);
+                    mbar_wait(bar_gen + kBarKvEmpty + st, (j / kStages) & 1, abort_flag, up.status);
                     if (!*abort_flag) load_tile(j + kStages);
                 }
+                if (kStages < 3 && j + 2 < num_tiles) issue_qk(j + 2);
             }
         }
     } else {
-        // ================= consumers: thread = M row =================
-        const int m = tid;
+        // ================= softmax groups: thread = M row =================
+        const int g = warp >> 2, m = tid & 127;
         const int qi = q0 + m / GROUP, head = kv_head * GROUP + m % GROUP;
         const bool row_ok = qi < p.seq_len;
         const int qpos = q_offset + qi;
-        // ---- Q row: fp32 -> [RoPE] -> * scale*log2e -> fp16 hi + lo, swizzled K-major ----
+        // ---- Q row: fp32 -> [RoPE] -> * scale*log2e -> fp16 hi + lo, swizzled K-major; group g converts half of the row ----
         {
             const float* src = p.q + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
 #pragma unroll 1
-            for (int c8 = 0; c8 < 8; ++c8) {          // dims [8 c8, 8 c8 + 8) and their partners + 64
+            for (int c8 = 4 * g; c8 < 4 * g + 4; ++c8) {          // dims [8 c8, 8 c8 + 8) and their partners + 64
                 float a[8], b[8];
 #pragma unroll
                 for (int h4 = 0; h4 < 2; ++h4) {
@@ -278,64 +314,68 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 *reinterpret_cast<uint4*>(sgen + kUmOffQlo + kUmRegion + off) = make_uint4(bl[0], bl[1], bl[2], bl[3]);
             }
             fence_async_smem();
-            tc_fence_before();
-            mbar_arrive(bar_gen + 8);     // phase 0 of p_full: "Q is in place"
+            mbar_arrive(bar_gen + kBarQFull);
         }
 
         float m_run = -INFINITY, l_run = 0.f;
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-        for (int j = 0; j < num_tiles; ++j) {
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tmem_s = tmem + 64u * g + lane_base, tmem_o = tmem + 128u + 128u * g + lane_base;
+        uint8_t* pgen = sgen + kUmOffP + g * 2 * kUmRegion;
+        const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
+        int my_tiles = 0;
+        for (int j = g; j < num_tiles; j += 2, ++my_tiles) {
             const int t0 = j * kUmTile;
-            mbar_wait(bar_gen + 6 + (j & 1), (j >> 1) & 1, abort_flag, up.status);
+            mbar_wait(bar_gen + kBarSFull + g, my_tiles & 1, abort_flag, up.status);
             tc_fence_after();
             float s[64];
             {
-                float lo[32], hi[32];
-                tmem_ld32(tmem_s0 + lane_base + 64u * (j & 1), lo);
-                tmem_ld32(tmem_s0 + lane_base + 64u * (j & 1) + 32u, hi);
+                uint32_t r0[32], r1[32];
+                tmem_ld32_nowait(tmem_s, r0);
+                tmem_ld32_nowait(tmem_s + 32u, r1);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) { s[c] = lo[c]; s[32 + c] = hi[c]; }
+                for (int c = 0; c < 32; ++c) { s[c] = __uint_as_float(r0[c]); s[32 + c] = __uint_as_float(r1[c]); }
             }
-            const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
             if (t0 + kUmTile - 1 > limit) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
             }
-            float mx = s[0];
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 1; c < 64; ++c) mx = fmaxf(mx, s[c]);
+            for (int c = 4; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_run, mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = fast_exp2(m_run - m_use);
             m_run = m_new;
-            float psum = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 64; ++c) {
                 s[c] = fast_exp2(s[c] - m_use);
-                psum += s[c];
+                ps4[c & 3] += s[c];
             }
-            l_run = fmaf(l_run, corr, psum);
-            // O(j-1) must be complete before O is rescaled and before P is overwritten
-            if (j > 0) {
-                mbar_wait(bar_gen + 9, (j - 1) & 1, abort_flag, up.status);
+            l_run = fmaf(l_run, corr, (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+            // this group's previous product must be complete before O_g is rescaled and before P_g is overwritten
+            if (my_tiles > 0) {
+                mbar_wait(bar_gen + kBarOFull + g, (my_tiles - 1) & 1, abort_flag, up.status);
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, corr != 1.f) && !*abort_flag) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
                         float o[32];
-                        tmem_ld32(tmem_o + lane_base + c0, o);
+                        tmem_ld32(tmem_o + c0, o);
 #pragma unroll
                         for (int c = 0; c < 32; ++c) o[c] *= corr;
-                        tmem_st32(tmem_o + lane_base + c0, o);
+                        tmem_st32(tmem_o + c0, o);
                     }
                 }
             }
             // the last tile: V rows past the cache length were not fetched; clear them (0 * stale bits must not be NaN)
             if (t0 + kUmTile > kv_len) {
-                mbar_wait(bar_gen + j % kStages, (j / kStages) & 1, abort_flag, up.status);
+                mbar_wait(bar_gen + kBarKvFull + j % kStages, (j / kStages) & 1, abort_flag, up.status);
                 uint8_t* vst = sgen + kUmOffStages + (j % kStages) * kStageBytes + kOffV;
                 const int first = kv_len - t0;
-                for (int idx = tid; idx < (kUmTile - first) * 16; idx += 128) {
+                for (int idx = m; idx < (kUmTile - first) * 16; idx += 128) {
                     const int row = first + idx / 16, part = idx % 16;    // 2 regions x 8 chunks
                     *reinterpret_cast<uint4*>(vst + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
@@ -351,39 +391,60 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     pl[e2] = pack_half2(x0 - hf.x, x1 - hf.y);
                 }
                 const uint32_t off = um_swz(m, c8);
-                *reinterpret_cast<uint4*>(sgen + kUmOffPhi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                *reinterpret_cast<uint4*>(sgen + kUmOffPlo + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                *reinterpret_cast<uint4*>(pgen + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(pgen + kUmRegion + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(bar_gen + 8);
+            mbar_arrive(bar_gen + kBarPFull + g);
         }
-        // ---- epilogue: O / l ----
-        if (num_tiles > 0) {
-            mbar_wait(bar_gen + 9, (num_tiles - 1) & 1, abort_flag, up.status);
+        // ---- merge the two groups' partial results and write O / l; group g writes dims [64 g, 64 g + 64) ----
+        if (my_tiles > 0) {
+            mbar_wait(bar_gen + kBarOFull + g, (my_tiles - 1) & 1, abort_flag, up.status);
             tc_fence_after();
         }
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        // (max, denominator) of each group's rows pass through the head of its own, now idle, P buffer
+        reinterpret_cast<float2*>(pgen)[m] = make_float2(m_run, l_run);
+        tc_fence_before();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        tc_fence_after();
+        const float2 ml0 = reinterpret_cast<const float2*>(sgen + kUmOffP)[m];
+        const float2 ml1 = reinterpret_cast<const float2*>(sgen + kUmOffP + 2 * kUmRegion)[m];
+        const float m0 = ml0.x, l0 = ml0.y, m1 = ml1.x, l1 = ml1.y;
+        const float mm = fmaxf(m0, m1);
+        const float w0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mm);
+        const float lsum = l0 * w0 + l1 * w1;
+        const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+        const bool have0 = num_tiles > 0, have1 = num_tiles > 1;
         float* dst = p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
+        const uint32_t tmem_o0 = tmem + 128u + lane_base, tmem_o1 = tmem + 256u + lane_base;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-            float o[32];
-            if (num_tiles > 0 && !*abort_flag) {
-                tmem_ld32(tmem_o + lane_base + c0, o);
+        for (int c0 = 64 * g; c0 < 64 * g + 64; c0 += 32) {
+            float o0[32], o1[32];
+            if (have0 && !*abort_flag) {
+                tmem_ld32(tmem_o0 + c0, o0);
             } else {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) o[c] = 0.f;
+                for (int c = 0; c < 32; ++c) o0[c] = 0.f;
+            }
+            if (have1 && !*abort_flag) {
+                tmem_ld32(tmem_o1 + c0, o1);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o1[c] = 0.f;
             }
             if (row_ok) {
 #pragma unroll
                 for (int c = 0; c < 32; c += 4)
-                    *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c] * inv, o[c + 1] * inv, o[c + 2] * inv, o[c + 3] * inv);
+                    *reinterpret_cast<float4*>(dst + c0 + c) =
+                        make_float4((o0[c] * w0 + o1[c] * w1) * inv, (o0[c + 1] * w0 + o1[c + 1] * w1) * inv,
+                                    (o0[c + 2] * w0 + o1[c + 2] * w1) * inv, (o0[c + 3] * w0 + o1[c + 3] * w1) * inv);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
 }  // namespace er
