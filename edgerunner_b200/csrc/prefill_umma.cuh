@@ -3,15 +3,22 @@
 // r + qOffset attends to keys 0 .. r + qOffset (Shaders/GQA.metal:278-387, Shaders/FlashAttention.metal:194-264).
 //
 // One CTA owns 128 "M rows" of one kv head: 128 / GROUP consecutive query rows x the GROUP query heads that share it.
-//   warps 0-3 and 4-7        two softmax groups of 128 threads; group g takes the tiles j with j % 2 == g and keeps its own
-//                            running maximum, denominator and O accumulator, so that one group's softmax overlaps the other
-//                            group's matrix products.  Thread t of a group owns M row t: it reads its row of S straight out
-//                            of tensor memory (no shuffles), writes its row of P and rescales its row of O when its maximum
-//                            moved.  The two partial results are merged once at the end.
-//   warp 8, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of 3 or 2 stages) and every tcgen05.mma
-// Per 64-token tile j, g = j % 2:  S_g[128x64]   = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims
-//                                  O_g[128x128] += Phi_g.V + Plo_g.V                   4 k-steps of 16 tokens
-// Tensor memory: S_0, S_1 at columns 0 and 64, O_0, O_1 at columns 128 and 256 (512 columns allocated).
+//   warps 0-7 (256 threads)  two threads per M row: thread (h, r) reads columns [32h, 32h+32) of row r of S straight out of
+//                            tensor memory, the two halves agree on the row maximum through shared memory (one named
+//                            barrier per tile), each writes its half of the P row back over S, and rescales its 64 columns
+//                            of the O row when the maximum moved.  Half a row per thread keeps the softmax of a tile
+//                            shorter than the tile's matrix products, which run meanwhile on the other S buffer.
+//   warp 8, one lane         issues every tcgen05.mma
+//   warp 9, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of 6 or 4 stages); a thread of its own,
+//                            because issuing a tile's loads costs about as many clocks as issuing its products
+// Per 64-token tile j, b = j % 2:  S_b[128x64] = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims, N = 64
+//                                  O[128x128] += Phi_b.V + Plo_b.V                   4 k-steps of 16 tokens, N = 128
+// (measured issue intervals of tcgen05.mma with M = 128, K = 16: 48 clocks at N = 64, 64 at N = 128, 127 at N = 256,
+// the same for an A operand in shared or tensor memory).
+// The A operands (Q, P) live in tensor memory: row r is lane r, column c holds elements 2c and 2c+1 as fp16, a
+// 16-element k-step is 8 columns.  Tensor memory (512 columns allocated): S_0, S_1 at 0 and 64 (P_b overwrites S_b in
+// place: hi parts in its first 32 columns, lo parts in the other 32; the products execute in issue order and S_b of
+// tile j+2 is issued after the P.V product of tile j), O at 128, Q hi at 256, Q lo at 320.
 // Q (pre-multiplied by scale*log2 e) and P enter as fp16 hi + lo pairs so that, with K and V exact in fp16, the result
 // keeps fp32 accuracy; the optional second K operand serves caches whose rows are expanded from fp32 (TurboQuant).
 // Shared-memory operand tiles use the 128-byte swizzle (what TMA writes with SWIZZLE_128B and what the matrix descriptors
@@ -28,16 +35,13 @@ namespace er {
 
 constexpr int kUmRows = 128;          // M rows per CTA
 constexpr int kUmTile = 64;           // tokens per K/V tile
-constexpr int kUmThreads = 288;
-constexpr int kUmRegion = kUmRows * 128;            // 16 KiB: 128 rows x 64 halves
+constexpr int kUmThreads = 320;
 constexpr int kUmKvRegion = kUmTile * 128;          // 8 KiB: 64 tokens x 64 halves
-constexpr int kUmOffQhi = 0, kUmOffQlo = 2 * kUmRegion;
-constexpr int kUmOffP = 4 * kUmRegion;              // per softmax group: P hi, P lo (2 regions)
-constexpr int kUmOffStages = 8 * kUmRegion;         // 128 KiB
+constexpr int kUmColS = 0, kUmColO = 128, kUmColQhi = 256, kUmColQlo = 320;   // tensor-memory columns
 __host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * kUmKvRegion; }   // K [Klo] V
-__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 2 : 3; }
+__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 4 : 6; }
 __host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
-    return kUmOffStages + um_stages(ksplit) * um_stage_bytes(ksplit) + 128 + 1024;   // + barriers, alignment slack
+    return um_stages(ksplit) * um_stage_bytes(ksplit) + 256 + 3072 + 1024;   // + barriers, (max, denominator) exchange, alignment slack
 }
 
 struct UmmaPrefillParams {
@@ -76,6 +80,12 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
                  "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// A operand in tensor memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }" ::"r"(d_tmem), "r"(a_tmem),
+                 "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -105,6 +115,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_st32_words(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+        "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16_words(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+                 "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
@@ -133,17 +159,19 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     constexpr int kStageBytes = um_stage_bytes(KSPLIT);
     constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
     constexpr int kOffKlo = 2 * kUmKvRegion;
-    // barriers: kv_full[s] 0..2, kv_empty[s] 3..5, s_full[g] 6..7, p_full[g] 8..9, o_full[g] 10..11, q_full 12
-    constexpr int kBarKvFull = 0, kBarKvEmpty = 3, kBarSFull = 6, kBarPFull = 8, kBarOFull = 10, kBarQFull = 12, kNumBars = 13;
+    constexpr int kBarKvFull = 0, kBarKvEmpty = kStages, kBarSFull = 2 * kStages, kBarPFull = kBarSFull + 2, kBarOFull = kBarSFull + 4,
+                  kBarQFull = kBarSFull + 5, kNumBars = kBarSFull + 6;
+    static_assert(kNumBars * 8 + 16 <= 256, "barrier block");
     extern __shared__ uint8_t um_smem_raw[];
     const PrefillParams& p = up.base;
     const uint32_t sbase = (smem_u32(um_smem_raw) + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
     uint8_t* sgen = um_smem_raw + (sbase - smem_u32(um_smem_raw));
-    uint64_t* bar_gen = reinterpret_cast<uint64_t*>(sgen + kUmOffStages + kStages * kStageBytes);
+    uint64_t* bar_gen = reinterpret_cast<uint64_t*>(sgen + kStages * kStageBytes);
     const uint32_t bars = smem_u32(bar_gen);
     auto bar = [&](int i) { return bars + 8u * i; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_gen + kNumBars);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + kNumBars + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + kNumBars) + 1;
+    float* xchg = reinterpret_cast<float*>(sgen + kStages * kStageBytes + 256);   // maxima [2 tile parities][2 halves][128 rows], then denominators [2][128]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = blockIdx.y;
     constexpr int kQRowsPerCta = kUmRows / GROUP;
@@ -161,7 +189,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(bar_gen + i, (i == kBarPFull || i == kBarPFull + 1) ? 128u : i == kBarQFull ? 256u : 1u);
+            mbar_init(bar_gen + i, (i == kBarPFull || i == kBarPFull + 1 || i == kBarQFull) ? 256u : 1u);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -173,16 +201,17 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // S_g at columns 64 g, O_g at columns 128 + 128 g
 
-    if (warp == 8) {
-        // ================= producer: TMA + MMA issue (one lane) =================
+    if (warp == 9) {
+        // ================= loader: TMA (one lane) =================
         if (lane == 0 && num_tiles > 0) {
             const int boxes = kUmTile / up.box_rows;
-            auto load_tile = [&](int tile) {
+            for (int tile = 0; tile < num_tiles; ++tile) {
                 const int st = tile % kStages;
+                if (tile >= kStages) mbar_wait(bar_gen + kBarKvEmpty + st, ((tile / kStages) - 1) & 1, abort_flag, up.status);
+                if (*abort_flag) break;
                 const int t0 = tile * kUmTile;
-                const uint32_t stage = sbase + kUmOffStages + st * kStageBytes;
+                const uint32_t stage = sbase + st * kStageBytes;
                 // rows past the cache length are not fetched (their pages may not exist); the consumers clear V there
                 int nbox = 0;
                 for (int b = 0; b < boxes; ++b) nbox += (t0 + b * up.box_rows < kv_len) ? 1 : 0;
@@ -208,76 +237,69 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                             tma_load_5d_sw(stage + kOffKlo + r * kUmKvRegion + off, &up.klo_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
                     }
                 }
-            };
+            }
+        }
+    } else if (warp == 8) {
+        // ================= MMA issue (one lane) =================
+        if (lane == 0 && num_tiles > 0) {
             constexpr uint32_t idesc_qk = umma_idesc(kUmRows, kUmTile, false);
             constexpr uint32_t idesc_pv = umma_idesc(kUmRows, kHeadDim, true);
-            // descriptor low words of the operands at k-step 0 (stage 0 for K / V); every other one is a constant away
+            // descriptor low words of the B operands at k-step 0 of stage 0; every other one is a constant away
             constexpr uint32_t kHi = umma_desc_hi(1024);
-            const uint32_t qhi_lo = umma_desc_lo(sbase + kUmOffQhi, 16), qlo_lo = umma_desc_lo(sbase + kUmOffQlo, 16);
-            const uint32_t k_lo = umma_desc_lo(sbase + kUmOffStages, 16), klo_lo = umma_desc_lo(sbase + kUmOffStages + kOffKlo, 16);
-            const uint32_t v_lo = umma_desc_lo(sbase + kUmOffStages + kOffV, kUmKvRegion);
-            const uint32_t p_lo = umma_desc_lo(sbase + kUmOffP, 16);
-            auto issue_qk = [&](int tile) {   // waits for the tile's K, then S_g = Q K^T
-                const int st = tile % kStages, g = tile & 1;
+            const uint32_t k_lo = umma_desc_lo(sbase, 16), klo_lo = umma_desc_lo(sbase + kOffKlo, 16);
+            const uint32_t v_lo = umma_desc_lo(sbase + kOffV, kUmKvRegion);
+            auto issue_qk = [&](int tile) {   // waits for the tile's K, then S_b = Q K^T
+                const int st = tile % kStages, b = tile & 1;
                 mbar_wait(bar_gen + kBarKvFull + st, (tile / kStages) & 1, abort_flag, up.status);
                 tc_fence_after();
                 if (*abort_flag) return;
                 const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
-                const uint32_t d = tmem + 64u * g;
+                const uint32_t d = tmem + kUmColS + 64u * b;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    constexpr int dummy = 0; (void)dummy;
-                    const uint32_t koff = ((kk >> 2) * kUmKvRegion + (kk & 3) * 32) >> 4, qoff = ((kk >> 2) * kUmRegion + (kk & 3) * 32) >> 4;
+                    const uint32_t koff = ((kk >> 2) * kUmKvRegion + (kk & 3) * 32) >> 4;
                     const uint64_t kd = umma_desc_pack(k_lo + st_off + koff, kHi);
-                    const uint64_t qh = umma_desc_pack(qhi_lo + qoff, kHi);
-                    umma_f16(d, qh, kd, idesc_qk, kk > 0);
-                    umma_f16(d, umma_desc_pack(qlo_lo + qoff, kHi), kd, idesc_qk, 1);
-                    if (KSPLIT) umma_f16(d, qh, umma_desc_pack(klo_lo + st_off + koff, kHi), idesc_qk, 1);
+                    umma_f16_ts(d, tmem + kUmColQhi + 8u * kk, kd, idesc_qk, kk > 0);
+                    umma_f16_ts(d, tmem + kUmColQlo + 8u * kk, kd, idesc_qk, 1);
+                    if (KSPLIT) umma_f16_ts(d, tmem + kUmColQhi + 8u * kk, umma_desc_pack(klo_lo + st_off + koff, kHi), idesc_qk, 1);
                 }
-                umma_commit(bar(kBarSFull + g));
+                umma_commit(bar(kBarSFull + b));
             };
-            for (int t = 0; t < min(kStages, num_tiles); ++t) load_tile(t);
-            mbar_wait(bar_gen + kBarQFull, 0, abort_flag, up.status);   // Q rows are in shared memory
+            mbar_wait(bar_gen + kBarQFull, 0, abort_flag, up.status);   // Q rows are in tensor memory
             tc_fence_after();
             issue_qk(0);
-            if (num_tiles > 1) issue_qk(1);
             for (int j = 0; j < num_tiles; ++j) {
-                const int st = j % kStages, g = j & 1;
-                mbar_wait(bar_gen + kBarPFull + g, (j >> 1) & 1, abort_flag, up.status);   // P_g of tile j written, S_g read
+                const int st = j % kStages, b = j & 1;
+                if (j + 1 < num_tiles) issue_qk(j + 1);     // runs while the softmax of tile j is being computed
+                mbar_wait(bar_gen + kBarPFull + b, (j >> 1) & 1, abort_flag, up.status);   // P of tile j written over S_b
                 tc_fence_after();
                 if (!*abort_flag) {
-                    const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4), pg_lo = p_lo + g * ((2 * kUmRegion) >> 4);
-                    const uint32_t d = tmem + 128u + 128u * g;
+                    const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
+                    const uint32_t d = tmem + kUmColO, pa = tmem + kUmColS + 64u * b;
 #pragma unroll
                     for (int kt = 0; kt < 4; ++kt) {
                         const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
-                        umma_f16(d, umma_desc_pack(pg_lo + ((kt * 32) >> 4), kHi), vd, idesc_pv, (j > 1 || kt > 0) ? 1u : 0u);
-                        umma_f16(d, umma_desc_pack(pg_lo + ((kUmRegion + kt * 32) >> 4), kHi), vd, idesc_pv, 1u);
+                        umma_f16_ts(d, pa + 8u * kt, vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
+                        umma_f16_ts(d, pa + 32u + 8u * kt, vd, idesc_pv, 1u);
                     }
-                    umma_commit(bar(kBarOFull + g));       // O_g includes tile j; P_g free
+                    umma_commit(bar(kBarOFull));           // O includes tile j
                     umma_commit(bar(kBarKvEmpty + st));    // stage free
                 }
-                // with three stages tile j + 2 is already in flight and its scores are queued first; with two, tile j + 2
-                // reuses this stage and can only be fetched once the product above has drained
-                if (kStages >= 3 && j + 2 < num_tiles) issue_qk(j + 2);
-                if (j + kStages < num_tiles) {
-                    mbar_wait(bar_gen + kBarKvEmpty + st, (j / kStages) & 1, abort_flag, up.status);
-                    if (!*abort_flag) load_tile(j + kStages);
-                }
-                if (kStages < 3 && j + 2 < num_tiles) issue_qk(j + 2);
             }
         }
     } else {
-        // ================= softmax groups: thread = M row =================
-        const int g = warp >> 2, m = tid & 127;
+        // ================= softmax: thread (h, m) = columns [32h, 32h+32) of M row m =================
+        const int h = warp >> 2, m = tid & 127;
         const int qi = q0 + m / GROUP, head = kv_head * GROUP + m % GROUP;
         const bool row_ok = qi < p.seq_len;
         const int qpos = q_offset + qi;
-        // ---- Q row: fp32 -> [RoPE] -> * scale*log2e -> fp16 hi + lo, swizzled K-major; group g converts half of the row ----
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        // ---- Q row: fp32 -> [RoPE] -> * scale*log2e -> fp16 hi + lo words; half 0 stores the hi parts, half 1 the lo parts ----
         {
             const float* src = p.q + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
-#pragma unroll 1
-            for (int c8 = 4 * g; c8 < 4 * g + 4; ++c8) {          // dims [8 c8, 8 c8 + 8) and their partners + 64
+            uint32_t w[64];   // word c = dims 2c, 2c+1
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {          // dims [8 c8, 8 c8 + 8) and their rotation partners + 64
                 float a[8], b[8];
 #pragma unroll
                 for (int h4 = 0; h4 < 2; ++h4) {
@@ -286,7 +308,6 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     a[4 * h4] = x.x; a[4 * h4 + 1] = x.y; a[4 * h4 + 2] = x.z; a[4 * h4 + 3] = x.w;
                     b[4 * h4] = y.x; b[4 * h4 + 1] = y.y; b[4 * h4 + 2] = y.z; b[4 * h4 + 3] = y.w;
                 }
-                uint32_t ah[4], al[4], bh[4], bl[4];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     if (p.apply_rope) {
@@ -300,68 +321,75 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 }
 #pragma unroll
                 for (int e2 = 0; e2 < 4; ++e2) {
-                    ah[e2] = pack_half2(a[2 * e2], a[2 * e2 + 1]);
-                    bh[e2] = pack_half2(b[2 * e2], b[2 * e2 + 1]);
-                    const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&ah[e2]));
-                    const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&bh[e2]));
-                    al[e2] = pack_half2(a[2 * e2] - af.x, a[2 * e2 + 1] - af.y);
-                    bl[e2] = pack_half2(b[2 * e2] - bf.x, b[2 * e2 + 1] - bf.y);
+                    const uint32_t ah = pack_half2(a[2 * e2], a[2 * e2 + 1]), bh = pack_half2(b[2 * e2], b[2 * e2 + 1]);
+                    if (h == 0) {
+                        w[4 * c8 + e2] = ah;
+                        w[32 + 4 * c8 + e2] = bh;
+                    } else {
+                        const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&ah));
+                        const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&bh));
+                        w[4 * c8 + e2] = pack_half2(a[2 * e2] - af.x, a[2 * e2 + 1] - af.y);
+                        w[32 + 4 * c8 + e2] = pack_half2(b[2 * e2] - bf.x, b[2 * e2 + 1] - bf.y);
+                    }
                 }
-                const uint32_t off = um_swz(m, c8);
-                *reinterpret_cast<uint4*>(sgen + kUmOffQhi + off) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
-                *reinterpret_cast<uint4*>(sgen + kUmOffQlo + off) = make_uint4(al[0], al[1], al[2], al[3]);
-                *reinterpret_cast<uint4*>(sgen + kUmOffQhi + kUmRegion + off) = make_uint4(bh[0], bh[1], bh[2], bh[3]);
-                *reinterpret_cast<uint4*>(sgen + kUmOffQlo + kUmRegion + off) = make_uint4(bl[0], bl[1], bl[2], bl[3]);
             }
-            fence_async_smem();
+            const uint32_t qcol = tmem + (h == 0 ? kUmColQhi : kUmColQlo) + lane_base;
+            uint32_t half_words[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) half_words[c] = w[c];
+            tmem_st32_words(qcol, half_words);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) half_words[c] = w[32 + c];
+            tmem_st32_words(qcol + 32u, half_words);
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(bar_gen + kBarQFull);
         }
 
-        float m_run = -INFINITY, l_run = 0.f;
-        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t tmem_s = tmem + 64u * g + lane_base, tmem_o = tmem + 128u + 128u * g + lane_base;
-        uint8_t* pgen = sgen + kUmOffP + g * 2 * kUmRegion;
+        float m_run = -INFINITY, l_run = 0.f;   // m_run: maximum of the whole row; l_run: denominator of this thread's columns
+        const uint32_t tmem_o = tmem + kUmColO + 64u * h + lane_base;   // this thread's 64 columns of the O row
         const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
-        int my_tiles = 0;
-        for (int j = g; j < num_tiles; j += 2, ++my_tiles) {
-            const int t0 = j * kUmTile;
-            mbar_wait(bar_gen + kBarSFull + g, my_tiles & 1, abort_flag, up.status);
+        for (int j = 0; j < num_tiles; ++j) {
+            const int t0 = j * kUmTile + 32 * h, b = j & 1;
+            const uint32_t tmem_s = tmem + kUmColS + 64u * b + lane_base;
+            mbar_wait(bar_gen + kBarSFull + b, (j >> 1) & 1, abort_flag, up.status);
             tc_fence_after();
-            float s[64];
+            float s[32];
             {
-                uint32_t r0[32], r1[32];
-                tmem_ld32_nowait(tmem_s, r0);
-                tmem_ld32_nowait(tmem_s + 32u, r1);
+                uint32_t r0[32];
+                tmem_ld32_nowait(tmem_s + 32u * h, r0);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) { s[c] = __uint_as_float(r0[c]); s[32 + c] = __uint_as_float(r1[c]); }
+                for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(r0[c]);
             }
-            if (t0 + kUmTile - 1 > limit) {
+            if (t0 + 31 > limit) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
+                for (int c = 0; c < 32; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
             }
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 4; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            for (int c = 4; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m_run, mx);
+            xchg[(b * 2 + h) * 128 + m] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float m_new = fmaxf(m_run, fmaxf(mx, xchg[(b * 2 + (h ^ 1)) * 128 + m]));
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = fast_exp2(m_run - m_use);
             m_run = m_new;
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
+            for (int c = 0; c < 32; ++c) {
                 s[c] = fast_exp2(s[c] - m_use);
                 ps4[c & 3] += s[c];
             }
             l_run = fmaf(l_run, corr, (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-            // this group's previous product must be complete before O_g is rescaled and before P_g is overwritten
-            if (my_tiles > 0) {
-                mbar_wait(bar_gen + kBarOFull + g, (my_tiles - 1) & 1, abort_flag, up.status);
+            // the previous product must be complete before O is rescaled
+            if (j > 0) {
+                mbar_wait(bar_gen + kBarOFull, (j - 1) & 1, abort_flag, up.status);
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, corr != 1.f) && !*abort_flag) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                    for (int c0 = 0; c0 < 64; c0 += 32) {
                         float o[32];
                         tmem_ld32(tmem_o + c0, o);
 #pragma unroll
@@ -371,74 +399,57 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 }
             }
             // the last tile: V rows past the cache length were not fetched; clear them (0 * stale bits must not be NaN)
-            if (t0 + kUmTile > kv_len) {
+            if (j * kUmTile + kUmTile > kv_len) {
                 mbar_wait(bar_gen + kBarKvFull + j % kStages, (j / kStages) & 1, abort_flag, up.status);
-                uint8_t* vst = sgen + kUmOffStages + (j % kStages) * kStageBytes + kOffV;
-                const int first = kv_len - t0;
-                for (int idx = m; idx < (kUmTile - first) * 16; idx += 128) {
+                uint8_t* vst = sgen + (j % kStages) * kStageBytes + kOffV;
+                const int first = kv_len - j * kUmTile;
+                for (int idx = tid; idx < (kUmTile - first) * 16; idx += 256) {
                     const int row = first + idx / 16, part = idx % 16;    // 2 regions x 8 chunks
                     *reinterpret_cast<uint4*>(vst + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                fence_async_smem();
             }
+            // this thread's half of the P row over the S row: hi words in columns [16h, 16h+16), lo words in [32+16h, 32+16h+16)
+            {
+                uint32_t ph[16], pl[16];
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                uint32_t ph[4], pl[4];
-#pragma unroll
-                for (int e2 = 0; e2 < 4; ++e2) {
-                    const float x0 = s[8 * c8 + 2 * e2], x1 = s[8 * c8 + 2 * e2 + 1];
-                    ph[e2] = pack_half2(x0, x1);
-                    const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&ph[e2]));
-                    pl[e2] = pack_half2(x0 - hf.x, x1 - hf.y);
+                for (int c = 0; c < 16; ++c) {
+                    const float x0 = s[2 * c], x1 = s[2 * c + 1];
+                    ph[c] = pack_half2(x0, x1);
+                    const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&ph[c]));
+                    pl[c] = pack_half2(x0 - hf.x, x1 - hf.y);
                 }
-                const uint32_t off = um_swz(m, c8);
-                *reinterpret_cast<uint4*>(pgen + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                *reinterpret_cast<uint4*>(pgen + kUmRegion + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                // (the other half-row thread has read its half of S_b: it published its maximum before the barrier above)
+                tmem_st16_words(tmem_s + 16u * h, ph);
+                tmem_st16_words(tmem_s + 32u + 16u * h, pl);
+                tmem_st_wait();
             }
-            fence_async_smem();
             tc_fence_before();
-            mbar_arrive(bar_gen + kBarPFull + g);
+            mbar_arrive(bar_gen + kBarPFull + b);
         }
-        // ---- merge the two groups' partial results and write O / l; group g writes dims [64 g, 64 g + 64) ----
-        if (my_tiles > 0) {
-            mbar_wait(bar_gen + kBarOFull + g, (my_tiles - 1) & 1, abort_flag, up.status);
+        // ---- O / l: thread (h, m) writes dims [64h, 64h+64) of its row ----
+        if (num_tiles > 0) {
+            mbar_wait(bar_gen + kBarOFull, (num_tiles - 1) & 1, abort_flag, up.status);
             tc_fence_after();
         }
-        // (max, denominator) of each group's rows pass through the head of its own, now idle, P buffer
-        reinterpret_cast<float2*>(pgen)[m] = make_float2(m_run, l_run);
-        tc_fence_before();
+        xchg[512 + h * 128 + m] = l_run;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        tc_fence_after();
-        const float2 ml0 = reinterpret_cast<const float2*>(sgen + kUmOffP)[m];
-        const float2 ml1 = reinterpret_cast<const float2*>(sgen + kUmOffP + 2 * kUmRegion)[m];
-        const float m0 = ml0.x, l0 = ml0.y, m1 = ml1.x, l1 = ml1.y;
-        const float mm = fmaxf(m0, m1);
-        const float w0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mm);
-        const float lsum = l0 * w0 + l1 * w1;
+        const float lsum = l_run + xchg[512 + (h ^ 1) * 128 + m];
         const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-        const bool have0 = num_tiles > 0, have1 = num_tiles > 1;
-        float* dst = p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim;
-        const uint32_t tmem_o0 = tmem + 128u + lane_base, tmem_o1 = tmem + 256u + lane_base;
+        float* dst = p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim + 64 * h;
 #pragma unroll 1
-        for (int c0 = 64 * g; c0 < 64 * g + 64; c0 += 32) {
-            float o0[32], o1[32];
-            if (have0 && !*abort_flag) {
-                tmem_ld32(tmem_o0 + c0, o0);
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+            float o[32];
+            if (num_tiles > 0 && !*abort_flag) {
+                tmem_ld32(tmem_o + c0, o);
             } else {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) o0[c] = 0.f;
-            }
-            if (have1 && !*abort_flag) {
-                tmem_ld32(tmem_o1 + c0, o1);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o1[c] = 0.f;
+                for (int c = 0; c < 32; ++c) o[c] = 0.f;
             }
             if (row_ok) {
 #pragma unroll
                 for (int c = 0; c < 32; c += 4)
-                    *reinterpret_cast<float4*>(dst + c0 + c) =
-                        make_float4((o0[c] * w0 + o1[c] * w1) * inv, (o0[c + 1] * w0 + o1[c + 1] * w1) * inv,
-                                    (o0[c + 2] * w0 + o1[c + 2] * w1) * inv, (o0[c + 3] * w0 + o1[c + 3] * w1) * inv);
+                    *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c] * inv, o[c + 1] * inv, o[c + 2] * inv, o[c + 3] * inv);
             }
         }
     }
