@@ -8,17 +8,21 @@
 //                            barrier per tile), each writes its half of the P row back over S, and rescales its 64 columns
 //                            of the O row when the maximum moved.  Half a row per thread keeps the softmax of a tile
 //                            shorter than the tile's matrix products, which run meanwhile on the other S buffer.
-//   warp 8, one lane         issues every tcgen05.mma
+//   warp 8, one lane         issues the score products S_b = Q.K^T, as far ahead as the three S buffers allow
+//   warp 10, one lane        issues the products O += P_b.V as the P rows arrive; two issuing threads, because the waits
+//                            of a single one (about 450 clocks per tile) left the tensor pipe idle between batches.  Products of
+//                            different threads are not ordered by issue: S_b of tile j+3 waits for a commit after P.V of tile j
 //   warp 9, one lane         issues the TMA loads of the K / V tiles (64 tokens, ring of 6 or 4 stages); a thread of its own,
 //                            because issuing a tile's loads costs about as many clocks as issuing its products
-// Per 64-token tile j, b = j % 2:  S_b[128x64] = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims, N = 64
+// Per 64-token tile j, b = j % 3:  S_b[128x64] = Qhi.K^T + Qlo.K^T [+ Qhi.Klo^T]   8 k-steps of 16 dims, N = 64
 //                                  O[128x128] += Phi_b.V + Plo_b.V                   4 k-steps of 16 tokens, N = 128
 // (measured issue intervals of tcgen05.mma with M = 128, K = 16: 48 clocks at N = 64, 64 at N = 128, 127 at N = 256,
 // the same for an A operand in shared or tensor memory).
 // The A operands (Q, P) live in tensor memory: row r is lane r, column c holds elements 2c and 2c+1 as fp16, a
-// 16-element k-step is 8 columns.  Tensor memory (512 columns allocated): S_0, S_1 at 0 and 64 (P_b overwrites S_b in
-// place: hi parts in its first 32 columns, lo parts in the other 32; the products execute in issue order and S_b of
-// tile j+2 is issued after the P.V product of tile j), O at 128, Q hi at 256, Q lo at 320.
+// 16-element k-step is 8 columns.  Tensor memory (512 columns allocated): S_0, S_1, S_2 at 0, 64, 128 (P_b overwrites S_b
+// in place: hi parts in its first 32 columns, lo parts in the other 32; the products execute in issue order and S_b of
+// tile j+3 is issued after the P.V product of tile j), O at 192, Q hi at 320, Q lo at 384.  Issue order: S(j+2), then
+// O += P(j).V(j): the softmax of tile j has two tiles' worth of products to hide behind.
 // Q (pre-multiplied by scale*log2 e) and P enter as fp16 hi + lo pairs so that, with K and V exact in fp16, the result
 // keeps fp32 accuracy; the optional second K operand serves caches whose rows are expanded from fp32 (TurboQuant).
 // Shared-memory operand tiles use the 128-byte swizzle (what TMA writes with SWIZZLE_128B and what the matrix descriptors
@@ -35,9 +39,10 @@ namespace er {
 
 constexpr int kUmRows = 128;          // M rows per CTA
 constexpr int kUmTile = 64;           // tokens per K/V tile
-constexpr int kUmThreads = 320;
+constexpr int kUmThreads = 352;
 constexpr int kUmKvRegion = kUmTile * 128;          // 8 KiB: 64 tokens x 64 halves
-constexpr int kUmColS = 0, kUmColO = 128, kUmColQhi = 256, kUmColQlo = 320;   // tensor-memory columns
+constexpr int kUmColS = 0, kUmColO = 192, kUmColQhi = 320, kUmColQlo = 384;   // tensor-memory columns
+constexpr int kUmSBufs = 3;           // S / P buffers: the scores run two tiles ahead of the softmax
 __host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * kUmKvRegion; }   // K [Klo] V
 __host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 4 : 6; }
 __host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
@@ -159,8 +164,8 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     constexpr int kStageBytes = um_stage_bytes(KSPLIT);
     constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
     constexpr int kOffKlo = 2 * kUmKvRegion;
-    constexpr int kBarKvFull = 0, kBarKvEmpty = kStages, kBarSFull = 2 * kStages, kBarPFull = kBarSFull + 2, kBarOFull = kBarSFull + 4,
-                  kBarQFull = kBarSFull + 5, kNumBars = kBarSFull + 6;
+    constexpr int kBarKvFull = 0, kBarKvEmpty = kStages, kBarSFull = 2 * kStages, kBarPFull = kBarSFull + kUmSBufs,
+                  kBarSFree = kBarPFull + kUmSBufs, kBarOFull = kBarSFree + kUmSBufs, kBarQFull = kBarOFull + 1, kNumBars = kBarQFull + 1;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier block");
     extern __shared__ uint8_t um_smem_raw[];
     const PrefillParams& p = up.base;
@@ -189,7 +194,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(bar_gen + i, (i == kBarPFull || i == kBarPFull + 1 || i == kBarQFull) ? 256u : 1u);
+            mbar_init(bar_gen + i, ((i >= kBarPFull && i < kBarPFull + kUmSBufs) || i == kBarQFull) ? 256u : 1u);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -249,7 +254,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
             const uint32_t k_lo = umma_desc_lo(sbase, 16), klo_lo = umma_desc_lo(sbase + kOffKlo, 16);
             const uint32_t v_lo = umma_desc_lo(sbase + kOffV, kUmKvRegion);
             auto issue_qk = [&](int tile) {   // waits for the tile's K, then S_b = Q K^T
-                const int st = tile % kStages, b = tile & 1;
+                const int st = tile % kStages, b = tile % kUmSBufs;
                 mbar_wait(bar_gen + kBarKvFull + st, (tile / kStages) & 1, abort_flag, up.status);
                 tc_fence_after();
                 if (*abort_flag) return;
@@ -267,24 +272,34 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
             };
             mbar_wait(bar_gen + kBarQFull, 0, abort_flag, up.status);   // Q rows are in tensor memory
             tc_fence_after();
-            issue_qk(0);
+            for (int t = 0; t < num_tiles; ++t) {
+                // S_b still holds the P rows of tile t - 3 until their product has been executed
+                if (t >= kUmSBufs) mbar_wait(bar_gen + kBarSFree + t % kUmSBufs, ((t / kUmSBufs) - 1) & 1, abort_flag, up.status);
+                issue_qk(t);
+            }
+        }
+    } else if (warp == 10) {
+        // ================= O += P.V issue (one lane) =================
+        if (lane == 0 && num_tiles > 0) {
+            constexpr uint32_t idesc_pv = umma_idesc(kUmRows, kHeadDim, true);
+            constexpr uint32_t kHi = umma_desc_hi(1024);
+            const uint32_t v_lo = umma_desc_lo(sbase + kOffV, kUmKvRegion);
             for (int j = 0; j < num_tiles; ++j) {
-                const int st = j % kStages, b = j & 1;
-                if (j + 1 < num_tiles) issue_qk(j + 1);     // runs while the softmax of tile j is being computed
-                mbar_wait(bar_gen + kBarPFull + b, (j >> 1) & 1, abort_flag, up.status);   // P of tile j written over S_b
+                const int st = j % kStages, b = j % kUmSBufs;
+                mbar_wait(bar_gen + kBarPFull + b, (j / kUmSBufs) & 1, abort_flag, up.status);   // P of tile j written over S_b
                 tc_fence_after();
-                if (!*abort_flag) {
-                    const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
-                    const uint32_t d = tmem + kUmColO, pa = tmem + kUmColS + 64u * b;
+                if (*abort_flag) break;
+                const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
+                const uint32_t d = tmem + kUmColO, pa = tmem + kUmColS + 64u * b;
 #pragma unroll
-                    for (int kt = 0; kt < 4; ++kt) {
-                        const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
-                        umma_f16_ts(d, pa + 8u * kt, vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
-                        umma_f16_ts(d, pa + 32u + 8u * kt, vd, idesc_pv, 1u);
-                    }
-                    umma_commit(bar(kBarOFull));           // O includes tile j
-                    umma_commit(bar(kBarKvEmpty + st));    // stage free
+                for (int kt = 0; kt < 4; ++kt) {
+                    const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
+                    umma_f16_ts(d, pa + 8u * kt, vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
+                    umma_f16_ts(d, pa + 32u + 8u * kt, vd, idesc_pv, 1u);
                 }
+                umma_commit(bar(kBarOFull));           // O includes tile j
+                umma_commit(bar(kBarKvEmpty + st));    // stage free
+                umma_commit(bar(kBarSFree + b));       // S_b free
             }
         }
     } else {
@@ -350,9 +365,9 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         const uint32_t tmem_o = tmem + kUmColO + 64u * h + lane_base;   // this thread's 64 columns of the O row
         const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
         for (int j = 0; j < num_tiles; ++j) {
-            const int t0 = j * kUmTile + 32 * h, b = j & 1;
+            const int t0 = j * kUmTile + 32 * h, b = j % kUmSBufs, xb = j & 1;
             const uint32_t tmem_s = tmem + kUmColS + 64u * b + lane_base;
-            mbar_wait(bar_gen + kBarSFull + b, (j >> 1) & 1, abort_flag, up.status);
+            mbar_wait(bar_gen + kBarSFull + b, (j / kUmSBufs) & 1, abort_flag, up.status);
             tc_fence_after();
             float s[32];
             {
@@ -370,9 +385,9 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
 #pragma unroll
             for (int c = 4; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            xchg[(b * 2 + h) * 128 + m] = mx;
+            xchg[(xb * 2 + h) * 128 + m] = mx;
             asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float m_new = fmaxf(m_run, fmaxf(mx, xchg[(b * 2 + (h ^ 1)) * 128 + m]));
+            const float m_new = fmaxf(m_run, fmaxf(mx, xchg[(xb * 2 + (h ^ 1)) * 128 + m]));
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = fast_exp2(m_run - m_use);
             m_run = m_new;
