@@ -406,6 +406,15 @@ def test_gqa_kernel_operator_matches_cpu_gqa(er, oracle):
     assert max_rel_err(got, want) < TOL
     got = gk.execute_f16kv(q, k16, v16, S, D, H, Hkv, causal=False, kv_seq_len=T)
     assert max_rel_err(got, oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=False)) < TOL
+    # a chunk large enough for the tcgen05 kernel (S * group >= 128), ragged against its 64-token tiles and 128-row CTAs
+    S, T, off = 200, 333, 133
+    q = normal_f16(rng, (S, H, D))
+    k16, v16 = normal_f16(rng, (T, Hkv, D)).astype(np.float16), normal_f16(rng, (T, Hkv, D)).astype(np.float16)
+    got = gk.execute_f16kv(q, k16, v16, S, D, H, Hkv, causal=True, kv_seq_len=T, q_offset=off)
+    want = oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=True, q_offset=off, threads=8)
+    assert max_rel_err(got, want) < TOL
+    got = gk.execute_f16kv(q, k16, v16, S, D, H, Hkv, causal=False, kv_seq_len=T)
+    assert max_rel_err(got, oracle.gqa_f16kv(q, k16.view(np.uint16), v16.view(np.uint16), causal=False, threads=8)) < TOL
 
 
 # --------------------------------------------------------------------------------------------- TurboQuant cache + decode
@@ -605,6 +614,11 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
     ("paged", 64, 32, 8, 1000, 130),          # configuration-4-shaped: 32 q / 8 kv heads, 64-token pages
     ("token_major", 0, 8, 8, 0, 64),          # group 1, prompt from an empty cache
     ("paged", 16, 16, 2, 129, 5),             # group 8
+    ("token_major", 0, 8, 8, 70, 150),        # group 1 on the tcgen05 kernel, token-major tensor maps
+    ("paged", 16, 16, 2, 1000, 40),           # group 8 on the tcgen05 kernel, 16-token pages (four TMA boxes per tile)
+    ("paged", 32, 16, 8, 63, 1),              # single row: falls back to the mma.sync kernel
+    ("head_major", 0, 32, 8, 700, 300),       # several CTAs per kv head
+    ("head_major", 0, 32, 8, 2000, 513),      # long context
 ])
 def test_chunked_prefill_attention(er, oracle, torch, layout, page_size, Hq, Hkv, ctx, S):
     """er_kv_attention_prefill: a chunk of S new tokens appended after `ctx` cached tokens; query row r (position ctx + r)
@@ -637,7 +651,12 @@ def test_chunked_prefill_attention(er, oracle, torch, layout, page_size, Hq, Hkv
     want = oracle.gqa_f16kv(q_rot, kc, vc, causal=True, q_offset=ctx, threads=8)
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
-    assert max_rel_err(got, want) < TOL
+    if ctx + S > 2048:
+        # thousands of fp32 accumulation steps leave ~2e-7 absolute noise on outputs of size 0.03: bound the error by
+        # the head row's largest output instead of element by element
+        assert attention_err(got, want) < 2e-5
+    else:
+        assert max_rel_err(got, want) < TOL
     # explicit offset form gives the same rows
     out2 = torch.empty_like(out)
     cache.attention_prefill(layer, 0, dev(torch, q), out2, Hq, S, sp, q_offset=ctx)
