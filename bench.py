@@ -54,6 +54,15 @@ WORKLOADS = {
     "cfg3": dict(name="cfg3: Llama-3.1-8B shape, 32 layers, batch 64, fp16 KV in 16-token pages, context U[1024,16384]",
                  layers=32, batch=64, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
                  page_size=16, theta=5.0e5),
+    # BASELINE.json configs[4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
+    # already in the cache (Qwen3-4B heads, TurboQuant turbo4/turbo4 rows in 64-token pages); tensor-core bound
+    "cfg4_prefill": dict(name="cfg4 prefill chunk: Qwen3-4B heads, 2048 query rows at the end of a 131072-token context, "
+                              "turbo4/turbo4 in 64-token pages, one layer, one sequence per step",
+                         prefill=True, heads=32, kv_heads=8, ctx=131072 - 2048, chunk=2048, precision="turboquant", kbits=4, vbits=4,
+                         norm="float16", layout="paged", page_size=64, theta=1.0e6),
+    "cfg4_prefill_f16": dict(name="cfg4 prefill chunk on an fp16 cache (same shape, 32768-token context)",
+                             prefill=True, heads=32, kv_heads=8, ctx=32768, chunk=2048, precision="float16", layout="paged",
+                             page_size=64, theta=1.0e6),
 }
 D = 128
 
@@ -347,7 +356,7 @@ def run_ours(args, w, lens):
     for s in range(W):
         cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
     barrier()
-    launches0 = er.lib().er_kernel_launch_count()
+    launches0 = er.lib().er.lib().er_kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for s in range(K):
@@ -355,7 +364,7 @@ def run_ours(args, w, lens):
         cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
     e1.record(stream)
     barrier()
-    launches = er.lib().er_kernel_launch_count() - launches0
+    launches = er.lib().er.lib().er_kernel_launch_count() - launches0
     ms_total = max_over_ranks(e0.elapsed_time(e1), device="cuda")
     # load window for the clock samples: the same steps again (positions rewound so the cache capacity holds)
     t_load = time.perf_counter()
@@ -506,9 +515,75 @@ def run_ours(args, w, lens):
         dist.destroy_process_group()
 
 
+def run_prefill(args, w):
+    """Chunked-prefill attention (er_kv_attention_prefill): step = one chunk of one sequence and one layer.  Useful FLOPs
+    4 * S * (ctx + (S + 1) / 2) * Hq * 128 (causal), against the measured cuBLAS bf16 peak."""
+    import torch
+    import edgerunner_b200 as er
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    H, Hkv, ctx, S = w["heads"], w["kv_heads"], w["ctx"], w["chunk"]
+    T = ctx + S
+    n_pages = (T + w["page_size"] - 1) // w["page_size"]
+    kw = dict(layout=er.Layout.paged, page_size=w["page_size"], num_pages=n_pages)
+    if w["precision"] == "float16":
+        cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16, **kw)
+    else:
+        cache = er.KVCache(T, 1, Hkv, D, er.Precision.turboquantV2, key_type=w["kbits"], value_type=w["vbits"],
+                           norm_format=er.NormFormat.float16, **kw)
+    cache.set_block_table(0, np.random.Generator(np.random.PCG64(4)).permutation(n_pages).astype(np.int32))
+    sp = er.step_params(rope_theta=w["theta"])
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for s0 in range(0, T, 8192):
+        n = min(8192, T - s0)
+        cache.write_rows(0, 0, s0, n, torch.randn((n, Hkv, D), device="cuda", generator=g).half().float(),
+                         torch.randn((n, Hkv, D), device="cuda", generator=g).half().float(), sp)
+    q = torch.randn((S, H, D), device="cuda", generator=g).half().float()
+    out = torch.empty((S, H, D), device="cuda")
+    K, W = args.steps, max(args.warmup, 0)
+    for _ in range(W):
+        cache.attention_prefill(0, 0, q, out, H, S, sp)
+    torch.cuda.synchronize()
+    launches0 = er.lib().er_kernel_launch_count()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        cache.attention_prefill(0, 0, q, out, H, S, sp)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / K
+    flops = 4.0 * S * (ctx + (S + 1) / 2.0) * H * D
+    tflops = flops / ms / 1e9
+    peak = None
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        peak, peak_src = 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+    print(json.dumps({
+        "metric": "prefill_attention_tflops", "value": round(tflops, 1), "unit": "TFLOP/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms, "higher_is_better": True, "dtype": "f16 operands (hi+lo pairs), f32 accumulate", "data": "synthetic",
+        "query_tokens_per_s_per_layer": round(S / ms * 1e3, 1),
+        "config": {"workload": w["name"], "q_heads": H, "kv_heads": Hkv, "context": ctx, "chunk": S,
+                   "l2": "K/V of a kv head are shared by the chunk's CTAs through L2 by design; inputs exceed L2 at this context"},
+        "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tflops / peak, 4),
+                     "peak_source": peak_src, "traffic": None,
+                     "note": "useful FLOPs; the kernel issues twice as many (fp16 hi+lo operand pairs)"},
+        "gpu_launches": int(er.lib().er_kernel_launch_count() - launches0), "clocks": clocks}))
+
+
 def main():
     args = parse_args()
     w = WORKLOADS[args.workload]
+    if w.get("prefill"):
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the prefill workloads are measured on the GPU path only"}))
+            return
+        run_prefill(args, w)
+        return
     lens = sequence_lengths(w)
     if args.impl == "reference":
         run_reference_impl(args, w, lens)
