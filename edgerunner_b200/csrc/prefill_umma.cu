@@ -77,7 +77,7 @@ int um_launch_group(const UmmaPrefillParams& up, int num_kv_heads, cudaStream_t 
 
 int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream) {
     if (status == nullptr) return kNotBuilt;
-    int box_rows = kUmTile;
+    int box_rows = 64;
     if (!p.addr.token_major && p.addr.pages_per_seq > 0) {
         box_rows = p.addr.page_size % 64 == 0 ? 64 : p.addr.page_size % 32 == 0 ? 32 : 16;
         if (p.addr.page_size % 16 != 0) return kNotBuilt;

@@ -38,13 +38,14 @@
 namespace er {
 
 constexpr int kUmRows = 128;          // M rows per CTA
-constexpr int kUmTile = 64;           // tokens per K/V tile
+__host__ __device__ constexpr int um_tile(bool ksplit) { return ksplit ? 64 : 128; }   // tokens per K/V tile
 constexpr int kUmThreads = 352;
-constexpr int kUmKvRegion = kUmTile * 128;          // 8 KiB: 64 tokens x 64 halves
-constexpr int kUmColS = 0, kUmColO = 192, kUmColQhi = 320, kUmColQlo = 384;   // tensor-memory columns
-constexpr int kUmSBufs = 3;           // S / P buffers: the scores run two tiles ahead of the softmax
-__host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * kUmKvRegion; }   // K [Klo] V
-__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 4 : 6; }
+__host__ __device__ constexpr int um_kv_region(bool ksplit) { return um_tile(ksplit) * 128; }   // tile tokens x 64 halves
+constexpr int kUmColS = 0, kUmColO = 256, kUmColQhi = 384, kUmColQlo = 448;   // tensor-memory columns
+// S / P buffers: two of 128 columns, or three of 64 with the second key operand (whose stages are half again as large)
+__host__ __device__ constexpr int um_sbufs(bool ksplit) { return ksplit ? 3 : 2; }
+__host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * um_kv_region(ksplit); }   // K [Klo] V
+__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 4 : 3; }
 __host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
     return um_stages(ksplit) * um_stage_bytes(ksplit) + 256 + 3072 + 1024;   // + barriers, (max, denominator) exchange, alignment slack
 }
@@ -162,6 +163,8 @@ template <int GROUP, bool KSPLIT>
 __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __grid_constant__ UmmaPrefillParams up) {
     constexpr int kStages = um_stages(KSPLIT);
     constexpr int kStageBytes = um_stage_bytes(KSPLIT);
+    constexpr int kUmTile = um_tile(KSPLIT), kUmKvRegion = um_kv_region(KSPLIT), kUmSBufs = um_sbufs(KSPLIT);
+    constexpr int kHalfCols = kUmTile / 2;     // S columns per softmax thread = P words per row and part
     constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
     constexpr int kOffKlo = 2 * kUmKvRegion;
     constexpr int kBarKvFull = 0, kBarKvEmpty = kStages, kBarSFull = 2 * kStages, kBarPFull = kBarSFull + kUmSBufs,
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 tc_fence_after();
                 if (*abort_flag) return;
                 const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
-                const uint32_t d = tmem + kUmColS + 64u * b;
+                const uint32_t d = tmem + kUmColS + static_cast<uint32_t>(kUmTile) * b;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t koff = ((kk >> 2) * kUmKvRegion + (kk & 3) * 32) >> 4;
@@ -290,12 +293,12 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 tc_fence_after();
                 if (*abort_flag) break;
                 const uint32_t st_off = static_cast<uint32_t>(st) * (kStageBytes >> 4);
-                const uint32_t d = tmem + kUmColO, pa = tmem + kUmColS + 64u * b;
+                const uint32_t d = tmem + kUmColO, pa = tmem + kUmColS + static_cast<uint32_t>(kUmTile) * b;
 #pragma unroll
-                for (int kt = 0; kt < 4; ++kt) {
+                for (int kt = 0; kt < kUmTile / 16; ++kt) {
                     const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
                     umma_f16_ts(d, pa + 8u * kt, vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
-                    umma_f16_ts(d, pa + 32u + 8u * kt, vd, idesc_pv, 1u);
+                    umma_f16_ts(d, pa + kHalfCols + 8u * kt, vd, idesc_pv, 1u);
                 }
                 umma_commit(bar(kBarOFull));           // O includes tile j
                 umma_commit(bar(kBarKvEmpty + st));    // stage free
@@ -365,25 +368,29 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         const uint32_t tmem_o = tmem + kUmColO + 64u * h + lane_base;   // this thread's 64 columns of the O row
         const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
         for (int j = 0; j < num_tiles; ++j) {
-            const int t0 = j * kUmTile + 32 * h, b = j % kUmSBufs, xb = j & 1;
-            const uint32_t tmem_s = tmem + kUmColS + 64u * b + lane_base;
+            const int t0 = j * kUmTile + kHalfCols * h, b = j % kUmSBufs, xb = j & 1;
+            const uint32_t tmem_s = tmem + kUmColS + static_cast<uint32_t>(kUmTile) * b + lane_base;
             mbar_wait(bar_gen + kBarSFull + b, (j / kUmSBufs) & 1, abort_flag, up.status);
             tc_fence_after();
-            float s[32];
+            float s[kHalfCols];
             {
-                uint32_t r0[32];
-                tmem_ld32_nowait(tmem_s + 32u * h, r0);
+                uint32_t r0[32], r1[32];
+                tmem_ld32_nowait(tmem_s + kHalfCols * h, r0);
+                if (kHalfCols == 64) tmem_ld32_nowait(tmem_s + kHalfCols * h + 32u, r1);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(r0[c]);
+                for (int c = 0; c < 32; ++c) {
+                    s[c] = __uint_as_float(r0[c]);
+                    if (kHalfCols == 64) s[(32 + c) % kHalfCols] = __uint_as_float(r1[c]);
+                }
             }
-            if (t0 + 31 > limit) {
+            if (t0 + kHalfCols - 1 > limit) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
+                for (int c = 0; c < kHalfCols; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
             }
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 4; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            for (int c = 4; c < kHalfCols; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             xchg[(xb * 2 + h) * 128 + m] = mx;
             asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -393,7 +400,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
             m_run = m_new;
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < kHalfCols; ++c) {
                 s[c] = fast_exp2(s[c] - m_use);
                 ps4[c & 3] += s[c];
             }
@@ -424,19 +431,26 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 }
                 fence_async_smem();
             }
-            // this thread's half of the P row over the S row: hi words in columns [16h, 16h+16), lo words in [32+16h, 32+16h+16)
+            // this thread's half of the P row over the S row: hi words in columns [W h, W h + W), lo words W columns further,
+            // W = kHalfCols / 2 words per thread and part; hi parts of the whole row fill the buffer's first half
+            // (the other half-row thread has read its half of S_b: it published its maximum before the barrier above)
             {
-                uint32_t ph[16], pl[16];
+                constexpr int W = kHalfCols / 2;
+                uint32_t ph[W], pl[W];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
+                for (int c = 0; c < W; ++c) {
                     const float x0 = s[2 * c], x1 = s[2 * c + 1];
                     ph[c] = pack_half2(x0, x1);
                     const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&ph[c]));
                     pl[c] = pack_half2(x0 - hf.x, x1 - hf.y);
                 }
-                // (the other half-row thread has read its half of S_b: it published its maximum before the barrier above)
-                tmem_st16_words(tmem_s + 16u * h, ph);
-                tmem_st16_words(tmem_s + 32u + 16u * h, pl);
+                if constexpr (W == 32) {
+                    tmem_st32_words(tmem_s + W * h, ph);
+                    tmem_st32_words(tmem_s + kHalfCols + W * h, pl);
+                } else {
+                    tmem_st16_words(tmem_s + W * h, ph);
+                    tmem_st16_words(tmem_s + kHalfCols + W * h, pl);
+                }
                 tmem_st_wait();
             }
             tc_fence_before();
