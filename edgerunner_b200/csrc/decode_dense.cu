@@ -1,5 +1,6 @@
 // Instantiations of the persistent flash-decode kernel for fp16 rows (GQA group sizes 1, 2, 4).
 #include "launchers.h"
+#include "tmap.h"
 
 namespace er {
 
@@ -25,27 +26,9 @@ int decode_dense_tile_tokens(int group) {
 }
 
 namespace {
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_entry() {
-    static EncodeTiledFn fn = [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
-            status != cudaDriverEntryPointSuccess) {
-            cudaGetLastError();
-            ptr = nullptr;
-        }
-        return reinterpret_cast<EncodeTiledFn>(ptr);
-    }();
-    return fn;
-}
-
 bool encode_one(CUtensorMap* map, const uint8_t* base, int64_t layer_stride, int tile, uint64_t layers, uint64_t seqs, uint64_t slots,
                 uint64_t kv_heads) {
-    EncodeTiledFn fn = encode_tiled_entry();
+    EncodeTiledFn fn = tensor_map_encode_entry();
     if (fn == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) return false;
     const cuuint64_t row = kRowBytesF16;
     const cuuint64_t dims[5] = {kHeadDim, kv_heads, slots, seqs, layers};

@@ -3,33 +3,16 @@
 #include "prefill_umma.cuh"
 
 #include "launchers.h"
+#include "tmap.h"
 
 namespace er {
 
 namespace {
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn um_encode_entry() {
-    static EncodeTiledFn fn = [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
-            status != cudaDriverEntryPointSuccess) {
-            cudaGetLastError();
-            ptr = nullptr;
-        }
-        return reinterpret_cast<EncodeTiledFn>(ptr);
-    }();
-    return fn;
-}
-
 // fp16 rows [outer][...][128]; box = 64 dims x box_rows tokens, 128-byte swizzle.
 //   token-major: dims {128, kv heads, slots, seqs, 1}        box {64, 1, box_rows, 1, 1}
 //   page-major : dims {128, page tokens, kv heads, pages, 1}  box {64, box_rows, 1, 1, 1}
 bool um_encode(CUtensorMap* map, const uint8_t* base, const KVAddressing& a, uint64_t outer_extent, int box_rows) {
-    EncodeTiledFn fn = um_encode_entry();
+    EncodeTiledFn fn = tensor_map_encode_entry();
     if (fn == nullptr || base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) return false;
     const cuuint64_t row = 256, hkv = static_cast<cuuint64_t>(a.num_kv_heads);
     cuuint64_t dims[5], strides[4];
