@@ -47,6 +47,11 @@ WORKLOADS = {
     "cfg2": dict(name="cfg2: Qwen3-0.6B shape, 28 layers, batch 8, TurboQuant turbo4 K / turbo3 V, fp16 norms, context 32768",
                  layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3, norm="float16",
                  layout="head_major", theta=1.0e6, outliers=True),
+    # next-tier row of the scope table: the q8_0 KV format on the cfg1 shape
+    "cfg1_q8": dict(name="cfg1 shape with a q8_0 KV cache (34-byte blocks of 32: fp16 scale + int8), context 4096",
+                    layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="q8_0", layout="head_major", theta=1.0e6),
+    "cfg1_q8_long": dict(name="cfg1 shape with a q8_0 KV cache at context 32768, batch 8",
+                         layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="q8_0", layout="head_major", theta=1.0e6),
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",
                          layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3,
                          norm="float16", layout="head_major", theta=1.0e6, outliers=True),
@@ -101,6 +106,8 @@ def row_bytes(w):
     """Algorithmic cache bytes per (token, kv head): K row + V row (+ stored norms)."""
     if w["precision"] == "float16":
         return 2 * D * 2
+    if w["precision"] == "q8_0":
+        return 2 * (D // 32) * 34
     nb = 2 if w.get("norm", "float32") == "float16" else 4
     return (D * w["kbits"] + 31) // 32 * 4 + (D * w["vbits"] + 31) // 32 * 4 + 2 * nb
 
@@ -188,7 +195,8 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
     threads = oracle.max_threads()
     L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
     rng = np.random.Generator(np.random.PCG64(7))
-    turbo = w["precision"] != "float16"
+    turbo = w["precision"] == "turboquant"
+    q8 = w["precision"] == "q8_0"
     max_len = max(lens) + 64
     # one layer's cache per sampled layer; lengths as in the workload
     def make_layer():
@@ -198,6 +206,9 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
                          kn=np.abs(rng.standard_normal(max_len * Hkv).astype(np.float32)) + 10,
                          vc=rng.integers(0, 2 ** 32, size=(max_len * Hkv, vw), dtype=np.uint32),
                          vn=np.abs(rng.standard_normal(max_len * Hkv).astype(np.float32)) + 10) for _ in range(B)]
+        if q8:
+            return [dict(k=rng.integers(0, 256, size=(max_len, Hkv, 136), dtype=np.uint8),
+                         v=rng.integers(0, 256, size=(max_len, Hkv, 136), dtype=np.uint8)) for _ in range(B)]
         return [dict(k=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16),
                      v=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16)) for _ in range(B)]
 
@@ -210,6 +221,8 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
             if turbo:
                 oracle.decode_step_turboquant(q, k, v, c["kc"], c["kn"], w["kbits"], c["vc"], c["vn"], w["vbits"], lens[b] + s,
                                               w["theta"], norm_fp16=w.get("norm") == "float16", threads=threads)
+            elif q8:
+                oracle.decode_step_q8(q, k, v, c["k"], c["v"], lens[b] + s, w["theta"], threads=threads)
             else:
                 oracle.decode_step_f16(q, k, v, c["k"], c["v"], lens[b] + s, w["theta"], threads=threads)
 
@@ -270,6 +283,8 @@ def build_cache(er, torch, w, lens, extra_tokens):
         kw = dict(page_size=ps, num_pages=need)
     if w["precision"] == "float16":
         cache = er.KVCache(cap, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, **kw)
+    elif w["precision"] == "q8_0":
+        cache = er.KVCache(cap, L, Hkv, D, er.Precision.q8_0, max_batch=B, layout=layout, **kw)
     else:
         nf = er.NormFormat.float16 if w.get("norm") == "float16" else er.NormFormat.float32
         cache = er.KVCache(cap, L, Hkv, D, er.Precision.turboquantV2, key_type=w["kbits"], value_type=w["vbits"], norm_format=nf,

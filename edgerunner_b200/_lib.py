@@ -65,6 +65,8 @@ SYMBOLS = {
     "er_kv_append_f16": (_i32, [_vp, _u32, _u32, _vp, _vp, _sz]),
     "er_kv_retrieve": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp, _sz, C.POINTER(_u32)]),
     "er_kv_retrieve_decoded_turboquant": (_i32, [_vp, _u32, _u32, _vp, _vp, _sz, C.POINTER(_u32)]),
+    "er_kv_retrieve_decoded_q8_0": (_i32, [_vp, _u32, _u32, _vp, _vp, _sz, C.POINTER(_u32)]),
+    "er_kv_retrieve_q8_0_rows": (_i32, [_vp, _u32, _u32, _vp, _vp, _sz, C.POINTER(_u32)]),
     "er_kv_retrieve_turboquant_rows": (_i32, [_vp, _u32, _u32, C.c_int, _vp, _vp, _vp, _vp, _sz, C.POINTER(_u32)]),
     "er_kv_device_buffers": (_i32, [_vp, _u32, C.POINTER(er_kv_buffers)]),
     "er_kv_cache_params": (_i32, [_vp, _u32, _u32, C.POINTER(ERKVCacheParams)]),
@@ -75,6 +77,7 @@ SYMBOLS = {
     "er_kv_get_block_table": (_i32, [_vp, _u32, _vp, _u32, C.POINTER(_u32)]),
     "er_rope_neox_f32": (_i32, [_vp, _vp, C.POINTER(ERRoPEParams), _vp]),
     "er_rope_neox_f32_to_f16": (_i32, [_vp, _vp, C.POINTER(ERRoPEParams), _vp]),
+    "er_quantize_q8_0_rows": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "er_turboquant_quantize_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "er_gqa_attention_f16kv": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),

@@ -20,6 +20,7 @@
 #include "er_common.cuh"
 #include "launchers.h"
 #include "prefill.cuh"
+#include "q8.cuh"
 #include "turboquant.cuh"
 
 using namespace er;
@@ -156,6 +157,7 @@ struct er_kv {
     int pool_pages = 0;           // pages per layer
     int pages_per_seq = 0;        // block-table stride (0 = identity addressing)
     bool token_major = false;
+    bool q8 = false;              // q8_0 rows: int8 part in the K / V slabs, four fp16 scales per row in the side slabs
     uint8_t* k_slab = nullptr;
     uint8_t* v_slab = nullptr;
     uint8_t* kn_slab = nullptr;
@@ -254,6 +256,16 @@ int32_t launch_append(er_kv* kv, AppendParams& ap, cudaStream_t stream) {
         return launch_turbo_append(tp, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), stream,
                                    check_launch);
     }
+    if (kv->q8) {
+        Q8AppendParams qp;
+        qp.base = ap;
+        qp.ks_base = kv->kn_slab;
+        qp.vs_base = kv->vn_slab;
+        qp.s_layer_stride_bytes = kv->n_layer_stride;
+        const int64_t jobs = 2 * static_cast<int64_t>(ap.rows) * kv->cfg.num_kv_heads;
+        q8_append_kernel<<<static_cast<unsigned>((jobs + 7) / 8), 256, 0, stream>>>(qp);
+        return check_launch("q8_append_kernel");
+    }
     if (kv->cfg.precision == ER_KV_FLOAT16)
         append_rope_dense_kernel<__half><<<ap.rows, 128, 0, stream>>>(ap);
     else
@@ -310,8 +322,8 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
     if (c->max_seq_len == 0 || c->num_layers == 0 || c->num_kv_heads == 0 || c->head_dim == 0)
         return fail(ER_ERR_SHAPE, "zero-sized cache dimension");
     switch (c->precision) {
-        case ER_KV_FLOAT32: case ER_KV_FLOAT16: case ER_KV_TURBOQUANT_V2: break;
-        case ER_KV_FLOAT8: case ER_KV_Q8_0: case ER_KV_TURBOQUANT_BALANCED: case ER_KV_TURBOQUANT_AGGRESSIVE:
+        case ER_KV_FLOAT32: case ER_KV_FLOAT16: case ER_KV_TURBOQUANT_V2: case ER_KV_Q8_0: break;
+        case ER_KV_FLOAT8: case ER_KV_TURBOQUANT_BALANCED: case ER_KV_TURBOQUANT_AGGRESSIVE:
             return fail(ER_ERR_UNSUPPORTED_STORAGE, "precision %u is outside this backend's scope", c->precision);
         default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
     }
@@ -321,6 +333,7 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
     if (kv->cfg.max_batch == 0) kv->cfg.max_batch = 1;
     if (static_cast<uint64_t>(kv->cfg.num_layers) * kv->cfg.max_batch > 1u << 20) { delete kv; return fail(ER_ERR_SHAPE, "layers*batch too large"); }
     kv->turbo = c->precision == ER_KV_TURBOQUANT_V2;
+    kv->q8 = c->precision == ER_KV_Q8_0;
     auto bail = [&](int32_t rc) { er_kv_destroy(kv); return rc; };
     if (cudaGetDevice(&kv->device) != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cudaGetDevice"));
     cudaDeviceGetAttribute(&kv->num_sms, cudaDevAttrMultiProcessorCount, kv->device);
@@ -332,6 +345,12 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         kv->k_row_bytes = tq_code_words(static_cast<int>(c->key_type)) * 4;
         kv->v_row_bytes = tq_code_words(static_cast<int>(c->value_type)) * 4;
         kv->norm_bytes = c->norm_format == ER_TQ_NORM_FLOAT16 ? 2 : 4;
+        if (kv->cfg.layout == ER_KV_LAYOUT_TOKEN_MAJOR) kv->cfg.layout = ER_KV_LAYOUT_HEAD_MAJOR;
+    } else if (kv->q8) {
+        // KVCache.resolvedStorageKind: headDim % 32 == 0 (KVCache.swift:764-768); the kernels here are built for 128
+        if (c->head_dim != kHeadDim) return bail(fail(ER_ERR_UNSUPPORTED_STORAGE, "q8_0 storage is built for head_dim 128"));
+        kv->k_row_bytes = kv->v_row_bytes = kQ8RowBytes;
+        kv->norm_bytes = kQ8ScaleBytes;
         if (kv->cfg.layout == ER_KV_LAYOUT_TOKEN_MAJOR) kv->cfg.layout = ER_KV_LAYOUT_HEAD_MAJOR;
     } else {
         kv->elem_bytes = c->precision == ER_KV_FLOAT32 ? 4 : 2;
@@ -369,7 +388,8 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         return cudaMemset(*p, 0, static_cast<size_t>(bytes)) == cudaSuccess;
     };
     if (!alloc(&kv->k_slab, kv->k_layer_stride * c->num_layers) || !alloc(&kv->v_slab, kv->v_layer_stride * c->num_layers) ||
-        !alloc(&kv->kn_slab, kv->n_layer_stride * c->num_layers) || !alloc(&kv->vn_slab, kv->n_layer_stride * c->num_layers))
+        !alloc(&kv->kn_slab, kv->n_layer_stride * c->num_layers + (kv->n_layer_stride ? 256 : 0)) ||
+        !alloc(&kv->vn_slab, kv->n_layer_stride * c->num_layers + (kv->n_layer_stride ? 256 : 0)))
         return bail(fail(ER_ERR_ALLOCATION_FAILED, "KV slabs (%lld + %lld bytes per layer, %u layers)",
                          static_cast<long long>(kv->k_layer_stride), static_cast<long long>(kv->v_layer_stride), c->num_layers));
     kv->h_lengths.assign(static_cast<size_t>(c->num_layers) * B, 0);
@@ -531,7 +551,7 @@ static int32_t host_append(er_kv* kv, uint32_t layer, uint32_t seq, const void* 
     if (rc != ER_OK) return rc;
     ER_CUDA(cudaMemcpy(kv->d_stage, hk, bytes, cudaMemcpyHostToDevice));
     ER_CUDA(cudaMemcpy(kv->d_stage + bytes, hv, bytes, cudaMemcpyHostToDevice));
-    if (kv->turbo) {
+    if (kv->turbo || kv->q8) {
         AppendParams ap{};
         ap.k = reinterpret_cast<const float*>(kv->d_stage);
         ap.v = reinterpret_cast<const float*>(kv->d_stage + bytes);
@@ -560,8 +580,8 @@ static int32_t host_append(er_kv* kv, uint32_t layer, uint32_t seq, const void* 
 int32_t er_kv_append_f32(er_kv* kv, uint32_t layer, uint32_t seq, const float* hk, const float* hv, size_t count) {
     if (!kv || !hk || !hv) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
-    // KVCache.append: float32 and TurboQuant precisions only; everything else is precisionMismatch (KVCache.swift:450-452).
-    if (kv->cfg.precision != ER_KV_FLOAT32 && !kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "append of Float rows into precision %u", kv->cfg.precision);
+    // KVCache.append: float32, q8_0 and TurboQuant precisions; everything else is precisionMismatch (KVCache.swift:436-452).
+    if (kv->cfg.precision != ER_KV_FLOAT32 && !kv->turbo && !kv->q8) return fail(ER_ERR_PRECISION_MISMATCH, "append of Float rows into precision %u", kv->cfg.precision);
     return host_append(kv, layer, seq, hk, hv, count, 4);
 }
 
@@ -586,6 +606,7 @@ int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
     // validateRequestedType (KVCache.swift:866-883)
     if (kv->turbo) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "TurboQuant cache");
+    if (kv->q8) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "q8_0 cache");
     if (static_cast<int>(element_bytes) != kv->elem_bytes) return fail(ER_ERR_PRECISION_MISMATCH, "requested %u-byte elements from a %d-byte cache", element_bytes, kv->elem_bytes);
     std::lock_guard<std::mutex> lock(kv->mu);
     int32_t rc = pull_lengths(kv);
@@ -684,7 +705,65 @@ int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t se
     return ER_OK;
 }
 
+// Shared body of the two q8_0 retrieves: rows in ring order -> decoded floats and / or 34-byte blocks.
+static int32_t q8_export(er_kv* kv, uint32_t layer, uint32_t seq, float* hk_values, float* hv_values, uint8_t* hk_blocks, uint8_t* hv_blocks,
+                         size_t capacity, uint32_t* token_count) {
+    if (!kv || !token_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (!kv->q8) return fail(ER_ERR_PRECISION_MISMATCH, "not a q8_0 cache");
+    const bool blocks = hk_blocks != nullptr || hv_blocks != nullptr;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    int32_t rc = pull_lengths(kv);
+    if (rc != ER_OK) return rc;
+    int first_slot, tokens;
+    logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
+    *token_count = static_cast<uint32_t>(tokens);
+    if (tokens == 0) return ER_OK;
+    const size_t rows = static_cast<size_t>(tokens) * kv->cfg.num_kv_heads;
+    const size_t unit = blocks ? kQ8PackedRowBytes : kHeadDim * sizeof(float);
+    const size_t need = blocks ? rows * kQ8PackedRowBytes : rows * kHeadDim;
+    if ((blocks ? (!hk_blocks || !hv_blocks) : (!hk_values || !hv_values)) || capacity < need)
+        return fail(ER_ERR_SHAPE, "output capacity %zu < %zu", capacity, need);
+    rc = ensure_stage(kv, 2 * rows * unit);
+    if (rc != ER_OK) return rc;
+    Q8ExportParams ep{};
+    ep.addr = kv->addressing();
+    ep.seq = static_cast<int>(seq); ep.tokens = tokens; ep.first_slot = first_slot;
+    for (int is_v = 0; is_v < 2; ++is_v) {
+        ep.rows = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+        ep.scales = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
+        ep.out_blocks = blocks ? kv->d_stage + is_v * rows * unit : nullptr;
+        ep.out_values = blocks ? nullptr : reinterpret_cast<float*>(kv->d_stage + is_v * rows * unit);
+        q8_export_rows_kernel<<<static_cast<unsigned>(std::min<size_t>((rows + 7) / 8, 8192)), 256>>>(ep);
+        if ((rc = check_launch("q8_export_rows_kernel")) != ER_OK) return rc;
+    }
+    ER_CUDA(cudaMemcpy(blocks ? static_cast<void*>(hk_blocks) : static_cast<void*>(hk_values), kv->d_stage, rows * unit, cudaMemcpyDeviceToHost));
+    ER_CUDA(cudaMemcpy(blocks ? static_cast<void*>(hv_blocks) : static_cast<void*>(hv_values), kv->d_stage + rows * unit, rows * unit,
+                       cudaMemcpyDeviceToHost));
+    return ER_OK;
+}
+
+int32_t er_kv_retrieve_decoded_q8_0(er_kv* kv, uint32_t layer, uint32_t seq, float* hk, float* hv, size_t capacity, uint32_t* token_count) {
+    return q8_export(kv, layer, seq, hk, hv, nullptr, nullptr, capacity, token_count);
+}
+
+int32_t er_kv_retrieve_q8_0_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint8_t* hk, uint8_t* hv, size_t capacity_bytes, uint32_t* token_count) {
+    if (!hk || !hv) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    return q8_export(kv, layer, seq, nullptr, nullptr, hk, hv, capacity_bytes, token_count);
+}
+
 // ---- stand-alone operators ----
+
+int32_t er_quantize_q8_0_rows(const float* source, uint32_t row_count, uint32_t source_row_stride, uint32_t destination_row_base,
+                              uint8_t* destination_blocks, void* stream) {
+    if (!source || !destination_blocks) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (source_row_stride < kHeadDim) return fail(ER_ERR_SHAPE, "source_row_stride %u < 128", source_row_stride);
+    if (row_count == 0) return ER_OK;
+    q8_quantize_rows_packed_kernel<<<(row_count + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(source, row_count, source_row_stride,
+                                                                                                    destination_row_base, destination_blocks);
+    return check_launch("q8_quantize_rows_packed_kernel");
+}
 
 static int32_t rope_common(const float* in, void* out, const ERRoPEParams* p, bool to_f16, void* stream) {
     if (!in || !out || !p) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
@@ -861,6 +940,8 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         if (kv->turbo)
             rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
                                group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type));
+        else if (kv->q8)
+            rc = decode_status(launch_decode_q8(group, p, kv->num_sms, stream), group, 8, 8);
         else {
             if (kv->token_major)
                 encode_token_major_maps(p, group, kv->cfg.num_layers, kv->cfg.max_batch, kv->cfg.max_seq_len, kv->cfg.num_kv_heads);
@@ -887,8 +968,8 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (!kv || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
-    if ((kv->cfg.precision != ER_KV_FLOAT16 && !kv->turbo) || kv->cfg.head_dim != kHeadDim)
-        return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16 and TurboQuant caches with head_dim 128");
+    if ((kv->cfg.precision != ER_KV_FLOAT16 && !kv->turbo && !kv->q8) || kv->cfg.head_dim != kHeadDim)
+        return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16, q8_0 and TurboQuant caches with head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
     if (seq_len == 0) return ER_OK;
     er_step_params s;
@@ -945,6 +1026,35 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         pp.seq = 0;
         s.apply_rope = 0;
     }
+    if (kv->q8) {
+        // gqa_attention_q8kv with seqLen > 1 (Shaders/GQA.metal:409-522): rows expanded to scale * q as fp16 hi (+ lo for the
+        // keys, which makes them exact: 11 + 7 significant bits), same tensor-core kernel
+        const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
+        const size_t rows_bytes = static_cast<size_t>(kv->cfg.num_kv_heads) * tpad * kHeadDim * 2;
+        rc = ensure_stage(kv, 3 * rows_bytes + 256);
+        if (rc != ER_OK) return rc;
+        __half* ek = reinterpret_cast<__half*>(kv->d_stage);
+        __half* ev = reinterpret_cast<__half*>(kv->d_stage + rows_bytes);
+        __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);
+        for (int is_v = 0; is_v < 2; ++is_v) {
+            Q8ExpandParams ep{};
+            ep.rows = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+            ep.scales = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
+            ep.out = is_v ? ev : ek;
+            ep.out_lo = is_v ? nullptr : ekl;
+            ep.addr = kv->addressing();
+            ep.len_ptr = pp.kv_len_ptr;
+            ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
+            const int64_t max_rows = static_cast<int64_t>(kv->cfg.max_seq_len) * kv->cfg.num_kv_heads;
+            q8_expand_rows_f16_kernel<<<static_cast<unsigned>(std::min<int64_t>((max_rows + 7) / 8, 16384)), 256, 0, cs>>>(ep);
+            if ((rc = check_launch("q8_expand_rows_f16_kernel")) != ER_OK) return rc;
+        }
+        pp.k_layer = reinterpret_cast<const uint8_t*>(ek);
+        pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
+        pp.k_lo_layer = reinterpret_cast<const uint8_t*>(ekl);
+        pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
+        pp.seq = 0;
+    }
     pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
     pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);
     pp.causal = 1;
@@ -952,7 +1062,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;
     if (pp.apply_rope) pp.inv_freq = kv->freq(s.rope_theta);
-    const uint64_t outer_extent = kv->turbo ? 1u : static_cast<uint64_t>(kv->pool_pages);
+    const uint64_t outer_extent = (kv->turbo || kv->q8) ? 1u : static_cast<uint64_t>(kv->pool_pages);
     const int rcl = launch_prefill(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, outer_extent, static_cast<int>(kv->cfg.num_kv_heads),
                                    kv->d_counters + 1, static_cast<cudaStream_t>(stream));
     g_launches.fetch_add(1, std::memory_order_relaxed);

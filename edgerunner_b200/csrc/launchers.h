@@ -19,6 +19,7 @@ int decode_dense_tile_tokens(int group);
 // (p.use_tmap stays 0 and the kernel copies row by row).
 int encode_token_major_maps(DecodeParams& p, int group, uint64_t layers, uint64_t seqs, uint64_t slots, uint64_t kv_heads);
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
+int launch_decode_q8(int group, const DecodeParams& p, int grid, cudaStream_t stream);
 struct PrefillParams;
 int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cudaStream_t stream);
 // tcgen05 version of the same kernel.  outer_extent: pages in the pool (page-major rows) or sequences (token-major rows)

@@ -94,3 +94,21 @@ class TurboQuantKernel:
         torch.cuda.synchronize()
         return (codes.cpu().numpy().view(np.uint32), signs.cpu().numpy().view(np.uint32),
                 mask.cpu().numpy().view(np.uint32), meta.cpu().numpy())
+
+
+class Q8Kernel:
+    """quantize_q8_0_rows (Shaders/Dequant_Q8_0.metal:19-49) on device buffers."""
+
+    def encode_quantize_rows(self, source, row_count, source_row_stride, destination_row_base, destination_blocks, stream=None):
+        check(lib().er_quantize_q8_0_rows(ptr(source), row_count, source_row_stride, destination_row_base, ptr(destination_blocks),
+                                          stream_ptr(stream)))
+
+    def execute_quantize_rows(self, rows):
+        """rows: [n, >=128] float32 -> uint8 [n, 136] (four 34-byte blocks per row)."""
+        torch = _torch()
+        x = torch.as_tensor(np.ascontiguousarray(rows, dtype=np.float32)).cuda()
+        n, stride = x.shape
+        out = torch.full((n, 136), 0xEE, dtype=torch.uint8, device="cuda")
+        self.encode_quantize_rows(x, n, stride, 0, out)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()

@@ -133,6 +133,24 @@ class KVCache:
         m = n.value * self.elements_per_token
         return k[:m], v[:m]
 
+    def retrieve_decoded_q8_0(self, layer, seq=0):
+        """KVCache.retrieveDecodedQ8_0 (KVCache.swift:882-908): (keys, values) as flat float32 arrays."""
+        cap = self.max_seq_len * self.elements_per_token
+        k, v = np.zeros(cap, dtype=np.float32), np.zeros(cap, dtype=np.float32)
+        n = C.c_uint32(0)
+        check(lib().er_kv_retrieve_decoded_q8_0(self._h, layer, seq, k.ctypes.data, v.ctypes.data, cap, C.byref(n)))
+        m = n.value * self.elements_per_token
+        return k[:m], v[:m]
+
+    def retrieve_q8_0_rows(self, layer, seq=0):
+        """Stored rows in the reference's block format: (k, v) uint8 [tokens, kv heads, 136]."""
+        cap = self.max_seq_len * self.num_kv_heads * 136
+        k, v = np.zeros(cap, dtype=np.uint8), np.zeros(cap, dtype=np.uint8)
+        n = C.c_uint32(0)
+        check(lib().er_kv_retrieve_q8_0_rows(self._h, layer, seq, k.ctypes.data, v.ctypes.data, cap, C.byref(n)))
+        m = n.value * self.num_kv_heads * 136
+        return k[:m].reshape(n.value, self.num_kv_heads, 136), v[:m].reshape(n.value, self.num_kv_heads, 136)
+
     def retrieve_turboquant_runtime_rows(self, layer, seq=0):
         """((k_codes, k_signs, k_mask, k_meta), (v_...)) in the reference's split-buffer row format."""
         out = []

@@ -147,6 +147,17 @@ public:
         return {std::move(k), std::move(v)};
     }
 
+    // retrieveDecodedQ8_0, KVCache.swift:882-908
+    std::pair<std::vector<float>, std::vector<float>> retrieveDecodedQ8_0(int layer, uint32_t seq = 0) const {
+        const size_t cap = static_cast<size_t>(maxSeqLen) * elementsPerToken();
+        std::vector<float> k(cap), v(cap);
+        uint32_t tokens = 0;
+        check(er_kv_retrieve_decoded_q8_0(handle_, static_cast<uint32_t>(layer), seq, k.data(), v.data(), cap, &tokens));
+        k.resize(static_cast<size_t>(tokens) * elementsPerToken());
+        v.resize(k.size());
+        return {std::move(k), std::move(v)};
+    }
+
     // retrieveTurboQuantRuntimeRows, KVCache.swift:588-629
     TurboQuantRuntimeRows retrieveTurboQuantRuntimeRows(int layer, bool values, uint32_t seq = 0) const {
         TurboQuantRuntimeRows r;

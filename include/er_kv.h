@@ -178,6 +178,15 @@ int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element
 /* KVCache.retrieveDecodedTurboQuant (KVCache.swift:524-586): rows dequantised on the device. */
 int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t seq, float* host_keys,
                                           float* host_values, size_t capacity_elements, uint32_t* token_count);
+/* KVCache.retrieveDecodedQ8_0 (KVCache.swift:882-908): rows of a q8_0 cache as scale * Float(q), logical order,
+ * [token][kvHead][dim]. */
+int32_t er_kv_retrieve_decoded_q8_0(er_kv* kv, uint32_t layer, uint32_t seq, float* host_keys, float* host_values,
+                                    size_t capacity_elements, uint32_t* token_count);
+/* The stored rows of a q8_0 cache in the reference's buffer format (KVCache.swift:175-184, 1007-1038): per row
+ * headDim / 32 blocks of 34 bytes (fp16 scale, 32 int8), rows in logical order, row = token * numKVHeads + kvHead.
+ * capacity_bytes bounds each copy. */
+int32_t er_kv_retrieve_q8_0_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint8_t* host_key_blocks, uint8_t* host_value_blocks,
+                                 size_t capacity_bytes, uint32_t* token_count);
 /* KVCache.retrieveTurboQuantRuntimeRows (KVCache.swift:588-629) in the reference's split-buffer row format:
  * codes [rows][words], residual signs [rows][4] (zero), outlier mask [rows][4] (zero), metadata [rows][2]
  * (rowNorm, 0).  rows = tokens*numKVHeads in logical order, row = token*numKVHeads + kvHead. */
@@ -206,6 +215,11 @@ int32_t er_kv_get_block_table(er_kv* kv, uint32_t seq, int32_t* host_page_ids, u
 int32_t er_rope_neox_f32(const float* in, float* out, const ERRoPEParams* params, void* stream);
 /* rope_neox_f32_to_f16 (Shaders/RoPE.metal:498-531): out is device fp16. */
 int32_t er_rope_neox_f32_to_f16(const float* in, uint16_t* out, const ERRoPEParams* params, void* stream);
+
+/* quantize_q8_0_rows (Shaders/Dequant_Q8_0.metal:19-49): source device [row_count][source_row_stride] float (the first
+ * 128 of each row are used) -> device blocks, row destination_row_base + i, 4 blocks of 34 bytes per row. */
+int32_t er_quantize_q8_0_rows(const float* source, uint32_t row_count, uint32_t source_row_stride, uint32_t destination_row_base,
+                              uint8_t* destination_blocks, void* stream);
 
 /* turboquant_quantize_rows for the fixed presets (Shaders/TurboQuant.metal:562-709; dispatched by
  * encodeTurboQuantRows, Sources/EdgeRunner/Models/LlamaLanguageModel.swift:1754-1818).  source: device

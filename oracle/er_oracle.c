@@ -811,6 +811,88 @@ ERO_API void ero_decode_step_turboquant(const float *q, const float *k, const fl
     free(k_rot);
 }
 
+/* ------------------------------------------------------------------ q8_0 KV rows
+ * KVCache.encodeQ8Row / decodeQ8Row (KVCache.swift:1007-1057; the GPU twin is quantize_q8_0_rows,
+ * Shaders/Dequant_Q8_0.metal:19-49): blocks of 32 elements, 34 bytes each = fp16 scale + 32 int8.
+ *   maxAbs  = running max(maxAbs, |x|) with Swift's max (a NaN operand never replaces maxAbs)
+ *   scale   = maxAbs > 0 ? maxAbs / 127 : 0           (fp32; the *unrounded* scale divides the values)
+ *   q       = Int8(clamping: (x / scale).rounded())   (round half away from zero; the Metal kernel uses rint and
+ *             clamps to [-127, 127] -- the two differ only on exact .5 ties and on -128, which |x| <= maxAbs excludes
+ *             up to rounding)
+ *   stored scale = Float16(scale)
+ * Decoding multiplies Float(Float16 scale) by Float(q). */
+ERO_API void ero_q8_encode_row(const float *x, int count, uint8_t *blocks) {
+    for (int b = 0; b < count / 32; ++b) {
+        const float *src = x + 32 * b;
+        uint8_t *dst = blocks + 34 * b;
+        float max_abs = 0.0f;
+        for (int i = 0; i < 32; ++i) {
+            float a = fabsf(src[i]);
+            if (a >= max_abs) max_abs = a;      /* Swift max(x, y) = y >= x ? y : x */
+        }
+        float scale = max_abs > 0.0f ? max_abs / 127.0f : 0.0f;
+        uint16_t hs = ero_f32_to_f16(scale);
+        dst[0] = (uint8_t)(hs & 0xFF);
+        dst[1] = (uint8_t)(hs >> 8);
+        for (int i = 0; i < 32; ++i) {
+            int q = 0;
+            if (scale != 0.0f) {
+                float r = roundf(src[i] / scale);          /* half away from zero */
+                if (!(r == r)) r = 0.0f;                    /* NaN ratio (inf / inf): the reference would trap */
+                if (r > 127.0f) r = 127.0f;
+                if (r < -128.0f) r = -128.0f;
+                q = (int)r;
+            }
+            dst[2 + i] = (uint8_t)(int8_t)q;
+        }
+    }
+}
+
+ERO_API void ero_q8_decode_row(const uint8_t *blocks, int count, float *out) {
+    for (int b = 0; b < count / 32; ++b) {
+        const uint8_t *src = blocks + 34 * b;
+        float scale = ero_f16_to_f32((uint16_t)(src[0] | (src[1] << 8)));
+        for (int i = 0; i < 32; ++i) out[32 * b + i] = scale * (float)(int8_t)src[2 + i];
+    }
+}
+
+/* gqa_attention_q8kv (Shaders/GQA.metal:389-522): rows are decoded to float (scale * float(q)), then the same
+ * attention as cpuGQA.  k/v: [kv_seq_len][num_kv_heads] rows of (head_dim / 32) * 34 bytes. */
+ERO_API void ero_gqa_q8kv(const float *q, const uint8_t *k8, const uint8_t *v8, float *out, int seq_len, int head_dim,
+                          int num_heads, int num_kv_heads, int causal, int kv_seq_len, int q_offset, int threads) {
+    if (kv_seq_len <= 0) kv_seq_len = seq_len;
+    size_t rows = (size_t)kv_seq_len * num_kv_heads, row_bytes = (size_t)(head_dim / 32) * 34;
+    float *k = (float *)malloc(rows * head_dim * sizeof(float));
+    float *v = (float *)malloc(rows * head_dim * sizeof(float));
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1)
+    for (long r = 0; r < (long)rows; ++r) {
+        ero_q8_decode_row(k8 + r * row_bytes, head_dim, k + r * head_dim);
+        ero_q8_decode_row(v8 + r * row_bytes, head_dim, v + r * head_dim);
+    }
+    ero_gqa_f32(q, k, v, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len, q_offset, threads);
+    free(k);
+    free(v);
+}
+
+/* One decode step of a q8_0 cache (fusedDecodePass on a q8_0 layer: NeoX RoPE of Q and K in fp32, quantize_q8_0_rows
+ * of the K and V rows into row pos*numKVHeads + kvHead, gqa_attention_q8kv over rows 0..pos). */
+ERO_API void ero_decode_step_q8(const float *q, const float *k, const float *v, uint8_t *k_cache, uint8_t *v_cache, float *out,
+                                int pos, int num_heads, int num_kv_heads, float theta, float scaling, int threads) {
+    float *q_rot = (float *)malloc(sizeof(float) * (size_t)num_heads * ERO_DIM);
+    float *k_rot = (float *)malloc(sizeof(float) * (size_t)num_kv_heads * ERO_DIM);
+    const size_t row_bytes = (ERO_DIM / 32) * 34;
+    ero_rope_neox_f32(q, q_rot, 1, (uint32_t)num_heads, ERO_DIM, (uint32_t)pos, theta, scaling, 1.0f);
+    ero_rope_neox_f32(k, k_rot, 1, (uint32_t)num_kv_heads, ERO_DIM, (uint32_t)pos, theta, scaling, 1.0f);
+    for (int h = 0; h < num_kv_heads; ++h) {
+        size_t row = (size_t)pos * num_kv_heads + h;
+        ero_q8_encode_row(k_rot + (size_t)h * ERO_DIM, ERO_DIM, k_cache + row * row_bytes);
+        ero_q8_encode_row(v + (size_t)h * ERO_DIM, ERO_DIM, v_cache + row * row_bytes);
+    }
+    ero_gqa_q8kv(q_rot, k_cache, v_cache, out, 1, ERO_DIM, num_heads, num_kv_heads, 1, pos + 1, pos, threads);
+    free(q_rot);
+    free(k_rot);
+}
+
 ERO_API int ero_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -108,6 +108,10 @@ def lib():
         C.c_float, C.c_float, C.c_int]
     L.ero_decode_step_turboquant.argtypes = [f32p, f32p, f32p, u32p, f32p, C.c_int, u32p, f32p, C.c_int, f32p,
                                              C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]
+    L.ero_q8_encode_row.argtypes = [f32p, C.c_int, u8p]
+    L.ero_q8_decode_row.argtypes = [u8p, C.c_int, f32p]
+    L.ero_gqa_q8kv.argtypes = [f32p, u8p, u8p, f32p] + [C.c_int] * 8
+    L.ero_decode_step_q8.argtypes = [f32p, f32p, f32p, u8p, u8p, f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
     _LIB = L
     return L
 
@@ -283,6 +287,55 @@ def tq_attention_decode(q, k_codes, k_norm, k_bits, v_codes, v_norm, v_bits, num
     lib().ero_tq_attention_decode(_p(q, F32), _p(k_codes, U32), _p(k_norm, F32), k_bits, _p(v_codes, U32),
                                   _p(v_norm, F32), v_bits, _p(out, F32), h, num_kv_heads, kv_len, float(scale),
                                   threads)
+    return out
+
+
+# ----------------------------------------------------------------------------- q8_0 KV rows
+
+def q8_encode_rows(x):
+    """x: [..., 128] float32 -> uint8 [..., 136] (four 34-byte blocks per row: fp16 scale, 32 int8)."""
+    x = _f32(x)
+    d = x.shape[-1]
+    rows = x.reshape(-1, d)
+    out = np.empty((rows.shape[0], d // 32 * 34), dtype=np.uint8)
+    U8 = C.POINTER(C.c_uint8)
+    for r in range(rows.shape[0]):
+        lib().ero_q8_encode_row(_p(rows[r], F32), d, out[r].ctypes.data_as(U8))
+    return out.reshape(x.shape[:-1] + (d // 32 * 34,))
+
+
+def q8_decode_rows(blocks, head_dim=DIM):
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    rows = blocks.reshape(-1, head_dim // 32 * 34)
+    out = np.empty((rows.shape[0], head_dim), dtype=np.float32)
+    U8 = C.POINTER(C.c_uint8)
+    for r in range(rows.shape[0]):
+        lib().ero_q8_decode_row(rows[r].ctypes.data_as(U8), head_dim, _p(out[r], F32))
+    return out.reshape(blocks.shape[:-1] + (head_dim,))
+
+
+def gqa_q8kv(q, k8, v8, causal=True, kv_seq_len=None, q_offset=0, threads=1):
+    """q: [S, H, 128]; k8/v8: [T, Hkv, 136] uint8 rows."""
+    q = _f32(q)
+    k8 = np.ascontiguousarray(k8, dtype=np.uint8)
+    v8 = np.ascontiguousarray(v8, dtype=np.uint8)
+    s, h, d = q.shape
+    t, hkv = k8.shape[0], k8.shape[1]
+    out = np.empty_like(q)
+    U8 = C.POINTER(C.c_uint8)
+    lib().ero_gqa_q8kv(_p(q, F32), k8.ctypes.data_as(U8), v8.ctypes.data_as(U8), _p(out, F32), s, d, h, hkv, 1 if causal else 0,
+                       t if kv_seq_len is None else kv_seq_len, q_offset, threads)
+    return out
+
+
+def decode_step_q8(q, k, v, k_cache, v_cache, pos, theta, scaling=1.0, threads=1):
+    """q: [H,128]; k, v: [Hkv,128]; caches: uint8 [T, Hkv, 136], row `pos` is written in place."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    out = np.empty_like(q)
+    U8 = C.POINTER(C.c_uint8)
+    assert k_cache.flags.c_contiguous and v_cache.flags.c_contiguous and k_cache.dtype == np.uint8
+    lib().ero_decode_step_q8(_p(q, F32), _p(k, F32), _p(v, F32), k_cache.ctypes.data_as(U8), v_cache.ctypes.data_as(U8), _p(out, F32),
+                             int(pos), q.shape[0], k.shape[0], float(theta), float(scaling), threads)
     return out
 
 

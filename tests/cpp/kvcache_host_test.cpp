@@ -33,7 +33,7 @@ int main(int argc, char** argv) {
     if (argc > 1 && std::strcmp(argv[1], "--no-device") == 0) {
         EXPECT(er_device_count() == 0);
         EXPECT(throws(KVCacheError::cuda, [] { KVCache c(16, 1, 2, 4, KVCache::Precision::float32); }));
-        EXPECT(throws(KVCacheError::unsupportedStorage, [] { KVCache c(16, 1, 2, 128, KVCache::Precision::q8_0); }));
+        EXPECT(throws(KVCacheError::unsupportedStorage, [] { KVCache c(16, 1, 2, 128, KVCache::Precision::float8); }));
         std::printf(failures ? "FAILED\n" : "ok (no device)\n");
         return failures ? 1 : 0;
     }

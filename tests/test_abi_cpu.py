@@ -58,7 +58,7 @@ def test_no_device_fails_loudly(er):
         er.KVCache(16, 1, 2, 4, er.Precision.float32)
     assert e.value.name == "cuda" and "no CPU fallback" in str(e.value)
     with pytest.raises(er.EdgeRunnerCUDAError) as e:
-        er.KVCache(16, 1, 2, 128, er.Precision.q8_0)
+        er.KVCache(16, 1, 2, 128, er.Precision.float8)
     assert e.value.name == "unsupportedStorage"
     with pytest.raises(er.EdgeRunnerCUDAError) as e:
         er.KVCache(0, 1, 2, 128, er.Precision.float16)

@@ -102,7 +102,7 @@ def test_kvcache_error_cases(er):
         t.retrieve(0, np.float32)
     assert e.value.name == "compressedRetrieveRequiresDecodedAPI"
     assert t.turboquant_buffers(0).key_row_bytes == 48
-    for prec in (er.Precision.float8, er.Precision.q8_0, er.Precision.turboQuantAggressive):
+    for prec in (er.Precision.float8, er.Precision.turboQuantBalanced, er.Precision.turboQuantAggressive):
         with pytest.raises(er.EdgeRunnerCUDAError) as e:
             er.KVCache(8, 1, 1, 128, prec)
         assert e.value.name == "unsupportedStorage"
@@ -605,6 +605,121 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
         q_rot = oracle.rope_neox(q[0, b][None], ctx, theta)[0]
         want = oracle.tq_attention_decode(q_rot, kc, kmeta[:, 0], 4, vc, vmeta[:, 0], 3, Hkv, ctx + 1, threads=8)
         assert attention_err(got[0, b], want) < TOL
+
+
+# --------------------------------------------------------------------------------------------- q8_0 cache
+
+def test_q8_0_quantize_rows_operator_bit_exact(er, oracle):
+    """er_quantize_q8_0_rows (quantize_q8_0_rows, Dequant_Q8_0.metal:19-49) against the oracle's encodeQ8Row: scales and
+    int8 codes bit for bit, including zero blocks, huge and tiny magnitudes, a row stride and exact ties."""
+    rng = rng_for(60)
+    rows = rng.standard_normal((257, 160), dtype=np.float32)
+    rows[3, :32] = 0.0
+    rows[4] *= 1e30
+    rows[5] *= 1e-30
+    rows[6, :4] = [127.0, 0.5, -0.5, 2.5]
+    rows[6, 4:32] = 0.0
+    got = er.Q8Kernel().execute_quantize_rows(rows)
+    want = oracle.q8_encode_rows(np.ascontiguousarray(rows[:, :128]))
+    assert np.array_equal(got, want)
+
+
+def _run_q8_config(er, oracle, torch, L, B, Hq, Hkv, ctx, steps, seed, layout, page_size=0, ragged=False, theta=THETA_QWEN3):
+    D = 128
+    rng = rng_for(seed)
+    lens = [ctx] * B if not ragged else [int(x) for x in rng.integers(max(1, ctx // 8), ctx + 1, size=B)]
+    T = (max(lens) + steps + 15) // 16 * 16
+    kw = {}
+    if layout == er.Layout.paged:
+        pages_per_seq = (T + page_size - 1) // page_size
+        num_pages = pages_per_seq * B + 2
+        kw = dict(page_size=page_size, num_pages=num_pages)
+        alloc = er.BlockTableAllocator(num_pages, page_size, free_order=rng.permutation(num_pages))
+    cache = er.KVCache(T, L, Hkv, D, er.Precision.q8_0, max_batch=B, layout=layout, **kw)
+    if layout == er.Layout.paged:
+        for b in range(B):
+            cache.set_block_table(b, alloc.ensure(b, lens[b] + steps))
+    sp = er.step_params(rope_theta=theta)
+    st = {}
+    for l in range(L):
+        for b in range(B):
+            n = lens[b]
+            K, V = normal_f16(rng, (n, Hkv, D)), normal_f16(rng, (n, Hkv, D))
+            cache.write_rows(l, b, 0, n, dev(torch, K), dev(torch, V), sp)
+            Kr = np.concatenate([oracle.rope_neox(K[t:t + 1], t, theta) for t in range(n)])
+            kc = np.zeros((n + steps, Hkv, 136), np.uint8)
+            vc = np.zeros((n + steps, Hkv, 136), np.uint8)
+            kc[:n], vc[:n] = oracle.q8_encode_rows(Kr), oracle.q8_encode_rows(V)
+            st[l, b] = [kc, vc]
+    torch.cuda.synchronize()
+    worst = 0.0
+    for s in range(steps):
+        q, k, v = normal_f16(rng, (L, B, Hq, D)), normal_f16(rng, (L, B, Hkv, D)), normal_f16(rng, (L, B, Hkv, D))
+        out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        got = out.cpu().numpy()
+        for l in range(L):
+            for b in range(B):
+                kc, vc = st[l, b]
+                want = oracle.decode_step_q8(q[l, b], k[l, b], v[l, b], kc, vc, lens[b] + s, theta, threads=8)
+                worst = max(worst, max_rel_err(got[l, b], want))
+    assert worst < TOL, worst
+    # stored rows in the reference's 34-byte block format: bit-exact, every row including the appended ones
+    for l in range(L):
+        for b in range(B):
+            gk, gv = cache.retrieve_q8_0_rows(l, seq=b)
+            kc, vc = st[l, b]
+            assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+            dk, dv = cache.retrieve_decoded_q8_0(l, seq=b)
+            assert np.array_equal(dk.reshape(-1, Hkv, D), oracle.q8_decode_rows(kc))
+            assert np.array_equal(dv.reshape(-1, Hkv, D), oracle.q8_decode_rows(vc))
+    return worst
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(16, 8), (8, 8), (32, 8), (16, 2)])
+def test_q8_0_decode_groups(er, oracle, torch, Hq, Hkv):
+    w = _run_q8_config(er, oracle, torch, L=2, B=1, Hq=Hq, Hkv=Hkv, ctx=333, steps=2, seed=70 + Hq, layout=er.Layout.head_major)
+    print("q8_0 group %d max rel err %.3e" % (Hq // Hkv, w))
+
+
+def test_q8_0_decode_batched_ragged_paged(er, oracle, torch):
+    _run_q8_config(er, oracle, torch, L=2, B=3, Hq=16, Hkv=8, ctx=700, steps=2, seed=75, layout=er.Layout.paged, page_size=32, ragged=True)
+
+
+def test_q8_0_host_append_errors_and_prefill(er, oracle, torch):
+    """KVCache.append on a q8_0 cache (appendQ8_0, KVCache.swift:977-1005), the typed-retrieve error, and chunked prefill
+    (gqa_attention_q8kv with seqLen > 1)."""
+    D, Hq, Hkv, theta = 128, 16, 8, 1.0e6
+    rng = rng_for(80)
+    c = er.KVCache(8, 1, Hkv, D, er.Precision.q8_0)
+    rows = []
+    for t in range(11):                                   # wraps the 8-slot ring
+        k, v = rng.standard_normal(Hkv * D, dtype=np.float32), rng.standard_normal(Hkv * D, dtype=np.float32)
+        c.append(0, k, v)
+        rows.append((k, v))
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        c.retrieve(0, np.float32)
+    assert e.value.name == "compressedRetrieveRequiresDecodedAPI"
+    gk, gv = c.retrieve_q8_0_rows(0)
+    want_k = np.stack([oracle.q8_encode_rows(k.reshape(Hkv, D)) for k, _ in rows[3:]])
+    want_v = np.stack([oracle.q8_encode_rows(v.reshape(Hkv, D)) for _, v in rows[3:]])
+    assert np.array_equal(gk, want_k) and np.array_equal(gv, want_v)       # oldest-first after the wrap
+    # chunked prefill: 150 new rows after 70 cached ones
+    ctx, S = 70, 150
+    cache = er.KVCache(256, 1, Hkv, D, er.Precision.q8_0)
+    sp = er.step_params(rope_theta=theta)
+    K, V = normal_f16(rng, (ctx + S, Hkv, D)), normal_f16(rng, (ctx + S, Hkv, D))
+    cache.write_rows(0, 0, 0, ctx + S, dev(torch, K), dev(torch, V), sp)
+    q = normal_f16(rng, (S, Hq, D))
+    out = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(0, 0, dev(torch, q), out, Hq, S, sp)
+    torch.cuda.synchronize()
+    Kr = np.concatenate([oracle.rope_neox(K[t:t + 1], t, theta) for t in range(ctx + S)])
+    want = oracle.gqa_q8kv(oracle.rope_neox(q, ctx, theta), oracle.q8_encode_rows(Kr), oracle.q8_encode_rows(V), causal=True,
+                           q_offset=ctx, threads=8)
+    assert attention_err(out.cpu().numpy(), want) < TOL     # values enter the product as one fp16 (2^-11)
 
 
 # --------------------------------------------------------------------------------------------- chunked prefill (tensor cores)

@@ -285,3 +285,39 @@ def test_splitk_merge_equals_single_pass(oracle):
     pa = [np.exp(s[a:b] - m) @ v[a:b] for (a, b), m in zip(parts, pm)]
     out = oracle.splitk_merge(pm, ps, np.stack(pa))
     assert np.max(np.abs(out - ref)) < 1e-5
+
+
+# ------------------------------------------------------------------------------------------------ q8_0 rows
+
+def test_q8_0_block_known_answers(oracle):
+    """encodeQ8Row / decodeQ8Row (KVCache.swift:1007-1057) on inputs whose answers follow from the rule itself: the test
+    pattern of the reference's own block test (DequantQ8_0Tests.swift:52-54: values i * 0.1 - 1.6), zeros, and a tie."""
+    x = np.zeros(128, np.float32)
+    x[:32] = np.arange(32, dtype=np.float32) * np.float32(0.1) - np.float32(1.6)
+    blocks = oracle.q8_encode_rows(x)
+    scale = np.float32(1.6) / np.float32(127.0)
+    assert blocks[:2].view(np.float16)[0] == np.float16(scale)
+    want = np.clip(np.sign(x[:32] / scale) * np.floor(np.abs(x[:32] / scale) + np.float32(0.5)), -128, 127).astype(np.int8)
+    assert np.array_equal(blocks[2:34].view(np.int8), want)
+    assert want[0] == -127 and want[16] == 0 and want[31] == 119
+    assert not blocks[34:].any()                         # all-zero blocks: scale 0, codes 0
+    dec = oracle.q8_decode_rows(blocks)
+    assert np.array_equal(dec[:32], np.float32(np.float16(scale)) * want.astype(np.float32))
+    # round half away from zero on an exact tie: max 127 -> scale 1, 0.5 -> 1, -0.5 -> -1, 2.5 -> 3
+    y = np.zeros(128, np.float32)
+    y[:4] = [127.0, 0.5, -0.5, 2.5]
+    q = oracle.q8_encode_rows(y)[2:6].view(np.int8)
+    assert list(q) == [127, 1, -1, 3]
+
+
+def test_q8_0_attention_matches_dequantised_float_attention(oracle):
+    rng = np.random.Generator(np.random.PCG64(77))
+    T, H, Hkv = 37, 4, 2
+    k = rng.standard_normal((T, Hkv, 128), dtype=np.float32)
+    v = rng.standard_normal((T, Hkv, 128), dtype=np.float32)
+    q = rng.standard_normal((3, H, 128), dtype=np.float32)
+    k8, v8 = oracle.q8_encode_rows(k), oracle.q8_encode_rows(v)
+    got = oracle.gqa_q8kv(q, k8, v8, causal=True, q_offset=T - 3)
+    want = oracle.gqa_f32(q, oracle.q8_decode_rows(k8), oracle.q8_decode_rows(v8), causal=True, q_offset=T - 3)
+    assert np.array_equal(got, want)
+    assert np.max(np.abs(oracle.q8_decode_rows(k8) - k)) < 0.02      # |x| <= ~4.5, step = max/127
