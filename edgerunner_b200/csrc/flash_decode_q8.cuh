@@ -5,7 +5,9 @@
 // run on mma.sync m16n8k16 with fp16 operands: an int8 is exact in fp16, so
 //   S[token][head] = sum_b kScale[token][b] * ( K8[token][block b] . q[head][block b] )     one accumulator per block b
 //   O^T[dim][head] += V8^T[dim][token] . ( p[token][head] * vScale[token][block(dim)] )^T    one B operand per block
-// keep fp32 accuracy with the queries and the scaled probabilities entering as fp16 hi + lo pairs.
+// keep fp32 accuracy with the queries and the scaled probabilities entering as fp16 hi + lo pairs.  p * vScale is small
+// (vScale = maxAbs / 127, p ~ 1 / context): it is carried times 64 so that its lo part stays a normal fp16 number
+// (64 * vScale <= 65504 for every scale an fp16-sourced row can have), and the outputs are divided by 64 when published.
 // Thread (g = lane / 4, c = lane % 4) reads tokens g and g + 8 of the warp's 16-token unit and, of every 32-element
 // block, the 8 bytes [8c, 8c + 8): byte pairs (0,1) and (2,3) feed the block's first k-step, (4,5) and (6,7) the second
 // (scores); for the outputs the same four pairs are the column pairs of the block's two 16-dim m-tiles, transposed with
@@ -48,6 +50,8 @@ struct Q8MmaPolicy {
     static constexpr bool kFusedAppend = false;   // rows are quantised by q8_append_kernel
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
 
+    static constexpr float kProbScale = 64.f, kInvProbScale = 1.f / 64.f;
+
     struct State {
         uint32_t qh[8][2], ql[8][2];   // B fragments of the (rotated) queries per k-step: fp16 hi and lo parts
         float m[2], l[2];              // heads 2c, 2c + 1
@@ -74,8 +78,8 @@ struct Q8MmaPolicy {
 #pragma unroll
                     for (int t = 0; t < 8; ++t) {
                         const int d0 = 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1);
-                        accs[h * kHeadDim + d0] = acc[t][e];
-                        accs[h * kHeadDim + d0 + 2] = acc[t][2 + e];
+                        accs[h * kHeadDim + d0] = acc[t][e] * kInvProbScale;
+                        accs[h * kHeadDim + d0 + 2] = acc[t][2 + e] * kInvProbScale;
                     }
                 }
             }
@@ -200,6 +204,8 @@ struct Q8MmaPolicy {
             load4(sbase + kOffKs + (r0 + 8) * 8, ks1, ok1);
             load4(sbase + kOffVs + r0 * 8, vs0, ok0);
             load4(sbase + kOffVs + (r0 + 8) * 8, vs1, ok1);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) { vs0[b] *= kProbScale; vs1[b] *= kProbScale; }
         }
         float s[4];   // (token g | g + 8) x (head 2c | 2c + 1)
         s[0] = ks0[0] * sb[0][0] + ks0[1] * sb[1][0] + ks0[2] * sb[2][0] + ks0[3] * sb[3][0];
