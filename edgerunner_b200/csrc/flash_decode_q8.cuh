@@ -9,7 +9,9 @@
 // (vScale = maxAbs / 127, p ~ 1 / context): it is carried times 64 so that its lo part stays a normal fp16 number
 // (64 * vScale <= 65504 for every scale an fp16-sourced row can have), and the outputs are divided by 64 when published.
 // Thread (g = lane / 4, c = lane % 4) reads tokens g and g + 8 of the warp's 16-token unit and, of every 32-element
-// block, the 8 bytes [8c, 8c + 8): byte pairs (0,1) and (2,3) feed the block's first k-step, (4,5) and (6,7) the second
+// block, the 8 bytes [8c, 8c + 8) -- adjacent in the cached row (q8_word_slot: 32 bytes at 32c, two 16-byte reads
+// that the warp's lanes spread over all banks; the plain element order made eight rows collide on the same banks and cost
+// 128 of the kernel's 198 shared-memory wavefronts per unit): byte pairs (0,1) and (2,3) feed the block's first k-step, (4,5) and (6,7) the second
 // (scores); for the outputs the same four pairs are the column pairs of the block's two 16-dim m-tiles, transposed with
 // movmatrix because there the contraction runs over tokens.  Pair conversion: the two bytes (sign bit flipped) become the
 // low mantissa bytes of two halves 0x64xx = 1024 + x + 128, minus 1152.
@@ -170,25 +172,31 @@ struct Q8MmaPolicy {
         const int g = lane >> 2, c = lane & 3;
         const uint32_t sbase = smem_u32(stage);
         const int r0 = unit * kUnitTokens + g;
-        const uint32_t krow = sbase + r0 * 128 + 8 * c, vrow = sbase + kOffV + r0 * 128 + 8 * c;
+        const uint32_t krow = sbase + r0 * 128 + 32 * c, vrow = sbase + kOffV + r0 * 128 + 32 * c;
         const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        auto load_row = [](uint32_t addr, uint32_t (&w)[8]) {   // words 2b, 2b + 1 = this thread's 8 bytes of block b
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr + 16) : "memory");
+        };
 
         // ---- scores: one accumulator per 32-element block ----
         float sb[4][4];
+        {
+            uint32_t k0[8], k1[8];
+            load_row(krow, k0);
+            load_row(krow + 8 * 128, k1);
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            uint32_t k0[2], k1[2];
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(k0[0]), "=r"(k0[1]) : "r"(krow + 32 * b) : "memory");
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(k1[0]), "=r"(k1[1]) : "r"(krow + 8 * 128 + 32 * b) : "memory");
+            for (int b = 0; b < 4; ++b) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) sb[b][e] = 0.f;
+                for (int e = 0; e < 4; ++e) sb[b][e] = 0.f;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const uint32_t w0 = k0[u] ^ 0x80808080u, w1 = k1[u] ^ 0x80808080u;
-                const uint32_t a0 = q8_pair_to_half2<0>(w0), a1 = q8_pair_to_half2<0>(w1);
-                const uint32_t a2 = q8_pair_to_half2<1>(w0), a3 = q8_pair_to_half2<1>(w1);
-                mma_m16n8k16(sb[b], a0, a1, a2, a3, st.qh[2 * b + u][0], st.qh[2 * b + u][1]);
-                mma_m16n8k16(sb[b], a0, a1, a2, a3, st.ql[2 * b + u][0], st.ql[2 * b + u][1]);
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t w0 = k0[2 * b + u] ^ 0x80808080u, w1 = k1[2 * b + u] ^ 0x80808080u;
+                    const uint32_t a0 = q8_pair_to_half2<0>(w0), a1 = q8_pair_to_half2<0>(w1);
+                    const uint32_t a2 = q8_pair_to_half2<1>(w0), a3 = q8_pair_to_half2<1>(w1);
+                    mma_m16n8k16(sb[b], a0, a1, a2, a3, st.qh[2 * b + u][0], st.qh[2 * b + u][1]);
+                    mma_m16n8k16(sb[b], a0, a1, a2, a3, st.ql[2 * b + u][0], st.ql[2 * b + u][1]);
+                }
             }
         }
         float ks0[4], ks1[4], vs0[4], vs1[4];
@@ -243,6 +251,9 @@ struct Q8MmaPolicy {
             }
         }
         // ---- outputs, block by block: B = (p * vScale[block]) as fp16 hi + lo, A = transposed int8 pairs ----
+        uint32_t v0[8], v1[8];
+        load_row(vrow, v0);
+        load_row(vrow + 8 * 128, v1);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const float w0 = p0 * vs0[b], w1 = p1 * vs0[b], w2 = p2 * vs1[b], w3 = p3 * vs1[b];
@@ -252,13 +263,10 @@ struct Q8MmaPolicy {
             const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
             const uint32_t b0l = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
             const uint32_t b1l = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
-            uint32_t v0[2], v1[2];
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v0[0]), "=r"(v0[1]) : "r"(vrow + 32 * b) : "memory");
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v1[0]), "=r"(v1[1]) : "r"(vrow + 8 * 128 + 32 * b) : "memory");
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 // rows at or past nvalid were never copied: their bytes are stale but finite after conversion, and p = 0
-                const uint32_t x0 = v0[u] ^ 0x80808080u, x1 = v1[u] ^ 0x80808080u;
+                const uint32_t x0 = v0[2 * b + u] ^ 0x80808080u, x1 = v1[2 * b + u] ^ 0x80808080u;
                 const uint32_t a0 = movmatrix_trans(q8_pair_to_half2<0>(x0));
                 const uint32_t a1 = movmatrix_trans(q8_pair_to_half2<1>(x0));
                 const uint32_t a2 = movmatrix_trans(q8_pair_to_half2<0>(x1));

@@ -4,6 +4,9 @@
 // buffers, KVCache.swift:175-184, 1007-1057; Shaders/Dequant_Q8_0.metal:19-49).  The cache keeps the two parts apart so
 // that every access is aligned: 128 bytes of int8 per row in the K / V slabs and 4 fp16 scales (8 bytes) per row in the
 // side slabs (the TurboQuant norm slabs' place); the reference's 34-byte blocks are produced on export.
+// Inside a cached row the 32 words are permuted so that the decode kernel's lanes read contiguous bytes: the word that
+// holds elements [4l, 4l + 4) (l = 0..31: block b = l / 8, 8-byte chunk c = (l % 8) / 2 of the block, half l % 2) is
+// stored at word 8c + 2b + l % 2, i.e. the four chunks c of the four blocks are adjacent (q8_word_slot).
 //   maxAbs = max |x| over the block (a NaN never becomes the maximum), scale = maxAbs > 0 ? maxAbs / 127 : 0 (fp32),
 //   q = clamp(round-half-away(x / scale), -128, 127) with the unrounded scale, stored scale = fp16(scale).
 #pragma once
@@ -16,6 +19,9 @@ namespace er {
 constexpr int kQ8RowBytes = 128;      // int8 part of a row
 constexpr int kQ8ScaleBytes = 8;      // four fp16 scales
 constexpr int kQ8PackedRowBytes = 136;
+
+// Position, inside a cached row, of the word that holds elements [4 lane, 4 lane + 4).
+__host__ __device__ constexpr int q8_word_slot(int lane) { return 8 * ((lane & 7) >> 1) + 2 * (lane >> 3) + (lane & 1); }
 
 // Lane holds elements [4 lane, 4 lane + 4) of a row; returns the four int8 as one word and the block's fp32 scale
 // (identical in the 8 lanes of a block).
@@ -99,7 +105,7 @@ __global__ void __launch_bounds__(256) q8_append_kernel(const __grid_constant__ 
     const int slot = static_cast<int>(pos % static_cast<uint32_t>(p.addr.max_seq_len));
     const int64_t ridx = row_index(p.addr, seq, h, slot);
     uint8_t* rows = is_v ? p.v_base + layer * p.v_layer_stride_bytes : p.k_base + layer * p.k_layer_stride_bytes;
-    reinterpret_cast<uint32_t*>(rows + ridx * kQ8RowBytes)[lane] = word;
+    reinterpret_cast<uint32_t*>(rows + ridx * kQ8RowBytes)[q8_word_slot(lane)] = word;
     if ((lane & 7) == 0) {
         uint8_t* sc = (is_v ? qp.vs_base : qp.ks_base) + layer * qp.s_layer_stride_bytes;
         reinterpret_cast<__half*>(sc + ridx * kQ8ScaleBytes)[lane >> 3] = __float2half_rn(scale);
@@ -143,7 +149,7 @@ __global__ void __launch_bounds__(256) q8_export_rows_kernel(const __grid_consta
         const int t = static_cast<int>(job / p.addr.num_kv_heads), h = static_cast<int>(job % p.addr.num_kv_heads);
         const int slot = (p.first_slot + t) % p.addr.max_seq_len;
         const int64_t ridx = row_index(p.addr, p.seq, h, slot);
-        const uint32_t word = reinterpret_cast<const uint32_t*>(p.rows + ridx * kQ8RowBytes)[lane];
+        const uint32_t word = reinterpret_cast<const uint32_t*>(p.rows + ridx * kQ8RowBytes)[q8_word_slot(lane)];
         const __half hs = reinterpret_cast<const __half*>(p.scales + ridx * kQ8ScaleBytes)[lane >> 3];
         if (p.out_blocks != nullptr) {
             uint8_t* blk = p.out_blocks + job * kQ8PackedRowBytes + (lane >> 3) * 34;
@@ -184,7 +190,7 @@ __global__ void __launch_bounds__(256) q8_expand_rows_f16_kernel(const __grid_co
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < total; row += static_cast<int64_t>(gridDim.x) * 8) {
         const int h = static_cast<int>(row / len), t = static_cast<int>(row % len);
         const int64_t ridx = row_index(p.addr, p.seq, h, t);
-        const uint32_t word = reinterpret_cast<const uint32_t*>(p.rows + ridx * kQ8RowBytes)[lane];
+        const uint32_t word = reinterpret_cast<const uint32_t*>(p.rows + ridx * kQ8RowBytes)[q8_word_slot(lane)];
         const float sc = __half2float(reinterpret_cast<const __half*>(p.scales + ridx * kQ8ScaleBytes)[lane >> 3]);
         float a[4];
 #pragma unroll
