@@ -7,12 +7,13 @@ namespace er {
 
 template <int KB, int VB>
 static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
-    // 14 consumer warps in two groups (112-token tiles, 4 stages, 136 registers): the fastest of the measured shapes; 16
-    // and 20 warps spill, 12 warps and thinner tiles hide less of the table-lookup latency.
+    // one group of 15 consumer warps over 240-token tiles, 3 stages: the fastest of the measured shapes for group 2 (3.55 ms
+    // per cfg2 step; two alternating groups of 7 warps 3.90, one group of 11 warps 3.98).  Group 4 keeps its merge buffers
+    // within shared memory with 11 warps.
     switch (group) {
-        case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 7, 2, 4>>(p, grid, stream);
-        case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 7, 2, 4>>(p, grid, stream);
-        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 7, 2, 4>>(p, grid, stream);
+        case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 15, 1, 3>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 15, 1, 3>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 11, 1, 3>>(p, grid, stream);
         default: return kNotBuilt;
     }
 }
