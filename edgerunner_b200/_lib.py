@@ -39,7 +39,8 @@ class er_kv_buffers(C.Structure):
 
 class er_step_params(C.Structure):
     _fields_ = [("rope_theta", C.c_float), ("rope_scaling", C.c_float), ("softmax_scale", C.c_float),
-                ("apply_rope", C.c_uint32), ("reserved", C.c_uint32 * 4)]
+                ("apply_rope", C.c_uint32), ("q_norm_weight", C.c_void_p), ("k_norm_weight", C.c_void_p),
+                ("rms_eps", C.c_float), ("norm_weight_layer_stride", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
 # status codes (include/er_kv.h)

@@ -32,6 +32,42 @@ struct AppendParams {
     InvFreqTable inv_freq;
 };
 
+// Per-head RMS norm, the first half of fused_qk_norm_rope_neox (Shaders/RoPE.metal:139-160):
+//   out = (x * rsqrt(sum(x^2) / 128 + eps)) * weight[dim].
+// The reference sums the 64 pair terms x[i]^2 + x[i+64]^2 with simd_sum per 32 pairs plus one add; the order inside
+// simd_sum is not specified, so it is fixed here (and in the CPU restatement the tests compare with) as the xor
+// butterfly 16, 8, 4, 2, 1 over the pair index, products and sums rounded separately, rsqrt correctly rounded.
+// One warp per head row; rows are [groups][heads_per_group][128] with one weight vector per group (a layer).
+struct HeadNormParams {
+    const float* in;
+    float* out;
+    const float* weight;       // [groups][weight_stride] (stride 0: shared)
+    int rows, rows_per_group, weight_stride;
+    float eps;
+};
+
+__global__ void __launch_bounds__(256) head_rms_norm_kernel(const __grid_constant__ HeadNormParams p) {
+    const int lane = threadIdx.x & 31;
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < p.rows; row += gridDim.x * 8) {
+        const float* x = p.in + static_cast<int64_t>(row) * kHeadDim;
+        const float a = x[lane], b = x[lane + 64], c = x[lane + 32], d = x[lane + 96];
+        float s0 = __fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b));      // pair index lane
+        float s1 = __fadd_rn(__fmul_rn(c, c), __fmul_rn(d, d));      // pair index lane + 32
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, off));
+            s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, off));
+        }
+        const float rs = __frsqrt_rn(__fadd_rn(__fdiv_rn(__fadd_rn(s0, s1), static_cast<float>(kHeadDim)), p.eps));
+        const float* w = p.weight + static_cast<int64_t>(row / p.rows_per_group) * p.weight_stride;
+        float* o = p.out + static_cast<int64_t>(row) * kHeadDim;
+        o[lane] = __fmul_rn(__fmul_rn(a, rs), w[lane]);
+        o[lane + 32] = __fmul_rn(__fmul_rn(c, rs), w[lane + 32]);
+        o[lane + 64] = __fmul_rn(__fmul_rn(b, rs), w[lane + 64]);
+        o[lane + 96] = __fmul_rn(__fmul_rn(d, rs), w[lane + 96]);
+    }
+}
+
 __device__ __forceinline__ void append_locate(const AppendParams& p, int r, int& layer, int& seq, uint32_t& pos) {
     if (p.bulk) {
         layer = p.fixed_layer;

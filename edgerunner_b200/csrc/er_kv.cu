@@ -172,6 +172,8 @@ struct er_kv {
     int* d_counters = nullptr;             // [0] done, [1] status, [16..] item counters
     uint8_t* d_stage = nullptr;            // staging for host-facing calls
     size_t stage_bytes = 0;
+    float* d_head_norm[2] = {nullptr, nullptr};   // normalised copies of a call's q and k rows (er_step_params norm weights)
+    size_t head_norm_floats[2] = {0, 0};
     float cached_theta = 0.f;
     InvFreqTable inv_freq{};
     unsigned long long* d_trace = nullptr;   // caller-owned diagnostics buffer (er_kv_set_trace)
@@ -236,7 +238,40 @@ int32_t step_defaults(const er_kv* kv, const er_step_params* in, er_step_params&
     if (out.rope_scaling == 0.f) out.rope_scaling = 1.f;
     if (out.softmax_scale == 0.f) out.softmax_scale = 1.0f / std::sqrt(static_cast<float>(kv->cfg.head_dim));
     if (out.apply_rope && !(out.rope_theta > 0.f)) return fail(ER_ERR_INVALID_ARGUMENT, "rope_theta must be > 0");
+    if (out.rms_eps == 0.f) out.rms_eps = 1e-6f;
     return ER_OK;
+}
+
+// Per-head RMS norm of `rows` head rows (rows_per_group consecutive rows share the weight vector of one layer) into the
+// cache's scratch slot `which` (0 = queries, 1 = keys); *rows_io is replaced by the normalised copy.  No-op for a null
+// weight pointer.
+int32_t apply_head_norm(er_kv* kv, int which, const float** rows_io, size_t rows, size_t rows_per_group, const float* weight,
+                        uint32_t first_group, const er_step_params& s, cudaStream_t stream) {
+    if (weight == nullptr || rows == 0) return ER_OK;
+    if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "head norm is built for head_dim 128");
+    {
+        std::lock_guard<std::mutex> lock(kv->mu);
+        const size_t need = rows * kHeadDim;
+        if (kv->head_norm_floats[which] < need) {
+            if (kv->d_head_norm[which]) cudaFree(kv->d_head_norm[which]);
+            kv->d_head_norm[which] = nullptr;
+            kv->head_norm_floats[which] = 0;
+            if (cudaMalloc(&kv->d_head_norm[which], need * sizeof(float)) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(ER_ERR_ALLOCATION_FAILED, "head-norm scratch of %zu floats", need);
+            }
+            kv->head_norm_floats[which] = need;
+        }
+    }
+    HeadNormParams hp{};
+    hp.in = *rows_io; hp.out = kv->d_head_norm[which];
+    hp.weight = weight + static_cast<size_t>(first_group) * s.norm_weight_layer_stride;
+    hp.rows = static_cast<int>(rows); hp.rows_per_group = static_cast<int>(rows_per_group);
+    hp.weight_stride = static_cast<int>(s.norm_weight_layer_stride);
+    hp.eps = s.rms_eps;
+    head_rms_norm_kernel<<<static_cast<unsigned>(std::min<size_t>((rows + 7) / 8, 4096)), 256, 0, stream>>>(hp);
+    *rows_io = kv->d_head_norm[which];
+    return check_launch("head_rms_norm_kernel");
 }
 
 int32_t launch_append(er_kv* kv, AppendParams& ap, cudaStream_t stream) {
@@ -417,6 +452,7 @@ void er_kv_destroy(er_kv* kv) {
     if (!kv) return;
     cudaFree(kv->k_slab); cudaFree(kv->v_slab); cudaFree(kv->kn_slab); cudaFree(kv->vn_slab);
     cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
+    cudaFree(kv->d_head_norm[0]); cudaFree(kv->d_head_norm[1]);
     cudaFree(kv->d_stage);
     cudaGetLastError();
     delete kv;
@@ -869,6 +905,9 @@ int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t lb, uint32_t le, const float* k
     if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "device append is built for head_dim 128");
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(le - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads,
+                         static_cast<size_t>(kv->cfg.max_batch) * kv->cfg.num_kv_heads, s.k_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
     AppendParams ap{};
     ap.k = k; ap.v = v;
@@ -889,6 +928,9 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
     if (static_cast<uint64_t>(start) + count > kv->cfg.max_seq_len) return fail(ER_ERR_SHAPE, "rows [%u, %u) exceed max_seq_len %u", start, start + count, kv->cfg.max_seq_len);
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
+    if (rc != ER_OK) return rc;
+    rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(count) * kv->cfg.num_kv_heads, static_cast<size_t>(count) * kv->cfg.num_kv_heads,
+                         s.k_norm_weight, layer, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
     AppendParams ap{};
@@ -959,6 +1001,9 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float*
     if (rc != ER_OK) return rc;
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
+                         s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
     return attention_locked(kv, lb, le, q, out, num_heads, pending ? 1 : 0, 0, s, static_cast<cudaStream_t>(stream));
 }
@@ -974,6 +1019,9 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (seq_len == 0) return ER_OK;
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
+    if (rc != ER_OK) return rc;
+    rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
+                         static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
     PrefillParams pp{};
@@ -1098,8 +1146,17 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.
     const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;
+    // Q / K head norms run first (one small launch each); everything below sees normalised rows and no weights
+    rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
+                         s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(le - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads,
+                         static_cast<size_t>(kv->cfg.max_batch) * kv->cfg.num_kv_heads, s.k_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    s.q_norm_weight = nullptr;
+    s.k_norm_weight = nullptr;
     if (!fused) {
-        rc = er_kv_append_rope_kv(kv, lb, le, k, v, sp, stream);
+        rc = er_kv_append_rope_kv(kv, lb, le, k, v, &s, stream);
         if (rc != ER_OK) return rc;
     }
     std::lock_guard<std::mutex> lock(kv->mu);

@@ -144,7 +144,14 @@ typedef struct {
     float rope_scaling;    /* ERRoPEParams.scalingFactor (1.0 = none) */
     float softmax_scale;   /* 0 -> 1/sqrt(head_dim) (GQAKernel.encode, GQAKernel.swift:134) */
     uint32_t apply_rope;   /* 1: NeoX-rotate Q and K at the row's position inside the call */
-    uint32_t reserved[4];
+    /* Per-head RMS norm of Q and K before RoPE -- the first half of fused_qk_norm_rope_neox (Shaders/RoPE.metal:119-173):
+     * x * rsqrt(mean(x^2) + rms_eps) * weight[dim].  Device pointers to headDim floats per layer (layer l reads
+     * weight + l * norm_weight_layer_stride; stride 0 = one vector for all layers); NULL = no norm for that tensor. */
+    const float* q_norm_weight;
+    const float* k_norm_weight;
+    float rms_eps;
+    uint32_t norm_weight_layer_stride;
+    uint32_t reserved[2];
 } er_step_params;
 
 const char* er_status_string(int32_t status);

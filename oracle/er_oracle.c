@@ -893,6 +893,37 @@ ERO_API void ero_decode_step_q8(const float *q, const float *k, const float *v, 
     free(k_rot);
 }
 
+/* Per-head RMS norm, the first half of fused_qk_norm_rope_neox (Shaders/RoPE.metal:139-160):
+ *   rs = rsqrt(sumSq / headDim + eps), out = raw * rs * weight[dim].
+ * sumSq is the simd_sum of the pair terms raw0^2 + raw1^2 (dims i and i + 64) over each 32 pairs plus one add; the order
+ * inside simd_sum is not specified by the reference, so it is fixed as the xor butterfly 16, 8, 4, 2, 1 over the pair
+ * index (the GPU kernel uses the same order).  rsqrt is evaluated in double and rounded once. */
+ERO_API void ero_head_rms_norm(const float *in, const float *weight, float eps, int rows, float *out) {
+    for (int r = 0; r < rows; ++r) {
+        const float *x = in + (size_t)r * ERO_DIM;
+        float s[2][32], t[32];
+        for (int half = 0; half < 2; ++half) {
+            for (int i = 0; i < 32; ++i) {
+                float a = x[32 * half + i], b = x[32 * half + i + 64];
+                float aa = a * a, bb = b * b;
+                s[half][i] = aa + bb;
+            }
+            for (int off = 16; off >= 1; off >>= 1) {
+                for (int i = 0; i < 32; ++i) t[i] = s[half][i] + s[half][i ^ off];
+                memcpy(s[half], t, sizeof(t));
+            }
+        }
+        float sum = s[0][0] + s[1][0];
+        float mean = sum / (float)ERO_DIM;
+        float arg = mean + eps;
+        float rs = (float)(1.0 / sqrt((double)arg));
+        for (int d = 0; d < ERO_DIM; ++d) {
+            float y = x[d] * rs;
+            out[(size_t)r * ERO_DIM + d] = y * weight[d];
+        }
+    }
+}
+
 ERO_API int ero_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -108,6 +108,7 @@ def lib():
         C.c_float, C.c_float, C.c_int]
     L.ero_decode_step_turboquant.argtypes = [f32p, f32p, f32p, u32p, f32p, C.c_int, u32p, f32p, C.c_int, f32p,
                                              C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]
+    L.ero_head_rms_norm.argtypes = [f32p, f32p, C.c_float, C.c_int, f32p]
     L.ero_q8_encode_row.argtypes = [f32p, C.c_int, u8p]
     L.ero_q8_decode_row.argtypes = [u8p, C.c_int, f32p]
     L.ero_gqa_q8kv.argtypes = [f32p, u8p, u8p, f32p] + [C.c_int] * 8
@@ -287,6 +288,14 @@ def tq_attention_decode(q, k_codes, k_norm, k_bits, v_codes, v_norm, v_bits, num
     lib().ero_tq_attention_decode(_p(q, F32), _p(k_codes, U32), _p(k_norm, F32), k_bits, _p(v_codes, U32),
                                   _p(v_norm, F32), v_bits, _p(out, F32), h, num_kv_heads, kv_len, float(scale),
                                   threads)
+    return out
+
+
+def head_rms_norm(x, weight, eps):
+    """Per-head RMS norm of fused_qk_norm_rope_neox: x [..., 128], weight [128]."""
+    x, weight = _f32(x), _f32(weight)
+    out = np.empty_like(x)
+    lib().ero_head_rms_norm(_p(x, F32), _p(weight, F32), float(eps), x.size // DIM, _p(out, F32))
     return out
 
 

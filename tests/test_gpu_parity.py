@@ -607,6 +607,77 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
         assert attention_err(got[0, b], want) < TOL
 
 
+# --------------------------------------------------------------------------------------------- Q/K head norm (fused_qk_norm_rope_neox)
+
+@pytest.mark.parametrize("precision", ["float16", "turbo", "q8_0"])
+def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision):
+    """er_step_params.q_norm_weight / k_norm_weight: per-head RMS norm before RoPE (fused_qk_norm_rope_neox,
+    Shaders/RoPE.metal:119-173) on every cache kind.  The K rows the cache ends up holding are compared bit for bit with
+    the oracle's norm -> RoPE -> store; the attention outputs within the usual bounds."""
+    L, B, Hq, Hkv, D, ctx, theta, eps = 2, 2, 16, 8, 128, 90, THETA_QWEN3, 1e-6
+    rng = rng_for(90)
+    wq = (1.0 + 0.1 * rng.standard_normal((L, D), dtype=np.float32)).astype(np.float32)
+    wk = (1.0 + 0.1 * rng.standard_normal((L, D), dtype=np.float32)).astype(np.float32)
+    dwq, dwk = dev(torch, wq), dev(torch, wk)
+    sp = er.step_params(rope_theta=theta, q_norm_weight=dwq, k_norm_weight=dwk, rms_eps=eps, norm_weight_layer_stride=D)
+    T = 128
+    if precision == "float16":
+        cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B)
+    elif precision == "turbo":
+        cache = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=3, max_batch=B)
+    else:
+        cache = er.KVCache(T, L, Hkv, D, er.Precision.q8_0, max_batch=B)
+    Kraw = normal_f16(rng, (L, B, ctx + 1, Hkv, D)) * 3.0
+    V = normal_f16(rng, (L, B, ctx + 1, Hkv, D))
+    for l in range(L):
+        for b in range(B):
+            cache.write_rows(l, b, 0, ctx, dev(torch, Kraw[l, b, :ctx]), dev(torch, V[l, b, :ctx]), sp)
+    q = normal_f16(rng, (L, B, Hq, D)) * 2.0
+    out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.decode_step(dev(torch, q), dev(torch, Kraw[:, :, ctx]), dev(torch, V[:, :, ctx]), out, Hq, sp)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for l in range(L):
+        for b in range(B):
+            Kn = oracle.head_rms_norm(Kraw[l, b], wk[l], eps)                   # [ctx+1, Hkv, D]
+            qn = oracle.head_rms_norm(q[l, b], wq[l], eps)
+            Kr = np.concatenate([oracle.rope_neox(Kn[t:t + 1], t, theta) for t in range(ctx + 1)])
+            qr = oracle.rope_neox(qn[None], ctx, theta)
+            if precision == "float16":
+                k16 = np.concatenate([oracle.rope_neox_to_f16(Kn[t:t + 1], t, theta) for t in range(ctx + 1)])
+                v16 = oracle.f32_to_f16_bits(V[l, b])
+                gk, gv = cache.retrieve(l, np.float16, seq=b)
+                assert np.array_equal(gk.view(np.uint16).reshape(-1, Hkv, D), k16)
+                want = oracle.gqa_f16kv(qr, k16, v16, causal=True, q_offset=ctx)[0]
+                assert max_rel_err(got[l, b], want) < TOL
+            elif precision == "q8_0":
+                k8, v8 = oracle.q8_encode_rows(Kr), oracle.q8_encode_rows(V[l, b])
+                gk, gv = cache.retrieve_q8_0_rows(l, seq=b)
+                assert np.array_equal(gk, k8) and np.array_equal(gv, v8)
+                want = oracle.gqa_q8kv(qr, k8, v8, causal=True, q_offset=ctx)[0]
+                assert max_rel_err(got[l, b], want) < TOL
+            else:
+                kc, kn = oracle.tq_encode_rows(Kr.reshape(-1, D), 4)
+                vc, vn = oracle.tq_encode_rows(V[l, b].reshape(-1, D), 3)
+                (gkc, _, _, gkm), _ = cache.retrieve_turboquant_runtime_rows(l, seq=b)
+                assert np.array_equal(gkc, kc) and np.array_equal(gkm[:, 0], kn)
+                want = oracle.tq_attention_decode(qr[0], kc, kn, 4, vc, vn, 3, Hkv, ctx + 1)
+                assert attention_err(got[l, b], want) < TOL
+    # chunked prefill with the query norm: the last 40 rows of sequence 0, layer 1, as a chunk
+    if precision == "float16":
+        S = 40
+        qc = normal_f16(rng, (S, Hq, D))
+        o2 = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.attention_prefill(1, 0, dev(torch, qc), o2, Hq, S, sp)
+        torch.cuda.synchronize()
+        Kn = oracle.head_rms_norm(Kraw[1, 0], wk[1], eps)
+        k16 = np.concatenate([oracle.rope_neox_to_f16(Kn[t:t + 1], t, theta) for t in range(ctx + 1)])
+        v16 = oracle.f32_to_f16_bits(V[1, 0])
+        qr = oracle.rope_neox(oracle.head_rms_norm(qc, wq[1], eps), ctx + 1 - S, theta)
+        want = oracle.gqa_f16kv(qr, k16, v16, causal=True, q_offset=ctx + 1 - S)
+        assert max_rel_err(o2.cpu().numpy(), want) < TOL
+
+
 # --------------------------------------------------------------------------------------------- q8_0 cache
 
 def test_q8_0_quantize_rows_operator_bit_exact(er, oracle):
