@@ -52,6 +52,9 @@ WORKLOADS = {
                     layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="q8_0", layout="head_major", theta=1.0e6),
     "cfg1_q8_long": dict(name="cfg1 shape with a q8_0 KV cache at context 32768, batch 8",
                          layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="q8_0", layout="head_major", theta=1.0e6),
+    "cfg3_4layers": dict(name="cfg3 shape with 4 of its 32 layers and 16 of its 64 sequences (profiler captures)",
+                         layers=4, batch=16, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
+                         page_size=16, theta=5.0e5),
     "cfg1_q8_4layers": dict(name="cfg1 shape with a q8_0 KV cache at context 32768, batch 8, 4 of the 28 layers (profiler captures)",
                             layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="q8_0", layout="head_major", theta=1.0e6),
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",

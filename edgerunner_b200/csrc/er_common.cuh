@@ -98,6 +98,20 @@ __device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* m
         : "memory");
 }
 
+// Per-head RMS-norm factor rsqrt(sum(x^2) / 128 + eps) of a 128-float row, summed in the order head_rms_norm_kernel uses
+// (pair terms x[i]^2 + x[i+64]^2, xor butterfly 16..1 over each 32 pairs, one add).  All 32 lanes take part.
+__device__ __forceinline__ float head_rms_scale(const float* row, float eps, int lane) {
+    const float a = __ldg(row + lane), b = __ldg(row + lane + 64), c = __ldg(row + lane + 32), d = __ldg(row + lane + 96);
+    float s0 = __fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b));
+    float s1 = __fadd_rn(__fmul_rn(c, c), __fmul_rn(d, d));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, off));
+        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, off));
+    }
+    return __frsqrt_rn(__fadd_rn(__fdiv_rn(__fadd_rn(s0, s1), static_cast<float>(kHeadDim)), eps));
+}
+
 // Named barrier among the consumer warps only (the producer warp never joins it).
 template <int THREADS>
 __device__ __forceinline__ void consumer_sync() {

@@ -977,6 +977,9 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
         p.apply_rope = s.apply_rope ? 1 : 0; p.rope_scaling = s.rope_scaling;
         if (p.apply_rope) p.inv_freq = kv->freq(s.rope_theta);
+        // only the fused fp16 step reaches here with weights set (the other entry points normalise beforehand)
+        p.q_norm_w = s.q_norm_weight; p.k_norm_w = s.k_norm_weight;
+        p.norm_stride = static_cast<int>(s.norm_weight_layer_stride); p.rms_eps = s.rms_eps;
         p.addr = kv->addressing();
         p.scratch = kv->d_scratch; p.done_counter = kv->d_counters; p.status = kv->d_counters + 1; p.item_counters = kv->d_counters + 16;
         if (kv->turbo)
@@ -1004,6 +1007,8 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float*
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
                          s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
+    s.q_norm_weight = nullptr;     // applied above; the kernel must not apply them again
+    s.k_norm_weight = nullptr;
     std::lock_guard<std::mutex> lock(kv->mu);
     return attention_locked(kv, lb, le, q, out, num_heads, pending ? 1 : 0, 0, s, static_cast<cudaStream_t>(stream));
 }
@@ -1146,16 +1151,17 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.
     const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;
-    // Q / K head norms run first (one small launch each); everything below sees normalised rows and no weights
-    rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
-                         s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
-    if (rc != ER_OK) return rc;
-    rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(le - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads,
-                         static_cast<size_t>(kv->cfg.max_batch) * kv->cfg.num_kv_heads, s.k_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
-    if (rc != ER_OK) return rc;
-    s.q_norm_weight = nullptr;
-    s.k_norm_weight = nullptr;
+    // Q / K head norms: the fp16 kernel applies them itself while it prepares Q and the new K row; the other formats run
+    // one small launch per tensor first, and everything below sees normalised rows and no weights
     if (!fused) {
+        rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
+                             s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+        if (rc != ER_OK) return rc;
+        rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(le - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads,
+                             static_cast<size_t>(kv->cfg.max_batch) * kv->cfg.num_kv_heads, s.k_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+        if (rc != ER_OK) return rc;
+        s.q_norm_weight = nullptr;
+        s.k_norm_weight = nullptr;
         rc = er_kv_append_rope_kv(kv, lb, le, k, v, &s, stream);
         if (rc != ER_OK) return rc;
     }

@@ -58,6 +58,12 @@ struct DecodeParams {
     float scale_log2;             // softmax scale * log2(e)
     float rope_scaling;
     int apply_rope;
+    // fp16 policy only: per-head RMS norm of Q and of the fused-append K row before RoPE (fused_qk_norm_rope_neox,
+    // Shaders/RoPE.metal:119-173); weights [layer][norm_stride], null = none
+    const float* q_norm_w;
+    const float* k_norm_w;
+    int norm_stride;
+    float rms_eps;
     KVAddressing addr;
     float* scratch;               // [gridDim.x][2][GROUP][130]
     int* item_counters;           // [pairs * kv heads], zero between launches
@@ -168,8 +174,8 @@ struct DensePolicy {
 
     __device__ static void init_extra(uint8_t*, int) {}
     __device__ __forceinline__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs,
-                                                  uint8_t* extra, int warp, int lane) {
-        load_q(p, st.q, qrow, cs, extra, warp, lane);
+                                                  uint8_t* extra, int warp, int lane, int layer) {
+        load_q(p, st.q, qrow, cs, extra, warp, lane, p.q_norm_w ? p.q_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr);
         st.reset();
     }
     __device__ __forceinline__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid,
@@ -219,14 +225,22 @@ struct DensePolicy {
 
     // Consumers: per-lane Q registers, NeoX-rotated in registers when asked.
     __device__ static void load_q(const DecodeParams& p, float (&q)[GROUP][kQRegs], const float* qrow, const float2* cs,
-                                  uint8_t*, int, int lane) {
+                                  uint8_t*, int, int lane, const float* qw) {
         const int i = lane & 7;
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             const float4* src = reinterpret_cast<const float4*>(qrow + g * kHeadDim + 8 * i);
             const float4 a0 = __ldg(src), a1 = __ldg(src + 1), b0 = __ldg(src + 16), b1 = __ldg(src + 17);
-            const float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            if (qw != nullptr) {
+                const float rs = head_rms_scale(qrow + g * kHeadDim, p.rms_eps, lane);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    xa[c] = __fmul_rn(__fmul_rn(xa[c], rs), __ldg(qw + 8 * i + c));
+                    xb[c] = __fmul_rn(__fmul_rn(xb[c], rs), __ldg(qw + 64 + 8 * i + c));
+                }
+            }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 if (p.apply_rope) {
@@ -344,10 +358,16 @@ struct DensePolicy {
         uint8_t* krow = stage + (unit * kUnitTokens + r) * kRowBytesF16;
         uint8_t* vrow = stage + kTileBytesF16 + (unit * kUnitTokens + r) * kRowBytesF16;
         __half* kh = reinterpret_cast<__half*>(krow);
+        const float* kw = p.k_norm_w ? p.k_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr;
+        const float rs = kw ? head_rms_scale(k_src, p.rms_eps, lane) : 1.f;
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
             const int d = lane + 32 * part;
             float x0 = __ldg(k_src + d), x1 = __ldg(k_src + d + kHalfDim);
+            if (kw != nullptr) {
+                x0 = __fmul_rn(__fmul_rn(x0, rs), __ldg(kw + d));
+                x1 = __fmul_rn(__fmul_rn(x1, rs), __ldg(kw + d + kHalfDim));
+            }
             if (p.apply_rope) {
                 float y0, y1;
                 rope_rotate(x0, x1, cs[d], y0, y1);
@@ -496,7 +516,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
 
                 typename POL::State st;
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
-                POL::load_q(p, st, qrow, cs, extra, warp, lane);
+                POL::load_q(p, st, qrow, cs, extra, warp, lane, layer);
 
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     if (NG > 1 && k % NG != wgroup) continue;

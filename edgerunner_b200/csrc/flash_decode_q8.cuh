@@ -126,7 +126,7 @@ struct Q8MmaPolicy {
 
     // Q row (NeoX-rotated when asked) -> B fragments.  k-step 2b + u of block b: label 2c + e -> dim 32b + 8c + 4u + e,
     // label 2c + 8 + e -> dim 32b + 8c + 4u + 2 + e; thread (g, c) holds head g.
-    __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane) {
+    __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane, int) {
         const int g = lane >> 2, c = lane & 3;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {

@@ -156,7 +156,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
     }
 
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t* extra,
-                                  int warp, int lane) {
+                                  int warp, int lane, int) {
         float* qrot = reinterpret_cast<float*>(extra + kOffQrot);
         Base::rotate_queries(p, qrot, qrow, cs, warp, lane);
         const int g = lane >> 2, c = lane & 3;
