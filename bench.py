@@ -87,6 +87,10 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-device-leg", action="store_true",
                     help="run only the device-resident timed leg (short runs under a profiler)")
+    ap.add_argument("--shard", default="sequence", choices=["sequence", "heads"],
+                    help="N > 1: 'sequence' = one replica of the workload per GPU (weak scaling, no collective); 'heads' = the kv "
+                         "heads of the one workload split over the GPUs, outputs exchanged by an NCCL all-gather per step (strong "
+                         "scaling; device leg only)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
     return ap.parse_args()
 
@@ -343,6 +347,13 @@ def run_ours(args, w, lens):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    shard_heads = args.shard == "heads" and world > 1
+    if shard_heads:
+        # rank r owns kv heads [r * Hkv / N, (r + 1) * Hkv / N) and their q heads: its cache and its q/k/v hold only those
+        if w["kv_heads"] % world:
+            raise SystemExit("--shard heads needs kv_heads %% gpus == 0")
+        w = dict(w, heads=w["heads"] // world, kv_heads=w["kv_heads"] // world)
+        args.only_device_leg = True
     L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
     K, W = args.steps, max(args.warmup, 0)
     sp = er.step_params(rope_theta=w["theta"])
@@ -361,7 +372,12 @@ def run_ours(args, w, lens):
     ks = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
     vs = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
     out = torch.empty((L, B, H, D), device="cuda", dtype=torch.float32)
+    gathered = torch.empty((world, L, B, H, D), device="cuda", dtype=torch.float32) if shard_heads else None
     stream = torch.cuda.current_stream()
+
+    def exchange():
+        if shard_heads:      # every rank ends the step with all heads' outputs: [rank][L][B][H / N][128]
+            dist.all_gather_into_tensor(gathered, out)
 
     def barrier():
         if world > 1:
@@ -375,6 +391,7 @@ def run_ours(args, w, lens):
     set_start()
     for s in range(W):
         cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+        exchange()
     barrier()
     launches0 = er.lib().er_kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -382,6 +399,7 @@ def run_ours(args, w, lens):
     for s in range(K):
         i = (W + s) % pool
         cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
+        exchange()
     e1.record(stream)
     barrier()
     launches = er.lib().er_kernel_launch_count() - launches0
@@ -399,7 +417,7 @@ def run_ours(args, w, lens):
     assert cache.device_status() == 0, "device-side wait timed out"
     for b, n in enumerate(base_positions):
         assert cache.total_written(0, b) == n + W + K
-    tokens = B * K * world
+    tokens = B * K * (1 if shard_heads else world)
     value = tokens / (ms_total * 1e-3)
     bytes_total = sum(step_bytes(w, lens, W + s) for s in range(K))
     hbm_gbs = bytes_total / (ms_total * 1e-3) / 1e9       # per GPU
@@ -408,7 +426,11 @@ def run_ours(args, w, lens):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
                               "ms_per_step": ms_total / K, "hbm_gbs_per_gpu": round(hbm_gbs, 1), "gpu_launches": int(launches),
-                              "config": {"workload": w["name"]}, "note": "device leg only"}))
+                              "scaling": "strong" if shard_heads else "weak",
+                              "config": {"workload": w["name"],
+                                         "sharding": ("kv heads split over the GPUs, NCCL all-gather of the outputs every step" if shard_heads
+                                                      else "by sequence, one replica per GPU, no collective") if world > 1 else "single GPU"},
+                              "note": "device leg only"}))
         if world > 1:
             dist.destroy_process_group()
         return
