@@ -20,6 +20,11 @@ class ERGQAParams(C.Structure):
                 ("qBlockSize", C.c_uint32), ("kvSeqLen", C.c_uint32), ("qOffset", C.c_uint32)]
 
 
+class ERWindowedGQAParams(C.Structure):
+    _fields_ = [("numHeads", C.c_uint32), ("numKVHeads", C.c_uint32), ("headDim", C.c_uint32), ("kvStart", C.c_uint32),
+                ("kvCount", C.c_uint32), ("kvCapacity", C.c_uint32), ("attentionScale", C.c_float)]
+
+
 class ERRoPEParams(C.Structure):
     _fields_ = [("seqLen", C.c_uint32), ("numHeads", C.c_uint32), ("headDim", C.c_uint32), ("startPos", C.c_uint32),
                 ("theta", C.c_float), ("scalingFactor", C.c_float), ("partialRotaryFactor", C.c_float)]
@@ -40,7 +45,7 @@ class er_kv_buffers(C.Structure):
 class er_step_params(C.Structure):
     _fields_ = [("rope_theta", C.c_float), ("rope_scaling", C.c_float), ("softmax_scale", C.c_float),
                 ("apply_rope", C.c_uint32), ("q_norm_weight", C.c_void_p), ("k_norm_weight", C.c_void_p),
-                ("rms_eps", C.c_float), ("norm_weight_layer_stride", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+                ("rms_eps", C.c_float), ("norm_weight_layer_stride", C.c_uint32), ("sliding_window", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 # status codes (include/er_kv.h)
@@ -82,6 +87,7 @@ SYMBOLS = {
     "er_turboquant_quantize_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "er_gqa_attention_f16kv": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
+    "er_gqa_attention_f16kv_windowed": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERWindowedGQAParams), _vp]),
     "er_kv_append_rope_kv": (_i32, [_vp, _u32, _u32, _vp, _vp, _stp, _vp]),
     "er_kv_attention_decode": (_i32, [_vp, _u32, _u32, _vp, _vp, _u32, _u32, _stp, _vp]),
     "er_kv_attention_prefill": (_i32, [_vp, _u32, _u32, _vp, _vp, _u32, _u32, _u32, _stp, _vp]),

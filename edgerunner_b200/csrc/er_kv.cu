@@ -896,6 +896,41 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
     return ER_OK;
 }
 
+int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const uint16_t* v, float* out, const ERWindowedGQAParams* wp,
+                                        void* stream) {
+    if (!q || !k || !v || !out || !wp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (wp->headDim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "headDim %u: this backend's attention kernels are built for 128", wp->headDim);
+    if (wp->numKVHeads == 0 || wp->numHeads % wp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", wp->numHeads, wp->numKVHeads);
+    if (wp->numKVHeads > 16) return fail(ER_ERR_UNSUPPORTED, "numKVHeads %u > 16 for the raw-buffer operator", wp->numKVHeads);
+    if (wp->kvCount > wp->kvCapacity) return fail(ER_ERR_SHAPE, "kvCount %u > kvCapacity %u", wp->kvCount, wp->kvCapacity);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (wp->kvCount == 0 || wp->kvCapacity == 0) {   // the shader's rule: no rows -> zeros
+        const cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(wp->numHeads) * kHeadDim * sizeof(float), s);
+        return e == cudaSuccess ? ER_OK : fail(ER_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    }
+    Workspace* ws = nullptr;
+    int32_t rc = get_workspace(&ws);
+    if (rc != ER_OK) return rc;
+    DecodeParams p{};
+    p.q = q; p.out = out;
+    p.k_base = reinterpret_cast<const uint8_t*>(k);
+    p.v_base = reinterpret_cast<const uint8_t*>(v);
+    p.lengths = nullptr;
+    p.num_layers = 1; p.batch = 1;
+    p.num_q_heads = static_cast<int>(wp->numHeads);
+    const float scale = wp->attentionScale != 0.f ? wp->attentionScale : 1.0f / std::sqrt(static_cast<float>(wp->headDim));
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.rope_scaling = 1.f;
+    p.addr.token_major = 1; p.addr.num_kv_heads = static_cast<int>(wp->numKVHeads);
+    p.addr.max_seq_len = static_cast<int>(wp->kvCapacity); p.addr.page_size = static_cast<int>(wp->kvCapacity);
+    p.scratch = ws->scratch; p.done_counter = ws->counters; p.status = ws->counters + 1; p.item_counters = ws->counters + 16;
+    p.fixed_kv_len = static_cast<int>(wp->kvCount);
+    p.fixed_start = static_cast<int>(wp->kvStart % wp->kvCapacity);
+    const int group = static_cast<int>(wp->numHeads / wp->numKVHeads);
+    encode_token_major_maps(p, group, 1, 1, wp->kvCapacity, wp->numKVHeads);   // used when the range starts at slot 0
+    return dispatch_decode_f16(group, p, ws->num_sms, s);
+}
+
 // ---- cache-level device operators ----
 
 int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t lb, uint32_t le, const float* k, const float* v, const er_step_params* sp, void* stream) {
@@ -952,6 +987,8 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
     if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "attention kernels are built for head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
     if (kv->cfg.precision == ER_KV_FLOAT32) return fail(ER_ERR_UNSUPPORTED, "attention over a float32 cache is outside this backend's scope");
+    if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
+        return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
     // (layer, sequence) pairs are scheduled kMaxPairs at a time.
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
@@ -981,6 +1018,7 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         p.q_norm_w = s.q_norm_weight; p.k_norm_w = s.k_norm_weight;
         p.norm_stride = static_cast<int>(s.norm_weight_layer_stride); p.rms_eps = s.rms_eps;
         p.addr = kv->addressing();
+        p.window = static_cast<int>(std::min<uint32_t>(s.sliding_window, 0x7fffffffu));
         p.scratch = kv->d_scratch; p.done_counter = kv->d_counters; p.status = kv->d_counters + 1; p.item_counters = kv->d_counters + 16;
         if (kv->turbo)
             rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
@@ -1025,6 +1063,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
     if (rc != ER_OK) return rc;
+    if (s.sliding_window > 0) return fail(ER_ERR_UNSUPPORTED, "sliding_window applies to decode calls only");
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
                          static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;

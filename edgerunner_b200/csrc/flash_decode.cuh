@@ -54,6 +54,11 @@ struct DecodeParams {
     int fused_append;             // 1: the warp that owns the new row's unit converts it, uses it and stores it
     unsigned long long* trace;    // optional [gridDim.x][8] globaltimer stamps (diagnostics), else nullptr
     int pending;                  // rows appended but not yet committed to `lengths`
+    // Sliding-window / ring-range attention over fp16 rows (gemma4_decode_gqa_f16kv_windowed, Shaders/Gemma4Decode.metal:236-283):
+    // the rows visited are ring slots (start + i) % max_seq_len, i < count.  With `lengths`: window > 0 keeps the newest
+    // min(window, rows written) rows; window == 0 visits slots [0, count) as before.  Without: start = fixed_start.
+    int window;
+    int fixed_start;
     int advance;                  // added to lengths[...] by the last CTA to finish
     float scale_log2;             // softmax scale * log2(e)
     float rope_scaling;
@@ -122,8 +127,17 @@ __device__ __forceinline__ Segment locate_segment(const int* prefix, int num_pai
 __device__ __forceinline__ int kv_length(const DecodeParams& p, int pair) {
     if (p.lengths == nullptr) return p.fixed_kv_len;
     const int layer = p.layer_begin + pair / p.batch, seq = pair % p.batch;
-    const int n = p.lengths[layer * p.batch + seq] + p.pending;
-    return n < p.addr.max_seq_len ? n : p.addr.max_seq_len;
+    int n = p.lengths[layer * p.batch + seq] + p.pending;
+    n = n < p.addr.max_seq_len ? n : p.addr.max_seq_len;
+    return (p.window > 0 && p.window < n) ? p.window : n;
+}
+
+// First ring slot of the rows an item visits (count = kv_length of the pair).
+__device__ __forceinline__ int kv_start(const DecodeParams& p, int pair, int count) {
+    if (p.lengths == nullptr) return p.fixed_start;
+    if (p.window <= 0) return 0;
+    const int layer = p.layer_begin + pair / p.batch, seq = pair % p.batch;
+    return (p.lengths[layer * p.batch + seq] + p.pending - count) % p.addr.max_seq_len;
 }
 
 // ------------------------------------------------------------------------------------------ dense fp16 policy
@@ -186,9 +200,20 @@ struct DensePolicy {
     // Producer: K and V rows [t0, t0+ntok) of (layer, seq, head) -> stage.  Token-major storage needs one
     // 256-byte copy per row; page-major storage one copy per touched page.
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq,
-                                      int head, int t0, int ntok, int lane) {
+                                      int head, int t0, int ntok, int lane, int start) {
         const uint8_t* kl = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vl = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        if (start != 0) {
+            // Ring range: row t of the item sits in slot (start + t) % max_seq_len, so a tile is one or two slot runs.
+            if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
+            __syncwarp();
+            const int cap = p.addr.max_seq_len;
+            const int s0 = (start + t0) % cap;
+            const int n0 = min(ntok, cap - s0);
+            issue_rows(p, stage, bar, kl, vl, seq, head, s0, n0, lane);
+            if (n0 < ntok) issue_rows(p, stage + n0 * kRowBytesF16, bar, kl, vl, seq, head, 0, ntok - n0, lane);
+            return;
+        }
         if (p.use_tmap) {
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar, 2u * kTileBytesF16);
@@ -200,6 +225,12 @@ struct DensePolicy {
         }
         if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
         __syncwarp();
+        issue_rows(p, stage, bar, kl, vl, seq, head, t0, ntok, lane);
+    }
+
+    // K and V rows of slots [t0, t0+ntok) -> stage (K tile) and stage + kTileBytesF16 (V tile); the caller has armed `bar`.
+    __device__ __forceinline__ static void issue_rows(const DecodeParams& p, uint8_t* stage, uint64_t* bar, const uint8_t* kl,
+                                                      const uint8_t* vl, int seq, int head, int t0, int ntok, int lane) {
         if (p.addr.token_major) {
             for (int c = lane; c < 2 * ntok; c += 32) {
                 const int is_v = c >= ntok;
@@ -487,13 +518,14 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
+                const int start = kv_start(p, sg.pair, kv_len);
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     const int nun = min(UPT, sg.u1 - tu);
                     const int t0 = tu * kUnitTokens;
                     const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
                     const int s = k % kStages;
                     if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status);
-                    POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane);
+                    POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start);
                 }
                 cur += sg.u1 - sg.u0;
             }
@@ -528,8 +560,9 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     if (k == 0 && tid == 0) stamp(2);
                     if (POL::kFusedAppend && p.fused_append && !flags[0]) {
                         const int slot_new = q_pos % p.addr.max_seq_len;
-                        if (wunit < nun && tu + wunit == (slot_new >> 4))
-                            POL::patch_new_row(p, smem + s * POL::kStageBytes, wunit, slot_new & 15, layer, seq, sg.head, slot_new,
+                        const int row_new = p.window > 0 ? kv_len - 1 : slot_new;   // the newest row closes a window
+                        if (wunit < nun && tu + wunit == (row_new >> 4))
+                            POL::patch_new_row(p, smem + s * POL::kStageBytes, wunit, row_new & 15, layer, seq, sg.head, slot_new,
                                                p.k_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim,
                                                p.v_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim, cs, lane);
                     }

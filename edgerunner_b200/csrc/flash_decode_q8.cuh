@@ -94,7 +94,7 @@ struct Q8MmaPolicy {
     __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
 
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
-                                      int t0, int ntok, int lane) {
+                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/) {
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
         const uint8_t* kn = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;

@@ -38,7 +38,7 @@ struct TurboStaging {
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
                                          const float2*, int) {}
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
-                                      int t0, int ntok, int lane) {
+                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/) {
         const int nb = p.norm_fp16 ? 2 : 4;
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;

@@ -3,6 +3,7 @@
     RoPEKernel        Sources/EdgeRunnerMetal/RoPEKernel.swift:4-307     (execute / encodeNeoX)
     GQAKernel         Sources/EdgeRunnerMetal/GQAKernel.swift:4-187      (execute / encode on fp16 K/V)
     TurboQuantKernel  Sources/EdgeRunnerMetal/TurboQuantKernel.swift:13-112 (quantize rows)
+    Gemma4DecodeKernels  Sources/EdgeRunnerMetal/Gemma4DecodeKernels.swift:537-660 (runDecodeGQAF16KVWindowed only)
 
 `encode*` methods enqueue on a stream with device buffers (the command-buffer style of the reference);
 `execute*` methods are the array-in / array-out convenience forms used by the reference's tests.
@@ -12,7 +13,7 @@ import math
 
 import numpy as np
 
-from ._lib import ERGQAParams, ERRoPEParams, check, lib, ptr, stream_ptr
+from ._lib import ERGQAParams, ERRoPEParams, ERWindowedGQAParams, check, lib, ptr, stream_ptr
 
 
 def _torch():
@@ -69,6 +70,31 @@ class GQAKernel:
         vd = torch.as_tensor(np.ascontiguousarray(v, dtype=np.float16)).cuda()
         out = torch.empty_like(qd)
         self.encode(qd, kd, vd, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len, q_offset)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
+
+class Gemma4DecodeKernels:
+    """The sliding-window decode attention of the Gemma 4 kernel holder; its other kernels are outside this backend."""
+
+    def encode_decode_gqa_f16kv_windowed(self, q_buffer, key_cache_buffer, value_cache_buffer, output_buffer, num_heads,
+                                         num_kv_heads, head_dim, kv_start, kv_count, kv_capacity, attention_scale=None,
+                                         stream=None):
+        p = ERWindowedGQAParams(num_heads, num_kv_heads, head_dim, kv_start, kv_count, kv_capacity,
+                                0.0 if attention_scale is None else attention_scale)
+        check(lib().er_gqa_attention_f16kv_windowed(ptr(q_buffer), ptr(key_cache_buffer), ptr(value_cache_buffer),
+                                                    ptr(output_buffer), C.byref(p), stream_ptr(stream)))
+
+    def run_decode_gqa_f16kv_windowed(self, q, k, v, num_heads, num_kv_heads, head_dim, kv_start, kv_count, kv_capacity,
+                                      attention_scale=None):
+        torch = _torch()
+        qd = torch.as_tensor(np.ascontiguousarray(q, dtype=np.float32)).cuda()
+        kd = torch.as_tensor(np.ascontiguousarray(k, dtype=np.float16)).cuda()
+        vd = torch.as_tensor(np.ascontiguousarray(v, dtype=np.float16)).cuda()
+        assert qd.numel() == num_heads * head_dim and kd.numel() == vd.numel() == kv_capacity * num_kv_heads * head_dim
+        out = torch.empty_like(qd)
+        self.encode_decode_gqa_f16kv_windowed(qd, kd, vd, out, num_heads, num_kv_heads, head_dim, kv_start, kv_count,
+                                              kv_capacity, attention_scale)
         torch.cuda.synchronize()
         return out.cpu().numpy()
 

@@ -263,6 +263,25 @@ public:
     }
 };
 
+// Gemma4DecodeKernels (Sources/EdgeRunnerMetal/Gemma4DecodeKernels.swift): the sliding-window decode attention only.
+class Gemma4DecodeKernels {
+public:
+    // encodeDecodeGQAF16KVWindowed: ring rows (kvStart + i) % kvCapacity, i < kvCount; attentionScale 0 -> 1/sqrt(headDim)
+    void encodeDecodeGQAF16KVWindowed(void* stream, const float* qBuffer, const uint16_t* keyCacheBuffer, const uint16_t* valueCacheBuffer,
+                                      float* outputBuffer, int numHeads, int numKVHeads, int headDim, int kvStart, int kvCount,
+                                      int kvCapacity, float attentionScale = 0.f) const {
+        ERWindowedGQAParams p{};
+        p.numHeads = static_cast<uint32_t>(numHeads);
+        p.numKVHeads = static_cast<uint32_t>(numKVHeads);
+        p.headDim = static_cast<uint32_t>(headDim);
+        p.kvStart = static_cast<uint32_t>(kvStart);
+        p.kvCount = static_cast<uint32_t>(kvCount);
+        p.kvCapacity = static_cast<uint32_t>(kvCapacity);
+        p.attentionScale = attentionScale;
+        check(er_gqa_attention_f16kv_windowed(qBuffer, keyCacheBuffer, valueCacheBuffer, outputBuffer, &p, stream));
+    }
+};
+
 class TurboQuantKernel {
 public:
     // turboquant_quantize_rows dispatch (encodeTurboQuantRows, LlamaLanguageModel.swift:1754-1818)

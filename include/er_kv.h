@@ -151,7 +151,12 @@ typedef struct {
     const float* k_norm_weight;
     float rms_eps;
     uint32_t norm_weight_layer_stride;
-    uint32_t reserved[2];
+    /* Sliding-window decode (Gemma4GPUKVCache.attentionRange, Sources/EdgeRunner/Models/Gemma4/Gemma4GPUKVCache.swift:206-216;
+     * gemma4_decode_gqa_f16kv_windowed, Shaders/Gemma4Decode.metal:236-283): > 0 -> a decode call attends to the newest
+     * min(sliding_window, rows in the ring) rows of each sequence, wherever they sit in the ring; 0 = every row held.
+     * float16 caches only (ER_ERR_UNSUPPORTED for the other precisions and for er_kv_attention_prefill). */
+    uint32_t sliding_window;
+    uint32_t reserved;
 } er_step_params;
 
 const char* er_status_string(int32_t status);
@@ -241,6 +246,23 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
  * q/out: device [seqLen][numHeads][headDim] float; k/v: device [kvSeqLen][numKVHeads][headDim] fp16. */
 int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out,
                                const ERGQAParams* params, void* stream);
+
+/* gemma4_decode_gqa_f16kv_windowed (Shaders/Gemma4Decode.metal:236-283; host wrapper runDecodeGQAF16KVWindowed,
+ * Gemma4DecodeKernels.swift): one query token against ring rows (kvStart + i) % kvCapacity, i < kvCount, of a token-major
+ * fp16 K/V pair.  q/out: device [numHeads][128] float; k/v: device [kvCapacity][numKVHeads][128] fp16.  kvCount == 0 or
+ * kvCapacity == 0 writes zeros (the shader's rule); kvCount > kvCapacity is ER_ERR_SHAPE.  attentionScale 0 ->
+ * 1/sqrt(headDim), the wrapper's default (Gemma 4 passes 1.0).  headDim is 128 in this backend (the reference's Gemma shapes are 256 / 512). */
+typedef struct {
+    uint32_t numHeads;
+    uint32_t numKVHeads;
+    uint32_t headDim;
+    uint32_t kvStart;
+    uint32_t kvCount;
+    uint32_t kvCapacity;
+    float attentionScale;
+} ERWindowedGQAParams;
+int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const uint16_t* v, float* out,
+                                        const ERWindowedGQAParams* params, void* stream);
 
 /* No counterpart in the reference.  Same operator and arguments as er_gqa_attention_f16kv, for hosts that cannot
  * let the library allocate: a server whose own pool already owns all free device memory, or a latency-critical

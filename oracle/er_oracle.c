@@ -254,6 +254,46 @@ ERO_API void ero_gqa_f16kv(const float *q, const uint16_t *k16, const uint16_t *
     free(v);
 }
 
+/* gemma4_decode_gqa_f16kv_windowed (Shaders/Gemma4Decode.metal:222-283): one query token against the ring rows
+ * physical = (kvStart + i) % kvCapacity, i < kvCount of a token-major fp16 cache.  Per output element: a pass for the
+ * largest score, then value += exp(score - max) * V and sum += exp(score - max) in row order, output value / sum
+ * (0 when sum is not positive or there are no rows).  The score is a sequential fp32 dot product times the scale.
+ * Parity unpinned: the reference's tests for this kernel (Gemma4DecodeKernelTests.swift:335-474) compare against a CPU
+ * routine on generated inputs and hold no literal outputs. */
+ERO_API void ero_gqa_f16kv_windowed(const float *q, const uint16_t *k16, const uint16_t *v16, float *out, int num_heads,
+                                    int num_kv_heads, int head_dim, int kv_start, int kv_count, int kv_capacity,
+                                    float scale) {
+    const float *lut = half_lut();
+    int group = num_heads / num_kv_heads;
+    if (kv_count <= 0 || kv_capacity <= 0) {
+        for (int i = 0; i < num_heads * head_dim; ++i) out[i] = 0.0f;
+        return;
+    }
+    float *scores = (float *)malloc(sizeof(float) * (size_t)kv_count);
+    for (int head = 0; head < num_heads; ++head) {
+        int kv_head = head / group;
+        float max_score = -INFINITY;
+        for (int i = 0; i < kv_count; ++i) {
+            size_t base = ((size_t)((kv_start + i) % kv_capacity) * num_kv_heads + kv_head) * head_dim;
+            float dot = 0.0f;
+            for (int d = 0; d < head_dim; ++d) dot += q[(size_t)head * head_dim + d] * lut[k16[base + d]];
+            scores[i] = dot * scale;
+            if (scores[i] > max_score) max_score = scores[i];
+        }
+        for (int d = 0; d < head_dim; ++d) {
+            float sum = 0.0f, value = 0.0f;
+            for (int i = 0; i < kv_count; ++i) {
+                size_t base = ((size_t)((kv_start + i) % kv_capacity) * num_kv_heads + kv_head) * head_dim;
+                float w = expf(scores[i] - max_score);
+                value += w * lut[v16[base + d]];
+                sum += w;
+            }
+            out[(size_t)head * head_dim + d] = sum > 0.0f ? value / sum : 0.0f;
+        }
+    }
+    free(scores);
+}
+
 /* Split-K merge of per-block (max, sum, unnormalised acc) partials as in
  * gqa_decode_attention_packed_f16kv_reduce, GQA.metal:753-776. */
 ERO_API void ero_splitk_merge(const float *part_max, const float *part_sum, const float *part_acc,

@@ -63,6 +63,7 @@ def lib():
     L.ero_gqa_f32.argtypes = [f32p, f32p, f32p, f32p] + [C.c_int] * 8
     L.ero_gqa_f16kv.argtypes = [f32p, u16p, u16p, f32p] + [C.c_int] * 8
     L.ero_splitk_merge.argtypes = [f32p, f32p, f32p, C.c_int, C.c_int, f32p]
+    L.ero_gqa_f16kv_windowed.argtypes = [f32p, u16p, u16p, f32p] + [C.c_int] * 6 + [C.c_float]
     L.ero_tq_sign.restype = C.c_float
     L.ero_tq_sign.argtypes = [C.c_int, C.c_int]
     L.ero_tq_centroid.restype = C.c_float
@@ -184,6 +185,19 @@ def gqa_f16kv(q, k16, v16, causal=True, q_offset=0, threads=1):
     out = np.empty_like(q)
     lib().ero_gqa_f16kv(_p(q, F32), _p(k16, U16), _p(v16, U16), _p(out, F32), s, d, h, hkv, int(causal), t,
                         q_offset, threads)
+    return out
+
+
+def gqa_f16kv_windowed(q, k16, v16, kv_start, kv_count, scale=None):
+    """q: [H,D] float32; k16, v16: [capacity,Hkv,D] fp16 bit patterns; rows (kv_start + i) % capacity, i < kv_count."""
+    q = _f32(q)
+    k16 = np.ascontiguousarray(k16, dtype=np.uint16)
+    v16 = np.ascontiguousarray(v16, dtype=np.uint16)
+    h, d = q.shape
+    cap, hkv, _ = k16.shape
+    out = np.empty_like(q)
+    lib().ero_gqa_f16kv_windowed(_p(q, F32), _p(k16, U16), _p(v16, U16), _p(out, F32), h, hkv, d, kv_start, kv_count, cap,
+                                 float(1.0 / np.sqrt(d)) if scale is None else float(scale))
     return out
 
 

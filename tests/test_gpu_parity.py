@@ -923,3 +923,117 @@ def test_prefill_then_decode_consistency(er, oracle, torch):
     b.attention_prefill(0, 0, dev(torch, q2), o_pf, Hq, 2, sp)
     torch.cuda.synchronize()
     assert max_rel_err(o_pf[1].cpu().numpy(), o_dec[0, 0].cpu().numpy()) < TOL
+
+
+# ------------------------------------------------------------------ sliding window / ring-range decode (fp16 rows)
+
+@pytest.mark.parametrize("Hq,Hkv,capacity,kv_start,kv_count,scale", [
+    (8, 2, 8, 5, 6, None),          # Gemma4DecodeKernelTests.windowedF16KVGQA: the range wraps the 8-slot ring
+    (8, 2, 4, 0, 4, 1.0),           # ...UnscaledAttention
+    (8, 2, 512, 0, 512, None),      # the "real Gemma cache capacities" list of the fast kernel's test
+    (8, 2, 512, 33, 512, None),
+    (16, 8, 4096, 127, 384, None),
+    (16, 8, 4096, 1536, 512, 1.0 / 16),
+    (4, 4, 4096, 3584, 512, None),
+    (16, 8, 700, 650, 333, None),   # capacity that is no multiple of the 16-row unit, wrapped, ragged ends
+    (8, 2, 8, 3, 0, None),          # empty range -> zeros
+])
+def test_windowed_gqa_operator(er, oracle, torch, Hq, Hkv, capacity, kv_start, kv_count, scale):
+    """er_gqa_attention_f16kv_windowed against the restatement of gemma4_decode_gqa_f16kv_windowed."""
+    D = 128
+    rng = rng_for(900 + capacity + kv_start)
+    q = normal_f16(rng, (Hq, D))
+    if scale == 1.0:
+        q *= 0.1      # unscaled attention: keep the scores in the range the reference's test uses
+    k, v = normal_f16(rng, (capacity, Hkv, D)), normal_f16(rng, (capacity, Hkv, D))
+    got = er.Gemma4DecodeKernels().run_decode_gqa_f16kv_windowed(q, k, v, Hq, Hkv, D, kv_start, kv_count, capacity, scale)
+    want = oracle.gqa_f16kv_windowed(q, k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16),
+                                     kv_start, kv_count, scale)
+    if kv_count == 0:
+        assert not got.any()
+    else:
+        assert max_rel_err(got, want) < TOL
+
+
+def test_windowed_gqa_operator_errors(er, torch):
+    z = torch.zeros(8 * 128 * 8, dtype=torch.float32, device="cuda")
+    g = er.Gemma4DecodeKernels()
+    with pytest.raises(er.EdgeRunnerCUDAError):      # more rows than the ring holds
+        g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 128, 0, 9, 8)
+    with pytest.raises(er.EdgeRunnerCUDAError):      # the reference's 256 / 512 head sizes are outside this backend
+        g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 256, 0, 4, 8)
+
+
+@pytest.mark.parametrize("layout,page_size,T,window,B", [
+    ("head_major", 0, 48, 20, 2),      # window inside a larger ring: the range wraps with the ring
+    ("token_major", 0, 48, 20, 1),
+    ("paged", 16, 48, 37, 2),
+    ("head_major", 0, 40, 40, 1),      # Gemma4GPUKVCache's shape: ring capacity == slidingWindow
+    ("head_major", 0, 24, 100, 1),     # window wider than the ring: every slot
+])
+def test_sliding_window_decode(er, oracle, torch, layout, page_size, T, window, B):
+    """er_step_params.sliding_window: each decode step attends to the newest min(window, rows held) rows
+    (Gemma4GPUKVCache.attentionRange), fused step and split calls alike, before and after the ring wraps."""
+    D, Hq, Hkv, theta = 128, 8, 4, 1e4
+    rng = rng_for(950 + T + window)
+    lay = getattr(er.Layout, layout)
+    kw = {}
+    if lay == er.Layout.paged:
+        per_seq = (T + page_size - 1) // page_size
+        kw = dict(page_size=page_size, num_pages=per_seq * B + 1)
+    cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16, max_batch=B, layout=lay, **kw)
+    if lay == er.Layout.paged:
+        alloc = er.BlockTableAllocator(per_seq * B + 1, page_size, free_order=rng.permutation(per_seq * B + 1))
+        for b in range(B):
+            cache.set_block_table(b, alloc.ensure(b, T))
+    sp = er.step_params(rope_theta=theta, sliding_window=window)
+    pre = [0, 5][:B]                       # sequence 1 starts with 5 rows: the two ranges differ
+    kc = np.zeros((B, T, Hkv, D), np.uint16)
+    vc = np.zeros((B, T, Hkv, D), np.uint16)
+    for b in range(B):
+        if pre[b]:
+            K, V = normal_f16(rng, (pre[b], Hkv, D)), normal_f16(rng, (pre[b], Hkv, D))
+            cache.write_rows(0, b, 0, pre[b], dev(torch, K), dev(torch, V), sp)
+            for t in range(pre[b]):
+                kc[b, t] = oracle.rope_neox_to_f16(K[t:t + 1], t, theta)[0]
+            vc[b, :pre[b]] = oracle.f32_to_f16_bits(V)
+    for s in range(T + 21):
+        q, k, v = normal_f16(rng, (1, B, Hq, D)), normal_f16(rng, (1, B, Hkv, D)), normal_f16(rng, (1, B, Hkv, D))
+        out = torch.full((1, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        if s % 3 == 2:      # split form
+            cache.append_rope_kv(dev(torch, k), dev(torch, v), sp)
+            cache.attention_decode(dev(torch, q), out, Hq, sp, pending=1)
+            cache.advance(1)
+        else:
+            cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        got = out.cpu().numpy()
+        for b in range(B):
+            pos = pre[b] + s
+            kc[b, pos % T] = oracle.rope_neox_to_f16(k[0, b][None], pos, theta)[0]
+            vc[b, pos % T] = oracle.f32_to_f16_bits(v[0, b])
+            count = min(pos + 1, T, window)
+            want = oracle.gqa_f16kv_windowed(oracle.rope_neox(q[0, b][None], pos, theta)[0], kc[b], vc[b],
+                                             (pos + 1 - count) % T, count)
+            assert max_rel_err(got[0, b], want) < TOL, (s, b)
+    for b in range(B):      # the ring itself is untouched by the window: newest T rows, oldest first
+        gk, gv = cache.retrieve(0, np.float16, seq=b)
+        n = pre[b] + T + 21
+        order = [(n + i) % T for i in range(T)]
+        assert np.array_equal(gk.view(np.uint16).reshape(T, Hkv, D), kc[b][order])
+        assert np.array_equal(gv.view(np.uint16).reshape(T, Hkv, D), vc[b][order])
+
+
+def test_sliding_window_unsupported_combinations(er, torch):
+    D, Hq, Hkv = 128, 8, 4
+    sp = er.step_params(sliding_window=8)
+    z = lambda *s: torch.zeros(s, dtype=torch.float32, device="cuda")
+    for prec, kw in ((er.Precision.q8_0, {}), (er.Precision.turboquantV2, dict(key_type=4, value_type=3))):
+        cache = er.KVCache(32, 1, Hkv, D, prec, **kw)
+        with pytest.raises(er.EdgeRunnerCUDAError):
+            cache.decode_step(z(1, 1, Hq, D), z(1, 1, Hkv, D), z(1, 1, Hkv, D), z(1, 1, Hq, D), Hq, sp)
+    cache = er.KVCache(32, 1, Hkv, D, er.Precision.float16)
+    cache.write_rows(0, 0, 0, 4, z(4, Hkv, D), z(4, Hkv, D), er.step_params())
+    with pytest.raises(er.EdgeRunnerCUDAError):
+        cache.attention_prefill(0, 0, z(4, Hq, D), z(4, Hq, D), Hq, 4, sp)

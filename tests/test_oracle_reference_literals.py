@@ -321,3 +321,42 @@ def test_q8_0_attention_matches_dequantised_float_attention(oracle):
     want = oracle.gqa_f32(q, oracle.q8_decode_rows(k8), oracle.q8_decode_rows(v8), causal=True, q_offset=T - 3)
     assert np.array_equal(got, want)
     assert np.max(np.abs(oracle.q8_decode_rows(k8) - k)) < 0.02      # |x| <= ~4.5, step = max/127
+
+
+def _windowed_inputs(num_heads, num_kv_heads, head_dim, capacity, mods):
+    """The generated inputs of the reference's windowed-attention tests (Gemma4DecodeKernelTests.swift:344-346, 389-391)."""
+    (qm, qo, qd), (km, ko, kd), (vm, vo, vd) = mods
+    q = np.array([((i % qm) - qo) / qd for i in range(num_heads * head_dim)], np.float32).reshape(num_heads, head_dim)
+    k = np.array([((i % km) - ko) / kd for i in range(capacity * num_kv_heads * head_dim)], np.float32)
+    v = np.array([((i % vm) - vo) / vd for i in range(capacity * num_kv_heads * head_dim)], np.float32)
+    shape = (capacity, num_kv_heads, head_dim)
+    return q, k.astype(np.float16).view(np.uint16).reshape(shape), v.astype(np.float16).view(np.uint16).reshape(shape)
+
+
+@pytest.mark.parametrize("head_dim,capacity,kv_start,kv_count,scale,mods", [
+    (256, 8, 5, 6, None, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0))),    # windowedF16KVGQA: wraps the 8-slot ring
+    (512, 8, 5, 6, None, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0))),
+    (256, 4, 0, 4, 1.0, ((17, 8, 11.0), (13, 6, 13.0), (7, 3, 7.0))),      # windowedF16KVGQAUnscaledAttention
+    (128, 8, 5, 6, None, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0))),    # the head size this backend's kernels are built for
+])
+def test_windowed_gqa_equals_attention_over_the_gathered_ring_rows(oracle, head_dim, capacity, kv_start, kv_count, scale, mods):
+    """gemma4_decode_gqa_f16kv_windowed on the reference tests' shapes and generated inputs: the ring range is a row
+    gather, so the result must equal the plain fp16-KV attention restatement over the gathered rows (within the fp32
+    noise of the two summation orders); the test's own CPU routine is the same two-pass form."""
+    q, k16, v16 = _windowed_inputs(8, 2, head_dim, capacity, mods)
+    got = oracle.gqa_f16kv_windowed(q, k16, v16, kv_start, kv_count, scale)
+    rows = [(kv_start + i) % capacity for i in range(kv_count)]
+    s = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    # gqa_f16kv scales by 1/sqrt(D): fold the requested scale into q
+    want = oracle.gqa_f16kv((q * (s * math.sqrt(head_dim)))[None], k16[rows], v16[rows], causal=False)[0]
+    assert np.abs(got - want).max() < 2e-6
+    kf, vf = k16.view(np.float16).astype(np.float64)[rows], v16.view(np.float16).astype(np.float64)[rows]
+    for head in (0, 3, 7):
+        sc = kf[:, head // 4] @ q[head].astype(np.float64) * s
+        w = np.exp(sc - sc.max())
+        assert np.abs(got[head] - (w / w.sum()) @ vf[:, head // 4]).max() < 2e-6
+
+
+def test_windowed_gqa_empty_range_is_zero(oracle):
+    q, k16, v16 = _windowed_inputs(8, 2, 128, 8, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0)))
+    assert not oracle.gqa_f16kv_windowed(q, k16, v16, 3, 0).any()
