@@ -64,6 +64,9 @@ WORKLOADS = {
     "cfg3": dict(name="cfg3: Llama-3.1-8B shape, 32 layers, batch 64, fp16 KV in 16-token pages, context U[1024,16384]",
                  layers=32, batch=64, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
                  page_size=16, theta=5.0e5),
+    "cfg3_contiguous": dict(name="cfg3 heads (32 q / 8 kv) on contiguous head-major rows, 8 layers, batch 8, context 32768 "
+                                 "(separates the page gather from the kernel; not a BASELINE configuration)",
+                            layers=8, batch=8, heads=32, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=5.0e5),
     # BASELINE.json configs[4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
     # already in the cache (Qwen3-4B heads, TurboQuant turbo4/turbo4 rows in 64-token pages); tensor-core bound
     "cfg4_prefill": dict(name="cfg4 prefill chunk: Qwen3-4B heads, 2048 query rows at the end of a 131072-token context, "

@@ -1,17 +1,23 @@
-// Instantiations of the persistent flash-decode kernel for fp16 rows (GQA group sizes 1, 2, 4).
+// Instantiations of the persistent flash-decode kernel for fp16 rows (GQA group sizes 1, 2, 4, 8).
 #include "launchers.h"
+#include "flash_decode_dense_mma.cuh"
 #include "tmap.h"
 
 namespace er {
+
+using Dense4 = DenseMmaPolicy<4, 11, 1, 2>;
+using Dense8 = DenseMmaPolicy<8, 10, 1, 2>;
 
 int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
     switch (group) {
         case 1: return launch_decode_policy<DensePolicy<1, 6, 2, 4>>(p, grid, stream);
         // 12 consumer warps in two groups over 96-token tiles, 4 stages: best of the measured shapes on B200
         case 2: return launch_decode_policy<DensePolicy<2, 6, 2, 4>>(p, grid, stream);
-        // group 4 holds 64 query registers per lane: 11 consumer warps + producer keep the 168-register budget (warps are
-        // allocated in fours); one group over 176-token tiles, 2 stages (5 % faster on 16-token pages than two groups of 5)
-        case 4: return launch_decode_policy<DensePolicy<4, 11, 1, 2>>(p, grid, stream);
+        // groups 4 and 8 run both contractions on the tensor cores (the lane-owns-dims form needs 512 FMAs per lane and unit
+        // for 4 heads and 128 query registers for 8): 11 consumer warps + producer keep the 168-register budget (warps
+        // are allocated in fours); one group over 176-token tiles, 2 stages
+        case 4: return launch_decode_policy<Dense4>(p, grid, stream);
+        case 8: return launch_decode_policy<Dense8>(p, grid, stream);
         default: return kNotBuilt;
     }
 }
@@ -20,7 +26,8 @@ int decode_dense_tile_tokens(int group) {
     switch (group) {
         case 1: return DensePolicy<1, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
         case 2: return DensePolicy<2, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
-        case 4: return DensePolicy<4, 11, 1, 2>::kUnitsPerTile * kUnitTokens;
+        case 4: return Dense4::kUnitsPerTile * kUnitTokens;
+        case 8: return Dense8::kUnitsPerTile * kUnitTokens;
         default: return 0;
     }
 }

@@ -308,6 +308,16 @@ def test_batched_ragged_paged_llama_shape(er, oracle, torch):
                       theta=5e5, page_size=16, ragged=True)
 
 
+@pytest.mark.parametrize("layout,page_size", [("head_major", 0), ("token_major", 0), ("paged", 32)])
+def test_group8_and_group4_tensor_core_policy(er, oracle, torch, layout, page_size):
+    """GQA groups 4 and 8 on fp16 rows run both contractions on the tensor cores: ragged batches, several steps, every
+    layout, contexts from a single row to several tiles."""
+    lay = getattr(er.Layout, layout)
+    _run_dense_config(er, oracle, torch, lay, L=2, B=3, Hq=32, Hkv=4, ctx=900, steps=3, seed=40, page_size=page_size, ragged=True)
+    _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=2, ctx=1, steps=19, seed=41, page_size=page_size)
+    _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=4, ctx=3, steps=20, seed=42, page_size=page_size)
+
+
 def test_group1_and_tiny_contexts(er, oracle, torch):
     _run_dense_config(er, oracle, torch, er.Layout.head_major, L=1, B=3, Hq=4, Hkv=4, ctx=40, steps=2, seed=5, ragged=True)
     _run_dense_config(er, oracle, torch, er.Layout.token_major, L=2, B=2, Hq=8, Hkv=2, ctx=1, steps=18, seed=6)
@@ -609,12 +619,13 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
 
 # --------------------------------------------------------------------------------------------- Q/K head norm (fused_qk_norm_rope_neox)
 
-@pytest.mark.parametrize("precision", ["float16", "turbo", "q8_0"])
-def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision):
+@pytest.mark.parametrize("precision,Hq,Hkv", [("float16", 16, 8), ("float16", 32, 8), ("float16", 32, 4), ("turbo", 16, 8),
+                                              ("q8_0", 16, 8)])
+def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision, Hq, Hkv):
     """er_step_params.q_norm_weight / k_norm_weight: per-head RMS norm before RoPE (fused_qk_norm_rope_neox,
     Shaders/RoPE.metal:119-173) on every cache kind.  The K rows the cache ends up holding are compared bit for bit with
     the oracle's norm -> RoPE -> store; the attention outputs within the usual bounds."""
-    L, B, Hq, Hkv, D, ctx, theta, eps = 2, 2, 16, 8, 128, 90, THETA_QWEN3, 1e-6
+    L, B, D, ctx, theta, eps = 2, 2, 128, 90, THETA_QWEN3, 1e-6
     rng = rng_for(90)
     wq = (1.0 + 0.1 * rng.standard_normal((L, D), dtype=np.float32)).astype(np.float32)
     wk = (1.0 + 0.1 * rng.standard_normal((L, D), dtype=np.float32)).astype(np.float32)
