@@ -833,13 +833,54 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
                                       out_mask, out_meta, static_cast<cudaStream_t>(stream), check_launch);
 }
 
+// Shapes the persistent flash-decode / tensor-core prefill kernels are built for; everything else on raw buffers goes
+// through generic_decode_kernel.
+static bool flash_shape(uint32_t head_dim, uint32_t heads, uint32_t kv_heads) {
+    const uint32_t g = heads / kv_heads;
+    return head_dim == kHeadDim && kv_heads <= 16 && (g == 1 || g == 2 || g == 4 || g == 8);
+}
+
+// One query row against ring rows (start + i) % capacity, i < count, of token-major fp16 buffers (count > 0).
+static int32_t generic_decode_row(Workspace* ws, const float* q, const uint16_t* k, const uint16_t* v, float* out, uint32_t heads,
+                                  uint32_t kv_heads, uint32_t head_dim, uint32_t start, uint32_t count, uint32_t capacity, float scale,
+                                  cudaStream_t stream) {
+    GenericDecodeParams p{};
+    p.q = q; p.out = out;
+    p.k = reinterpret_cast<const __half*>(k);
+    p.v = reinterpret_cast<const __half*>(v);
+    p.num_heads = static_cast<int>(heads); p.num_kv_heads = static_cast<int>(kv_heads); p.head_dim = static_cast<int>(head_dim);
+    p.start = static_cast<int>(start); p.count = static_cast<int>(count); p.capacity = static_cast<int>(capacity);
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.scratch = ws->scratch; p.counters = ws->counters + 16;
+    const int rc = launch_decode_generic(p, ws->num_sms, kScratchFloatsPerCta * static_cast<size_t>(ws->num_sms), ws->counter_ints - 16, stream);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rc == kNotBuilt)
+        return fail(ER_ERR_UNSUPPORTED, "attention on raw buffers: headDim %u must be even and <= 512, numHeads %u <= %zu", head_dim, heads,
+                    ws->counter_ints - 16);
+    if (rc != 0) return fail(ER_ERR_CUDA, "generic_decode_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return ER_OK;
+}
+
 int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out, const ERGQAParams* gp, void* stream) {
     if (!q || !k || !v || !out || !gp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
-    if (gp->headDim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "headDim %u: this backend's attention kernels are built for 128", gp->headDim);
     if (gp->numKVHeads == 0 || gp->numHeads % gp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", gp->numHeads, gp->numKVHeads);
-    if (gp->numKVHeads > 16) return fail(ER_ERR_UNSUPPORTED, "numKVHeads %u > 16 for the raw-buffer operator", gp->numKVHeads);
     const uint32_t kv_seq = gp->kvSeqLen > 0 ? gp->kvSeqLen : gp->seqLen;
     if (gp->seqLen == 0 || kv_seq == 0) return ER_OK;
+    if (!flash_shape(gp->headDim, gp->numHeads, gp->numKVHeads)) {
+        // other head sizes / groups: one launch of the generic kernel per query row (row r sees keys 0 .. r + qOffset)
+        Workspace* gws = nullptr;
+        int32_t grc = get_workspace(&gws);
+        if (grc != ER_OK) return grc;
+        const float sc = gp->scale != 0.f ? gp->scale : 1.0f / std::sqrt(static_cast<float>(gp->headDim));
+        const size_t row_elems = static_cast<size_t>(gp->numHeads) * gp->headDim;
+        for (uint32_t r = 0; r < gp->seqLen; ++r) {
+            const uint64_t visible = gp->causal ? std::min<uint64_t>(kv_seq, static_cast<uint64_t>(r) + gp->qOffset + 1) : kv_seq;
+            grc = generic_decode_row(gws, q + r * row_elems, k, v, out + r * row_elems, gp->numHeads, gp->numKVHeads, gp->headDim, 0,
+                                     static_cast<uint32_t>(visible), kv_seq, sc, static_cast<cudaStream_t>(stream));
+            if (grc != ER_OK) return grc;
+        }
+        return ER_OK;
+    }
     if (gp->seqLen > 1) {   // prompt / chunk: tensor-core kernel
         PrefillParams pp{};
         pp.q = q; pp.out = out;
@@ -899,18 +940,19 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
 int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const uint16_t* v, float* out, const ERWindowedGQAParams* wp,
                                         void* stream) {
     if (!q || !k || !v || !out || !wp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
-    if (wp->headDim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "headDim %u: this backend's attention kernels are built for 128", wp->headDim);
     if (wp->numKVHeads == 0 || wp->numHeads % wp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", wp->numHeads, wp->numKVHeads);
-    if (wp->numKVHeads > 16) return fail(ER_ERR_UNSUPPORTED, "numKVHeads %u > 16 for the raw-buffer operator", wp->numKVHeads);
     if (wp->kvCount > wp->kvCapacity) return fail(ER_ERR_SHAPE, "kvCount %u > kvCapacity %u", wp->kvCount, wp->kvCapacity);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (wp->kvCount == 0 || wp->kvCapacity == 0) {   // the shader's rule: no rows -> zeros
-        const cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(wp->numHeads) * kHeadDim * sizeof(float), s);
+        const cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(wp->numHeads) * wp->headDim * sizeof(float), s);
         return e == cudaSuccess ? ER_OK : fail(ER_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     }
     Workspace* ws = nullptr;
     int32_t rc = get_workspace(&ws);
     if (rc != ER_OK) return rc;
+    if (!flash_shape(wp->headDim, wp->numHeads, wp->numKVHeads))   // the reference's Gemma 4 head sizes (256 / 512) land here
+        return generic_decode_row(ws, q, k, v, out, wp->numHeads, wp->numKVHeads, wp->headDim, wp->kvStart % wp->kvCapacity, wp->kvCount,
+                                  wp->kvCapacity, wp->attentionScale != 0.f ? wp->attentionScale : 1.0f / std::sqrt(static_cast<float>(wp->headDim)), s);
     DecodeParams p{};
     p.q = q; p.out = out;
     p.k_base = reinterpret_cast<const uint8_t*>(k);

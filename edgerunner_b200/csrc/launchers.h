@@ -27,6 +27,23 @@ int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cuda
 // shape or the layout is not covered (the caller then uses launch_prefill_f16).
 int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream);
 
+// One query token against ring rows (start + i) % capacity, i < count, of token-major fp16 K/V [capacity][kv heads][head_dim];
+// any even head_dim <= 512, any GQA group (decode_generic.cu).  scratch: nsplit x heads x (head_dim + 2) floats at most
+// scratch_floats; counters: one zeroed int per head.  chunk / nsplit are filled by the launcher.
+struct GenericDecodeParams {
+    const float* q;      // [num_heads][head_dim]
+    const __half* k;
+    const __half* v;
+    float* out;          // [num_heads][head_dim]
+    int num_heads, num_kv_heads, head_dim;
+    int start, count, capacity;
+    float scale_log2;
+    float* scratch;
+    int* counters;
+    int chunk, nsplit;
+};
+int launch_decode_generic(GenericDecodeParams p, int num_sms, size_t scratch_floats, size_t counter_ints, cudaStream_t stream);
+
 template <class POL>
 inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
     constexpr int kSmem = DecodeSmem<POL>::kTotal;

@@ -243,7 +243,9 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
                                     void* stream);
 
 /* GQAKernel.encode on an fp16 K/V pair -> gqa_attention_f16kv (GQAKernel.swift:113-172, Shaders/GQA.metal:278-387).
- * q/out: device [seqLen][numHeads][headDim] float; k/v: device [kvSeqLen][numKVHeads][headDim] fp16. */
+ * q/out: device [seqLen][numHeads][headDim] float; k/v: device [kvSeqLen][numKVHeads][headDim] fp16.
+ * headDim 128 with 1/2/4/8 query heads per kv head and <= 16 kv heads: persistent flash-decode kernel (seqLen 1) or
+ * tensor-core prefill kernel (seqLen > 1); other even headDim <= 512 / groups: a plain split kernel, one launch per row. */
 int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out,
                                const ERGQAParams* params, void* stream);
 
@@ -251,7 +253,9 @@ int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t
  * Gemma4DecodeKernels.swift): one query token against ring rows (kvStart + i) % kvCapacity, i < kvCount, of a token-major
  * fp16 K/V pair.  q/out: device [numHeads][128] float; k/v: device [kvCapacity][numKVHeads][128] fp16.  kvCount == 0 or
  * kvCapacity == 0 writes zeros (the shader's rule); kvCount > kvCapacity is ER_ERR_SHAPE.  attentionScale 0 ->
- * 1/sqrt(headDim), the wrapper's default (Gemma 4 passes 1.0).  headDim is 128 in this backend (the reference's Gemma shapes are 256 / 512). */
+ * 1/sqrt(headDim), the wrapper's default (Gemma 4 passes 1.0).  headDim 128 with 1/2/4/8 query heads per kv head runs the
+ * persistent flash-decode kernel; any other even headDim <= 512 (the reference's Gemma shapes are 256 / 512) or group
+ * runs a plain split kernel. */
 typedef struct {
     uint32_t numHeads;
     uint32_t numKVHeads;

@@ -967,12 +967,68 @@ def test_windowed_gqa_operator(er, oracle, torch, Hq, Hkv, capacity, kv_start, k
 
 
 def test_windowed_gqa_operator_errors(er, torch):
-    z = torch.zeros(8 * 128 * 8, dtype=torch.float32, device="cuda")
+    z = torch.zeros(8 * 1024 * 8, dtype=torch.float32, device="cuda")
     g = er.Gemma4DecodeKernels()
     with pytest.raises(er.EdgeRunnerCUDAError):      # more rows than the ring holds
         g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 128, 0, 9, 8)
-    with pytest.raises(er.EdgeRunnerCUDAError):      # the reference's 256 / 512 head sizes are outside this backend
-        g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 256, 0, 4, 8)
+    with pytest.raises(er.EdgeRunnerCUDAError):      # head sizes above 512 (and odd ones) are not built
+        g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 1024, 0, 4, 8)
+    with pytest.raises(er.EdgeRunnerCUDAError):
+        g.encode_decode_gqa_f16kv_windowed(z, z, z, z, 8, 2, 127, 0, 4, 8)
+
+
+def _formula_inputs(num_heads, num_kv_heads, head_dim, capacity, mods):
+    """Generated inputs of the reference's windowed-attention tests (Gemma4DecodeKernelTests.swift:344-346, 389-391)."""
+    (qm, qo, qd), (km, ko, kd), (vm, vo, vd) = mods
+    q = np.array([((i % qm) - qo) / qd for i in range(num_heads * head_dim)], np.float32).reshape(num_heads, head_dim)
+    shape = (capacity, num_kv_heads, head_dim)
+    n = capacity * num_kv_heads * head_dim
+    k = np.array([((i % km) - ko) / kd for i in range(n)], np.float32).astype(np.float16).reshape(shape)
+    v = np.array([((i % vm) - vo) / vd for i in range(n)], np.float32).astype(np.float16).reshape(shape)
+    return q, k, v
+
+
+@pytest.mark.parametrize("head_dim,capacity,kv_start,kv_count,scale,mods", [
+    (256, 8, 5, 6, None, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0))),    # windowedF16KVGQA, both Gemma head sizes
+    (512, 8, 5, 6, None, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0))),
+    (256, 4, 0, 4, 1.0, ((17, 8, 11.0), (13, 6, 13.0), (7, 3, 7.0))),      # windowedF16KVGQAUnscaledAttention
+    (256, 512, 0, 512, None, None),        # "real Gemma cache capacities" (fast kernel's test), seeded random inputs
+    (256, 512, 33, 512, None, None),
+    (512, 4096, 127, 384, None, None),
+    (512, 4096, 1536, 512, None, None),
+    (512, 4096, 3584, 512, None, None),
+    (64, 100, 90, 77, None, None),         # small head size, odd capacity, wrapped
+])
+def test_windowed_gqa_operator_reference_test_shapes(er, oracle, torch, head_dim, capacity, kv_start, kv_count, scale, mods):
+    """The shapes of Gemma4DecodeKernelTests (8 q / 2 kv heads, head sizes 256 and 512) with the tests' generated inputs,
+    at the tests' tolerance of 2e-3 absolute and at this suite's relative bound."""
+    Hq, Hkv = 8, 2
+    if mods is not None:
+        q, k, v = _formula_inputs(Hq, Hkv, head_dim, capacity, mods)
+    else:
+        rng = rng_for(970 + capacity + kv_start)
+        q, k, v = normal_f16(rng, (Hq, head_dim)) * 0.5, normal_f16(rng, (capacity, Hkv, head_dim)), normal_f16(rng, (capacity, Hkv, head_dim))
+    got = er.Gemma4DecodeKernels().run_decode_gqa_f16kv_windowed(q, k, v, Hq, Hkv, head_dim, kv_start, kv_count, capacity, scale)
+    want = oracle.gqa_f16kv_windowed(q, k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16),
+                                     kv_start, kv_count, scale)
+    assert np.abs(got - want).max() < 2e-3
+    assert attention_err(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,S,T,q_offset,causal", [
+    (6, 2, 64, 5, 40, 35, True),       # group 3, head size 64: neither is a template of the persistent kernels
+    (12, 4, 128, 1, 300, 0, False),    # group 3 at head size 128
+    (40, 20, 96, 3, 50, 47, True),     # more than 16 kv heads
+    (4, 4, 256, 2, 64, 62, True),
+])
+def test_gqa_operator_other_head_sizes_and_groups(er, oracle, torch, Hq, Hkv, D, S, T, q_offset, causal):
+    """er_gqa_attention_f16kv outside the persistent kernels' shapes: one launch of the generic kernel per query row."""
+    rng = rng_for(980 + D + Hq)
+    q, k, v = normal_f16(rng, (S, Hq, D)), normal_f16(rng, (T, Hkv, D)), normal_f16(rng, (T, Hkv, D))
+    got = er.GQAKernel().execute_f16kv(q, k, v, S, D, Hq, Hkv, causal, kv_seq_len=T, q_offset=q_offset).reshape(S, Hq, D)
+    want = oracle.gqa_f16kv(q, k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16), causal=causal,
+                            q_offset=q_offset)
+    assert max_rel_err(got, want) < TOL
 
 
 @pytest.mark.parametrize("layout,page_size,T,window,B", [
