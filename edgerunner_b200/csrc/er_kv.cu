@@ -111,7 +111,7 @@ int32_t decode_status(int rc, int group, int kbits, int vbits) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rc == 0) return ER_OK;
     if (rc == kNotBuilt)
-        return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4 (and 8 on fp16 and q8_0 rows) and presets turbo3/turbo4 are",
+        return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4, 8 and presets turbo3/turbo4 are",
                     group, kbits, vbits);
     return fail(ER_ERR_CUDA, "flash_decode_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
 }

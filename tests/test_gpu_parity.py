@@ -517,6 +517,13 @@ def test_turboquant_config4_shape_paged(er, oracle, torch):
                       norm_format=er.NormFormat.float16, layout=er.Layout.paged, page_size=64, ragged=True)
 
 
+@pytest.mark.parametrize("kbits,vbits", [(4, 4), (4, 3), (3, 3)])
+def test_turboquant_group8(er, oracle, torch, kbits, vbits):
+    """8 query heads per kv head (one full n-tile of the tensor-core policy) on TurboQuant rows."""
+    _run_turbo_config(er, oracle, torch, L=1, B=2, Hq=32, Hkv=4, ctx=600, steps=2, seed=60 + kbits + vbits, kbits=kbits, vbits=vbits,
+                      norm_format=er.NormFormat.float32, layout=er.Layout.head_major, ragged=True)
+
+
 def test_turboquant_host_append_and_decoded_retrieve(er, oracle):
     """KVCache.append on a TurboQuant cache + retrieveDecodedTurboQuant (KVCacheTests.swift:221-240) against the
     oracle's cache; decoded rows equal up to the float rounding of the inverse transform's scale order."""
