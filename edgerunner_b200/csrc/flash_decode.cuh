@@ -199,10 +199,36 @@ struct DensePolicy {
 
     // Producer: K and V rows [t0, t0+ntok) of (layer, seq, head) -> stage.  Token-major storage needs one
     // 256-byte copy per row; page-major storage one copy per touched page.
+    template <class WAIT>
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq,
-                                      int head, int t0, int ntok, int lane, int start) {
+                                      int head, int t0, int ntok, int lane, int start, WAIT&& wait_free) {
         const uint8_t* kl = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vl = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        if (start == 0 && !p.use_tmap && !p.addr.token_major && p.addr.pages_per_seq != 0) {
+            // Paged rows: each lane looks its page up in the block table BEFORE waiting for the stage, so that the
+            // dependent global read overlaps the time the consumers still need (it sat on the refill path otherwise).
+            const int ps = p.addr.page_size;
+            const int first_page = t0 / ps;
+            const int ncopy = 2 * ((t0 + ntok - 1) / ps - first_page + 1);
+            const int tb = max(t0, (first_page + (lane >> 1)) * ps);
+            const int te = min(t0 + ntok, (first_page + (lane >> 1) + 1) * ps);
+            const int64_t row = lane < ncopy ? row_index(p.addr, seq, head, tb) : 0;
+            wait_free();
+            if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
+            __syncwarp();
+            if (lane < ncopy)
+                bulk_g2s(stage + (lane & 1) * kTileBytesF16 + (tb - t0) * kRowBytesF16, ((lane & 1) ? vl : kl) + row * kRowBytesF16,
+                         static_cast<uint32_t>(te - tb) * kRowBytesF16, bar);
+            for (int c = lane + 32; c < ncopy; c += 32) {
+                const int is_v = c & 1, sgi = c >> 1;
+                const int b = max(t0, (first_page + sgi) * ps);
+                const int e = min(t0 + ntok, (first_page + sgi + 1) * ps);
+                bulk_g2s(stage + is_v * kTileBytesF16 + (b - t0) * kRowBytesF16,
+                         (is_v ? vl : kl) + row_index(p.addr, seq, head, b) * kRowBytesF16, static_cast<uint32_t>(e - b) * kRowBytesF16, bar);
+            }
+            return;
+        }
+        wait_free();
         if (start != 0) {
             // Ring range: row t of the item sits in slot (start + t) % max_seq_len, so a tile is one or two slot runs.
             if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * kRowBytesF16 * 2);
@@ -524,8 +550,11 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     const int t0 = tu * kUnitTokens;
                     const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
                     const int s = k % kStages;
-                    if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status);
-                    POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start);
+                    // the policy calls this once, after any address lookups that can run while the stage is still busy
+                    auto wait_free = [&]() {
+                        if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status);
+                    };
+                    POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start, wait_free);
                 }
                 cur += sg.u1 - sg.u0;
             }

@@ -93,8 +93,9 @@ struct Q8MmaPolicy {
                                          const float2*, int) {}
     __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
 
+    template <class WAIT>
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
-                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/) {
+                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/, WAIT&& wait_free) {
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
         const uint8_t* kn = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
@@ -102,6 +103,9 @@ struct Q8MmaPolicy {
         const int ps = p.addr.page_size;
         const int first_page = t0 / ps;
         const int nseg = (t0 + ntok - 1) / ps - first_page + 1;
+        // the lane's first copy: its page is looked up in the block table while the stage is still busy
+        const int64_t row0 = lane < 4 * nseg ? row_index(p.addr, seq, head, max(t0, (first_page + (lane >> 2)) * ps)) : 0;
+        wait_free();
         if (lane == 0) {   // scale copies are rounded up to 16 bytes per page segment
             uint32_t bytes = static_cast<uint32_t>(ntok) * 256u;
             for (int sgi = 0; sgi < nseg; ++sgi) {
@@ -115,7 +119,7 @@ struct Q8MmaPolicy {
             const int kind = c & 3, sgi = c >> 2;
             const int tb = max(t0, (first_page + sgi) * ps);
             const int te = min(t0 + ntok, (first_page + sgi + 1) * ps);
-            const int64_t row = row_index(p.addr, seq, head, tb);
+            const int64_t row = c == lane ? row0 : row_index(p.addr, seq, head, tb);
             const uint32_t rows = static_cast<uint32_t>(te - tb);
             if (kind == 0) bulk_g2s(stage + (tb - t0) * 128, kc + row * 128, rows * 128, bar);
             else if (kind == 1) bulk_g2s(stage + kOffV + (tb - t0) * 128, vc + row * 128, rows * 128, bar);

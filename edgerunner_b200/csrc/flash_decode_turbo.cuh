@@ -37,24 +37,28 @@ struct TurboStaging {
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
                                          const float2*, int) {}
+    template <class WAIT>
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
-                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/) {
+                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/, WAIT&& wait_free) {
         const int nb = p.norm_fp16 ? 2 : 4;
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
         const uint8_t* kn = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
         const uint8_t* vn = p.vn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
-        if (lane == 0)
-            mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * (kKW + kVW) * 4 + 2u * ((static_cast<uint32_t>(ntok) * nb + 15u) & ~15u));
-        __syncwarp();
         const int ps = p.addr.page_size;
         const int first_page = t0 / ps;
         const int nseg = (t0 + ntok - 1) / ps - first_page + 1;
+        // the lane's first copy: its page is looked up in the block table while the stage is still busy
+        const int64_t row0 = lane < 4 * nseg ? row_index(p.addr, seq, head, max(t0, (first_page + (lane >> 2)) * ps)) : 0;
+        wait_free();
+        if (lane == 0)
+            mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ntok) * (kKW + kVW) * 4 + 2u * ((static_cast<uint32_t>(ntok) * nb + 15u) & ~15u));
+        __syncwarp();
         for (int c = lane; c < 4 * nseg; c += 32) {
             const int kind = c & 3, sgi = c >> 2;
             const int tb = max(t0, (first_page + sgi) * ps);
             const int te = min(t0 + ntok, (first_page + sgi + 1) * ps);
-            const int64_t row = row_index(p.addr, seq, head, tb);
+            const int64_t row = c == lane ? row0 : row_index(p.addr, seq, head, tb);
             const uint32_t rows = static_cast<uint32_t>(te - tb);
             if (kind == 0) bulk_g2s(stage + (tb - t0) * kKW * 4, kc + row * (kKW * 4), rows * kKW * 4, bar);
             else if (kind == 1) bulk_g2s(stage + kKcBytes + (tb - t0) * kVW * 4, vc + row * (kVW * 4), rows * kVW * 4, bar);
