@@ -303,6 +303,7 @@ def build_cache(er, torch, w, lens, extra_tokens):
                            max_batch=B, layout=layout, **kw)
     if layout == er.Layout.paged:
         rng = np.random.Generator(np.random.PCG64(2))
+        # ER_BENCH_IDENTITY_PAGES=1: pages in order instead of the random permutation (separates DRAM locality from the gather)
         alloc = er.BlockTableAllocator(kw["num_pages"], w["page_size"], free_order=(np.arange(kw["num_pages"]) if os.environ.get("ER_BENCH_IDENTITY_PAGES") else rng.permutation(kw["num_pages"])))
         for b, n in enumerate(lens):
             cache.set_block_table(b, alloc.ensure(b, n + extra_tokens))
