@@ -98,6 +98,10 @@ __device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* m
         : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
 // Per-head RMS-norm factor rsqrt(sum(x^2) / 128 + eps) of a 128-float row, summed in the order head_rms_norm_kernel uses
 // (pair terms x[i]^2 + x[i+64]^2, xor butterfly 16..1 over each 32 pairs, one add).  All 32 lanes take part.
 __device__ __forceinline__ float head_rms_scale(const float* row, float eps, int lane) {

@@ -545,6 +545,14 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
                 const int start = kv_start(p, sg.pair, kv_len);
+                // The consumers read this item's query rows (and the new K/V row) only when they get here, several tiles
+                // later: pull the lines into L2 now so that the item switch does not wait on DRAM.
+                if (lane < GROUP * 4)
+                    prefetch_l2(reinterpret_cast<const uint8_t*>(p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim) + lane * 128);
+                if (POL::kFusedAppend && p.fused_append && lane >= 24) {
+                    const int64_t off = (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim * 4 + (lane & 3) * 128;
+                    prefetch_l2(reinterpret_cast<const uint8_t*>((lane & 4) ? p.v_new : p.k_new) + off);
+                }
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     const int nun = min(UPT, sg.u1 - tu);
                     const int t0 = tu * kUnitTokens;

@@ -67,6 +67,7 @@ class KVCache:
         cfg.norm_format, cfg.max_batch, cfg.layout = int(norm_format), max_batch, int(layout)
         cfg.page_size, cfg.num_pages = page_size, num_pages
         self._h = C.c_void_p()
+        self._destroy = lib().er_kv_destroy      # held by the object: close() may run while the interpreter shuts down
         check(lib().er_kv_create(C.byref(cfg), C.byref(self._h)))
         got = er_kv_config()
         check(lib().er_kv_get_config(self._h, C.byref(got)))
@@ -79,8 +80,8 @@ class KVCache:
 
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:
-            lib().er_kv_destroy(self._h)
-            self._h = C.c_void_p()
+            self._destroy(self._h)
+            self._h.value = None
 
     __del__ = close
 
