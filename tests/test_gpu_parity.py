@@ -1038,17 +1038,19 @@ def test_gqa_operator_other_head_sizes_and_groups(er, oracle, torch, Hq, Hkv, D,
     assert max_rel_err(got, want) < TOL
 
 
-@pytest.mark.parametrize("layout,page_size,T,window,B", [
-    ("head_major", 0, 48, 20, 2),      # window inside a larger ring: the range wraps with the ring
-    ("token_major", 0, 48, 20, 1),
-    ("paged", 16, 48, 37, 2),
-    ("head_major", 0, 40, 40, 1),      # Gemma4GPUKVCache's shape: ring capacity == slidingWindow
-    ("head_major", 0, 24, 100, 1),     # window wider than the ring: every slot
+@pytest.mark.parametrize("layout,page_size,T,window,B,Hq", [
+    ("head_major", 0, 48, 20, 2, 8),      # window inside a larger ring: the range wraps with the ring
+    ("token_major", 0, 48, 20, 1, 8),
+    ("paged", 16, 48, 37, 2, 8),
+    ("head_major", 0, 40, 40, 1, 8),      # Gemma4GPUKVCache's shape: ring capacity == slidingWindow
+    ("head_major", 0, 24, 100, 1, 8),     # window wider than the ring: every slot
+    ("paged", 16, 208, 190, 2, 16),       # 4 heads per kv head (tensor-core policy), tiles that cross the ring end
+    ("token_major", 0, 64, 33, 1, 32),    # 8 heads per kv head
 ])
-def test_sliding_window_decode(er, oracle, torch, layout, page_size, T, window, B):
+def test_sliding_window_decode(er, oracle, torch, layout, page_size, T, window, B, Hq):
     """er_step_params.sliding_window: each decode step attends to the newest min(window, rows held) rows
     (Gemma4GPUKVCache.attentionRange), fused step and split calls alike, before and after the ring wraps."""
-    D, Hq, Hkv, theta = 128, 8, 4, 1e4
+    D, Hkv, theta = 128, 4, 1e4
     rng = rng_for(950 + T + window)
     lay = getattr(er.Layout, layout)
     kw = {}
