@@ -94,6 +94,9 @@ def parse_args():
                     help="N > 1: 'sequence' = one replica of the workload per GPU (weak scaling, no collective); 'heads' = the kv "
                          "heads of the one workload split over the GPUs, outputs exchanged by an NCCL all-gather per step (strong "
                          "scaling; device leg only)")
+    ap.add_argument("--cta-timeline", action="store_true",
+                    help="with --only-device-leg: one extra step with the kernel's per-CTA phase stamps (er_kv_set_trace), reported "
+                         "as cta_timeline_us = [min, median, max] over the CTAs, microseconds after the first CTA started")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
     return ap.parse_args()
 
@@ -427,6 +430,19 @@ def run_ours(args, w, lens):
     hbm_gbs = bytes_total / (ms_total * 1e-3) / 1e9       # per GPU
 
     if args.only_device_leg:
+        timeline = None
+        if args.cta_timeline and rank == 0:
+            n_ctas = cache.set_trace(None, 0)
+            stamps = torch.zeros(n_ctas, 8, dtype=torch.int64, device="cuda")
+            cache.set_trace(stamps, n_ctas)
+            set_start()
+            cache.decode_step(qs[0], ks[0], vs[0], out, H, sp, stream=stream)
+            torch.cuda.synchronize()
+            cache.set_trace(None, 0)
+            t = stamps.cpu().numpy().astype(np.float64)
+            t = (t - t[:, 0].min()) / 1e3
+            names = ["cta_start", "work_list_built", "first_tile_landed", "streaming_done", "before_exit_sync", "after_exit_sync", "cta_end"]
+            timeline = {nm: [round(float(f(t[:, i])), 2) for f in (np.min, np.median, np.max)] for i, nm in enumerate(names)}
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
                               "ms_per_step": ms_total / K, "hbm_gbs_per_gpu": round(hbm_gbs, 1), "gpu_launches": int(launches),
@@ -434,7 +450,7 @@ def run_ours(args, w, lens):
                               "config": {"workload": w["name"],
                                          "sharding": ("kv heads split over the GPUs, NCCL all-gather of the outputs every step" if shard_heads
                                                       else "by sequence, one replica per GPU, no collective") if world > 1 else "single GPU"},
-                              "note": "device leg only"}))
+                              "note": "device leg only", **({"cta_timeline_us": timeline} if timeline else {})}))
         if world > 1:
             dist.destroy_process_group()
         return

@@ -492,14 +492,17 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
         mbar_init_fence();
     }
     POL::init_extra(extra, tid);
-    // ---- unit prefix over (layer, sequence) pairs, built by warp 0 ----
+    // ---- unit prefix over (layer, sequence) pairs: all threads fetch the lengths (one round of global reads), warp 0
+    // turns the unit counts into an exclusive scan in place ----
+    for (int j = tid; j < num_pairs; j += blockDim.x) prefix[j] = (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+    __syncthreads();
     if (warp == 0) {
         const int per_lane = (num_pairs + 31) / 32;
         const int begin = lane * per_lane;
         int sum = 0;
         for (int k = 0; k < per_lane; ++k) {
             const int j = begin + k;
-            if (j < num_pairs) sum += (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+            if (j < num_pairs) sum += prefix[j];
         }
         int incl = sum;
 #pragma unroll
@@ -510,9 +513,10 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
         int run = incl - sum;
         for (int k = 0; k < per_lane; ++k) {
             const int j = begin + k;
-            if (j < num_pairs) {
+            if (j < num_pairs) {   // a lane rewrites only its own entries
+                const int units = prefix[j];
                 prefix[j] = run;
-                run += (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+                run += units;
             }
         }
         if (lane == 31) prefix[num_pairs] = incl;
@@ -570,17 +574,23 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
             // ================= consumer warps =================
             float* prob = prob_all + warp * GROUP * kUnitTokens;
             const int wgroup = warp / UPT, wunit = warp % UPT;   // tiles k with k % NG == wgroup are this warp's
-            int k = 0, item_visit = 0;
+            int k = 0, cs_buf = 0, cs_pos = -1;
             int64_t cur = range_begin;
             while (cur < range_end) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
                 const int q_pos = (p.lengths == nullptr) ? p.fixed_q_pos : p.lengths[layer * p.batch + seq] + p.pending - 1;
-                float2* cs = cos_sin + (item_visit & 1) * kHalfDim;
-                ++item_visit;
-                if (p.apply_rope && tid < kHalfDim)
-                    cs[tid] = rope_cos_sin(static_cast<uint32_t>(q_pos), p.inv_freq.f[tid], p.rope_scaling);
+                // The (cos, sin) table depends on the position only: the kv heads of a sequence and all layers of a sequence
+                // share it, so it is rebuilt (double-precision sincos) only when the position changes.  Two buffers: a
+                // rebuild never touches the one the previous visit's stragglers may still be reading.
+                if (p.apply_rope && q_pos != cs_pos) {
+                    cs_buf ^= 1;
+                    cs_pos = q_pos;
+                    if (tid < kHalfDim)
+                        cos_sin[cs_buf * kHalfDim + tid] = rope_cos_sin(static_cast<uint32_t>(q_pos), p.inv_freq.f[tid], p.rope_scaling);
+                }
+                float2* cs = cos_sin + cs_buf * kHalfDim;
                 consumer_sync<NW * 32>();
 
                 typename POL::State st;
