@@ -1113,3 +1113,43 @@ def test_sliding_window_unsupported_combinations(er, torch):
     cache.write_rows(0, 0, 0, 4, z(4, Hkv, D), z(4, Hkv, D), er.step_params())
     with pytest.raises(er.EdgeRunnerCUDAError):
         cache.attention_prefill(0, 0, z(4, Hq, D), z(4, Hq, D), Hq, 4, sp)
+
+
+# ------------------------------------------------------------------ seeded random shapes
+
+def test_seeded_random_decode_shapes(er, oracle, torch):
+    """40 decode configurations drawn from a fixed seed: storage format x layout x page size x heads per kv head x batch x
+    context x steps x ragged lengths, each checked like the hand-written cases (cache bytes bit-exact, attention within bound)."""
+    rng = rng_for(31337)
+    for _ in range(40):
+        kind = str(rng.choice(["dense", "q8", "turbo"]))
+        Hkv, group = int(rng.choice([1, 2, 4, 8])), int(rng.choice([1, 2, 4, 8]))
+        layout = str(rng.choice(["head_major", "token_major", "paged"])) if kind == "dense" else str(rng.choice(["head_major", "paged"]))
+        ps = int(rng.choice([16, 32, 64])) if layout == "paged" else 0
+        L, B, ctx, steps = int(rng.integers(1, 4)), int(rng.integers(1, 5)), int(rng.integers(1, 1200)), int(rng.integers(1, 4))
+        ragged, seed = bool(rng.integers(0, 2)), int(rng.integers(0, 1 << 30))
+        common = dict(L=L, B=B, Hq=Hkv * group, Hkv=Hkv, ctx=ctx, steps=steps, seed=seed, page_size=ps, ragged=ragged)
+        lay = getattr(er.Layout, layout)
+        if kind == "dense":
+            _run_dense_config(er, oracle, torch, lay, **common)
+        elif kind == "q8":
+            _run_q8_config(er, oracle, torch, layout=lay, **common)
+        else:
+            _run_turbo_config(er, oracle, torch, kbits=int(rng.choice([3, 4])), vbits=int(rng.choice([3, 4])),
+                              norm_format=er.NormFormat.float16 if rng.integers(0, 2) else er.NormFormat.float32, layout=lay, **common)
+
+
+def test_seeded_random_windowed_operator_shapes(er, oracle, torch):
+    """60 ring ranges drawn from a fixed seed over head sizes 64 / 128 / 256 / 512 and 1 / 2 / 4 / 8 heads per kv head."""
+    rng = rng_for(31338)
+    for _ in range(60):
+        Hkv, group = int(rng.choice([1, 2, 4, 8])), int(rng.choice([1, 2, 4, 8]))
+        cap = int(rng.integers(1, 3000))
+        cnt, st, D = int(rng.integers(0, cap + 1)), int(rng.integers(0, cap)), int(rng.choice([128, 128, 64, 256, 512]))
+        q, k, v = normal_f16(rng, (Hkv * group, D)), normal_f16(rng, (cap, Hkv, D)), normal_f16(rng, (cap, Hkv, D))
+        got = er.Gemma4DecodeKernels().run_decode_gqa_f16kv_windowed(q, k, v, Hkv * group, Hkv, D, st, cnt, cap)
+        want = oracle.gqa_f16kv_windowed(q, k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16), st, cnt)
+        if cnt == 0:
+            assert not got.any()
+        else:
+            assert max_rel_err(got, want) < TOL, (Hkv, group, D, cap, st, cnt)
