@@ -123,7 +123,8 @@ int launch_prefill(int group, const PrefillParams& pp, uint64_t outer_extent, in
         const char* e = std::getenv("ER_PREFILL_KERNEL");
         return e != nullptr && std::strcmp(e, "mma_sync") == 0;
     }();
-    if (!force_legacy && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
+    // windowed chunks (short key ranges by construction) stay on the mma.sync kernel, which carries the window mask
+    if (!force_legacy && pp.window <= 0 && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
         const int rc = launch_prefill_umma(group, pp, outer_extent, num_kv_heads, status, stream);
         if (rc != kNotBuilt) return rc;
     }
@@ -1105,7 +1106,8 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
     if (rc != ER_OK) return rc;
-    if (s.sliding_window > 0) return fail(ER_ERR_UNSUPPORTED, "sliding_window applies to decode calls only");
+    if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
+        return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
                          static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
@@ -1192,6 +1194,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
     pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);
     pp.causal = 1;
+    pp.window = static_cast<int>(std::min<uint32_t>(s.sliding_window, 0x7fffffffu));
     pp.num_q_heads = static_cast<int>(num_heads);
     pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;

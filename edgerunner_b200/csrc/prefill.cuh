@@ -39,6 +39,8 @@ struct PrefillParams {
     int q_offset_from_end;   // 1: q_offset = kv_len - seq_len (the query rows are the newest rows of the cache)
     int q_offset;            // absolute position of query row 0
     int causal;
+    int window;              // > 0: query row at position P also ignores keys before P - window + 1 (sliding-window layers;
+                             // Gemma4GPUKVCache.attentionRange); the mma.sync kernel only
     int num_q_heads;
     float scale_log2;
     float rope_scaling;
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
     const int q_last = min(q0 + kQRowsPerCta, p.seq_len) - 1;
     const int kv_hi = p.causal ? min(pp.kv_len, q_last + pp.q_offset + 1) : pp.kv_len;
     const int num_tiles = (kv_hi + kPfTileTokens - 1) / kPfTileTokens;
+    // a sliding window hides every tile that ends before the first query row's window begins
+    const int tile_lo = p.window > 0 ? max(0, q0 + pp.q_offset - p.window + 1) / kPfTileTokens : 0;
 
     auto load_tile = [&](int tile, int stage) {
         const int t0 = tile * kPfTileTokens;
@@ -172,9 +176,9 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
         cp_async_commit();
     };
 
-    if (num_tiles > 0) load_tile(0, 0);
-    for (int tile = 0; tile < num_tiles; ++tile) {
-        const int stage = tile & 1;
+    if (num_tiles > tile_lo) load_tile(tile_lo, 0);
+    for (int tile = tile_lo; tile < num_tiles; ++tile) {
+        const int stage = (tile - tile_lo) & 1;
         if (tile + 1 < num_tiles) { load_tile(tile + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
         const uint32_t ks = smem_base + stage * kStageTiles * kPfTileBytes, vs = ks + kPfTileBytes, kls = vs + kPfTileBytes;
@@ -211,7 +215,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
                 const int t = t0 + 8 * j + 2 * qlane + (c & 1);
                 const int hrow = c >> 1;
                 const int qi = hrow ? qi_hi : qi_lo;
-                const bool vis = t < pp.kv_len && (!p.causal || t <= qi + pp.q_offset);
+                const bool vis = t < pp.kv_len && (!p.causal || t <= qi + pp.q_offset) &&
+                                 (p.window <= 0 || t > qi + pp.q_offset - p.window);
                 s[j][c] = vis ? s[j][c] : -INFINITY;
                 mx[hrow] = fmaxf(mx[hrow], s[j][c]);
             }

@@ -1109,10 +1109,48 @@ def test_sliding_window_unsupported_combinations(er, torch):
         cache = er.KVCache(32, 1, Hkv, D, prec, **kw)
         with pytest.raises(er.EdgeRunnerCUDAError):
             cache.decode_step(z(1, 1, Hq, D), z(1, 1, Hkv, D), z(1, 1, Hkv, D), z(1, 1, Hq, D), Hq, sp)
-    cache = er.KVCache(32, 1, Hkv, D, er.Precision.float16)
-    cache.write_rows(0, 0, 0, 4, z(4, Hkv, D), z(4, Hkv, D), er.step_params())
-    with pytest.raises(er.EdgeRunnerCUDAError):
-        cache.attention_prefill(0, 0, z(4, Hq, D), z(4, Hq, D), Hq, 4, sp)
+        cache.write_rows(0, 0, 0, 4, z(4, Hkv, D), z(4, Hkv, D), er.step_params())
+        with pytest.raises(er.EdgeRunnerCUDAError):
+            cache.attention_prefill(0, 0, z(4, Hq, D), z(4, Hq, D), Hq, 4, sp)
+
+
+@pytest.mark.parametrize("layout,page_size,Hq,Hkv,ctx,S,window", [
+    ("head_major", 0, 8, 4, 300, 200, 64),       # window much shorter than the context: leading tiles are skipped
+    ("paged", 32, 16, 4, 50, 130, 100),          # window longer than the context of the first rows
+    ("token_major", 0, 8, 8, 0, 77, 1),          # every row sees only itself
+    ("head_major", 0, 32, 4, 700, 40, 5000),     # window wider than everything: plain causal attention
+])
+def test_sliding_window_prefill(er, oracle, torch, layout, page_size, Hq, Hkv, ctx, S, window):
+    """er_kv_attention_prefill with er_step_params.sliding_window: query row at position P sees keys
+    max(0, P - window + 1) .. P (Gemma4GPUKVCache.attentionRange applied per row of the chunk)."""
+    D, theta = 128, 1.0e4
+    rng = rng_for(990 + S + window)
+    T = (ctx + S + 15) // 16 * 16
+    lay = getattr(er.Layout, layout)
+    kw = {}
+    if lay == er.Layout.paged:
+        n_pages = (T + page_size - 1) // page_size + 2
+        kw = dict(page_size=page_size, num_pages=n_pages)
+    cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16, layout=lay, **kw)
+    if lay == er.Layout.paged:
+        alloc = er.BlockTableAllocator(n_pages, page_size, free_order=rng.permutation(n_pages))
+        cache.set_block_table(0, alloc.ensure(0, ctx + S))
+    sp = er.step_params(rope_theta=theta, sliding_window=window)
+    K, V = normal_f16(rng, (ctx + S, Hkv, D)), normal_f16(rng, (ctx + S, Hkv, D))
+    cache.write_rows(0, 0, 0, ctx + S, dev(torch, K), dev(torch, V), sp)
+    q = normal_f16(rng, (S, Hq, D))
+    out = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(0, 0, dev(torch, q), out, Hq, S, sp)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    kc = np.concatenate([oracle.rope_neox_to_f16(K[t:t + 1], t, theta) for t in range(ctx + S)])
+    vc = oracle.f32_to_f16_bits(V)
+    q_rot = oracle.rope_neox(q, ctx, theta)
+    for r in range(S):
+        pos = ctx + r
+        count = min(window, pos + 1)
+        want = oracle.gqa_f16kv_windowed(q_rot[r], kc, vc, pos + 1 - count, count)
+        assert max_rel_err(got[r], want) < TOL, r
 
 
 # ------------------------------------------------------------------ seeded random shapes
