@@ -494,32 +494,37 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     POL::init_extra(extra, tid);
     // ---- unit prefix over (layer, sequence) pairs: all threads fetch the lengths (one round of global reads), warp 0
     // turns the unit counts into an exclusive scan in place ----
-    for (int j = tid; j < num_pairs; j += blockDim.x) prefix[j] = (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
-    __syncthreads();
-    if (warp == 0) {
-        const int per_lane = (num_pairs + 31) / 32;
-        const int begin = lane * per_lane;
-        int sum = 0;
-        for (int k = 0; k < per_lane; ++k) {
-            const int j = begin + k;
-            if (j < num_pairs) sum += prefix[j];
-        }
-        int incl = sum;
+    {
+        int len[8];   // eight independent reads in flight per thread, then the (never needed at >= 256 threads) remainder
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
+        for (int i = 0; i < 8; ++i) {
+            const int j = tid + i * static_cast<int>(blockDim.x);
+            len[i] = j < num_pairs ? kv_length(p, j) : 0;
         }
-        int run = incl - sum;
-        for (int k = 0; k < per_lane; ++k) {
-            const int j = begin + k;
-            if (j < num_pairs) {   // a lane rewrites only its own entries
-                const int units = prefix[j];
-                prefix[j] = run;
-                run += units;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int j = tid + i * static_cast<int>(blockDim.x);
+            if (j < num_pairs) prefix[j] = (len[i] + kUnitTokens - 1) / kUnitTokens;
+        }
+        for (int j = tid + 8 * static_cast<int>(blockDim.x); j < num_pairs; j += blockDim.x)
+            prefix[j] = (kv_length(p, j) + kUnitTokens - 1) / kUnitTokens;
+    }
+    __syncthreads();
+    if (warp == 0) {   // 32 consecutive entries per pass (conflict-free), running total carried in registers
+        int carry = 0;
+        for (int base = 0; base < num_pairs; base += 32) {
+            const int j = base + lane;
+            const int units = j < num_pairs ? prefix[j] : 0;
+            int incl = units;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
             }
+            if (j < num_pairs) prefix[j] = carry + incl - units;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
         }
-        if (lane == 31) prefix[num_pairs] = incl;
+        if (lane == 0) prefix[num_pairs] = carry;
     }
     __syncthreads();
     if (tid == 0) stamp(1);
