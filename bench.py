@@ -207,7 +207,9 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
     workload: `layers_sampled` of the model's layers per step, throughput scaled to the full layer count."""
     from oracle import er_oracle as oracle
     oracle.build()
-    threads = oracle.max_threads()
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; only one rank runs this leg, so it takes the cores the process may
+    # use (the oracle passes the count in a num_threads clause, which overrides the environment)
+    threads = max(oracle.max_threads(), len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
     rng = np.random.Generator(np.random.PCG64(7))
     turbo = w["precision"] == "turboquant"
