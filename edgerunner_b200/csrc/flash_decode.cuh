@@ -480,9 +480,10 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     auto stamp = [&](int slot) {   // diagnostics: per-CTA phase times
         if (p.trace != nullptr) p.trace[blockIdx.x * 8 + slot] = global_timer_ns();
     };
-    if (tid == 0) stamp(0);
     const int num_pairs = p.num_layers * p.batch;
 
+    // let the next kernel of the stream be placed as this one's CTAs leave (it waits below before reading anything)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         flags[0] = 0; flags[1] = 0; flags[2] = 0;
         for (int s = 0; s < kStages; ++s) {
@@ -492,6 +493,10 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
         mbar_init_fence();
     }
     POL::init_extra(extra, tid);
+    // everything above touches shared memory only; global memory (lengths, cache rows, scratch, counters, trace) belongs to
+    // the previous kernel of the stream until it has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) stamp(0);
     // ---- unit prefix over (layer, sequence) pairs: all threads fetch the lengths (one round of global reads), warp 0
     // turns the unit counts into an exclusive scan in place ----
     {

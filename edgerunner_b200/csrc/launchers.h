@@ -57,8 +57,20 @@ inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t st
         if (e != cudaSuccess) return static_cast<int>(e);
         configured_device = device;
     }
-    flash_decode_kernel<POL><<<grid, (POL::kUnitsPerTile * POL::kWarpGroups + 1) * 32, kSmem, stream>>>(p);
-    return static_cast<int>(cudaGetLastError());
+    // Programmatic dependent launch: the CTAs of this launch may be placed while the previous kernel of the stream drains
+    // (one CTA per SM, so each starts when that SM's previous CTA has left); the kernel waits for the previous grid
+    // (griddepcontrol.wait) before it touches global memory, so only launch latency and the CTA prologue overlap.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3((POL::kUnitsPerTile * POL::kWarpGroups + 1) * 32);
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, flash_decode_kernel<POL>, p));
 }
 
 }  // namespace er
