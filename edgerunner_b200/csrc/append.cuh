@@ -201,6 +201,9 @@ __global__ void rope_neox_kernel(const float* in, OUT* out, uint32_t seq_len, ui
 // device staging area with plain 16-byte loads -- one launch instead of three copy-engine transfers.
 __global__ void gather_host_inputs_kernel(const float4* q, const float4* k, const float4* v, float4* dq, float4* dk,
                                           float4* dv, int nq4, int nkv4) {
+    // the decode kernel that follows is a programmatic dependent launch: let its CTAs be placed and run their
+    // shared-memory prologue now (it waits for this grid before it reads the gathered rows)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int total = nq4 + 2 * nkv4;
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
         if (e < nq4) dq[e] = q[e];
