@@ -64,6 +64,8 @@ struct Q8AppendParams {
 // [NeoX RoPE on K ->] quantise -> cache slot.  One warp per (source row, kv head, K | V) job.  Replaces rope_neox_f32 +
 // 2 x quantize_q8_0_rows of the decode pass on a q8_0 layer.
 __global__ void __launch_bounds__(256) q8_append_kernel(const __grid_constant__ Q8AppendParams qp) {
+    // the decode kernel behind this one is a programmatic dependent launch: its CTAs may be placed and build their tables now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const AppendParams& p = qp.base;
     const int lane = threadIdx.x & 31;
     const int hkv = p.addr.num_kv_heads;

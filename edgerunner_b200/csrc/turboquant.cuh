@@ -126,6 +126,8 @@ __global__ void __launch_bounds__(kQuantWarps * 32) tq_append_kernel(const __gri
                                                                     int jobs_per_warp) {
     __shared__ float tile_all[kQuantWarps][kQuantRowsPerWarp * kQuantRowStride];
     __shared__ __align__(16) uint32_t pack_all[kQuantWarps][kQuantRowsPerWarp * 16];
+    // the decode kernel behind this one is a programmatic dependent launch: its CTAs may be placed and build their tables now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const AppendParams& p = tp.base;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* tile = tile_all[warp];
