@@ -33,7 +33,7 @@ class ERRoPEParams(C.Structure):
 class er_kv_config(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("max_seq_len", "num_layers", "num_kv_heads", "head_dim", "precision",
                                           "key_type", "value_type", "norm_format", "max_batch", "layout",
-                                          "page_size", "num_pages")] + [("reserved", C.c_uint32 * 4)]
+                                          "page_size", "num_pages", "prefill_kernel")] + [("reserved", C.c_uint32 * 3)]
 
 
 class er_kv_buffers(C.Structure):
@@ -85,6 +85,7 @@ SYMBOLS = {
     "er_rope_neox_f32_to_f16": (_i32, [_vp, _vp, C.POINTER(ERRoPEParams), _vp]),
     "er_quantize_q8_0_rows": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "er_turboquant_quantize_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "er_gqa_attention_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv_windowed": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERWindowedGQAParams), _vp]),
@@ -97,6 +98,10 @@ SYMBOLS = {
     "er_kv_write_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _stp, _vp]),
     "er_kernel_launch_count": (C.c_uint64, []),
     "er_kv_device_status": (_i32, [_vp]),
+    "er_kv_clear_device_status": (_i32, [_vp]),
+    "er_kv_debug_wait_probe": (_i32, [_vp, _u32, C.c_int]),
+    "er_workspace_status": (_i32, []),
+    "er_gqa_attention_f16kv_static_status": (_i32, []),
     "er_kv_set_trace": (_i32, [_vp, _vp, _u32]),
     "er_host_alloc": (_i32, [C.POINTER(_vp), _sz]),
     "er_host_free": (_i32, [_vp]),

@@ -130,7 +130,9 @@ __global__ void __launch_bounds__(128) append_rope_dense_kernel(const __grid_con
             }
         }
         uint8_t* base = is_v ? p.v_base + layer * p.v_layer_stride_bytes : p.k_base + layer * p.k_layer_stride_bytes;
-        uint8_t* dst = base + row_index(p.addr, seq, h, slot) * kRowBytes;
+        const int64_t ridx = row_index_for_write(p.addr, seq, h, slot);
+        if (ridx < 0) continue;   // no page behind the slot: dropped, the status word says so
+        uint8_t* dst = base + ridx * kRowBytes;
         store8<ELEM>(dst + 8 * i * sizeof(ELEM), xa);
         store8<ELEM>(dst + (64 + 8 * i) * sizeof(ELEM), xb);
     }
@@ -144,7 +146,8 @@ __global__ void scatter_row_kernel(const uint8_t* src, uint8_t* base, KVAddressi
     const int total = addr.num_kv_heads * row_bytes;
     for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < total; b += gridDim.x * blockDim.x) {
         const int h = b / row_bytes, off = b % row_bytes;
-        base[row_index(addr, seq, h, slot) * row_bytes + off] = src[b];
+        const int64_t ridx = row_index_for_write(addr, seq, h, slot);
+        if (ridx >= 0) base[ridx * row_bytes + off] = src[b];
     }
 }
 

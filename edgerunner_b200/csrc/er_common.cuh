@@ -16,6 +16,8 @@ constexpr int kMaxPairs = 2048;        // (layer, sequence) pairs one launch can
 
 // Device status codes mirrored to the host as ER_ERR_DEVICE_TIMEOUT.
 constexpr int kStatusTimeout = -12;
+// A row of a paged cache fell into a block-table entry that holds no page (mirrored as ER_ERR_OUT_OF_PAGES).
+constexpr int kStatusOutOfPages = -10;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -60,7 +62,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait on an mbarrier phase.  `abort_flag` lives in shared memory: once any thread of the CTA has
 // given up, every later wait returns at once, so the CTA still walks its whole control flow (all named
 // barriers and arrivals are reached) and exits; the host sees the status word, never a hung kernel.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+// `limit_ns` is the patience of this wait (2 s unless the launch carries a shorter one for a test of this very path).
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          uint64_t limit_ns = 2000000000ull) {
     if (*abort_flag) return;
     if (mbar_try_wait(bar, parity)) return;
     const uint64_t start = global_timer_ns();
@@ -68,7 +72,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3FFu) == 0u) {
             if (*abort_flag) return;
-            if (global_timer_ns() - start > 2000000000ull) {   // 2 s
+            if (global_timer_ns() - start > limit_ns) {
                 *abort_flag = 1;
                 atomicExch(status, kStatusTimeout);
                 return;
@@ -187,7 +191,8 @@ struct KVAddressing {
     int max_seq_len;        // ring length
     int page_size;          // tokens per page (== padded ring length for HEAD_MAJOR)
     int pages_per_seq;      // block-table stride; 0 = identity (page id = sequence index)
-    const int32_t* block_table;
+    const int32_t* block_table;   // [seq][pages_per_seq] page ids, -1 = no page assigned
+    int* status;            // device status word of the owning cache (paged layout only), else nullptr
 };
 
 __device__ __forceinline__ int64_t row_index(const KVAddressing& a, int seq, int head, int slot) {
@@ -201,8 +206,23 @@ __device__ __forceinline__ int64_t row_index(const KVAddressing& a, int seq, int
     } else {
         page = __ldg(a.block_table + static_cast<int64_t>(seq) * a.pages_per_seq + slot / a.page_size);
         in_page = slot % a.page_size;
+        if (page < 0) {   // no page behind this slot: readers get page 0 (in bounds, flagged), never a wild address
+            if (a.status != nullptr) atomicExch(a.status, kStatusOutOfPages);
+            page = 0;
+        }
     }
     return (static_cast<int64_t>(page) * a.num_kv_heads + head) * a.page_size + in_page;
+}
+
+// Row index for a WRITE: -1 (and the status word set) when the slot's block-table entry holds no page, so that a row
+// beyond the pages a sequence was given is dropped instead of landing in another sequence's page.
+__device__ __forceinline__ int64_t row_index_for_write(const KVAddressing& a, int seq, int head, int slot) {
+    if (!a.token_major && a.pages_per_seq != 0 &&
+        __ldg(a.block_table + static_cast<int64_t>(seq) * a.pages_per_seq + slot / a.page_size) < 0) {
+        if (a.status != nullptr) atomicExch(a.status, kStatusOutOfPages);
+        return -1;
+    }
+    return row_index(a, seq, head, slot);
 }
 
 }  // namespace er

@@ -78,8 +78,9 @@ struct Workspace {
     size_t counter_ints = 0;
 };
 
+constexpr int kMaxDevices = 64;
 std::mutex g_ws_mu;
-std::vector<Workspace> g_ws;
+Workspace g_ws[kMaxDevices];   // one per device ordinal; never moves, so returned pointers stay valid
 
 constexpr size_t kScratchFloatsPerCta = 2 * 8 * 130;   // two slots, up to 8 q heads per kv head
 
@@ -96,14 +97,27 @@ int32_t make_workspace(Workspace& w, int device, size_t item_counters) {
 int32_t get_workspace(Workspace** out) {
     int device = 0;
     ER_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(ER_ERR_UNSUPPORTED, "device ordinal %d beyond %d", device, kMaxDevices - 1);
     std::lock_guard<std::mutex> lock(g_ws_mu);
-    for (auto& w : g_ws)
-        if (w.device == device) { *out = &w; return ER_OK; }
-    g_ws.reserve(16);
-    g_ws.emplace_back();
-    int32_t rc = make_workspace(g_ws.back(), device, static_cast<size_t>(kMaxPairs) * 16);
-    if (rc != ER_OK) { g_ws.pop_back(); return rc; }
-    *out = &g_ws.back();
+    Workspace& w = g_ws[device];
+    if (w.device != device) {
+        Workspace fresh;
+        int32_t rc = make_workspace(fresh, device, static_cast<size_t>(kMaxPairs) * 16);
+        if (rc != ER_OK) {
+            cudaFree(fresh.scratch); cudaFree(fresh.counters); cudaGetLastError();
+            return rc;
+        }
+        w = fresh;
+    }
+    *out = &w;
+    return ER_OK;
+}
+
+// The raw-buffer operators read q with 16-byte loads and copy K / V rows with bulk copies that need 16-byte global
+// addresses: a misaligned sub-buffer is refused here instead of faulting on the device.
+int32_t check_raw_pointers(const void* q, const void* k, const void* v, const void* out) {
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return fail(ER_ERR_INVALID_ARGUMENT, "q, k, v and out must be 16-byte aligned device addresses");
     return ER_OK;
 }
 
@@ -117,12 +131,9 @@ int32_t decode_status(int rc, int group, int kbits, int vbits) {
 }
 
 // Chunked prefill: the tcgen05 kernel when the chunk fills at least one 128-row CTA tile and the layout is covered, else
-// the mma.sync kernel.  ER_PREFILL_KERNEL=mma_sync in the environment forces the latter (A/B measurements).
-int launch_prefill(int group, const PrefillParams& pp, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream) {
-    static const bool force_legacy = [] {
-        const char* e = std::getenv("ER_PREFILL_KERNEL");
-        return e != nullptr && std::strcmp(e, "mma_sync") == 0;
-    }();
+// the mma.sync kernel; force_legacy (er_kv_config.prefill_kernel == ER_PREFILL_KERNEL_MMA_SYNC) always takes the latter.
+int launch_prefill(int group, const PrefillParams& pp, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream,
+                   bool force_legacy = false) {
     // windowed chunks (short key ranges by construction) stay on the mma.sync kernel, which carries the window mask
     if (!force_legacy && pp.window <= 0 && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
         const int rc = launch_prefill_umma(group, pp, outer_extent, num_kv_heads, status, stream);
@@ -177,6 +188,9 @@ struct er_kv {
     size_t head_norm_floats[2] = {0, 0};
     float cached_theta = 0.f;
     InvFreqTable inv_freq{};
+    uint32_t probe_wait_limit_us = 0;        // er_kv_debug_wait_probe: patience of the next decode launches' waits
+    int probe_withhold_tiles = 0;
+    int* h_status = nullptr;                 // pinned host word: er_kv_decode_step_host copies the device status here
     unsigned long long* d_trace = nullptr;   // caller-owned diagnostics buffer (er_kv_set_trace)
     uint32_t trace_ctas = 0;
     std::mutex mu;
@@ -189,6 +203,7 @@ struct er_kv {
         a.page_size = page_tokens;
         a.pages_per_seq = pages_per_seq;
         a.block_table = d_block_table;
+        a.status = pages_per_seq > 0 ? d_counters + 1 : nullptr;
         return a;
     }
     const InvFreqTable& freq(float theta) {
@@ -230,6 +245,33 @@ int32_t push_lengths(er_kv* kv) {
 int32_t check_layers(const er_kv* kv, uint32_t b, uint32_t e) {
     if (b >= e || e > kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer range [%u, %u) of %u", b, e, kv->cfg.num_layers);
     return ER_OK;
+}
+
+// Every launch of a cache's kernels must go to the GPU that holds its slabs: with another device current the launch
+// would carry foreign pointers (a fault, or peer loads where peer access is on).
+int32_t check_device(const er_kv* kv) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return fail(ER_ERR_CUDA, "cudaGetDevice"); }
+    if (device != kv->device)
+        return fail(ER_ERR_INVALID_ARGUMENT, "cache lives on device %d but device %d is current", kv->device, device);
+    return ER_OK;
+}
+
+// Paged layout: rows [0, end_row) of `seq` must lie in pages the block table has been given (host copy; kv->mu held).
+int32_t check_page_coverage(const er_kv* kv, uint32_t seq, uint64_t end_row) {
+    if (kv->pages_per_seq == 0) return ER_OK;
+    const uint64_t need = std::min<uint64_t>(end_row, kv->cfg.max_seq_len);
+    const uint64_t have = static_cast<uint64_t>(kv->h_block_count[seq]) * static_cast<uint64_t>(kv->page_tokens);
+    if (need > have)
+        return fail(ER_ERR_OUT_OF_PAGES, "sequence %u needs pages for %llu rows but its block table covers %llu", seq,
+                    static_cast<unsigned long long>(need), static_cast<unsigned long long>(have));
+    return ER_OK;
+}
+
+int32_t device_status_to_code(int status) {
+    if (status == kStatusTimeout) return fail(ER_ERR_DEVICE_TIMEOUT, "a bounded wait inside a kernel gave up");
+    if (status == kStatusOutOfPages) return fail(ER_ERR_OUT_OF_PAGES, "a row fell into a block-table entry without a page (the row was dropped)");
+    return status == 0 ? ER_OK : fail(ER_ERR_CUDA, "device status word %d", status);
 }
 
 bool is_dense(const er_kv* kv) { return kv->cfg.precision == ER_KV_FLOAT32 || kv->cfg.precision == ER_KV_FLOAT16; }
@@ -363,6 +405,7 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
             return fail(ER_ERR_UNSUPPORTED_STORAGE, "precision %u is outside this backend's scope", c->precision);
         default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
     }
+    if (c->prefill_kernel > ER_PREFILL_KERNEL_MMA_SYNC) return fail(ER_ERR_INVALID_ARGUMENT, "unknown prefill_kernel %u", c->prefill_kernel);
     if (er_device_count() <= 0) return fail(ER_ERR_CUDA, "no CUDA device: this backend has no CPU fallback");
     er_kv* kv = new er_kv();
     kv->cfg = *c;
@@ -433,10 +476,10 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         cudaMemset(kv->d_lengths, 0, kv->h_lengths.size() * sizeof(int32_t)) != cudaSuccess)
         return bail(fail(ER_ERR_ALLOCATION_FAILED, "length table"));
     if (kv->pages_per_seq > 0) {
-        kv->h_block_table.assign(static_cast<size_t>(B) * kv->pages_per_seq, 0);
+        kv->h_block_table.assign(static_cast<size_t>(B) * kv->pages_per_seq, -1);   // -1 = no page assigned
         kv->h_block_count.assign(B, 0);
         if (cudaMalloc(&kv->d_block_table, kv->h_block_table.size() * sizeof(int32_t)) != cudaSuccess ||
-            cudaMemset(kv->d_block_table, 0, kv->h_block_table.size() * sizeof(int32_t)) != cudaSuccess)
+            cudaMemset(kv->d_block_table, 0xFF, kv->h_block_table.size() * sizeof(int32_t)) != cudaSuccess)
             return bail(fail(ER_ERR_ALLOCATION_FAILED, "block table"));
     }
     const size_t counters = 16 + static_cast<size_t>(c->num_layers) * B * c->num_kv_heads;
@@ -444,6 +487,9 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         cudaMalloc(&kv->d_counters, sizeof(int) * counters) != cudaSuccess ||
         cudaMemset(kv->d_counters, 0, sizeof(int) * counters) != cudaSuccess)
         return bail(fail(ER_ERR_ALLOCATION_FAILED, "scratch"));
+    if (cudaHostAlloc(reinterpret_cast<void**>(&kv->h_status), sizeof(int), cudaHostAllocDefault) != cudaSuccess)
+        return bail(fail(ER_ERR_ALLOCATION_FAILED, "pinned status word"));
+    *kv->h_status = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cache initialisation"));
     *out = kv;
     return ER_OK;
@@ -455,6 +501,7 @@ void er_kv_destroy(er_kv* kv) {
     cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
     cudaFree(kv->d_head_norm[0]); cudaFree(kv->d_head_norm[1]);
     cudaFree(kv->d_stage);
+    if (kv->h_status) cudaFreeHost(kv->h_status);
     cudaGetLastError();
     delete kv;
 }
@@ -541,7 +588,7 @@ int32_t er_kv_set_block_table(er_kv* kv, uint32_t seq, const int32_t* pages, uin
     std::lock_guard<std::mutex> lock(kv->mu);
     int32_t* row = kv->h_block_table.data() + static_cast<size_t>(seq) * kv->pages_per_seq;
     std::copy(pages, pages + count, row);
-    std::fill(row + count, row + kv->pages_per_seq, 0);
+    std::fill(row + count, row + kv->pages_per_seq, -1);
     kv->h_block_count[seq] = count;
     ER_CUDA(cudaMemcpy(kv->d_block_table + static_cast<size_t>(seq) * kv->pages_per_seq, row,
                        sizeof(int32_t) * kv->pages_per_seq, cudaMemcpyHostToDevice));
@@ -579,10 +626,15 @@ static int32_t host_append(er_kv* kv, uint32_t layer, uint32_t seq, const void* 
     const size_t per_token = static_cast<size_t>(kv->cfg.num_kv_heads) * kv->cfg.head_dim;
     if (count != per_token) return fail(ER_ERR_SHAPE, "expected %zu elements per token, got %zu", per_token, count);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    int32_t rc = check_device(kv);
+    if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
-    int32_t rc = pull_lengths(kv);
+    rc = pull_lengths(kv);
     if (rc != ER_OK) return rc;
     int32_t& total = kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq];
+    // the row goes to ring slot total % maxSeqLen: that slot's page must exist
+    rc = check_page_coverage(kv, seq, static_cast<uint64_t>(total % static_cast<int32_t>(kv->cfg.max_seq_len)) + 1);
+    if (rc != ER_OK) return rc;
     const size_t bytes = per_token * src_elem_bytes;
     rc = ensure_stage(kv, 2 * bytes);
     if (rc != ER_OK) return rc;
@@ -645,9 +697,10 @@ int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element
     if (kv->turbo) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "TurboQuant cache");
     if (kv->q8) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "q8_0 cache");
     if (static_cast<int>(element_bytes) != kv->elem_bytes) return fail(ER_ERR_PRECISION_MISMATCH, "requested %u-byte elements from a %d-byte cache", element_bytes, kv->elem_bytes);
-    std::lock_guard<std::mutex> lock(kv->mu);
-    int32_t rc = pull_lengths(kv);
+    int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    if ((rc = pull_lengths(kv)) != ER_OK) return rc;
     int first_slot, tokens;
     logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
     *token_count = static_cast<uint32_t>(tokens);
@@ -675,9 +728,10 @@ int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, 
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
     if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
-    std::lock_guard<std::mutex> lock(kv->mu);
-    int32_t rc = pull_lengths(kv);
+    int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    if ((rc = pull_lengths(kv)) != ER_OK) return rc;
     int first_slot, tokens;
     logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
     const size_t rows = static_cast<size_t>(tokens) * kv->cfg.num_kv_heads;
@@ -714,9 +768,10 @@ int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t se
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
     if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
-    std::lock_guard<std::mutex> lock(kv->mu);
-    int32_t rc = pull_lengths(kv);
+    int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    if ((rc = pull_lengths(kv)) != ER_OK) return rc;
     int first_slot, tokens;
     logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
     *token_count = static_cast<uint32_t>(tokens);
@@ -750,9 +805,10 @@ static int32_t q8_export(er_kv* kv, uint32_t layer, uint32_t seq, float* hk_valu
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
     if (!kv->q8) return fail(ER_ERR_PRECISION_MISMATCH, "not a q8_0 cache");
     const bool blocks = hk_blocks != nullptr || hv_blocks != nullptr;
-    std::lock_guard<std::mutex> lock(kv->mu);
-    int32_t rc = pull_lengths(kv);
+    int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(kv->mu);
+    if ((rc = pull_lengths(kv)) != ER_OK) return rc;
     int first_slot, tokens;
     logical_window(kv, kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq], first_slot, tokens);
     *token_count = static_cast<uint32_t>(tokens);
@@ -865,6 +921,7 @@ static int32_t generic_decode_row(Workspace* ws, const float* q, const uint16_t*
 int32_t er_gqa_attention_f16kv(const float* q, const uint16_t* k, const uint16_t* v, float* out, const ERGQAParams* gp, void* stream) {
     if (!q || !k || !v || !out || !gp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (gp->numKVHeads == 0 || gp->numHeads % gp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", gp->numHeads, gp->numKVHeads);
+    if (check_raw_pointers(q, k, v, out) != ER_OK) return ER_ERR_INVALID_ARGUMENT;
     const uint32_t kv_seq = gp->kvSeqLen > 0 ? gp->kvSeqLen : gp->seqLen;
     if (gp->seqLen == 0 || kv_seq == 0) return ER_OK;
     if (!flash_shape(gp->headDim, gp->numHeads, gp->numKVHeads)) {
@@ -943,6 +1000,7 @@ int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const
     if (!q || !k || !v || !out || !wp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (wp->numKVHeads == 0 || wp->numHeads % wp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", wp->numHeads, wp->numKVHeads);
     if (wp->kvCount > wp->kvCapacity) return fail(ER_ERR_SHAPE, "kvCount %u > kvCapacity %u", wp->kvCount, wp->kvCapacity);
+    if (check_raw_pointers(q, k, v, out) != ER_OK) return ER_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (wp->kvCount == 0 || wp->kvCapacity == 0) {   // the shader's rule: no rows -> zeros
         const cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(wp->numHeads) * wp->headDim * sizeof(float), s);
@@ -974,6 +1032,30 @@ int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const
     return dispatch_decode_f16(group, p, ws->num_sms, s);
 }
 
+int32_t er_gqa_attention_f32(const float* q, const float* k, const float* v, float* out, const float* additive_mask,
+                             const ERGQAParams* gp, void* stream) {
+    if (!q || !k || !v || !out || !gp) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    // GQAKernel.encode's preconditions (GQAKernel.swift:123-125)
+    if (gp->numKVHeads == 0 || gp->numHeads % gp->numKVHeads != 0) return fail(ER_ERR_SHAPE, "numHeads %u not divisible by numKVHeads %u", gp->numHeads, gp->numKVHeads);
+    if (gp->headDim == 0 || gp->headDim > 512 || gp->headDim % 4 != 0) return fail(ER_ERR_SHAPE, "headDim %u (1...512, divisible by 4)", gp->headDim);
+    const uint32_t kv_seq = gp->kvSeqLen > 0 ? gp->kvSeqLen : gp->seqLen;
+    if (gp->seqLen == 0) return ER_OK;
+    AttentionF32Params fp{};
+    fp.q = q; fp.out = out; fp.k = k; fp.v = v;
+    fp.mask = additive_mask; fp.mask_stride = static_cast<int>(kv_seq);
+    fp.seq_len = static_cast<int>(gp->seqLen); fp.head_dim = static_cast<int>(gp->headDim);
+    fp.num_heads = static_cast<int>(gp->numHeads); fp.num_kv_heads = static_cast<int>(gp->numKVHeads);
+    fp.causal = gp->causal ? 1 : 0; fp.q_offset = static_cast<int>(gp->qOffset); fp.kv_len = static_cast<int>(kv_seq);
+    fp.scale = gp->scale != 0.f ? gp->scale : 1.0f / std::sqrt(static_cast<float>(gp->headDim));
+    fp.addr.token_major = 1; fp.addr.num_kv_heads = static_cast<int>(gp->numKVHeads);
+    fp.addr.max_seq_len = static_cast<int>(std::max<uint32_t>(kv_seq, 1)); fp.addr.page_size = fp.addr.max_seq_len;
+    const int rc = launch_attention_f32(fp, 1, static_cast<cudaStream_t>(stream));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rc == kNotBuilt) return fail(ER_ERR_UNSUPPORTED, "attention_f32_kernel: numHeads %u beyond the grid limit", gp->numHeads);
+    if (rc != 0) return fail(ER_ERR_CUDA, "attention_f32_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return ER_OK;
+}
+
 // ---- cache-level device operators ----
 
 int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t lb, uint32_t le, const float* k, const float* v, const er_step_params* sp, void* stream) {
@@ -983,6 +1065,7 @@ int32_t er_kv_append_rope_kv(er_kv* kv, uint32_t lb, uint32_t le, const float* k
     if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "device append is built for head_dim 128");
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(le - lb) * kv->cfg.max_batch * kv->cfg.num_kv_heads,
                          static_cast<size_t>(kv->cfg.max_batch) * kv->cfg.num_kv_heads, s.k_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
@@ -1007,6 +1090,11 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
     if (rc != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
+    {
+        std::lock_guard<std::mutex> lock(kv->mu);
+        if ((rc = check_page_coverage(kv, seq, static_cast<uint64_t>(start) + count)) != ER_OK) return rc;
+    }
     rc = apply_head_norm(kv, 1, &k, static_cast<size_t>(count) * kv->cfg.num_kv_heads, static_cast<size_t>(count) * kv->cfg.num_kv_heads,
                          s.k_norm_weight, layer, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
@@ -1029,7 +1117,30 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
                                 const float* v_new = nullptr) {
     if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "attention kernels are built for head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
-    if (kv->cfg.precision == ER_KV_FLOAT32) return fail(ER_ERR_UNSUPPORTED, "attention over a float32 cache is outside this backend's scope");
+    if (kv->cfg.precision == ER_KV_FLOAT32) {
+        // float32 rows: the fp32 operator's kernel (gqa_attention_f32, Shaders/GQA.metal:18-143) reading the cache in place
+        if (s.sliding_window > 0) return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches");
+        AttentionF32Params fp{};
+        fp.q = q; fp.out = out;
+        fp.k = reinterpret_cast<const float*>(kv->k_slab); fp.v = reinterpret_cast<const float*>(kv->v_slab);
+        fp.layer_stride_elems = kv->k_layer_stride / 4;
+        fp.seq_len = 1; fp.head_dim = kHeadDim; fp.num_heads = static_cast<int>(num_heads); fp.num_kv_heads = static_cast<int>(kv->cfg.num_kv_heads);
+        fp.causal = 0; fp.scale = s.softmax_scale;
+        fp.lengths = kv->d_lengths; fp.layer_begin = static_cast<int>(lb); fp.batch = static_cast<int>(kv->cfg.max_batch); fp.pending = static_cast<int>(pending);
+        fp.apply_rope = s.apply_rope ? 1 : 0; fp.rope_scaling = s.rope_scaling;
+        if (fp.apply_rope) fp.inv_freq = kv->freq(s.rope_theta);
+        fp.addr = kv->addressing();
+        const int problems = static_cast<int>((le - lb) * kv->cfg.max_batch);
+        const int frc = launch_attention_f32(fp, problems, stream);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (frc != 0) return fail(frc == kNotBuilt ? ER_ERR_UNSUPPORTED : ER_ERR_CUDA, "attention_f32_kernel: %s",
+                                  frc == kNotBuilt ? "shape not covered" : cudaGetErrorString(static_cast<cudaError_t>(frc)));
+        if (advance != 0) {
+            add_lengths_kernel<<<(problems + 255) / 256, 256, 0, stream>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), problems, static_cast<int>(advance));
+            return check_launch("add_lengths_kernel");
+        }
+        return ER_OK;
+    }
     if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
         return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
@@ -1062,6 +1173,7 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         p.norm_stride = static_cast<int>(s.norm_weight_layer_stride); p.rms_eps = s.rms_eps;
         p.addr = kv->addressing();
         p.window = static_cast<int>(std::min<uint32_t>(s.sliding_window, 0x7fffffffu));
+        p.wait_limit_us = kv->probe_wait_limit_us; p.withhold_tiles = kv->probe_withhold_tiles;
         p.scratch = kv->d_scratch; p.done_counter = kv->d_counters; p.status = kv->d_counters + 1; p.item_counters = kv->d_counters + 16;
         if (kv->turbo)
             rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
@@ -1085,6 +1197,7 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float*
     if (rc != ER_OK) return rc;
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(le - lb) * kv->cfg.max_batch * num_heads, static_cast<size_t>(kv->cfg.max_batch) * num_heads,
                          s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
@@ -1108,6 +1221,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (rc != ER_OK) return rc;
     if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
         return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
                          static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
@@ -1201,7 +1315,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (pp.apply_rope) pp.inv_freq = kv->freq(s.rope_theta);
     const uint64_t outer_extent = (kv->turbo || kv->q8) ? 1u : static_cast<uint64_t>(kv->pool_pages);
     const int rcl = launch_prefill(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, outer_extent, static_cast<int>(kv->cfg.num_kv_heads),
-                                   kv->d_counters + 1, static_cast<cudaStream_t>(stream));
+                                   kv->d_counters + 1, static_cast<cudaStream_t>(stream), kv->cfg.prefill_kernel == ER_PREFILL_KERNEL_MMA_SYNC);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
     if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
@@ -1218,6 +1332,7 @@ int32_t er_kv_advance(er_kv* kv, uint32_t lb, uint32_t le, uint32_t count, void*
     if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
     int32_t rc = check_layers(kv, lb, le);
     if (rc != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     const int n = static_cast<int>((le - lb) * kv->cfg.max_batch);
     add_lengths_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), n, static_cast<int>(count));
     return check_launch("add_lengths_kernel");
@@ -1230,8 +1345,9 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     if (rc != ER_OK) return rc;
     er_step_params s;
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    const bool one_launch = le - lb <= layers_per_launch;
+    const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32;
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.
     const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;
@@ -1273,6 +1389,7 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     if (!kv || !hq || !hk || !hv || !hout) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     int32_t rc = check_layers(kv, lb, le);
     if (rc != ER_OK) return rc;
+    if ((rc = check_device(kv)) != ER_OK) return rc;
     const size_t rows = static_cast<size_t>(le - lb) * kv->cfg.max_batch;
     const size_t q_bytes = rows * num_heads * kv->cfg.head_dim * 4, kv_bytes = rows * kv->cfg.num_kv_heads * kv->cfg.head_dim * 4;
     {
@@ -1305,8 +1422,11 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
                            step_out, num_heads, sp, stream);
     if (rc != ER_OK) return rc;
     if (!mout) ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
+    // the step's device status travels back with the results: a bounded wait that gave up, or a row without a page,
+    // is this call's error and not garbage returned as success
+    ER_CUDA(cudaMemcpyAsync(kv->h_status, kv->d_counters + 1, sizeof(int), cudaMemcpyDeviceToHost, s));
     ER_CUDA(cudaStreamSynchronize(s));
-    return ER_OK;
+    return device_status_to_code(*kv->h_status);
 }
 
 int32_t er_kv_set_trace(er_kv* kv, uint64_t* device_buffer, uint32_t capacity_ctas) {
@@ -1321,7 +1441,37 @@ int32_t er_kv_device_status(er_kv* kv) {
     if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
     int status = 0;
     ER_CUDA(cudaMemcpy(&status, kv->d_counters + 1, sizeof(int), cudaMemcpyDeviceToHost));
-    return status;
+    return device_status_to_code(status);
+}
+
+int32_t er_kv_debug_wait_probe(er_kv* kv, uint32_t wait_limit_us, int withhold_tiles) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    if (withhold_tiles && (wait_limit_us == 0 || wait_limit_us > 100000))
+        return fail(ER_ERR_INVALID_ARGUMENT, "withholding the tiles needs a wait limit of 1 .. 100000 microseconds");
+    std::lock_guard<std::mutex> lock(kv->mu);
+    kv->probe_wait_limit_us = wait_limit_us;
+    kv->probe_withhold_tiles = withhold_tiles ? 1 : 0;
+    return ER_OK;
+}
+
+int32_t er_kv_clear_device_status(er_kv* kv) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    ER_CUDA(cudaMemset(kv->d_counters + 1, 0, sizeof(int)));
+    return ER_OK;
+}
+
+int32_t er_workspace_status(void) {
+    int device = 0;
+    ER_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return ER_OK;
+    int status = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mu);
+        if (g_ws[device].device != device) return ER_OK;   // no raw-buffer operator has run on this device yet
+        ER_CUDA(cudaMemcpy(&status, g_ws[device].counters + 1, sizeof(int), cudaMemcpyDeviceToHost));
+        if (status != 0) ER_CUDA(cudaMemset(g_ws[device].counters + 1, 0, sizeof(int)));
+    }
+    return device_status_to_code(status);
 }
 
 }  // extern "C"

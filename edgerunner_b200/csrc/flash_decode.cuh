@@ -60,6 +60,11 @@ struct DecodeParams {
     int window;
     int fixed_start;
     int advance;                  // added to lengths[...] by the last CTA to finish
+    // Diagnostics of the bounded waits: wait_limit_us > 0 replaces the 2 s patience of every mbarrier wait of the launch;
+    // withhold_tiles = 1 makes the producer warp issue no copy at all, so the consumers' first wait runs out, the launch
+    // walks its whole control flow with the abort flag set and the status word reads kStatusTimeout (outputs undefined).
+    uint32_t wait_limit_us;
+    int withhold_tiles;
     float scale_log2;             // softmax scale * log2(e)
     float rope_scaling;
     int apply_rope;
@@ -440,12 +445,13 @@ struct DensePolicy {
         reinterpret_cast<__half2*>(&vv)[1] = __halves2half2(__float2half_rn(v4.z), __float2half_rn(v4.w));
         reinterpret_cast<uint2*>(vrow)[lane] = vv;
         __syncwarp();
-        const int64_t row = row_index(p.addr, seq, head, slot);
+        const int64_t row = row_index_for_write(p.addr, seq, head, slot);
         const bool is_v = lane >= 16;
         const uint4 val = *reinterpret_cast<const uint4*>((is_v ? vrow : krow) + (lane & 15) * 16);
         uint8_t* dst = const_cast<uint8_t*>(is_v ? p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes
                                                  : p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes);
-        *reinterpret_cast<uint4*>(dst + row * kRowBytesF16 + (lane & 15) * 16) = val;
+        if (row >= 0)   // a slot without a page keeps the row out of the cache (status word set)
+            *reinterpret_cast<uint4*>(dst + row * kRowBytesF16 + (lane & 15) * 16) = val;
         // generic-proxy writes to the stage precede its next refill by the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -550,10 +556,11 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
         const int64_t range_begin = cta_range_start(cta, total_units, active);
         const int64_t range_end = cta_range_start(cta + 1, total_units, active);
 
+        const uint64_t wait_ns = p.wait_limit_us > 0 ? static_cast<uint64_t>(p.wait_limit_us) * 1000ull : 2000000000ull;
         if (warp == NW) {
             // ================= producer warp =================
             int k = 0;
-            int64_t cur = range_begin;
+            int64_t cur = p.withhold_tiles ? range_end : range_begin;
             while (cur < range_end) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
@@ -574,7 +581,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     const int s = k % kStages;
                     // the policy calls this once, after any address lookups that can run while the stage is still busy
                     auto wait_free = [&]() {
-                        if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status);
+                        if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status, wait_ns);
                     };
                     POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start, wait_free);
                 }
@@ -613,7 +620,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     const int t0 = tu * kUnitTokens;
                     const int ntok = min(kv_len, (tu + nun) * kUnitTokens) - t0;
                     const int s = k % kStages;
-                    mbar_wait(&full_bar[s], (k / kStages) & 1, &flags[0], p.status);
+                    mbar_wait(&full_bar[s], (k / kStages) & 1, &flags[0], p.status, wait_ns);
                     if (k == 0 && tid == 0) stamp(2);
                     if (POL::kFusedAppend && p.fused_append && !flags[0]) {
                         const int slot_new = q_pos % p.addr.max_seq_len;

@@ -44,6 +44,29 @@ struct GenericDecodeParams {
 };
 int launch_decode_generic(GenericDecodeParams p, int num_sms, size_t scratch_floats, size_t counter_ints, cudaStream_t stream);
 
+// GQA attention over float32 K / V rows (attention_f32.cu): raw [kvSeqLen][kv heads][head_dim] buffers (lengths ==
+// nullptr, one problem, seq_len query rows, optional additive mask [seq_len][mask_stride]) or a float32 cache (lengths
+// set: one problem per (layer, sequence) of [layer_begin, ...), one query row each, kv length read on the device).
+struct AttentionF32Params {
+    const float* q;       // [problems][seq_len][num_heads][head_dim]
+    float* out;
+    const float* k;       // rows of layer 0
+    const float* v;
+    int64_t layer_stride_elems;
+    const float* mask;    // additive, or nullptr
+    int mask_stride;
+    int seq_len, head_dim, num_heads, num_kv_heads;
+    int causal, q_offset, kv_len;
+    float scale;
+    const int32_t* lengths;
+    int layer_begin, batch, pending;
+    int apply_rope;       // cache mode, head_dim 128: NeoX-rotate the query row at position kv_len - 1
+    float rope_scaling;
+    KVAddressing addr;
+    InvFreqTable inv_freq;
+};
+int launch_attention_f32(const AttentionF32Params& p, int problems, cudaStream_t stream);
+
 template <class POL>
 inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
     constexpr int kSmem = DecodeSmem<POL>::kTotal;

@@ -27,7 +27,8 @@ namespace {
 constexpr int kStaticMaxCtas = 256;        // CTAs of one launch (one per SM; a B200 has 148)
 constexpr int kStaticMaxGroup = 4;         // query heads per kv head
 constexpr int kStaticMaxKVHeads = 16;      // kv heads of one call
-constexpr int kStaticCounterBytes = 1024;  // [0] CTAs done, [1] device status, [16 .. 16+kv heads) per-head counters
+constexpr int kStaticCounterBytes = 1024;  // [0] CTAs done, [16 .. 16+kv heads) per-head counters, [255] device status
+constexpr int kStaticStatusIndex = 255;    // outside the range each call re-zeroes: sticky until read
 constexpr int kStaticPartialBytes = kStaticMaxCtas * 2 * kStaticMaxGroup * 130 * 4;   // two partial slots per CTA
 constexpr int kStaticScratchBytes = kStaticCounterBytes + kStaticPartialBytes;        // 1 065 984 bytes (~1.02 MiB)
 
@@ -65,6 +66,8 @@ extern "C" int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t*
                                                  const ERGQAParams* gp, void* stream) {
     using namespace er;
     if (!q || !k || !v || !out || !gp) return report_error(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return report_error(ER_ERR_INVALID_ARGUMENT, "q, k, v and out must be 16-byte aligned device addresses");
     if (gp->headDim != kHeadDim) return report_error(ER_ERR_UNSUPPORTED, "headDim must be 128");
     if (gp->numKVHeads == 0 || gp->numHeads % gp->numKVHeads != 0) return report_error(ER_ERR_SHAPE, "numHeads must be a multiple of numKVHeads");
     const int group = static_cast<int>(gp->numHeads / gp->numKVHeads);
@@ -88,8 +91,8 @@ extern "C" int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t*
         return report_error(ER_ERR_UNSUPPORTED, msg);
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left: the counters must start at zero.
-    e = cudaMemsetAsync(scratch, 0, kStaticCounterBytes, s);
+    // The array keeps whatever the previous call left: the counters must start at zero (the status word stays).
+    e = cudaMemsetAsync(scratch, 0, kStaticStatusIndex * sizeof(int), s);
     if (e != cudaSuccess) return report_error(ER_ERR_CUDA, cudaGetErrorString(e));
 
     int* counters = reinterpret_cast<int*>(scratch);
@@ -105,7 +108,7 @@ extern "C" int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t*
     p.addr.token_major = 1; p.addr.num_kv_heads = static_cast<int>(gp->numKVHeads);
     p.addr.max_seq_len = static_cast<int>(kv_seq); p.addr.page_size = static_cast<int>(kv_seq);
     p.scratch = reinterpret_cast<float*>(scratch + kStaticCounterBytes);
-    p.done_counter = counters; p.status = counters + 1; p.item_counters = counters + 16;
+    p.done_counter = counters; p.status = counters + kStaticStatusIndex; p.item_counters = counters + 16;
     encode_token_major_maps(p, group, 1, 1, kv_seq, gp->numKVHeads);   // host-side descriptor encoding: no device allocation
     for (uint32_t r = 0; r < gp->seqLen; ++r) {   // row r sees keys 0 .. r + qOffset (Shaders/GQA.metal:345)
         const uint64_t visible = gp->causal ? (static_cast<uint64_t>(r) + gp->qOffset + 1 < kv_seq ? static_cast<uint64_t>(r) + gp->qOffset + 1 : kv_seq) : kv_seq;
@@ -118,4 +121,27 @@ extern "C" int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t*
         if (lrc != 0) return report_error(ER_ERR_CUDA, cudaGetErrorString(static_cast<cudaError_t>(lrc)));
     }
     return ER_OK;
+}
+
+// Reads (and clears) the status word the kernels of er_gqa_attention_f16kv_static leave in the built-in workspace of the
+// current device: ER_ERR_DEVICE_TIMEOUT when a bounded wait inside one of them gave up.  Synchronises with the device;
+// like the operator itself it allocates nothing.
+extern "C" int32_t er_gqa_attention_f16kv_static_status(void) {
+    using namespace er;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return report_error(ER_ERR_CUDA, cudaGetErrorString(e));
+    unsigned char* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mu);
+        if (device < 0 || device >= kMaxDevices || g_device_scratch[device] == nullptr) return ER_OK;   // never used here
+        scratch = g_device_scratch[device];
+    }
+    int status = 0;
+    int* word = reinterpret_cast<int*>(scratch) + kStaticStatusIndex;
+    e = cudaMemcpy(&status, word, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && status != 0) e = cudaMemset(word, 0, sizeof(int));
+    if (e != cudaSuccess) return report_error(ER_ERR_CUDA, cudaGetErrorString(e));
+    if (status == kStatusTimeout) return report_error(ER_ERR_DEVICE_TIMEOUT, "a bounded wait inside a kernel gave up");
+    return status == 0 ? ER_OK : report_error(ER_ERR_CUDA, "unexpected device status");
 }

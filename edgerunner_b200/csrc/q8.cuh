@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(256) q8_append_kernel(const __grid_constant__ 
     float scale;
     const uint32_t word = q8_quantize_lane(x, scale);
     const int slot = static_cast<int>(pos % static_cast<uint32_t>(p.addr.max_seq_len));
-    const int64_t ridx = row_index(p.addr, seq, h, slot);
+    const int64_t ridx = row_index_for_write(p.addr, seq, h, slot);
+    if (ridx < 0) return;   // no page behind the slot: dropped, the status word says so
     uint8_t* rows = is_v ? p.v_base + layer * p.v_layer_stride_bytes : p.k_base + layer * p.k_layer_stride_bytes;
     reinterpret_cast<uint32_t*>(rows + ridx * kQ8RowBytes)[q8_word_slot(lane)] = word;
     if ((lane & 7) == 0) {

@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(kQuantWarps * 32) tq_append_kernel(const __gri
         uint32_t pos;
         append_locate(p, r, layer, seq, pos);
         const int slot = static_cast<int>(pos % static_cast<uint32_t>(p.addr.max_seq_len));
-        const int64_t ridx = row_index(p.addr, seq, h, slot);
+        const int64_t ridx = row_index_for_write(p.addr, seq, h, slot);
+        if (ridx < 0) continue;   // no page behind the slot: dropped, the status word says so
         uint8_t* codes = (is_v ? p.v_base + layer * p.v_layer_stride_bytes : p.k_base + layer * p.k_layer_stride_bytes) +
                          ridx * (words * 4);
         // 16-byte vector stores: words*4 bytes = 32 / 48 / 64.

@@ -44,6 +44,34 @@ class GQAKernel:
     block_size = 16                 # GQAKernel.blockSize
     max_optimized_head_dim = 128    # GQAKernel.maxOptimizedHeadDim
 
+    max_supported_head_dim = 512    # GQAKernel.maxSupportedHeadDim
+
+    def encode_f32(self, q_buffer, k_buffer, v_buffer, output_buffer, seq_len, head_dim, num_heads, num_kv_heads, causal,
+                   kv_seq_len=0, q_offset=0, additive_mask_buffer=None, stream=None):
+        """GQAKernel.encode (GQAKernel.swift:113-172): float32 q/k/v/out device buffers, optional additive mask
+        [seq_len, kv_seq_len] (-inf hides a key)."""
+        p = ERGQAParams(seq_len, head_dim, num_heads, num_kv_heads, num_heads // num_kv_heads, 1.0 / math.sqrt(head_dim),
+                        int(bool(causal)), self.block_size, self.block_size, kv_seq_len, q_offset)
+        check(lib().er_gqa_attention_f32(ptr(q_buffer), ptr(k_buffer), ptr(v_buffer), ptr(output_buffer),
+                                         ptr(additive_mask_buffer), C.byref(p), stream_ptr(stream)))
+
+    def execute(self, q, k, v, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len=0, q_offset=0, additive_mask=None):
+        """GQAKernel.execute (GQAKernel.swift:27-110): arrays in, array out."""
+        torch = _torch()
+        eff = kv_seq_len if kv_seq_len > 0 else seq_len
+        qd = torch.as_tensor(np.ascontiguousarray(q, dtype=np.float32)).cuda()
+        kd = torch.as_tensor(np.ascontiguousarray(k, dtype=np.float32)).cuda()
+        vd = torch.as_tensor(np.ascontiguousarray(v, dtype=np.float32)).cuda()
+        assert qd.numel() == seq_len * num_heads * head_dim and kd.numel() == vd.numel() == eff * num_kv_heads * head_dim
+        md = None
+        if additive_mask is not None:
+            md = torch.as_tensor(np.ascontiguousarray(additive_mask, dtype=np.float32)).cuda()
+            assert md.numel() == seq_len * eff
+        out = torch.empty_like(qd)
+        self.encode_f32(qd, kd, vd, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len, q_offset, md)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
     def encode(self, q_buffer, k_buffer, v_buffer, output_buffer, seq_len, head_dim, num_heads, num_kv_heads, causal,
                kv_seq_len=0, q_offset=0, scale=None, stream=None):
         """fp16 K/V variant (pipelineF16KV): q/out float32 [S,H,D], k/v float16 [T,Hkv,D] device buffers."""

@@ -60,12 +60,13 @@ def step_params(rope_theta=10000.0, rope_scaling=1.0, softmax_scale=0.0, apply_r
 class KVCache:
     def __init__(self, max_seq_len, num_layers, num_kv_heads, head_dim, precision, *, key_type=TurboQuantFixedType.turbo3,
                  value_type=TurboQuantFixedType.turbo3, norm_format=NormFormat.float32, max_batch=1,
-                 layout=Layout.head_major, page_size=0, num_pages=0):
+                 layout=Layout.head_major, page_size=0, num_pages=0, prefill_kernel=0):
         cfg = er_kv_config()
         cfg.max_seq_len, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim = max_seq_len, num_layers, num_kv_heads, head_dim
         cfg.precision, cfg.key_type, cfg.value_type = int(precision), int(key_type), int(value_type)
         cfg.norm_format, cfg.max_batch, cfg.layout = int(norm_format), max_batch, int(layout)
         cfg.page_size, cfg.num_pages = page_size, num_pages
+        cfg.prefill_kernel = int(prefill_kernel)     # 0 = automatic, 1 = always the mma.sync kernel (A/B measurements)
         self._h = C.c_void_p()
         self._destroy = lib().er_kv_destroy      # held by the object: close() may run while the interpreter shuts down
         check(lib().er_kv_create(C.byref(cfg), C.byref(self._h)))
@@ -258,4 +259,12 @@ class KVCache:
         return check(lib().er_kv_set_trace(self._h, ptr(buffer), capacity_ctas))
 
     def device_status(self):
+        """0, or the negative status a kernel of this cache left behind (ER_ERR_DEVICE_TIMEOUT, ER_ERR_OUT_OF_PAGES)."""
         return lib().er_kv_device_status(self._h)
+
+    def clear_device_status(self):
+        check(lib().er_kv_clear_device_status(self._h))
+
+    def debug_wait_probe(self, wait_limit_us=0, withhold_tiles=False):
+        """Test hook of the bounded-wait path (er_kv_debug_wait_probe); (0, False) restores normal operation."""
+        check(lib().er_kv_debug_wait_probe(self._h, wait_limit_us, int(bool(withhold_tiles))))

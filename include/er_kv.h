@@ -107,6 +107,11 @@ enum { ER_KV_LAYOUT_TOKEN_MAJOR = 0, ER_KV_LAYOUT_HEAD_MAJOR = 1, ER_KV_LAYOUT_P
  * KVCache.swift:1095-1096); the compact format keeps rowNorm as fp16 and drops the always-zero rest. */
 enum { ER_TQ_NORM_FLOAT32 = 0, ER_TQ_NORM_FLOAT16 = 1 };
 
+/* Chunked-prefill kernel choice (the counterpart of the reference's pipeline selection by shape in
+ * GQAKernel.encode, GQAKernel.swift:136-160): AUTO runs the tcgen05 kernel when the chunk fills a 128-row CTA tile
+ * and the mma.sync kernel otherwise; MMA_SYNC always runs the latter (A/B measurements). */
+enum { ER_PREFILL_KERNEL_AUTO = 0, ER_PREFILL_KERNEL_MMA_SYNC = 1 };
+
 typedef struct {
     uint32_t max_seq_len;   /* ring length per sequence (tokens) */
     uint32_t num_layers;
@@ -120,7 +125,8 @@ typedef struct {
     uint32_t layout;        /* ER_KV_LAYOUT_* (TurboQuant storage ignores TOKEN_MAJOR and uses HEAD_MAJOR) */
     uint32_t page_size;     /* tokens per page, multiple of 16 (PAGED only) */
     uint32_t num_pages;     /* pages in the shared pool (PAGED only) */
-    uint32_t reserved[4];
+    uint32_t prefill_kernel; /* ER_PREFILL_KERNEL_*: which chunked-prefill kernel er_kv_attention_prefill may use */
+    uint32_t reserved[3];
 } er_kv_config;
 
 typedef struct er_kv er_kv;
@@ -217,7 +223,10 @@ int32_t er_kv_advance_write_position(er_kv* kv, uint32_t layer, uint32_t seq, ui
 int32_t er_kv_set_position(er_kv* kv, uint32_t seq, uint32_t position);
 
 /* Paged layout: install the block table of one sequence (page ids into the shared pool, one per page_size
- * tokens).  The allocator that hands out page ids lives above this ABI (host side). */
+ * tokens).  The allocator that hands out page ids lives above this ABI (host side).  Entries beyond page_count hold no
+ * page: a host-side write that would land there (er_kv_append_*, er_kv_write_rows) returns ER_ERR_OUT_OF_PAGES before
+ * anything is launched; a device-side append (er_kv_append_rope_kv, er_kv_decode_step) drops the row and sets the
+ * device status word to ER_ERR_OUT_OF_PAGES (see er_kv_device_status) -- no other sequence's page is touched. */
 int32_t er_kv_set_block_table(er_kv* kv, uint32_t seq, const int32_t* host_page_ids, uint32_t page_count);
 int32_t er_kv_get_block_table(er_kv* kv, uint32_t seq, int32_t* host_page_ids, uint32_t capacity, uint32_t* page_count);
 
@@ -243,7 +252,15 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
                                     uint32_t* out_residual_signs, uint32_t* out_outlier_mask, float* out_metadata,
                                     void* stream);
 
-/* GQAKernel.encode on an fp16 K/V pair -> gqa_attention_f16kv (GQAKernel.swift:113-172, Shaders/GQA.metal:278-387).
+/* GQAKernel.encode / GQAKernel.execute (GQAKernel.swift:27-172) -> gqa_attention_f32, gqa_attention_f32_wide,
+ * gqa_attention_f32_masked_wide (Shaders/GQA.metal:18-276): float32 K / V.  q/out: device [seqLen][numHeads][headDim]
+ * float; k/v: device [kvSeqLen][numKVHeads][headDim] float; additive_mask: device [seqLen][kvSeqLen] float added to the
+ * scaled scores (-inf entries hide a key), or NULL -- the additiveMaskBuffer argument.  headDim 1...512, divisible by 4
+ * (the wrapper's preconditions); a query row with no visible finite score yields zeros. */
+int32_t er_gqa_attention_f32(const float* q, const float* k, const float* v, float* out, const float* additive_mask,
+                             const ERGQAParams* params, void* stream);
+
+/* The fp16-K/V pipeline of the same holder -> gqa_attention_f16kv (GQAKernel.swift:113-172, Shaders/GQA.metal:278-387).
  * q/out: device [seqLen][numHeads][headDim] float; k/v: device [kvSeqLen][numKVHeads][headDim] fp16.
  * headDim 128 with 1/2/4/8 query heads per kv head and <= 16 kv heads: persistent flash-decode kernel (seqLen 1) or
  * tensor-core prefill kernel (seqLen > 1); other even headDim <= 512 / groups: a plain split kernel, one launch per row. */
@@ -276,8 +293,9 @@ int32_t er_gqa_attention_f16kv_windowed(const float* q, const uint16_t* k, const
  * cudaMalloc / cudaFree of any kind.  Limits: numKVHeads <= 16, numHeads / numKVHeads in {1, 2, 4}, at most 256 SMs;
  * anything larger is rejected with ER_ERR_UNSUPPORTED.  The first call on a device looks up the array's device
  * address (make that call before starting a stream capture).  All calls share the one array: it keeps the last
- * call's contents (the counters are re-zeroed on the stream at every call) and two calls that overlap on the GPU
- * race -- keep them on one stream or order them yourself. */
+ * call's contents (the counters are re-zeroed on the stream at every call; the status word stays until
+ * er_gqa_attention_f16kv_static_status reads it) and two calls that overlap on the GPU race -- keep them on one stream
+ * or order them yourself. */
 int32_t er_gqa_attention_f16kv_static(const float* q, const uint16_t* k, const uint16_t* v, float* out,
                                       const ERGQAParams* params, void* stream);
 
@@ -331,8 +349,23 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
 
 /* Number of kernels this library has launched since load (all caches, this process). */
 uint64_t er_kernel_launch_count(void);
-/* Device status word of the cache: 0, or ER_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel expired. */
+/* Device status word of the cache (synchronises with the device): ER_OK, ER_ERR_DEVICE_TIMEOUT if a bounded wait inside a
+ * kernel expired (the launch still ran to its end; its outputs are not valid), or ER_ERR_OUT_OF_PAGES if a device-side
+ * append met a block-table entry without a page (that row was dropped, nothing else was touched).  The word is sticky
+ * until er_kv_clear_device_status.  er_kv_decode_step_host returns the same codes by itself. */
 int32_t er_kv_device_status(er_kv* kv);
+int32_t er_kv_clear_device_status(er_kv* kv);
+/* Test hook for that status path: decode launches of this cache that follow wait at most `wait_limit_us` microseconds
+ * (0 = the normal 2 s) on each of their internal barriers, and with withhold_tiles != 0 their copy-issuing warp stays
+ * idle, so the first wait runs out: the launch still runs to its end on its own (nothing traps or spins), its outputs
+ * are undefined and the status word reads ER_ERR_DEVICE_TIMEOUT.  (0, 0) restores normal operation. */
+int32_t er_kv_debug_wait_probe(er_kv* kv, uint32_t wait_limit_us, int withhold_tiles);
+/* The same word for the raw-buffer operators (er_gqa_attention_f16kv, er_gqa_attention_f16kv_windowed) on the current
+ * device; reading it clears it.  Those operators share one workspace per device: keep their calls on one stream (or
+ * order them yourself), two that overlap on the GPU race on the split-K partials. */
+int32_t er_workspace_status(void);
+/* And for er_gqa_attention_f16kv_static's built-in workspace on the current device; reading it clears it. */
+int32_t er_gqa_attention_f16kv_static_status(void);
 
 /* Diagnostics (the counterpart of the reference's per-phase trace collectors,
  * Sources/EdgeRunner/Models/LlamaLanguageModel.swift:6322-6558): while a buffer is installed every CTA of a decode

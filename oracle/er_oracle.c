@@ -183,10 +183,11 @@ ERO_API void ero_convert_f16_to_f32(const uint16_t *in, float *out, size_t n) {
 
 /* cpuGQA, GQATests.swift:9-67: two-pass softmax, [S,H,D] layouts, causal rule
  * "key k visible to query row r iff k <= r + qOffset".  Masked scores are
- * -greatestFiniteMagnitude (their exp underflows to 0). */
+ * -greatestFiniteMagnitude (their exp underflows to 0).  additive_mask (or NULL) is
+ * [seq_len][kv_seq_len], added to the scaled score (GQATests.swift:46). */
 static void gqa_one_head(const float *q, const float *k, const float *v, float *out, int seq_len,
                          int head_dim, int num_heads, int num_kv_heads, int causal, int kv_seq_len,
-                         int q_offset, int head, float *scores) {
+                         int q_offset, int head, float *scores, const float *additive_mask) {
     float scale = 1.0f / sqrtf((float)head_dim);
     int group = num_heads / num_kv_heads;
     int q_stride = num_heads * head_dim;
@@ -199,7 +200,7 @@ static void gqa_one_head(const float *q, const float *k, const float *v, float *
             const float *kv = k + (size_t)k_row * kv_stride + (size_t)kv_head * head_dim;
             float dot = 0.0f;
             for (int d = 0; d < head_dim; ++d) dot += qv[d] * kv[d];
-            scores[k_row] = dot * scale;
+            scores[k_row] = dot * scale + (additive_mask ? additive_mask[(size_t)q_row * kv_seq_len + k_row] : 0.0f);
         }
         float max_val = 0.0f;
         if (kv_seq_len > 0) {
@@ -219,9 +220,19 @@ static void gqa_one_head(const float *q, const float *k, const float *v, float *
     }
 }
 
+ERO_API void ero_gqa_f32_masked(const float *q, const float *k, const float *v, float *out, int seq_len,
+                                int head_dim, int num_heads, int num_kv_heads, int causal, int kv_seq_len,
+                                int q_offset, int threads, const float *additive_mask);
+
 ERO_API void ero_gqa_f32(const float *q, const float *k, const float *v, float *out, int seq_len,
                          int head_dim, int num_heads, int num_kv_heads, int causal, int kv_seq_len,
                          int q_offset, int threads) {
+    ero_gqa_f32_masked(q, k, v, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len, q_offset, threads, NULL);
+}
+
+ERO_API void ero_gqa_f32_masked(const float *q, const float *k, const float *v, float *out, int seq_len,
+                                int head_dim, int num_heads, int num_kv_heads, int causal, int kv_seq_len,
+                                int q_offset, int threads, const float *additive_mask) {
     if (kv_seq_len <= 0) kv_seq_len = seq_len;
     (void)threads;
 #pragma omp parallel num_threads(threads > 0 ? threads : 1)
@@ -230,7 +241,7 @@ ERO_API void ero_gqa_f32(const float *q, const float *k, const float *v, float *
 #pragma omp for schedule(dynamic, 1)
         for (int head = 0; head < num_heads; ++head)
             gqa_one_head(q, k, v, out, seq_len, head_dim, num_heads, num_kv_heads, causal, kv_seq_len,
-                         q_offset, head, scores);
+                         q_offset, head, scores, additive_mask);
         free(scores);
     }
 }

@@ -61,6 +61,7 @@ def lib():
     L.ero_convert_f32_to_f16.argtypes = [f32p, u16p, C.c_size_t]
     L.ero_convert_f16_to_f32.argtypes = [u16p, f32p, C.c_size_t]
     L.ero_gqa_f32.argtypes = [f32p, f32p, f32p, f32p] + [C.c_int] * 8
+    L.ero_gqa_f32_masked.argtypes = [f32p, f32p, f32p, f32p] + [C.c_int] * 8 + [f32p]
     L.ero_gqa_f16kv.argtypes = [f32p, u16p, u16p, f32p] + [C.c_int] * 8
     L.ero_splitk_merge.argtypes = [f32p, f32p, f32p, C.c_int, C.c_int, f32p]
     L.ero_gqa_f16kv_windowed.argtypes = [f32p, u16p, u16p, f32p] + [C.c_int] * 6 + [C.c_float]
@@ -165,13 +166,19 @@ def rope_neox_to_f16(x, start_pos, theta, scaling=1.0, partial=1.0):
 
 # ----------------------------------------------------------------------------- dense attention
 
-def gqa_f32(q, k, v, causal=True, q_offset=0, threads=1):
-    """q: [S,H,D]; k, v: [T,Hkv,D] float32 -> [S,H,D] (cpuGQA)."""
+def gqa_f32(q, k, v, causal=True, q_offset=0, threads=1, additive_mask=None):
+    """q: [S,H,D]; k, v: [T,Hkv,D] float32 -> [S,H,D] (cpuGQA); additive_mask: [S,T] added to the scaled scores."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     s, h, d = q.shape
     t, hkv, _ = k.shape
     out = np.empty_like(q)
-    lib().ero_gqa_f32(_p(q, F32), _p(k, F32), _p(v, F32), _p(out, F32), s, d, h, hkv, int(causal), t, q_offset, threads)
+    if additive_mask is None:
+        lib().ero_gqa_f32(_p(q, F32), _p(k, F32), _p(v, F32), _p(out, F32), s, d, h, hkv, int(causal), t, q_offset, threads)
+    else:
+        m = _f32(additive_mask)
+        assert m.size == s * t
+        lib().ero_gqa_f32_masked(_p(q, F32), _p(k, F32), _p(v, F32), _p(out, F32), s, d, h, hkv, int(causal), t, q_offset,
+                                 threads, _p(m, F32))
     return out
 
 

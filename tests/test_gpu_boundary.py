@@ -1,0 +1,231 @@
+"""GPU tests of the boundary's guard rails and of the float32 operator, all through the C ABI:
+
+* GQAKernel.execute on float32 K/V with the additive mask -- the reference's own test inputs
+  (Tests/EdgeRunnerMetalTests/GQATests.swift:232-324, closed-form fixtures) against the CPU oracle (cpuGQA);
+* attention over a float32 cache;
+* paged caches: a write past the pages a sequence owns is refused on the host, dropped (and flagged) on the device,
+  and never lands in another sequence's page;
+* raw-buffer operators refuse misaligned pointers before anything is launched; a cache refuses another device;
+* a bounded wait that runs out comes back as ER_ERR_DEVICE_TIMEOUT with the context still usable (the launch returns
+  by itself: the producer warp is told to stay idle and the waits get a 300-microsecond patience).
+"""
+import numpy as np
+import pytest
+
+from helpers import max_rel_err, normal_f16, rng_for
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def er():
+    import edgerunner_b200 as er
+    assert er.lib().er_device_count() > 0
+    return er
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    return torch
+
+
+def dev(torch, a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def _closed_form(n, mod, shift, step):
+    return ((np.arange(n) % mod) - shift).astype(np.float32) * np.float32(step)
+
+
+def test_gqa_f32_additive_mask_reference_inputs(er, oracle):
+    gk = er.GQAKernel()
+    # gqaAdditiveMaskMatchesCPUReference (GQATests.swift:232-275)
+    S, D, H, Hkv = 8, 128, 4, 2
+    q, k, v = _closed_form(S * H * D, 17, 8, 0.025), _closed_form(S * Hkv * D, 13, 6, 0.025), _closed_form(S * Hkv * D, 11, 5, 0.02)
+    mask = np.zeros((S, S), dtype=np.float32)
+    mask[1, 0], mask[1, 2], mask[5, 4], mask[6, 7] = -np.inf, 2.0, -3.0, -np.inf
+    want = oracle.gqa_f32(q.reshape(S, H, D), k.reshape(S, Hkv, D), v.reshape(S, Hkv, D), causal=False, additive_mask=mask)
+    got = gk.execute(q, k, v, S, D, H, Hkv, False, additive_mask=mask).reshape(want.shape)
+    assert np.abs(got - want).max() < 1e-4          # the reference's bound
+    # gqaAdditiveMaskUsesEffectiveKVSeqLen (GQATests.swift:277-324)
+    S, T, off, D = 2, 5, 3, 64
+    q, k, v = _closed_form(S * H * D, 17, 8, 0.02), _closed_form(T * Hkv * D, 19, 9, 0.02), _closed_form(T * Hkv * D, 23, 11, 0.015)
+    mask = np.zeros((S, T), dtype=np.float32)
+    mask[0, 1], mask[0, 4], mask[1, 2] = -2.0, -np.inf, 1.5
+    want = oracle.gqa_f32(q.reshape(S, H, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), causal=True, q_offset=off, additive_mask=mask)
+    got = gk.execute(q, k, v, S, D, H, Hkv, True, kv_seq_len=T, q_offset=off, additive_mask=mask).reshape(want.shape)
+    assert np.abs(got - want).max() < 1e-4
+    # a fully masked query row yields zeros (the shader's `maxScore == -inf` rule, GQA.metal:213-216)
+    mask[:] = 0
+    mask[0, :] = -np.inf
+    got = gk.execute(q, k, v, S, D, H, Hkv, True, kv_seq_len=T, q_offset=off, additive_mask=mask).reshape(want.shape)
+    assert np.all(got[0] == 0) and np.isfinite(got).all()
+
+
+@pytest.mark.parametrize("D,H,Hkv,S,T", [(128, 4, 2, 4, 4), (256, 4, 2, 4, 4), (512, 8, 1, 3, 9), (64, 6, 3, 5, 37), (4, 2, 2, 1, 3)])
+def test_gqa_f32_head_sizes_against_oracle(er, oracle, D, H, Hkv, S, T):
+    """gqaHeadDim128AndWideDimensionsMatchCPUReference (GQATests.swift:326-363) and ragged shapes, seeded N(0,1)."""
+    rng = rng_for(900 + D)
+    q = rng.standard_normal((S, H, D), dtype=np.float32)
+    k = rng.standard_normal((T, Hkv, D), dtype=np.float32)
+    v = rng.standard_normal((T, Hkv, D), dtype=np.float32)
+    gk = er.GQAKernel()
+    for causal, off in ((True, T - S), (False, 0)):
+        want = oracle.gqa_f32(q, k, v, causal=causal, q_offset=off)
+        got = gk.execute(q, k, v, S, D, H, Hkv, causal, kv_seq_len=T, q_offset=off).reshape(want.shape)
+        assert max_rel_err(got, want) < TOL, (D, causal)
+        assert np.abs(got - want).max() < 1e-4
+
+
+def test_float32_cache_attention_and_step(er, torch, oracle):
+    """Decode over a float32 cache: host appends (KVCache.append), then device steps with RoPE; oracle = cpuGQA over the
+    retrieved rows with the query rotated by the oracle's RoPE."""
+    rng = rng_for(41)
+    L, B, H, Hkv, D, T = 2, 2, 8, 4, 128, 37
+    theta = 1.0e6
+    c = er.KVCache(64, L, Hkv, D, er.Precision.float32, max_batch=B)
+    sp = er.step_params(rope_theta=theta)
+    ks = rng.standard_normal((L, B, T, Hkv, D), dtype=np.float32)
+    vs = rng.standard_normal((L, B, T, Hkv, D), dtype=np.float32)
+    for l in range(L):
+        for b in range(B):
+            c.write_rows(l, b, 0, T, dev(torch, ks[l, b]), dev(torch, vs[l, b]), sp)
+    q = rng.standard_normal((L, B, H, D), dtype=np.float32)
+    kn = rng.standard_normal((L, B, Hkv, D), dtype=np.float32)
+    vn = rng.standard_normal((L, B, Hkv, D), dtype=np.float32)
+    out = torch.full((L, B, H, D), float("nan"), device="cuda")
+    c.decode_step(dev(torch, q), dev(torch, kn), dev(torch, vn), out, H, sp)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert c.total_written(0, 0) == T + 1 and c.total_written(1, 1) == T + 1
+    for l in range(L):
+        for b in range(B):
+            kc, vc = c.retrieve(l, np.float32, seq=b)
+            kc, vc = kc.reshape(T + 1, Hkv, D), vc.reshape(T + 1, Hkv, D)
+            # rows in the cache are the oracle's RoPE of the inputs, bit for bit
+            want_k = np.concatenate([oracle.rope_neox(ks[l, b], 0, theta), oracle.rope_neox(kn[l, b][None], T, theta)])
+            assert np.array_equal(kc, want_k) and np.array_equal(vc[-1], vn[l, b])
+            qr = oracle.rope_neox(q[l, b][None], T, theta)
+            want = oracle.gqa_f32(qr, kc, vc, causal=False)[0]
+            assert max_rel_err(got[l, b], want) < TOL
+
+
+def test_paged_rows_without_a_page_are_refused_or_dropped(er, torch):
+    L, B, Hkv, D, PS = 1, 2, 2, 128, 16
+    rng = rng_for(5)
+    sp = er.step_params(rope_theta=1e4)
+    c = er.KVCache(64, L, Hkv, D, er.Precision.float16, max_batch=B, layout=er.Layout.paged, page_size=PS, num_pages=6)
+    c.set_block_table(0, [0, 3])          # sequence 0 owns 32 rows; pool page 0 is ITS first page
+    c.set_block_table(1, [5])             # sequence 1 owns 16 rows
+    k0 = dev(torch, normal_f16(rng, (32, Hkv, D)))
+    v0 = dev(torch, normal_f16(rng, (32, Hkv, D)))
+    c.write_rows(0, 0, 0, 32, k0, v0, sp)
+    c.write_rows(0, 1, 0, 16, k0[:16], v0[:16], sp)
+    torch.cuda.synchronize()
+
+    def snapshot():
+        c.set_position(32, seq=0)
+        c.set_position(16, seq=1)
+        return [np.concatenate(c.retrieve(0, np.float16, seq=b)).view(np.uint16).copy() for b in range(B)]
+
+    before = snapshot()
+    # host side: refused before any launch
+    launches = er.lib().er_kernel_launch_count()
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        c.write_rows(0, 1, 16, 4, k0[:4], v0[:4], sp)
+    assert e.value.name == "outOfPages" and er.lib().er_kernel_launch_count() == launches
+    # device side: sequence 1 is full (16 rows, one page); a decode step appends row 16 -> no page -> dropped + flagged
+    H = 4
+    q = dev(torch, normal_f16(rng, (L, B, H, D)))
+    kn = dev(torch, normal_f16(rng, (L, B, Hkv, D)))
+    vn = dev(torch, normal_f16(rng, (L, B, Hkv, D)))
+    out = torch.zeros((L, B, H, D), device="cuda")
+    c.set_position(31, seq=0)             # sequence 0 appends into its own second page (slot 31): legal
+    c.decode_step(q, kn, vn, out, H, sp)
+    torch.cuda.synchronize()
+    assert c.device_status() == -10        # ER_ERR_OUT_OF_PAGES
+    c.clear_device_status()
+    after = snapshot()
+    assert c.device_status() == 0
+    # sequence 1 (whose row was dropped) is unchanged; sequence 0 -- the owner of pool page 0, where a table entry of 0
+    # would have sent the dropped row -- changed in its own slot 31 only (K half and V half of the concatenation)
+    assert np.array_equal(before[1], after[1])
+    diff = np.nonzero(before[0] != after[0])[0]
+    half, row = 32 * Hkv * D, Hkv * D
+    assert diff.size > 0 and np.all((diff % half) // row == 31)
+    c.set_position(31, seq=0)
+    c.set_position(16, seq=1)
+    hq = q.cpu().numpy()
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:    # the host-buffer step reports it by itself
+        c.decode_step_host(hq, kn.cpu().numpy(), vn.cpu().numpy(), np.empty_like(hq), H, sp)
+    assert e.value.name == "outOfPages"
+    c.clear_device_status()
+
+
+def test_raw_operators_refuse_misaligned_pointers(er, torch):
+    gk = er.GQAKernel()
+    H, Hkv, T = 4, 2, 40
+    q = torch.zeros(H * 128 + 8, device="cuda")
+    kv = torch.zeros(T * Hkv * 128 + 8, dtype=torch.float16, device="cuda")
+    out = torch.zeros(H * 128 + 8, device="cuda")
+    launches = er.lib().er_kernel_launch_count()
+    for bad in ("q", "k", "out"):
+        ptrs = dict(q=q.data_ptr(), k=kv.data_ptr(), v=kv.data_ptr(), out=out.data_ptr())
+        ptrs[bad] += 4
+        for fn in (gk.encode, gk.encode_static_workspace):
+            with pytest.raises(er.EdgeRunnerCUDAError) as e:
+                fn(ptrs["q"], ptrs["k"], ptrs["v"], ptrs["out"], 1, 128, H, Hkv, True, kv_seq_len=T, q_offset=T - 1)
+            assert e.value.name == "invalidArgument" and "16-byte" in str(e.value)
+    assert er.lib().er_kernel_launch_count() == launches          # nothing was launched
+
+
+def test_cache_refuses_another_device(er, torch):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with torch.cuda.device(0):
+        c = er.KVCache(32, 1, 2, 128, er.Precision.float16)
+        k = torch.zeros((1, 1, 2, 128), device="cuda")
+    sp = er.step_params()
+    launches = er.lib().er_kernel_launch_count()
+    with torch.cuda.device(1):
+        with pytest.raises(er.EdgeRunnerCUDAError) as e:
+            c.append_rope_kv(k, k, sp)
+        assert e.value.name == "invalidArgument" and "device" in str(e.value)
+    assert er.lib().er_kernel_launch_count() == launches
+
+
+@pytest.mark.parametrize("precision", ["float16", "turboquant", "q8_0"])
+def test_bounded_wait_runs_out_and_reports(er, torch, oracle, precision):
+    rng = rng_for(123)
+    L, B, H, Hkv, D, T = 1, 1, 4, 2, 128, 200
+    kw = dict(max_batch=B)
+    if precision == "turboquant":
+        c = er.KVCache(256, L, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=3, **kw)
+    else:
+        c = er.KVCache(256, L, Hkv, D, getattr(er.Precision, precision), **kw)
+    sp = er.step_params(rope_theta=1e4)
+    k = dev(torch, normal_f16(rng, (T, Hkv, D)))
+    v = dev(torch, normal_f16(rng, (T, Hkv, D)))
+    c.write_rows(0, 0, 0, T, k, v, sp)
+    q = dev(torch, normal_f16(rng, (L, B, H, D)))
+    out = torch.zeros((L, B, H, D), device="cuda")
+    c.attention_decode(q, out, H, sp)
+    torch.cuda.synchronize()
+    good = out.cpu().numpy().copy()
+    assert c.device_status() == 0
+    c.debug_wait_probe(wait_limit_us=300, withhold_tiles=True)
+    c.attention_decode(q, out, H, sp)         # the tiles never arrive: every wait gives up after 300 us
+    torch.cuda.synchronize()                  # the launch returns by itself
+    assert c.device_status() == -12           # ER_ERR_DEVICE_TIMEOUT
+    c.debug_wait_probe(0, False)
+    c.clear_device_status()
+    out.zero_()
+    c.attention_decode(q, out, H, sp)         # the context, the cache and its counters are still good
+    torch.cuda.synchronize()
+    assert c.device_status() == 0
+    assert np.array_equal(out.cpu().numpy(), good)
