@@ -96,6 +96,12 @@ SYMBOLS = {
     "er_kv_decode_step_host": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _stp, _vp]),
     "er_kv_advance": (_i32, [_vp, _u32, _u32, _u32, _vp]),
     "er_kv_write_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _stp, _vp]),
+    "er_kv_set_output_sharding": (_i32, [_vp, _u32, _u32, C.POINTER(_vp), _u32]),
+    "er_relayout_head_shards": (_i32, [_vp, _vp, _u32, _u32, _u32, _vp]),
+    "er_peer_buffer_create": (_i32, [_sz, C.POINTER(_vp), _vp]),
+    "er_peer_buffer_open": (_i32, [_vp, C.POINTER(_vp)]),
+    "er_peer_buffer_close": (_i32, [_vp]),
+    "er_peer_buffer_destroy": (_i32, [_vp]),
     "er_kernel_launch_count": (C.c_uint64, []),
     "er_kv_device_status": (_i32, [_vp]),
     "er_kv_clear_device_status": (_i32, [_vp]),

@@ -215,6 +215,22 @@ __global__ void gather_host_inputs_kernel(const float4* q, const float4* k, cons
     }
 }
 
+// After an all-gather of kv-head shards: gathered [world][pairs][local_heads][128] -> full [pairs][world * local_heads][128]
+// (pair = (layer, sequence); rank r's heads land at head offset r * local_heads).  16-byte elements.
+__global__ void relayout_head_shards_kernel(const float4* __restrict__ gathered, float4* __restrict__ full, uint32_t world,
+                                            uint32_t pairs, uint32_t local_heads) {
+    constexpr uint32_t kVec = kHeadDim / 4;
+    const uint64_t per_rank = static_cast<uint64_t>(pairs) * local_heads * kVec;
+    const uint64_t total = per_rank * world;
+    for (uint64_t e = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t r = static_cast<uint32_t>(e / per_rank);
+        const uint64_t rem = e % per_rank;
+        const uint64_t pair = rem / (local_heads * kVec);
+        const uint32_t hv = static_cast<uint32_t>(rem % (local_heads * kVec));
+        full[(pair * world + r) * local_heads * kVec + hv] = gathered[e];
+    }
+}
+
 __global__ void add_lengths_kernel(int32_t* lengths, int begin, int count, int delta) {
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x)
         lengths[begin + e] += delta;

@@ -188,6 +188,10 @@ struct er_kv {
     size_t head_norm_floats[2] = {0, 0};
     float cached_theta = 0.f;
     InvFreqTable inv_freq{};
+    uint32_t out_heads_total = 0;            // er_kv_set_output_sharding: 0 = outputs are [layers][batch][num_heads][128]
+    uint32_t out_head_offset = 0;
+    uint32_t num_peers = 0;
+    float* peer_out[7] = {};
     uint32_t probe_wait_limit_us = 0;        // er_kv_debug_wait_probe: patience of the next decode launches' waits
     int probe_withhold_tiles = 0;
     int* h_status = nullptr;                 // pinned host word: er_kv_decode_step_host copies the device status here
@@ -1153,6 +1157,15 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         int32_t rc;
         DecodeParams p{};
         p.q = q + off; p.out = out + off;
+        if (kv->out_heads_total > 0) {   // kv-head sharding: rows of out_heads_total heads, this cache's heads at an offset
+            if (kv->out_head_offset + num_heads > kv->out_heads_total)
+                return fail(ER_ERR_SHAPE, "output sharding: heads [%u, %u) exceed %u", kv->out_head_offset, kv->out_head_offset + num_heads, kv->out_heads_total);
+            const size_t out_off = static_cast<size_t>(l0 - lb) * kv->cfg.max_batch * kv->out_heads_total * kHeadDim;
+            p.out = out + out_off;
+            p.out_heads_total = static_cast<int>(kv->out_heads_total); p.out_head_offset = static_cast<int>(kv->out_head_offset);
+            p.num_peers = static_cast<int>(kv->num_peers);
+            for (uint32_t r = 0; r < kv->num_peers; ++r) p.peer_out[r] = kv->peer_out[r] + out_off;
+        }
         p.k_base = kv->k_slab; p.v_base = kv->v_slab;
         p.k_layer_stride_bytes = kv->k_layer_stride; p.v_layer_stride_bytes = kv->v_layer_stride;
         p.kn_base = kv->kn_slab; p.vn_base = kv->vn_slab; p.n_layer_stride_bytes = kv->n_layer_stride;
@@ -1442,6 +1455,64 @@ int32_t er_kv_device_status(er_kv* kv) {
     int status = 0;
     ER_CUDA(cudaMemcpy(&status, kv->d_counters + 1, sizeof(int), cudaMemcpyDeviceToHost));
     return device_status_to_code(status);
+}
+
+int32_t er_kv_set_output_sharding(er_kv* kv, uint32_t heads_total, uint32_t head_offset, float* const* peer_outputs, uint32_t num_peers) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    if (num_peers > 7 || (num_peers > 0 && (!peer_outputs || heads_total == 0))) return fail(ER_ERR_INVALID_ARGUMENT, "at most 7 peers, and peers need heads_total > 0");
+    if (kv->cfg.precision == ER_KV_FLOAT32 && heads_total > 0) return fail(ER_ERR_UNSUPPORTED, "output sharding is built for the flash-decode kernels (fp16, q8_0, TurboQuant rows)");
+    for (uint32_t r = 0; r < num_peers; ++r)
+        if (!peer_outputs[r] || (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u)) return fail(ER_ERR_INVALID_ARGUMENT, "peer output %u is null or not 16-byte aligned", r);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    kv->out_heads_total = heads_total; kv->out_head_offset = heads_total ? head_offset : 0; kv->num_peers = heads_total ? num_peers : 0;
+    for (uint32_t r = 0; r < 7; ++r) kv->peer_out[r] = r < kv->num_peers ? peer_outputs[r] : nullptr;
+    return ER_OK;
+}
+
+// ---- device buffers other processes on this node can map (CUDA IPC) ----
+
+int32_t er_peer_buffer_create(size_t bytes, void** device_ptr, uint8_t* handle_out) {
+    if (!device_ptr || !handle_out || bytes == 0) return fail(ER_ERR_INVALID_ARGUMENT, "null argument or zero size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return fail(ER_ERR_ALLOCATION_FAILED, "peer buffer of %zu bytes", bytes); }
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); cudaGetLastError(); return fail(ER_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e)); }
+    ER_CUDA(cudaMemset(p, 0, bytes));
+    std::memcpy(handle_out, &h, sizeof(h));
+    *device_ptr = p;
+    return ER_OK;
+}
+
+int32_t er_peer_buffer_open(const uint8_t* handle, void** device_ptr) {
+    if (!handle || !device_ptr) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    const cudaError_t e = cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(ER_ERR_CUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e)); }
+    return ER_OK;
+}
+
+int32_t er_peer_buffer_close(void* opened_ptr) {
+    if (!opened_ptr) return ER_OK;
+    ER_CUDA(cudaIpcCloseMemHandle(opened_ptr));
+    return ER_OK;
+}
+
+int32_t er_peer_buffer_destroy(void* device_ptr) {
+    if (!device_ptr) return ER_OK;
+    ER_CUDA(cudaFree(device_ptr));
+    return ER_OK;
+}
+
+int32_t er_relayout_head_shards(const float* gathered, float* full, uint32_t world, uint32_t pairs, uint32_t local_heads, void* stream) {
+    if (!gathered || !full) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    const uint64_t vec = static_cast<uint64_t>(world) * pairs * local_heads * (kHeadDim / 4);
+    if (vec == 0) return ER_OK;
+    relayout_head_shards_kernel<<<static_cast<unsigned>(std::min<uint64_t>((vec + 255) / 256, 148 * 16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(gathered), reinterpret_cast<float4*>(full), world, pairs, local_heads);
+    return check_launch("relayout_head_shards_kernel");
 }
 
 int32_t er_kv_debug_wait_probe(er_kv* kv, uint32_t wait_limit_us, int withhold_tiles) {

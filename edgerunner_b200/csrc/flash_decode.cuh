@@ -65,6 +65,14 @@ struct DecodeParams {
     // walks its whole control flow with the abort flag set and the status word reads kStatusTimeout (outputs undefined).
     uint32_t wait_limit_us;
     int withhold_tiles;
+    // kv-head sharding across GPUs: this launch computes num_q_heads of out_heads_total query heads (0 = not sharded) and
+    // writes its rows at head offset out_head_offset of a [pair][out_heads_total][128] buffer -- its own (`out`) and the
+    // same buffer on num_peers other GPUs (peer_out: their mapped addresses), so that every GPU ends the step holding all
+    // heads without a separate all-gather.  Plain stores to peer memory; nothing is ever read from a peer.
+    int out_heads_total;
+    int out_head_offset;
+    int num_peers;
+    float* peer_out[7];
     float scale_log2;             // softmax scale * log2(e)
     float rope_scaling;
     int apply_rope;
@@ -456,7 +464,7 @@ struct DensePolicy {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
 
-    __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
+    __device__ static void store_out(const DecodeParams&, int64_t, const float*, int, int) {}
 };
 
 // ------------------------------------------------------------------------------------------ the kernel
@@ -544,11 +552,15 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     int active = static_cast<int>(min(static_cast<int64_t>(gridDim.x), (total_units + UPT - 1) / UPT));
     const int cta = blockIdx.x;
 
+    const int out_heads = p.out_heads_total > 0 ? p.out_heads_total : p.num_q_heads;   // heads per row of the output buffer
     // Sequences without any row produce a zero output row (invSum = 0 rule, Shaders/GQA.metal:379).
     for (int j = cta; j < num_pairs; j += gridDim.x) {
         if (prefix[j + 1] == prefix[j]) {
-            float* o = p.out + static_cast<int64_t>(j) * p.num_q_heads * kHeadDim;
-            for (int e = tid; e < p.num_q_heads * kHeadDim; e += blockDim.x) o[e] = 0.f;
+            const int64_t off = (static_cast<int64_t>(j) * out_heads + p.out_head_offset) * kHeadDim;
+            for (int e = tid; e < p.num_q_heads * kHeadDim; e += blockDim.x) {
+                p.out[off + e] = 0.f;
+                for (int r = 0; r < p.num_peers; ++r) p.peer_out[r][off + e] = 0.f;
+            }
         }
     }
 
@@ -644,9 +656,15 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 consumer_sync<NW * 32>();
                 const bool sole = (sg.u0 == 0 && sg.u1 == sg.units);
                 const int item = sg.pair * hkv + sg.head;
-                float* out_item = p.out + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
+                const int64_t out_off = (static_cast<int64_t>(sg.pair) * out_heads + p.out_head_offset + sg.head * GROUP) * kHeadDim;
+                float* out_item = p.out + out_off;
                 // Outputs of the rotated (TurboQuant) space pass through shared memory for the inverse transform.
                 float* fin = POL::kRotated ? reinterpret_cast<float*>(extra + POL::kOffFin) : out_item;
+                auto emit = [&](int idx, float val) {   // a finished output element: local buffer (or staging) + the peers' copies
+                    fin[idx] = val;
+                    if (!POL::kRotated)
+                        for (int r = 0; r < p.num_peers; ++r) p.peer_out[r][out_off + idx] = val;
+                };
                 const int slot = (range_begin > sg.item_unit0) ? 0 : 1;
                 float* my_scratch = p.scratch + (static_cast<int64_t>(cta) * 2 + slot) * GROUP * 130;
                 for (int idx = tid; idx < GROUP * kHeadDim; idx += NW * 32) {
@@ -662,7 +680,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                         A = fmaf(merge_acc[(w * GROUP + g) * kHeadDim + d], wgt, A);
                     }
                     if (sole) {
-                        fin[idx] = Lsum > 0.f ? A / Lsum : 0.f;
+                        emit(idx, Lsum > 0.f ? A / Lsum : 0.f);
                     } else {
                         if (d == 0) {
                             my_scratch[g * 130] = M;
@@ -707,14 +725,14 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                                 Lsum = fmaf(__ldcg(sc + 1), wgt, Lsum);
                                 A = fmaf(__ldcg(sc + 2 + d), wgt, A);
                             }
-                            fin[idx] = Lsum > 0.f ? A / Lsum : 0.f;
+                            emit(idx, Lsum > 0.f ? A / Lsum : 0.f);
                         }
                         if (tid == 0) p.item_counters[item] = 0;
                     }
                 }
                 if (POL::kRotated && wrote) {   // CTA-uniform condition
                     consumer_sync<NW * 32>();
-                    POL::store_out(out_item, fin, warp, lane);
+                    POL::store_out(p, out_off, fin, warp, lane);
                 }
                 cur += sg.u1 - sg.u0;
             }

@@ -91,7 +91,7 @@ struct Q8MmaPolicy {
     __device__ static void init_extra(uint8_t*, int) {}
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
                                          const float2*, int) {}
-    __device__ static void store_out(float* out_item, const float*, int, int) { (void)out_item; }
+    __device__ static void store_out(const DecodeParams&, int64_t, const float*, int, int) {}
 
     template <class WAIT>
     __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,

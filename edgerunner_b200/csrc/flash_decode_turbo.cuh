@@ -93,12 +93,15 @@ struct TurboStaging {
         return fp16 ? __half2float(reinterpret_cast<const __half*>(base)[idx]) : reinterpret_cast<const float*>(base)[idx];
     }
 
-    __device__ static void store_out(float* out_item, const float* fin, int warp, int lane) {
+    __device__ static void store_out(const DecodeParams& p, int64_t out_off, const float* fin, int warp, int lane) {
         if (warp < GROUP) {
             const float4 t = *reinterpret_cast<const float4*>(fin + warp * kHeadDim + 4 * lane);
             float a[4] = {t.x, t.y, t.z, t.w};
             warp_tq_inverse(a, lane);
-            *reinterpret_cast<float4*>(out_item + warp * kHeadDim + 4 * lane) = make_float4(a[0], a[1], a[2], a[3]);
+            const float4 o = make_float4(a[0], a[1], a[2], a[3]);
+            const int64_t e = out_off + warp * kHeadDim + 4 * lane;
+            *reinterpret_cast<float4*>(p.out + e) = o;
+            for (int r = 0; r < p.num_peers; ++r) *reinterpret_cast<float4*>(p.peer_out[r] + e) = o;   // kv-head sharding
         }
     }
 };

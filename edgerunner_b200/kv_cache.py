@@ -262,6 +262,12 @@ class KVCache:
         """0, or the negative status a kernel of this cache left behind (ER_ERR_DEVICE_TIMEOUT, ER_ERR_OUT_OF_PAGES)."""
         return lib().er_kv_device_status(self._h)
 
+    def set_output_sharding(self, heads_total, head_offset, peer_outputs=()):
+        """kv-head sharding (er_kv_set_output_sharding): decode launches write their rows at head offset `head_offset` of
+        [layers, batch, heads_total, 128] buffers -- the call's `out` and the raw peer addresses in `peer_outputs`."""
+        arr = (C.c_void_p * max(len(peer_outputs), 1))(*[int(p) for p in peer_outputs])
+        check(lib().er_kv_set_output_sharding(self._h, heads_total, head_offset, arr, len(peer_outputs)))
+
     def clear_device_status(self):
         check(lib().er_kv_clear_device_status(self._h))
 

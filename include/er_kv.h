@@ -347,6 +347,29 @@ int32_t er_kv_advance(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, uint3
 int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start, uint32_t count, const float* k,
                          const float* v, const er_step_params* params, void* stream);
 
+/* ---- kv-head sharding across the GPUs of one node (no counterpart in the reference, which is single-device) ----
+ * Rank r of G holds kv heads [r * Hkv / G, (r + 1) * Hkv / G) in its own er_kv cache and the query heads that attend to
+ * them.  Attention needs no reduction across ranks, only the concatenation of the per-head outputs; two ways to get it:
+ *
+ * (1) Fused: er_kv_set_output_sharding makes every decode launch of the cache write its finished rows straight into a
+ *     [layers][batch][heads_total][128] buffer at head offset `head_offset` -- the `out` argument of the call -- and into
+ *     the same buffer of up to 7 peer GPUs (`peer_outputs`: addresses obtained with er_peer_buffer_open), with ordinary
+ *     stores from the kernel's merge epilogue.  When every rank's launch has completed (order that with any barrier,
+ *     e.g. a 4-byte all-reduce enqueued behind the step) each GPU holds all heads.  Nothing is read from a peer.
+ *     heads_total == 0 turns it off.
+ * (2) Library collective: each rank computes its [layers][batch][local_heads][128] slice, an all-gather (NCCL) yields
+ *     [world][layers][batch][local_heads][128], and er_relayout_head_shards turns that into
+ *     [layers][batch][world * local_heads][128] (pairs = layers * batch). */
+int32_t er_kv_set_output_sharding(er_kv* kv, uint32_t heads_total, uint32_t head_offset, float* const* peer_outputs, uint32_t num_peers);
+int32_t er_relayout_head_shards(const float* gathered, float* full, uint32_t world, uint32_t pairs, uint32_t local_heads, void* stream);
+/* Device buffers another process of this node can map (CUDA IPC): create one here (zero-filled) and hand the 64-byte
+ * handle to the peers (any channel); a peer maps it with er_peer_buffer_open (which also enables peer access between the
+ * two GPUs) and unmaps it with er_peer_buffer_close before the owner calls er_peer_buffer_destroy. */
+int32_t er_peer_buffer_create(size_t bytes, void** device_ptr, uint8_t* handle_out /* 64 bytes */);
+int32_t er_peer_buffer_open(const uint8_t* handle /* 64 bytes */, void** device_ptr);
+int32_t er_peer_buffer_close(void* opened_ptr);
+int32_t er_peer_buffer_destroy(void* device_ptr);
+
 /* Number of kernels this library has launched since load (all caches, this process). */
 uint64_t er_kernel_launch_count(void);
 /* Device status word of the cache (synchronises with the device): ER_OK, ER_ERR_DEVICE_TIMEOUT if a bounded wait inside a
