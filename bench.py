@@ -1,19 +1,27 @@
 #!/usr/bin/env python3
 """Benchmark of the decode-time KV path: append of RoPE'd K/V + GQA flash-decode attention.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg2|cfg3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--legs cfg1,cfg2]
 
 One "step" = one decode step of the whole model stack of the workload: every layer appends one token per sequence
-and runs attention over its cache.  Default workload (`cfg1`): 28-layer Qwen3-0.6B shape (16 q / 8 kv heads,
-head_dim 128), batch 1, fp16 cache, context 4096 growing by one token per step, synthetic seeded N(0,1) inputs.
+and runs attention over its cache.  Default workload (`cfg3`, the largest configuration that fits one GPU): 32-layer
+Llama-3.1-8B shape (32 q / 8 kv heads, head_dim 128), batch 64 with context lengths uniform in [1024, 16384], fp16 cache
+in 16-token pages behind a seeded random block table, synthetic seeded N(0,1) inputs.
 
-Prints ONE JSON line (rank 0).  `value` is device-timed throughput with inputs resident in HBM; `e2e` is the same
-metric through the host-buffer entry point (er_kv_decode_step_host) with H2D/D2H copies inside the timed region;
-`roofline` is the attention kernel's algorithmic bytes over its CUDA-event-timed duration against the measured
-copy bandwidth; `cpu_baseline` times the CPU restatement of the reference path on the host cores.
+Multi-GPU (`--gpus N`, launched by torchrun, one rank per GPU): the kv heads of that ONE workload are split over the
+ranks (strong scaling: `value` = the batch's tokens per second of the whole job).  Every rank ends each step holding the
+outputs of all heads as [layers, batch, heads, 128]: the decode kernel's merge epilogue stores its rows into every
+peer's buffer (CUDA IPC, plain stores) and a 4-byte all-reduce orders the step's completion (`--exchange p2p`, default),
+or an NCCL all-gather plus a re-layout kernel (`--exchange nccl`).  The exchange is inside the timed region; before
+timing, the exchanged tensor of a small case is checked bit for bit against the shards computed on the rank's own GPU.
 
-Multi-GPU (`--gpus N`, launched by torchrun, one rank per GPU): the path shards by sequence with no data-path
-collective -- every rank advances its own sequence(s) -- so scaling is weak and `value` sums all ranks.
+Prints ONE JSON line (rank 0).  `value` is device-timed (CUDA events, max over ranks, median of `--repeats` timed
+regions of K steps) with inputs resident in HBM; `e2e` is the same metric with this step's q/k/v copied from pinned host
+memory and the result copied back inside the timed region (er_kv_decode_step_host on one GPU); `roofline` is the
+attention kernel's algorithmic bytes over its CUDA-event-timed duration against the measured copy bandwidth;
+`cpu_baseline` times the CPU restatement of the reference path on the host cores; `legs` (one GPU only) carries the same
+figures for the other single-GPU configurations (cfg1: 28 layers, batch 1, context 4096; cfg2: TurboQuant K4/V3, batch 8,
+context 32768).
 
 `--impl reference` times the reference's own CPU implementation of the path (its Swift sources cannot be built
 here, so this is the C restatement under oracle/) with all host threads, on the same workload.
@@ -35,7 +43,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode_kv_append_attention_tokens_per_s"
 WORKLOADS = {
-    # BASELINE.json configs[1]: the configuration the metric is quoted on
+    # BASELINE.json configs[1]
     "cfg1": dict(name="cfg1: Qwen3-0.6B shape, 28 layers, batch 1, fp16 KV, context 4096, 1 token appended per step",
                  layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="head_major", theta=1.0e6),
     "cfg1_token_major": dict(name="cfg1 with the reference's token-major [slot][kvHead][dim] ring layout",
@@ -60,13 +68,19 @@ WORKLOADS = {
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",
                          layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3,
                          norm="float16", layout="head_major", theta=1.0e6, outliers=True),
-    # BASELINE.json configs[3] (single-GPU form: all kv heads on one GPU)
+    # BASELINE.json configs[3]: the largest configuration that fits one GPU (73 GB of cache) -- the default workload
     "cfg3": dict(name="cfg3: Llama-3.1-8B shape, 32 layers, batch 64, fp16 KV in 16-token pages, context U[1024,16384]",
                  layers=32, batch=64, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
                  page_size=16, theta=5.0e5),
     "cfg3_contiguous": dict(name="cfg3 heads (32 q / 8 kv) on contiguous head-major rows, 8 layers, batch 8, context 32768 "
                                  "(separates the page gather from the kernel; not a BASELINE configuration)",
                             layers=8, batch=8, heads=32, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=5.0e5),
+    # BASELINE.json configs[4], decode leg on one GPU: 2 of the 16 sequences with all heads (an 8-GPU run gives each pair of
+    # GPUs 4 sequences and each GPU half of the heads: the same 10 GB of codes per GPU)
+    "cfg4_decode_slice": dict(name="cfg4 decode, one GPU's share: Qwen3-4B shape, 36 layers, 2 of the 16 sequences at context 131072, "
+                                   "TurboQuant turbo4 K / turbo4 V, fp16 norms, 64-token pages",
+                              layers=36, batch=2, heads=32, kv_heads=8, ctx=131072, precision="turboquant", kbits=4, vbits=4,
+                              norm="float16", layout="paged", page_size=64, theta=1.0e6),
     # BASELINE.json configs[4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
     # already in the cache (Qwen3-4B heads, TurboQuant turbo4/turbo4 rows in 64-token pages); tensor-core bound
     "cfg4_prefill": dict(name="cfg4 prefill chunk: Qwen3-4B heads, 2048 query rows at the end of a 131072-token context, "
@@ -78,22 +92,29 @@ WORKLOADS = {
                              page_size=64, theta=1.0e6),
 }
 D = 128
+DEFAULT_WORKLOAD = "cfg3"
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
-    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--legs", default=None,
+                    help="comma-separated extra single-GPU workloads reported under `legs` (default: cfg1,cfg2 with the default "
+                         "workload on one GPU, none otherwise; '' = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-device-leg", action="store_true",
                     help="run only the device-resident timed leg (short runs under a profiler)")
-    ap.add_argument("--shard", default="sequence", choices=["sequence", "heads"],
-                    help="N > 1: 'sequence' = one replica of the workload per GPU (weak scaling, no collective); 'heads' = the kv "
-                         "heads of the one workload split over the GPUs, outputs exchanged by an NCCL all-gather per step (strong "
-                         "scaling; device leg only)")
+    ap.add_argument("--shard", default="heads", choices=["sequence", "heads"],
+                    help="N > 1: 'heads' = the kv heads of the one workload split over the GPUs, every GPU ends a step with all "
+                         "heads' outputs (strong scaling); 'sequence' = one replica of the workload per GPU, no exchange (weak scaling)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="--shard heads: 'p2p' = peer stores from the decode kernel's epilogue + a 4-byte all-reduce; 'nccl' = "
+                         "all-gather + re-layout kernel")
     ap.add_argument("--cta-timeline", action="store_true",
                     help="with --only-device-leg: one extra step with the kernel's per-CTA phase stamps (er_kv_set_trace), reported "
                          "as cta_timeline_us = [min, median, max] over the CTAs, microseconds after the first CTA started")
@@ -112,9 +133,16 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch from the committed ncu capture of the same
-# workload (profiles/flash_decode_dense_g2_cfg1.md); None where no capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"cfg1": 471218688 + 4663040}
+# DRAM traffic of one attention launch relative to its algorithmic bytes, from the committed ncu captures
+# (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launch): the captures are
+# taken on a slice of the workload (a few GB on the device) and traffic grows in proportion to the rows processed, so
+# the full launch's traffic is the ratio times its algorithmic bytes.
+NCU_TRAFFIC_RATIO = {
+    "float16/group2": (475.9 / 475.8, "profiles/flash_decode_dense_g2_cfg1.md (cfg1, full launch)"),
+    "float16/group4": ((2252.2 + 5.4) / (2250.7 + 1.0 + 5.4), "profiles/flash_decode_dense_mma_g4_cfg3.md (cfg3, 4 of 32 layers, 16 of 64 sequences)"),
+    "turboquant/group2": ((973.9 + 10.0) / (973.1 + 0.5 + 10.0), "profiles/flash_decode_turbo_mma_cfg2.md (cfg2, 4 of 28 layers)"),
+    "q8_0/group2": ((2282.5 + 7.2) / (2281.7 + 7.2), "profiles/flash_decode_q8_g2.md (batch 8, context 32768, 4 of 28 layers)"),
+}
 
 
 def row_bytes(w):
@@ -214,8 +242,15 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
     rng = np.random.Generator(np.random.PCG64(7))
     turbo = w["precision"] == "turboquant"
     q8 = w["precision"] == "q8_0"
-    max_len = max(lens) + 64
+    pad = 96 + (steps or 0) + warmup      # rows the timed steps append
+    max_len = max(lens) + pad
     # one layer's cache per sampled layer; lengths as in the workload
+    base16 = rng.standard_normal(1 << 22, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+    def rows16(shape):
+        """fp16 N(0,1) rows: a 4M-element seeded block repeated (the values do not change the work done)."""
+        return np.resize(base16, int(np.prod(shape))).reshape(shape)
+
     def make_layer():
         if turbo:
             kw, vw = (D * w["kbits"] + 31) // 32, (D * w["vbits"] + 31) // 32
@@ -226,8 +261,7 @@ def cpu_reference_leg(w, lens, budget_s, steps=None, warmup=1):
         if q8:
             return [dict(k=rng.integers(0, 256, size=(max_len, Hkv, 136), dtype=np.uint8),
                          v=rng.integers(0, 256, size=(max_len, Hkv, 136), dtype=np.uint8)) for _ in range(B)]
-        return [dict(k=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16),
-                     v=rng.standard_normal((max_len, Hkv, D), dtype=np.float32).astype(np.float16).view(np.uint16)) for _ in range(B)]
+        return [dict(k=rows16((lens[b] + pad, Hkv, D)), v=rows16((lens[b] + pad, Hkv, D))) for b in range(B)]
 
     def one_layer_step(layer, s):
         for b in range(B):
@@ -277,9 +311,10 @@ def run_reference_impl(args, w, lens):
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], "implementation": "CPU restatement of the reference path (oracle/er_oracle.c), "
-                   "OpenMP over heads; the reference's Swift/Metal sources cannot be built in this environment"},
+        "scaling": "strong" if (args.shard == "heads" or args.gpus == 1) else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(w, lens, args.gpus, args.shard == "heads", args),
+        "implementation": "CPU restatement of the reference path (oracle/er_oracle.c), OpenMP over heads, on rank 0's host cores; the "
+                          "reference's Swift/Metal sources cannot be built in this environment",
         "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
         "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -339,261 +374,375 @@ def fill_cache(er, torch, cache, w, lens, sp, seed):
     torch.cuda.synchronize()
 
 
-def run_ours(args, w, lens):
-    import torch
-    import torch.distributed as dist
-    import edgerunner_b200 as er
-    from edgerunner_b200.sharding import max_over_ranks
+class Context:
+    """Process-wide handles of a GPU run: torch, torch.distributed, the package, rank layout, the launch stream."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus > 1 and world != args.gpus:
-        raise SystemExit("--gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, world))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        import edgerunner_b200 as er
+        self.torch, self.dist, self.er = torch, dist, er
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if args.gpus > 1 and self.world != args.gpus:
+            raise SystemExit("--gpus %d needs torchrun with %d ranks (WORLD_SIZE=%d)" % (args.gpus, args.gpus, self.world))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+        self.stream = torch.cuda.current_stream()
 
-    shard_heads = args.shard == "heads" and world > 1
-    if shard_heads:
-        # rank r owns kv heads [r * Hkv / N, (r + 1) * Hkv / N) and their q heads: its cache and its q/k/v hold only those
-        if w["kv_heads"] % world:
-            raise SystemExit("--shard heads needs kv_heads %% gpus == 0")
-        w = dict(w, heads=w["heads"] // world, kv_heads=w["kv_heads"] // world)
-        args.only_device_leg = True
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        from edgerunner_b200.sharding import max_over_ranks
+        return max_over_ranks(x, device="cuda")
+
+
+def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()):
+    """Times the decode step of one workload on this process's GPU (and, with shard_heads, its peers).  Returns the
+    figures of the JSON line as a dict; rank-local values are already reduced (max over ranks) where the contract says so."""
+    torch, dist, er = cx.torch, cx.dist, cx.er
+    from edgerunner_b200.sharding import HeadShardedDecoder
+    world, rank = (cx.world, cx.rank) if shard_heads or args.shard == "sequence" else (1, 0)
+    sharded = shard_heads and world > 1
+    w = dict(w_full, heads=w_full["heads"] // world, kv_heads=w_full["kv_heads"] // world) if sharded else dict(w_full)
+    if sharded and w_full["kv_heads"] % world:
+        raise SystemExit("--shard heads needs kv_heads %% gpus == 0")
     L, B, H, Hkv = w["layers"], len(lens), w["heads"], w["kv_heads"]
-    K, W = args.steps, max(args.warmup, 0)
+    Hfull = w_full["heads"]
     sp = er.step_params(rope_theta=w["theta"])
     cache = build_cache(er, torch, w, lens, K + W + 8)
     fill_cache(er, torch, cache, w, lens, sp, seed=1000 + rank)
-    base_positions = list(lens)
+    dec = HeadShardedDecoder(cache, L, B, Hfull, w_full["kv_heads"], world if sharded else 1, rank if sharded else 0,
+                             exchange=args.exchange) if shard_heads else None
+    stream = cx.stream
 
     def set_start():
-        for b, n in enumerate(base_positions):
+        for b, n in enumerate(lens):
             cache.set_position(n, seq=b)
 
     g = torch.Generator(device="cuda")
     g.manual_seed(5 + rank)
-    pool = min(K + W, 64)      # distinct per-step inputs, cycled (a step's cost does not depend on their values)
+    pool = min(K + W, 24 if L * B * H > 32768 else 64)   # distinct per-step inputs, cycled (a step's cost does not depend on their values)
     qs = torch.randn((pool, L, B, H, D), generator=g, device="cuda").half().float()
     ks = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
     vs = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
-    out = torch.empty((L, B, H, D), device="cuda", dtype=torch.float32)
-    gathered = torch.empty((world, L, B, H, D), device="cuda", dtype=torch.float32) if shard_heads else None
-    stream = torch.cuda.current_stream()
+    out = dec.full if dec is not None else torch.empty((L, B, H, D), device="cuda", dtype=torch.float32)
 
-    def exchange():
-        if shard_heads:      # every rank ends the step with all heads' outputs: [rank][L][B][H / N][128]
-            dist.all_gather_into_tensor(gathered, out)
+    def step(i, exchange=True):
+        if dec is not None:
+            dec.step(qs[i], ks[i], vs[i], sp, stream=stream, exchange=exchange)
+        else:
+            cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def timed_regions(n, exchange=True):
+        """n regions of K steps (after W warm-up steps each, positions rewound): per-region ms, max over ranks."""
+        ms, launches = [], None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(n):
+            set_start()
+            for s in range(W):
+                step(s % pool, exchange)
+            cx.barrier()
+            l0 = er.lib().er_kernel_launch_count()
+            e0.record(stream)
+            for s in range(K):
+                step((W + s) % pool, exchange)
+            e1.record(stream)
+            cx.barrier()
+            if launches is None:
+                launches = int(er.lib().er_kernel_launch_count() - l0)
+            ms.append(cx.max_over_ranks(e0.elapsed_time(e1)) if (sharded or args.shard == "sequence") else e0.elapsed_time(e1))
+        return ms, launches
 
-    # ---- leg 1: device-resident inputs, whole step through er_kv_decode_step ----
-    sampler = ClockSampler(local_rank)
+    # ---- leg 1: device-resident inputs, whole step (and the exchange) inside the timed region ----
+    sampler = ClockSampler(cx.local_rank)
     if rank == 0:
         sampler.start()
-    set_start()
-    for s in range(W):
-        cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
-        exchange()
-    barrier()
-    launches0 = er.lib().er_kernel_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for s in range(K):
-        i = (W + s) % pool
-        cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
-        exchange()
-    e1.record(stream)
-    barrier()
-    launches = er.lib().er_kernel_launch_count() - launches0
-    ms_total = max_over_ranks(e0.elapsed_time(e1), device="cuda")
-    # load window for the clock samples: the same steps again (positions rewound so the cache capacity holds)
+    regions, launches = timed_regions(repeats)
+    ms_region = statistics.median(regions)
+    for b, n in enumerate(lens):
+        assert cache.total_written(0, b) == n + W + K
+    compute_regions = None
+    if sharded:      # the same steps without the exchange (and without the peer stores): the rank's own compute
+        dec.set_peer_stores(False)
+        compute_regions, _ = timed_regions(max(3, repeats // 2 + 1), exchange=False)
+        dec.set_peer_stores(True)
+    # load window for the clock samples: the same steps again for about a second
     t_load = time.perf_counter()
-    while rank == 0 and time.perf_counter() - t_load < 1.5:
+    while rank == 0 and not sharded and time.perf_counter() - t_load < 1.0:
         set_start()
-        for s in range(min(K + W, 128)):
-            cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+        for s in range(min(K + W, 64)):
+            step(s % pool)
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
-    for b, n in enumerate(base_positions):      # restore the post-run state the checks below expect
-        cache.set_position(n + W + K, seq=b)
-    assert cache.device_status() == 0, "device-side wait timed out"
-    for b, n in enumerate(base_positions):
-        assert cache.total_written(0, b) == n + W + K
-    tokens = B * K * (1 if shard_heads else world)
-    value = tokens / (ms_total * 1e-3)
-    bytes_total = sum(step_bytes(w, lens, W + s) for s in range(K))
-    hbm_gbs = bytes_total / (ms_total * 1e-3) / 1e9       # per GPU
+    assert cache.device_status() == 0, "device status word is set (timeout / out of pages)"
+    replicas = cx.world if (args.shard == "sequence" and not shard_heads) else 1
+    tokens = B * K * replicas
+    value = tokens / (ms_region * 1e-3)
+    bytes_region = sum(step_bytes(w, lens, W + s) for s in range(K))        # this GPU's rows
+    ms_compute = statistics.median(compute_regions) if compute_regions else ms_region
+    hbm_gbs = bytes_region / (ms_compute * 1e-3) / 1e9
+    res = {"value": value, "ms_per_step": ms_region / K, "regions_ms": [round(x, 4) for x in regions], "gpu_launches": launches,
+           "hbm_gbs_per_gpu": round(hbm_gbs, 1), "clocks": clocks, "tokens_per_region": tokens}
+    if sharded:
+        res["exchange"] = {"kind": dec.exchange, "compute_only_ms_per_step": ms_compute / K,
+                           "share_of_step": round(max(0.0, 1.0 - ms_compute / ms_region), 4),
+                           "payload_bytes_per_gpu_per_step": L * B * H * D * 4 * (world - 1),
+                           "note": ("peer stores from the decode kernel's merge epilogue into every GPU's [layers, batch, heads, 128] buffer "
+                                    "+ one 4-byte NCCL all-reduce behind the launch" if dec.exchange == "p2p" else
+                                    "NCCL all-gather of [layers, batch, heads / N, 128] + re-layout kernel")}
+        if getattr(dec, "p2p_refused", None):
+            res["exchange"]["p2p_refused"] = dec.p2p_refused
 
     if args.only_device_leg:
-        timeline = None
         if args.cta_timeline and rank == 0:
             n_ctas = cache.set_trace(None, 0)
             stamps = torch.zeros(n_ctas, 8, dtype=torch.int64, device="cuda")
             cache.set_trace(stamps, n_ctas)
             set_start()
-            cache.decode_step(qs[0], ks[0], vs[0], out, H, sp, stream=stream)
+            step(0)
             torch.cuda.synchronize()
             cache.set_trace(None, 0)
             t = stamps.cpu().numpy().astype(np.float64)
             t = (t - t[:, 0].min()) / 1e3
             names = ["cta_start", "work_list_built", "first_tile_landed", "streaming_done", "before_exit_sync", "after_exit_sync", "cta_end"]
-            timeline = {nm: [round(float(f(t[:, i])), 2) for f in (np.min, np.median, np.max)] for i, nm in enumerate(names)}
-        if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-                              "ms_per_step": ms_total / K, "hbm_gbs_per_gpu": round(hbm_gbs, 1), "gpu_launches": int(launches),
-                              "scaling": "strong" if shard_heads else "weak",
-                              "config": {"workload": w["name"],
-                                         "sharding": ("kv heads split over the GPUs, NCCL all-gather of the outputs every step" if shard_heads
-                                                      else "by sequence, one replica per GPU, no collective") if world > 1 else "single GPU"},
-                              "note": "device leg only", **({"cta_timeline_us": timeline} if timeline else {})}))
-        if world > 1:
-            dist.destroy_process_group()
-        return
+            res["cta_timeline_us"] = {nm: [round(float(f(t[:, i])), 2) for f in (np.min, np.median, np.max)] for i, nm in enumerate(names)}
+        _close(dec, cache)
+        return res
 
-    # ---- leg 2: per-kernel durations (append / attention) with CUDA events, same steps, split entry points ----
-    set_start()
-    for s in range(W):
-        cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
-    torch.cuda.synchronize()
-    n_probe = min(K, 64)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_probe)]
-    for s in range(n_probe):
-        i = (W + s) % pool
-        evs[s][0].record(stream)
-        cache.append_rope_kv(ks[i], vs[i], sp, stream=stream)
-        evs[s][1].record(stream)
-        cache.attention_decode(qs[i], out, H, sp, pending=1, stream=stream)
-        evs[s][2].record(stream)
-        cache.advance(1, stream=stream)
-    torch.cuda.synchronize()
-    t_append = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
-    t_attn = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
-    attn_bytes = statistics.mean(step_bytes(w, lens, W + s) for s in range(n_probe)) - B * Hkv * row_bytes(w) * L
+    # ---- roofline of the attention kernel ----
     peak, peak_src = measured_peaks()
-    split_attn_ms = t_attn
-    fused_single_launch = int(launches) == K        # fp16 rows: the timed region is K launches of the one fused kernel
+    fused_single_launch = launches == K        # fp16 rows: the timed region is K launches of the one fused kernel
+    t_append = 0.0
     if fused_single_launch:
-        # the kernel's average launch duration is the timed region itself (events around the K launches of leg 1);
-        # the split-call figure above pays an event pair and a second launch per step
-        t_attn = ms_total / K
-        attn_bytes = bytes_total / K
+        t_attn, attn_bytes, timed_as = ms_compute / K, bytes_region / K, "the K launches of the timed region (append fused into the kernel)"
+        split_attn_ms = None
+    else:
+        # q8_0 / TurboQuant rows: append kernel + attention kernel; the attention launch between per-step events
+        set_start()
+        for s in range(W):
+            cache.decode_step(qs[s % pool], ks[s % pool], vs[s % pool], out, H, sp, stream=stream)
+        torch.cuda.synchronize()
+        n_probe = min(K, 64)
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_probe)]
+        for s in range(n_probe):
+            i = (W + s) % pool
+            evs[s][0].record(stream)
+            cache.append_rope_kv(ks[i], vs[i], sp, stream=stream)
+            evs[s][1].record(stream)
+            cache.attention_decode(qs[i], out, H, sp, pending=1, stream=stream)
+            evs[s][2].record(stream)
+            cache.advance(1, stream=stream)
+        torch.cuda.synchronize()
+        t_append = statistics.median(e[0].elapsed_time(e[1]) for e in evs)
+        t_attn = statistics.median(e[1].elapsed_time(e[2]) for e in evs)
+        attn_bytes = statistics.mean(step_bytes(w, lens, W + s) for s in range(n_probe)) - B * Hkv * row_bytes(w) * L
+        split_attn_ms, timed_as = t_attn, "attention launch between per-step CUDA events (split entry points), median"
     achieved = attn_bytes / (t_attn * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
-                "traffic_source": ("ncu capture summarised in profiles/flash_decode_dense_g2_cfg1.md, taken at context ~4100 where the "
-                                   "algorithmic bytes are 475.8 MB; the timed steps here run a few hundred tokens further")
-                if args.workload == "cfg1" else None,
-                "peak_source": peak_src,
-                "algorithmic_bytes_per_launch": int(attn_bytes), "launch_ms": round(t_attn, 5),
-                "append_kernel_ms": round(t_append, 5), "frac_of_8tbs": round(achieved / 8000.0, 4),
-                "timed_as": ("the K launches of the timed region (append fused into the kernel)" if fused_single_launch
-                             else "attention launch between per-step CUDA events (split entry points)"),
-                "split_call_attention_launch_ms": round(split_attn_ms, 5)}
+    ratio = NCU_TRAFFIC_RATIO.get("%s/group%d" % (w["precision"], H // Hkv))
+    res["roofline"] = {"bound": "hbm", "kernel": "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                       "frac": round(achieved / peak, 4),
+                       "traffic": int(attn_bytes * ratio[0]) if ratio else None,
+                       "traffic_source": ("algorithmic bytes x %.4f, the DRAM-traffic ratio of the ncu capture in %s" % ratio) if ratio else None,
+                       "peak_source": peak_src, "algorithmic_bytes_per_launch": int(attn_bytes), "launch_ms": round(t_attn, 5),
+                       "append_kernel_ms": round(t_append, 5), "frac_of_8tbs": round(achieved / 8000.0, 4), "timed_as": timed_as,
+                       "per_gpu": True}
+    if split_attn_ms is not None:
+        res["roofline"]["split_call_attention_launch_ms"] = round(split_attn_ms, 5)
 
-    # ---- leg 3: end to end through the host-buffer entry point (H2D q/k/v + D2H out every step) ----
-    hq = torch.empty((pool, L, B, H, D), dtype=torch.float32).pin_memory().copy_(qs.cpu())
-    hk = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(ks.cpu())
-    hv = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(vs.cpu())
-    hout = torch.empty((L, B, H, D), dtype=torch.float32).pin_memory()
-    set_start()
-    # raw addresses of the pinned buffers (the entry point takes plain pointers; slicing tensors per step would add tens of
-    # microseconds of interpreter time to an 84 us step) and a numpy view for reading the result on the host
-    hq_p = [hq[i].data_ptr() for i in range(pool)]
-    hk_p = [hk[i].data_ptr() for i in range(pool)]
-    hv_p = [hv[i].data_ptr() for i in range(pool)]
-    hout_p, hout_np, stream_p = hout.data_ptr(), hout.numpy(), stream.cuda_stream
-    for s in range(W):
-        cache.decode_step_host(hq_p[s % pool], hk_p[s % pool], hv_p[s % pool], hout_p, H, sp, stream=stream_p)
-    barrier()
-    e0.record(stream)
-    t0 = time.perf_counter()
-    checksum = 0.0
-    for s in range(K):
-        i = (W + s) % pool
-        cache.decode_step_host(hq_p[i], hk_p[i], hv_p[i], hout_p, H, sp, stream=stream_p)
-        checksum += float(hout_np[0, 0, 0, 0])       # the host reads the step's result
-    e1.record(stream)
-    barrier()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms), device="cuda")
-    assert math.isfinite(checksum)
-    e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
-           "h2d_bytes_per_step": int(hq[0].numel() + hk[0].numel() + hv[0].numel()) * 4, "d2h_bytes_per_step": int(hout.numel()) * 4,
-           "entry_point": "er_kv_decode_step_host"}
+    # ---- end to end: this step's q/k/v from pinned host memory, the result back to the host, every step ----
+    if "e2e" in extras:
+        hq = torch.empty((pool, L, B, H, D), dtype=torch.float32).pin_memory().copy_(qs.cpu())
+        hk = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(ks.cpu())
+        hv = torch.empty((pool, L, B, Hkv, D), dtype=torch.float32).pin_memory().copy_(vs.cpu())
+        hout = torch.empty((L, B, Hfull if dec is not None else H, D), dtype=torch.float32).pin_memory()
+        hout_np = hout.numpy()
+        if dec is None or not sharded:
+            # one GPU: the host-buffer entry point of the C ABI (raw addresses: slicing tensors per step would add tens of
+            # microseconds of interpreter time to a step)
+            if dec is not None:
+                dec.close()
+                dec = None
+            hq_p, hk_p, hv_p = [hq[i].data_ptr() for i in range(pool)], [hk[i].data_ptr() for i in range(pool)], [hv[i].data_ptr() for i in range(pool)]
+            hout_p, stream_p = hout.data_ptr(), stream.cuda_stream
 
-    # ---- leg 4: one launch per layer (how a model that interleaves its own projections would call it), plain
-    #      launches and replayed as a CUDA graph of the 28 launches (positions live on the device, so one captured
-    #      step can be replayed for every following step) ----
-    def per_layer_step(i):
-        for l in range(L):
-            cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=torch.cuda.current_stream())
+            def host_step(i):
+                cache.decode_step_host(hq_p[i], hk_p[i], hv_p[i], hout_p, H, sp, stream=stream_p)
+            entry = "er_kv_decode_step_host"
+        else:
+            dq, dk, dv = torch.empty_like(qs[0]), torch.empty_like(ks[0]), torch.empty_like(vs[0])
 
-    set_start()
-    for s in range(min(W, 4)):
-        per_layer_step(s % pool)
-    torch.cuda.synchronize()
-    n_pl = min(K, 32)
-    e0.record(stream)
-    for s in range(n_pl):
-        per_layer_step((W + s) % pool)
-    e1.record(stream)
-    torch.cuda.synchronize()
-    per_layer_tok_s = B * n_pl / (e0.elapsed_time(e1) * 1e-3)
-    per_layer_graph_tok_s = None
-    try:
+            def host_step(i):
+                dq.copy_(hq[i], non_blocking=True)
+                dk.copy_(hk[i], non_blocking=True)
+                dv.copy_(hv[i], non_blocking=True)
+                dec.step(dq, dk, dv, sp, stream=stream)
+                hout.copy_(dec.full, non_blocking=True)
+                stream.synchronize()
+            entry = "HeadShardedDecoder.step with pinned host q/k/v slices in and the gathered [layers, batch, heads, 128] tensor out"
+        e2e_regions = []
+        checksum = 0.0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(max(3, repeats // 2 + 1)):
+            set_start()
+            for s in range(W):
+                host_step(s % pool)
+            cx.barrier()
+            e0.record(stream)
+            t0 = time.perf_counter()
+            for s in range(K):
+                host_step((W + s) % pool)
+                checksum += float(hout_np[0, 0, 0, 0])       # the host reads the step's result
+            e1.record(stream)
+            cx.barrier()
+            wall_ms = (time.perf_counter() - t0) * 1e3
+            x = max(e0.elapsed_time(e1), wall_ms)
+            e2e_regions.append(cx.max_over_ranks(x) if sharded else x)
+        assert math.isfinite(checksum)
+        e2e_ms = statistics.median(e2e_regions)
+        res["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                      "h2d_bytes_per_step": int(hq[0].numel() + hk[0].numel() + hv[0].numel()) * 4 * (world if sharded else 1),
+                      "d2h_bytes_per_step": int(hout.numel()) * 4 * (world if sharded else 1), "entry_point": entry,
+                      "regions_ms": [round(x, 4) for x in e2e_regions]}
+
+    # ---- one launch per layer (how a model that interleaves its own projections calls it), plain launches and replayed
+    #      as a CUDA graph of the layer launches (positions live on the device, so one captured step replays for every
+    #      following step) ----
+    if "per_layer" in extras and dec is None:
+        def per_layer_step(i):
+            for l in range(L):
+                cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=torch.cuda.current_stream())
+
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         set_start()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            per_layer_step(0)                      # warm the capture stream
-        torch.cuda.current_stream().wait_stream(side)
+        for s in range(min(W, 4)):
+            per_layer_step(s % pool)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            per_layer_step(0)
-        set_start()
-        for _ in range(4):
-            graph.replay()
+        n_pl = min(K, 32)
+        e0.record(stream)
+        for s in range(n_pl):
+            per_layer_step((W + s) % pool)
+        e1.record(stream)
         torch.cuda.synchronize()
-        e0.record()
-        for _ in range(n_pl):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        per_layer_graph_tok_s = B * n_pl / (e0.elapsed_time(e1) * 1e-3)
-        assert cache.total_written(0, 0) == base_positions[0] + 4 + n_pl
-    except Exception as exc:   # graph capture is an optional extra figure
-        per_layer_graph_tok_s = "unavailable: %s" % (str(exc).splitlines()[0][:120] if str(exc) else type(exc).__name__)
+        pl_ms = e0.elapsed_time(e1) / n_pl
+        res["per_layer_launch"] = {"tokens_per_s": B / (pl_ms * 1e-3), "us_per_layer_launch": round(pl_ms * 1e3 / L, 3)}
+        try:
+            set_start()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                per_layer_step(0)                      # warm the capture stream
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                per_layer_step(0)
+            set_start()
+            for _ in range(4):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n_pl):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            g_ms = e0.elapsed_time(e1) / n_pl
+            assert cache.total_written(0, 0) == lens[0] + 4 + n_pl
+            res["per_layer_launch"]["cuda_graph_tokens_per_s"] = B / (g_ms * 1e-3)
+            res["per_layer_launch"]["cuda_graph_us_per_layer_launch"] = round(g_ms * 1e3 / L, 3)
+        except Exception as exc:   # graph capture is an optional extra figure
+            res["per_layer_launch"]["cuda_graph_tokens_per_s"] = "unavailable: %s" % (str(exc).splitlines()[0][:120] if str(exc) else type(exc).__name__)
+
+    _close(dec, cache)
+    del qs, ks, vs
+    torch.cuda.empty_cache()
+    return res
+
+
+def _close(dec, cache):
+    if dec is not None:
+        dec.close()
+    cache.close()
+
+
+def config_of(w, lens, world, shard_heads, args):
+    return {"workload": w["name"], "layers": w["layers"], "batch": len(lens), "q_heads": w["heads"], "kv_heads": w["kv_heads"],
+            "head_dim": D, "kv_storage": w["precision"], "layout": w["layout"],
+            "launch": "layer-batched: one persistent attention launch per step for all layers (fp16 rows: the append is fused into it; "
+                      "q8_0 / TurboQuant rows: one append launch first)",
+            "sharding": ("kv heads split over the %d GPUs (%d kv heads each); every GPU ends a step with all heads' outputs, exchange "
+                         "inside the timed region" % (world, w["kv_heads"] // world)) if (shard_heads and world > 1) else
+                        ("by sequence, one replica of the workload per GPU, no collective" if world > 1 else "single GPU, all kv heads"),
+            "l2": "cache bytes read per step per GPU (%.0f MB) exceed the 126 MB L2; no flush needed" % (step_bytes(w, lens, 0) / max(world if shard_heads else 1, 1) / 1e6),
+            "timing": "median of %d timed regions of %d steps, CUDA events, max over ranks" % (args.repeats, args.steps)}
+
+
+def run_ours(args, w, lens):
+    cx = Context(args)
+    torch, dist = cx.torch, cx.dist
+    K, W = args.steps, max(args.warmup, 0)
+    shard_heads = args.shard == "heads"
+    sharded = shard_heads and cx.world > 1
+    verified = None
+    if sharded:
+        from edgerunner_b200.sharding import verify_exchange
+        # parity first: the exchanged [layers, batch, heads, 128] tensor of a small paged case, bit for bit against the
+        # shards computed on this rank's own GPU (raises on any difference)
+        verified = verify_exchange(cx.er, cx.world, cx.rank, args.exchange)
+    extras = () if args.only_device_leg else ("e2e",) + (("per_layer",) if w["batch"] == 1 and not sharded else ())
+    res = measure_decode(cx, args, w, lens, K, W, args.repeats, shard_heads, extras)
+
+    legs = {}
+    leg_names = args.legs
+    if leg_names is None:
+        leg_names = "cfg1,cfg2" if (args.workload == DEFAULT_WORKLOAD and cx.world == 1 and not args.only_device_leg) else ""
+    for name in [x for x in leg_names.split(",") if x]:
+        if cx.world > 1:
+            break                       # the other configurations are single-GPU figures
+        lw = WORKLOADS[name]
+        llens = sequence_lengths(lw)
+        lk = max(K, 100) if lw["batch"] == 1 else K        # a cfg1 step is ~80 us: 100 steps per region
+        r = measure_decode(cx, args, lw, llens, lk, max(W, 8), args.repeats, False, ("e2e",) + (("per_layer",) if lw["batch"] == 1 else ()))
+        legs[name] = {"config": {"workload": lw["name"]}, "value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
+                      "steps": lk, "regions_ms": r["regions_ms"], "hbm_gbs": r["hbm_gbs_per_gpu"], "roofline": r.get("roofline"),
+                      "e2e": r.get("e2e"), "gpu_launches": r["gpu_launches"], **({"per_layer_launch": r["per_layer_launch"]} if "per_layer_launch" in r else {})}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and not args.only_device_leg:
         r = cpu_reference_leg(w, lens, args.cpu_seconds)
         cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
 
-    if rank == 0:
+    if cx.rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w["name"], "layers": L, "batch_per_gpu": B, "q_heads": H, "kv_heads": Hkv, "head_dim": D,
-                       "kv_storage": w["precision"], "layout": w["layout"],
-                       "launch": "layer-batched: one append + one persistent attention launch per step for all layers",
-                       "sharding": "by sequence, one replica of the workload per GPU, no collective" if world > 1 else "single GPU",
-                       "l2": "cache bytes read per step (%.0f MB) exceed the 126 MB L2; no flush needed" % (step_bytes(w, lens, W) / 1e6),
-                       "per_layer_launch_tokens_per_s": per_layer_tok_s,
-                       "per_layer_launch_cuda_graph_tokens_per_s": per_layer_graph_tok_s},
-            "hbm_gbs_per_gpu": round(hbm_gbs, 1), "frac_of_8tbs": round(hbm_gbs / 8000.0, 4),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "metric": METRIC, "value": res["value"], "unit": "tokens/s", "n_gpus": cx.world, "steps": K, "warmup": W,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong" if (shard_heads or cx.world == 1) else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config_of(w, lens, cx.world, shard_heads, args),
+            "repeats": args.repeats, "regions_ms": res["regions_ms"],
+            "hbm_gbs_per_gpu": res["hbm_gbs_per_gpu"], "frac_of_8tbs": round(res["hbm_gbs_per_gpu"] / 8000.0, 4),
+            "roofline": res.get("roofline"), "cpu_baseline": cpu, "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"],
+            "clocks": res["clocks"],
         }
+        if "exchange" in res:
+            line["exchange"] = dict(res["exchange"], verified_before_timing="exchanged outputs of a small paged case equal the per-shard "
+                                    "reference bit for bit on every rank (%s)" % verified)
+        if "per_layer_launch" in res:
+            line["per_layer_launch"] = res["per_layer_launch"]
+        if "cta_timeline_us" in res:
+            line["cta_timeline_us"] = res["cta_timeline_us"]
+        if args.only_device_leg:
+            line["note"] = "device leg only"
+        if legs:
+            line["legs"] = legs
         print(json.dumps(line))
-    if world > 1:
+    if cx.world > 1:
         dist.destroy_process_group()
 
 
