@@ -519,7 +519,8 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
 
     # ---- roofline of the attention kernel ----
     peak, peak_src = measured_peaks()
-    fused_single_launch = launches == K        # fp16 rows: the timed region is K launches of the one fused kernel
+    # fp16 rows: the timed region is K launches of the one fused kernel (plus K re-layout launches behind an NCCL all-gather)
+    fused_single_launch = launches == K or (sharded and dec.exchange == "nccl" and w["precision"] == "float16" and launches == 2 * K)
     t_append = 0.0
     if fused_single_launch:
         t_attn, attn_bytes, timed_as = ms_compute / K, bytes_region / K, "the K launches of the timed region (append fused into the kernel)"

@@ -1254,18 +1254,19 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
         const size_t rows_bytes = static_cast<size_t>(kv->cfg.num_kv_heads) * tpad * kHeadDim * 2;
         const size_t q_bytes = static_cast<size_t>(n_qrows) * kHeadDim * 4;
-        rc = ensure_stage(kv, 3 * rows_bytes + q_bytes + 256);
+        rc = ensure_stage(kv, 4 * rows_bytes + q_bytes + 256);
         if (rc != ER_OK) return rc;
         __half* ek = reinterpret_cast<__half*>(kv->d_stage);
         __half* ev = reinterpret_cast<__half*>(kv->d_stage + rows_bytes);
-        __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);   // the keys keep their fp16 rounding residue
-        float* qrot = reinterpret_cast<float*>(kv->d_stage + 3 * rows_bytes);
+        __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);   // keys and values keep their fp16 rounding residue
+        __half* evl = reinterpret_cast<__half*>(kv->d_stage + 3 * rows_bytes);
+        float* qrot = reinterpret_cast<float*>(kv->d_stage + 4 * rows_bytes);
         for (int is_v = 0; is_v < 2; ++is_v) {
             TurboExpandParams ep{};
             ep.codes = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
             ep.norms = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
             ep.out = is_v ? ev : ek;
-            ep.out_lo = is_v ? nullptr : ekl;
+            ep.out_lo = is_v ? evl : ekl;
             ep.addr = kv->addressing();
             ep.len_ptr = pp.kv_len_ptr;
             ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad; ep.norm_fp16 = kv->norm_bytes == 2;
@@ -1285,26 +1286,28 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         pp.k_layer = reinterpret_cast<const uint8_t*>(ek);
         pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
         pp.k_lo_layer = reinterpret_cast<const uint8_t*>(ekl);
+        pp.v_lo_layer = reinterpret_cast<const uint8_t*>(evl);
         pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
         pp.seq = 0;
         s.apply_rope = 0;
     }
     if (kv->q8) {
-        // gqa_attention_q8kv with seqLen > 1 (Shaders/GQA.metal:409-522): rows expanded to scale * q as fp16 hi (+ lo for the
-        // keys, which makes them exact: 11 + 7 significant bits), same tensor-core kernel
+        // gqa_attention_q8kv with seqLen > 1 (Shaders/GQA.metal:409-522): rows expanded to scale * q as fp16 hi + lo (exact:
+        // 11 + 7 significant bits), same tensor-core kernel
         const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
         const size_t rows_bytes = static_cast<size_t>(kv->cfg.num_kv_heads) * tpad * kHeadDim * 2;
-        rc = ensure_stage(kv, 3 * rows_bytes + 256);
+        rc = ensure_stage(kv, 4 * rows_bytes + 256);
         if (rc != ER_OK) return rc;
         __half* ek = reinterpret_cast<__half*>(kv->d_stage);
         __half* ev = reinterpret_cast<__half*>(kv->d_stage + rows_bytes);
         __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);
+        __half* evl = reinterpret_cast<__half*>(kv->d_stage + 3 * rows_bytes);
         for (int is_v = 0; is_v < 2; ++is_v) {
             Q8ExpandParams ep{};
             ep.rows = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
             ep.scales = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
             ep.out = is_v ? ev : ek;
-            ep.out_lo = is_v ? nullptr : ekl;
+            ep.out_lo = is_v ? evl : ekl;
             ep.addr = kv->addressing();
             ep.len_ptr = pp.kv_len_ptr;
             ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
@@ -1315,6 +1318,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         pp.k_layer = reinterpret_cast<const uint8_t*>(ek);
         pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
         pp.k_lo_layer = reinterpret_cast<const uint8_t*>(ekl);
+        pp.v_lo_layer = reinterpret_cast<const uint8_t*>(evl);
         pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
         pp.seq = 0;
     }

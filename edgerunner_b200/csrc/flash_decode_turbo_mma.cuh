@@ -3,19 +3,24 @@
 // gqa_attention_turboquant_decode (Shaders/TurboQuant.metal:1794-2001) as two small GEMMs per 16-token unit:
 //   S[token][head]  = K~[token][dim] . qR[head][dim]      A = centroid pairs looked up from the code stream, B = qR
 //   O^T[dim][head] += V~^T[dim][token] . P^T[token][head]  A = transposed centroid pairs, B = transposed (p_t * vNorm_t)
-// A code stream yields two adjacent *dims* of one token per lookup (one half2 register).  That is an A fragment when
-// the contraction runs over dims (scores); for the P.V product the contraction runs over tokens, so every looked-up
-// 8x8 block passes through movmatrix.trans first.
+// Row, column and contraction indices of an mma are only labels, so they are assigned to suit the code stream:
 //
-// Thread (g = lane / 4, c = lane % 4) reads tokens g and g + 8 of the warp's 16-token unit, and of each row the 32
-// consecutive codes [32c, 32c + 32) (4 * bits bytes).  The contraction index of an mma is only a label, so the labels
-// are assigned to make that chunk contiguous:
-//   scores, k-step s:   label 2c + e -> dim 32c + 4s + e,     label 2c + 8 + e -> dim 32c + 4s + 2 + e      (e = 0, 1)
-//   outputs, m-tile mt: row n        -> dim 32(n/2) + 4mt + n%2,   row n + 8   -> dim 32(n/2) + 4mt + 2 + n%2
-// Queries, probabilities and the keys' centroids enter as fp16 hi + lo pairs (scores: qh.ch + ql.ch + qh.cl); the values'
-// centroids as one fp16.  All tables hold sigma * centroid with a per-codebook sigma chosen so that every centroid
-// rounds to fp16 with < 6e-5 relative error (tq_fp16_scales.h); 1 / sigma is folded into the softmax scale and the
-// value norms.
+// Scores.  Thread (g = lane / 4, c = lane % 4) reads, of the two tokens behind S rows g and g + 8, the 32 consecutive codes
+// [32c, 32c + 32) (4 * bits bytes).  A lookup of a code PAIR (two adjacent dims of one token) returns the A-fragment
+// registers directly (hi parts, lo parts); k-step s: label 2c + e -> dim 32c + 4s + e, label 2c + 8 + e -> dim
+// 32c + 4s + 2 + e (e = 0, 1).  Queries enter as fp16 hi + lo B fragments: S = Kh.qh + Kh.ql + Kl.qh.
+//
+// Outputs.  The contraction runs over tokens, and a code stream never yields two tokens of one dim.  So the value table is
+// indexed by a SINGLE code and returns half2(hi, lo) of its centroid: the two halves sit on adjacent contraction labels
+// (2c, 2c + 1) and the probability of that token is duplicated on both, which makes one mma.k16 cover 8 tokens with
+// fp32-accurate values: O^T += [Vh | Vl] . [p ; p].  Thread (g, c) owns dims [16g, 16g + 16) (m-tile mt: row g -> dim
+// 16g + 2mt, row g + 8 -> dim 16g + 2mt + 1) of tokens c, c + 4, c + 8, c + 12, a contiguous 2 * bits bytes per token.  The S
+// rows are labelled so that the transposed probabilities land on exactly those tokens: S row label n < 8 is token n / 2 +
+// 4 (n % 2), label n + 8 is that token + 8 (movmatrix.trans of the S fragment hands thread (g', c') labels 2c', 2c' + 1).
+//
+// Queries, probabilities and all centroids therefore carry ~22 significant bits (fp16 hi + lo), which keeps the outputs
+// within the element-wise 2e-3 bound of the fp32 CPU statement.  Tables hold sigma * centroid with a per-codebook sigma
+// (tq_fp16_scales.h) that minimises the hi parts' rounding; 1 / sigma is folded into the softmax scale and the value norms.
 #pragma once
 
 #include "flash_decode_turbo.cuh"
@@ -91,16 +96,19 @@ template <int GROUP, int KBITS, int VBITS, int UNITS_PER_TILE = 6, int WARP_GROU
 struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
     using Base = TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
     static_assert(GROUP <= 8, "one n-tile of heads");
-    static constexpr int kKPairs = 1 << (2 * KBITS), kVPairs = 1 << (2 * VBITS);
-    // Lookup tables indexed by a pair of codes, one column per lane (no bank conflicts):
-    //   keys    [pairs][32 lanes] x 8 bytes: half2 (hi parts of the two centroids), half2 (lo parts); scores pass through
-    //           exp2, so the keys' centroids keep their fp16 rounding residue as a second operand
-    //   values  [pairs][32 lanes] x 4 bytes: half2 of the two centroids
+    static constexpr int kKPairs = 1 << (2 * KBITS), kVCodes = 1 << VBITS;
+    // Lookup tables, one column per lane (no bank conflicts):
+    //   keys    [code pairs][32 lanes] x 8 bytes: half2 (hi parts of the two centroids), half2 (lo parts)
+    //   values  [codes][32 lanes] x 4 bytes: half2 (hi part, lo part) of the centroid; the table starts on a 2 KB boundary of
+    //           the shared window so that an entry's address is base | code << 7 | lane << 2 (one logic op after the shift)
     static constexpr int kOffQrot = 0;
     static constexpr int kOffFin = GROUP * kHeadDim * 4;
     static constexpr int kOffLutK = 2 * GROUP * kHeadDim * 4;
     static constexpr int kOffLutV = kOffLutK + kKPairs * 256;
-    static constexpr int kExtraBytes = kOffLutV + kVPairs * 128;
+    static constexpr int kExtraBytes = kOffLutV + 2048 + kVCodes * 128;
+    __device__ __forceinline__ static uint32_t lutv_base(const uint8_t* extra) {
+        return (smem_u32(extra) + kOffLutV + 2047u) & ~2047u;
+    }
 
     struct State {
         uint32_t qh[8][2], ql[8][2];   // B fragments of the rotated queries per k-step: fp16 hi and lo parts
@@ -116,7 +124,6 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         }
         __device__ __forceinline__ void publish(float* ml, float* accs, int lane) const {
             const int g = lane >> 2, c = lane & 3;
-            const int d0 = 32 * (g >> 1) + (g & 1);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -126,17 +133,15 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                         ml[h * 2 + 1] = l[e];
                     }
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) {
-                        accs[h * kHeadDim + d0 + 4 * t] = acc[t][e];
-                        accs[h * kHeadDim + d0 + 4 * t + 2] = acc[t][2 + e];
-                    }
+                    for (int t = 0; t < 8; ++t)   // m-tile t: row g -> dim 16g + 2t, row g + 8 -> dim 16g + 2t + 1
+                        *reinterpret_cast<float2*>(accs + h * kHeadDim + 16 * g + 2 * t) = make_float2(acc[t][e], acc[t][2 + e]);
                 }
             }
         }
     };
 
     __device__ static void init_extra(uint8_t* extra, int tid) {
-        const uint32_t lk = smem_u32(extra) + kOffLutK, lv = smem_u32(extra) + kOffLutV;
+        const uint32_t lk = smem_u32(extra) + kOffLutK, lv = lutv_base(extra);
         for (int e = tid; e < kKPairs * 32; e += Base::kThreads) {
             const int pv = e >> 5;
             const float c0 = __fmul_rn(tq_centroids<KBITS>()[pv & ((1 << KBITS) - 1)], tq_fp16_scale<KBITS>());
@@ -147,11 +152,10 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                          "r"(pack_half2(c0 - hf.x, c1 - hf.y))
                          : "memory");
         }
-        for (int e = tid; e < kVPairs * 32; e += Base::kThreads) {
-            const int pv = e >> 5;
-            const uint32_t v = pack_half2(__fmul_rn(tq_centroids<VBITS>()[pv & ((1 << VBITS) - 1)], tq_fp16_scale<VBITS>()),
-                                          __fmul_rn(tq_centroids<VBITS>()[pv >> VBITS], tq_fp16_scale<VBITS>()));
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lv + 4 * e), "r"(v) : "memory");
+        for (int e = tid; e < kVCodes * 32; e += Base::kThreads) {
+            const float cv = __fmul_rn(tq_centroids<VBITS>()[e >> 5], tq_fp16_scale<VBITS>());
+            const float hi = __half2float(__float2half_rn(cv));
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lv + 4 * e), "r"(pack_half2(hi, cv - hi)) : "memory");
         }
     }
 
@@ -190,34 +194,70 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         }
     }
 
+    // Address of the table entry of code I (0..15) of a 16-code chunk held as (lo: codes' bits 0..31, hi: the rest).
+    template <int I>
+    __device__ __forceinline__ static uint32_t value_entry(uint32_t lutv, uint32_t lo, uint32_t hi) {
+        constexpr int bit = I * VBITS;
+        constexpr uint32_t mask = static_cast<uint32_t>(kVCodes - 1) << 7;
+        uint32_t v;
+        if constexpr (bit + VBITS <= 32) {
+            if constexpr (bit >= 7) v = lo >> (bit - 7); else v = lo << (7 - bit);
+        } else if constexpr (bit >= 32) {
+            if constexpr (bit - 32 >= 7) v = hi >> (bit - 32 - 7); else v = hi << (7 - (bit - 32));
+        } else {
+            v = __funnelshift_r(lo, hi, bit - 7);   // the code straddles the two words (3-bit codes only; bit = 30)
+        }
+        return (v & mask) | lutv;
+    }
+
+    // m-tile T of O^T: dims 16g + 2T (row g) and 16g + 2T + 1 (row g + 8), both k-steps (tokens c, c + 4 | c + 8, c + 12).
     template <int T>
-    __device__ __forceinline__ static void value_tiles(State& st, uint32_t lutv, const uint32_t (&v0)[VBITS],
-                                                       const uint32_t (&v1)[VBITS], uint32_t b0, uint32_t b1, uint32_t b0l, uint32_t b1l) {
+    __device__ __forceinline__ static void value_tiles(State& st, uint32_t lutv, const uint32_t (&vlo)[4], const uint32_t (&vhi)[4],
+                                                       const uint32_t (&bh)[4], const uint32_t (&bl)[4]) {
         if constexpr (T < 8) {
-            const uint32_t a0 = movmatrix_trans(lds_u32(lutv + pair_offset<VBITS, 2 * T, 7>(v0)));
-            const uint32_t a1 = movmatrix_trans(lds_u32(lutv + pair_offset<VBITS, 2 * T + 1, 7>(v0)));
-            const uint32_t a2 = movmatrix_trans(lds_u32(lutv + pair_offset<VBITS, 2 * T, 7>(v1)));
-            const uint32_t a3 = movmatrix_trans(lds_u32(lutv + pair_offset<VBITS, 2 * T + 1, 7>(v1)));
-            mma_m16n8k16(st.acc[T], a0, a1, a2, a3, b0, b1);
-            mma_m16n8k16(st.acc[T], a0, a1, a2, a3, b0l, b1l);
-            value_tiles<T + 1>(st, lutv, v0, v1, b0, b1, b0l, b1l);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t a0 = lds_u32(value_entry<2 * T>(lutv, vlo[2 * j], vhi[2 * j]));
+                const uint32_t a1 = lds_u32(value_entry<2 * T + 1>(lutv, vlo[2 * j], vhi[2 * j]));
+                const uint32_t a2 = lds_u32(value_entry<2 * T>(lutv, vlo[2 * j + 1], vhi[2 * j + 1]));
+                const uint32_t a3 = lds_u32(value_entry<2 * T + 1>(lutv, vlo[2 * j + 1], vhi[2 * j + 1]));
+                mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bh[2 * j], bh[2 * j + 1]);
+                mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bl[2 * j], bl[2 * j + 1]);
+            }
+            value_tiles<T + 1>(st, lutv, vlo, vhi, bh, bl);
         }
     }
 
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
                                         const uint8_t* extra, int lane) {
-        const uint32_t lutk = smem_u32(extra) + kOffLutK + 8 * lane, lutv = smem_u32(extra) + kOffLutV + 4 * lane;
+        const uint32_t lutk = smem_u32(extra) + kOffLutK + 8 * lane, lutv = lutv_base(extra) + 4 * lane;
         const int g = lane >> 2, c = lane & 3;
+        const int tk0 = (g >> 1) + 4 * (g & 1);   // token behind S row g (row g + 8: tk0 + 8)
         const uint32_t sbase = smem_u32(stage);
-        const uint32_t kc = sbase + ((unit * kUnitTokens + g) * Base::kKW + c * KBITS) * 4;
-        const uint32_t vc = sbase + Base::kKcBytes + ((unit * kUnitTokens + g) * Base::kVW + c * VBITS) * 4;
-        uint32_t k0[KBITS], k1[KBITS], v0[VBITS], v1[VBITS];
+        const uint32_t kc = sbase + ((unit * kUnitTokens + tk0) * Base::kKW + c * KBITS) * 4;
+        uint32_t k0[KBITS], k1[KBITS], vlo[4], vhi[4];
         load_code_chunk<KBITS>(kc, k0);
         load_code_chunk<KBITS>(kc + 32 * Base::kKW, k1);
-        load_code_chunk<VBITS>(vc, v0);
-        load_code_chunk<VBITS>(vc + 32 * Base::kVW, v1);
-        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
-        const int r0 = unit * kUnitTokens + g;
+        // value codes: dims [16g, 16g + 16) of tokens c + 4j -- 2 * VBITS bytes at byte 2 * VBITS * g of the row
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t row = sbase + Base::kKcBytes + (unit * kUnitTokens + c + 4 * j) * Base::kVW * 4;
+            if constexpr (VBITS == 4) {
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(vlo[j]), "=r"(vhi[j]) : "r"(row + 8 * g) : "memory");
+            } else if constexpr (VBITS == 3) {
+                // 6 bytes at offset 6g: the two aligned words around them, shifted by 16 bits for odd g
+                const uint32_t w = row + ((3 * g) >> 1) * 4;
+                const uint32_t wa = lds_u32_stage(w), wb = lds_u32_stage(w + 4);
+                const uint32_t sh = (g & 1) * 16;
+                vlo[j] = __funnelshift_r(wa, wb, sh);
+                vhi[j] = wb >> sh;
+            } else {
+                vlo[j] = lds_u32_stage(row + 4 * g);
+                vhi[j] = 0;
+            }
+        }
+        const bool ok0 = tk0 < nvalid, ok1 = tk0 + 8 < nvalid;
+        const int r0 = unit * kUnitTokens + tk0;
         const float kn0 = ok0 ? Base::load_norm(stage + Base::kOffKn, r0, p.norm_fp16) : 0.f;
         const float kn1 = ok1 ? Base::load_norm(stage + Base::kOffKn, r0 + 8, p.norm_fp16) : 0.f;
         constexpr float inv_sk = 1.f / tq_fp16_scale<KBITS>(), inv_sv = 1.f / tq_fp16_scale<VBITS>();
@@ -225,7 +265,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         const float vn1 = ok1 ? Base::load_norm(stage + Base::kOffVn, r0 + 8, p.norm_fp16) * inv_sv : 0.f;
         const float sc = p.scale_log2 * inv_sk;
 
-        float s[4] = {0.f, 0.f, 0.f, 0.f};   // (token g | g + 8) x (head 2c | 2c + 1)
+        float s[4] = {0.f, 0.f, 0.f, 0.f};   // (token tk0 | tk0 + 8) x (head 2c | 2c + 1)
         score_steps<0>(s, lutk, k0, k1, st);
         s[0] = ok0 ? (kn0 * s[0]) * sc : -INFINITY;
         s[1] = ok0 ? (kn0 * s[1]) * sc : -INFINITY;
@@ -238,7 +278,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
         }
-        const float m0 = fmaxf(st.m[0], mx0), m1 = fmaxf(st.m[1], mx1);   // finite: token 0 of the unit is valid
+        const float m0 = fmaxf(st.m[0], mx0), m1 = fmaxf(st.m[1], mx1);   // finite: token 0 of the unit (S row 0) is valid
         const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
         const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
         float sum0 = p0 + p2, sum1 = p1 + p3;
@@ -257,15 +297,19 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                 st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
             }
         }
-        // (p_t * vNorm_t)[token][head] blocks, as fp16 hi + lo parts -> B fragments [token pair][head]
+        // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed: thread (g', c') receives head g' of the tokens behind
+        // labels 2c', 2c' + 1 (c', c' + 4) and, from the rows g + 8, of c' + 8, c' + 12; each value is duplicated on the two
+        // contraction labels that carry the hi and the lo half of a centroid
         const float w0 = p0 * vn0, w1 = p1 * vn0, w2 = p2 * vn1, w3 = p3 * vn1;
         const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
         const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h01));
-        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
-        const uint32_t b0l = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
-        const uint32_t b1l = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
-        value_tiles<0>(st, lutv, v0, v1, b0, b1, b0l, b1l);
+        const uint32_t x0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h01));
+        const uint32_t x1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
+        const uint32_t y0 = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
+        const uint32_t y1 = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
+        const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
+        const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
+        value_tiles<0>(st, lutv, vlo, vhi, bh, bl);
     }
 };
 

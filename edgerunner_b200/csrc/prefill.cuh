@@ -23,7 +23,7 @@ constexpr int kPfRows = 64;                      // M rows per CTA
 constexpr int kPfThreads = 128;
 constexpr int kPfTileBytes = kPfTileTokens * kHeadDim * 2;   // 16 KiB per K or V tile
 constexpr int kPfSmemBytes = 4 * kPfTileBytes;               // K,V x 2 stages
-constexpr int kPfSmemBytesSplit = 6 * kPfTileBytes;          // K hi, K lo, V x 2 stages
+constexpr int kPfSmemBytesSplit = 8 * kPfTileBytes;          // K hi, V hi, K lo, V lo x 2 stages
 
 struct PrefillParams {
     const float* q;          // [seq_len][num_q_heads][128]
@@ -31,6 +31,7 @@ struct PrefillParams {
     const uint8_t* k_layer;  // first row of the layer
     const uint8_t* v_layer;
     const uint8_t* k_lo_layer;   // KSPLIT kernels: second fp16 operand of K (rows = k - fp16(k) of an fp32 source), same addressing
+    const uint8_t* v_lo_layer;   // ... and of V (set together with k_lo_layer)
     KVAddressing addr;
     int seq;                 // sequence index inside the cache
     int seq_len;             // query rows
@@ -82,11 +83,12 @@ __device__ __forceinline__ uint32_t pf_swizzle(int row, int chunk) {
     return static_cast<uint32_t>(row * 256 + (((chunk & 8) | ((chunk ^ row) & 7)) << 4));
 }
 
-// KSPLIT: K is the sum of two fp16 tensors (k_layer + k_lo_layer), as produced from fp32 rows that must not lose their
-// low mantissa bits before the softmax (TurboQuant norm * centroid); one more mma per fragment (qh.kh + ql.kh + qh.kl).
+// KSPLIT: K and V are each the sum of two fp16 tensors (k_layer + k_lo_layer, v_layer + v_lo_layer), as produced from
+// fp32 rows that must not lose their low mantissa bits (TurboQuant norm * centroid, q8_0 scale * code); one more mma per
+// fragment on either side (qh.kh + ql.kh + qh.kl;  ph.vh + pl.vh + ph.vl).
 template <int GROUP, bool KSPLIT = false>
 __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_constant__ PrefillParams p) {
-    constexpr int kStageTiles = KSPLIT ? 3 : 2;
+    constexpr int kStageTiles = KSPLIT ? 4 : 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = lane >> 2, qlane = lane & 3;
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
 
     auto load_tile = [&](int tile, int stage) {
         const int t0 = tile * kPfTileTokens;
-        const uint32_t ks = smem_base + stage * kStageTiles * kPfTileBytes, vs = ks + kPfTileBytes, kls = vs + kPfTileBytes;
+        const uint32_t ks = smem_base + stage * kStageTiles * kPfTileBytes, vs = ks + kPfTileBytes, kls = vs + kPfTileBytes, vls = kls + kPfTileBytes;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int c = tid + i * kPfThreads;       // 1024 chunks of 16 bytes per tensor
@@ -171,7 +173,10 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
             const int64_t ridx = row_index(p.addr, p.seq, kv_head, ok ? t : 0);
             cp_async_16(ks + pf_swizzle(row, chunk), p.k_layer + ridx * 256 + chunk * 16, ok);
             cp_async_16(vs + pf_swizzle(row, chunk), p.v_layer + ridx * 256 + chunk * 16, ok);
-            if (KSPLIT) cp_async_16(kls + pf_swizzle(row, chunk), p.k_lo_layer + ridx * 256 + chunk * 16, ok);
+            if (KSPLIT) {
+                cp_async_16(kls + pf_swizzle(row, chunk), p.k_lo_layer + ridx * 256 + chunk * 16, ok);
+                cp_async_16(vls + pf_swizzle(row, chunk), p.v_lo_layer + ridx * 256 + chunk * 16, ok);
+            }
         }
         cp_async_commit();
     };
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
         const int stage = (tile - tile_lo) & 1;
         if (tile + 1 < num_tiles) { load_tile(tile + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
-        const uint32_t ks = smem_base + stage * kStageTiles * kPfTileBytes, vs = ks + kPfTileBytes, kls = vs + kPfTileBytes;
+        const uint32_t ks = smem_base + stage * kStageTiles * kPfTileBytes, vs = ks + kPfTileBytes, kls = vs + kPfTileBytes, vls = kls + kPfTileBytes;
         const int t0 = tile * kPfTileTokens;
 
         // ---- S = Q K^T (log2 domain) ----
@@ -271,6 +276,11 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
                 mma_16816(o[2 * jd2], pl, b[0], b[1]);
                 mma_16816(o[2 * jd2 + 1], ph, b[2], b[3]);
                 mma_16816(o[2 * jd2 + 1], pl, b[2], b[3]);
+                if (KSPLIT) {
+                    ldmatrix_x4_trans(b, vls + pf_swizzle(row, chunk));
+                    mma_16816(o[2 * jd2], ph, b[0], b[1]);
+                    mma_16816(o[2 * jd2 + 1], ph, b[2], b[3]);
+                }
             }
         }
         __syncthreads();

@@ -72,7 +72,9 @@ int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent
     up.status = status;
     if (!um_encode(&up.k_map, p.k_layer, p.addr, outer_extent, box_rows) || !um_encode(&up.v_map, p.v_layer, p.addr, outer_extent, box_rows))
         return kNotBuilt;
-    if (p.k_lo_layer != nullptr && !um_encode(&up.klo_map, p.k_lo_layer, p.addr, outer_extent, box_rows)) return kNotBuilt;
+    if (p.k_lo_layer != nullptr && (p.v_lo_layer == nullptr || !um_encode(&up.klo_map, p.k_lo_layer, p.addr, outer_extent, box_rows) ||
+                                    !um_encode(&up.vlo_map, p.v_lo_layer, p.addr, outer_extent, box_rows)))
+        return kNotBuilt;
     switch (group) {
         case 1: return um_launch_group<1>(up, num_kv_heads, stream);
         case 2: return um_launch_group<2>(up, num_kv_heads, stream);

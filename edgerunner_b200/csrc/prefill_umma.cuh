@@ -44,14 +44,14 @@ __host__ __device__ constexpr int um_kv_region(bool ksplit) { return um_tile(ksp
 constexpr int kUmColS = 0, kUmColO = 256, kUmColQhi = 384, kUmColQlo = 448;   // tensor-memory columns
 // S / P buffers: two of 128 columns, or three of 64 with the second key operand (whose stages are half again as large)
 __host__ __device__ constexpr int um_sbufs(bool ksplit) { return ksplit ? 3 : 2; }
-__host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 6 : 4) * um_kv_region(ksplit); }   // K [Klo] V
-__host__ __device__ constexpr int um_stages(bool ksplit) { return ksplit ? 4 : 3; }
+__host__ __device__ constexpr int um_stage_bytes(bool ksplit) { return (ksplit ? 8 : 4) * um_kv_region(ksplit); }   // K [Klo] V [Vlo]
+__host__ __device__ constexpr int um_stages(bool) { return 3; }
 __host__ __device__ constexpr int um_smem_bytes(bool ksplit) {
     return um_stages(ksplit) * um_stage_bytes(ksplit) + 256 + 3072 + 1024;   // + barriers, (max, denominator) exchange, alignment slack
 }
 
 struct UmmaPrefillParams {
-    CUtensorMap k_map, v_map, klo_map;   // 5-D, box {64 dims, ...}: see encode_prefill_maps
+    CUtensorMap k_map, v_map, klo_map, vlo_map;   // 5-D, box {64 dims, ...}: see encode_prefill_maps
     PrefillParams base;
     int box_rows;                        // tokens per TMA box (64 / box_rows boxes per region and tile)
     int layer;                           // coordinate of the maps' outermost dimension
@@ -165,8 +165,8 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     constexpr int kStageBytes = um_stage_bytes(KSPLIT);
     constexpr int kUmTile = um_tile(KSPLIT), kUmKvRegion = um_kv_region(KSPLIT), kUmSBufs = um_sbufs(KSPLIT);
     constexpr int kHalfCols = kUmTile / 2;     // S columns per softmax thread = P words per row and part
-    constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2)
-    constexpr int kOffKlo = 2 * kUmKvRegion;
+    constexpr int kOffV = (KSPLIT ? 4 : 2) * kUmKvRegion;     // inside a stage: K (2 regions) [Klo (2)] V (2) [Vlo (2)]
+    constexpr int kOffKlo = 2 * kUmKvRegion, kOffVlo = 6 * kUmKvRegion;
     constexpr int kBarKvFull = 0, kBarKvEmpty = kStages, kBarSFull = 2 * kStages, kBarPFull = kBarSFull + kUmSBufs,
                   kBarSFree = kBarPFull + kUmSBufs, kBarOFull = kBarSFree + kUmSBufs, kBarQFull = kBarOFull + 1, kNumBars = kBarQFull + 1;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier block");
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 int nbox = 0;
                 for (int b = 0; b < boxes; ++b) nbox += (t0 + b * up.box_rows < kv_len) ? 1 : 0;
                 const uint32_t box_bytes = static_cast<uint32_t>(up.box_rows) * 128u;
-                mbar_arrive_expect_tx(bar_gen + kBarKvFull + st, nbox * box_bytes * (KSPLIT ? 6u : 4u));
+                mbar_arrive_expect_tx(bar_gen + kBarKvFull + st, nbox * box_bytes * (KSPLIT ? 8u : 4u));
                 for (int b = 0; b < nbox; ++b) {
                     const int slot = t0 + b * up.box_rows;
                     int c1, c2, c3;
@@ -241,8 +241,10 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     for (int r = 0; r < 2; ++r) {
                         tma_load_5d_sw(stage + r * kUmKvRegion + off, &up.k_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
                         tma_load_5d_sw(stage + kOffV + r * kUmKvRegion + off, &up.v_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
-                        if (KSPLIT)
+                        if (KSPLIT) {
                             tma_load_5d_sw(stage + kOffKlo + r * kUmKvRegion + off, &up.klo_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
+                            tma_load_5d_sw(stage + kOffVlo + r * kUmKvRegion + off, &up.vlo_map, 64 * r, c1, c2, c3, up.layer, bar(kBarKvFull + st));
+                        }
                     }
                 }
             }
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         if (lane == 0 && num_tiles > 0) {
             constexpr uint32_t idesc_pv = umma_idesc(kUmRows, kHeadDim, true);
             constexpr uint32_t kHi = umma_desc_hi(1024);
-            const uint32_t v_lo = umma_desc_lo(sbase + kOffV, kUmKvRegion);
+            const uint32_t v_lo = umma_desc_lo(sbase + kOffV, kUmKvRegion), vlo_lo = umma_desc_lo(sbase + kOffVlo, kUmKvRegion);
             for (int j = 0; j < num_tiles; ++j) {
                 const int st = j % kStages, b = j % kUmSBufs;
                 mbar_wait(bar_gen + kBarPFull + b, (j / kUmSBufs) & 1, abort_flag, up.status);   // P of tile j written over S_b
@@ -299,6 +301,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     const uint64_t vd = umma_desc_pack(v_lo + st_off + ((kt * 2048) >> 4), kHi);
                     umma_f16_ts(d, pa + 8u * kt, vd, idesc_pv, (j > 0 || kt > 0) ? 1u : 0u);
                     umma_f16_ts(d, pa + kHalfCols + 8u * kt, vd, idesc_pv, 1u);
+                    if (KSPLIT) umma_f16_ts(d, pa + 8u * kt, umma_desc_pack(vlo_lo + st_off + ((kt * 2048) >> 4), kHi), idesc_pv, 1u);
                 }
                 umma_commit(bar(kBarOFull));           // O includes tile j
                 umma_commit(bar(kBarKvEmpty + st));    // stage free
@@ -428,6 +431,8 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 for (int idx = tid; idx < (kUmTile - first) * 16; idx += 256) {
                     const int row = first + idx / 16, part = idx % 16;    // 2 regions x 8 chunks
                     *reinterpret_cast<uint4*>(vst + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    if (KSPLIT)
+                        *reinterpret_cast<uint4*>(vst + (kOffVlo - kOffV) + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
                 fence_async_smem();
             }
