@@ -18,6 +18,8 @@ constexpr int kMaxPairs = 2048;        // (layer, sequence) pairs one launch can
 constexpr int kStatusTimeout = -12;
 // A row of a paged cache fell into a block-table entry that holds no page (mirrored as ER_ERR_OUT_OF_PAGES).
 constexpr int kStatusOutOfPages = -10;
+// A kernel found its shared-memory window somewhere its table layout cannot use (mirrored as ER_ERR_UNSUPPORTED).
+constexpr int kStatusBadLayout = -11;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -275,6 +275,7 @@ int32_t check_page_coverage(const er_kv* kv, uint32_t seq, uint64_t end_row) {
 int32_t device_status_to_code(int status) {
     if (status == kStatusTimeout) return fail(ER_ERR_DEVICE_TIMEOUT, "a bounded wait inside a kernel gave up");
     if (status == kStatusOutOfPages) return fail(ER_ERR_OUT_OF_PAGES, "a row fell into a block-table entry without a page (the row was dropped)");
+    if (status == kStatusBadLayout) return fail(ER_ERR_UNSUPPORTED, "a decode kernel could not place its tables in this device's shared-memory window");
     return status == 0 ? ER_OK : fail(ER_ERR_CUDA, "device status word %d", status);
 }
 

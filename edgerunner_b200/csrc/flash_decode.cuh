@@ -102,7 +102,8 @@ struct DecodeSmem {
     static constexpr int kOffBars = kOffCosSin + 2 * kHalfDim * 8;
     static constexpr int kOffFlags = kOffBars + 2 * POL::kStages * 8;
     static constexpr int kOffExtra = (kOffFlags + 32 + 127) & ~127;
-    static constexpr int kTotal = kOffExtra + POL::kExtraBytes;
+    // kExtraBytes < 0: the policy lays its own tables out over everything up to the CTA maximum of 227 KB
+    static constexpr int kTotal = POL::kExtraBytes < 0 ? 232448 : kOffExtra + POL::kExtraBytes;
 };
 
 __device__ __forceinline__ int64_t cta_range_start(int cta, int64_t total_units, int active) {
@@ -191,15 +192,15 @@ struct DensePolicy {
     static constexpr int kTileBytesF16 = UNITS_PER_TILE * kUnitTokens * kRowBytesF16;   // per K or V tile
     static constexpr int kStageBytes = 2 * kTileBytesF16;
     static constexpr int kExtraBytes = 0;
-    static constexpr int kOffFin = 0;
     static constexpr bool kRotated = false;
+    __device__ static float* fin_ptr(uint8_t*) { return nullptr; }
     static constexpr bool kFusedAppend = true;
     // A warp group must meet consecutive phases of the stages it visits: tiles go to groups round-robin.
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
     static constexpr int kQRegs = 16;   // per head: dims [8i,8i+8) then [64+8i,64+8i+8), i = lane % 8
     using State = LaneState<GROUP, kQRegs>;
 
-    __device__ static void init_extra(uint8_t*, int) {}
+    __device__ static bool init_extra(uint8_t*, int, int) { return true; }
     __device__ __forceinline__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs,
                                                   uint8_t* extra, int warp, int lane, int layer) {
         load_q(p, st.q, qrow, cs, extra, warp, lane, p.q_norm_w ? p.q_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr);
@@ -506,7 +507,10 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
         }
         mbar_init_fence();
     }
-    POL::init_extra(extra, tid);
+    if (!POL::init_extra(extra, tid, L::kTotal - L::kOffExtra)) {   // CTA-uniform: the policy's shared-memory plan does not fit
+        if (tid == 0) atomicExch(p.status, kStatusBadLayout);
+        return;
+    }
     // everything above touches shared memory only; global memory (lengths, cache rows, scratch, counters, trace) belongs to
     // the previous kernel of the stream until it has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -659,7 +663,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 const int64_t out_off = (static_cast<int64_t>(sg.pair) * out_heads + p.out_head_offset + sg.head * GROUP) * kHeadDim;
                 float* out_item = p.out + out_off;
                 // Outputs of the rotated (TurboQuant) space pass through shared memory for the inverse transform.
-                float* fin = POL::kRotated ? reinterpret_cast<float*>(extra + POL::kOffFin) : out_item;
+                float* fin = POL::kRotated ? POL::fin_ptr(extra) : out_item;
                 auto emit = [&](int idx, float val) {   // a finished output element: local buffer (or staging) + the peers' copies
                     fin[idx] = val;
                     if (!POL::kRotated)

@@ -47,7 +47,7 @@ struct Q8MmaPolicy {
     static constexpr int kOffVs = kOffKs + kTileTokens * 8;
     static constexpr int kStageBytes = kOffVs + kTileTokens * 8;
     static constexpr int kExtraBytes = 0;
-    static constexpr int kOffFin = 0;
+    __device__ static float* fin_ptr(uint8_t*) { return nullptr; }
     static constexpr bool kRotated = false;
     static constexpr bool kFusedAppend = false;   // rows are quantised by q8_append_kernel
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
@@ -88,7 +88,7 @@ struct Q8MmaPolicy {
         }
     };
 
-    __device__ static void init_extra(uint8_t*, int) {}
+    __device__ static bool init_extra(uint8_t*, int, int) { return true; }
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
                                          const float2*, int) {}
     __device__ static void store_out(const DecodeParams&, int64_t, const float*, int, int) {}

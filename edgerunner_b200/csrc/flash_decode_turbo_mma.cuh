@@ -92,28 +92,53 @@ __host__ __device__ constexpr float tq_fp16_scale() {
     return BITS == 2 ? ER_TQ_FP16_SCALE_2BIT : BITS == 3 ? ER_TQ_FP16_SCALE_3BIT : ER_TQ_FP16_SCALE_4BIT;
 }
 
+// Shared-memory plan of the TurboQuant policy.  The CTA takes the whole 227 KB.  The key table sits on a 64 KB boundary of the
+// shared window so that the address of an entry is ONE instruction away from the code word: for 4-bit keys the index of
+// a code pair is a byte of the word, and prmt drops it into byte 1 of (table | lane << 3); 3-bit pairs need a shift and one
+// logic op.  Everything the kernel itself lays out (stages, merge buffers, ...) lies below that boundary, the value table
+// and the query / output staging rows above the table.
+struct TurboSmemPlan {
+    uint32_t lut_k;    // window address of the key table, 64 KB aligned
+    uint32_t lut_v;    // window address of the value table (16 KB aligned), right behind the key table
+    uint32_t rows;     // window address of the rotated-query and output staging rows
+};
+
 template <int GROUP, int KBITS, int VBITS, int UNITS_PER_TILE = 6, int WARP_GROUPS = 2, int STAGES = 4>
 struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
     using Base = TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
     static_assert(GROUP <= 8, "one n-tile of heads");
-    static constexpr int kKPairs = 1 << (2 * KBITS), kVCodes = 1 << VBITS;
-    // Lookup tables, one column per lane (no bank conflicts):
-    //   keys    [code pairs][32 lanes] x 8 bytes: half2 (hi parts of the two centroids), half2 (lo parts)
-    //   values  [codes][32 lanes] x 4 bytes: half2 (hi part, lo part) of the centroid; the table starts on a 2 KB boundary of
-    //           the shared window so that an entry's address is base | code << 7 | lane << 2 (one logic op after the shift)
-    static constexpr int kOffQrot = 0;
-    static constexpr int kOffFin = GROUP * kHeadDim * 4;
-    static constexpr int kOffLutK = 2 * GROUP * kHeadDim * 4;
-    static constexpr int kOffLutV = kOffLutK + kKPairs * 256;
-    static constexpr int kExtraBytes = kOffLutV + 2048 + kVCodes * 128;
-    __device__ __forceinline__ static uint32_t lutv_base(const uint8_t* extra) {
-        return (smem_u32(extra) + kOffLutV + 2047u) & ~2047u;
+    static constexpr int kKPairs = 1 << (2 * KBITS);
+    // Lookup tables, one column per lane (no bank conflicts), 8-byte entries:
+    //   keys    [code pairs (dims d, d + 1 of a token)][32 lanes]: half2 (hi parts of the two centroids), half2 (lo parts)
+    //   values  3-bit: [code pairs][32 lanes]: half2 (hi, lo) of dim d, half2 (hi, lo) of dim d + 1 -- the two A registers of an
+    //           output m-tile.  4-bit values with 4-bit keys read the key table (same codebook) and re-pair the halves with two
+    //           prmt; 4-bit values with 3-bit keys keep a table of their own.
+    static constexpr bool kVSharesK = (VBITS == KBITS);
+    static constexpr int kVPairs = 1 << (2 * VBITS);
+    static constexpr int kLutKBytes = kKPairs * 256;                       // 64 KB for 4-bit keys, 16 KB for 3-bit
+    static constexpr int kLutVBytes = kVSharesK ? 0 : kVPairs * 256;
+    static constexpr bool kValuesFirst = kLutVBytes > kLutKBytes;          // the 64 KB table takes the 64 KB boundary
+    static constexpr int kExtraBytes = -1;                                 // DecodeSmem: the kernel takes the CTA maximum
+
+    __device__ __forceinline__ static TurboSmemPlan plan(const uint8_t* extra) {
+        TurboSmemPlan pl;
+        const uint32_t first = (smem_u32(extra) + 65535u) & ~65535u;
+        pl.lut_k = kValuesFirst ? first + kLutVBytes : first;
+        pl.lut_v = kVSharesK ? pl.lut_k : (kValuesFirst ? first : first + kLutKBytes);
+        pl.rows = first + kLutKBytes + kLutVBytes;
+        return pl;
     }
+    // generic pointer to a window address at or above `extra`
+    __device__ __forceinline__ static float* window_ptr(uint8_t* extra, uint32_t addr) {
+        return reinterpret_cast<float*>(extra + (addr - smem_u32(extra)));
+    }
+    __device__ __forceinline__ static float* fin_ptr(uint8_t* extra) { return window_ptr(extra, plan(extra).rows + GROUP * kHeadDim * 4); }
 
     struct State {
         uint32_t qh[8][2], ql[8][2];   // B fragments of the rotated queries per k-step: fp16 hi and lo parts
         float m[2], l[2];              // heads 2c, 2c + 1
         float acc[8][4];               // O^T fragments: [m-tile][(row g | row g + 8) x (head 2c | 2c + 1)]
+        uint32_t lut_k, lut_v;         // this lane's column of the tables: table address | lane << 3
         __device__ __forceinline__ void reset() {
             m[0] = m[1] = -INFINITY;
             l[0] = l[1] = 0.f;
@@ -140,29 +165,40 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         }
     };
 
-    __device__ static void init_extra(uint8_t* extra, int tid) {
-        const uint32_t lk = smem_u32(extra) + kOffLutK, lv = lutv_base(extra);
+    // false when the plan does not fit the CTA's shared memory (the window base is not where this layout expects it)
+    __device__ static bool init_extra(uint8_t* extra, int tid, int smem_bytes_after_extra) {
+        const TurboSmemPlan pl = plan(extra);
+        if (pl.rows + 2u * GROUP * kHeadDim * 4u > smem_u32(extra) + static_cast<uint32_t>(smem_bytes_after_extra)) return false;
         for (int e = tid; e < kKPairs * 32; e += Base::kThreads) {
             const int pv = e >> 5;
             const float c0 = __fmul_rn(tq_centroids<KBITS>()[pv & ((1 << KBITS) - 1)], tq_fp16_scale<KBITS>());
             const float c1 = __fmul_rn(tq_centroids<KBITS>()[pv >> KBITS], tq_fp16_scale<KBITS>());
             const __half2 hi = __floats2half2_rn(c0, c1);
             const float2 hf = __half22float2(hi);
-            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(lk + 8 * e), "r"(*reinterpret_cast<const uint32_t*>(&hi)),
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(pl.lut_k + 8 * e), "r"(*reinterpret_cast<const uint32_t*>(&hi)),
                          "r"(pack_half2(c0 - hf.x, c1 - hf.y))
                          : "memory");
         }
-        for (int e = tid; e < kVCodes * 32; e += Base::kThreads) {
-            const float cv = __fmul_rn(tq_centroids<VBITS>()[e >> 5], tq_fp16_scale<VBITS>());
-            const float hi = __half2float(__float2half_rn(cv));
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lv + 4 * e), "r"(pack_half2(hi, cv - hi)) : "memory");
+        if constexpr (!kVSharesK) {
+            for (int e = tid; e < kVPairs * 32; e += Base::kThreads) {
+                const int pv = e >> 5;
+                const float c0 = __fmul_rn(tq_centroids<VBITS>()[pv & ((1 << VBITS) - 1)], tq_fp16_scale<VBITS>());
+                const float c1 = __fmul_rn(tq_centroids<VBITS>()[pv >> VBITS], tq_fp16_scale<VBITS>());
+                const float h0 = __half2float(__float2half_rn(c0)), h1 = __half2float(__float2half_rn(c1));
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(pl.lut_v + 8 * e), "r"(pack_half2(h0, c0 - h0)), "r"(pack_half2(h1, c1 - h1))
+                             : "memory");
+            }
         }
+        return true;
     }
 
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t* extra,
                                   int warp, int lane, int) {
-        float* qrot = reinterpret_cast<float*>(extra + kOffQrot);
+        const TurboSmemPlan pl = plan(extra);
+        float* qrot = window_ptr(extra, pl.rows);
         Base::rotate_queries(p, qrot, qrow, cs, warp, lane);
+        st.lut_k = pl.lut_k | (lane << 3);
+        st.lut_v = pl.lut_v | (lane << 3);
         const int g = lane >> 2, c = lane & 3;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
@@ -178,59 +214,85 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         st.reset();
     }
 
-    template <int S>
-    __device__ __forceinline__ static void score_steps(float (&s)[4], uint32_t lutk, const uint32_t (&k0)[KBITS],
-                                                       const uint32_t (&k1)[KBITS], const State& st) {
-        if constexpr (S < 8) {
-            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-            lds_u32x2(lutk + pair_offset<KBITS, 2 * S, 8>(k0), a0, e0);
-            lds_u32x2(lutk + pair_offset<KBITS, 2 * S, 8>(k1), a1, e1);
-            lds_u32x2(lutk + pair_offset<KBITS, 2 * S + 1, 8>(k0), a2, e2);
-            lds_u32x2(lutk + pair_offset<KBITS, 2 * S + 1, 8>(k1), a3, e3);
-            mma_m16n8k16(s, a0, a1, a2, a3, st.qh[S][0], st.qh[S][1]);
-            mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
-            mma_m16n8k16(s, e0, e1, e2, e3, st.qh[S][0], st.qh[S][1]);
-            score_steps<S + 1>(s, lutk, k0, k1, st);
+    // Address of the key-table entry of code pair PI (dims 2 PI, 2 PI + 1 of the lane's 32-code chunk).
+    template <int PI>
+    __device__ __forceinline__ static uint32_t key_entry(const uint32_t (&w)[KBITS], uint32_t lut) {
+        if constexpr (KBITS == 4) {
+            return __byte_perm(w[PI >> 2], lut, 0x7604 | ((PI & 3) << 4));   // byte PI of the chunk -> byte 1 of the address
+        } else {
+            constexpr int bit = PI * 2 * KBITS, word = bit >> 5, sh = bit & 31;
+            constexpr uint32_t mask = static_cast<uint32_t>(kKPairs - 1) << 8;
+            uint32_t v;
+            if constexpr (sh + 2 * KBITS > 32) v = __funnelshift_r(w[word], w[word + 1], sh - 8);
+            else if constexpr (sh >= 8) v = w[word] >> (sh - 8);
+            else v = w[word] << (8 - sh);
+            return (v & mask) | lut;
         }
     }
 
-    // Address of the table entry of code I (0..15) of a 16-code chunk held as (lo: codes' bits 0..31, hi: the rest).
-    template <int I>
-    __device__ __forceinline__ static uint32_t value_entry(uint32_t lutv, uint32_t lo, uint32_t hi) {
-        constexpr int bit = I * VBITS;
-        constexpr uint32_t mask = static_cast<uint32_t>(kVCodes - 1) << 7;
-        uint32_t v;
-        if constexpr (bit + VBITS <= 32) {
-            if constexpr (bit >= 7) v = lo >> (bit - 7); else v = lo << (7 - bit);
-        } else if constexpr (bit >= 32) {
-            if constexpr (bit - 32 >= 7) v = hi >> (bit - 32 - 7); else v = hi << (7 - (bit - 32));
-        } else {
-            v = __funnelshift_r(lo, hi, bit - 7);   // the code straddles the two words (3-bit codes only; bit = 30)
+    template <int S>
+    __device__ __forceinline__ static void score_steps(float (&s)[4], const uint32_t (&k0)[KBITS], const uint32_t (&k1)[KBITS],
+                                                       const State& st) {
+        if constexpr (S < 8) {
+            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+            lds_u32x2(key_entry<2 * S>(k0, st.lut_k), a0, e0);
+            lds_u32x2(key_entry<2 * S>(k1, st.lut_k), a1, e1);
+            lds_u32x2(key_entry<2 * S + 1>(k0, st.lut_k), a2, e2);
+            lds_u32x2(key_entry<2 * S + 1>(k1, st.lut_k), a3, e3);
+            mma_m16n8k16(s, a0, a1, a2, a3, st.qh[S][0], st.qh[S][1]);
+            mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
+            mma_m16n8k16(s, e0, e1, e2, e3, st.qh[S][0], st.qh[S][1]);
+            score_steps<S + 1>(s, k0, k1, st);
         }
-        return (v & mask) | lutv;
+    }
+
+    // The two A registers of output m-tile T for one token: half2 (hi, lo) of dims 16g + 2T and 16g + 2T + 1, looked up by the
+    // code pair T of the token's 16-code chunk (lo: bits 0..31, hi: the rest).
+    template <int T>
+    __device__ __forceinline__ static void value_pair(uint32_t lut, uint32_t lo, uint32_t hi, uint32_t& a_even, uint32_t& a_odd) {
+        uint32_t addr;
+        if constexpr (VBITS == 4) {
+            addr = __byte_perm(T < 4 ? lo : hi, lut, 0x7604 | ((T & 3) << 4));
+        } else {
+            constexpr int bit = T * 2 * VBITS;
+            constexpr uint32_t mask = static_cast<uint32_t>(kVPairs - 1) << 8;
+            uint32_t v;
+            if constexpr (bit < 32 && bit + 2 * VBITS > 32) v = __funnelshift_r(lo, hi, bit - 8);
+            else if constexpr (bit >= 32) { if constexpr (bit - 32 >= 8) v = hi >> (bit - 32 - 8); else v = hi << (8 - (bit - 32)); }
+            else if constexpr (bit >= 8) v = lo >> (bit - 8);
+            else v = lo << (8 - bit);
+            addr = (v & mask) | lut;
+        }
+        uint32_t x, y;
+        lds_u32x2(addr, x, y);
+        if constexpr (kVSharesK) {   // key-table layout (hi, hi), (lo, lo) -> (hi, lo) per dim
+            a_even = __byte_perm(x, y, 0x5410);
+            a_odd = __byte_perm(x, y, 0x7632);
+        } else {
+            a_even = x;
+            a_odd = y;
+        }
     }
 
     // m-tile T of O^T: dims 16g + 2T (row g) and 16g + 2T + 1 (row g + 8), both k-steps (tokens c, c + 4 | c + 8, c + 12).
     template <int T>
-    __device__ __forceinline__ static void value_tiles(State& st, uint32_t lutv, const uint32_t (&vlo)[4], const uint32_t (&vhi)[4],
+    __device__ __forceinline__ static void value_tiles(State& st, const uint32_t (&vlo)[4], const uint32_t (&vhi)[4],
                                                        const uint32_t (&bh)[4], const uint32_t (&bl)[4]) {
         if constexpr (T < 8) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                const uint32_t a0 = lds_u32(value_entry<2 * T>(lutv, vlo[2 * j], vhi[2 * j]));
-                const uint32_t a1 = lds_u32(value_entry<2 * T + 1>(lutv, vlo[2 * j], vhi[2 * j]));
-                const uint32_t a2 = lds_u32(value_entry<2 * T>(lutv, vlo[2 * j + 1], vhi[2 * j + 1]));
-                const uint32_t a3 = lds_u32(value_entry<2 * T + 1>(lutv, vlo[2 * j + 1], vhi[2 * j + 1]));
+                uint32_t a0, a1, a2, a3;
+                value_pair<T>(st.lut_v, vlo[2 * j], vhi[2 * j], a0, a1);
+                value_pair<T>(st.lut_v, vlo[2 * j + 1], vhi[2 * j + 1], a2, a3);
                 mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bh[2 * j], bh[2 * j + 1]);
                 mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bl[2 * j], bl[2 * j + 1]);
             }
-            value_tiles<T + 1>(st, lutv, vlo, vhi, bh, bl);
+            value_tiles<T + 1>(st, vlo, vhi, bh, bl);
         }
     }
 
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
                                         const uint8_t* extra, int lane) {
-        const uint32_t lutk = smem_u32(extra) + kOffLutK + 8 * lane, lutv = lutv_base(extra) + 4 * lane;
         const int g = lane >> 2, c = lane & 3;
         const int tk0 = (g >> 1) + 4 * (g & 1);   // token behind S row g (row g + 8: tk0 + 8)
         const uint32_t sbase = smem_u32(stage);
@@ -266,7 +328,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         const float sc = p.scale_log2 * inv_sk;
 
         float s[4] = {0.f, 0.f, 0.f, 0.f};   // (token tk0 | tk0 + 8) x (head 2c | 2c + 1)
-        score_steps<0>(s, lutk, k0, k1, st);
+        score_steps<0>(s, k0, k1, st);
         s[0] = ok0 ? (kn0 * s[0]) * sc : -INFINITY;
         s[1] = ok0 ? (kn0 * s[1]) * sc : -INFINITY;
         s[2] = ok1 ? (kn1 * s[2]) * sc : -INFINITY;
@@ -309,7 +371,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         const uint32_t y1 = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
         const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
         const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
-        value_tiles<0>(st, lutv, vlo, vhi, bh, bl);
+        value_tiles<0>(st, vlo, vhi, bh, bl);
     }
 };
 
