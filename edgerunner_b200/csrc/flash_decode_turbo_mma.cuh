@@ -14,9 +14,8 @@
 // indexed by a SINGLE code and returns half2(hi, lo) of its centroid: the two halves sit on adjacent contraction labels
 // (2c, 2c + 1) and the probability of that token is duplicated on both, which makes one mma.k16 cover 8 tokens with
 // fp32-accurate values: O^T += [Vh | Vl] . [p ; p].  Thread (g, c) owns dims [16g, 16g + 16) (m-tile mt: row g -> dim
-// 16g + 2mt, row g + 8 -> dim 16g + 2mt + 1) of tokens c, c + 4, c + 8, c + 12, a contiguous 2 * bits bytes per token.  The S
-// rows are labelled so that the transposed probabilities land on exactly those tokens: S row label n < 8 is token n / 2 +
-// 4 (n % 2), label n + 8 is that token + 8 (movmatrix.trans of the S fragment hands thread (g', c') labels 2c', 2c' + 1).
+// 16g + 2mt, row g + 8 -> dim 16g + 2mt + 1) of tokens 2c, 2c + 1, 2c + 8, 2c + 9, a contiguous 2 * bits bytes per token: the
+// tokens movmatrix.trans of the S fragment (rows g, g + 8) hands thread (g', c') -- rows 2c', 2c' + 1 and 2c' + 8, 2c' + 9.
 //
 // Queries, probabilities and all centroids therefore carry ~22 significant bits (fp16 hi + lo), which keeps the outputs
 // within the element-wise 2e-3 bound of the fp32 CPU statement.  Tables hold sigma * centroid with a per-codebook sigma
@@ -274,7 +273,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         }
     }
 
-    // m-tile T of O^T: dims 16g + 2T (row g) and 16g + 2T + 1 (row g + 8), both k-steps (tokens c, c + 4 | c + 8, c + 12).
+    // m-tile T of O^T: dims 16g + 2T (row g) and 16g + 2T + 1 (row g + 8), both k-steps (tokens 2c, 2c + 1 | 2c + 8, 2c + 9).
     template <int T>
     __device__ __forceinline__ static void value_tiles(State& st, const uint32_t (&vlo)[4], const uint32_t (&vhi)[4],
                                                        const uint32_t (&bh)[4], const uint32_t (&bl)[4]) {
@@ -294,16 +293,16 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
                                         const uint8_t* extra, int lane) {
         const int g = lane >> 2, c = lane & 3;
-        const int tk0 = (g >> 1) + 4 * (g & 1);   // token behind S row g (row g + 8: tk0 + 8)
+        const int tk0 = g;                          // token behind S row g (row g + 8: g + 8)
         const uint32_t sbase = smem_u32(stage);
         const uint32_t kc = sbase + ((unit * kUnitTokens + tk0) * Base::kKW + c * KBITS) * 4;
         uint32_t k0[KBITS], k1[KBITS], vlo[4], vhi[4];
         load_code_chunk<KBITS>(kc, k0);
         load_code_chunk<KBITS>(kc + 32 * Base::kKW, k1);
-        // value codes: dims [16g, 16g + 16) of tokens c + 4j -- 2 * VBITS bytes at byte 2 * VBITS * g of the row
+        // value codes: dims [16g, 16g + 16) of tokens 2c, 2c + 1, 2c + 8, 2c + 9 -- 2 * VBITS bytes at byte 2 * VBITS * g of the row
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t row = sbase + Base::kKcBytes + (unit * kUnitTokens + c + 4 * j) * Base::kVW * 4;
+            const uint32_t row = sbase + Base::kKcBytes + (unit * kUnitTokens + 2 * c + (j & 1) + 8 * (j >> 1)) * Base::kVW * 4;
             if constexpr (VBITS == 4) {
                 asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(vlo[j]), "=r"(vhi[j]) : "r"(row + 8 * g) : "memory");
             } else if constexpr (VBITS == 3) {
@@ -359,8 +358,8 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                 st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
             }
         }
-        // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed: thread (g', c') receives head g' of the tokens behind
-        // labels 2c', 2c' + 1 (c', c' + 4) and, from the rows g + 8, of c' + 8, c' + 12; each value is duplicated on the two
+        // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed: thread (g', c') receives head g' of tokens 2c', 2c' + 1
+        // and, from the rows g + 8, of 2c' + 8, 2c' + 9; each value is duplicated on the two
         // contraction labels that carry the hi and the lo half of a centroid
         const float w0 = p0 * vn0, w1 = p1 * vn0, w2 = p2 * vn1, w3 = p3 * vn1;
         const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
