@@ -33,7 +33,7 @@ class ERRoPEParams(C.Structure):
 class er_kv_config(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("max_seq_len", "num_layers", "num_kv_heads", "head_dim", "precision",
                                           "key_type", "value_type", "norm_format", "max_batch", "layout",
-                                          "page_size", "num_pages", "prefill_kernel")] + [("reserved", C.c_uint32 * 3)]
+                                          "page_size", "num_pages", "prefill_kernel", "decode_kernel")] + [("reserved", C.c_uint32 * 2)]
 
 
 class er_kv_buffers(C.Structure):

@@ -411,6 +411,7 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
     }
     if (c->prefill_kernel > ER_PREFILL_KERNEL_MMA_SYNC) return fail(ER_ERR_INVALID_ARGUMENT, "unknown prefill_kernel %u", c->prefill_kernel);
+    if (c->decode_kernel > ER_DECODE_KERNEL_SLIM) return fail(ER_ERR_INVALID_ARGUMENT, "unknown decode_kernel %u", c->decode_kernel);
     if (er_device_count() <= 0) return fail(ER_ERR_CUDA, "no CUDA device: this backend has no CPU fallback");
     er_kv* kv = new er_kv();
     kv->cfg = *c;
@@ -1195,9 +1196,23 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         else if (kv->q8)
             rc = decode_status(launch_decode_q8(group, p, kv->num_sms, stream), group, 8, 8);
         else {
-            if (kv->token_major)
-                encode_token_major_maps(p, group, kv->cfg.num_layers, kv->cfg.max_batch, kv->cfg.max_seq_len, kv->cfg.num_kv_heads);
-            rc = dispatch_decode_f16(group, p, kv->num_sms, stream);
+            // small launches (one layer of a small batch) skip the persistent kernel's staging pipeline
+            const uint64_t capacity_bytes = static_cast<uint64_t>(l1 - l0) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kv->cfg.max_seq_len * 2 * kRowBytesF16;
+            const bool want_slim = kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM ||
+                                   (kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO && capacity_bytes <= (128ull << 20));
+            int src = kNotBuilt;
+            if (want_slim && p.trace == nullptr && kv->probe_withhold_tiles == 0) {
+                const int items = static_cast<int>((l1 - l0) * kv->cfg.max_batch * kv->cfg.num_kv_heads);
+                const int splits = decode_slim_splits(group, items, kv->num_sms, kScratchFloatsPerCta * static_cast<size_t>(std::max(kv->num_sms, 1)));
+                if (splits > 0) src = launch_decode_slim(group, p, splits, stream);
+            }
+            if (src != kNotBuilt) {
+                rc = decode_status(src, group, 16, 16);
+            } else {
+                if (kv->token_major)
+                    encode_token_major_maps(p, group, kv->cfg.num_layers, kv->cfg.max_batch, kv->cfg.max_seq_len, kv->cfg.num_kv_heads);
+                rc = dispatch_decode_f16(group, p, kv->num_sms, stream);
+            }
         }
         if (rc != ER_OK) return rc;
     }

@@ -60,13 +60,14 @@ def step_params(rope_theta=10000.0, rope_scaling=1.0, softmax_scale=0.0, apply_r
 class KVCache:
     def __init__(self, max_seq_len, num_layers, num_kv_heads, head_dim, precision, *, key_type=TurboQuantFixedType.turbo3,
                  value_type=TurboQuantFixedType.turbo3, norm_format=NormFormat.float32, max_batch=1,
-                 layout=Layout.head_major, page_size=0, num_pages=0, prefill_kernel=0):
+                 layout=Layout.head_major, page_size=0, num_pages=0, prefill_kernel=0, decode_kernel=0):
         cfg = er_kv_config()
         cfg.max_seq_len, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim = max_seq_len, num_layers, num_kv_heads, head_dim
         cfg.precision, cfg.key_type, cfg.value_type = int(precision), int(key_type), int(value_type)
         cfg.norm_format, cfg.max_batch, cfg.layout = int(norm_format), max_batch, int(layout)
         cfg.page_size, cfg.num_pages = page_size, num_pages
         cfg.prefill_kernel = int(prefill_kernel)     # 0 = automatic, 1 = always the mma.sync kernel (A/B measurements)
+        cfg.decode_kernel = int(decode_kernel)       # float16 caches: 0 = automatic, 1 = persistent kernel, 2 = slim kernel
         self._h = C.c_void_p()
         self._destroy = lib().er_kv_destroy      # held by the object: close() may run while the interpreter shuts down
         check(lib().er_kv_create(C.byref(cfg), C.byref(self._h)))

@@ -112,6 +112,13 @@ enum { ER_TQ_NORM_FLOAT32 = 0, ER_TQ_NORM_FLOAT16 = 1 };
  * and the mma.sync kernel otherwise; MMA_SYNC always runs the latter (A/B measurements). */
 enum { ER_PREFILL_KERNEL_AUTO = 0, ER_PREFILL_KERNEL_MMA_SYNC = 1 };
 
+/* Decode kernel choice for float16 caches.  The reference dispatches attention once per layer
+ * (Sources/EdgeRunner/Models/LlamaLanguageModel.swift:3867-3881): a few MB of rows per call.  AUTO runs such small calls
+ * (capacity of the addressed rows up to 128 MB, GQA group 1/2/4, no sliding window) on a kernel without a staging
+ * pipeline, and everything else on the persistent stream-K kernel; PERSISTENT / SLIM force one of them where its shape
+ * rules allow (parity tests run both). */
+enum { ER_DECODE_KERNEL_AUTO = 0, ER_DECODE_KERNEL_PERSISTENT = 1, ER_DECODE_KERNEL_SLIM = 2 };
+
 typedef struct {
     uint32_t max_seq_len;   /* ring length per sequence (tokens) */
     uint32_t num_layers;
@@ -126,7 +133,8 @@ typedef struct {
     uint32_t page_size;     /* tokens per page, multiple of 16 (PAGED only) */
     uint32_t num_pages;     /* pages in the shared pool (PAGED only) */
     uint32_t prefill_kernel; /* ER_PREFILL_KERNEL_*: which chunked-prefill kernel er_kv_attention_prefill may use */
-    uint32_t reserved[3];
+    uint32_t decode_kernel;  /* ER_DECODE_KERNEL_*: float16 caches */
+    uint32_t reserved[2];
 } er_kv_config;
 
 typedef struct er_kv er_kv;

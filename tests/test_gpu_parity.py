@@ -209,8 +209,11 @@ def _oracle_dense_cache(oracle, K, V, theta):
     return kc, oracle.f32_to_f16_bits(V)
 
 
+KERNELS = [("persistent", 1), ("slim", 2)]       # er_kv_config.decode_kernel: both fp16 decode kernels run every dense case
+
+
 def _run_dense_config(er, oracle, torch, layout, L, B, Hq, Hkv, ctx, steps, seed, theta=THETA_QWEN3, page_size=0,
-                      ragged=False, max_seq_len=None):
+                      ragged=False, max_seq_len=None, decode_kernel=0):
     D = 128
     rng = rng_for(seed)
     lens = [ctx] * B if not ragged else [int(x) for x in rng.integers(max(1, ctx // 8), ctx + 1, size=B)]
@@ -223,7 +226,7 @@ def _run_dense_config(er, oracle, torch, layout, L, B, Hq, Hkv, ctx, steps, seed
         num_pages = pages_per_seq * B + 3
         kw = dict(page_size=page_size, num_pages=num_pages)
         alloc = er.BlockTableAllocator(num_pages, page_size, free_order=rng.permutation(num_pages))
-    cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, **kw)
+    cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, decode_kernel=decode_kernel, **kw)
     if alloc:
         for b in range(B):
             cache.set_block_table(b, alloc.ensure(b, lens[b] + steps))
@@ -267,12 +270,13 @@ def _run_dense_config(er, oracle, torch, layout, L, B, Hq, Hkv, ctx, steps, seed
     return worst
 
 
-def test_config0_single_layer_decode(er, oracle, torch):
+@pytest.mark.parametrize("kernel,dk", KERNELS)
+def test_config0_single_layer_decode(er, oracle, torch, kernel, dk):
     """Configuration 0: Qwen3-0.6B-shaped layer, 16 q heads / 8 kv heads / head_dim 128, fp16 cache pre-filled with
     512 tokens, append 1 token, RoPE theta 1e6 at positions 0..512, output fp32 [16,128]."""
     for layout in (er.Layout.head_major, er.Layout.token_major):
-        worst = _run_dense_config(er, oracle, torch, layout, L=1, B=1, Hq=16, Hkv=8, ctx=512, steps=1, seed=0)
-        print("config0 %s max rel err %.3e" % (layout.name, worst))
+        worst = _run_dense_config(er, oracle, torch, layout, L=1, B=1, Hq=16, Hkv=8, ctx=512, steps=1, seed=0, decode_kernel=dk)
+        print("config0 %s %s kernel max rel err %.3e" % (layout.name, kernel, worst))
 
 
 def test_config0_against_committed_golden(er, oracle, torch):
@@ -294,18 +298,20 @@ def test_config0_against_committed_golden(er, oracle, torch):
     assert np.array_equal(gv.view(np.uint16).reshape(513, 8, 128)[[0, 1, 255, 511, 512]], gold["v_rows"])
 
 
-def test_multilayer_steps_all_layouts(er, oracle, torch):
+@pytest.mark.parametrize("kernel,dk", KERNELS)
+def test_multilayer_steps_all_layouts(er, oracle, torch, kernel, dk):
     """Configuration-1-shaped (several independent layers, consecutive decode steps) at a size the oracle finishes
     quickly, in every storage layout; odd context so tiles end ragged."""
     for layout, ps in ((er.Layout.head_major, 0), (er.Layout.token_major, 0), (er.Layout.paged, 16), (er.Layout.paged, 64)):
-        _run_dense_config(er, oracle, torch, layout, L=3, B=1, Hq=16, Hkv=8, ctx=777, steps=3, seed=3, page_size=ps)
+        _run_dense_config(er, oracle, torch, layout, L=3, B=1, Hq=16, Hkv=8, ctx=777, steps=3, seed=3, page_size=ps, decode_kernel=dk)
 
 
-def test_batched_ragged_paged_llama_shape(er, oracle, torch):
+@pytest.mark.parametrize("kernel,dk", KERNELS)
+def test_batched_ragged_paged_llama_shape(er, oracle, torch, kernel, dk):
     """Configuration-3-shaped: 32 q heads / 8 kv heads (group 4), 16-token pages, block tables a seeded random
     permutation of a shared pool, ragged context lengths."""
     _run_dense_config(er, oracle, torch, er.Layout.paged, L=2, B=5, Hq=32, Hkv=8, ctx=1500, steps=2, seed=2,
-                      theta=5e5, page_size=16, ragged=True)
+                      theta=5e5, page_size=16, ragged=True, decode_kernel=dk)
 
 
 @pytest.mark.parametrize("layout,page_size", [("head_major", 0), ("token_major", 0), ("paged", 32)])
@@ -313,22 +319,25 @@ def test_group8_and_group4_tensor_core_policy(er, oracle, torch, layout, page_si
     """GQA groups 4 and 8 on fp16 rows run both contractions on the tensor cores: ragged batches, several steps, every
     layout, contexts from a single row to several tiles."""
     lay = getattr(er.Layout, layout)
-    _run_dense_config(er, oracle, torch, lay, L=2, B=3, Hq=32, Hkv=4, ctx=900, steps=3, seed=40, page_size=page_size, ragged=True)
-    _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=2, ctx=1, steps=19, seed=41, page_size=page_size)
-    _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=4, ctx=3, steps=20, seed=42, page_size=page_size)
+    for dk in (1, 0):      # group 8 exists in the persistent kernel only; 0 = automatic choice (slim for group 4 here)
+        _run_dense_config(er, oracle, torch, lay, L=2, B=3, Hq=32, Hkv=4, ctx=900, steps=3, seed=40, page_size=page_size, ragged=True, decode_kernel=dk)
+        _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=2, ctx=1, steps=19, seed=41, page_size=page_size, decode_kernel=dk)
+        _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=4, ctx=3, steps=20, seed=42, page_size=page_size, decode_kernel=dk)
 
 
-def test_group1_and_tiny_contexts(er, oracle, torch):
-    _run_dense_config(er, oracle, torch, er.Layout.head_major, L=1, B=3, Hq=4, Hkv=4, ctx=40, steps=2, seed=5, ragged=True)
-    _run_dense_config(er, oracle, torch, er.Layout.token_major, L=2, B=2, Hq=8, Hkv=2, ctx=1, steps=18, seed=6)
+@pytest.mark.parametrize("kernel,dk", KERNELS)
+def test_group1_and_tiny_contexts(er, oracle, torch, kernel, dk):
+    _run_dense_config(er, oracle, torch, er.Layout.head_major, L=1, B=3, Hq=4, Hkv=4, ctx=40, steps=2, seed=5, ragged=True, decode_kernel=dk)
+    _run_dense_config(er, oracle, torch, er.Layout.token_major, L=2, B=2, Hq=8, Hkv=2, ctx=1, steps=18, seed=6, decode_kernel=dk)
 
 
-def test_ring_wrap_decode(er, oracle, torch):
+@pytest.mark.parametrize("kernel,dk", KERNELS)
+def test_ring_wrap_decode(er, oracle, torch, kernel, dk):
     """More decode steps than ring slots: new rows overwrite the oldest slots and attention covers the whole ring
     (reads ignore the wrap: softmax is order-independent and K carries its absolute RoPE position)."""
     D, Hq, Hkv, T = 128, 4, 2, 32
     rng = rng_for(9)
-    cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16)
+    cache = er.KVCache(T, 1, Hkv, D, er.Precision.float16, decode_kernel=dk)
     sp = er.step_params(rope_theta=1e4)
     kc = np.zeros((T, Hkv, D), np.uint16)
     vc = np.zeros((T, Hkv, D), np.uint16)
@@ -355,23 +364,24 @@ def test_append_then_attention_split_calls(er, oracle, torch):
     """er_kv_append_rope_kv + er_kv_attention_decode(pending=1) + er_kv_advance == er_kv_decode_step."""
     rng = rng_for(12)
     L, B, Hq, Hkv, D, ctx = 2, 2, 8, 4, 128, 300
-    caches = [er.KVCache(512, L, Hkv, D, er.Precision.float16, max_batch=B) for _ in range(2)]
-    sp = er.step_params(rope_theta=1e6)
-    for l in range(L):
-        for b in range(B):
-            K, V = normal_f16(rng, (ctx, Hkv, D)), normal_f16(rng, (ctx, Hkv, D))
-            for c in caches:
-                c.write_rows(l, b, 0, ctx, dev(torch, K), dev(torch, V), sp)
-    q, k, v = (dev(torch, normal_f16(rng, (L, B, h, D))) for h in (Hq, Hkv, Hkv))
-    o1 = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
-    o2 = torch.empty_like(o1)
-    caches[0].decode_step(q, k, v, o1, Hq, sp)
-    caches[1].append_rope_kv(k, v, sp)
-    caches[1].attention_decode(q, o2, Hq, sp, pending=1)
-    caches[1].advance(1)
-    torch.cuda.synchronize()
-    assert torch.equal(o1, o2)
-    assert caches[0].total_written(1, 1) == caches[1].total_written(1, 1) == ctx + 1
+    for dk in (1, 2):
+        caches = [er.KVCache(512, L, Hkv, D, er.Precision.float16, max_batch=B, decode_kernel=dk) for _ in range(2)]
+        sp = er.step_params(rope_theta=1e6)
+        for l in range(L):
+            for b in range(B):
+                K, V = normal_f16(rng, (ctx, Hkv, D)), normal_f16(rng, (ctx, Hkv, D))
+                for c in caches:
+                    c.write_rows(l, b, 0, ctx, dev(torch, K), dev(torch, V), sp)
+        q, k, v = (dev(torch, normal_f16(rng, (L, B, h, D))) for h in (Hq, Hkv, Hkv))
+        o1 = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
+        o2 = torch.empty_like(o1)
+        caches[0].decode_step(q, k, v, o1, Hq, sp)
+        caches[1].append_rope_kv(k, v, sp)
+        caches[1].attention_decode(q, o2, Hq, sp, pending=1)
+        caches[1].advance(1)
+        torch.cuda.synchronize()
+        assert torch.equal(o1, o2), dk
+        assert caches[0].total_written(1, 1) == caches[1].total_written(1, 1) == ctx + 1
 
 
 def test_decode_step_host_buffers(er, oracle, torch):
@@ -628,9 +638,9 @@ def test_config2_shape_long_context_sampled(er, oracle, torch):
 
 # --------------------------------------------------------------------------------------------- Q/K head norm (fused_qk_norm_rope_neox)
 
-@pytest.mark.parametrize("precision,Hq,Hkv", [("float16", 16, 8), ("float16", 32, 8), ("float16", 32, 4), ("turbo", 16, 8),
-                                              ("q8_0", 16, 8)])
-def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision, Hq, Hkv):
+@pytest.mark.parametrize("precision,Hq,Hkv,dk", [("float16", 16, 8, 1), ("float16", 16, 8, 2), ("float16", 32, 8, 1), ("float16", 32, 8, 2),
+                                                 ("float16", 32, 4, 1), ("turbo", 16, 8, 0), ("q8_0", 16, 8, 0)])
+def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision, Hq, Hkv, dk):
     """er_step_params.q_norm_weight / k_norm_weight: per-head RMS norm before RoPE (fused_qk_norm_rope_neox,
     Shaders/RoPE.metal:119-173) on every cache kind.  The K rows the cache ends up holding are compared bit for bit with
     the oracle's norm -> RoPE -> store; the attention outputs within the usual bounds."""
@@ -642,7 +652,7 @@ def test_qk_head_norm_then_rope_decode_and_prefill(er, oracle, torch, precision,
     sp = er.step_params(rope_theta=theta, q_norm_weight=dwq, k_norm_weight=dwk, rms_eps=eps, norm_weight_layer_stride=D)
     T = 128
     if precision == "float16":
-        cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B)
+        cache = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, decode_kernel=dk)   # 1 = persistent, 2 = slim kernel
     elif precision == "turbo":
         cache = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=3, max_batch=B)
     else:
