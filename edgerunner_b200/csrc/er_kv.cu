@@ -1201,10 +1201,14 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
             const bool want_slim = kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM ||
                                    (kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO && capacity_bytes <= (128ull << 20));
             int src = kNotBuilt;
-            if (want_slim && p.trace == nullptr && kv->probe_withhold_tiles == 0) {
+            if (want_slim && kv->probe_withhold_tiles == 0) {
                 const int items = static_cast<int>((l1 - l0) * kv->cfg.max_batch * kv->cfg.num_kv_heads);
-                const int splits = decode_slim_splits(group, items, kv->num_sms, kScratchFloatsPerCta * static_cast<size_t>(std::max(kv->num_sms, 1)));
+                const int splits = decode_slim_splits(group, items, static_cast<int>((kv->cfg.max_seq_len + 15) / 16), kv->num_sms,
+                                                      kScratchFloatsPerCta * static_cast<size_t>(std::max(kv->num_sms, 1)));
+                // diagnostics buffer: one row of stamps per CTA of this grid
+                p.trace = (kv->d_trace != nullptr && kv->trace_ctas >= static_cast<uint32_t>(items) * static_cast<uint32_t>(std::max(splits, 1))) ? kv->d_trace : nullptr;
                 if (splits > 0) src = launch_decode_slim(group, p, splits, stream);
+                if (src == kNotBuilt) p.trace = (kv->d_trace != nullptr && kv->trace_ctas >= static_cast<uint32_t>(kv->num_sms)) ? kv->d_trace : nullptr;
             }
             if (src != kNotBuilt) {
                 rc = decode_status(src, group, 16, 16);

@@ -20,7 +20,7 @@ int decode_dense_tile_tokens(int group);
 int encode_token_major_maps(DecodeParams& p, int group, uint64_t layers, uint64_t seqs, uint64_t slots, uint64_t kv_heads);
 // fp16 rows, small launches (decode_slim.cu): grid (splits, kv heads, (layer, sequence) pairs), no staging.  kNotBuilt when
 // the launch uses something only the persistent kernel has (ring ranges, sliding windows, sharded outputs, groups > 4).
-int decode_slim_splits(int group, int items, int num_sms, size_t scratch_floats);
+int decode_slim_splits(int group, int items, int max_units, int num_sms, size_t scratch_floats);
 int launch_decode_slim(int group, const DecodeParams& p, int splits, cudaStream_t stream);
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 int launch_decode_q8(int group, const DecodeParams& p, int grid, cudaStream_t stream);

@@ -70,7 +70,8 @@ def test_peer_store_epilogue_on_one_gpu(er):
         q = torch.as_tensor(rng.standard_normal((L, B, H, 128), dtype=np.float32)).cuda()
         for r in range(2):
             shard = HeadShard(H, Hkv, 2, r)
-            c = er.KVCache(256, L, shard.local_kv_heads, 128, getattr(er.Precision, precision), max_batch=B, **kw)
+            # decode_kernel=1: the sharded output layout exists in the persistent kernel, so the plain run uses it too (bitwise)
+            c = er.KVCache(256, L, shard.local_kv_heads, 128, getattr(er.Precision, precision), max_batch=B, decode_kernel=1, **kw)
             for l in range(L):
                 for b in range(B):
                     kk = torch.as_tensor(rng.standard_normal((T, shard.local_kv_heads, 128), dtype=np.float32)).cuda()
