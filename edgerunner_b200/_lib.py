@@ -85,6 +85,7 @@ SYMBOLS = {
     "er_rope_neox_f32_to_f16": (_i32, [_vp, _vp, C.POINTER(ERRoPEParams), _vp]),
     "er_quantize_q8_0_rows": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "er_turboquant_quantize_rows": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "er_turboquant_quantize_rows_outliers": (_i32, [_vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "er_gqa_attention_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),
     "er_gqa_attention_f16kv_static": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(ERGQAParams), _vp]),

@@ -22,6 +22,7 @@
 #include "prefill.cuh"
 #include "q8.cuh"
 #include "turboquant.cuh"
+#include "turboquant_outlier.cuh"
 
 using namespace er;
 
@@ -894,6 +895,28 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
     if (row_count == 0) return ER_OK;
     return launch_turbo_quantize_rows(source, row_count, source_row_stride, dst_row_base, static_cast<int>(bits), out_codes, out_signs,
                                       out_mask, out_meta, static_cast<cudaStream_t>(stream), check_launch);
+}
+
+int32_t er_turboquant_quantize_rows_outliers(const float* source, uint32_t row_count, uint32_t source_row_stride, uint32_t dst_row_base,
+                                             uint32_t regular_bits, uint32_t high_bits, uint32_t high_count, uint32_t use_quantization_benefit,
+                                             uint32_t* out_codes, uint32_t* out_signs, uint32_t* out_mask, float* out_meta, void* stream) {
+    if (!source || !out_codes || !out_signs || !out_mask || !out_meta) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (regular_bits < 2 || regular_bits > 4 || high_bits <= regular_bits || high_bits > 5 || high_count == 0 || high_count > kHeadDim)
+        return fail(ER_ERR_INVALID_ARGUMENT, "regular bits %u (2..4), high-precision bits %u (regular < high <= 5), channel count %u (1..128)",
+                    regular_bits, high_bits, high_count);
+    if (source_row_stride < kHeadDim || source_row_stride % 4 != 0) return fail(ER_ERR_SHAPE, "source_row_stride %u (>= 128, multiple of 4)", source_row_stride);
+    if (reinterpret_cast<uintptr_t>(source) & 15u) return fail(ER_ERR_INVALID_ARGUMENT, "source must be 16-byte aligned");
+    if (row_count == 0) return ER_OK;
+    TurboOutlierParams op{};
+    op.source = source; op.rows = row_count; op.stride = source_row_stride; op.dst_row_base = dst_row_base;
+    op.regular_bits = static_cast<int>(regular_bits); op.high_bits = static_cast<int>(high_bits); op.high_count = static_cast<int>(high_count);
+    op.use_benefit = use_quantization_benefit ? 1 : 0;
+    // TurboQuantLayout (TurboQuant.swift:275-319): base plane + side band, each rounded up to words
+    op.words_per_row = (kHeadDim * op.regular_bits + 31) / 32 + (op.high_count * (op.high_bits - op.regular_bits) + 31) / 32;
+    op.out_codes = out_codes; op.out_signs = out_signs; op.out_mask = out_mask; op.out_meta = out_meta;
+    const unsigned blocks = std::min<unsigned>((row_count + kOutlierWarps - 1) / kOutlierWarps, 148u * 8u);
+    tq_quantize_rows_outlier_kernel<<<blocks, kOutlierWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(op);
+    return check_launch("tq_quantize_rows_outlier_kernel");
 }
 
 // Shapes the persistent flash-decode / tensor-core prefill kernels are built for; everything else on raw buffers goes

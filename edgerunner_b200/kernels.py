@@ -134,6 +134,32 @@ class TurboQuantKernel:
                                                 ptr(out_codes), ptr(out_residual_signs), ptr(out_outlier_mask),
                                                 ptr(out_metadata), stream_ptr(stream)))
 
+    PRESETS = {"balanced": (3, 5, 32), "aggressive": (2, 3, 32)}   # TurboQuantPreset.descriptor (TurboQuant.swift:78-84, 117-124)
+
+    def encode_quantize_rows_outliers(self, source, row_count, source_row_stride, destination_row_base, regular_bits, high_bits,
+                                      high_count, use_quantization_benefit, out_codes, out_residual_signs, out_outlier_mask,
+                                      out_metadata, stream=None):
+        check(lib().er_turboquant_quantize_rows_outliers(ptr(source), row_count, source_row_stride, destination_row_base, regular_bits,
+                                                         high_bits, high_count, int(bool(use_quantization_benefit)), ptr(out_codes),
+                                                         ptr(out_residual_signs), ptr(out_outlier_mask), ptr(out_metadata),
+                                                         stream_ptr(stream)))
+
+    def execute_quantize_rows_preset(self, rows, preset, use_quantization_benefit=False):
+        """rows: [n, >=128] float32, preset "balanced" | "aggressive" -> (codes [n,w] u32, signs [n,4], mask [n,4], meta [n,2])."""
+        torch = _torch()
+        rb, hb, cnt = self.PRESETS[preset]
+        x = torch.as_tensor(np.ascontiguousarray(rows, dtype=np.float32)).cuda()
+        n, stride = x.shape
+        w = (128 * rb + 31) // 32 + (cnt * (hb - rb) + 31) // 32
+        codes = torch.full((n, w), -1, dtype=torch.int32, device="cuda")
+        signs = torch.full((n, 4), -1, dtype=torch.int32, device="cuda")
+        mask = torch.full((n, 4), -1, dtype=torch.int32, device="cuda")
+        meta = torch.full((n, 2), float("nan"), dtype=torch.float32, device="cuda")
+        self.encode_quantize_rows_outliers(x, n, stride, 0, rb, hb, cnt, use_quantization_benefit, codes, signs, mask, meta)
+        torch.cuda.synchronize()
+        return (codes.cpu().numpy().view(np.uint32), signs.cpu().numpy().view(np.uint32),
+                mask.cpu().numpy().view(np.uint32), meta.cpu().numpy())
+
     def execute_quantize_rows(self, rows, bits):
         """rows: [n, >=128] float32 -> (codes [n,w] u32, signs [n,4], mask [n,4], meta [n,2])."""
         torch = _torch()

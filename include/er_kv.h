@@ -82,8 +82,9 @@ enum {
     ER_ERR_DEVICE_TIMEOUT = -12 /* a bounded device-side wait gave up; see er_kv_device_status */
 };
 
-/* KVCache.Precision raw values (KVCache.swift:39-49). float8 / q8_0 / balanced / aggressive are accepted
- * by er_kv_create only to report ER_ERR_UNSUPPORTED_STORAGE. */
+/* KVCache.Precision raw values (KVCache.swift:39-49). float8 / balanced / aggressive are accepted by er_kv_create only
+ * to report ER_ERR_UNSUPPORTED_STORAGE (the balanced / aggressive row encoder exists as an operator:
+ * er_turboquant_quantize_rows_outliers). */
 enum {
     ER_KV_FLOAT32 = 0,
     ER_KV_FLOAT16 = 1,
@@ -259,6 +260,19 @@ int32_t er_turboquant_quantize_rows(const float* source, uint32_t row_count, uin
                                     uint32_t destination_row_base, uint32_t bits, uint32_t* out_codes,
                                     uint32_t* out_residual_signs, uint32_t* out_outlier_mask, float* out_metadata,
                                     void* stream);
+
+/* turboquant_quantize_rows for the presets with high-precision channels and a QJL residual (Shaders/TurboQuant.metal:562-709;
+ * TurboQuantReferenceEncoder.encode, TurboQuant.swift:1003-1100): balanced = (3, 5, 32), aggressive = (2, 3, 32)
+ * (TurboQuantPreset.descriptor, TurboQuant.swift:78-84, 117-124).  The `high_count` channels with the largest selection
+ * score -- |rotated value| (keys, .magnitude), or the quantisation benefit (values, use_quantization_benefit != 0) --
+ * get `high_bits` codes; the split device buffers are the reference's: codes [rows][base + side-band words] (split-plane
+ * packing), residual signs [rows][4], outlier mask [rows][4], metadata [rows][2] = (rowNorm, residualNorm).  Bit-exact
+ * against the CPU encoder on finite rows.  Storing such rows in an er_kv cache and attention over them are not built. */
+int32_t er_turboquant_quantize_rows_outliers(const float* source, uint32_t row_count, uint32_t source_row_stride,
+                                             uint32_t destination_row_base, uint32_t regular_bits, uint32_t high_bits,
+                                             uint32_t high_count, uint32_t use_quantization_benefit, uint32_t* out_codes,
+                                             uint32_t* out_residual_signs, uint32_t* out_outlier_mask, float* out_metadata,
+                                             void* stream);
 
 /* GQAKernel.encode / GQAKernel.execute (GQAKernel.swift:27-172) -> gqa_attention_f32, gqa_attention_f32_wide,
  * gqa_attention_f32_masked_wide (Shaders/GQA.metal:18-276): float32 K / V.  q/out: device [seqLen][numHeads][headDim]

@@ -331,11 +331,13 @@ static const float kCent3[8] = ER_TQ_CENTROIDS_3BIT;
 static const float kThr3[7] = ER_TQ_THRESHOLDS_3BIT;
 static const float kCent4[16] = ER_TQ_CENTROIDS_4BIT;
 static const float kThr4[15] = ER_TQ_THRESHOLDS_4BIT;
+static const float kCent5[32] = ER_TQ_CENTROIDS_5BIT;
+static const float kThr5[31] = ER_TQ_THRESHOLDS_5BIT;
 static const uint32_t kSigns1Neg[4] = ER_TQ_SIGNS1_NEGMASK;
 static const uint32_t kSigns2Neg[4] = ER_TQ_SIGNS2_NEGMASK;
 
-static const float *centroids_for(int bits) { return bits == 2 ? kCent2 : bits == 3 ? kCent3 : bits == 4 ? kCent4 : NULL; }
-static const float *thresholds_for(int bits) { return bits == 2 ? kThr2 : bits == 3 ? kThr3 : bits == 4 ? kThr4 : NULL; }
+static const float *centroids_for(int bits) { return bits == 2 ? kCent2 : bits == 3 ? kCent3 : bits == 4 ? kCent4 : bits == 5 ? kCent5 : NULL; }
+static const float *thresholds_for(int bits) { return bits == 2 ? kThr2 : bits == 3 ? kThr3 : bits == 4 ? kThr4 : bits == 5 ? kThr5 : NULL; }
 
 static float sign1(int i) { return (kSigns1Neg[i >> 5] >> (i & 31)) & 1u ? -1.0f : 1.0f; }
 static float sign2(int i) { return (kSigns2Neg[i >> 5] >> (i & 31)) & 1u ? -1.0f : 1.0f; }
@@ -522,6 +524,105 @@ ERO_API void ero_tq_encode(const float *x, int count, int bits, uint32_t *code_w
     *row_norm = recon_norm > 0.0f ? (norm / recon_norm) : norm;
     ero_tq_pack_codes(codes, ERO_DIM, bits, code_words);
     if (rotated_out) memcpy(rotated_out, rotated, sizeof(rotated));
+}
+
+/* ---- presets with high-precision channels and a QJL residual: balanced (3 + 5 bits, 32 channels) and aggressive
+ * (2 + 3 bits, 32 channels), TurboQuantPreset.descriptor, TurboQuant.swift:78-84, 117-124 ---- */
+
+/* TurboQuantReferenceEncoder.topKMask (TurboQuant.swift:1185-1238): the `count` channels with the largest selection score,
+ *   .magnitude            |value|
+ *   .quantizationBenefit  (value - regularCentroid)^2 - (value - highCentroid)^2   (products and difference rounded separately)
+ * Equal scores keep channel order (the sort is applied to an index-ordered sequence and the GPU twin, the selection loop of
+ * turboquant_quantize_rows, Shaders/TurboQuant.metal:637-652, takes the first maximum): score descending, index ascending. */
+static float selection_score(float value, int regular_bits, int high_bits, int use_benefit) {
+    if (!use_benefit) return fabsf(value);
+    float rc = centroids_for(regular_bits)[ero_tq_code_for(value, regular_bits)];
+    float hc = centroids_for(high_bits)[ero_tq_code_for(value, high_bits)];
+    float re = value - rc, he = value - hc;
+    float re2 = re * re, he2 = he * he;
+    return re2 - he2;
+}
+ERO_API void ero_tq_topk_mask(const float *values, int count, int regular_bits, int high_bits, int use_benefit, uint8_t *mask) {
+    float score[ERO_DIM];
+    for (int i = 0; i < ERO_DIM; ++i) { score[i] = selection_score(values[i], regular_bits, high_bits, use_benefit); mask[i] = 0; }
+    for (int pick = 0; pick < count && pick < ERO_DIM; ++pick) {
+        int best = -1;
+        for (int i = 0; i < ERO_DIM; ++i) {
+            if (mask[i]) continue;
+            if (best < 0 || score[i] > score[best]) best = i;
+        }
+        mask[best] = 1;
+    }
+}
+
+/* TurboQuantLayout code words of such a preset (TurboQuant.swift:275-319): base plane 128 * regularBits bits, side band
+ * highCount * (highBits - regularBits) bits, each rounded up to words: aggressive 8 + 1, balanced 12 + 2. */
+ERO_API int ero_tq_preset_code_words(int regular_bits, int high_bits, int high_count) {
+    return (ERO_DIM * regular_bits + 31) / 32 + (high_count * (high_bits - regular_bits) + 31) / 32;
+}
+
+/* TurboQuantReferenceEncoder.encode, the residual path (TurboQuant.swift:1003-1100; usesResidualPath, :1420-1426):
+ *   rowNorm (left-to-right Float sum); !(rowNorm > 0) -> all-zero row
+ *   normalized = x / rowNorm; rotated = randomizedHadamard(normalized); mask = topKMask(rotated)
+ *   code[d] = (mask[d] ? highBook : regularBook).code(for: rotated[d]); recon[d] = that book's centroid
+ *   residual = normalized - inverseRandomizedHadamard(recon); residualNorm = sqrt(sum residual^2)
+ *   residualSigns bit d = randomizedHadamard(residual)[d] >= 0          (the seeds are ignored by the transform, :891-921)
+ *   codes packed split-plane (BitPacker.packCodes with a mask, :1463-1488); stored rowNorm is the plain row norm. */
+ERO_API void ero_tq_encode_preset(const float *x, int count, int regular_bits, int high_bits, int high_count, int use_benefit,
+                                  uint32_t *code_words, uint32_t *residual_signs, uint32_t *outlier_mask, float *row_norm,
+                                  float *residual_norm) {
+    int nwords = ero_tq_preset_code_words(regular_bits, high_bits, high_count);
+    float sum = 0.0f;
+    for (int i = 0; i < count; ++i) sum = sum + (x[i] * x[i]);
+    float norm = sqrtf(sum);
+    for (int w = 0; w < nwords; ++w) code_words[w] = 0;
+    for (int i = 0; i < 4; ++i) { residual_signs[i] = 0; outlier_mask[i] = 0; }
+    *row_norm = 0.0f;
+    *residual_norm = 0.0f;
+    if (!(norm > 0.0f)) return;
+    float normalized[ERO_DIM], rotated[ERO_DIM], recon[ERO_DIM], approx[ERO_DIM], residual[ERO_DIM], projected[ERO_DIM];
+    for (int i = 0; i < ERO_DIM; ++i) normalized[i] = i < count ? x[i] / norm : 0.0f;
+    ero_tq_forward(normalized, ERO_DIM, rotated);
+    uint8_t mask[ERO_DIM], codes[ERO_DIM];
+    ero_tq_topk_mask(rotated, high_count, regular_bits, high_bits, use_benefit, mask);
+    for (int i = 0; i < ERO_DIM; ++i) {
+        int bits = mask[i] ? high_bits : regular_bits;
+        codes[i] = (uint8_t)ero_tq_code_for(rotated[i], bits);
+        recon[i] = centroids_for(bits)[codes[i]];
+        if (mask[i]) outlier_mask[i >> 5] |= 1u << (i & 31);
+    }
+    ero_tq_inverse(recon, approx);
+    float rsum = 0.0f;
+    for (int i = 0; i < ERO_DIM; ++i) { residual[i] = normalized[i] - approx[i]; rsum = rsum + (residual[i] * residual[i]); }
+    ero_tq_forward(residual, ERO_DIM, projected);
+    for (int i = 0; i < ERO_DIM; ++i) if (projected[i] >= 0.0f) residual_signs[i >> 5] |= 1u << (i & 31);
+    uint32_t packed[32];
+    int n = ero_tq_pack_codes_split(codes, mask, ERO_DIM, regular_bits, high_bits, packed);
+    for (int w = 0; w < n && w < nwords; ++w) code_words[w] = packed[w];
+    *row_norm = norm;
+    *residual_norm = sqrtf(rsum);
+}
+
+/* approximateDecode of such a row (TurboQuant.swift:1117-1170):
+ *   x_hat = (inverse(centroids) + inverse(+-1 signs) * qjlScale / 128 * residualNorm * residualWeight) * rowNorm,
+ * qjlScale = sqrt(pi / 2) (TurboQuantTransform.qjlScale, :876). */
+ERO_API void ero_tq_decode_preset(const uint32_t *code_words, const uint32_t *residual_signs, const uint32_t *outlier_mask,
+                                  int regular_bits, int high_bits, int high_count, float row_norm, float residual_norm,
+                                  float residual_weight, int count, float *out) {
+    uint8_t mask[ERO_DIM], codes[ERO_DIM];
+    float recon[ERO_DIM], approx[ERO_DIM], dir[ERO_DIM], qjl[ERO_DIM];
+    for (int i = 0; i < ERO_DIM; ++i) mask[i] = (outlier_mask[i >> 5] >> (i & 31)) & 1u;
+    int nwords = ero_tq_preset_code_words(regular_bits, high_bits, high_count);
+    ero_tq_unpack_codes_split(code_words, nwords, mask, ERO_DIM, regular_bits, high_bits, codes);
+    for (int i = 0; i < ERO_DIM; ++i) recon[i] = centroids_for(mask[i] ? high_bits : regular_bits)[codes[i]];
+    ero_tq_inverse(recon, approx);
+    for (int i = 0; i < ERO_DIM; ++i) dir[i] = (residual_signs[i >> 5] >> (i & 31)) & 1u ? 1.0f : -1.0f;
+    ero_tq_inverse(dir, qjl);
+    const float qjl_scale = sqrtf(3.14159265358979323846f / 2.0f);
+    for (int i = 0; i < count; ++i) {
+        float q = qjl[i] * qjl_scale * (1.0f / (float)ERO_DIM) * residual_norm * residual_weight;
+        out[i] = (approx[i] + q) * row_norm;
+    }
 }
 
 /* approximateDecode for fixed presets, TurboQuant.swift:1117-1147:

@@ -85,6 +85,10 @@ def lib():
     L.ero_tq_unpack_codes_split.argtypes = [u32p, C.c_int, u8p, C.c_int, C.c_int, C.c_int, u8p]
     L.ero_tq_encode.argtypes = [f32p, C.c_int, C.c_int, u32p, u32p, u32p, f32p, f32p, f32p]
     L.ero_tq_decode.argtypes = [u32p, C.c_int, C.c_float, C.c_int, f32p]
+    L.ero_tq_topk_mask.argtypes = [f32p, C.c_int, C.c_int, C.c_int, C.c_int, u8p]
+    L.ero_tq_preset_code_words.argtypes = [C.c_int] * 3
+    L.ero_tq_encode_preset.argtypes = [f32p] + [C.c_int] * 5 + [u32p, u32p, u32p, f32p, f32p]
+    L.ero_tq_decode_preset.argtypes = [u32p, u32p, u32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int, f32p]
     L.ero_tq_score.restype = C.c_float
     L.ero_tq_score.argtypes = [f32p, C.c_int, u32p, C.c_int, C.c_float, C.c_float, f32p]
     L.ero_tq_attention_decode.argtypes = [f32p, u32p, f32p, C.c_int, u32p, f32p, C.c_int, f32p,
@@ -278,6 +282,48 @@ def tq_encode_rows(x, bits):
                         C.byref(rn), C.byref(resn), None)
         norms[r] = rn.value
     return codes, norms
+
+
+# TurboQuantPreset.descriptor of the presets with high-precision channels (TurboQuant.swift:78-84, 117-124):
+# (regularBits, highPrecisionBits, highPrecisionChannelCount)
+PRESETS = {"balanced": (3, 5, 32), "aggressive": (2, 3, 32)}
+
+
+def tq_topk_mask(values, count, regular_bits, high_bits, use_benefit=False):
+    v = _f32(values)
+    mask = np.zeros(DIM, dtype=np.uint8)
+    lib().ero_tq_topk_mask(_p(v, F32), count, regular_bits, high_bits, int(use_benefit), _p(mask, U8))
+    return mask.astype(bool)
+
+
+def tq_encode_preset(x, preset, use_benefit=False):
+    """One row through TurboQuantReferenceEncoder.encode with a balanced / aggressive preset ->
+    (code words, residual sign words [4], outlier mask words [4], rowNorm, residualNorm)."""
+    rb, hb, n = PRESETS[preset]
+    x = _f32(x).ravel()
+    words = lib().ero_tq_preset_code_words(rb, hb, n)
+    codes, signs, mask = np.zeros(words, np.uint32), np.zeros(4, np.uint32), np.zeros(4, np.uint32)
+    rn, resn = C.c_float(0), C.c_float(0)
+    lib().ero_tq_encode_preset(_p(x, F32), x.size, rb, hb, n, int(use_benefit), _p(codes, U32), _p(signs, U32), _p(mask, U32),
+                               C.byref(rn), C.byref(resn))
+    return codes, signs, mask, np.float32(rn.value), np.float32(resn.value)
+
+
+def tq_encode_rows_preset(x, preset, use_benefit=False):
+    """x: [n, 128] -> (codes [n, words], signs [n, 4], mask [n, 4], meta [n, 2] = (rowNorm, residualNorm))."""
+    x = _f32(x).reshape(-1, DIM)
+    rows = [tq_encode_preset(r, preset, use_benefit) for r in x]
+    return (np.stack([r[0] for r in rows]), np.stack([r[1] for r in rows]), np.stack([r[2] for r in rows]),
+            np.array([[r[3], r[4]] for r in rows], dtype=np.float32))
+
+
+def tq_decode_preset(codes, signs, mask, preset, row_norm, residual_norm, residual_weight=1.0, count=DIM):
+    rb, hb, n = PRESETS[preset]
+    out = np.zeros(count, dtype=np.float32)
+    codes, signs, mask = (np.ascontiguousarray(a, dtype=np.uint32) for a in (codes, signs, mask))
+    lib().ero_tq_decode_preset(_p(codes, U32), _p(signs, U32), _p(mask, U32), rb, hb, n, float(row_norm), float(residual_norm),
+                               float(residual_weight), count, _p(out, F32))
+    return out
 
 
 def tq_decode(codes, bits, row_norm, count=DIM):

@@ -181,6 +181,29 @@ def test_quantize_rows_bit_exact(er, oracle, bits):
     assert not meta[:, 1].any()                                    # residualNorm == 0
 
 
+@pytest.mark.parametrize("preset", ["balanced", "aggressive"])
+@pytest.mark.parametrize("benefit", [False, True])
+def test_quantize_rows_outlier_presets_bit_exact(er, oracle, preset, benefit):
+    """turboquant_quantize_rows for the presets with 32 high-precision channels and a QJL residual (Shaders/TurboQuant.metal:
+    562-709) against the CPU encoder (TurboQuantReferenceEncoder.encode, TurboQuant.swift:1003-1100): packed split-plane
+    codes, outlier mask, residual signs and both norms bit for bit, with the keys' (.magnitude) and the values'
+    (.quantizationBenefit) selection rule.  Finite rows (random, outlier channels, closed-form signals, ties, zero rows)."""
+    x = _quantizer_inputs()[:-2]                                   # the NaN / inf rows have no defined selection order
+    ties = np.zeros((4, 128), dtype=np.float32)
+    ties[0, [5, 9, 70, 100]] = [0.5, -0.5, 0.5, 0.25]
+    ties[1, :] = 1.0                                               # every score equal: channels 0..31 are selected
+    ties[2, ::3] = -2.0
+    ties[3, 64:] = np.linspace(1, 2, 64, dtype=np.float32)
+    x = np.concatenate([x, ties])
+    codes, signs, mask, meta = er.TurboQuantKernel().execute_quantize_rows_preset(x, preset, benefit)
+    wc, ws, wm, wmeta = oracle.tq_encode_rows_preset(x, preset, benefit)
+    assert np.array_equal(mask, wm)
+    assert np.array_equal(codes, wc)
+    assert np.array_equal(signs, ws)
+    assert np.array_equal(meta.view(np.uint32), wmeta.view(np.uint32))       # (rowNorm, residualNorm)
+    assert (np.unpackbits(mask[x.any(axis=1)].view(np.uint8), axis=1).sum(axis=1) == 32).all()
+
+
 def test_quantize_rows_stride_and_base(er, oracle, torch):
     rng = rng_for(22)
     x = rng.standard_normal((37, 160), dtype=np.float32)           # source_row_stride 160 > 128

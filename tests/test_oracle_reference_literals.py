@@ -360,3 +360,61 @@ def test_windowed_gqa_equals_attention_over_the_gathered_ring_rows(oracle, head_
 def test_windowed_gqa_empty_range_is_zero(oracle):
     q, k16, v16 = _windowed_inputs(8, 2, 128, 8, ((13, 6, 17.0), (11, 5, 19.0), (7, 3, 11.0)))
     assert not oracle.gqa_f16kv_windowed(q, k16, v16, 3, 0).any()
+
+
+# ---- presets with high-precision channels and a QJL residual (balanced, aggressive) ----
+
+def _make_signal():
+    """makeSignal of the reference's encoder tests (TurboQuantReferenceTests.swift:331-336)."""
+    i = np.arange(128, dtype=np.float32)
+    return (np.sin(i * np.float32(0.17)) + np.cos(i * np.float32(0.07)) * np.float32(0.5)).astype(np.float32)
+
+
+def test_outlier_preset_layout_literals(oracle):
+    # layoutMatchesExpectedRowSize (TurboQuantReferenceTests.swift:112-143): aggressive 8 + 1 words, balanced 12 + 2
+    assert oracle.lib().ero_tq_preset_code_words(2, 3, 32) == 9
+    assert oracle.lib().ero_tq_preset_code_words(3, 5, 32) == 14
+
+
+@pytest.mark.parametrize("preset", ["aggressive", "balanced"])
+def test_outlier_preset_encoder_properties(oracle, preset):
+    """aggressiveEncodingIsDeterministic / approximateDecodeProducesFiniteValues (TurboQuantReferenceTests.swift:41-85): the
+    properties the reference asserts on makeSignal(), plus the structure of the row (32 selected channels, the selected
+    ones are the largest by the selection rule, split-plane round trip of the codes)."""
+    x = _make_signal()
+    rb, hb, cnt = oracle.PRESETS[preset]
+    for benefit in (False, True):
+        a = oracle.tq_encode_preset(x, preset, benefit)
+        b = oracle.tq_encode_preset(x, preset, benefit)
+        assert all(np.array_equal(u, v) for u, v in zip(a, b))
+        codes, signs, mask, row_norm, res_norm = a
+        assert codes.size > 0 and signs.size == 4 and mask.size == 4
+        bits = np.unpackbits(mask.view(np.uint8), bitorder="little")
+        assert bits.sum() == cnt
+        acc = np.float32(0)
+        for t in x:                                      # rowNorm: Float sum of squares accumulated left to right
+            acc = np.float32(acc + np.float32(t * t))
+        assert row_norm == np.sqrt(acc)                  # the residual path stores the plain norm, not the corrected one
+        assert 0 < res_norm < 1
+        dec = oracle.tq_decode_preset(codes, signs, mask, preset, row_norm, res_norm)
+        assert dec.shape == x.shape and np.isfinite(dec).all()
+        assert float(np.mean((x - dec) ** 2)) < 10          # the reference's bound; the encoder actually reaches ~0.03
+        # the mask is exactly the top-32 of the selection score over the rotated, normalised row
+        rot = oracle.tq_forward(x / row_norm)
+        want = oracle.tq_topk_mask(rot, cnt, rb, hb, benefit)
+        assert np.array_equal(bits.astype(bool), want)
+        if not benefit:
+            mag = np.abs(rot)
+            assert mag[want].min() >= mag[~want].max()
+    # an all-zero row encodes to an all-zero row (TurboQuant.swift:1018-1028)
+    z = oracle.tq_encode_preset(np.zeros(128, np.float32), preset)
+    assert not z[0].any() and not z[1].any() and not z[2].any() and z[3] == 0 and z[4] == 0
+
+
+def test_topk_ties_keep_channel_order(oracle):
+    v = np.zeros(128, np.float32)
+    v[[5, 9, 70, 100]] = [0.5, -0.5, 0.5, 0.25]          # three equal magnitudes, then a smaller one
+    m = oracle.tq_topk_mask(v, 2, 2, 3)
+    assert np.nonzero(m)[0].tolist() == [5, 9]             # equal scores: the lower channel wins
+    m = oracle.tq_topk_mask(v, 4, 2, 3)
+    assert np.nonzero(m)[0].tolist() == [5, 9, 70, 100]

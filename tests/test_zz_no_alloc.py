@@ -5,7 +5,9 @@ free HBM, or a thread that must stay off the driver's allocation path), so this 
 in an array built into the library.  The test drives both entry points through the C ABI on the same inputs, twice
 in a row (the second call finds the first call's leftovers in the shared workspace), and expects outputs within the
 attention tolerance of the other GPU tests -- bit-identical for single query rows, where both run the same kernel
-(multi-row calls of the regular entry point use the tensor-core prefill kernel instead)."""
+(multi-row calls of the regular entry point use the tensor-core prefill kernel instead) -- and against the CPU oracle;
+one case is a multi-row call long enough that every row's launch is split over many CTAs and merged through the shared
+workspace.  The workspace's status word is read back at the end (no bounded wait may have given up)."""
 import numpy as np
 import pytest
 
@@ -18,7 +20,7 @@ def _rel(got, ref):
     return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), floor)))
 
 
-def test_static_workspace_entry_point_matches_regular_one():
+def test_static_workspace_entry_point_matches_regular_one(oracle):
     import torch
     import edgerunner_b200 as er
 
@@ -28,6 +30,7 @@ def test_static_workspace_entry_point_matches_regular_one():
         (1, 700, 16, 8, True, 699),
         (3, 150, 8, 2, True, 147),
         (1, 33, 4, 4, False, 0),
+        (4, 6000, 8, 2, True, 5996),          # four rows, each launch split over all SMs (partials merged through the workspace)
     ]
     for call in range(2):                      # two calls in a row share the built-in workspace
         for S, T, H, Hkv, causal, off in cases:
@@ -44,6 +47,10 @@ def test_static_workspace_entry_point_matches_regular_one():
             assert _rel(g, w) < TOL, (call, S, T, H, Hkv)
             if S == 1:
                 assert np.array_equal(g, w)
+            ref = oracle.gqa_f16kv(q.cpu().numpy(), k.cpu().numpy().view(np.uint16), v.cpu().numpy().view(np.uint16), causal=causal,
+                                   q_offset=off, threads=8)
+            assert _rel(g, ref) < TOL, ("oracle", call, S, T, H, Hkv)
+    assert er.lib().er_gqa_attention_f16kv_static_status() == 0      # no bounded wait gave up in any of those launches
 
 
 def test_static_workspace_rejects_shapes_beyond_its_limits():
