@@ -183,6 +183,52 @@ struct LaneState {
     }
 };
 
+// Tensor-core policies: fold a warp's running (max, denominator, O^T fragments) into the warp's merge buffer and restart
+// the accumulators from zero.  The tensor cores add into their fp32 accumulators with truncation, so a long chain of
+// accumulating mma instructions drifts by about half an ulp of the accumulator per instruction (measured on the prefill
+// kernels: an error growing linearly with the context); folding every few units keeps each chain short and does the long
+// sum in round-to-nearest fp32.  The buffer holds the same (max, denominator) / [head][128] layout State::publish writes,
+// so the CTA-level merge is unchanged.  dim_of(t, g, second) maps fragment (m-tile t, row g or g + 8) to its output dim.
+template <int GROUP, class DIM>
+__device__ __forceinline__ void mma_state_fold(float (&m)[2], float (&l)[2], float (&acc)[8][4], float* ml, float* accs, int lane,
+                                               bool first, float acc_scale, float l_scale, DIM dim_of) {
+    const int g = lane >> 2, c = lane & 3;
+    float wb[2], ws[2], mn[2], lb[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int h = 2 * c + e;
+        const float mb = (first || h >= GROUP) ? -INFINITY : ml[h * 2];
+        lb[e] = (first || h >= GROUP) ? 0.f : ml[h * 2 + 1];
+        mn[e] = fmaxf(mb, m[e]);
+        wb[e] = mb == -INFINITY ? 0.f : fast_exp2(mb - mn[e]);
+        ws[e] = m[e] == -INFINITY ? 0.f : fast_exp2(m[e] - mn[e]);
+    }
+    __syncwarp();   // every lane has read the buffer's (max, denominator) before the g == 0 lanes replace them
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int h = 2 * c + e;
+        if (h < GROUP) {
+            if (g == 0) {
+                ml[h * 2] = mn[e];
+                ml[h * 2 + 1] = fmaf(lb[e], wb[e], l[e] * l_scale * ws[e]);
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                float* a0 = accs + h * kHeadDim + dim_of(t, g, 0);
+                float* a1 = accs + h * kHeadDim + dim_of(t, g, 1);
+                *a0 = fmaf(first ? 0.f : *a0, wb[e], acc[t][e] * acc_scale * ws[e]);
+                *a1 = fmaf(first ? 0.f : *a1, wb[e], acc[t][2 + e] * acc_scale * ws[e]);
+            }
+        }
+        l[e] = 0.f;
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+    __syncwarp();
+}
+
 template <int GROUP, int UNITS_PER_TILE = 8, int WARP_GROUPS = 1, int STAGES = 3>
 struct DensePolicy {
     static constexpr int kGroup = GROUP;
@@ -193,6 +239,7 @@ struct DensePolicy {
     static constexpr int kStageBytes = 2 * kTileBytesF16;
     static constexpr int kExtraBytes = 0;
     static constexpr bool kRotated = false;
+    static constexpr int kFoldUnits = 0;   // scalar fp32 FMAs round to nearest: no accumulator folding
     __device__ static float* fin_ptr(uint8_t*) { return nullptr; }
     static constexpr bool kFusedAppend = true;
     // A warp group must meet consecutive phases of the stages it visits: tiles go to groups round-robin.
@@ -630,6 +677,10 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
                 POL::load_q(p, st, qrow, cs, extra, warp, lane, layer);
 
+                float* my_ml = merge_ml + warp * GROUP * 2;
+                float* my_acc = merge_acc + warp * GROUP * kHeadDim;
+                int since_fold = 0;
+                bool folded = false;
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     if (NG > 1 && k % NG != wgroup) continue;
                     const int nun = min(UPT, sg.u1 - tu);
@@ -649,6 +700,13 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     if (wunit < nun && !flags[0]) {
                         const int nvalid = min(kUnitTokens, ntok - wunit * kUnitTokens);
                         POL::process_unit(p, smem + s * POL::kStageBytes, wunit, nvalid, st, prob, extra, lane);
+                        if constexpr (POL::kFoldUnits > 0) {
+                            if (++since_fold == POL::kFoldUnits) {   // keep the tensor cores' accumulation chains short
+                                st.fold(my_ml, my_acc, lane, !folded);
+                                folded = true;
+                                since_fold = 0;
+                            }
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -656,7 +714,11 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
 
                 if (tid == 0) stamp(3);   // last write wins: end of this CTA's streaming
                 // ---- merge the consumer warps of this CTA ----
-                st.publish(merge_ml + warp * GROUP * 2, merge_acc + warp * GROUP * kHeadDim, lane);
+                if constexpr (POL::kFoldUnits > 0) {
+                    if (folded) st.fold(my_ml, my_acc, lane, false); else st.publish(my_ml, my_acc, lane);
+                } else {
+                    st.publish(my_ml, my_acc, lane);
+                }
                 consumer_sync<NW * 32>();
                 const bool sole = (sg.u0 == 0 && sg.u1 == sg.units);
                 const int item = sg.pair * hkv + sg.head;

@@ -58,7 +58,12 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
                 }
             }
         }
+        __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
+            mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, 1.f, kProbScale,
+                                  [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
+        }
     };
+    static constexpr int kFoldUnits = 8;
 
     // Q rows (per-head RMS norm, then NeoX rotation, when asked) -> B fragments; thread (g, c) holds head g.
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane,

@@ -86,7 +86,12 @@ struct Q8MmaPolicy {
                 }
             }
         }
+        __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
+            mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, kInvProbScale, 1.f,
+                                  [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
+        }
     };
+    static constexpr int kFoldUnits = 8;
 
     __device__ static bool init_extra(uint8_t*, int, int) { return true; }
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,

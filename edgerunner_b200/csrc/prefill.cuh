@@ -249,11 +249,16 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
             psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
             l_run[h] = fmaf(l_run[h], corr[h], psum[h]);
         }
+        // The tensor cores add into their fp32 accumulators with truncation, which biases a long accumulation chain by about
+        // half an ulp of the accumulator per instruction (measured: error growing linearly with the context, 6e-5 of the
+        // row's largest output at 20000 keys).  So each tile's P V product starts from zero (a chain of 8 to 12
+        // instructions) and is added to the running output with ordinary round-to-nearest fp32 arithmetic.
+        float ot[16][4];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            ot[j][0] = ot[j][1] = ot[j][2] = ot[j][3] = 0.f;
         }
-        // ---- O += P V, P as fp16 hi + lo A fragments (k-step t16 = tokens 16*t16 .. +15 = score tiles 2*t16, 2*t16+1) ----
+        // ---- O_tile = P V, P as fp16 hi + lo A fragments (k-step t16 = tokens 16*t16 .. +15 = score tiles 2*t16, 2*t16+1) ----
 #pragma unroll
         for (int t16 = 0; t16 < 4; ++t16) {
             uint32_t ph[4], pl[4];
@@ -272,16 +277,21 @@ __global__ void __launch_bounds__(kPfThreads) prefill_f16_kernel(const __grid_co
                 uint32_t b[4];
                 const int row = 16 * t16 + (lane & 7) + ((lane >> 3) & 1) * 8, chunk = 2 * jd2 + (lane >> 4);
                 ldmatrix_x4_trans(b, vs + pf_swizzle(row, chunk));
-                mma_16816(o[2 * jd2], ph, b[0], b[1]);
-                mma_16816(o[2 * jd2], pl, b[0], b[1]);
-                mma_16816(o[2 * jd2 + 1], ph, b[2], b[3]);
-                mma_16816(o[2 * jd2 + 1], pl, b[2], b[3]);
+                mma_16816(ot[2 * jd2], ph, b[0], b[1]);
+                mma_16816(ot[2 * jd2], pl, b[0], b[1]);
+                mma_16816(ot[2 * jd2 + 1], ph, b[2], b[3]);
+                mma_16816(ot[2 * jd2 + 1], pl, b[2], b[3]);
                 if (KSPLIT) {
                     ldmatrix_x4_trans(b, vls + pf_swizzle(row, chunk));
-                    mma_16816(o[2 * jd2], ph, b[0], b[1]);
-                    mma_16816(o[2 * jd2 + 1], ph, b[2], b[3]);
+                    mma_16816(ot[2 * jd2], ph, b[0], b[1]);
+                    mma_16816(ot[2 * jd2 + 1], ph, b[2], b[3]);
                 }
             }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            o[j][0] = fmaf(o[j][0], corr[0], ot[j][0]); o[j][1] = fmaf(o[j][1], corr[0], ot[j][1]);
+            o[j][2] = fmaf(o[j][2], corr[1], ot[j][2]); o[j][3] = fmaf(o[j][3], corr[1], ot[j][3]);
         }
         __syncthreads();
     }
