@@ -63,7 +63,7 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
                                   [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
         }
     };
-    static constexpr int kFoldUnits = 8;
+    static constexpr int kFoldUnits = 32;   // chains of about 128 accumulating mma per output fragment
 
     // Q rows (per-head RMS norm, then NeoX rotation, when asked) -> B fragments; thread (g, c) holds head g.
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane,

@@ -91,7 +91,7 @@ struct Q8MmaPolicy {
                                   [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
         }
     };
-    static constexpr int kFoldUnits = 8;
+    static constexpr int kFoldUnits = 32;   // chains of about 128 accumulating mma per output fragment
 
     __device__ static bool init_extra(uint8_t*, int, int) { return true; }
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,

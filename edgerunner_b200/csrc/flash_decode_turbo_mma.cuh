@@ -166,7 +166,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, 1.f, 1.f, [](int t, int g, int second) { return 16 * g + 2 * t + second; });
         }
     };
-    static constexpr int kFoldUnits = 8;   // 4 accumulating mma per output fragment and unit -> chains of 32
+    static constexpr int kFoldUnits = 32;   // chains of about 128 accumulating mma per output fragment
 
     // false when the plan does not fit the CTA's shared memory (the window base is not where this layout expects it)
     __device__ static bool init_extra(uint8_t* extra, int tid, int smem_bytes_after_extra) {
