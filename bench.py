@@ -75,6 +75,11 @@ WORKLOADS = {
     "cfg3_contiguous": dict(name="cfg3 heads (32 q / 8 kv) on contiguous head-major rows, 8 layers, batch 8, context 32768 "
                                  "(separates the page gather from the kernel; not a BASELINE configuration)",
                             layers=8, batch=8, heads=32, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=5.0e5),
+    # BASELINE.json configs[4] as a whole job (run_cfg4): prefill chunk over all layers, then 128 decode steps
+    "cfg4": dict(name="cfg4: Qwen3-4B shape, 36 layers, context 131072, TurboQuant turbo4 K / turbo4 V in 64-token pages; one 2048-token "
+                      "prefill chunk per sequence, then 128 decode steps",
+                 layers=36, batch=16, heads=32, kv_heads=8, ctx=131072, chunk=2048, decode_steps=128, precision="turboquant", kbits=4, vbits=4,
+                 norm="float16", layout="paged", page_size=64, theta=1.0e6),
     # BASELINE.json configs[4], decode leg on one GPU: 2 of the 16 sequences with all heads (an 8-GPU run gives each pair of
     # GPUs 4 sequences and each GPU half of the heads: the same 10 GB of codes per GPU)
     "cfg4_decode_slice": dict(name="cfg4 decode, one GPU's share: Qwen3-4B shape, 36 layers, 2 of the 16 sequences at context 131072, "
@@ -807,9 +812,137 @@ def run_prefill(args, w):
         "gpu_launches": int(er.lib().er_kernel_launch_count() - launches0), "clocks": clocks}))
 
 
+def run_cfg4(args):
+    """BASELINE configs[4]: Qwen3-4B shape (36 layers, 32 q / 8 kv heads), TurboQuant turbo4 K / turbo4 V rows with fp16 norms in
+    64-token pages, sequences at context 131072: ONE chunked-prefill step that appends 2048 tokens per sequence (causal,
+    tensor-core kernel, every layer), then 128 decode steps.  GPUs are split by sequence x kv-head group: pairs of GPUs
+    share 4 sequences and hold 4 kv heads each (outputs exchanged inside the pair); one GPU alone runs 2 sequences with all
+    heads -- the same 10 GB of codes per GPU at every N, so `scaling` is weak and `value` counts all sequences."""
+    cx = Context(args)
+    torch, dist, er = cx.torch, cx.dist, cx.er
+    from edgerunner_b200.sharding import HeadShardedDecoder, HeadShard
+    w = WORKLOADS["cfg4"]
+    L, Hfull, Hkv_full, ctx, chunk, ps = w["layers"], w["heads"], w["kv_heads"], w["ctx"], w["chunk"], w["page_size"]
+    steps = args.steps if args.steps != 20 else w["decode_steps"]       # 128 unless --steps says otherwise
+    head_groups = 2 if cx.world > 1 else 1
+    if cx.world > 1 and cx.world % 2:
+        raise SystemExit("cfg4 needs 1 GPU or an even number of GPUs (pairs share sequences)")
+    pair = cx.rank // head_groups
+    B = 2 if cx.world == 1 else 4
+    total_seqs = B * max(cx.world // head_groups, 1)
+    group = None
+    if cx.world > 1:
+        groups = [dist.new_group([2 * g, 2 * g + 1]) for g in range(cx.world // 2)]
+        group = groups[pair]
+    shard = HeadShard(Hfull, Hkv_full, head_groups, cx.rank % head_groups)
+    H, Hkv = shard.local_heads, shard.local_kv_heads
+    T = ctx + chunk + steps + 8
+    pages_per_seq = (T + ps - 1) // ps
+    cache = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=w["kbits"], value_type=w["vbits"], norm_format=er.NormFormat.float16,
+                       max_batch=B, layout=er.Layout.paged, page_size=ps, num_pages=pages_per_seq * B)
+    rng = np.random.Generator(np.random.PCG64(2 + pair))
+    alloc = er.BlockTableAllocator(pages_per_seq * B, ps, free_order=rng.permutation(pages_per_seq * B))
+    for b in range(B):
+        cache.set_block_table(b, alloc.ensure(b, T))
+    sp = er.step_params(rope_theta=w["theta"])
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + cx.rank)
+    for l in range(L):
+        for b in range(B):
+            for s0 in range(0, ctx, 16384):
+                n = min(16384, ctx - s0)
+                cache.write_rows(l, b, s0, n, torch.randn((n, Hkv, D), generator=g, device="cuda").half().float(),
+                                 torch.randn((n, Hkv, D), generator=g, device="cuda").half().float(), sp)
+    torch.cuda.synchronize()
+    stream = cx.stream
+    # ---- the prefill step: per layer and sequence, append the chunk's K / V rows, then causal attention of its 2048 query rows ----
+    kc = torch.randn((chunk, Hkv, D), generator=g, device="cuda").half().float()
+    vc = torch.randn((chunk, Hkv, D), generator=g, device="cuda").half().float()
+    qc = torch.randn((chunk, H, D), generator=g, device="cuda").half().float()
+    oc = torch.empty((chunk, H, D), device="cuda")
+    og = torch.empty((head_groups, chunk, H, D), device="cuda") if cx.world > 1 else None
+    cx.barrier()
+    sampler = ClockSampler(cx.local_rank)
+    if cx.rank == 0:
+        sampler.start()
+    launches0 = er.lib().er_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for l in range(L):
+        for b in range(B):
+            cache.write_rows(l, b, ctx, chunk, kc, vc, sp, stream=stream)
+            cache.attention_prefill(l, b, qc, oc, H, chunk, sp, stream=stream)
+            if og is not None:
+                dist.all_gather_into_tensor(og, oc, group=group)      # the pair ends the chunk with all heads' rows
+    e1.record(stream)
+    cx.barrier()
+    prefill_ms = cx.max_over_ranks(e0.elapsed_time(e1))
+    prefill_launches = int(er.lib().er_kernel_launch_count() - launches0)
+    flops_rank = 4.0 * chunk * (ctx + (chunk + 1) / 2.0) * H * D * L * B
+    # ---- 128 decode steps ----
+    dec = HeadShardedDecoder(cache, L, B, Hfull, Hkv_full, head_groups, cx.rank % head_groups, exchange=args.exchange, group=group)
+    pool = 8
+    qs = torch.randn((pool, L, B, H, D), generator=g, device="cuda").half().float()
+    ks = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
+    vs = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
+    for s in range(max(args.warmup, 1)):
+        dec.step(qs[s % pool], ks[s % pool], vs[s % pool], sp, stream=stream)
+    for b in range(B):
+        cache.set_position(ctx + chunk, seq=b)
+    cx.barrier()
+    launches0 = er.lib().er_kernel_launch_count()
+    e0.record(stream)
+    for s in range(steps):
+        dec.step(qs[s % pool], ks[s % pool], vs[s % pool], sp, stream=stream)
+    e1.record(stream)
+    cx.barrier()
+    decode_ms = cx.max_over_ranks(e0.elapsed_time(e1))
+    decode_launches = int(er.lib().er_kernel_launch_count() - launches0)
+    clocks = sampler.stop() if cx.rank == 0 else None
+    assert cache.device_status() == 0
+    wl = dict(w, precision="turboquant", heads=H, kv_heads=Hkv, norm="float16")
+    lens = [ctx + chunk] * B
+    dec_bytes = sum(step_bytes(wl, lens, s) for s in range(steps))
+    peak, peak_src = measured_peaks()
+    tpeak = None
+    try:
+        tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+    except Exception:
+        pass
+    if cx.rank == 0:
+        total_ms = prefill_ms + decode_ms
+        tokens = total_seqs * (chunk + steps)
+        print(json.dumps({
+            "metric": METRIC, "value": tokens / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": cx.world, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": decode_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "layers": L, "sequences": total_seqs, "sequences_per_gpu_group": B, "q_heads": Hfull, "kv_heads": Hkv_full,
+                       "sharding": ("%d sequence groups x %d kv-head groups; outputs exchanged inside each pair of GPUs" % (cx.world // head_groups, head_groups))
+                       if cx.world > 1 else "single GPU: 2 sequences, all kv heads (one GPU's share of the 8-GPU split)",
+                       "value_is": "all tokens of the job (prefill chunk + decode steps) over prefill time + decode time"},
+            "prefill": {"ms": prefill_ms, "tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1), "peak_tflops_sustained": tpeak,
+                        "frac_of_sustained_bf16": round(flops_rank / prefill_ms / 1e9 / tpeak, 4) if tpeak else None,
+                        "chunk_tokens_per_s": total_seqs * chunk / (prefill_ms * 1e-3), "gpu_launches": prefill_launches,
+                        "note": "useful FLOPs 4 S (ctx + (S+1)/2) Hq 128 per layer and sequence; includes the chunk's append and the expansion of "
+                                "the sequence's codes to fp16 hi + lo rows that the tensor-core kernel reads"},
+            "decode": {"ms_per_step": decode_ms / steps, "tokens_per_s": total_seqs * steps / (decode_ms * 1e-3),
+                       "hbm_gbs_per_gpu": round(dec_bytes / (decode_ms * 1e-3) / 1e9, 1), "frac_of_measured_copy_peak": round(dec_bytes / (decode_ms * 1e-3) / 1e9 / peak, 4),
+                       "peak_source": peak_src, "gpu_launches": decode_launches, "exchange": dec.exchange},
+            "gpu_launches": prefill_launches + decode_launches, "clocks": clocks}))
+    dec.close()
+    cache.close()
+    if cx.world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     w = WORKLOADS[args.workload]
+    if args.workload == "cfg4":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "cfg4 is measured on the GPU path only (the CPU leg runs the default workload)"}))
+            return
+        run_cfg4(args)
+        return
     if w.get("prefill"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the prefill workloads are measured on the GPU path only"}))
