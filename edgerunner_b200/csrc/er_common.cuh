@@ -111,7 +111,7 @@ __device__ __forceinline__ void prefetch_l2(const void* ptr) {
 // Per-head RMS-norm factor rsqrt(sum(x^2) / 128 + eps) of a 128-float row, summed in the order head_rms_norm_kernel uses
 // (pair terms x[i]^2 + x[i+64]^2, xor butterfly 16..1 over each 32 pairs, one add).  All 32 lanes take part.
 __device__ __forceinline__ float head_rms_scale(const float* row, float eps, int lane) {
-    const float a = __ldg(row + lane), b = __ldg(row + lane + 64), c = __ldg(row + lane + 32), d = __ldg(row + lane + 96);
+    const float a = __ldcg(row + lane), b = __ldcg(row + lane + 64), c = __ldcg(row + lane + 32), d = __ldcg(row + lane + 96);
     float s0 = __fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b));
     float s1 = __fadd_rn(__fmul_rn(c, c), __fmul_rn(d, d));
 #pragma unroll

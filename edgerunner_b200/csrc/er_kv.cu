@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <chrono>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -195,7 +196,14 @@ struct er_kv {
     float* peer_out[7] = {};
     uint32_t probe_wait_limit_us = 0;        // er_kv_debug_wait_probe: patience of the next decode launches' waits
     int probe_withhold_tiles = 0;
-    int* h_status = nullptr;                 // pinned host word: er_kv_decode_step_host copies the device status here
+    int* h_status = nullptr;                 // pinned, device-mapped host words: [0] the device status copied by er_kv_decode_step_host;
+                                             // [2], [3] = {epoch, status} written by the last CTA of a host-buffer decode launch
+    int* d_host_done = nullptr;              // device alias of h_status + 2 (nullptr: memory not mapped)
+    int host_epoch = 0;
+    const float* hostio_q = nullptr;         // set by er_kv_decode_step_host around its launch: the step's rows in mapped host memory
+    const float* hostio_k = nullptr;
+    const float* hostio_v = nullptr;
+    bool hostio_used = false;                // the launch took the rows from there and will signal h_status[2]
     unsigned long long* d_trace = nullptr;   // caller-owned diagnostics buffer (er_kv_set_trace)
     uint32_t trace_ctas = 0;
     std::mutex mu;
@@ -494,9 +502,13 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         cudaMalloc(&kv->d_counters, sizeof(int) * counters) != cudaSuccess ||
         cudaMemset(kv->d_counters, 0, sizeof(int) * counters) != cudaSuccess)
         return bail(fail(ER_ERR_ALLOCATION_FAILED, "scratch"));
-    if (cudaHostAlloc(reinterpret_cast<void**>(&kv->h_status), sizeof(int), cudaHostAllocDefault) != cudaSuccess)
+    if (cudaHostAlloc(reinterpret_cast<void**>(&kv->h_status), 4 * sizeof(int), cudaHostAllocMapped) != cudaSuccess)
         return bail(fail(ER_ERR_ALLOCATION_FAILED, "pinned status word"));
-    *kv->h_status = 0;
+    for (int i = 0; i < 4; ++i) kv->h_status[i] = 0;
+    {
+        void* alias = nullptr;
+        if (cudaHostGetDevicePointer(&alias, kv->h_status, 0) == cudaSuccess) kv->d_host_done = static_cast<int*>(alias) + 2; else cudaGetLastError();
+    }
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cache initialisation"));
     *out = kv;
     return ER_OK;
@@ -1141,6 +1153,12 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
     return check_launch("set_min_length_kernel");
 }
 
+// float16 caches: launches over a small amount of rows (one layer of a small batch) skip the persistent kernel
+static bool uses_slim_kernel(const er_kv* kv, uint32_t layers) {
+    const uint64_t capacity_bytes = static_cast<uint64_t>(layers) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kv->cfg.max_seq_len * 2 * kRowBytesF16;
+    return kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM || (kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO && capacity_bytes <= (128ull << 20));
+}
+
 static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
                                 uint32_t advance, const er_step_params& s, cudaStream_t stream, const float* k_new = nullptr,
                                 const float* v_new = nullptr) {
@@ -1220,9 +1238,7 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
             rc = decode_status(launch_decode_q8(group, p, kv->num_sms, stream), group, 8, 8);
         else {
             // small launches (one layer of a small batch) skip the persistent kernel's staging pipeline
-            const uint64_t capacity_bytes = static_cast<uint64_t>(l1 - l0) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kv->cfg.max_seq_len * 2 * kRowBytesF16;
-            const bool want_slim = kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM ||
-                                   (kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO && capacity_bytes <= (128ull << 20));
+            const bool want_slim = uses_slim_kernel(kv, l1 - l0);
             int src = kNotBuilt;
             if (want_slim && kv->probe_withhold_tiles == 0) {
                 const int items = static_cast<int>((l1 - l0) * kv->cfg.max_batch * kv->cfg.num_kv_heads);
@@ -1238,6 +1254,12 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
             } else {
                 if (kv->token_major)
                     encode_token_major_maps(p, group, kv->cfg.num_layers, kv->cfg.max_batch, kv->cfg.max_seq_len, kv->cfg.num_kv_heads);
+                if (kv->hostio_q != nullptr && p.fused_append && l0 == lb && l1 == le && kv->d_host_done != nullptr) {
+                    // host-buffer step in one launch: the kernel pulls the rows itself and reports to the host word
+                    p.host_q = kv->hostio_q; p.host_k = kv->hostio_k; p.host_v = kv->hostio_v;
+                    p.host_done = kv->d_host_done; p.host_epoch = ++kv->host_epoch;
+                    kv->hostio_used = true;
+                }
                 rc = dispatch_decode_f16(group, p, kv->num_sms, stream);
             }
         }
@@ -1463,24 +1485,63 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     const void* mk = mapped_device_pointer(hk);
     const void* mv = mapped_device_pointer(hv);
     void* mout = mapped_device_pointer(hout);
-    if (mq && mk && mv && q_bytes % 16 == 0 && kv_bytes % 16 == 0) {
-        // pinned inputs: one gather launch reads them over the bus
-        const int nq4 = static_cast<int>(q_bytes / 16), nkv4 = static_cast<int>(kv_bytes / 16);
-        const int blocks = std::min(2 * std::max(kv->num_sms, 1), (nq4 + 2 * nkv4 + 255) / 256);
-        gather_host_inputs_kernel<<<blocks, 256, 0, s>>>(static_cast<const float4*>(mq), static_cast<const float4*>(mk),
-                                                         static_cast<const float4*>(mv), reinterpret_cast<float4*>(dq),
-                                                         reinterpret_cast<float4*>(dk), reinterpret_cast<float4*>(dv), nq4, nkv4);
-        if ((rc = check_launch("gather_host_inputs_kernel")) != ER_OK) return rc;
-    } else {
-        ER_CUDA(cudaMemcpyAsync(dq, hq, q_bytes, cudaMemcpyHostToDevice, s));
-        ER_CUDA(cudaMemcpyAsync(dk, hk, kv_bytes, cudaMemcpyHostToDevice, s));
-        ER_CUDA(cudaMemcpyAsync(dv, hv, kv_bytes, cudaMemcpyHostToDevice, s));
+    const bool mapped_in = mq && mk && mv && q_bytes % 16 == 0 && kv_bytes % 16 == 0;
+    // float16 rows, one persistent launch for the whole call, everything pinned: no gather launch, no copy, no stream
+    // synchronisation -- the decode kernel's producer warps pull the rows of their own item visits from the mapped buffers
+    // while earlier tiles stream, its merging warps store the output rows into host memory, and its last CTA writes
+    // {epoch, status} to a mapped host word this thread polls.
+    bool in_kernel = false;
+    if (mapped_in && mout && kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim && kv->d_host_done != nullptr &&
+        !uses_slim_kernel(kv, le - lb) && le - lb <= std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch)) {
+        std::lock_guard<std::mutex> lock(kv->mu);
+        kv->hostio_q = static_cast<const float*>(mq); kv->hostio_k = static_cast<const float*>(mk); kv->hostio_v = static_cast<const float*>(mv);
+        kv->hostio_used = false;
+        in_kernel = true;
+    }
+    if (!in_kernel) {
+        if (mapped_in) {
+            // pinned inputs: one gather launch reads them over the bus
+            const int nq4 = static_cast<int>(q_bytes / 16), nkv4 = static_cast<int>(kv_bytes / 16);
+            const int blocks = std::min(2 * std::max(kv->num_sms, 1), (nq4 + 2 * nkv4 + 255) / 256);
+            gather_host_inputs_kernel<<<blocks, 256, 0, s>>>(static_cast<const float4*>(mq), static_cast<const float4*>(mk),
+                                                             static_cast<const float4*>(mv), reinterpret_cast<float4*>(dq),
+                                                             reinterpret_cast<float4*>(dk), reinterpret_cast<float4*>(dv), nq4, nkv4);
+            if ((rc = check_launch("gather_host_inputs_kernel")) != ER_OK) return rc;
+        } else {
+            ER_CUDA(cudaMemcpyAsync(dq, hq, q_bytes, cudaMemcpyHostToDevice, s));
+            ER_CUDA(cudaMemcpyAsync(dk, hk, kv_bytes, cudaMemcpyHostToDevice, s));
+            ER_CUDA(cudaMemcpyAsync(dv, hv, kv_bytes, cudaMemcpyHostToDevice, s));
+        }
     }
     // pinned output: the merging warps store the rows straight into host memory
     float* step_out = mout ? static_cast<float*>(mout) : reinterpret_cast<float*>(dout);
     rc = er_kv_decode_step(kv, lb, le, reinterpret_cast<const float*>(dq), reinterpret_cast<const float*>(dk), reinterpret_cast<const float*>(dv),
                            step_out, num_heads, sp, stream);
+    bool signalled = false;
+    int epoch = 0;
+    if (in_kernel) {
+        std::lock_guard<std::mutex> lock(kv->mu);
+        kv->hostio_q = kv->hostio_k = kv->hostio_v = nullptr;
+        signalled = kv->hostio_used;
+        epoch = kv->host_epoch;
+        kv->hostio_used = false;
+    }
     if (rc != ER_OK) return rc;
+    if (in_kernel && !signalled) return fail(ER_ERR_CUDA, "host-buffer step: the decode launch did not take the mapped rows");
+    if (signalled) {
+        // the launch reports by itself; poll its word (its patience for device waits is 2 s, so well past that means a lost launch)
+        volatile int* done = kv->h_status + 2;
+        const auto t0 = std::chrono::steady_clock::now();
+        uint32_t spins = 0;
+        while (done[0] != epoch) {
+            if ((++spins & 0xFFFu) == 0u && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(10)) {
+                ER_CUDA(cudaStreamSynchronize(s));
+                if (done[0] != epoch) return fail(ER_ERR_CUDA, "host-buffer step: the launch ended without reporting");
+            }
+        }
+        std::atomic_thread_fence(std::memory_order_acquire);
+        return device_status_to_code(done[1]);
+    }
     if (!mout) ER_CUDA(cudaMemcpyAsync(hout, dout, q_bytes, cudaMemcpyDeviceToHost, s));
     // the step's device status travels back with the results: a bounded wait that gave up, or a row without a page,
     // is this call's error and not garbage returned as success

@@ -87,8 +87,26 @@ struct DecodeParams {
     int* item_counters;           // [pairs * kv heads], zero between launches
     int* done_counter;            // zero between launches
     int* status;
+    // Host-buffer steps (fp16 policies with the fused append): the step's q / k / v rows still lie in pinned, device-mapped
+    // host memory at host_q / host_k / host_v (same shapes as q / k_new / v_new, which then name device staging buffers).
+    // The producer warp of every CTA pulls the rows of the CTA's own item visits over the bus one visit ahead of the
+    // consumers and stores them at q / k_new / v_new; the consumers wait on a counter in shared memory.  host_done (mapped
+    // host memory, two ints) receives {host_epoch, status word} from the last CTA after every output row: the host waits
+    // on it instead of on the stream.
+    const float* host_q;
+    const float* host_k;
+    const float* host_v;
+    int* host_done;
+    int host_epoch;
     InvFreqTable inv_freq;
 };
+
+// 16-byte load that is never served from a stale cache line (mapped host memory changes between launches).
+__device__ __forceinline__ float4 ld_volatile_f4(const float4* ptr) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr) : "memory");
+    return v;
+}
 
 template <class POL>
 struct DecodeSmem {
@@ -348,7 +366,7 @@ struct DensePolicy {
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             const float4* src = reinterpret_cast<const float4*>(qrow + g * kHeadDim + 8 * i);
-            const float4 a0 = __ldg(src), a1 = __ldg(src + 1), b0 = __ldg(src + 16), b1 = __ldg(src + 17);
+            const float4 a0 = __ldcg(src), a1 = __ldcg(src + 1), b0 = __ldcg(src + 16), b1 = __ldcg(src + 17);   // L2: the rows may have been staged by this launch
             float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
             if (qw != nullptr) {
@@ -481,7 +499,7 @@ struct DensePolicy {
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
             const int d = lane + 32 * part;
-            float x0 = __ldg(k_src + d), x1 = __ldg(k_src + d + kHalfDim);
+            float x0 = __ldcg(k_src + d), x1 = __ldcg(k_src + d + kHalfDim);
             if (kw != nullptr) {
                 x0 = __fmul_rn(__fmul_rn(x0, rs), __ldg(kw + d));
                 x1 = __fmul_rn(__fmul_rn(x1, rs), __ldg(kw + d + kHalfDim));
@@ -495,7 +513,7 @@ struct DensePolicy {
             kh[d] = __float2half_rn(x0);
             kh[d + kHalfDim] = __float2half_rn(x1);
         }
-        const float4 v4 = __ldg(reinterpret_cast<const float4*>(v_src) + lane);
+        const float4 v4 = __ldcg(reinterpret_cast<const float4*>(v_src) + lane);
         uint2 vv;
         reinterpret_cast<__half2*>(&vv)[0] = __halves2half2(__float2half_rn(v4.x), __float2half_rn(v4.y));
         reinterpret_cast<__half2*>(&vv)[1] = __halves2half2(__float2half_rn(v4.z), __float2half_rn(v4.w));
@@ -534,7 +552,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     float2* cos_sin = reinterpret_cast<float2*>(smem + L::kOffCosSin);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
     uint64_t* empty_bar = full_bar + kStages;
-    volatile int* flags = reinterpret_cast<volatile int*>(smem + L::kOffFlags);   // [0] abort [1] item-last [2] grid-last
+    volatile int* flags = reinterpret_cast<volatile int*>(smem + L::kOffFlags);   // [0] abort [1] item-last [2] grid-last [3] item visits whose host rows have landed
     uint8_t* extra = smem + L::kOffExtra;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -547,7 +565,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     // let the next kernel of the stream be placed as this one's CTAs leave (it waits below before reading anything)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
-        flags[0] = 0; flags[1] = 0; flags[2] = 0;
+        flags[0] = 0; flags[1] = 0; flags[2] = 0; flags[3] = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], UPT);
@@ -624,18 +642,44 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
             // ================= producer warp =================
             int k = 0;
             int64_t cur = p.withhold_tiles ? range_end : range_begin;
+            // host-buffer step: rows of the next item visit, in flight over the bus while this visit's tiles are issued
+            const bool hostio = POL::kFusedAppend && p.host_q != nullptr;
+            float4 hq_r[GROUP], hk_r = make_float4(0.f, 0.f, 0.f, 0.f), hv_r = hk_r;
+            int64_t hq_off = 0, hkv_off = 0;
+            int landed = 0;
+            auto host_load = [&](const Segment& s2) {
+                hq_off = (static_cast<int64_t>(s2.pair) * p.num_q_heads + s2.head * GROUP) * kHeadDim;
+                hkv_off = (static_cast<int64_t>(s2.pair) * hkv + s2.head) * kHeadDim;
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) hq_r[g] = ld_volatile_f4(reinterpret_cast<const float4*>(p.host_q + hq_off) + g * 32 + lane);
+                hk_r = ld_volatile_f4(reinterpret_cast<const float4*>(p.host_k + hkv_off) + lane);
+                hv_r = ld_volatile_f4(reinterpret_cast<const float4*>(p.host_v + hkv_off) + lane);
+            };
+            auto host_store = [&]() {   // the loaded rows become the staged rows of their visit; then the consumers may start it
+#pragma unroll
+                for (int g = 0; g < GROUP; ++g) reinterpret_cast<float4*>(const_cast<float*>(p.q) + hq_off)[g * 32 + lane] = hq_r[g];
+                reinterpret_cast<float4*>(const_cast<float*>(p.k_new) + hkv_off)[lane] = hk_r;
+                reinterpret_cast<float4*>(const_cast<float*>(p.v_new) + hkv_off)[lane] = hv_r;
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) flags[3] = ++landed;
+            };
+            if (hostio && cur < range_end) host_load(locate_segment(prefix, num_pairs, hkv, cur, range_end));
             while (cur < range_end) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
                 const int start = kv_start(p, sg.pair, kv_len);
-                // The consumers read this item's query rows (and the new K/V row) only when they get here, several tiles
-                // later: pull the lines into L2 now so that the item switch does not wait on DRAM.
-                if (lane < GROUP * 4)
-                    prefetch_l2(reinterpret_cast<const uint8_t*>(p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim) + lane * 128);
-                if (POL::kFusedAppend && p.fused_append && lane >= 24) {
-                    const int64_t off = (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim * 4 + (lane & 3) * 128;
-                    prefetch_l2(reinterpret_cast<const uint8_t*>((lane & 4) ? p.v_new : p.k_new) + off);
+                bool rows_pending = hostio;   // staged right after the visit's first tile is on its way
+                if (!hostio) {
+                    // The consumers read this item's query rows (and the new K/V row) only when they get here, several tiles
+                    // later: pull the lines into L2 now so that the item switch does not wait on DRAM.
+                    if (lane < GROUP * 4)
+                        prefetch_l2(reinterpret_cast<const uint8_t*>(p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim) + lane * 128);
+                    if (POL::kFusedAppend && p.fused_append && lane >= 24) {
+                        const int64_t off = (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim * 4 + (lane & 3) * 128;
+                        prefetch_l2(reinterpret_cast<const uint8_t*>((lane & 4) ? p.v_new : p.k_new) + off);
+                    }
                 }
                 for (int tu = sg.u0; tu < sg.u1; tu += UPT, ++k) {
                     const int nun = min(UPT, sg.u1 - tu);
@@ -647,6 +691,12 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                         if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status, wait_ns);
                     };
                     POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start, wait_free);
+                    if (rows_pending) {
+                        rows_pending = false;
+                        host_store();
+                        const int64_t nxt = cur + (sg.u1 - sg.u0);
+                        if (nxt < range_end) host_load(locate_segment(prefix, num_pairs, hkv, nxt, range_end));
+                    }
                 }
                 cur += sg.u1 - sg.u0;
             }
@@ -654,7 +704,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
             // ================= consumer warps =================
             float* prob = prob_all + warp * GROUP * kUnitTokens;
             const int wgroup = warp / UPT, wunit = warp % UPT;   // tiles k with k % NG == wgroup are this warp's
-            int k = 0, cs_buf = 0, cs_pos = -1;
+            int k = 0, cs_buf = 0, cs_pos = -1, visit = 0;
             int64_t cur = range_begin;
             while (cur < range_end) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
@@ -672,6 +722,20 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 }
                 float2* cs = cos_sin + cs_buf * kHalfDim;
                 consumer_sync<NW * 32>();
+                if (POL::kFusedAppend && p.host_q != nullptr) {   // the producer warp has this visit's host rows staged?
+                    if (flags[3] <= visit && !flags[0]) {
+                        const uint64_t t_start = global_timer_ns();
+                        uint32_t spins = 0;
+                        while (flags[3] <= visit && !flags[0]) {
+                            if ((++spins & 0xFFu) == 0u && global_timer_ns() - t_start > wait_ns) {
+                                flags[0] = 1;
+                                atomicExch(p.status, kStatusTimeout);
+                            }
+                        }
+                    }
+                    __threadfence();
+                    ++visit;
+                }
 
                 typename POL::State st;
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
@@ -810,7 +874,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     __syncthreads();
     if (tid == 0) stamp(5);
     if (tid == 0) {
-        __threadfence();
+        if (p.host_done != nullptr) __threadfence_system(); else __threadfence();   // output rows may lie in host memory
         const int prev = atomicAdd(p.done_counter, 1);
         flags[2] = (prev == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
     }
@@ -818,7 +882,16 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     if (flags[2]) {
         if (p.advance != 0 && p.lengths != nullptr)
             for (int e = tid; e < num_pairs; e += blockDim.x) p.lengths[p.layer_begin * p.batch + e] += p.advance;
-        if (tid == 0) *p.done_counter = 0;
+        if (tid == 0) {
+            *p.done_counter = 0;
+            if (p.host_done != nullptr) {   // every CTA's rows are out (their fences precede the counter): tell the host
+                __threadfence_system();
+                const int st = *reinterpret_cast<volatile int*>(p.status);
+                reinterpret_cast<volatile int*>(p.host_done)[1] = st;
+                __threadfence_system();
+                reinterpret_cast<volatile int*>(p.host_done)[0] = p.host_epoch;
+            }
+        }
     }
     if (tid == 0) stamp(6);
 }

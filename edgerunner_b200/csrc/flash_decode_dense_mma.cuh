@@ -86,8 +86,8 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
             if (g < GROUP) {
                 const int d0 = 32 * b + 8 * c;
                 auto load8 = [&](int d, float (&out)[8]) {
-                    const float4 lo4 = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d));
-                    const float4 hi4 = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d + 4));
+                    const float4 lo4 = __ldcg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d));
+                    const float4 hi4 = __ldcg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d + 4));
                     out[0] = lo4.x; out[1] = lo4.y; out[2] = lo4.z; out[3] = lo4.w;
                     out[4] = hi4.x; out[5] = hi4.y; out[6] = hi4.z; out[7] = hi4.w;
                     if (qw != nullptr) {

@@ -427,6 +427,60 @@ def test_decode_step_host_buffers(er, oracle, torch):
     assert torch.equal(out_d.cpu(), hout)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(16, 8), (32, 8), (8, 8)])
+def test_decode_step_host_rows_pulled_by_the_kernel(er, torch, Hq, Hkv):
+    """Host-buffer steps on the persistent fp16 kernel: with every buffer pinned the launch pulls its q / k / v rows out of
+    host memory itself (no gather launch, no stream synchronisation; the last CTA reports to a host word).  Several steps
+    re-use the SAME pinned buffers with new contents (a stale cached line would show), ragged batch, pages; outputs and
+    cache rows must equal the device-buffer step's bit for bit.  A pageable output buffer takes the copy path instead."""
+    rng = rng_for(113)
+    L, B, D, ps = 3, 5, 128, 16
+    lens = [700, 33, 1, 260, 415]
+    T = 768
+    pages = (T // ps) * B
+    caches = []
+    for _ in range(3):
+        c = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, layout=er.Layout.paged, page_size=ps, num_pages=pages, decode_kernel=1)
+        alloc = er.BlockTableAllocator(pages, ps, free_order=rng_for(5).permutation(pages))
+        for b in range(B):
+            c.set_block_table(b, alloc.ensure(b, T))
+        caches.append(c)
+    sp = er.step_params(rope_theta=1e6)
+    for l in range(L):
+        for b in range(B):
+            K, V = normal_f16(rng, (lens[b], Hkv, D)), normal_f16(rng, (lens[b], Hkv, D))
+            for c in caches:
+                c.write_rows(l, b, 0, lens[b], dev(torch, K), dev(torch, V), sp)
+    hq = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
+    hk = torch.empty((L, B, Hkv, D), dtype=torch.float32).pin_memory()
+    hv = torch.empty((L, B, Hkv, D), dtype=torch.float32).pin_memory()
+    hout = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
+    pageable_out = np.empty((L, B, Hq, D), dtype=np.float32)
+    out_d = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
+    launches = er.lib().er_kernel_launch_count
+    for step in range(4):
+        q, k, v = (normal_f16(rng, (L, B, h, D)) for h in (Hq, Hkv, Hkv))
+        hq.copy_(torch.as_tensor(q)); hk.copy_(torch.as_tensor(k)); hv.copy_(torch.as_tensor(v))
+        caches[0].decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out_d, Hq, sp)
+        n0 = launches()
+        hout.fill_(float("nan"))
+        caches[1].decode_step_host(hq, hk, hv, hout, Hq, sp)      # returns with the rows in hout: no synchronize here
+        got = hout.clone()
+        assert launches() - n0 == 1                               # the decode launch alone
+        caches[2].decode_step_host(hq, hk, hv, pageable_out, Hq, sp)
+        torch.cuda.synchronize()
+        assert torch.equal(out_d.cpu(), got), step
+        assert np.array_equal(out_d.cpu().numpy(), pageable_out), step
+    for c in caches[1:]:
+        assert c.device_status() == 0
+        for l in range(L):
+            for b in range(B):
+                assert c.total_written(l, b) == lens[b] + 4
+                k0, v0 = caches[0].retrieve(l, np.float16, seq=b)
+                k1, v1 = c.retrieve(l, np.float16, seq=b)
+                assert np.array_equal(k0.view(np.uint16), k1.view(np.uint16)) and np.array_equal(v0.view(np.uint16), v1.view(np.uint16))
+
+
 def test_gqa_kernel_operator_matches_cpu_gqa(er, oracle):
     """GQAKernel on raw fp16 K/V buffers (pipelineF16KV), prefill semantics: the reference's own test shape
     (GQATests.swift:365-434: S=16, D=128, 8 q / 2 kv heads, causal, inputs in [-0.25, 0.25], |err| < 2e-3) plus
