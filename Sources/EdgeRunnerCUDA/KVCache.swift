@@ -192,4 +192,13 @@ public final class KVCache: @unchecked Sendable {
     }
     /// Status word the kernels of this cache leave behind (a bounded wait that gave up, a row without a page).
     public func checkDeviceStatus() throws { try check(er_kv_device_status(handle)) }
+
+    /// Pages as bytes (prefix reuse): `pageBytes` covers all layers; buffers may be device or (pinned) host memory.
+    public var pageBytes: Int { Int(er_kv_page_bytes(handle)) }
+    public func exportPages(_ pages: [Int32], into buffer: UnsafeMutableRawPointer, byteCount: Int, stream: UnsafeMutableRawPointer? = nil) throws {
+        try check(er_kv_export_pages(handle, pages, UInt32(pages.count), buffer, byteCount, stream))
+    }
+    public func importPages(_ pages: [Int32], from buffer: UnsafeRawPointer, byteCount: Int, stream: UnsafeMutableRawPointer? = nil) throws {
+        try check(er_kv_import_pages(handle, pages, UInt32(pages.count), buffer, byteCount, stream))
+    }
 }

@@ -33,7 +33,8 @@ class ERRoPEParams(C.Structure):
 class er_kv_config(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("max_seq_len", "num_layers", "num_kv_heads", "head_dim", "precision",
                                           "key_type", "value_type", "norm_format", "max_batch", "layout",
-                                          "page_size", "num_pages", "prefill_kernel", "decode_kernel")] + [("reserved", C.c_uint32 * 2)]
+                                          "page_size", "num_pages", "prefill_kernel", "decode_kernel")] + [
+        ("key_residual_scale", C.c_float), ("value_residual_scale", C.c_float)]
 
 
 class er_kv_buffers(C.Structure):
@@ -110,6 +111,9 @@ SYMBOLS = {
     "er_workspace_status": (_i32, []),
     "er_gqa_attention_f16kv_static_status": (_i32, []),
     "er_kv_set_trace": (_i32, [_vp, _vp, _u32]),
+    "er_kv_page_bytes": (C.c_int64, [_vp]),
+    "er_kv_export_pages": (_i32, [_vp, _vp, _u32, _vp, _sz, _vp]),
+    "er_kv_import_pages": (_i32, [_vp, _vp, _u32, _vp, _sz, _vp]),
     "er_host_alloc": (_i32, [C.POINTER(_vp), _sz]),
     "er_host_free": (_i32, [_vp]),
 }

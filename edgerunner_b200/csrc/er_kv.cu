@@ -24,6 +24,7 @@
 #include "q8.cuh"
 #include "turboquant.cuh"
 #include "turboquant_outlier.cuh"
+#include "turboquant_outlier_cache.cuh"
 
 using namespace er;
 
@@ -172,6 +173,10 @@ struct er_kv {
     int pages_per_seq = 0;        // block-table stride (0 = identity addressing)
     bool token_major = false;
     bool q8 = false;              // q8_0 rows: int8 part in the K / V slabs, four fp16 scales per row in the side slabs
+    bool outlier = false;         // balanced / aggressive TurboQuant rows: codes + mask + signs + two norms in one block per row
+    OutlierFormat ofmt{};
+    float* d_outlier_partial = nullptr;   // split partials of the outlier decode kernel
+    size_t outlier_partial_floats = 0;
     uint8_t* k_slab = nullptr;
     uint8_t* v_slab = nullptr;
     uint8_t* kn_slab = nullptr;
@@ -348,6 +353,17 @@ int32_t launch_append(er_kv* kv, AppendParams& ap, cudaStream_t stream) {
         return launch_turbo_append(tp, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), stream,
                                    check_launch);
     }
+    if (kv->outlier) {
+        OutlierAppendParams op;
+        op.base = ap;
+        op.fmt = kv->ofmt;
+        op.k_use_benefit = kv->cfg.key_type == ER_TQ_SELECT_QUANTIZATION_BENEFIT ? 1 : 0;                 // default: magnitude
+        op.v_use_benefit = kv->cfg.value_type == ER_TQ_SELECT_MAGNITUDE ? 0 : 1;                          // default: benefit
+        const int64_t jobs = 2 * static_cast<int64_t>(ap.rows) * kv->cfg.num_kv_heads;
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((jobs + kOutlierWarps - 1) / kOutlierWarps, 1 << 16));
+        tq_outlier_append_kernel<<<blocks, kOutlierWarps * 32, 0, stream>>>(op);
+        return check_launch("tq_outlier_append_kernel");
+    }
     if (kv->q8) {
         Q8AppendParams qp;
         qp.base = ap;
@@ -414,8 +430,9 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
     if (c->max_seq_len == 0 || c->num_layers == 0 || c->num_kv_heads == 0 || c->head_dim == 0)
         return fail(ER_ERR_SHAPE, "zero-sized cache dimension");
     switch (c->precision) {
-        case ER_KV_FLOAT32: case ER_KV_FLOAT16: case ER_KV_TURBOQUANT_V2: case ER_KV_Q8_0: break;
-        case ER_KV_FLOAT8: case ER_KV_TURBOQUANT_BALANCED: case ER_KV_TURBOQUANT_AGGRESSIVE:
+        case ER_KV_FLOAT32: case ER_KV_FLOAT16: case ER_KV_TURBOQUANT_V2: case ER_KV_Q8_0:
+        case ER_KV_TURBOQUANT_BALANCED: case ER_KV_TURBOQUANT_AGGRESSIVE: break;
+        case ER_KV_FLOAT8:
             return fail(ER_ERR_UNSUPPORTED_STORAGE, "precision %u is outside this backend's scope", c->precision);
         default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
     }
@@ -428,6 +445,7 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
     if (static_cast<uint64_t>(kv->cfg.num_layers) * kv->cfg.max_batch > 1u << 20) { delete kv; return fail(ER_ERR_SHAPE, "layers*batch too large"); }
     kv->turbo = c->precision == ER_KV_TURBOQUANT_V2;
     kv->q8 = c->precision == ER_KV_Q8_0;
+    kv->outlier = c->precision == ER_KV_TURBOQUANT_BALANCED || c->precision == ER_KV_TURBOQUANT_AGGRESSIVE;
     auto bail = [&](int32_t rc) { er_kv_destroy(kv); return rc; };
     if (cudaGetDevice(&kv->device) != cudaSuccess) return bail(fail(ER_ERR_CUDA, "cudaGetDevice"));
     cudaDeviceGetAttribute(&kv->num_sms, cudaDevAttrMultiProcessorCount, kv->device);
@@ -439,6 +457,16 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         kv->k_row_bytes = tq_code_words(static_cast<int>(c->key_type)) * 4;
         kv->v_row_bytes = tq_code_words(static_cast<int>(c->value_type)) * 4;
         kv->norm_bytes = c->norm_format == ER_TQ_NORM_FLOAT16 ? 2 : 4;
+        if (kv->cfg.layout == ER_KV_LAYOUT_TOKEN_MAJOR) kv->cfg.layout = ER_KV_LAYOUT_HEAD_MAJOR;
+    } else if (kv->outlier) {
+        // TurboQuantPreset.balanced / .aggressive descriptors (TurboQuant.swift:267-327): 3 / 5 bits and 2 / 3 bits, 32 channels
+        if (c->head_dim != kHeadDim) return bail(fail(ER_ERR_SHAPE, "TurboQuant storage needs head_dim 128 (TurboQuantLayout.supportedDimension)"));
+        for (uint32_t t : {c->key_type, c->value_type})
+            if (t > ER_TQ_SELECT_QUANTIZATION_BENEFIT)
+                return bail(fail(ER_ERR_INVALID_ARGUMENT, "outlier selection %u (expected ER_TQ_SELECT_*)", t));
+        kv->ofmt = c->precision == ER_KV_TURBOQUANT_BALANCED ? outlier_format(3, 5, 32) : outlier_format(2, 3, 32);
+        kv->k_row_bytes = kv->v_row_bytes = kv->ofmt.row_words * 4;
+        kv->norm_bytes = 0;
         if (kv->cfg.layout == ER_KV_LAYOUT_TOKEN_MAJOR) kv->cfg.layout = ER_KV_LAYOUT_HEAD_MAJOR;
     } else if (kv->q8) {
         // KVCache.resolvedStorageKind: headDim % 32 == 0 (KVCache.swift:764-768); the kernels here are built for 128
@@ -519,7 +547,7 @@ void er_kv_destroy(er_kv* kv) {
     cudaFree(kv->k_slab); cudaFree(kv->v_slab); cudaFree(kv->kn_slab); cudaFree(kv->vn_slab);
     cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
     cudaFree(kv->d_head_norm[0]); cudaFree(kv->d_head_norm[1]);
-    cudaFree(kv->d_stage);
+    cudaFree(kv->d_stage); cudaFree(kv->d_outlier_partial);
     if (kv->h_status) cudaFreeHost(kv->h_status);
     cudaGetLastError();
     delete kv;
@@ -659,7 +687,7 @@ static int32_t host_append(er_kv* kv, uint32_t layer, uint32_t seq, const void* 
     if (rc != ER_OK) return rc;
     ER_CUDA(cudaMemcpy(kv->d_stage, hk, bytes, cudaMemcpyHostToDevice));
     ER_CUDA(cudaMemcpy(kv->d_stage + bytes, hv, bytes, cudaMemcpyHostToDevice));
-    if (kv->turbo || kv->q8) {
+    if (kv->turbo || kv->q8 || kv->outlier) {
         AppendParams ap{};
         ap.k = reinterpret_cast<const float*>(kv->d_stage);
         ap.v = reinterpret_cast<const float*>(kv->d_stage + bytes);
@@ -689,7 +717,7 @@ int32_t er_kv_append_f32(er_kv* kv, uint32_t layer, uint32_t seq, const float* h
     if (!kv || !hk || !hv) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     // KVCache.append: float32, q8_0 and TurboQuant precisions; everything else is precisionMismatch (KVCache.swift:436-452).
-    if (kv->cfg.precision != ER_KV_FLOAT32 && !kv->turbo && !kv->q8) return fail(ER_ERR_PRECISION_MISMATCH, "append of Float rows into precision %u", kv->cfg.precision);
+    if (kv->cfg.precision != ER_KV_FLOAT32 && !kv->turbo && !kv->q8 && !kv->outlier) return fail(ER_ERR_PRECISION_MISMATCH, "append of Float rows into precision %u", kv->cfg.precision);
     return host_append(kv, layer, seq, hk, hv, count, 4);
 }
 
@@ -713,7 +741,7 @@ int32_t er_kv_retrieve(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t element
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
     // validateRequestedType (KVCache.swift:866-883)
-    if (kv->turbo) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "TurboQuant cache");
+    if (kv->turbo || kv->outlier) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "TurboQuant cache");
     if (kv->q8) return fail(ER_ERR_COMPRESSED_RETRIEVE_REQUIRES_DECODED_API, "q8_0 cache");
     if (static_cast<int>(element_bytes) != kv->elem_bytes) return fail(ER_ERR_PRECISION_MISMATCH, "requested %u-byte elements from a %d-byte cache", element_bytes, kv->elem_bytes);
     int32_t rc = check_device(kv);
@@ -746,7 +774,7 @@ int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, 
     if (!kv || !row_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
-    if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
+    if (!kv->turbo && !kv->outlier) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
     int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
@@ -757,6 +785,25 @@ int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, 
     *row_count = static_cast<uint32_t>(rows);
     if (rows == 0) return ER_OK;
     if (capacity_rows < rows || !h_codes || !h_meta) return fail(ER_ERR_SHAPE, "output capacity %zu < %zu rows", capacity_rows, rows);
+    if (kv->outlier) {   // codes | signs | mask | meta, split out of the cached blocks on the device
+        const size_t code_bytes = rows * kv->ofmt.wpr * 4;
+        const size_t o_signs = (code_bytes + 255) & ~size_t(255), o_mask = o_signs + rows * 16, o_meta = o_mask + rows * 16;
+        rc = ensure_stage(kv, o_meta + rows * 8);
+        if (rc != ER_OK) return rc;
+        OutlierExportParams ep;
+        ep.rows = (is_value ? kv->v_slab : kv->k_slab) + layer * (is_value ? kv->v_layer_stride : kv->k_layer_stride);
+        ep.codes = reinterpret_cast<uint32_t*>(kv->d_stage); ep.signs = reinterpret_cast<uint32_t*>(kv->d_stage + o_signs);
+        ep.mask = reinterpret_cast<uint32_t*>(kv->d_stage + o_mask); ep.meta = reinterpret_cast<float*>(kv->d_stage + o_meta);
+        ep.fmt = kv->ofmt; ep.addr = kv->addressing();
+        ep.seq = static_cast<int>(seq); ep.first_slot = first_slot; ep.tokens = tokens;
+        tq_outlier_export_rows_kernel<<<static_cast<unsigned>(std::min<size_t>((rows + 7) / 8, 8192)), 256>>>(ep);
+        if ((rc = check_launch("tq_outlier_export_rows_kernel")) != ER_OK) return rc;
+        ER_CUDA(cudaMemcpy(h_codes, ep.codes, code_bytes, cudaMemcpyDeviceToHost));
+        ER_CUDA(cudaMemcpy(h_meta, ep.meta, rows * 8, cudaMemcpyDeviceToHost));
+        if (h_signs) ER_CUDA(cudaMemcpy(h_signs, ep.signs, rows * 16, cudaMemcpyDeviceToHost));
+        if (h_mask) ER_CUDA(cudaMemcpy(h_mask, ep.mask, rows * 16, cudaMemcpyDeviceToHost));
+        return ER_OK;
+    }
     const int row_bytes = is_value ? kv->v_row_bytes : kv->k_row_bytes;
     const size_t code_bytes = rows * row_bytes, norm_bytes = rows * kv->norm_bytes;
     const size_t norm_off = (code_bytes + 255) & ~size_t(255);
@@ -786,7 +833,7 @@ int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t se
     if (!kv || !token_count) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
-    if (!kv->turbo) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
+    if (!kv->turbo && !kv->outlier) return fail(ER_ERR_PRECISION_MISMATCH, "not a TurboQuant cache");
     int32_t rc = check_device(kv);
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
@@ -800,6 +847,23 @@ int32_t er_kv_retrieve_decoded_turboquant(er_kv* kv, uint32_t layer, uint32_t se
     if (!hk || !hv || capacity < elems) return fail(ER_ERR_SHAPE, "output capacity %zu < %zu elements", capacity, elems);
     rc = ensure_stage(kv, 2 * elems * 4);
     if (rc != ER_OK) return rc;
+    if (kv->outlier) {
+        // approximateDecode: keys with the default residualWeight 1, values with the contract's valueResidualScale
+        // (KVCache.swift:556-581)
+        OutlierDecodeRowsParams dp;
+        dp.fmt = kv->ofmt; dp.addr = kv->addressing();
+        dp.seq = static_cast<int>(seq); dp.first_slot = first_slot; dp.tokens = tokens;
+        for (int is_v = 0; is_v < 2; ++is_v) {
+            dp.rows = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+            dp.out = reinterpret_cast<float*>(kv->d_stage) + is_v * elems;
+            dp.residual_weight = is_v ? kv->cfg.value_residual_scale : 1.0f;
+            tq_outlier_decode_rows_kernel<<<static_cast<unsigned>(std::min<size_t>((rows + 7) / 8, 8192)), 256>>>(dp);
+            if ((rc = check_launch("tq_outlier_decode_rows_kernel")) != ER_OK) return rc;
+        }
+        ER_CUDA(cudaMemcpy(hk, kv->d_stage, elems * 4, cudaMemcpyDeviceToHost));
+        ER_CUDA(cudaMemcpy(hv, kv->d_stage + elems * 4, elems * 4, cudaMemcpyDeviceToHost));
+        return ER_OK;
+    }
     TurboDecodeRowsParams dp;
     dp.addr = kv->addressing();
     dp.seq = static_cast<int>(seq); dp.first_slot = first_slot; dp.tokens = tokens;
@@ -1191,6 +1255,51 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
     if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
         return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
+    if (kv->outlier) {
+        // balanced / aggressive rows: the general form of gqa_attention_turboquant_decode (Shaders/TurboQuant.metal:1794-2001)
+        const int pairs = static_cast<int>((le - lb) * kv->cfg.max_batch);
+        if (pairs > 65535) return fail(ER_ERR_UNSUPPORTED, "%d (layer, sequence) pairs in one call; at most 65535", pairs);
+        const int items = pairs * static_cast<int>(kv->cfg.num_kv_heads);
+        int splits = std::max(1, (4 * std::max(kv->num_sms, 1) + items - 1) / items);
+        splits = std::min(splits, std::max(1, static_cast<int>((kv->cfg.max_seq_len + 63) / 64)));
+        const size_t need = static_cast<size_t>(items) * splits * group * kOutlierPartialStride;
+        if (kv->outlier_partial_floats < need) {
+            if (kv->d_outlier_partial) cudaFree(kv->d_outlier_partial);
+            kv->d_outlier_partial = nullptr;
+            kv->outlier_partial_floats = 0;
+            if (cudaMalloc(&kv->d_outlier_partial, need * sizeof(float)) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(ER_ERR_ALLOCATION_FAILED, "split partials of %zu floats", need);
+            }
+            kv->outlier_partial_floats = need;
+        }
+        OutlierDecodeParams op{};
+        op.q = q; op.out = out;
+        op.k_base = kv->k_slab; op.v_base = kv->v_slab;
+        op.k_layer_stride_bytes = kv->k_layer_stride; op.v_layer_stride_bytes = kv->v_layer_stride;
+        op.lengths = kv->d_lengths; op.layer_begin = static_cast<int>(lb); op.batch = static_cast<int>(kv->cfg.max_batch);
+        op.num_q_heads = static_cast<int>(num_heads); op.pending = static_cast<int>(pending); op.splits = splits;
+        op.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+        op.apply_rope = s.apply_rope ? 1 : 0; op.rope_scaling = s.rope_scaling;
+        if (op.apply_rope) op.inv_freq = kv->freq(s.rope_theta);
+        op.k_res_coef = kQjlScale * kv->cfg.key_residual_scale; op.v_res_coef = kQjlScale * kv->cfg.value_residual_scale;
+        op.fmt = kv->ofmt; op.addr = kv->addressing();
+        op.partial = kv->d_outlier_partial;
+        if (kv->out_heads_total > 0) {
+            if (kv->num_peers > 0) return fail(ER_ERR_UNSUPPORTED, "peer outputs are built for the flash-decode kernels");
+            if (kv->out_head_offset + num_heads > kv->out_heads_total) return fail(ER_ERR_SHAPE, "output sharding: heads exceed %u", kv->out_heads_total);
+            op.out_heads_total = static_cast<int>(kv->out_heads_total); op.out_head_offset = static_cast<int>(kv->out_head_offset);
+        }
+        const int orc = launch_outlier_decode(group, op, pairs, stream);
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        if (orc != 0) return fail(orc == kNotBuilt ? ER_ERR_UNSUPPORTED : ER_ERR_CUDA, "tq_outlier_decode_kernel: %s",
+                                  orc == kNotBuilt ? "GQA groups 1, 2, 4, 8 are built" : cudaGetErrorString(static_cast<cudaError_t>(orc)));
+        if (advance != 0) {
+            add_lengths_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), pairs, static_cast<int>(advance));
+            return check_launch("add_lengths_kernel");
+        }
+        return ER_OK;
+    }
     // (layer, sequence) pairs are scheduled kMaxPairs at a time.
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
     if (kv->cfg.max_batch > static_cast<uint32_t>(kMaxPairs)) return fail(ER_ERR_UNSUPPORTED, "max_batch %u > %d", kv->cfg.max_batch, kMaxPairs);
@@ -1290,7 +1399,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     if (!kv || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
     if (layer >= kv->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
     if (seq >= kv->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
-    if ((kv->cfg.precision != ER_KV_FLOAT16 && !kv->turbo && !kv->q8) || kv->cfg.head_dim != kHeadDim)
+    if ((kv->cfg.precision != ER_KV_FLOAT16 && !kv->turbo && !kv->q8 && !kv->outlier) || kv->cfg.head_dim != kHeadDim)
         return fail(ER_ERR_UNSUPPORTED, "chunked prefill attention is built for float16, q8_0 and TurboQuant caches with head_dim 128");
     if (num_heads == 0 || num_heads % kv->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kv->cfg.num_kv_heads);
     if (seq_len == 0) return ER_OK;
@@ -1313,7 +1422,8 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.kv_len_ptr = kv->d_lengths + static_cast<size_t>(layer) * kv->cfg.max_batch + seq;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     const int n_qrows = static_cast<int>(seq_len * num_heads);
-    if (kv->turbo) {
+    const bool rotated = kv->turbo || kv->outlier;
+    if (rotated) {
         // Rotated-space formulation: expand the sequence's codes to fp16 rows norm*centroid, rotate the queries, run the
         // same tensor-core kernel, rotate the outputs back.
         const int tpad = (static_cast<int>(kv->cfg.max_seq_len) + 15) & ~15;
@@ -1326,7 +1436,20 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         __half* ekl = reinterpret_cast<__half*>(kv->d_stage + 2 * rows_bytes);   // keys and values keep their fp16 rounding residue
         __half* evl = reinterpret_cast<__half*>(kv->d_stage + 3 * rows_bytes);
         float* qrot = reinterpret_cast<float*>(kv->d_stage + 4 * rows_bytes);
-        for (int is_v = 0; is_v < 2; ++is_v) {
+        for (int is_v = 0; is_v < 2 && kv->outlier; ++is_v) {   // effective coordinates: centroid + residual term, times rowNorm
+            OutlierExpandParams ep{};
+            ep.rows = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
+            ep.out = is_v ? ev : ek;
+            ep.out_lo = is_v ? evl : ekl;
+            ep.fmt = kv->ofmt; ep.addr = kv->addressing();
+            ep.len_ptr = pp.kv_len_ptr;
+            ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
+            ep.res_coef = kQjlScale * (is_v ? kv->cfg.value_residual_scale : kv->cfg.key_residual_scale);
+            const int64_t max_rows = static_cast<int64_t>(kv->cfg.max_seq_len) * kv->cfg.num_kv_heads;
+            tq_outlier_expand_rows_kernel<<<static_cast<unsigned>(std::min<int64_t>((max_rows + 7) / 8, 16384)), 256, 0, cs>>>(ep);
+            if ((rc = check_launch("tq_outlier_expand_rows_kernel")) != ER_OK) return rc;
+        }
+        for (int is_v = 0; is_v < 2 && kv->turbo; ++is_v) {
             TurboExpandParams ep{};
             ep.codes = (is_v ? kv->v_slab : kv->k_slab) + layer * (is_v ? kv->v_layer_stride : kv->k_layer_stride);
             ep.norms = (is_v ? kv->vn_slab : kv->kn_slab) + layer * kv->n_layer_stride;
@@ -1395,13 +1518,13 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;
     if (pp.apply_rope) pp.inv_freq = kv->freq(s.rope_theta);
-    const uint64_t outer_extent = (kv->turbo || kv->q8) ? 1u : static_cast<uint64_t>(kv->pool_pages);
+    const uint64_t outer_extent = (rotated || kv->q8) ? 1u : static_cast<uint64_t>(kv->pool_pages);
     const int rcl = launch_prefill(static_cast<int>(num_heads / kv->cfg.num_kv_heads), pp, outer_extent, static_cast<int>(kv->cfg.num_kv_heads),
                                    kv->d_counters + 1, static_cast<cudaStream_t>(stream), kv->cfg.prefill_kernel == ER_PREFILL_KERNEL_MMA_SYNC);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
     if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
-    if (kv->turbo) {
+    if (rotated) {
         TurboRotateParams rp{};
         rp.in = out; rp.out = out; rp.rows = n_qrows; rp.heads = static_cast<int>(num_heads); rp.inverse = 1;
         tq_rotate_rows_kernel<<<std::min((n_qrows + 7) / 8, 4096), 256, 0, cs>>>(rp);
@@ -1429,7 +1552,7 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
     if ((rc = check_device(kv)) != ER_OK) return rc;
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32;
+    const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32 || kv->outlier;
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.
     const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;
@@ -1548,6 +1671,59 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     ER_CUDA(cudaMemcpyAsync(kv->h_status, kv->d_counters + 1, sizeof(int), cudaMemcpyDeviceToHost, s));
     ER_CUDA(cudaStreamSynchronize(s));
     return device_status_to_code(*kv->h_status);
+}
+
+// ---- pages as bytes: prefix reuse across sequences and caches of the same shape ----
+
+namespace {
+struct PageGeometry { size_t k, v, n; };   // bytes of one page of one layer in the K / V slabs and in each side slab
+PageGeometry page_geometry(const er_kv* kv) {
+    const size_t rows = static_cast<size_t>(kv->cfg.num_kv_heads) * static_cast<size_t>(kv->page_tokens);
+    return {rows * kv->k_row_bytes, rows * kv->v_row_bytes, rows * kv->norm_bytes};
+}
+int32_t move_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, uint8_t* buffer, size_t buffer_bytes, bool to_buffer, void* stream) {
+    if (!kv || (!page_ids && count) || (!buffer && count)) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (kv->token_major) return fail(ER_ERR_UNSUPPORTED, "page export / import needs the head-major or the paged layout");
+    int32_t rc = check_device(kv);
+    if (rc != ER_OK) return rc;
+    const PageGeometry g = page_geometry(kv);
+    const size_t L = kv->cfg.num_layers, per_page = L * (g.k + g.v + 2 * g.n);
+    if (buffer_bytes < per_page * count) return fail(ER_ERR_INVALID_ARGUMENT, "buffer of %zu bytes for %u pages of %zu bytes", buffer_bytes, count, per_page);
+    for (uint32_t i = 0; i < count; ++i)
+        if (page_ids[i] < 0 || page_ids[i] >= kv->pool_pages) return fail(ER_ERR_INVALID_ARGUMENT, "page %d of a pool of %d", page_ids[i], kv->pool_pages);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::lock_guard<std::mutex> lock(kv->mu);
+    for (uint32_t i = 0; i < count; ++i) {
+        uint8_t* at = buffer + per_page * i;
+        // one strided copy per slab: `layers` runs of a page's bytes, a layer stride apart in the cache, packed in the buffer
+        auto slab = [&](uint8_t* base, int64_t layer_stride, size_t bytes) -> cudaError_t {
+            if (bytes == 0) return cudaSuccess;
+            uint8_t* in_cache = base + static_cast<size_t>(page_ids[i]) * bytes;
+            const cudaError_t e = to_buffer ? cudaMemcpy2DAsync(at, bytes, in_cache, static_cast<size_t>(layer_stride), bytes, L, cudaMemcpyDefault, s)
+                                            : cudaMemcpy2DAsync(in_cache, static_cast<size_t>(layer_stride), at, bytes, bytes, L, cudaMemcpyDefault, s);
+            at += bytes * L;
+            return e;
+        };
+        ER_CUDA(slab(kv->k_slab, kv->k_layer_stride, g.k));
+        ER_CUDA(slab(kv->v_slab, kv->v_layer_stride, g.v));
+        ER_CUDA(slab(kv->kn_slab, kv->n_layer_stride, g.n));
+        ER_CUDA(slab(kv->vn_slab, kv->n_layer_stride, g.n));
+    }
+    return ER_OK;
+}
+}  // namespace
+
+int64_t er_kv_page_bytes(er_kv* kv) {
+    if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
+    if (kv->token_major) return fail(ER_ERR_UNSUPPORTED, "page export / import needs the head-major or the paged layout");
+    const PageGeometry g = page_geometry(kv);
+    return static_cast<int64_t>(kv->cfg.num_layers * (g.k + g.v + 2 * g.n));
+}
+int32_t er_kv_export_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, void* buffer, size_t buffer_bytes, void* stream) {
+    return move_pages(kv, page_ids, count, static_cast<uint8_t*>(buffer), buffer_bytes, true, stream);
+}
+int32_t er_kv_import_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, const void* buffer, size_t buffer_bytes, void* stream) {
+    return move_pages(kv, page_ids, count, static_cast<uint8_t*>(const_cast<void*>(buffer)), buffer_bytes, false, stream);
 }
 
 int32_t er_kv_set_trace(er_kv* kv, uint64_t* device_buffer, uint32_t capacity_ctas) {

@@ -1,5 +1,5 @@
 // TurboQuant device math (tables, code lookup, warp-level transforms) shared by the quantise kernels and the
-// decode policy.  TurboQuant row codec on the device: seeded-sign randomized Hadamard rotation, Lloyd-Max scalar codes,
+// decode policy.  TurboQuant row codec on the device: randomized Hadamard rotation with the reference's fixed sign tables (the reference ignores its seed, TurboQuant.swift:918-921), Lloyd-Max scalar codes,
 // corrected per-row norm.  Restates, warp-cooperatively, what the reference does with one thread per row:
 //   turboquant_quantize_rows           Shaders/TurboQuant.metal:562-709
 //   TurboQuantReferenceEncoder.encode  Sources/EdgeRunnerMetal/TurboQuant.swift:1003-1074 (fixed presets)

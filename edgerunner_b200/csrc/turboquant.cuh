@@ -117,6 +117,38 @@ struct TurboAppendParams {
     int norm_fp16;
 };
 
+// A source row of an append (kv head h of source row r) as a warp holds it -- lane L: coordinates 4L .. 4L + 3 -- with the
+// NeoX rotation of K rows at the row's position applied (cos / sin exactly rounded: these values decide cache bits).
+__device__ __forceinline__ float4 tq_append_load_row(const AppendParams& p, bool is_v, int r, int h, int lane) {
+    const int hkv = p.addr.num_kv_heads;
+    const float* src = (is_v ? p.v : p.k) + (static_cast<int64_t>(r) * hkv + h) * kHeadDim;
+    float4 x = __ldg(reinterpret_cast<const float4*>(src + 4 * lane));
+    if (!is_v && p.apply_rope) {
+        int layer, seq;
+        uint32_t pos;
+        append_locate(p, r, layer, seq, pos);
+        // lane holds dims 4*lane..+3; the NeoX partner (d +- 64) lives 16 lanes away.
+        float xs[4] = {x.x, x.y, x.z, x.w}, ys[4];
+        // Lanes l and l^16 need the same four (cos, sin) pairs: each computes two and they swap.
+        const int base_pair = 4 * (lane & 15), mine = (lane >> 4) * 2;
+        const float2 m0 = rope_cos_sin(pos, p.inv_freq.f[base_pair + mine], p.rope_scaling);
+        const float2 m1 = rope_cos_sin(pos, p.inv_freq.f[base_pair + mine + 1], p.rope_scaling);
+        float2 o0, o1;
+        o0.x = __shfl_xor_sync(0xffffffffu, m0.x, 16); o0.y = __shfl_xor_sync(0xffffffffu, m0.y, 16);
+        o1.x = __shfl_xor_sync(0xffffffffu, m1.x, 16); o1.y = __shfl_xor_sync(0xffffffffu, m1.y, 16);
+        const float2 cs4[4] = {lane < 16 ? m0 : o0, lane < 16 ? m1 : o1, lane < 16 ? o0 : m0, lane < 16 ? o1 : m1};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float other = __shfl_xor_sync(0xffffffffu, xs[c], 16);
+            float y0, y1;
+            if (lane < 16) { rope_rotate(xs[c], other, cs4[c], y0, y1); ys[c] = y0; }
+            else           { rope_rotate(other, xs[c], cs4[c], y0, y1); ys[c] = y1; }
+        }
+        x = make_float4(ys[0], ys[1], ys[2], ys[3]);
+    }
+    return x;
+}
+
 // Fused decode/prefill append for a TurboQuant cache: [NeoX RoPE on K] -> quantise -> packed row + norm
 // into the cache slot.  Job j = (source row r, kv head h, K or V); a warp takes `jobs_per_warp`
 // consecutive jobs.  Replaces RoPE(K) + 2 x turboquant_quantize_rows per layer
@@ -147,31 +179,7 @@ __global__ void __launch_bounds__(kQuantWarps * 32) tq_append_kernel(const __gri
     for (int jj = 0; jj < njobs; ++jj) {
         const int64_t job = first + jj;
         const int r = static_cast<int>(job / hkv), h = static_cast<int>(job % hkv);
-        const float* src = (is_v ? p.v : p.k) + (static_cast<int64_t>(r) * hkv + h) * kHeadDim;
-        float4 x = __ldg(reinterpret_cast<const float4*>(src + 4 * lane));
-        if (!is_v && p.apply_rope) {
-            int layer, seq;
-            uint32_t pos;
-            append_locate(p, r, layer, seq, pos);
-            // lane holds dims 4*lane..+3; the NeoX partner (d +- 64) lives 16 lanes away.
-            float xs[4] = {x.x, x.y, x.z, x.w}, ys[4];
-            // Lanes l and l^16 need the same four (cos, sin) pairs: each computes two and they swap.
-            const int base_pair = 4 * (lane & 15), mine = (lane >> 4) * 2;
-            const float2 m0 = rope_cos_sin(pos, p.inv_freq.f[base_pair + mine], p.rope_scaling);
-            const float2 m1 = rope_cos_sin(pos, p.inv_freq.f[base_pair + mine + 1], p.rope_scaling);
-            float2 o0, o1;
-            o0.x = __shfl_xor_sync(0xffffffffu, m0.x, 16); o0.y = __shfl_xor_sync(0xffffffffu, m0.y, 16);
-            o1.x = __shfl_xor_sync(0xffffffffu, m1.x, 16); o1.y = __shfl_xor_sync(0xffffffffu, m1.y, 16);
-            const float2 cs4[4] = {lane < 16 ? m0 : o0, lane < 16 ? m1 : o1, lane < 16 ? o0 : m0, lane < 16 ? o1 : m1};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float other = __shfl_xor_sync(0xffffffffu, xs[c], 16);
-                float y0, y1;
-                if (lane < 16) { rope_rotate(xs[c], other, cs4[c], y0, y1); ys[c] = y0; }
-                else           { rope_rotate(other, xs[c], cs4[c], y0, y1); ys[c] = y1; }
-            }
-            x = make_float4(ys[0], ys[1], ys[2], ys[3]);
-        }
+        const float4 x = tq_append_load_row(p, is_v, r, h, lane);
         float* row = tile + jj * kQuantRowStride + 4 * lane;
         row[0] = x.x; row[1] = x.y; row[2] = x.z; row[3] = x.w;
     }

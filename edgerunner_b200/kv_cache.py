@@ -16,6 +16,15 @@ from ._lib import (EdgeRunnerCUDAError, ERKVCacheParams, check, er_kv_buffers, e
 ALL_SEQUENCES = 0xFFFFFFFF
 
 
+def _sync_current_stream(stream):
+    """Host-visible completion of copies enqueued on `stream` (None: the whole device)."""
+    import torch
+    if stream is None or isinstance(stream, int):
+        torch.cuda.synchronize()
+    else:
+        stream.synchronize()
+
+
 class Precision(enum.IntEnum):
     """KVCache.Precision raw values (KVCache.swift:39-49)."""
     float32 = 0
@@ -32,6 +41,13 @@ class TurboQuantFixedType(enum.IntEnum):
     turbo2 = 2
     turbo3 = 3
     turbo4 = 4
+
+
+class OutlierSelection(enum.IntEnum):
+    """TurboQuantOutlierSelection (TurboQuant.swift:1185-1238); default_ = the contract's rule for the tensor."""
+    default_ = 0
+    magnitude = 1
+    quantizationBenefit = 2
 
 
 class Layout(enum.IntEnum):
@@ -58,10 +74,19 @@ def step_params(rope_theta=10000.0, rope_scaling=1.0, softmax_scale=0.0, apply_r
 
 
 class KVCache:
-    def __init__(self, max_seq_len, num_layers, num_kv_heads, head_dim, precision, *, key_type=TurboQuantFixedType.turbo3,
-                 value_type=TurboQuantFixedType.turbo3, norm_format=NormFormat.float32, max_batch=1,
-                 layout=Layout.head_major, page_size=0, num_pages=0, prefill_kernel=0, decode_kernel=0):
+    def __init__(self, max_seq_len, num_layers, num_kv_heads, head_dim, precision, *, key_type=None, value_type=None,
+                 norm_format=NormFormat.float32, max_batch=1, layout=Layout.head_major, page_size=0, num_pages=0,
+                 prefill_kernel=0, decode_kernel=0, key_residual_scale=0.0, value_residual_scale=0.0):
+        """key_type / value_type: TurboQuantFixedType for turboquantV2 caches (default turbo3, the reference's contract);
+        OutlierSelection for turboQuantBalanced / turboQuantAggressive caches (default: keys by magnitude, values by
+        quantisation benefit), whose residual scales default to the contract's 0."""
+        preset = int(precision) in (int(Precision.turboQuantBalanced), int(Precision.turboQuantAggressive))
+        if key_type is None:
+            key_type = 0 if preset else TurboQuantFixedType.turbo3
+        if value_type is None:
+            value_type = 0 if preset else TurboQuantFixedType.turbo3
         cfg = er_kv_config()
+        cfg.key_residual_scale, cfg.value_residual_scale = float(key_residual_scale), float(value_residual_scale)
         cfg.max_seq_len, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim = max_seq_len, num_layers, num_kv_heads, head_dim
         cfg.precision, cfg.key_type, cfg.value_type = int(precision), int(key_type), int(value_type)
         cfg.norm_format, cfg.max_batch, cfg.layout = int(norm_format), max_batch, int(layout)
@@ -94,7 +119,12 @@ class KVCache:
 
     @property
     def is_turboquant(self):
-        return self.precision == Precision.turboquantV2
+        return self.precision in (Precision.turboquantV2, Precision.turboQuantBalanced, Precision.turboQuantAggressive)
+
+    @property
+    def outlier_preset(self):
+        """(regular bits, high-precision bits, high-precision channels) of a balanced / aggressive cache, else None."""
+        return {Precision.turboQuantBalanced: (3, 5, 32), Precision.turboQuantAggressive: (2, 3, 32)}.get(self.precision)
 
     @property
     def elements_per_token(self):
@@ -166,6 +196,9 @@ class KVCache:
         cap = self.max_seq_len * self.num_kv_heads
         for is_value, bits in ((0, self.key_type), (1, self.value_type)):
             words = (128 * bits + 31) // 32
+            if self.outlier_preset is not None:
+                rb, hb, n_high = self.outlier_preset
+                words = (128 * rb + n_high * (hb - rb) + 31) // 32
             codes = np.zeros((cap, words), dtype=np.uint32)
             signs = np.zeros((cap, 4), dtype=np.uint32)
             mask = np.zeros((cap, 4), dtype=np.uint32)
@@ -254,6 +287,32 @@ class KVCache:
 
     def write_rows(self, layer, seq, start, count, k, v, params, stream=None):
         check(lib().er_kv_write_rows(self._h, layer, seq, start, count, ptr(k), ptr(v), C.byref(params), stream_ptr(stream)))
+
+    def page_bytes(self):
+        """Bytes of one page over all layers, side arrays included (er_kv_page_bytes)."""
+        return check(lib().er_kv_page_bytes(self._h))
+
+    def export_pages(self, page_ids, buffer=None, stream=None):
+        """Pack the pages into `buffer` (torch CUDA / pinned tensor, numpy array or raw address; default: a new numpy
+        uint8 array, copied synchronously) and return it."""
+        ids = np.ascontiguousarray(page_ids, dtype=np.int32)
+        need = int(self.page_bytes()) * len(ids)
+        own = buffer is None
+        if own:
+            buffer = np.empty(need, dtype=np.uint8)
+        size = need if isinstance(buffer, int) else int(buffer.nbytes if hasattr(buffer, "nbytes") else buffer.numel() * buffer.element_size())
+        check(lib().er_kv_export_pages(self._h, ids.ctypes.data, len(ids), ptr(buffer), size, stream_ptr(stream)))
+        if own or stream is None:
+            _sync_current_stream(stream)
+        return buffer
+
+    def import_pages(self, page_ids, buffer, stream=None):
+        ids = np.ascontiguousarray(page_ids, dtype=np.int32)
+        size = int(self.page_bytes()) * len(ids) if isinstance(buffer, int) else int(
+            buffer.nbytes if hasattr(buffer, "nbytes") else buffer.numel() * buffer.element_size())
+        check(lib().er_kv_import_pages(self._h, ids.ctypes.data, len(ids), ptr(buffer), size, stream_ptr(stream)))
+        if stream is None:
+            _sync_current_stream(stream)
 
     def set_trace(self, buffer, capacity_ctas):
         """Install (or, with None, remove) a device int64 buffer [capacity_ctas, 8] for per-CTA phase timestamps."""

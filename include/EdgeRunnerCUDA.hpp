@@ -80,6 +80,8 @@ public:
         uint32_t maxBatch = 1;
         Layout layout = Layout::headMajor;
         uint32_t pageSize = 0, numPages = 0;
+        uint32_t prefillKernel = ER_PREFILL_KERNEL_AUTO, decodeKernel = ER_DECODE_KERNEL_AUTO;   // A/B switches, er_kv_config
+        float keyResidualScale = 0.f, valueResidualScale = 0.f;   // balanced / aggressive rows: TurboQuantV2Contract's residual scales
     };
 
     // KVCache.init(device:maxSeqLen:numLayers:numKVHeads:headDim:precision:) throws, KVCache.swift:192-275
@@ -98,6 +100,15 @@ public:
         c.layout = static_cast<uint32_t>(opt.layout);
         c.page_size = opt.pageSize;
         c.num_pages = opt.numPages;
+        c.prefill_kernel = opt.prefillKernel;
+        c.decode_kernel = opt.decodeKernel;
+        c.key_residual_scale = opt.keyResidualScale;
+        c.value_residual_scale = opt.valueResidualScale;
+        if (precision == Precision::turboQuantBalanced || precision == Precision::turboQuantAggressive) {
+            // key_type / value_type name the channel-selection rules there; 0 = the contract's (magnitude / quantisation benefit)
+            if (c.key_type > ER_TQ_SELECT_QUANTIZATION_BENEFIT) c.key_type = ER_TQ_SELECT_DEFAULT;
+            if (c.value_type > ER_TQ_SELECT_QUANTIZATION_BENEFIT) c.value_type = ER_TQ_SELECT_DEFAULT;
+        }
         check(er_kv_create(&c, &handle_));
         options_ = opt;
     }
@@ -111,6 +122,9 @@ public:
     const Precision precision;
 
     int elementsPerToken() const { return numKVHeads * headDim; }
+    bool isTurboQuant() const {   // KVCache.Precision.isTurboQuant
+        return precision == Precision::turboquantV2 || precision == Precision::turboQuantBalanced || precision == Precision::turboQuantAggressive;
+    }
     int currentLength() const { return check(er_kv_current_length(handle_)); }
     er_kv* handle() const { return handle_; }
 
@@ -163,6 +177,8 @@ public:
         TurboQuantRuntimeRows r;
         const uint32_t bits = values ? options_.valueType : options_.keyType;
         r.codeWordsPerRow = (128 * bits + 31) / 32;
+        if (precision == Precision::turboQuantBalanced) r.codeWordsPerRow = 14;    // TurboQuantReferenceTests.swift:112-143
+        if (precision == Precision::turboQuantAggressive) r.codeWordsPerRow = 9;
         const size_t cap = static_cast<size_t>(maxSeqLen) * numKVHeads;
         r.codes.resize(cap * r.codeWordsPerRow);
         r.residualSigns.resize(cap * 4);
@@ -182,14 +198,14 @@ public:
     std::pair<void*, void*> metalBuffers(int layer) const {
         er_kv_buffers b{};
         check(er_kv_device_buffers(handle_, static_cast<uint32_t>(layer), &b));
-        if (precision == Precision::turboquantV2) throw KVCacheError(ER_ERR_COMPRESSED_BUFFER_ACCESS_REQUIRES_TURBOQUANT_API);
+        if (isTurboQuant()) throw KVCacheError(ER_ERR_COMPRESSED_BUFFER_ACCESS_REQUIRES_TURBOQUANT_API);
         return {b.keys, b.values};
     }
     // turboQuantMetalBuffers(layer:), KVCache.swift:647-667
     er_kv_buffers turboQuantMetalBuffers(int layer) const {
         er_kv_buffers b{};
         check(er_kv_device_buffers(handle_, static_cast<uint32_t>(layer), &b));
-        if (precision != Precision::turboquantV2) throw KVCacheError(ER_ERR_PRECISION_MISMATCH);
+        if (!isTurboQuant()) throw KVCacheError(ER_ERR_PRECISION_MISMATCH);
         return b;
     }
 
@@ -223,10 +239,101 @@ public:
                                      static_cast<uint32_t>(numHeads), &params, stream));
     }
 
+    // The pieces of a step (LlamaLanguageModel.swift:3649-3941): append without advancing, attention over the rows plus
+    // `pending` uncommitted ones, advance.
+    void appendRoPEKV(int layerBegin, int layerEnd, const float* k, const float* v, const er_step_params& params, void* stream = nullptr) {
+        check(er_kv_append_rope_kv(handle_, static_cast<uint32_t>(layerBegin), static_cast<uint32_t>(layerEnd), k, v, &params, stream));
+    }
+    void attentionDecode(int layerBegin, int layerEnd, const float* q, float* out, int numHeads, int pending, const er_step_params& params,
+                         void* stream = nullptr) {
+        check(er_kv_attention_decode(handle_, static_cast<uint32_t>(layerBegin), static_cast<uint32_t>(layerEnd), q, out,
+                                     static_cast<uint32_t>(numHeads), static_cast<uint32_t>(pending), &params, stream));
+    }
+    void advance(int layerBegin, int layerEnd, int count = 1, void* stream = nullptr) {
+        check(er_kv_advance(handle_, static_cast<uint32_t>(layerBegin), static_cast<uint32_t>(layerEnd), static_cast<uint32_t>(count), stream));
+    }
+    // Prefill: rows [start, start + count) of one (layer, sequence) from device float [count][numKVHeads][headDim], then
+    // causal attention of a chunk of query rows (prefill dispatch, LlamaLanguageModel.swift:2286, 2940-2957).
+    void writeRows(int layer, uint32_t seq, int start, int count, const float* k, const float* v, const er_step_params& params,
+                   void* stream = nullptr) {
+        check(er_kv_write_rows(handle_, static_cast<uint32_t>(layer), seq, static_cast<uint32_t>(start), static_cast<uint32_t>(count), k, v,
+                               &params, stream));
+    }
+    void attentionPrefill(int layer, uint32_t seq, const float* q, float* out, int numHeads, int seqLen, int qOffset,
+                          const er_step_params& params, void* stream = nullptr) {
+        check(er_kv_attention_prefill(handle_, static_cast<uint32_t>(layer), seq, q, out, static_cast<uint32_t>(numHeads),
+                                      static_cast<uint32_t>(seqLen), static_cast<uint32_t>(qOffset), &params, stream));
+    }
+    int64_t totalWritten(int layer, uint32_t seq = 0) const { return er_kv_total_written(handle_, static_cast<uint32_t>(layer), seq); }
+    er_kv_config config() const {
+        er_kv_config c{};
+        check(er_kv_get_config(handle_, &c));
+        return c;
+    }
+    std::vector<int32_t> blockTable(uint32_t seq) const {
+        std::vector<int32_t> pages(static_cast<size_t>(maxSeqLen) / 16 + 1);
+        uint32_t n = 0;
+        check(er_kv_get_block_table(handle_, seq, pages.data(), static_cast<uint32_t>(pages.size()), &n));
+        pages.resize(n);
+        return pages;
+    }
+    // The stored 34-byte q8_0 blocks (KVCache.swift:175-184, 1007-1038), rows in logical order.
+    std::pair<std::vector<uint8_t>, std::vector<uint8_t>> retrieveQ8_0Rows(int layer, uint32_t seq = 0) const {
+        const size_t cap = static_cast<size_t>(maxSeqLen) * numKVHeads * (headDim / 32) * 34;
+        std::vector<uint8_t> k(cap), v(cap);
+        uint32_t tokens = 0;
+        check(er_kv_retrieve_q8_0_rows(handle_, static_cast<uint32_t>(layer), seq, k.data(), v.data(), cap, &tokens));
+        k.resize(static_cast<size_t>(tokens) * numKVHeads * (headDim / 32) * 34);
+        v.resize(k.size());
+        return {std::move(k), std::move(v)};
+    }
+    // Device status word of this cache's kernels: throws ER_ERR_DEVICE_TIMEOUT / ER_ERR_OUT_OF_PAGES when one was left.
+    void checkDeviceStatus() const { check(er_kv_device_status(handle_)); }
+    void clearDeviceStatus() { check(er_kv_clear_device_status(handle_)); }
+    // kv heads split over GPUs: decode launches write this cache's heads into rows of headsTotal heads (own buffer + peers').
+    void setOutputSharding(int headsTotal, int headOffset, const std::vector<float*>& peerOutputs = {}) {
+        check(er_kv_set_output_sharding(handle_, static_cast<uint32_t>(headsTotal), static_cast<uint32_t>(headOffset),
+                                        peerOutputs.empty() ? nullptr : peerOutputs.data(), static_cast<uint32_t>(peerOutputs.size())));
+    }
+    // Pages as bytes (prefix reuse): size of a page over all layers; pack pages into / write pages from a device or host buffer.
+    size_t pageBytes() const {
+        const int64_t n = er_kv_page_bytes(handle_);
+        if (n < 0) throw KVCacheError(static_cast<int32_t>(n));
+        return static_cast<size_t>(n);
+    }
+    void exportPages(const std::vector<int32_t>& pages, void* buffer, size_t bufferBytes, void* stream = nullptr) const {
+        check(er_kv_export_pages(handle_, pages.data(), static_cast<uint32_t>(pages.size()), buffer, bufferBytes, stream));
+    }
+    void importPages(const std::vector<int32_t>& pages, const void* buffer, size_t bufferBytes, void* stream = nullptr) {
+        check(er_kv_import_pages(handle_, pages.data(), static_cast<uint32_t>(pages.size()), buffer, bufferBytes, stream));
+    }
+    int setTrace(uint64_t* deviceBuffer, uint32_t capacityCtas) { return check(er_kv_set_trace(handle_, deviceBuffer, capacityCtas)); }
+
 private:
     er_kv* handle_ = nullptr;
     Options options_;
 };
+
+// A device buffer other processes of the node can map (CUDA IPC) -- the peers' output buffers of a kv-head-sharded step.
+class PeerBuffer {
+public:
+    explicit PeerBuffer(size_t bytes) : owner_(true) { check(er_peer_buffer_create(bytes, &ptr_, handle_)); }
+    explicit PeerBuffer(const uint8_t* handle64) : owner_(false) { check(er_peer_buffer_open(handle64, &ptr_)); }
+    ~PeerBuffer() { if (ptr_) { if (owner_) er_peer_buffer_destroy(ptr_); else er_peer_buffer_close(ptr_); } }
+    PeerBuffer(const PeerBuffer&) = delete;
+    PeerBuffer& operator=(const PeerBuffer&) = delete;
+    float* data() const { return static_cast<float*>(ptr_); }
+    const uint8_t* handle() const { return handle_; }   // 64 bytes, meaningful on the creating side
+
+private:
+    void* ptr_ = nullptr;
+    uint8_t handle_[64] = {};
+    bool owner_;
+};
+// After an NCCL all-gather of [world][pairs][localHeads][128]: rows of world * localHeads heads.
+inline void relayoutHeadShards(const float* gathered, float* full, int world, int pairs, int localHeads, void* stream = nullptr) {
+    check(er_relayout_head_shards(gathered, full, static_cast<uint32_t>(world), static_cast<uint32_t>(pairs), static_cast<uint32_t>(localHeads), stream));
+}
 
 class RoPEKernel {
 public:
@@ -238,6 +345,13 @@ public:
                        static_cast<uint32_t>(startPos), theta, scalingFactor, partialRotaryFactor};
         check(er_rope_neox_f32(inputBuffer, outputBuffer, &p, stream));
     }
+    // rope_neox_f32_to_f16 (Shaders/RoPE.metal:498-531): the K row of a step, rotated and rounded to fp16
+    void encodeNeoXToF16(void* stream, const float* inputBuffer, uint16_t* outputBuffer, int seqLen, int numHeads, int headDim,
+                         int startPos = 0, float theta = 10000.f, float scalingFactor = 1.f, float partialRotaryFactor = 1.f) const {
+        ERRoPEParams p{static_cast<uint32_t>(seqLen), static_cast<uint32_t>(numHeads), static_cast<uint32_t>(headDim),
+                       static_cast<uint32_t>(startPos), theta, scalingFactor, partialRotaryFactor};
+        check(er_rope_neox_f32_to_f16(inputBuffer, outputBuffer, &p, stream));
+    }
 };
 
 class GQAKernel {
@@ -248,6 +362,28 @@ public:
     // qOffset:) on fp16 K/V (pipelineF16KV), GQAKernel.swift:113-172
     void encode(void* stream, const float* qBuffer, const uint16_t* kBuffer, const uint16_t* vBuffer, float* outputBuffer,
                 int seqLen, int headDim, int numHeads, int numKVHeads, bool causal, int kvSeqLen = 0, int qOffset = 0) const {
+        const ERGQAParams p = params(seqLen, headDim, numHeads, numKVHeads, causal, kvSeqLen, qOffset);
+        check(er_gqa_attention_f16kv(qBuffer, kBuffer, vBuffer, outputBuffer, &p, stream));
+    }
+    // The fp32 pipelines of the same holder (gqa_attention_f32 / _masked_wide, Shaders/GQA.metal:18-276): K / V float,
+    // additiveMaskBuffer [seqLen][kvSeqLen] float or null (GQAKernel.swift:122).
+    void encodeF32(void* stream, const float* qBuffer, const float* kBuffer, const float* vBuffer, float* outputBuffer,
+                   int seqLen, int headDim, int numHeads, int numKVHeads, bool causal, int kvSeqLen = 0, int qOffset = 0,
+                   const float* additiveMaskBuffer = nullptr) const {
+        const ERGQAParams p = params(seqLen, headDim, numHeads, numKVHeads, causal, kvSeqLen, qOffset);
+        check(er_gqa_attention_f32(qBuffer, kBuffer, vBuffer, outputBuffer, additiveMaskBuffer, &p, stream));
+    }
+    // fp16 K/V with the split-K workspace built into the library (no device allocation by the call); no reference counterpart.
+    void encodeStaticWorkspace(void* stream, const float* qBuffer, const uint16_t* kBuffer, const uint16_t* vBuffer, float* outputBuffer,
+                               int seqLen, int headDim, int numHeads, int numKVHeads, bool causal, int kvSeqLen = 0, int qOffset = 0) const {
+        const ERGQAParams p = params(seqLen, headDim, numHeads, numKVHeads, causal, kvSeqLen, qOffset);
+        check(er_gqa_attention_f16kv_static(qBuffer, kBuffer, vBuffer, outputBuffer, &p, stream));
+    }
+    static void checkStaticWorkspaceStatus() { check(er_gqa_attention_f16kv_static_status()); }
+    static void checkWorkspaceStatus() { check(er_workspace_status()); }
+
+private:
+    static ERGQAParams params(int seqLen, int headDim, int numHeads, int numKVHeads, bool causal, int kvSeqLen, int qOffset) {
         ERGQAParams p{};
         p.seqLen = static_cast<uint32_t>(seqLen);
         p.headDim = static_cast<uint32_t>(headDim);
@@ -259,7 +395,7 @@ public:
         p.kvBlockSize = p.qBlockSize = blockSize;
         p.kvSeqLen = static_cast<uint32_t>(kvSeqLen);
         p.qOffset = static_cast<uint32_t>(qOffset);
-        check(er_gqa_attention_f16kv(qBuffer, kBuffer, vBuffer, outputBuffer, &p, stream));
+        return p;
     }
 };
 
@@ -290,6 +426,22 @@ public:
         check(er_turboquant_quantize_rows(source, static_cast<uint32_t>(rowCount), static_cast<uint32_t>(sourceRowStride),
                                           static_cast<uint32_t>(destinationRowBase), static_cast<uint32_t>(bits), codes,
                                           residualSigns, outlierMask, metadata, stream));
+    }
+    // The same dispatch for presets with high-precision channels and a QJL residual (balanced: 3 / 5 bits, aggressive: 2 / 3,
+    // 32 channels): preferQuantizationBenefitSelection chooses the values' selection rule (TurboQuant.swift:1185-1238).
+    void encodeQuantizeRowsOutliers(void* stream, const float* source, int rowCount, int sourceRowStride, int destinationRowBase,
+                                    int regularBits, int highPrecisionBits, int highPrecisionCount, bool preferQuantizationBenefitSelection,
+                                    uint32_t* codes, uint32_t* residualSigns, uint32_t* outlierMask, float* metadata) const {
+        check(er_turboquant_quantize_rows_outliers(source, static_cast<uint32_t>(rowCount), static_cast<uint32_t>(sourceRowStride),
+                                                   static_cast<uint32_t>(destinationRowBase), static_cast<uint32_t>(regularBits),
+                                                   static_cast<uint32_t>(highPrecisionBits), static_cast<uint32_t>(highPrecisionCount),
+                                                   preferQuantizationBenefitSelection ? 1u : 0u, codes, residualSigns, outlierMask, metadata, stream));
+    }
+    // quantize_q8_0_rows (Shaders/Dequant_Q8_0.metal:19-49): 4 blocks of 34 bytes per 128-float row
+    void encodeQuantizeQ8Rows(void* stream, const float* source, int rowCount, int sourceRowStride, int destinationRowBase,
+                              uint8_t* destinationBlocks) const {
+        check(er_quantize_q8_0_rows(source, static_cast<uint32_t>(rowCount), static_cast<uint32_t>(sourceRowStride),
+                                    static_cast<uint32_t>(destinationRowBase), destinationBlocks, stream));
     }
 };
 

@@ -82,9 +82,11 @@ enum {
     ER_ERR_DEVICE_TIMEOUT = -12 /* a bounded device-side wait gave up; see er_kv_device_status */
 };
 
-/* KVCache.Precision raw values (KVCache.swift:39-49). float8 / balanced / aggressive are accepted by er_kv_create only
- * to report ER_ERR_UNSUPPORTED_STORAGE (the balanced / aggressive row encoder exists as an operator:
- * er_turboquant_quantize_rows_outliers). */
+/* KVCache.Precision raw values (KVCache.swift:39-49). float8 is accepted by er_kv_create only to report
+ * ER_ERR_UNSUPPORTED_STORAGE.  BALANCED (3-bit codes, the 32 best channels 5-bit) and AGGRESSIVE (2-bit, 32 channels 3-bit)
+ * keep every row as codes + outlier mask + QJL residual signs + (rowNorm, residualNorm); key_type / value_type then hold the
+ * keys' / values' channel-selection rule (ER_TQ_SELECT_*), and key_residual_scale / value_residual_scale the weights of the
+ * residual term in attention (TurboQuantV2Contract.keyResidualScale / valueResidualScale: 0 in the reference's contract). */
 enum {
     ER_KV_FLOAT32 = 0,
     ER_KV_FLOAT16 = 1,
@@ -97,6 +99,9 @@ enum {
 
 /* TurboQuantFixedType (TurboQuant.swift:172-190): the value is the bit width of the preset. */
 enum { ER_TQ_TURBO2 = 2, ER_TQ_TURBO3 = 3, ER_TQ_TURBO4 = 4 };
+/* TurboQuantOutlierSelection (TurboQuant.swift:1185-1238) for BALANCED / AGGRESSIVE caches.  DEFAULT is the reference's
+ * contract: keys by magnitude, values by quantisation benefit (TurboQuantV2Contract.keyOutlierSelection / valueOutlierSelection). */
+enum { ER_TQ_SELECT_DEFAULT = 0, ER_TQ_SELECT_MAGNITUDE = 1, ER_TQ_SELECT_QUANTIZATION_BENEFIT = 2 };
 
 /* Storage layouts.  The reference has exactly one: a token-major ring per layer
  * ([slot][kvHead][dim], KVCache.swift:357-370).  HEAD_MAJOR keeps each kv head's tokens contiguous
@@ -126,7 +131,7 @@ typedef struct {
     uint32_t num_kv_heads;  /* heads held by THIS cache (a kv-head shard holds its slice only) */
     uint32_t head_dim;
     uint32_t precision;     /* ER_KV_* */
-    uint32_t key_type;      /* ER_TQ_* when precision == ER_KV_TURBOQUANT_V2 */
+    uint32_t key_type;      /* ER_TQ_TURBO* when precision == ER_KV_TURBOQUANT_V2; ER_TQ_SELECT_* for BALANCED / AGGRESSIVE */
     uint32_t value_type;
     uint32_t norm_format;   /* ER_TQ_NORM_* */
     uint32_t max_batch;     /* sequences held (the reference's cache is the max_batch == 1 case) */
@@ -135,7 +140,8 @@ typedef struct {
     uint32_t num_pages;     /* pages in the shared pool (PAGED only) */
     uint32_t prefill_kernel; /* ER_PREFILL_KERNEL_*: which chunked-prefill kernel er_kv_attention_prefill may use */
     uint32_t decode_kernel;  /* ER_DECODE_KERNEL_*: float16 caches */
-    uint32_t reserved[2];
+    float key_residual_scale;   /* BALANCED / AGGRESSIVE: weight of the QJL residual term of the scores (0 = off, the contract) */
+    float value_residual_scale; /* ... and of the outputs; also the residualWeight of decoded value rows */
 } er_kv_config;
 
 typedef struct er_kv er_kv;
@@ -368,6 +374,19 @@ int32_t er_kv_advance(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, uint3
  * Sets totalWritten of (layer, seq) to max(totalWritten, start + count). */
 int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start, uint32_t count, const float* k,
                          const float* v, const er_step_params* params, void* stream);
+
+/* ---- pages as bytes (no counterpart in the reference, whose prefix reuse is setPosition on one ring) ----
+ * A page of the paged layout (of the head-major layout: one sequence's whole ring, page id = sequence index) holds
+ * page_size tokens of every kv head; er_kv_page_bytes is its size over ALL layers, side arrays (TurboQuant norms, q8_0
+ * scales) included.  er_kv_export_pages packs pages page_ids[0..count) into `buffer` (device, or host memory -- pinned for
+ * an asynchronous copy), er_kv_import_pages writes such bytes into pages of a cache of the same shape and format (this one or
+ * another): a prompt prefix computed once can be parked on the host, handed to another cache, or attached to several
+ * sequences (import into fresh pages, er_kv_set_block_table, er_kv_set_position).  Positions are not part of a page: RoPE'd
+ * keys carry their absolute position, so a prefix keeps its meaning only at the same token offsets.  Copies are enqueued
+ * on `stream` and ordered with the cache's kernels there. */
+int64_t er_kv_page_bytes(er_kv* kv);
+int32_t er_kv_export_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, void* buffer, size_t buffer_bytes, void* stream);
+int32_t er_kv_import_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, const void* buffer, size_t buffer_bytes, void* stream);
 
 /* ---- kv-head sharding across the GPUs of one node (no counterpart in the reference, which is single-device) ----
  * Rank r of G holds kv heads [r * Hkv / G, (r + 1) * Hkv / G) in its own er_kv cache and the query heads that attend to

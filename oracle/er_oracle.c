@@ -703,6 +703,69 @@ ERO_API void ero_tq_attention_decode(const float *q, const uint32_t *k_codes, co
     }
 }
 
+/* The same attention over rows of a preset with high-precision channels and a QJL residual (balanced, aggressive), restating
+ *   cpuTurboQuantAttention          TurboQuantAttentionTests.swift:1207-1260 (score = rowNorm * (mseDot + qjlScale * residualNorm *
+ *                                   keyResidualScale * residualDot) * scale, two-pass softmax)
+ *   decodeTurboValueOutput          :1394-1440 (rotated MSE part + rotated residual part, one inverse transform each, output =
+ *                                   mse + residual * qjlScale * valueResidualScale)
+ * and gqa_attention_turboquant_decode (Shaders/TurboQuant.metal:1794-2001), whose residual path is off when keyResidualScale == 0
+ * (:1818).  The transforms ignore their seeds (TurboQuant.swift:891-921), so qResidual == qRot.  Rows as the encoder writes them:
+ * codes [rows][words] split-plane, signs / mask [rows][4], meta [rows][2] = (rowNorm, residualNorm); row = token*numKVHeads + kvHead. */
+ERO_API void ero_tq_attention_decode_preset(const float *q, const uint32_t *k_codes, const uint32_t *k_signs, const uint32_t *k_mask,
+                                            const float *k_meta, const uint32_t *v_codes, const uint32_t *v_signs,
+                                            const uint32_t *v_mask, const float *v_meta, int regular_bits, int high_bits,
+                                            int high_count, float key_residual_scale, float value_residual_scale, float *out,
+                                            int num_heads, int num_kv_heads, int kv_len, float scale, int threads) {
+    int group = num_heads / num_kv_heads;
+    int words = ero_tq_preset_code_words(regular_bits, high_bits, high_count);
+    const float qjl = sqrtf(3.14159265358979323846f / 2.0f);
+    (void)threads;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads > 0 ? threads : 1)
+    for (int head = 0; head < num_heads; ++head) {
+        int kv_head = head / group;
+        float q_rot[ERO_DIM];
+        ero_tq_forward(q + (size_t)head * ERO_DIM, ERO_DIM, q_rot);
+        float *scores = (float *)malloc(sizeof(float) * (size_t)(kv_len > 0 ? kv_len : 1));
+        uint8_t codes[ERO_DIM], mask[ERO_DIM];
+        for (int t = 0; t < kv_len; ++t) {
+            size_t row = (size_t)t * num_kv_heads + kv_head;
+            for (int d = 0; d < ERO_DIM; ++d) mask[d] = (k_mask[row * 4 + (d >> 5)] >> (d & 31)) & 1u;
+            ero_tq_unpack_codes_split(k_codes + row * words, words, mask, ERO_DIM, regular_bits, high_bits, codes);
+            float mse = 0.0f, res = 0.0f;
+            for (int d = 0; d < ERO_DIM; ++d) {
+                mse += q_rot[d] * centroids_for(mask[d] ? high_bits : regular_bits)[codes[d]];
+                res += q_rot[d] * (((k_signs[row * 4 + (d >> 5)] >> (d & 31)) & 1u) ? 1.0f : -1.0f);
+            }
+            scores[t] = k_meta[row * 2] * (mse + (qjl * k_meta[row * 2 + 1] * key_residual_scale * res)) * scale;
+        }
+        float acc[ERO_DIM], acc_res[ERO_DIM], o_mse[ERO_DIM], o_res[ERO_DIM];
+        for (int d = 0; d < ERO_DIM; ++d) { acc[d] = 0.0f; acc_res[d] = 0.0f; }
+        if (kv_len > 0) {
+            float max_score = scores[0];
+            for (int t = 1; t < kv_len; ++t) if (scores[t] > max_score) max_score = scores[t];
+            float sum = 0.0f;
+            for (int t = 0; t < kv_len; ++t) { scores[t] = expf(scores[t] - max_score); sum += scores[t]; }
+            for (int t = 0; t < kv_len; ++t) {
+                size_t row = (size_t)t * num_kv_heads + kv_head;
+                float weight = scores[t] / sum;
+                for (int d = 0; d < ERO_DIM; ++d) mask[d] = (v_mask[row * 4 + (d >> 5)] >> (d & 31)) & 1u;
+                ero_tq_unpack_codes_split(v_codes + row * words, words, mask, ERO_DIM, regular_bits, high_bits, codes);
+                for (int d = 0; d < ERO_DIM; ++d)
+                    acc[d] += weight * v_meta[row * 2] * centroids_for(mask[d] ? high_bits : regular_bits)[codes[d]];
+                if (value_residual_scale != 0.0f && v_meta[row * 2 + 1] != 0.0f) {
+                    float mag = weight * v_meta[row * 2] * v_meta[row * 2 + 1];
+                    for (int d = 0; d < ERO_DIM; ++d)
+                        acc_res[d] += mag * (((v_signs[row * 4 + (d >> 5)] >> (d & 31)) & 1u) ? 1.0f : -1.0f);
+                }
+            }
+        }
+        ero_tq_inverse(acc, o_mse);
+        ero_tq_inverse(acc_res, o_res);
+        for (int d = 0; d < ERO_DIM; ++d) out[(size_t)head * ERO_DIM + d] = o_mse[d] + (o_res[d] * qjl * value_residual_scale);
+        free(scores);
+    }
+}
+
 /* ------------------------------------------------------------------ KV ring cache (host logic) */
 
 /* KVCache, KVCache.swift:12-1138, reduced to what the hot path uses: float32 / float16

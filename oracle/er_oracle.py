@@ -93,6 +93,8 @@ def lib():
     L.ero_tq_score.argtypes = [f32p, C.c_int, u32p, C.c_int, C.c_float, C.c_float, f32p]
     L.ero_tq_attention_decode.argtypes = [f32p, u32p, f32p, C.c_int, u32p, f32p, C.c_int, f32p,
                                           C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+    L.ero_tq_attention_decode_preset.argtypes = [f32p, u32p, u32p, u32p, f32p, u32p, u32p, u32p, f32p, C.c_int, C.c_int, C.c_int,
+                                                 C.c_float, C.c_float, f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
     L.ero_kv_create.restype = C.c_void_p
     L.ero_kv_create.argtypes = [C.c_int] * 7
     L.ero_kv_destroy.argtypes = [C.c_void_p]
@@ -355,6 +357,26 @@ def tq_attention_decode(q, k_codes, k_norm, k_bits, v_codes, v_norm, v_bits, num
     lib().ero_tq_attention_decode(_p(q, F32), _p(k_codes, U32), _p(k_norm, F32), k_bits, _p(v_codes, U32),
                                   _p(v_norm, F32), v_bits, _p(out, F32), h, num_kv_heads, kv_len, float(scale),
                                   threads)
+    return out
+
+
+def tq_attention_decode_preset(q, k_rows, v_rows, preset, num_kv_heads, kv_len, key_residual_scale=0.0,
+                               value_residual_scale=0.0, scale=None, threads=1):
+    """q: [H,128]; k_rows / v_rows: (codes [T*Hkv, w], signs [T*Hkv, 4], mask [T*Hkv, 4], meta [T*Hkv, 2]) as
+    tq_encode_rows_preset returns them (row = token*Hkv + kvHead)."""
+    q = _f32(q)
+    rb, hb, hc = PRESETS[preset]
+    kc, ks, km, kmeta = (np.ascontiguousarray(a) for a in k_rows)
+    vc, vs, vm, vmeta = (np.ascontiguousarray(a) for a in v_rows)
+    out = np.empty_like(q)
+    if scale is None:
+        scale = 1.0 / np.sqrt(np.float32(DIM))
+    lib().ero_tq_attention_decode_preset(_p(q, F32), _p(kc.astype(np.uint32, copy=False), U32), _p(ks.astype(np.uint32, copy=False), U32),
+                                         _p(km.astype(np.uint32, copy=False), U32), _p(_f32(kmeta), F32),
+                                         _p(vc.astype(np.uint32, copy=False), U32), _p(vs.astype(np.uint32, copy=False), U32),
+                                         _p(vm.astype(np.uint32, copy=False), U32), _p(_f32(vmeta), F32), rb, hb, hc,
+                                         C.c_float(key_residual_scale), C.c_float(value_residual_scale), _p(out, F32),
+                                         q.shape[0], num_kv_heads, kv_len, C.c_float(scale), threads)
     return out
 
 

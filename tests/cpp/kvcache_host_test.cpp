@@ -1,6 +1,7 @@
 // C++ counterpart of the reference's KVCacheTests (Tests/EdgeRunnerMetalTests/KVCacheTests.swift) run against the
 // C++ host mirror (include/EdgeRunnerCUDA.hpp) over the C ABI.  `--no-device` only checks the error path a machine
 // without a GPU must take; without arguments every case runs on the current device.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -99,6 +100,71 @@ int main(int argc, char** argv) {
         EXPECT(c.turboQuantMetalBuffers(0).key_bytes > 0);
         EXPECT(throws(KVCacheError::compressedBufferAccessRequiresTurboQuantAPI, [&] { c.metalBuffers(0); }));
         EXPECT(throws(KVCacheError::compressedRetrieveRequiresDecodedAPI, [&] { c.retrieve<float>(0); }));
+    }
+    {   // a decode step with host buffers on a paged fp16 cache (both fp16 decode kernels), checked against a direct evaluation
+        for (uint32_t kernel : {uint32_t(ER_DECODE_KERNEL_PERSISTENT), uint32_t(ER_DECODE_KERNEL_SLIM)}) {
+            KVCache::Options opt;
+            opt.layout = KVCache::Layout::paged;
+            opt.pageSize = 16;
+            opt.numPages = 4;
+            opt.decodeKernel = kernel;
+            KVCache c(64, 1, 1, 128, KVCache::Precision::float16, opt);
+            EXPECT(throws(KVCacheError::outOfPages, [&] { c.appendF16(0, std::vector<uint16_t>(128, 0x3C00), std::vector<uint16_t>(128, 0x3C00)); }));
+            c.setBlockTable(0, {2, 0, 3, 1});
+            EXPECT((c.blockTable(0) == std::vector<int32_t>{2, 0, 3, 1}));
+            EXPECT(c.config().page_size == 16 && c.config().decode_kernel == kernel);
+            // rows whose values are exact in fp16: (i % 7 - 3) / 8
+            auto row = [](int t, int shift) { std::vector<float> r(128); for (int i = 0; i < 128; ++i) r[i] = float((i * (t + 2) + shift) % 7 - 3) / 8.f; return r; };
+            auto bits = [](const std::vector<float>& r) {   // those values as fp16 bit patterns
+                std::vector<uint16_t> b(r.size());
+                for (size_t i = 0; i < r.size(); ++i) {
+                    const float a = std::fabs(r[i]);
+                    uint16_t h = 0;
+                    if (a == 0.125f) h = 0x3000; else if (a == 0.25f) h = 0x3400; else if (a == 0.375f) h = 0x3600;
+                    b[i] = r[i] < 0 ? uint16_t(h | 0x8000) : h;
+                }
+                return b;
+            };
+            std::vector<std::vector<float>> K, V;
+            for (int t = 0; t < 20; ++t) {   // 20 rows: two pages
+                K.push_back(row(t, 1)); V.push_back(row(t, 4));
+                c.appendF16(0, bits(K.back()), bits(V.back()));
+            }
+            K.push_back(row(20, 1)); V.push_back(row(20, 4));
+            std::vector<float> q = signal(0.4f), out(128, NAN);
+            er_step_params sp{};
+            sp.rope_theta = 10000.f;
+            sp.apply_rope = 0;
+            c.decodeStepHost(0, 1, q.data(), K.back().data(), V.back().data(), out.data(), 1, sp);
+            EXPECT(c.totalWritten(0) == 21 && c.currentLength() == 21);
+            c.checkDeviceStatus();
+            std::vector<double> s(21), want(128, 0.0);
+            double m = -1e30, l = 0;
+            for (int t = 0; t < 21; ++t) {
+                double d = 0;
+                for (int i = 0; i < 128; ++i) d += double(q[i]) * K[t][i];
+                s[t] = d / std::sqrt(128.0);
+                m = std::max(m, s[t]);
+            }
+            for (int t = 0; t < 21; ++t) { s[t] = std::exp(s[t] - m); l += s[t]; }
+            for (int t = 0; t < 21; ++t) for (int i = 0; i < 128; ++i) want[i] += s[t] / l * V[t][i];
+            double worst = 0;
+            for (int i = 0; i < 128; ++i) worst = std::max(worst, std::fabs(out[i] - want[i]));
+            EXPECT(worst < 2e-6);
+            auto kv = c.retrieve<uint16_t>(0);
+            EXPECT(kv.first.size() == 21 * 128 && std::vector<uint16_t>(kv.first.end() - 128, kv.first.end()) == bits(K.back()));
+        }
+    }
+    {   // q8_0 rows: the stored 34-byte blocks (KVCache.swift:977-1039)
+        KVCache c(8, 1, 1, 128, KVCache::Precision::q8_0);
+        std::vector<float> k(128), v(128);
+        for (int i = 0; i < 128; ++i) { k[i] = float(i % 32) - 16.f; v[i] = 0.5f * float(i % 5); }
+        c.append(0, k, v);
+        auto rows = c.retrieveQ8_0Rows(0);
+        EXPECT(rows.first.size() == 4 * 34 && rows.second.size() == 4 * 34);
+        EXPECT(int8_t(rows.first[2]) == -127 && int8_t(rows.first[2 + 31]) == 119);   // scale 16/127: -16 -> -127, 15 -> 119.06
+        auto dec = c.retrieveDecodedQ8_0(0);
+        EXPECT(dec.first.size() == 128 && std::fabs(dec.first[0] + 16.f) < 0.01f);
     }
     {   // block-table allocator
         edgerunner::BlockTableAllocator a(6, 16, {3, 1, 4, 0, 5, 2});

@@ -229,3 +229,87 @@ def test_bounded_wait_runs_out_and_reports(er, torch, oracle, precision):
     torch.cuda.synchronize()
     assert c.device_status() == 0
     assert np.array_equal(out.cpu().numpy(), good)
+
+
+@pytest.mark.parametrize("precision", ["float16", "q8_0", "turboquant"])
+def test_pages_exported_and_imported_for_prefix_reuse(er, torch, precision):
+    """er_kv_export_pages / er_kv_import_pages: a prompt prefix written once into sequence 0 of cache A is parked in host
+    memory, then attached (other page ids, another sequence) to cache B of the same shape and, through a device buffer, to a
+    second sequence of cache A.  Rows read back from the copies must equal the original bit for bit, decode steps on them up to the summation order."""
+    rng = np.random.Generator(np.random.PCG64(404))
+    L, Hq, Hkv, D, ps, T, B = 3, 16, 8, 128, 16, 160, 3
+    pages = (T // ps) * B
+    prec = {"float16": er.Precision.float16, "q8_0": er.Precision.q8_0, "turboquant": er.Precision.turboquantV2}[precision]
+    kw = dict(key_type=4, value_type=3, norm_format=er.NormFormat.float16) if precision == "turboquant" else {}
+    sp = er.step_params(rope_theta=1e6)
+
+    def make(order_seed):
+        c = er.KVCache(T, L, Hkv, D, prec, max_batch=B, layout=er.Layout.paged, page_size=ps, num_pages=pages, **kw)
+        return c, er.BlockTableAllocator(pages, ps, free_order=np.random.Generator(np.random.PCG64(order_seed)).permutation(pages))
+
+    a, alloc_a = make(1)
+    b, alloc_b = make(2)
+    n = 70                                                     # 4 full pages + 6 rows of a fifth
+    src_pages = alloc_a.ensure(0, n)
+    a.set_block_table(0, src_pages)
+    for l in range(L):
+        k = torch.as_tensor(rng.standard_normal((n, Hkv, D), dtype=np.float32)).cuda()
+        v = torch.as_tensor(rng.standard_normal((n, Hkv, D), dtype=np.float32)).cuda()
+        a.write_rows(l, 0, 0, n, k, v, sp)
+    per_page = a.page_bytes()
+    assert per_page == b.page_bytes() and per_page > 0
+    parked = a.export_pages(src_pages)                         # numpy bytes on the host
+    assert parked.nbytes == per_page * len(src_pages)
+    dst_pages = alloc_b.ensure(2, n)
+    b.set_block_table(2, dst_pages)
+    b.import_pages(dst_pages, parked)
+    b.set_position(n, seq=2)
+    # second copy inside cache A through a device buffer, on a stream
+    stream = torch.cuda.Stream()
+    dev_buf = torch.empty(parked.nbytes, dtype=torch.uint8, device="cuda")
+    twin_pages = alloc_a.ensure(1, n)
+    a.set_block_table(1, twin_pages)
+    a.export_pages(src_pages, dev_buf, stream=stream)
+    a.import_pages(twin_pages, dev_buf, stream=stream)
+    stream.synchronize()
+    a.set_position(n, seq=1)
+    a.set_position(n, seq=0)
+
+    def rows(c, l, seq):
+        if precision == "float16":
+            k, v = c.retrieve(l, np.float16, seq=seq)
+            return [k.view(np.uint16), v.view(np.uint16)]
+        if precision == "q8_0":
+            return list(c.retrieve_q8_0_rows(l, seq=seq))
+        (kc, _, _, km), (vc, _, _, vm) = c.retrieve_turboquant_runtime_rows(l, seq=seq)
+        return [kc, km.view(np.uint32), vc, vm.view(np.uint32)]
+
+    for l in range(L):
+        want = rows(a, l, 0)
+        for c, seq in ((b, 2), (a, 1)):
+            got = rows(c, l, seq)
+            assert all(np.array_equal(x, y) for x, y in zip(want, got)), (l, seq)
+    # one decode step with the same q / k / v on all three sequences: identical outputs
+    q1 = rng.standard_normal((L, 1, Hq, D), dtype=np.float32)
+    k1 = rng.standard_normal((L, 1, Hkv, D), dtype=np.float32)
+    v1 = rng.standard_normal((L, 1, Hkv, D), dtype=np.float32)
+    q, k, v = (torch.as_tensor(np.repeat(x, B, axis=1)).cuda() for x in (q1, k1, v1))
+    for c, al, seqs in ((a, alloc_a, (2,)), (b, alloc_b, (0, 1))):   # the idle sequences get a page for their one new row
+        for s_ in seqs:
+            c.set_block_table(s_, al.ensure(s_, 1))
+    out_a = torch.empty((L, B, Hq, D), device="cuda")
+    out_b = torch.empty((L, B, Hq, D), device="cuda")
+    a.decode_step(q, k, v, out_a, Hq, sp)
+    b.decode_step(q, k, v, out_b, Hq, sp)
+    torch.cuda.synchronize()
+    assert a.device_status() == 0 and b.device_status() == 0
+    # same rows, same query: equal up to the summation order (the sequences fall on different CTA boundaries)
+    assert torch.isfinite(out_a).all()
+    tol = 2e-5 * float(out_a[:, 0].abs().max())
+    assert float((out_a[:, 0] - out_a[:, 1]).abs().max()) < tol and float((out_a[:, 0] - out_b[:, 2]).abs().max()) < tol
+    with pytest.raises(er.EdgeRunnerCUDAError):
+        a.export_pages([pages])                                # beyond the pool
+    tm = er.KVCache(32, 1, Hkv, D, er.Precision.float16, layout=er.Layout.token_major)
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        tm.page_bytes()
+    assert e.value.name == "unsupported"

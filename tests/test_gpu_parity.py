@@ -102,10 +102,16 @@ def test_kvcache_error_cases(er):
         t.retrieve(0, np.float32)
     assert e.value.name == "compressedRetrieveRequiresDecodedAPI"
     assert t.turboquant_buffers(0).key_row_bytes == 48
-    for prec in (er.Precision.float8, er.Precision.turboQuantBalanced, er.Precision.turboQuantAggressive):
-        with pytest.raises(er.EdgeRunnerCUDAError) as e:
-            er.KVCache(8, 1, 1, 128, prec)
-        assert e.value.name == "unsupportedStorage"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        er.KVCache(8, 1, 1, 128, er.Precision.float8)
+    assert e.value.name == "unsupportedStorage"
+    b = er.KVCache(8, 1, 1, 128, er.Precision.turboQuantBalanced)      # presets with high-precision channels: TurboQuant accessors too
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        b.metal_buffers(0)
+    assert e.value.name == "compressedBufferAccessRequiresTurboQuantAPI"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        b.retrieve(0, np.float32)
+    assert e.value.name == "compressedRetrieveRequiresDecodedAPI"
 
 
 def test_set_position_and_advance(er):
@@ -585,6 +591,105 @@ def _run_turbo_config(er, oracle, torch, L, B, Hq, Hkv, ctx, steps, seed, kbits,
             assert np.array_equal(gkmeta[:, 0], kn[:n]) and np.array_equal(gvmeta[:, 0], vn[:n])
             assert not gkmeta[:, 1].any() and not gks.any() and not gkm.any() and not gvs.any() and not gvm.any()
     return worst
+
+
+@pytest.mark.parametrize("preset", ["balanced", "aggressive"])
+@pytest.mark.parametrize("Hq,Hkv,layout,scales", [(16, 8, "head_major", (0.0, 0.0)), (8, 2, "paged", (1.0 / 128, 1.0 / 128)),
+                                                   (4, 4, "head_major", (0.0, 1.0 / 64)), (16, 2, "paged", (0.0, 0.0))])
+def test_outlier_preset_caches(er, oracle, torch, preset, Hq, Hkv, layout, scales):
+    """Caches of balanced / aggressive rows (32 high-precision channels, QJL residual signs, two norms per row): rows written
+    by prefill fill, by the host append and by decode steps are bit-identical to the CPU encoder's (keys selected by magnitude,
+    values by quantisation benefit, TurboQuantV2Contract); decode attention (gqa_attention_turboquant_decode's general form,
+    Shaders/TurboQuant.metal:1794-2001), chunked prefill attention and approximateDecode against the CPU restatements, with
+    the residual term off (the reference's contract) and on."""
+    D, L, B, steps = 128, 2, 2, 2
+    rng = rng_for(700 + Hq + len(preset))
+    prec = er.Precision.turboQuantBalanced if preset == "balanced" else er.Precision.turboQuantAggressive
+    lens = [150, 37]
+    T = 208
+    kw = {}
+    if layout == "paged":
+        ps = 16
+        pages = (T // ps) * B + 1
+        kw = dict(layout=er.Layout.paged, page_size=ps, num_pages=pages)
+        alloc = er.BlockTableAllocator(pages, ps, free_order=rng.permutation(pages))
+    ks, vs = scales
+    cache = er.KVCache(T, L, Hkv, D, prec, max_batch=B, key_residual_scale=ks, value_residual_scale=vs, **kw)
+    if layout == "paged":
+        for b in range(B):
+            cache.set_block_table(b, alloc.ensure(b, T))
+    theta = THETA_QWEN3
+    sp = er.step_params(rope_theta=theta)
+    rows = {}
+
+    def encode(Krot, V):
+        return [oracle.tq_encode_rows_preset(Krot.reshape(-1, D), preset, False), oracle.tq_encode_rows_preset(V.reshape(-1, D), preset, True)]
+
+    def cat(a, b_):
+        return [tuple(np.concatenate([x, y]) for x, y in zip(a[i], b_[i])) for i in range(2)]
+
+    for l in range(L):
+        for b in range(B):
+            n = lens[b]
+            K, V = normal_f16(rng, (n, Hkv, D)), normal_f16(rng, (n, Hkv, D))
+            cache.write_rows(l, b, 0, n, dev(torch, K), dev(torch, V), sp)
+            Kr = np.concatenate([oracle.rope_neox(K[t:t + 1], t, theta) for t in range(n)])
+            rows[l, b] = encode(Kr, V)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for s in range(steps):
+        q, k, v = normal_f16(rng, (L, B, Hq, D)), normal_f16(rng, (L, B, Hkv, D)), normal_f16(rng, (L, B, Hkv, D))
+        out = torch.full((L, B, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        got = out.cpu().numpy()
+        for l in range(L):
+            for b in range(B):
+                pos = lens[b] + s
+                rows[l, b] = cat(rows[l, b], encode(oracle.rope_neox(k[l, b][None], pos, theta), v[l, b][None]))
+                qr = oracle.rope_neox(q[l, b][None], pos, theta)[0]
+                want = oracle.tq_attention_decode_preset(qr, rows[l, b][0], rows[l, b][1], preset, Hkv, pos + 1, ks, vs, threads=8)
+                worst = max(worst, max_rel_err(got[l, b], want))
+    print("%s rows, residual scales %s: decode worst element-wise relative error %.2e" % (preset, scales, worst))
+    assert worst < TOL, worst
+    # stored rows in the reference's split buffers, bit for bit; decoded rows (approximateDecode: keys with residualWeight 1,
+    # values with the contract's scale)
+    for l in range(L):
+        for b in range(B):
+            got_k, got_v = cache.retrieve_turboquant_runtime_rows(l, seq=b)
+            for got_rows, want_rows in ((got_k, rows[l, b][0]), (got_v, rows[l, b][1])):
+                for g, w_ in zip(got_rows, want_rows):
+                    assert np.array_equal(np.asarray(g).view(np.uint32), np.asarray(w_).view(np.uint32)), (l, b)
+    dk, dv = cache.retrieve_decoded_turboquant(0, seq=1)
+    n1 = lens[1] + steps
+    for got_dec, want_rows, weight in ((dk, rows[0, 1][0], 1.0), (dv, rows[0, 1][1], vs)):
+        c_, s_, m_, meta = want_rows
+        want = np.stack([oracle.tq_decode_preset(c_[i], s_[i], m_[i], preset, meta[i, 0], meta[i, 1], weight) for i in range(n1 * Hkv)])
+        assert np.array_equal(np.asarray(got_dec).reshape(-1, D).view(np.uint32), want.view(np.uint32))
+    # one more row through the host append (no rotation: rows as given, KVCache.swift:909-975)
+    hk, hv = normal_f16(rng, (Hkv, D)), normal_f16(rng, (Hkv, D))
+    cache.append(1, hk, hv, seq=1)
+    (gk, _), (gv, _) = [(r[0][-Hkv:], None) for r in cache.retrieve_turboquant_runtime_rows(1, seq=1)]
+    want_h = encode(hk, hv)
+    assert np.array_equal(gk, want_h[0][0]) and np.array_equal(gv, want_h[1][0])
+    cache.set_position(n1, seq=1)
+    # chunked prefill over sequence 0 of layer 0: 64 query rows at the end of the context
+    S = 64
+    n0 = lens[0] + steps
+    qc = normal_f16(rng, (S, Hq, D))
+    outp = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(0, 0, dev(torch, qc), outp, Hq, S, sp, q_offset=n0 - S)
+    torch.cuda.synchronize()
+    gp = outp.cpu().numpy()
+    wp = 0.0
+    for r in range(0, S, 7):
+        pos = n0 - S + r
+        qr = oracle.rope_neox(qc[r][None], pos, theta)[0]
+        want = oracle.tq_attention_decode_preset(qr, rows[0, 0][0], rows[0, 0][1], preset, Hkv, pos + 1, ks, vs, threads=8)
+        wp = max(wp, max_rel_err(gp[r], want))
+    print("%s rows: prefill worst element-wise relative error %.2e" % (preset, wp))
+    assert wp < TOL, wp
 
 
 @pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4)])
