@@ -222,8 +222,9 @@ int32_t er_kv_retrieve_decoded_q8_0(er_kv* kv, uint32_t layer, uint32_t seq, flo
 int32_t er_kv_retrieve_q8_0_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint8_t* host_key_blocks, uint8_t* host_value_blocks,
                                  size_t capacity_bytes, uint32_t* token_count);
 /* KVCache.retrieveTurboQuantRuntimeRows (KVCache.swift:588-629) in the reference's split-buffer row format:
- * codes [rows][words], residual signs [rows][4] (zero), outlier mask [rows][4] (zero), metadata [rows][2]
- * (rowNorm, 0).  rows = tokens*numKVHeads in logical order, row = token*numKVHeads + kvHead. */
+ * codes [rows][words], residual signs [rows][4], outlier mask [rows][4], metadata [rows][2] = (rowNorm, residualNorm) --
+ * signs, mask and residualNorm are zero for the fixed presets; BALANCED / AGGRESSIVE caches return what the encoder
+ * stored (words = 14 / 9, split-plane codes).  rows = tokens*numKVHeads in logical order, row = token*numKVHeads + kvHead. */
 int32_t er_kv_retrieve_turboquant_rows(er_kv* kv, uint32_t layer, uint32_t seq, int is_value, uint32_t* host_codes,
                                        uint32_t* host_residual_signs, uint32_t* host_outlier_mask,
                                        float* host_metadata, size_t capacity_rows, uint32_t* row_count);
