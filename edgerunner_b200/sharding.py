@@ -231,8 +231,10 @@ def small_paged_case(er, seed=3, layers=2, batch=5, num_heads=32, num_kv_heads=8
     params = er.step_params(rope_theta=theta)
 
     def make_cache(local_kv_heads):
+        # the persistent kernel on both sides of a comparison: launches that write sharded rows always use it, and a
+        # bit-for-bit check needs the same summation order
         c = er.KVCache(cap, layers, local_kv_heads, 128, er.Precision.float16, max_batch=batch, layout=er.Layout.paged,
-                       page_size=page_size, num_pages=pages)
+                       page_size=page_size, num_pages=pages, decode_kernel=1)
         alloc = er.BlockTableAllocator(pages, page_size, free_order=order)
         for b, n in enumerate(lens):
             c.set_block_table(b, alloc.ensure(b, n + steps))

@@ -149,3 +149,17 @@ def test_all_gather_of_head_slices_gloo_world2(tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o
         assert "rank %d ok" % r in o
+
+
+def test_heterogeneous_cache_refusals_need_no_device():
+    """The share-map checks of the heterogeneous initializer (KVCache.swift:297-333) run before anything touches a device."""
+    import edgerunner_b200 as er
+    for dims, src, prec in (([256, 256], [1, 1], er.Precision.float16),          # shares a later layer
+                            ([256, 512], [0, 0], er.Precision.float16),          # head sizes differ
+                            ([256, 256, 256], [0, 0, 1], er.Precision.float16),  # source does not own its buffers
+                            ([256], [0, 0], er.Precision.float16),               # lengths differ
+                            ([256, 256], [0, 7], er.Precision.float16),          # out of range
+                            ([128], [0], er.Precision.q8_0)):                    # dense only
+        with pytest.raises(er.EdgeRunnerCUDAError) as e:
+            er.HeterogeneousKVCache(32, 2, dims, src, prec)
+        assert e.value.name == "unsupportedStorage"

@@ -313,3 +313,54 @@ def test_pages_exported_and_imported_for_prefix_reuse(er, torch, precision):
     with pytest.raises(er.EdgeRunnerCUDAError) as e:
         tm.page_bytes()
     assert e.value.name == "unsupported"
+
+
+def test_heterogeneous_layers_and_shared_kv(er, torch, oracle):
+    """KVCache.init(... headDimByLayer:kvSourceLayers: ...) (KVCache.swift:276-392): per-layer head sizes, a layer that
+    aliases an earlier layer's buffers, the initializer's refusals; attention over a 256-wide layer through the windowed
+    raw-buffer operator on the buffers the cache hands out, against the CPU routine."""
+    Hkv, T = 2, 32
+    dims, src = [256, 512, 256, 256, 512], [0, 1, 2, 0, 1]
+    c = er.HeterogeneousKVCache(T, Hkv, dims, src, er.Precision.float16)
+    assert c.head_dim == 256 and c.head_dim_for_layer(1) == 512 and not c.owns_buffers(3) and c.owns_buffers(2)
+    rng = np.random.Generator(np.random.PCG64(9))
+    rows = {l: [] for l in (0, 1, 2)}
+    for t in range(5):
+        for l in (0, 1, 2):
+            k = rng.standard_normal(Hkv * dims[l]).astype(np.float16)
+            v = rng.standard_normal(Hkv * dims[l]).astype(np.float16)
+            c.append_f16(l, k, v)
+            rows[l].append((k, v))
+    for l, s_ in enumerate(src):                          # a shared layer reads its source's rows
+        k, v = c.retrieve(l, np.float16)
+        assert np.array_equal(k.view(np.uint16), np.concatenate([r[0] for r in rows[s_]]).view(np.uint16))
+        assert np.array_equal(v.view(np.uint16), np.concatenate([r[1] for r in rows[s_]]).view(np.uint16))
+    assert c.metal_buffers(3) == c.metal_buffers(0) and c.metal_buffers(2) != c.metal_buffers(0)
+    assert c.cache_params(4).currentLen == 5 and c.current_length == 5
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        c.retrieve(5, np.float16)
+    assert e.value.name == "invalidLayer"
+    for bad in (([256, 256], [1, 1]), ([256, 512], [0, 0]), ([256, 256, 256], [0, 0, 1]), ([256], [0, 0]), ([], [])):
+        with pytest.raises(er.EdgeRunnerCUDAError) as e:
+            er.HeterogeneousKVCache(T, Hkv, bad[0], bad[1], er.Precision.float16)
+        assert e.value.name == "unsupportedStorage"
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:
+        er.HeterogeneousKVCache(T, Hkv, [128], [0], er.Precision.turboquantV2)
+    assert e.value.name == "unsupportedStorage"
+    # attention of 8 query heads over layer 3 (= layer 0's rows, head size 256) with the windowed operator
+    H, D = 8, 256
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    kbuf, vbuf = c.metal_buffers(3)
+    qd = torch.as_tensor(q).cuda()
+    out = torch.empty((H, D), device="cuda")
+    er.Gemma4DecodeKernels().encode_decode_gqa_f16kv_windowed(qd, kbuf, vbuf, out, H, Hkv, D, 0, 5, T)
+    torch.cuda.synchronize()
+    k16 = np.zeros((T, Hkv, D), np.float16)
+    v16 = np.zeros((T, Hkv, D), np.float16)
+    for t, (k, v) in enumerate(rows[0]):
+        k16[t], v16[t] = k.reshape(Hkv, D), v.reshape(Hkv, D)
+    want = oracle.gqa_f16kv_windowed(q, k16.view(np.uint16), v16.view(np.uint16), 0, 5)
+    got = out.cpu().numpy()
+    floor = 1e-3 * np.abs(want).max()
+    assert float(np.max(np.abs(got - want) / np.maximum(np.abs(want), floor))) < 2e-3
+    c.close()
