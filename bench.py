@@ -583,16 +583,13 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
                 cache.decode_step_host(hq_p[i], hk_p[i], hv_p[i], hout_p, H, sp, stream=stream_p)
             entry = "er_kv_decode_step_host"
         else:
-            dq, dk, dv = torch.empty_like(qs[0]), torch.empty_like(ks[0]), torch.empty_like(vs[0])
+            hout = torch.empty((L, B, H, D), dtype=torch.float32).pin_memory()      # this rank's heads; the ranks' buffers together = the result
+            hout_np = hout.numpy()
 
             def host_step(i):
-                dq.copy_(hq[i], non_blocking=True)
-                dk.copy_(hk[i], non_blocking=True)
-                dv.copy_(hv[i], non_blocking=True)
-                dec.step(dq, dk, dv, sp, stream=stream)
-                hout.copy_(dec.full, non_blocking=True)
-                stream.synchronize()
-            entry = "HeadShardedDecoder.step with pinned host q/k/v slices in and the gathered [layers, batch, heads, 128] tensor out"
+                dec.step_host(hq[i], hk[i], hv[i], hout, sp, stream=stream)
+            entry = ("HeadShardedDecoder.step_host: pinned host q/k/v slices in (pulled by the decode kernel), exchange on the device, "
+                     "every rank's own heads [layers, batch, heads / N, 128] out to pinned host memory")
         e2e_regions = []
         checksum = 0.0
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

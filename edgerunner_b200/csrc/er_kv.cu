@@ -1589,6 +1589,12 @@ static void* mapped_device_pointer(const void* host) {
     return attr.devicePointer;
 }
 
+static bool is_device_pointer(const void* p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return attr.type == cudaMemoryTypeDevice;
+}
+
 int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float* hq, const float* hk, const float* hv, float* hout,
                                uint32_t num_heads, const er_step_params* sp, void* stream) {
     if (!kv || !hq || !hk || !hv || !hout) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
@@ -1608,13 +1614,17 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     const void* mk = mapped_device_pointer(hk);
     const void* mv = mapped_device_pointer(hv);
     void* mout = mapped_device_pointer(hout);
+    // `hout` may also name device memory (a kv-head shard's step writes into the gathered buffer): the rows then stay on the
+    // device and the call returns as soon as its work is enqueued -- the host buffers must stay untouched until the stream
+    // has passed the step, and the status word is read with er_kv_device_status.
+    const bool out_on_device = mout == nullptr && is_device_pointer(hout);
     const bool mapped_in = mq && mk && mv && q_bytes % 16 == 0 && kv_bytes % 16 == 0;
     // float16 rows, one persistent launch for the whole call, everything pinned: no gather launch, no copy, no stream
     // synchronisation -- the decode kernel's producer warps pull the rows of their own item visits from the mapped buffers
     // while earlier tiles stream, its merging warps store the output rows into host memory, and its last CTA writes
     // {epoch, status} to a mapped host word this thread polls.
     bool in_kernel = false;
-    if (mapped_in && mout && kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim && kv->d_host_done != nullptr &&
+    if (mapped_in && (mout || out_on_device) && kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim && kv->d_host_done != nullptr &&
         !uses_slim_kernel(kv, le - lb) && le - lb <= std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch)) {
         std::lock_guard<std::mutex> lock(kv->mu);
         kv->hostio_q = static_cast<const float*>(mq); kv->hostio_k = static_cast<const float*>(mk); kv->hostio_v = static_cast<const float*>(mv);
@@ -1637,7 +1647,7 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
         }
     }
     // pinned output: the merging warps store the rows straight into host memory
-    float* step_out = mout ? static_cast<float*>(mout) : reinterpret_cast<float*>(dout);
+    float* step_out = out_on_device ? hout : (mout ? static_cast<float*>(mout) : reinterpret_cast<float*>(dout));
     rc = er_kv_decode_step(kv, lb, le, reinterpret_cast<const float*>(dq), reinterpret_cast<const float*>(dk), reinterpret_cast<const float*>(dv),
                            step_out, num_heads, sp, stream);
     bool signalled = false;
@@ -1651,6 +1661,7 @@ int32_t er_kv_decode_step_host(er_kv* kv, uint32_t lb, uint32_t le, const float*
     }
     if (rc != ER_OK) return rc;
     if (in_kernel && !signalled) return fail(ER_ERR_CUDA, "host-buffer step: the decode launch did not take the mapped rows");
+    if (out_on_device) return ER_OK;
     if (signalled) {
         // the launch reports by itself; poll its word (its patience for device waits is 2 s, so well past that means a lost launch)
         volatile int* done = kv->h_status + 2;

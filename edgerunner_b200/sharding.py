@@ -161,6 +161,27 @@ class HeadShardedDecoder:
             self.cache.decode_step(q_local, k_local, v_local, self.full, hl, params, stream=stream)
         return self.full
 
+    def step_host(self, hq_local, hk_local, hv_local, hout_local, params, stream=None):
+        """The same step from pinned host memory: this rank's q / k / v slices come straight out of `hq_local`, `hk_local`,
+        `hv_local` (the decode kernel pulls the rows itself on float16 caches), the exchange runs, and the rank's own heads
+        `[layers, batch, local_heads, 128]` are copied to the pinned `hout_local` -- the ranks' host buffers together hold the
+        step's result once.  Returns after the stream has finished the step."""
+        hl = self.shard.local_heads
+        target = self.out_local if self.exchange == "nccl" else self.full
+        self.cache.decode_step_host(hq_local, hk_local, hv_local, target, hl, params, stream=stream)
+        if self.exchange == "nccl":
+            from ._lib import check, lib, ptr, stream_ptr
+            dist.all_gather_into_tensor(self.gathered, self.out_local, group=self.group)
+            check(lib().er_relayout_head_shards(ptr(self.gathered), ptr(self.full), self.world, self.layers * self.batch, hl,
+                                                stream_ptr(stream)))
+            hout_local.copy_(self.out_local, non_blocking=True)
+        else:
+            if self.exchange == "p2p":
+                dist.all_reduce(self._flag, group=self.group)
+            hout_local.copy_(self.full[:, :, self.shard.q_begin:self.shard.q_end], non_blocking=True)
+        (stream if stream is not None and not isinstance(stream, int) else torch.cuda.current_stream()).synchronize()
+        return self.full
+
     def set_peer_stores(self, enabled):
         """p2p exchange only: drop / restore the peer stores (the rank then fills its own buffer only)."""
         if self.exchange == "p2p":
@@ -264,8 +285,16 @@ def verify_exchange(er, world, rank, exchange, group=None):
     dec = HeadShardedDecoder(cache, case["layers"], case["batch"], case["num_heads"], case["num_kv_heads"], world, rank, exchange, group)
     used = dec.exchange
     for s in range(case["steps"]):
-        full = dec.step(shard.slice_q(case["q"][s]).contiguous(), shard.slice_kv(case["k"][s]).contiguous(),
-                        shard.slice_kv(case["v"][s]).contiguous(), case["params"])
+        ql, kl, vl = (shard.slice_q(case["q"][s]).contiguous(), shard.slice_kv(case["k"][s]).contiguous(),
+                      shard.slice_kv(case["v"][s]).contiguous())
+        if s + 1 < case["steps"]:
+            full = dec.step(ql, kl, vl, case["params"])
+        else:   # the last step from pinned host memory: same rows on the device, the rank's own heads on the host
+            hq, hk, hv = (x.cpu().pin_memory() for x in (ql, kl, vl))
+            hout = torch.empty(ql.shape, dtype=torch.float32).pin_memory()
+            full = dec.step_host(hq, hk, hv, hout, case["params"])
+            if not torch.equal(hout, want[s][:, :, shard.q_begin:shard.q_end].cpu()):
+                raise AssertionError("rank %d: host rows of step_host (%s) differ from the per-shard reference" % (rank, used))
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier(group=group)

@@ -361,8 +361,14 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
 int32_t er_kv_decode_step(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* q, const float* k,
                           const float* v, float* out, uint32_t num_heads, const er_step_params* params, void* stream);
 
-/* Same step with HOST buffers (pinned or pageable): copies q/k/v in, runs the step, copies `out` back and
- * waits.  This is the call a host-side model loop makes when its activations live in host memory. */
+/* Same step with HOST buffers (pinned or pageable): q/k/v come from host memory, `out` goes back to it, and the call
+ * returns when the rows are there (with the step's device status as its result).  This is the call a host-side model
+ * loop makes when its activations live in host memory.  With every buffer pinned (cudaHostAlloc / er_host_alloc) a
+ * float16 cache runs the step as ONE launch: the kernel pulls its q/k/v rows out of the mapped buffers while earlier
+ * tiles stream, stores the output rows into host memory and reports to a host word the call polls -- no staging copy, no
+ * stream synchronisation.  `host_out` may also be DEVICE memory (a kv-head shard writing into the gathered buffer of
+ * er_kv_set_output_sharding): the call then only enqueues the step and returns; keep host_q/k/v untouched until `stream`
+ * has passed it and read the status with er_kv_device_status.  One step in flight per cache. */
 int32_t er_kv_decode_step_host(er_kv* kv, uint32_t layer_begin, uint32_t layer_end, const float* host_q,
                                const float* host_k, const float* host_v, float* host_out, uint32_t num_heads,
                                const er_step_params* params, void* stream);

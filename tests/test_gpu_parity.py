@@ -445,7 +445,7 @@ def test_decode_step_host_rows_pulled_by_the_kernel(er, torch, Hq, Hkv):
     T = 768
     pages = (T // ps) * B
     caches = []
-    for _ in range(3):
+    for _ in range(4):
         c = er.KVCache(T, L, Hkv, D, er.Precision.float16, max_batch=B, layout=er.Layout.paged, page_size=ps, num_pages=pages, decode_kernel=1)
         alloc = er.BlockTableAllocator(pages, ps, free_order=rng_for(5).permutation(pages))
         for b in range(B):
@@ -463,6 +463,7 @@ def test_decode_step_host_rows_pulled_by_the_kernel(er, torch, Hq, Hkv):
     hout = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
     pageable_out = np.empty((L, B, Hq, D), dtype=np.float32)
     out_d = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
+    out_dev = torch.empty((L, B, Hq, D), dtype=torch.float32, device="cuda")
     launches = er.lib().er_kernel_launch_count
     for step in range(4):
         q, k, v = (normal_f16(rng, (L, B, h, D)) for h in (Hq, Hkv, Hkv))
@@ -474,9 +475,14 @@ def test_decode_step_host_rows_pulled_by_the_kernel(er, torch, Hq, Hkv):
         got = hout.clone()
         assert launches() - n0 == 1                               # the decode launch alone
         caches[2].decode_step_host(hq, hk, hv, pageable_out, Hq, sp)
+        n1 = launches()
+        out_dev.fill_(float("nan"))
+        caches[3].decode_step_host(hq, hk, hv, out_dev, Hq, sp)    # device output: enqueued only, rows pulled by the kernel
+        assert launches() - n1 == 1
         torch.cuda.synchronize()
         assert torch.equal(out_d.cpu(), got), step
         assert np.array_equal(out_d.cpu().numpy(), pageable_out), step
+        assert torch.equal(out_d, out_dev), step
     for c in caches[1:]:
         assert c.device_status() == 0
         for l in range(L):
