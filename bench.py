@@ -46,6 +46,8 @@ WORKLOADS = {
     # BASELINE.json configs[1]
     "cfg1": dict(name="cfg1: Qwen3-0.6B shape, 28 layers, batch 1, fp16 KV, context 4096, 1 token appended per step",
                  layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="head_major", theta=1.0e6),
+    "cfg1_per_layer": dict(name="cfg1 with one call per layer (28 launches per step: how a model that interleaves its own projections calls the path)",
+                           layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="head_major", theta=1.0e6, per_layer=True),
     "cfg1_token_major": dict(name="cfg1 with the reference's token-major [slot][kvHead][dim] ring layout",
                              layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="token_major",
                              theta=1.0e6),
@@ -440,8 +442,22 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
     vs = torch.randn((pool, L, B, Hkv, D), generator=g, device="cuda").half().float()
     out = dec.full if dec is not None else torch.empty((L, B, H, D), device="cuda", dtype=torch.float32)
 
+    # raw addresses of every (step, layer) slice: one call per layer must not pay for tensor slicing in the interpreter
+    layer_ptrs = None
+    if not sharded and (w.get("per_layer") or "per_layer" in extras):
+        layer_ptrs = [[(qs[i, l].data_ptr(), ks[i, l].data_ptr(), vs[i, l].data_ptr(), out[l].data_ptr()) for l in range(L)] for i in range(pool)]
+    stream_raw = stream.cuda_stream
+
+    def per_layer_step(i, on=None):
+        on = stream_raw if on is None else on
+        for l in range(L):
+            a = layer_ptrs[i][l]
+            cache.decode_step(a[0], a[1], a[2], a[3], H, sp, layer_begin=l, layer_end=l + 1, stream=on)
+
     def step(i, exchange=True):
-        if dec is not None:
+        if w.get("per_layer") and not sharded:
+            per_layer_step(i)
+        elif dec is not None:
             dec.step(qs[i], ks[i], vs[i], sp, stream=stream, exchange=exchange)
         else:
             cache.decode_step(qs[i], ks[i], vs[i], out, H, sp, stream=stream)
@@ -527,7 +543,12 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
     # fp16 rows: the timed region is K launches of the one fused kernel (plus K re-layout launches behind an NCCL all-gather)
     fused_single_launch = launches == K or (sharded and dec.exchange == "nccl" and w["precision"] == "float16" and launches == 2 * K)
     t_append = 0.0
-    if fused_single_launch:
+    kernel_name = "flash_decode_kernel"
+    if w.get("per_layer") and launches == K * L:
+        # one fused launch per layer: the region's time over its K * L launches
+        t_attn, attn_bytes, timed_as = ms_compute / (K * L), bytes_region / (K * L), "the K x layers launches of the timed region, back to back on one stream"
+        split_attn_ms, kernel_name = None, "decode_slim_kernel"
+    elif fused_single_launch:
         t_attn, attn_bytes, timed_as = ms_compute / K, bytes_region / K, "the K launches of the timed region (append fused into the kernel)"
         split_attn_ms = None
     else:
@@ -553,7 +574,7 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
         split_attn_ms, timed_as = t_attn, "attention launch between per-step CUDA events (split entry points), median"
     achieved = attn_bytes / (t_attn * 1e-3) / 1e9
     ratio = NCU_TRAFFIC_RATIO.get("%s/group%d" % (w["precision"], H // Hkv))
-    res["roofline"] = {"bound": "hbm", "kernel": "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+    res["roofline"] = {"bound": "hbm", "kernel": kernel_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                        "frac": round(achieved / peak, 4),
                        "traffic": int(attn_bytes * ratio[0]) if ratio else None,
                        "traffic_source": ("algorithmic bytes x %.4f, the DRAM-traffic ratio of the ncu capture in %s" % ratio) if ratio else None,
@@ -619,10 +640,6 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
     #      as a CUDA graph of the layer launches (positions live on the device, so one captured step replays for every
     #      following step) ----
     if "per_layer" in extras and dec is None:
-        def per_layer_step(i):
-            for l in range(L):
-                cache.decode_step(qs[i, l], ks[i, l], vs[i, l], out[l], H, sp, layer_begin=l, layer_end=l + 1, stream=torch.cuda.current_stream())
-
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         set_start()
         for s in range(min(W, 4)):
@@ -641,12 +658,12 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                per_layer_step(0)                      # warm the capture stream
+                per_layer_step(0, side.cuda_stream)    # warm the capture stream
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                per_layer_step(0)
+                per_layer_step(0, torch.cuda.current_stream().cuda_stream)
             set_start()
             for _ in range(4):
                 graph.replay()
