@@ -110,8 +110,17 @@ __device__ __forceinline__ void prefetch_l2(const void* ptr) {
 
 // Per-head RMS-norm factor rsqrt(sum(x^2) / 128 + eps) of a 128-float row, summed in the order head_rms_norm_kernel uses
 // (pair terms x[i]^2 + x[i+64]^2, xor butterfly 16..1 over each 32 pairs, one add).  All 32 lanes take part.
+// A load of a step's q / k / v row.  COHERENT = false: the rows are inputs of the launch (read-only path, L1).  true: the
+// launch itself staged them (host-buffer steps), so they are read at L2, the point its own stores are visible at.
+template <bool COHERENT, typename T>
+__device__ __forceinline__ T ld_step_row(const T* ptr) {
+    if constexpr (COHERENT) return __ldcg(ptr); else return __ldg(ptr);
+}
+
+template <bool COHERENT = false>
 __device__ __forceinline__ float head_rms_scale(const float* row, float eps, int lane) {
-    const float a = __ldcg(row + lane), b = __ldcg(row + lane + 64), c = __ldcg(row + lane + 32), d = __ldcg(row + lane + 96);
+    const float a = ld_step_row<COHERENT>(row + lane), b = ld_step_row<COHERENT>(row + lane + 64), c = ld_step_row<COHERENT>(row + lane + 32),
+                d = ld_step_row<COHERENT>(row + lane + 96);
     float s0 = __fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b));
     float s1 = __fadd_rn(__fmul_rn(c, c), __fmul_rn(d, d));
 #pragma unroll

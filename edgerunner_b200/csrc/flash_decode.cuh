@@ -266,9 +266,10 @@ struct DensePolicy {
     using State = LaneState<GROUP, kQRegs>;
 
     __device__ static bool init_extra(uint8_t*, int, int) { return true; }
+    template <bool COHERENT = false>
     __device__ __forceinline__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs,
                                                   uint8_t* extra, int warp, int lane, int layer) {
-        load_q(p, st.q, qrow, cs, extra, warp, lane, p.q_norm_w ? p.q_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr);
+        load_q<COHERENT>(p, st.q, qrow, cs, extra, warp, lane, p.q_norm_w ? p.q_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr);
         st.reset();
     }
     __device__ __forceinline__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid,
@@ -360,17 +361,18 @@ struct DensePolicy {
     }
 
     // Consumers: per-lane Q registers, NeoX-rotated in registers when asked.
+    template <bool COHERENT = false>
     __device__ static void load_q(const DecodeParams& p, float (&q)[GROUP][kQRegs], const float* qrow, const float2* cs,
                                   uint8_t*, int, int lane, const float* qw) {
         const int i = lane & 7;
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             const float4* src = reinterpret_cast<const float4*>(qrow + g * kHeadDim + 8 * i);
-            const float4 a0 = __ldcg(src), a1 = __ldcg(src + 1), b0 = __ldcg(src + 16), b1 = __ldcg(src + 17);   // L2: the rows may have been staged by this launch
+            const float4 a0 = ld_step_row<COHERENT>(src), a1 = ld_step_row<COHERENT>(src + 1), b0 = ld_step_row<COHERENT>(src + 16), b1 = ld_step_row<COHERENT>(src + 17);
             float xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             float xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
             if (qw != nullptr) {
-                const float rs = head_rms_scale(qrow + g * kHeadDim, p.rms_eps, lane);
+                const float rs = head_rms_scale<COHERENT>(qrow + g * kHeadDim, p.rms_eps, lane);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     xa[c] = __fmul_rn(__fmul_rn(xa[c], rs), __ldg(qw + 8 * i + c));
@@ -488,6 +490,7 @@ struct DensePolicy {
     // Fused append (rope_neox_f32_to_f16 + convert_f32_to_f16 of the decode pass, Shaders/RoPE.metal:498-531,
     // LlamaLanguageModel.swift:3676-3684): the warp whose unit holds the new token's slot converts the new K/V
     // row into the staged tile (so attention sees it) and stores both rows to the cache with 16-byte stores.
+    template <bool COHERENT = false>
     __device__ static void patch_new_row(const DecodeParams& p, uint8_t* stage, int unit, int r, int layer, int seq,
                                          int head, int slot, const float* k_src, const float* v_src, const float2* cs,
                                          int lane) {
@@ -495,11 +498,11 @@ struct DensePolicy {
         uint8_t* vrow = stage + kTileBytesF16 + (unit * kUnitTokens + r) * kRowBytesF16;
         __half* kh = reinterpret_cast<__half*>(krow);
         const float* kw = p.k_norm_w ? p.k_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr;
-        const float rs = kw ? head_rms_scale(k_src, p.rms_eps, lane) : 1.f;
+        const float rs = kw ? head_rms_scale<COHERENT>(k_src, p.rms_eps, lane) : 1.f;
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
             const int d = lane + 32 * part;
-            float x0 = __ldcg(k_src + d), x1 = __ldcg(k_src + d + kHalfDim);
+            float x0 = ld_step_row<COHERENT>(k_src + d), x1 = ld_step_row<COHERENT>(k_src + d + kHalfDim);
             if (kw != nullptr) {
                 x0 = __fmul_rn(__fmul_rn(x0, rs), __ldg(kw + d));
                 x1 = __fmul_rn(__fmul_rn(x1, rs), __ldg(kw + d + kHalfDim));
@@ -513,7 +516,7 @@ struct DensePolicy {
             kh[d] = __float2half_rn(x0);
             kh[d + kHalfDim] = __float2half_rn(x1);
         }
-        const float4 v4 = __ldcg(reinterpret_cast<const float4*>(v_src) + lane);
+        const float4 v4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(v_src) + lane);
         uint2 vv;
         reinterpret_cast<__half2*>(&vv)[0] = __halves2half2(__float2half_rn(v4.x), __float2half_rn(v4.y));
         reinterpret_cast<__half2*>(&vv)[1] = __halves2half2(__float2half_rn(v4.z), __float2half_rn(v4.w));
@@ -535,9 +538,12 @@ struct DensePolicy {
 
 // ------------------------------------------------------------------------------------------ the kernel
 
-template <class POL>
+// HOSTIO: the variant that pulls the step's rows out of mapped host memory and reports to a host word (host-buffer steps on
+// fused-append policies); a separate instantiation, so that the ordinary launch carries none of its code.
+template <class POL, bool HOSTIO = false>
 __global__ void __launch_bounds__((POL::kUnitsPerTile * POL::kWarpGroups + 1) * 32, 1)
 flash_decode_kernel(const __grid_constant__ DecodeParams p) {
+    static_assert(!HOSTIO || POL::kFusedAppend, "host rows are pulled by the policies that append the new row themselves");
     using L = DecodeSmem<POL>;
     constexpr int GROUP = POL::kGroup;
     constexpr int kStages = POL::kStages;
@@ -643,7 +649,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
             int k = 0;
             int64_t cur = p.withhold_tiles ? range_end : range_begin;
             // host-buffer step: rows of the next item visit, in flight over the bus while this visit's tiles are issued
-            const bool hostio = POL::kFusedAppend && p.host_q != nullptr;
+            constexpr bool hostio = HOSTIO;
             float4 hq_r[GROUP], hk_r = make_float4(0.f, 0.f, 0.f, 0.f), hv_r = hk_r;
             int64_t hq_off = 0, hkv_off = 0;
             int landed = 0;
@@ -664,13 +670,13 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 __syncwarp();
                 if (lane == 0) flags[3] = ++landed;
             };
-            if (hostio && cur < range_end) host_load(locate_segment(prefix, num_pairs, hkv, cur, range_end));
+            if constexpr (hostio) { if (cur < range_end) host_load(locate_segment(prefix, num_pairs, hkv, cur, range_end)); }
             while (cur < range_end) {
                 const Segment sg = locate_segment(prefix, num_pairs, hkv, cur, range_end);
                 const int layer = p.layer_begin + sg.pair / p.batch, seq = sg.pair % p.batch;
                 const int kv_len = kv_length(p, sg.pair);
                 const int start = kv_start(p, sg.pair, kv_len);
-                bool rows_pending = hostio;   // staged right after the visit's first tile is on its way
+                [[maybe_unused]] bool rows_pending = hostio;   // staged right after the visit's first tile is on its way
                 if (!hostio) {
                     // The consumers read this item's query rows (and the new K/V row) only when they get here, several tiles
                     // later: pull the lines into L2 now so that the item switch does not wait on DRAM.
@@ -691,11 +697,13 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                         if (k >= kStages) mbar_wait(&empty_bar[s], ((k / kStages) - 1) & 1, &flags[0], p.status, wait_ns);
                     };
                     POL::issue_tile(p, smem + s * POL::kStageBytes, &full_bar[s], layer, seq, sg.head, t0, ntok, lane, start, wait_free);
-                    if (rows_pending) {
-                        rows_pending = false;
-                        host_store();
-                        const int64_t nxt = cur + (sg.u1 - sg.u0);
-                        if (nxt < range_end) host_load(locate_segment(prefix, num_pairs, hkv, nxt, range_end));
+                    if constexpr (hostio) {
+                        if (rows_pending) {
+                            rows_pending = false;
+                            host_store();
+                            const int64_t nxt = cur + (sg.u1 - sg.u0);
+                            if (nxt < range_end) host_load(locate_segment(prefix, num_pairs, hkv, nxt, range_end));
+                        }
                     }
                 }
                 cur += sg.u1 - sg.u0;
@@ -722,7 +730,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                 }
                 float2* cs = cos_sin + cs_buf * kHalfDim;
                 consumer_sync<NW * 32>();
-                if (POL::kFusedAppend && p.host_q != nullptr) {   // the producer warp has this visit's host rows staged?
+                if constexpr (HOSTIO) {   // the producer warp has this visit's host rows staged?
                     if (flags[3] <= visit && !flags[0]) {
                         const uint64_t t_start = global_timer_ns();
                         uint32_t spins = 0;
@@ -739,7 +747,8 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
 
                 typename POL::State st;
                 const float* qrow = p.q + (static_cast<int64_t>(sg.pair) * p.num_q_heads + sg.head * GROUP) * kHeadDim;
-                POL::load_q(p, st, qrow, cs, extra, warp, lane, layer);
+                if constexpr (HOSTIO) POL::template load_q<true>(p, st, qrow, cs, extra, warp, lane, layer);
+                else POL::load_q(p, st, qrow, cs, extra, warp, lane, layer);
 
                 float* my_ml = merge_ml + warp * GROUP * 2;
                 float* my_acc = merge_acc + warp * GROUP * kHeadDim;
@@ -756,10 +765,14 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
                     if (POL::kFusedAppend && p.fused_append && !flags[0]) {
                         const int slot_new = q_pos % p.addr.max_seq_len;
                         const int row_new = p.window > 0 ? kv_len - 1 : slot_new;   // the newest row closes a window
-                        if (wunit < nun && tu + wunit == (row_new >> 4))
-                            POL::patch_new_row(p, smem + s * POL::kStageBytes, wunit, row_new & 15, layer, seq, sg.head, slot_new,
+                        if (wunit < nun && tu + wunit == (row_new >> 4)) {
+                            if constexpr (HOSTIO) POL::template patch_new_row<true>(p, smem + s * POL::kStageBytes, wunit, row_new & 15, layer, seq, sg.head, slot_new,
                                                p.k_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim,
                                                p.v_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim, cs, lane);
+                            else POL::patch_new_row(p, smem + s * POL::kStageBytes, wunit, row_new & 15, layer, seq, sg.head, slot_new,
+                                               p.k_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim,
+                                               p.v_new + (static_cast<int64_t>(sg.pair) * hkv + sg.head) * kHeadDim, cs, lane);
+                        }
                     }
                     if (wunit < nun && !flags[0]) {
                         const int nvalid = min(kUnitTokens, ntok - wunit * kUnitTokens);
@@ -874,7 +887,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
     __syncthreads();
     if (tid == 0) stamp(5);
     if (tid == 0) {
-        if (p.host_done != nullptr) __threadfence_system(); else __threadfence();   // output rows may lie in host memory
+        if constexpr (HOSTIO) __threadfence_system(); else __threadfence();   // HOSTIO: output rows may lie in host memory
         const int prev = atomicAdd(p.done_counter, 1);
         flags[2] = (prev == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
     }
@@ -884,7 +897,7 @@ flash_decode_kernel(const __grid_constant__ DecodeParams p) {
             for (int e = tid; e < num_pairs; e += blockDim.x) p.lengths[p.layer_begin * p.batch + e] += p.advance;
         if (tid == 0) {
             *p.done_counter = 0;
-            if (p.host_done != nullptr) {   // every CTA's rows are out (their fences precede the counter): tell the host
+            if (HOSTIO && p.host_done != nullptr) {   // every CTA's rows are out (their fences precede the counter): tell the host
                 __threadfence_system();
                 const int st = *reinterpret_cast<volatile int*>(p.status);
                 reinterpret_cast<volatile int*>(p.host_done)[1] = st;

@@ -66,6 +66,7 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
     static constexpr int kFoldUnits = 32;   // chains of about 128 accumulating mma per output fragment
 
     // Q rows (per-head RMS norm, then NeoX rotation, when asked) -> B fragments; thread (g, c) holds head g.
+    template <bool COHERENT = false>
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane,
                                   int layer) {
         const int g = lane >> 2, c = lane & 3;
@@ -74,7 +75,7 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
         if (qw != nullptr) {
 #pragma unroll
             for (int h = 0; h < GROUP; ++h) {
-                const float r = head_rms_scale(qrow + h * kHeadDim, p.rms_eps, lane);
+                const float r = head_rms_scale<COHERENT>(qrow + h * kHeadDim, p.rms_eps, lane);
                 if (h == g) rs = r;
             }
         }
@@ -86,8 +87,8 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
             if (g < GROUP) {
                 const int d0 = 32 * b + 8 * c;
                 auto load8 = [&](int d, float (&out)[8]) {
-                    const float4 lo4 = __ldcg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d));
-                    const float4 hi4 = __ldcg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d + 4));
+                    const float4 lo4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d));
+                    const float4 hi4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d + 4));
                     out[0] = lo4.x; out[1] = lo4.y; out[2] = lo4.z; out[3] = lo4.w;
                     out[4] = hi4.x; out[5] = hi4.y; out[6] = hi4.z; out[7] = hi4.w;
                     if (qw != nullptr) {

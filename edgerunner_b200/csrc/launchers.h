@@ -71,8 +71,8 @@ struct AttentionF32Params {
 };
 int launch_attention_f32(const AttentionF32Params& p, int problems, cudaStream_t stream);
 
-template <class POL>
-inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
+template <class POL, bool HOSTIO>
+inline int launch_decode_variant(const DecodeParams& p, int grid, cudaStream_t stream) {
     constexpr int kSmem = DecodeSmem<POL>::kTotal;
     static_assert(kSmem <= 232448, "decode kernel exceeds the 227 KiB shared-memory limit of an sm_100 CTA");
     static int configured_device = -1;   // the attribute is per device and sticky: set it once
@@ -80,7 +80,7 @@ inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t st
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (configured_device != device) {
-        e = cudaFuncSetAttribute(flash_decode_kernel<POL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        e = cudaFuncSetAttribute(flash_decode_kernel<POL, HOSTIO>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured_device = device;
     }
@@ -97,7 +97,16 @@ inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, flash_decode_kernel<POL>, p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, flash_decode_kernel<POL, HOSTIO>, p));
+}
+
+// p.host_q set (host-buffer step on a policy with the fused append): the variant of the kernel that pulls the rows itself.
+template <class POL>
+inline int launch_decode_policy(const DecodeParams& p, int grid, cudaStream_t stream) {
+    if constexpr (POL::kFusedAppend) {
+        if (p.host_q != nullptr) return launch_decode_variant<POL, true>(p, grid, stream);
+    }
+    return launch_decode_variant<POL, false>(p, grid, stream);
 }
 
 }  // namespace er
