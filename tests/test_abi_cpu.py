@@ -163,3 +163,45 @@ def test_heterogeneous_cache_refusals_need_no_device():
         with pytest.raises(er.EdgeRunnerCUDAError) as e:
             er.HeterogeneousKVCache(32, 2, dims, src, prec)
         assert e.value.name == "unsupportedStorage"
+
+
+def test_layer_contract_matches_the_reference_tests():
+    """TurboQuantV2Contract's per-layer resolution, pinned to the literals of the reference's own test
+    (Tests/EdgeRunnerMetalTests/TurboQuantAttentionTests.swift:23-140, which sets the same variables)."""
+    from edgerunner_b200 import TurboQuantLayerContract as C_
+    c = C_.from_environment({})
+    assert (c.key_type, c.value_type) == ("turbo3", "turbo3")
+    assert c.key_cache_type_for(0, 28) == "turbo3" and c.value_cache_type_for(0, 28) == "turbo3"
+    assert c.key_preset_for(0, 28) == "turbo3" and c.value_preset_for(0, 28) == "turbo3"
+    c = C_.from_environment({"EDGERUNNER_TURBOQUANT_KEY_TYPE": "turbo4"})
+    assert c.key_type == "turbo4" and c.key_preset_for(0, 1) == "turbo4"
+    assert C_.from_environment({"EDGERUNNER_TURBOQUANT_VALUE_POLICY": "boundaryTurbo4"}).value_policy == "boundaryTurbo4"
+    c = C_.from_environment({"EDGERUNNER_TURBOQUANT_EARLY_Q8_LAYERS": "1"})
+    assert [c.key_cache_type_for(l, 28) for l in (0, 1)] == ["q8_0", "turbo3"]
+    assert [c.value_cache_type_for(l, 28) for l in (0, 1)] == ["q8_0", "turbo3"]
+    assert c.key_preset_for(0, 28) is None and c.value_preset_for(0, 28) is None
+    assert c.key_preset_for(1, 28) == "turbo3" and c.value_preset_for(1, 28) == "turbo3"
+    c = C_.from_environment({"EDGERUNNER_TURBOQUANT_EARLY_Q8_KEY_LAYERS": "1"})
+    assert [c.key_cache_type_for(l, 28) for l in (0, 1)] == ["q8_0", "turbo3"]
+    assert [c.value_cache_type_for(l, 28) for l in (0, 1)] == ["turbo3", "turbo3"]
+    assert c.key_preset_for(0, 28) is None and c.value_preset_for(0, 28) == "turbo3"
+    c = C_.from_environment({"EDGERUNNER_TURBOQUANT_KEY_PRESET": "planar3", "EDGERUNNER_TURBOQUANT_VALUE_CACHE_TYPE": "dense"})
+    assert c.key_cache_type_for(0, 28) == "turbo3" and c.value_cache_type_for(0, 28) == "dense"
+    assert c.key_preset_for(0, 28) == "planar3" and c.value_preset_for(0, 28) is None
+    # forkAdaptiveModeSevenMapsBoundaryVToQ8 (:127-140)
+    c = C_.from_environment({"EDGERUNNER_TURBOQUANT_VALUE_TYPE": "turbo2", "TURBO_LAYER_ADAPTIVE": "7"})
+    assert [c.value_cache_type_for(l, 28) for l in (0, 1, 2, 25, 26, 27)] == ["q8_0", "q8_0", "turbo2", "turbo2", "q8_0", "q8_0"]
+    # the mode inferred from turbo2 values is the same one (TurboQuant.swift:656-658); short stacks stay uniform
+    c = C_(value_type="turbo2")
+    assert c.value_cache_type_for(0, 28) == "q8_0" and c.value_cache_type_for(0, 6) == "turbo2"
+    assert C_.residual_scale("balanced") == 0.0
+
+
+def test_policy_cache_refuses_mixed_family_layers_without_a_device():
+    import edgerunner_b200 as er
+    from edgerunner_b200.layer_contract import cache_arguments
+    assert cache_arguments("turbo4", "turbo3")[0] == er.Precision.turboquantV2
+    assert cache_arguments("q8_0", "turbo3") is None and cache_arguments("turbo3", "dense") is None
+    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # layer 0: q8_0 keys with turbo3 values
+        er.PolicyKVCache(64, 4, 2, 128, er.TurboQuantLayerContract(early_q8_key_layers=1))
+    assert e.value.name == "unsupportedStorage" and "layer 0" in str(e.value)

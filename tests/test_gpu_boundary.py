@@ -364,3 +364,40 @@ def test_heterogeneous_layers_and_shared_kv(er, torch, oracle):
     floor = 1e-3 * np.abs(want).max()
     assert float(np.max(np.abs(got - want) / np.maximum(np.abs(want), floor))) < 2e-3
     c.close()
+
+
+def test_policy_cache_follows_the_layer_contract(er, torch):
+    """A 10-layer stack under TurboQuantV2Contract with turbo4 keys / turbo3 values and the firstLast4Q8 adaptive mode: layers
+    0-3 and 6-9 keep q8_0 rows, layers 4-5 TurboQuant rows; every layer's step through PolicyKVCache equals the step of a
+    uniform cache of that layer's formats.  (Modes that put turbo2 values next to turbo4 ones resolve too, but decode attention
+    is built for 3- and 4-bit rows.)"""
+    L, Hq, Hkv, D, ctx = 10, 8, 2, 128, 90
+    contract = er.TurboQuantLayerContract(key_type="turbo4", adaptive_mode=1)
+    pc = er.PolicyKVCache(128, L, Hkv, D, contract)
+    assert pc.layer_types[0] == ("q8_0", "q8_0") and pc.layer_types[3] == ("q8_0", "q8_0") and pc.layer_types[6] == ("q8_0", "q8_0")
+    assert pc.layer_types[4] == ("turbo4", "turbo3") and pc.layer_types[5] == ("turbo4", "turbo3")
+    assert sorted(len(pc.layers_of(p)) for p in pc.caches) == [2, 8]
+    mixed = er.TurboQuantLayerContract(key_type="turbo4", early_q8_layers=2, adaptive_mode=5)      # boundaryTurbo4
+    assert [mixed.value_cache_type_for(l, L) for l in (0, 1, 2, 8, 9)] == ["q8_0", "q8_0", "turbo2", "turbo4", "turbo4"]
+    rng = np.random.Generator(np.random.PCG64(77))
+    sp = er.step_params(rope_theta=1e6)
+    from edgerunner_b200.layer_contract import cache_arguments
+    for layer in (0, 4, 5, 9):
+        K = torch.as_tensor(rng.standard_normal((ctx, Hkv, D), dtype=np.float32)).cuda()
+        V = torch.as_tensor(rng.standard_normal((ctx, Hkv, D), dtype=np.float32)).cuda()
+        q = torch.as_tensor(rng.standard_normal((1, Hq, D), dtype=np.float32)).cuda()
+        k = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
+        v = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
+        cache, local = pc.at(layer)
+        cache.write_rows(local, 0, 0, ctx, K, V, sp)
+        precision, extra = cache_arguments(*pc.layer_types[layer])
+        ref = er.KVCache(128, 1, Hkv, D, precision, **extra)
+        ref.write_rows(0, 0, 0, ctx, K, V, sp)
+        got, want = torch.empty((1, Hq, D), device="cuda"), torch.empty((1, Hq, D), device="cuda")
+        pc.decode_step(layer, q, k, v, got, Hq, sp)
+        ref.decode_step(q, k, v, want, Hq, sp)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), layer
+        assert cache.total_written(local, 0) == ctx + 1
+        ref.close()
+    pc.close()
