@@ -191,6 +191,13 @@ public final class KVCache: @unchecked Sendable {
                                           qOffset.map(UInt32.init) ?? UInt32.max, &sp, stream), layer: layer)
     }
     /// Status word the kernels of this cache leave behind (a bounded wait that gave up, a row without a page).
+    /// Layers whose keys and values use different row formats: attention with this cache's K rows and `values`' V rows.
+    public func attentionDecode(withValuesOf values: KVCache, layers: Range<Int>, q: UnsafePointer<Float>, out: UnsafeMutablePointer<Float>,
+                                numHeads: Int, pending: Int, params: inout er_step_params, stream: UnsafeMutableRawPointer? = nil) throws {
+        try check(er_kv_attention_decode_pair(handle, values.handle, UInt32(layers.lowerBound), UInt32(layers.upperBound), q, out,
+                                              UInt32(numHeads), UInt32(pending), &params, stream))
+    }
+
     public func checkDeviceStatus() throws { try check(er_kv_device_status(handle)) }
 
     /// Pages as bytes (prefix reuse): `pageBytes` covers all layers; buffers may be device or (pinned) host memory.

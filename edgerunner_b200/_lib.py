@@ -111,6 +111,8 @@ SYMBOLS = {
     "er_workspace_status": (_i32, []),
     "er_gqa_attention_f16kv_static_status": (_i32, []),
     "er_kv_set_trace": (_i32, [_vp, _vp, _u32]),
+    "er_kv_attention_decode_pair": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp, _u32, _u32, _vp, _vp]),
+    "er_kv_attention_prefill_pair": (_i32, [_vp, _vp, _u32, _u32, _vp, _vp, _u32, _u32, _u32, _vp, _vp]),
     "er_kv_page_bytes": (C.c_int64, [_vp]),
     "er_kv_export_pages": (_i32, [_vp, _vp, _u32, _vp, _sz, _vp]),
     "er_kv_import_pages": (_i32, [_vp, _vp, _u32, _vp, _sz, _vp]),

@@ -1217,6 +1217,79 @@ int32_t er_kv_write_rows(er_kv* kv, uint32_t layer, uint32_t seq, uint32_t start
     return check_launch("set_min_length_kernel");
 }
 
+// One side (keys or values) of a cache as the SIMT attention kernel reads it.
+static int32_t row_source(const er_kv* kv, bool is_value, RowSource& s) {
+    s = RowSource{};
+    s.rows = is_value ? kv->v_slab : kv->k_slab;
+    s.layer_stride_bytes = is_value ? kv->v_layer_stride : kv->k_layer_stride;
+    s.side = is_value ? kv->vn_slab : kv->kn_slab;
+    s.side_layer_stride_bytes = kv->n_layer_stride;
+    s.addr = kv->addressing();
+    if (kv->cfg.head_dim != kHeadDim) return fail(ER_ERR_UNSUPPORTED, "attention kernels are built for head_dim 128");
+    if (kv->outlier) {
+        s.format = kRowsOutlier; s.ofmt = kv->ofmt;
+        s.res_coef = kQjlScale * (is_value ? kv->cfg.value_residual_scale : kv->cfg.key_residual_scale);
+    } else if (kv->turbo) {
+        s.format = kRowsTurbo; s.bits = static_cast<int>(is_value ? kv->cfg.value_type : kv->cfg.key_type); s.norm_fp16 = kv->norm_bytes == 2;
+    } else if (kv->q8) {
+        s.format = kRowsQ8;
+    } else if (kv->cfg.precision == ER_KV_FLOAT16 && !kv->token_major) {
+        s.format = kRowsF16;
+    } else {
+        return fail(ER_ERR_UNSUPPORTED, "this kernel reads float16 (head-major or paged), q8_0 and TurboQuant rows");
+    }
+    return ER_OK;
+}
+
+// Attention of `rows_per_pair` query rows per (layer, sequence) with the K rows of `kk` and the V rows of `vv` (the same cache,
+// or two caches of the same geometry holding the two sides of layers whose keys and values use different formats).
+// kk->mu is held by the caller when kk == vv; otherwise both are taken here.
+static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
+                              int rows_per_pair, int q_pos0, int fixed_seq, const er_step_params& s, cudaStream_t stream) {
+    if (num_heads == 0 || num_heads % kk->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kk->cfg.num_kv_heads);
+    if (s.sliding_window > 0) return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches on the flash-decode kernels");
+    const int group = static_cast<int>(num_heads / kk->cfg.num_kv_heads);
+    const int pairs = fixed_seq >= 0 ? static_cast<int>(le - lb) : static_cast<int>((le - lb) * kk->cfg.max_batch);
+    const int64_t problems = static_cast<int64_t>(pairs) * rows_per_pair;
+    if (problems > 65535) return fail(ER_ERR_UNSUPPORTED, "%lld attention problems in one call; at most 65535", static_cast<long long>(problems));
+    const int items = static_cast<int>(problems) * static_cast<int>(kk->cfg.num_kv_heads);
+    int splits = std::max(1, (4 * std::max(kk->num_sms, 1) + items - 1) / items);
+    splits = std::min(splits, std::max(1, static_cast<int>((kk->cfg.max_seq_len + 63) / 64)));
+    const size_t need = static_cast<size_t>(items) * splits * group * kOutlierPartialStride;
+    if (kk->outlier_partial_floats < need) {
+        if (kk->d_outlier_partial) cudaFree(kk->d_outlier_partial);
+        kk->d_outlier_partial = nullptr;
+        kk->outlier_partial_floats = 0;
+        if (cudaMalloc(&kk->d_outlier_partial, need * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(ER_ERR_ALLOCATION_FAILED, "split partials of %zu floats", need);
+        }
+        kk->outlier_partial_floats = need;
+    }
+    SimtDecodeParams op{};
+    int32_t rc = row_source(kk, false, op.k);
+    if (rc != ER_OK) return rc;
+    if ((rc = row_source(vv, true, op.v)) != ER_OK) return rc;
+    op.q = q; op.out = out;
+    op.lengths = kk->d_lengths; op.layer_begin = static_cast<int>(lb); op.batch = static_cast<int>(kk->cfg.max_batch);
+    op.num_q_heads = static_cast<int>(num_heads); op.pending = static_cast<int>(pending); op.splits = splits;
+    op.fixed_seq = fixed_seq; op.rows_per_pair = rows_per_pair; op.q_pos0 = q_pos0;
+    op.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+    op.apply_rope = s.apply_rope ? 1 : 0; op.rope_scaling = s.rope_scaling;
+    if (op.apply_rope) op.inv_freq = kk->freq(s.rope_theta);
+    op.partial = kk->d_outlier_partial;
+    if (kk->out_heads_total > 0) {
+        if (kk->num_peers > 0) return fail(ER_ERR_UNSUPPORTED, "peer outputs are built for the flash-decode kernels");
+        if (kk->out_head_offset + num_heads > kk->out_heads_total) return fail(ER_ERR_SHAPE, "output sharding: heads exceed %u", kk->out_heads_total);
+        op.out_heads_total = static_cast<int>(kk->out_heads_total); op.out_head_offset = static_cast<int>(kk->out_head_offset);
+    }
+    const int orc = launch_simt_decode(group, op, pairs, stream);
+    g_launches.fetch_add(2, std::memory_order_relaxed);
+    if (orc != 0) return fail(orc == kNotBuilt ? ER_ERR_UNSUPPORTED : ER_ERR_CUDA, "simt_decode_kernel: %s",
+                              orc == kNotBuilt ? "GQA groups 1, 2, 4, 8 are built" : cudaGetErrorString(static_cast<cudaError_t>(orc)));
+    return ER_OK;
+}
+
 // float16 caches: launches over a small amount of rows (one layer of a small batch) skip the persistent kernel
 static bool uses_slim_kernel(const er_kv* kv, uint32_t layers) {
     const uint64_t capacity_bytes = static_cast<uint64_t>(layers) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kv->cfg.max_seq_len * 2 * kRowBytesF16;
@@ -1255,46 +1328,13 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
     if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
         return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
-    if (kv->outlier) {
-        // balanced / aggressive rows: the general form of gqa_attention_turboquant_decode (Shaders/TurboQuant.metal:1794-2001)
-        const int pairs = static_cast<int>((le - lb) * kv->cfg.max_batch);
-        if (pairs > 65535) return fail(ER_ERR_UNSUPPORTED, "%d (layer, sequence) pairs in one call; at most 65535", pairs);
-        const int items = pairs * static_cast<int>(kv->cfg.num_kv_heads);
-        int splits = std::max(1, (4 * std::max(kv->num_sms, 1) + items - 1) / items);
-        splits = std::min(splits, std::max(1, static_cast<int>((kv->cfg.max_seq_len + 63) / 64)));
-        const size_t need = static_cast<size_t>(items) * splits * group * kOutlierPartialStride;
-        if (kv->outlier_partial_floats < need) {
-            if (kv->d_outlier_partial) cudaFree(kv->d_outlier_partial);
-            kv->d_outlier_partial = nullptr;
-            kv->outlier_partial_floats = 0;
-            if (cudaMalloc(&kv->d_outlier_partial, need * sizeof(float)) != cudaSuccess) {
-                cudaGetLastError();
-                return fail(ER_ERR_ALLOCATION_FAILED, "split partials of %zu floats", need);
-            }
-            kv->outlier_partial_floats = need;
-        }
-        OutlierDecodeParams op{};
-        op.q = q; op.out = out;
-        op.k_base = kv->k_slab; op.v_base = kv->v_slab;
-        op.k_layer_stride_bytes = kv->k_layer_stride; op.v_layer_stride_bytes = kv->v_layer_stride;
-        op.lengths = kv->d_lengths; op.layer_begin = static_cast<int>(lb); op.batch = static_cast<int>(kv->cfg.max_batch);
-        op.num_q_heads = static_cast<int>(num_heads); op.pending = static_cast<int>(pending); op.splits = splits;
-        op.scale_log2 = s.softmax_scale * 1.4426950408889634f;
-        op.apply_rope = s.apply_rope ? 1 : 0; op.rope_scaling = s.rope_scaling;
-        if (op.apply_rope) op.inv_freq = kv->freq(s.rope_theta);
-        op.k_res_coef = kQjlScale * kv->cfg.key_residual_scale; op.v_res_coef = kQjlScale * kv->cfg.value_residual_scale;
-        op.fmt = kv->ofmt; op.addr = kv->addressing();
-        op.partial = kv->d_outlier_partial;
-        if (kv->out_heads_total > 0) {
-            if (kv->num_peers > 0) return fail(ER_ERR_UNSUPPORTED, "peer outputs are built for the flash-decode kernels");
-            if (kv->out_head_offset + num_heads > kv->out_heads_total) return fail(ER_ERR_SHAPE, "output sharding: heads exceed %u", kv->out_heads_total);
-            op.out_heads_total = static_cast<int>(kv->out_heads_total); op.out_head_offset = static_cast<int>(kv->out_head_offset);
-        }
-        const int orc = launch_outlier_decode(group, op, pairs, stream);
-        g_launches.fetch_add(2, std::memory_order_relaxed);
-        if (orc != 0) return fail(orc == kNotBuilt ? ER_ERR_UNSUPPORTED : ER_ERR_CUDA, "tq_outlier_decode_kernel: %s",
-                                  orc == kNotBuilt ? "GQA groups 1, 2, 4, 8 are built" : cudaGetErrorString(static_cast<cudaError_t>(orc)));
+    // balanced / aggressive rows (the general form of gqa_attention_turboquant_decode, Shaders/TurboQuant.metal:1794-2001) and
+    // 2-bit TurboQuant rows (no tensor-core policy is built for them) run on the SIMT kernel
+    if (kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2))) {
+        const int32_t src = simt_attention(kv, kv, lb, le, q, out, num_heads, pending, 1, -1, -1, s, stream);
+        if (src != ER_OK) return src;
         if (advance != 0) {
+            const int pairs = static_cast<int>((le - lb) * kv->cfg.max_batch);
             add_lengths_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(kv->d_lengths, static_cast<int>(lb * kv->cfg.max_batch), pairs, static_cast<int>(advance));
             return check_launch("add_lengths_kernel");
         }
@@ -1392,6 +1432,59 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t lb, uint32_t le, const float*
     s.k_norm_weight = nullptr;
     std::lock_guard<std::mutex> lock(kv->mu);
     return attention_locked(kv, lb, le, q, out, num_heads, pending ? 1 : 0, 0, s, static_cast<cudaStream_t>(stream));
+}
+
+// ---- layers whose keys and values use different row formats: the two sides live in two caches of the same geometry ----
+
+static int32_t check_pair(const er_kv* kk, const er_kv* vv) {
+    if (kk->cfg.max_seq_len != vv->cfg.max_seq_len || kk->cfg.max_batch != vv->cfg.max_batch || kk->cfg.num_kv_heads != vv->cfg.num_kv_heads ||
+        kk->cfg.num_layers != vv->cfg.num_layers || kk->device != vv->device)
+        return fail(ER_ERR_SHAPE, "the key cache and the value cache of a pair must agree in max_seq_len, max_batch, num_kv_heads, num_layers and device");
+    return ER_OK;
+}
+
+int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads,
+                                    uint32_t pending, const er_step_params* sp, void* stream) {
+    if (!key_cache || !value_cache || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rc = check_layers(key_cache, lb, le);
+    if (rc != ER_OK) return rc;
+    if ((rc = check_pair(key_cache, value_cache)) != ER_OK) return rc;
+    er_step_params s;
+    if ((rc = step_defaults(key_cache, sp, s)) != ER_OK) return rc;
+    if ((rc = check_device(key_cache)) != ER_OK) return rc;
+    rc = apply_head_norm(key_cache, 0, &q, static_cast<size_t>(le - lb) * key_cache->cfg.max_batch * num_heads,
+                         static_cast<size_t>(key_cache->cfg.max_batch) * num_heads, s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(key_cache->mu);
+    return simt_attention(key_cache, value_cache, lb, le, q, out, num_heads, pending ? 1 : 0, 1, -1, -1, s, static_cast<cudaStream_t>(stream));
+}
+
+int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer, uint32_t seq, const float* q, float* out,
+                                     uint32_t num_heads, uint32_t seq_len, uint32_t q_offset, const er_step_params* sp, void* stream) {
+    if (!key_cache || !value_cache || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
+    if (layer >= key_cache->cfg.num_layers) return fail(ER_ERR_INVALID_LAYER, "layer %u", layer);
+    if (seq >= key_cache->cfg.max_batch) return fail(ER_ERR_INVALID_ARGUMENT, "sequence %u", seq);
+    if (seq_len == 0) return ER_OK;
+    int32_t rc = check_pair(key_cache, value_cache);
+    if (rc != ER_OK) return rc;
+    er_step_params s;
+    if ((rc = step_defaults(key_cache, sp, s)) != ER_OK) return rc;
+    if ((rc = check_device(key_cache)) != ER_OK) return rc;
+    rc = apply_head_norm(key_cache, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
+                         static_cast<cudaStream_t>(stream));
+    if (rc != ER_OK) return rc;
+    std::lock_guard<std::mutex> lock(key_cache->mu);
+    // query row r sits at position q_offset + r (UINT32_MAX: the chunk's rows are the newest rows) and sees the keys up to it
+    const int q_pos0 = q_offset == UINT32_MAX ? -1 : static_cast<int>(q_offset);
+    if (q_pos0 >= 0) {
+        // rows_per_pair counts back from the cache length: the chunk must end at the newest row
+        if ((rc = pull_lengths(key_cache)) != ER_OK) return rc;
+        const int32_t total = key_cache->h_lengths[static_cast<size_t>(layer) * key_cache->cfg.max_batch + seq];
+        if (static_cast<int64_t>(q_offset) + seq_len != total)
+            return fail(ER_ERR_UNSUPPORTED, "pair prefill: the chunk [%u, %u) must end at the sequence's %d rows", q_offset, q_offset + seq_len, total);
+    }
+    return simt_attention(key_cache, value_cache, layer, layer + 1, q, out, num_heads, 0, static_cast<int>(seq_len), q_pos0, static_cast<int>(seq), s,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
@@ -1552,7 +1645,8 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
     if ((rc = check_device(kv)) != ER_OK) return rc;
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32 || kv->outlier;
+    const bool simt_rows = kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2));
+    const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32 || simt_rows;
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.
     const bool fused = kv->cfg.precision == ER_KV_FLOAT16 && kv->cfg.head_dim == kHeadDim;

@@ -12,9 +12,11 @@
 //   score = <fwd(q), eK> * scale ;  out = inverse( sum_t p_t * eV_t ) / sum_t p_t
 // (the reference keeps the centroid part and the sign part in two accumulators and transforms both back with the same
 // matrix -- its transforms ignore their seeds, TurboQuant.swift:891-921 -- so one accumulator holds their sum).
-// This first version is plain SIMT, one token per warp step: correct and bounded by instruction issue, not by HBM.
+// Decode attention over these rows runs on the backend's SIMT kernel (simt_decode_kernel below: one token per warp step,
+// any row format on either side): correct and bounded by instruction issue, not by HBM.
 #pragma once
 
+#include "q8.cuh"
 #include "turboquant.cuh"
 #include "turboquant_outlier.cuh"
 
@@ -121,44 +123,101 @@ __global__ void __launch_bounds__(kOutlierWarps * 32) tq_outlier_append_kernel(c
     }
 }
 
-// ------------------------------------------------------------------------------------------ decode attention
+// ------------------------------------------------------------------------------------------ decode attention (SIMT, any row format)
 
-struct OutlierDecodeParams {
-    const float* q;               // [layers][batch][num_q_heads][128]
-    const uint8_t* k_base;
-    const uint8_t* v_base;
-    int64_t k_layer_stride_bytes, v_layer_stride_bytes;
-    const int32_t* lengths;
-    int layer_begin, batch, num_q_heads, pending, splits;
-    float scale_log2, rope_scaling, k_res_coef, v_res_coef;
-    int apply_rope;
-    OutlierFormat fmt;
+// Where the K rows or the V rows of an attention call come from: any row format of the backend, read with a lane owning
+// coordinates 4L .. 4L + 3.  The two sides of a call are independent -- they may differ in format and even lie in
+// different caches (layers whose keys and values use different cache types: gqa_attention_q8k_turboquant(_decode),
+// gqa_attention_turboquant_decode_f16v, Shaders/TurboQuant.metal:1651-2399).
+enum RowFormat : int { kRowsF16 = 0, kRowsQ8 = 1, kRowsTurbo = 2, kRowsOutlier = 3 };
+
+struct RowSource {
+    int format;                 // RowFormat
+    const uint8_t* rows;        // first row of layer 0
+    const uint8_t* side;        // q8_0: four fp16 scales per row; TurboQuant fixed presets: one norm per row
+    int64_t layer_stride_bytes, side_layer_stride_bytes;
+    int bits;                   // kRowsTurbo: code width
+    int norm_fp16;              // kRowsTurbo: the stored norm is fp16
+    OutlierFormat ofmt;         // kRowsOutlier
+    float res_coef;             // kRowsOutlier: sqrt(pi/2) * residual scale
     KVAddressing addr;
+};
+
+// The lane's four coordinates of row `slot` of (layer, seq, kv head), scaled by the row's norm / block scale.
+__device__ __forceinline__ void read_row_lane4(const RowSource& s, int layer, int seq, int head, int slot, int lane, float e[4]) {
+    const int64_t ridx = row_index(s.addr, seq, head, slot);
+    const uint8_t* rows = s.rows + static_cast<int64_t>(layer) * s.layer_stride_bytes;
+    if (s.format == kRowsF16) {
+        const uint2 w = *reinterpret_cast<const uint2*>(rows + ridx * kRowBytesF16 + 8 * lane);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+        e[0] = a.x; e[1] = a.y; e[2] = b.x; e[3] = b.y;
+    } else if (s.format == kRowsQ8) {
+        const uint32_t word = reinterpret_cast<const uint32_t*>(rows + ridx * kQ8RowBytes)[q8_word_slot(lane)];
+        const uint8_t* side = s.side + static_cast<int64_t>(layer) * s.side_layer_stride_bytes;
+        const float sc = __half2float(reinterpret_cast<const __half*>(side + ridx * kQ8ScaleBytes)[lane >> 3]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) e[c] = sc * static_cast<float>(static_cast<int8_t>((word >> (8 * c)) & 0xFF));
+    } else if (s.format == kRowsTurbo) {
+        const int words = (kHeadDim * s.bits + 31) / 32;
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(rows + ridx * (words * 4));
+        const uint8_t* side = s.side + static_cast<int64_t>(layer) * s.side_layer_stride_bytes;
+        const float norm = s.norm_fp16 ? __half2float(reinterpret_cast<const __half*>(side)[ridx]) : reinterpret_cast<const float*>(side)[ridx];
+        // 4 * bits <= 16 bits at bit 4 * bits * lane: a piece never leaves the row's words
+        const int off = 4 * s.bits * lane, w0 = off >> 5, sh = off & 31;
+        uint32_t piece = w[w0] >> sh;
+        if (sh + 4 * s.bits > 32) piece |= w[w0 + 1] << (32 - sh);
+        const float* cent = tq_centroids_rt(s.bits);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) e[c] = norm * cent[(piece >> (s.bits * c)) & ((1u << s.bits) - 1u)];
+    } else {
+        tq_outlier_lane_values(reinterpret_cast<const uint32_t*>(rows + ridx * (s.ofmt.row_words * 4)), s.ofmt, lane, s.res_coef, true, e);
+    }
+}
+
+__host__ __device__ inline bool rows_are_rotated(int format) { return format == kRowsTurbo || format == kRowsOutlier; }
+
+struct SimtDecodeParams {
+    const float* q;               // [pairs][rows_per_pair][num_q_heads][128]
+    RowSource k, v;
+    const int32_t* lengths;       // tokens written, [layers][batch] of the KEY side's cache
+    int layer_begin, batch, num_q_heads, pending, splits;
+    int fixed_seq;                // >= 0: every problem is this sequence and pair = layer offset (chunks of one sequence)
+    // rows_per_pair > 1: a chunk of query rows per (layer, sequence); row r sees keys [0, kv_len - (rows_per_pair - 1 - r))
+    // and sits at position q_pos0 + r (q_pos0 < 0: the chunk's last row is the newest token)
+    int rows_per_pair, q_pos0;
+    float scale_log2, rope_scaling;
+    int apply_rope;
     InvFreqTable inv_freq;
-    float* partial;               // [pairs * kv heads][splits][group][132]: max (log2 domain), sum, pad, pad, acc[128]
-    float* out;                   // [pairs][out_heads][128]
+    float* partial;               // [pairs * rows * kv heads][splits][group][132]: max (log2 domain), sum, pad, pad, acc[128]
+    float* out;                   // [pairs][rows][out_heads][128]
     int out_heads_total, out_head_offset;
 };
 
 constexpr int kOutlierDecodeWarps = 8;
 constexpr int kOutlierPartialStride = 132;
 
-// grid (splits, kv heads, (layer, sequence) pairs); every warp walks tokens split_begin + warp, + 8, ...
+// grid (splits, kv heads, (layer, sequence) pairs x query rows); every warp walks tokens split_begin + warp, + 8, ...
+// Scores live in the keys' space (rotated for TurboQuant keys: the query is transformed once), outputs in the values' space
+// (one inverse transform at the end for TurboQuant values).
 template <int GROUP>
-__global__ void __launch_bounds__(kOutlierDecodeWarps * 32) tq_outlier_decode_kernel(const __grid_constant__ OutlierDecodeParams p) {
+__global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(const __grid_constant__ SimtDecodeParams p) {
     __shared__ __align__(16) float s_q[GROUP][kHeadDim];
     __shared__ float s_ml[kOutlierDecodeWarps][GROUP][2];
     __shared__ __align__(16) float s_acc[kOutlierDecodeWarps][GROUP][kHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int split = blockIdx.x, head = blockIdx.y, pair = blockIdx.z;
-    const int hkv = p.addr.num_kv_heads;
-    const int layer = p.layer_begin + pair / p.batch, seq = pair % p.batch;
+    const int split = blockIdx.x, head = blockIdx.y;
+    const int problem = blockIdx.z, pair = problem / p.rows_per_pair, qrow = problem % p.rows_per_pair;
+    const int hkv = p.k.addr.num_kv_heads;
+    const int layer = p.fixed_seq >= 0 ? p.layer_begin + pair : p.layer_begin + pair / p.batch;
+    const int seq = p.fixed_seq >= 0 ? p.fixed_seq : pair % p.batch;
     const int written = p.lengths[layer * p.batch + seq] + p.pending;
-    const int kv_len = written < p.addr.max_seq_len ? written : p.addr.max_seq_len;
-    const uint32_t q_pos = static_cast<uint32_t>(written > 0 ? written - 1 : 0);
-    // ---- the group's query rows: [NeoX RoPE ->] randomizedHadamard, scaled for exp2 ----
+    const int cap = p.k.addr.max_seq_len;
+    const int visible = written - (p.rows_per_pair - 1 - qrow);
+    const int kv_len = visible < 0 ? 0 : (visible < cap ? visible : cap);
+    const uint32_t q_pos = static_cast<uint32_t>(p.q_pos0 >= 0 ? p.q_pos0 + qrow : (visible > 0 ? visible - 1 : 0));
+    // ---- the group's query rows: [NeoX RoPE ->] [randomizedHadamard ->] scaled for exp2 ----
     for (int g = warp; g < GROUP; g += kOutlierDecodeWarps) {
-        const float4 x = *reinterpret_cast<const float4*>(p.q + (static_cast<int64_t>(pair) * p.num_q_heads + head * GROUP + g) * kHeadDim + 4 * lane);
+        const float4 x = *reinterpret_cast<const float4*>(p.q + (static_cast<int64_t>(problem) * p.num_q_heads + head * GROUP + g) * kHeadDim + 4 * lane);
         float a[4] = {x.x, x.y, x.z, x.w};
         if (p.apply_rope) {
 #pragma unroll
@@ -170,7 +229,7 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) tq_outlier_decode_ke
                 else           { rope_rotate(other, a[c], cs, y0, y1); a[c] = y1; }
             }
         }
-        warp_tq_forward(a, lane);
+        if (rows_are_rotated(p.k.format)) warp_tq_forward(a, lane);
         *reinterpret_cast<float4*>(&s_q[g][4 * lane]) = make_float4(a[0] * p.scale_log2, a[1] * p.scale_log2, a[2] * p.scale_log2, a[3] * p.scale_log2);
     }
     __syncthreads();
@@ -182,17 +241,13 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) tq_outlier_decode_ke
     }
     const int per = (kv_len + p.splits - 1) / p.splits;
     const int t_begin = split * per, t_end = min(kv_len, t_begin + per);
-    const uint8_t* kl = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
-    const uint8_t* vl = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
-    const int row_bytes = p.fmt.row_words * 4;
     float m[GROUP], l[GROUP], acc[GROUP][4];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
     for (int t = t_begin + warp; t < t_end; t += kOutlierDecodeWarps) {
-        const int64_t ridx = row_index(p.addr, seq, head, t);
         float ek[4], ev[4];
-        tq_outlier_lane_values(reinterpret_cast<const uint32_t*>(kl + ridx * row_bytes), p.fmt, lane, p.k_res_coef, true, ek);
-        tq_outlier_lane_values(reinterpret_cast<const uint32_t*>(vl + ridx * row_bytes), p.fmt, lane, p.v_res_coef, true, ev);
+        read_row_lane4(p.k, layer, seq, head, t, lane, ek);
+        read_row_lane4(p.v, layer, seq, head, t, lane, ev);
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             float s = fmaf(qr[g][3], ek[3], fmaf(qr[g][2], ek[2], fmaf(qr[g][1], ek[1], qr[g][0] * ek[0])));
@@ -213,7 +268,7 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) tq_outlier_decode_ke
         *reinterpret_cast<float4*>(&s_acc[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
     __syncthreads();
-    const int item = pair * hkv + head;
+    const int item = problem * hkv + head;
     for (int idx = threadIdx.x; idx < GROUP * kHeadDim; idx += kOutlierDecodeWarps * 32) {
         const int g = idx >> 7, d = idx & 127;
         float M = -INFINITY;
@@ -234,13 +289,13 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) tq_outlier_decode_ke
 
 // One warp per (item, head of the group): combine the splits, transform back, normalise, store.
 template <int GROUP>
-__global__ void tq_outlier_merge_kernel(const __grid_constant__ OutlierDecodeParams p, int items) {
+__global__ void simt_decode_merge_kernel(const __grid_constant__ SimtDecodeParams p, int items) {
     const int lane = threadIdx.x & 31;
     const int64_t job = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (job >= static_cast<int64_t>(items) * GROUP) return;
     const int item = static_cast<int>(job / GROUP), g = static_cast<int>(job % GROUP);
-    const int hkv = p.addr.num_kv_heads;
-    const int pair = item / hkv, head = item % hkv;
+    const int hkv = p.k.addr.num_kv_heads;
+    const int problem = item / hkv, head = item % hkv;
     const float* base = p.partial + (static_cast<int64_t>(item) * p.splits * GROUP + g) * kOutlierPartialStride;
     float M = -INFINITY;
     for (int s = 0; s < p.splits; ++s) M = fmaxf(M, base[static_cast<int64_t>(s) * GROUP * kOutlierPartialStride]);
@@ -252,25 +307,26 @@ __global__ void tq_outlier_merge_kernel(const __grid_constant__ OutlierDecodePar
         const float4 v = *reinterpret_cast<const float4*>(ps + 4 + 4 * lane);
         a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]); a[2] = fmaf(v.z, wgt, a[2]); a[3] = fmaf(v.w, wgt, a[3]);
     }
-    warp_tq_inverse(a, lane);
+    if (rows_are_rotated(p.v.format)) warp_tq_inverse(a, lane);
     const float inv = L > 0.f ? 1.f / L : 0.f;   // a sequence without rows: zeros (invSum = 0 rule)
     const int out_heads = p.out_heads_total > 0 ? p.out_heads_total : p.num_q_heads;
-    float* dst = p.out + (static_cast<int64_t>(pair) * out_heads + p.out_head_offset + head * GROUP + g) * kHeadDim;
+    float* dst = p.out + (static_cast<int64_t>(problem) * out_heads + p.out_head_offset + head * GROUP + g) * kHeadDim;
     *reinterpret_cast<float4*>(dst + 4 * lane) = make_float4(a[0] * inv, a[1] * inv, a[2] * inv, a[3] * inv);
 }
 
-inline int launch_outlier_decode(int group, const OutlierDecodeParams& p, int pairs, cudaStream_t stream) {
-    const dim3 grid(static_cast<unsigned>(p.splits), static_cast<unsigned>(p.addr.num_kv_heads), static_cast<unsigned>(pairs));
-    const int items = pairs * p.addr.num_kv_heads;
+inline int launch_simt_decode(int group, const SimtDecodeParams& p, int pairs, cudaStream_t stream) {
+    const int problems = pairs * p.rows_per_pair;
+    const dim3 grid(static_cast<unsigned>(p.splits), static_cast<unsigned>(p.k.addr.num_kv_heads), static_cast<unsigned>(problems));
+    const int items = problems * p.k.addr.num_kv_heads;
     const int merge_blocks = (items * group + 7) / 8;
     switch (group) {
-#define ER_OUTLIER_CASE(G)                                                                      \
-    case G:                                                                                     \
-        tq_outlier_decode_kernel<G><<<grid, kOutlierDecodeWarps * 32, 0, stream>>>(p);          \
-        tq_outlier_merge_kernel<G><<<merge_blocks, 256, 0, stream>>>(p, items);                 \
+#define ER_SIMT_CASE(G)                                                                   \
+    case G:                                                                               \
+        simt_decode_kernel<G><<<grid, kOutlierDecodeWarps * 32, 0, stream>>>(p);          \
+        simt_decode_merge_kernel<G><<<merge_blocks, 256, 0, stream>>>(p, items);          \
         break;
-        ER_OUTLIER_CASE(1) ER_OUTLIER_CASE(2) ER_OUTLIER_CASE(4) ER_OUTLIER_CASE(8)
-#undef ER_OUTLIER_CASE
+        ER_SIMT_CASE(1) ER_SIMT_CASE(2) ER_SIMT_CASE(4) ER_SIMT_CASE(8)
+#undef ER_SIMT_CASE
         default: return kNotBuilt;
     }
     return static_cast<int>(cudaGetLastError());

@@ -270,6 +270,19 @@ class KVCache:
         check(lib().er_kv_attention_prefill(self._h, layer, seq, ptr(q), ptr(out), num_heads, seq_len, off, C.byref(params),
                                             stream_ptr(stream)))
 
+    def attention_decode_with_values_of(self, value_cache, q, out, num_heads, params, pending=0, layer_begin=0, layer_end=None,
+                                        stream=None):
+        """Decode attention with THIS cache's K rows and `value_cache`'s V rows (layers whose keys and values use different
+        row formats; er_kv_attention_decode_pair)."""
+        le = self.num_layers if layer_end is None else layer_end
+        check(lib().er_kv_attention_decode_pair(self._h, value_cache._h, layer_begin, le, ptr(q), ptr(out), num_heads, pending,
+                                                C.byref(params), stream_ptr(stream)))
+
+    def attention_prefill_with_values_of(self, value_cache, layer, seq, q, out, num_heads, seq_len, params, q_offset=None, stream=None):
+        off = 0xFFFFFFFF if q_offset is None else q_offset
+        check(lib().er_kv_attention_prefill_pair(self._h, value_cache._h, layer, seq, ptr(q), ptr(out), num_heads, seq_len, off,
+                                                 C.byref(params), stream_ptr(stream)))
+
     def decode_step(self, q, k, v, out, num_heads, params, layer_begin=0, layer_end=None, stream=None):
         le = self.num_layers if layer_end is None else layer_end
         check(lib().er_kv_decode_step(self._h, layer_begin, le, ptr(q), ptr(k), ptr(v), ptr(out), num_heads,

@@ -8,8 +8,9 @@ mapping with the reference's variable names for callers that want the same knobs
 
 `PolicyKVCache` keeps one `er_kv` cache per distinct (key type, value type) pair of the model's layers and maps every
 layer to (cache, local layer).  Pairs whose two sides belong to different families (q8_0 keys with TurboQuant values,
-TurboQuant keys with dense values, ...) have no attention kernel in this backend yet: creating such a layer raises
-unsupportedStorage and names the layer, so the caller can fall back to a uniform type for it."""
+TurboQuant keys with dense values, ...: the reference's hybrid layers) keep TWO caches of the same geometry, one in the
+keys' format and one in the values' -- each stores both of its slabs, so such layers cost one unused slab per side --
+and run attention through er_kv_attention_decode_pair (the keys' cache supplies K, the values' cache V)."""
 from dataclasses import dataclass
 from typing import Mapping, Optional
 
@@ -180,8 +181,14 @@ def cache_arguments(key_type, value_type):
     return None
 
 
+def _side_arguments(cache_type):
+    """A cache whose rows of BOTH sides use `cache_type` (one side of a mixed-family layer reads only its own slab)."""
+    return cache_arguments(cache_type, cache_type)
+
+
 class PolicyKVCache:
-    """One cache per (key type, value type) pair of a layer stack that follows a TurboQuantLayerContract."""
+    """One cache (or, for mixed-family layers, one pair of caches) per (key type, value type) pair of a layer stack that
+    follows a TurboQuantLayerContract."""
 
     def __init__(self, max_seq_len, num_layers, num_kv_heads, head_dim, contract=None, *, max_batch=1, layout=Layout.head_major,
                  norm_format=NormFormat.float32, page_size=0, num_pages=0):
@@ -191,45 +198,76 @@ class PolicyKVCache:
                             for l in range(num_layers)]
         groups = {}
         for layer, pair in enumerate(self.layer_types):
-            if cache_arguments(*pair) is None:
-                raise EdgeRunnerCUDAError(_lib.ER_ERR_UNSUPPORTED_STORAGE,
-                                          "layer %d: %s keys with %s values (no attention kernel for this pair)" % (layer, pair[0], pair[1]))
             groups.setdefault(pair, []).append(layer)
+
+        def make(precision, extra, count):
+            return KVCache(max_seq_len, count, num_kv_heads, head_dim, precision, max_batch=max_batch, layout=layout,
+                           norm_format=norm_format, page_size=page_size, num_pages=num_pages, **extra)
+
         self._caches, self._slot = {}, {}
         for pair, layers in groups.items():
-            precision, extra = cache_arguments(*pair)
-            self._caches[pair] = KVCache(max_seq_len, len(layers), num_kv_heads, head_dim, precision, max_batch=max_batch, layout=layout,
-                                         norm_format=norm_format, page_size=page_size, num_pages=num_pages, **extra)
+            whole = cache_arguments(*pair)
+            if whole is not None:
+                caches = (make(whole[0], whole[1], len(layers)),)
+            else:
+                caches = tuple(make(*_side_arguments(t), len(layers)) for t in pair)     # (keys' cache, values' cache)
+            self._caches[pair] = caches
             for local, layer in enumerate(layers):
-                self._slot[layer] = (self._caches[pair], local)
+                self._slot[layer] = (caches, local)
 
     def close(self):
-        for c in self._caches.values():
-            c.close()
+        for caches in self._caches.values():
+            for c in caches:
+                c.close()
 
     @property
     def caches(self):
-        """{(key type, value type): KVCache} -- a step runs once per cache, over that cache's layers."""
+        """{(key type, value type): (cache,) or (keys' cache, values' cache)}."""
         return dict(self._caches)
 
     def layers_of(self, pair):
         return [l for l, p in enumerate(self.layer_types) if p == pair]
 
+    def is_mixed(self, layer):
+        return len(self.at(layer)[0]) == 2
+
     def at(self, layer):
-        """(cache, local layer index) of a model layer."""
+        """((cache,) or (keys' cache, values' cache), local layer index) of a model layer."""
         if not 0 <= layer < self.num_layers:
             raise EdgeRunnerCUDAError(_lib.ER_ERR_INVALID_LAYER, "layer %d" % layer)
         return self._slot[layer]
 
+    def write_rows(self, layer, seq, start, count, k, v, params, stream=None):
+        caches, local = self.at(layer)
+        for c in caches:
+            c.write_rows(local, seq, start, count, k, v, params, stream=stream)
+
     def decode_step(self, layer, q, k, v, out, num_heads, params, stream=None):
         """One layer's step (the per-layer dispatch of fusedDecodePass): q [batch, heads, 128], k / v [batch, kv heads, 128]."""
-        cache, local = self.at(layer)
-        cache.decode_step(q, k, v, out, num_heads, params, layer_begin=local, layer_end=local + 1, stream=stream)
+        caches, local = self.at(layer)
+        if len(caches) == 1:
+            caches[0].decode_step(q, k, v, out, num_heads, params, layer_begin=local, layer_end=local + 1, stream=stream)
+            return
+        kc, vc = caches
+        for c in caches:           # each side quantises the step's rows into its own format
+            c.append_rope_kv(k, v, params, layer_begin=local, layer_end=local + 1, stream=stream)
+        kc.attention_decode_with_values_of(vc, q, out, num_heads, params, pending=1, layer_begin=local, layer_end=local + 1, stream=stream)
+        for c in caches:
+            c.advance(1, layer_begin=local, layer_end=local + 1, stream=stream)
+
+    def attention_prefill(self, layer, seq, q, out, num_heads, seq_len, params, q_offset=None, stream=None):
+        caches, local = self.at(layer)
+        if len(caches) == 1:
+            caches[0].attention_prefill(local, seq, q, out, num_heads, seq_len, params, q_offset=q_offset, stream=stream)
+        else:
+            caches[0].attention_prefill_with_values_of(caches[1], local, seq, q, out, num_heads, seq_len, params, q_offset=q_offset, stream=stream)
 
     def set_block_table(self, seq, pages):
-        for c in self._caches.values():
-            c.set_block_table(seq, pages)
+        for caches in self._caches.values():
+            for c in caches:
+                c.set_block_table(seq, pages)
 
     def reset(self):
-        for c in self._caches.values():
-            c.reset()
+        for caches in self._caches.values():
+            for c in caches:
+                c.reset()

@@ -264,6 +264,17 @@ public:
         check(er_kv_attention_prefill(handle_, static_cast<uint32_t>(layer), seq, q, out, static_cast<uint32_t>(numHeads),
                                       static_cast<uint32_t>(seqLen), static_cast<uint32_t>(qOffset), &params, stream));
     }
+    // Layers whose keys and values use different row formats: attention with THIS cache's K rows and `values`' V rows.
+    void attentionDecodeWithValuesOf(const KVCache& values, int layerBegin, int layerEnd, const float* q, float* out, int numHeads,
+                                     int pending, const er_step_params& params, void* stream = nullptr) {
+        check(er_kv_attention_decode_pair(handle_, values.handle_, static_cast<uint32_t>(layerBegin), static_cast<uint32_t>(layerEnd), q, out,
+                                          static_cast<uint32_t>(numHeads), static_cast<uint32_t>(pending), &params, stream));
+    }
+    void attentionPrefillWithValuesOf(const KVCache& values, int layer, uint32_t seq, const float* q, float* out, int numHeads, int seqLen,
+                                      int qOffset, const er_step_params& params, void* stream = nullptr) {
+        check(er_kv_attention_prefill_pair(handle_, values.handle_, static_cast<uint32_t>(layer), seq, q, out, static_cast<uint32_t>(numHeads),
+                                           static_cast<uint32_t>(seqLen), static_cast<uint32_t>(qOffset), &params, stream));
+    }
     int64_t totalWritten(int layer, uint32_t seq = 0) const { return er_kv_total_written(handle_, static_cast<uint32_t>(layer), seq); }
     er_kv_config config() const {
         er_kv_config c{};

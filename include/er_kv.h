@@ -355,6 +355,18 @@ int32_t er_kv_attention_decode(er_kv* kv, uint32_t layer_begin, uint32_t layer_e
 int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
                                 uint32_t seq_len, uint32_t q_offset, const er_step_params* params, void* stream);
 
+/* Layers whose keys and values use DIFFERENT row formats (the reference's hybrid layers: q8_0 keys with TurboQuant values,
+ * TurboQuant keys with float16 values, ...: gqa_attention_q8k_turboquant(_decode), gqa_attention_turboquant_decode_f16v,
+ * Shaders/TurboQuant.metal:1651-2399; chosen per layer by TurboQuantV2Contract, TurboQuant.swift:432-488).  The two sides live
+ * in two caches of the same geometry (max_seq_len, max_batch, num_kv_heads, num_layers): append the step's rows to both
+ * (er_kv_append_rope_kv), run attention with the K rows of `key_cache` and the V rows of `value_cache`, advance both.  Any
+ * pair of float16 (head-major / paged), q8_0 and TurboQuant caches (all presets) is accepted; positions are the key cache's.
+ * A plain SIMT kernel serves these calls (correct, not tuned).  The prefill form takes a chunk that ends at the newest row. */
+int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer_begin, uint32_t layer_end, const float* q,
+                                    float* out, uint32_t num_heads, uint32_t pending, const er_step_params* params, void* stream);
+int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer, uint32_t seq, const float* q, float* out,
+                                     uint32_t num_heads, uint32_t seq_len, uint32_t q_offset, const er_step_params* params, void* stream);
+
 /* Whole decode step for layers [layer_begin, layer_end): append + attention + advance of the write position by
  * one, enqueued back to back (the body of fusedDecodePass steps 2-5, LlamaLanguageModel.swift:3649-3941).
  * Positions live on the device, so a captured CUDA graph of this call can be replayed step after step. */

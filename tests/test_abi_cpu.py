@@ -197,11 +197,10 @@ def test_layer_contract_matches_the_reference_tests():
     assert C_.residual_scale("balanced") == 0.0
 
 
-def test_policy_cache_refuses_mixed_family_layers_without_a_device():
+def test_policy_cache_pairs_for_mixed_family_layers():
     import edgerunner_b200 as er
     from edgerunner_b200.layer_contract import cache_arguments
     assert cache_arguments("turbo4", "turbo3")[0] == er.Precision.turboquantV2
-    assert cache_arguments("q8_0", "turbo3") is None and cache_arguments("turbo3", "dense") is None
-    with pytest.raises(er.EdgeRunnerCUDAError) as e:       # layer 0: q8_0 keys with turbo3 values
-        er.PolicyKVCache(64, 4, 2, 128, er.TurboQuantLayerContract(early_q8_key_layers=1))
-    assert e.value.name == "unsupportedStorage" and "layer 0" in str(e.value)
+    assert cache_arguments("q8_0", "turbo3") is None and cache_arguments("turbo3", "dense") is None      # two caches, one per side
+    c = er.TurboQuantLayerContract(early_q8_key_layers=1)
+    assert (c.key_cache_type_for(0, 4), c.value_cache_type_for(0, 4)) == ("q8_0", "turbo3")

@@ -388,7 +388,7 @@ def test_policy_cache_follows_the_layer_contract(er, torch):
         q = torch.as_tensor(rng.standard_normal((1, Hq, D), dtype=np.float32)).cuda()
         k = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
         v = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
-        cache, local = pc.at(layer)
+        (cache,), local = pc.at(layer)
         cache.write_rows(local, 0, 0, ctx, K, V, sp)
         precision, extra = cache_arguments(*pc.layer_types[layer])
         ref = er.KVCache(128, 1, Hkv, D, precision, **extra)
@@ -400,4 +400,69 @@ def test_policy_cache_follows_the_layer_contract(er, torch):
         assert torch.equal(got, want), layer
         assert cache.total_written(local, 0) == ctx + 1
         ref.close()
+    pc.close()
+
+
+def _decoded_rows(cache, layer, which, np_):
+    """A cache's K (which = 0) or V (1) rows of sequence 0 as float32 [tokens, kv heads, 128], through its own decoded retrieve."""
+    if cache.precision.name == "float16":
+        return cache.retrieve(layer, np_.float16)[which].astype(np_.float32).reshape(-1, cache.num_kv_heads, 128)
+    if cache.precision.name == "q8_0":
+        return np_.asarray(cache.retrieve_decoded_q8_0(layer)[which]).reshape(-1, cache.num_kv_heads, 128)
+    return np_.asarray(cache.retrieve_decoded_turboquant(layer)[which]).reshape(-1, cache.num_kv_heads, 128)
+
+
+@pytest.mark.parametrize("contract_kw,layer_pair", [
+    (dict(early_q8_key_layers=2), ("q8_0", "turbo3")),                       # gqa_attention_q8k_turboquant(_decode)
+    (dict(key_type="turbo4", value_cache_type="dense"), ("turbo4", "dense")),  # gqa_attention_turboquant_decode_f16v
+    (dict(key_cache_type="dense", value_type="turbo4", adaptive_mode=0), ("dense", "turbo4")),
+    (dict(key_type="turbo3", value_cache_type="q8_0"), ("turbo3", "q8_0")),
+])
+def test_mixed_family_layers_through_pair_caches(er, torch, oracle, contract_kw, layer_pair):
+    """Layers whose keys and values use different cache types (the reference's hybrid layers, chosen per layer by
+    TurboQuantV2Contract): the two sides live in two caches; decode steps and a prefill chunk through PolicyKVCache equal plain
+    fp32 attention over the rows each side decodes to (the transforms are orthonormal, so scores in the keys' rotated space and
+    outputs transformed back from the values' space are attention over the decoded rows)."""
+    L, Hq, Hkv, D, ctx, steps = 3, 8, 2, 128, 75, 2
+    theta = 1e6
+    pc = er.PolicyKVCache(128, L, Hkv, D, er.TurboQuantLayerContract(**contract_kw))
+    assert pc.layer_types[0] == layer_pair and pc.is_mixed(0)
+    (kc, vc), local = pc.at(0)
+    rng = np.random.Generator(np.random.PCG64(31))
+    sp = er.step_params(rope_theta=theta)
+    K = torch.as_tensor(rng.standard_normal((ctx, Hkv, D), dtype=np.float32).astype(np.float16).astype(np.float32)).cuda()
+    V = torch.as_tensor(rng.standard_normal((ctx, Hkv, D), dtype=np.float32).astype(np.float16).astype(np.float32)).cuda()
+    pc.write_rows(0, 0, 0, ctx, K, V, sp)
+    worst = 0.0
+    for s_ in range(steps):
+        q = rng.standard_normal((1, Hq, D), dtype=np.float32)
+        k = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
+        v = torch.as_tensor(rng.standard_normal((1, Hkv, D), dtype=np.float32)).cuda()
+        out = torch.full((1, Hq, D), float("nan"), device="cuda")
+        pc.decode_step(0, torch.as_tensor(q).cuda(), k, v, out, Hq, sp)
+        torch.cuda.synchronize()
+        n = ctx + s_ + 1
+        assert kc.total_written(local, 0) == n and vc.total_written(local, 0) == n
+        Kd, Vd = _decoded_rows(kc, local, 0, np), _decoded_rows(vc, local, 1, np)
+        assert Kd.shape[0] == n and Vd.shape[0] == n
+        qr = oracle.rope_neox(q, n - 1, theta)
+        want = oracle.gqa_f32(qr, Kd, Vd, causal=False)[0]
+        got = out.cpu().numpy()[0]
+        floor = 1e-3 * np.abs(want).max()
+        worst = max(worst, float(np.max(np.abs(got - want) / np.maximum(np.abs(want), floor))))
+    # a chunk of 16 query rows at the end of the sequence
+    S, n = 16, ctx + steps
+    qc = rng.standard_normal((S, Hq, D), dtype=np.float32)
+    outp = torch.full((S, Hq, D), float("nan"), device="cuda")
+    pc.attention_prefill(0, 0, torch.as_tensor(qc).cuda(), outp, Hq, S, sp, q_offset=n - S)
+    torch.cuda.synchronize()
+    gp = outp.cpu().numpy()
+    for r in range(S):
+        qr = oracle.rope_neox(qc[r][None], n - S + r, theta)
+        want = oracle.gqa_f32(qr, Kd[:n - S + r + 1], Vd[:n - S + r + 1], causal=False)[0]
+        floor = 1e-3 * np.abs(want).max()
+        worst = max(worst, float(np.max(np.abs(gp[r] - want) / np.maximum(np.abs(want), floor))))
+    print("%s keys / %s values: worst element-wise relative error %.2e" % (layer_pair[0], layer_pair[1], worst))
+    assert worst < 2e-3
+    assert kc.device_status() == 0 and vc.device_status() == 0
     pc.close()

@@ -698,7 +698,7 @@ def test_outlier_preset_caches(er, oracle, torch, preset, Hq, Hkv, layout, scale
     assert wp < TOL, wp
 
 
-@pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4)])
+@pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4), (4, 2), (2, 3), (2, 2)])      # 2-bit sides: the SIMT kernel
 def test_turboquant_decode_presets(er, oracle, torch, kbits, vbits):
     w = _run_turbo_config(er, oracle, torch, L=2, B=1, Hq=16, Hkv=8, ctx=333, steps=2, seed=40 + kbits * 4 + vbits, kbits=kbits,
                           vbits=vbits, norm_format=er.NormFormat.float32, layout=er.Layout.head_major)
