@@ -1247,7 +1247,6 @@ static int32_t row_source(const er_kv* kv, bool is_value, RowSource& s) {
 static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
                               int rows_per_pair, int q_pos0, int fixed_seq, const er_step_params& s, cudaStream_t stream) {
     if (num_heads == 0 || num_heads % kk->cfg.num_kv_heads != 0) return fail(ER_ERR_SHAPE, "num_heads %u not divisible by num_kv_heads %u", num_heads, kk->cfg.num_kv_heads);
-    if (s.sliding_window > 0) return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches on the flash-decode kernels");
     const int group = static_cast<int>(num_heads / kk->cfg.num_kv_heads);
     const int pairs = fixed_seq >= 0 ? static_cast<int>(le - lb) : static_cast<int>((le - lb) * kk->cfg.max_batch);
     const int64_t problems = static_cast<int64_t>(pairs) * rows_per_pair;
@@ -1274,6 +1273,7 @@ static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, co
     op.lengths = kk->d_lengths; op.layer_begin = static_cast<int>(lb); op.batch = static_cast<int>(kk->cfg.max_batch);
     op.num_q_heads = static_cast<int>(num_heads); op.pending = static_cast<int>(pending); op.splits = splits;
     op.fixed_seq = fixed_seq; op.rows_per_pair = rows_per_pair; op.q_pos0 = q_pos0;
+    op.window = static_cast<int>(std::min<uint32_t>(s.sliding_window, 0x7fffffffu));
     op.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     op.apply_rope = s.apply_rope ? 1 : 0; op.rope_scaling = s.rope_scaling;
     if (op.apply_rope) op.inv_freq = kk->freq(s.rope_theta);
@@ -1325,12 +1325,13 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         }
         return ER_OK;
     }
-    if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
-        return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
     // balanced / aggressive rows (the general form of gqa_attention_turboquant_decode, Shaders/TurboQuant.metal:1794-2001) and
-    // 2-bit TurboQuant rows (no tensor-core policy is built for them) run on the SIMT kernel
-    if (kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2))) {
+    // 2-bit TurboQuant rows run on the SIMT kernel
+    // (no tensor-core policy is built for them), and sliding windows over q8_0 / TurboQuant rows (a window start that is not a
+    // multiple of 8 tokens breaks the 16-byte alignment the bulk copies of the side arrays need)
+    if (kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
+        (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)) {
         const int32_t src = simt_attention(kv, kv, lb, le, q, out, num_heads, pending, 1, -1, -1, s, stream);
         if (src != ER_OK) return src;
         if (advance != 0) {
@@ -1499,13 +1500,23 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
     er_step_params s;
     int32_t rc = step_defaults(kv, sp, s);
     if (rc != ER_OK) return rc;
-    if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)
-        return fail(ER_ERR_UNSUPPORTED, "sliding_window is built for float16 caches (the reference's windowed kernel reads fp16 rows)");
     if ((rc = check_device(kv)) != ER_OK) return rc;
     rc = apply_head_norm(kv, 0, &q, static_cast<size_t>(seq_len) * num_heads, static_cast<size_t>(seq_len) * num_heads, s.q_norm_weight, layer, s,
                          static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(kv->mu);
+    if (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16) {
+        // windowed chunks over q8_0 / TurboQuant rows: the SIMT kernel, a problem per query row (the chunk ends at the newest row)
+        const int q_pos0 = q_offset == UINT32_MAX ? -1 : static_cast<int>(q_offset);
+        if (q_pos0 >= 0) {
+            if ((rc = pull_lengths(kv)) != ER_OK) return rc;
+            const int32_t total = kv->h_lengths[static_cast<size_t>(layer) * kv->cfg.max_batch + seq];
+            if (static_cast<int64_t>(q_offset) + seq_len != total)
+                return fail(ER_ERR_UNSUPPORTED, "windowed prefill on this cache: the chunk [%u, %u) must end at the sequence's %d rows", q_offset, q_offset + seq_len, total);
+        }
+        return simt_attention(kv, kv, layer, layer + 1, q, out, num_heads, 0, static_cast<int>(seq_len), q_pos0, static_cast<int>(seq), s,
+                              static_cast<cudaStream_t>(stream));
+    }
     PrefillParams pp{};
     pp.q = q; pp.out = out;
     pp.k_layer = kv->k_slab + layer * kv->k_layer_stride;
@@ -1645,7 +1656,8 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
     if ((rc = check_device(kv)) != ER_OK) return rc;
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    const bool simt_rows = kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2));
+    const bool simt_rows = kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
+                           (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16 && kv->cfg.precision != ER_KV_FLOAT32);
     const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32 || simt_rows;
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are
     // quantised by the append kernel first.

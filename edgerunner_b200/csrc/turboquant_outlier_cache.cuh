@@ -185,6 +185,7 @@ struct SimtDecodeParams {
     // rows_per_pair > 1: a chunk of query rows per (layer, sequence); row r sees keys [0, kv_len - (rows_per_pair - 1 - r))
     // and sits at position q_pos0 + r (q_pos0 < 0: the chunk's last row is the newest token)
     int rows_per_pair, q_pos0;
+    int window;                   // > 0: a query row sees only the newest `window` of its visible rows (sliding-window layers)
     float scale_log2, rope_scaling;
     int apply_rope;
     InvFreqTable inv_freq;
@@ -239,12 +240,16 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(c
         const float4 t = *reinterpret_cast<const float4*>(&s_q[g][4 * lane]);
         qr[g][0] = t.x; qr[g][1] = t.y; qr[g][2] = t.z; qr[g][3] = t.w;
     }
-    const int per = (kv_len + p.splits - 1) / p.splits;
-    const int t_begin = split * per, t_end = min(kv_len, t_begin + per);
+    // the rows visited: logical positions [visible - count, visible), i.e. ring slots position % capacity
+    const int count = p.window > 0 && p.window < kv_len ? p.window : kv_len;
+    const int first_pos = (visible > 0 ? visible : 0) - count;
+    const int per = (count + p.splits - 1) / p.splits;
+    const int t_begin = split * per, t_end = min(count, t_begin + per);
     float m[GROUP], l[GROUP], acc[GROUP][4];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
-    for (int t = t_begin + warp; t < t_end; t += kOutlierDecodeWarps) {
+    for (int i = t_begin + warp; i < t_end; i += kOutlierDecodeWarps) {
+        const int t = (first_pos + i) % cap;
         float ek[4], ev[4];
         read_row_lane4(p.k, layer, seq, head, t, lane, ek);
         read_row_lane4(p.v, layer, seq, head, t, lane, ev);

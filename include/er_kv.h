@@ -176,7 +176,8 @@ typedef struct {
      * gemma4_decode_gqa_f16kv_windowed, Shaders/Gemma4Decode.metal:236-283): > 0 -> a decode call attends to the newest
      * min(sliding_window, rows in the ring) rows of each sequence, wherever they sit in the ring; 0 = every row held.
      * er_kv_attention_prefill applies the same rule per query row (row at position P sees keys P - sliding_window + 1 .. P).
-     * float16 caches only (ER_ERR_UNSUPPORTED for the other precisions). */
+     * Every cache format but float32; q8_0 / TurboQuant caches run windowed calls on the SIMT kernel, and their windowed prefill
+     * chunks must end at the sequence's newest row. */
     uint32_t sliding_window;
     uint32_t reserved;
 } er_step_params;

@@ -1301,17 +1301,67 @@ def test_sliding_window_decode(er, oracle, torch, layout, page_size, T, window, 
         assert np.array_equal(gv.view(np.uint16).reshape(T, Hkv, D), vc[b][order])
 
 
-def test_sliding_window_unsupported_combinations(er, torch):
-    D, Hq, Hkv = 128, 8, 4
-    sp = er.step_params(sliding_window=8)
-    z = lambda *s: torch.zeros(s, dtype=torch.float32, device="cuda")
-    for prec, kw in ((er.Precision.q8_0, {}), (er.Precision.turboquantV2, dict(key_type=4, value_type=3))):
-        cache = er.KVCache(32, 1, Hkv, D, prec, **kw)
-        with pytest.raises(er.EdgeRunnerCUDAError):
-            cache.decode_step(z(1, 1, Hq, D), z(1, 1, Hkv, D), z(1, 1, Hkv, D), z(1, 1, Hq, D), Hq, sp)
-        cache.write_rows(0, 0, 0, 4, z(4, Hkv, D), z(4, Hkv, D), er.step_params())
-        with pytest.raises(er.EdgeRunnerCUDAError):
-            cache.attention_prefill(0, 0, z(4, Hq, D), z(4, Hq, D), Hq, 4, sp)
+@pytest.mark.parametrize("precision,kw", [("q8_0", {}), ("turboquantV2", dict(key_type=4, value_type=3)), ("turboQuantBalanced", {})])
+def test_sliding_window_on_compressed_caches(er, oracle, torch, precision, kw):
+    """er_step_params.sliding_window on q8_0 / TurboQuant caches (decode steps over a wrapping ring, and a windowed chunk):
+    each query row attends to the newest min(window, rows held) rows.  Checked against fp32 attention over the rows the
+    cache decodes to (retrieve_decoded_*: logical order)."""
+    D, Hq, Hkv, T, window, theta = 128, 8, 2, 48, 20, 1e6
+    cache = er.KVCache(T, 1, Hkv, D, getattr(er.Precision, precision), **kw)
+    sp = er.step_params(rope_theta=theta, sliding_window=window)
+    rng = rng_for(515)
+    ctx = 40
+    cache.write_rows(0, 0, 0, ctx, dev(torch, normal_f16(rng, (ctx, Hkv, D))), dev(torch, normal_f16(rng, (ctx, Hkv, D))), er.step_params(rope_theta=theta))
+
+    preset = {"turboQuantBalanced": "balanced"}.get(precision)
+
+    def decoded():
+        if preset:      # decoded key rows of these presets carry the residual term (approximateDecode's default weight): use the stored rows
+            kr, vr = cache.retrieve_turboquant_runtime_rows(0)
+            return kr, vr
+        k, v = cache.retrieve_decoded_q8_0(0) if precision == "q8_0" else cache.retrieve_decoded_turboquant(0)
+        return np.asarray(k).reshape(-1, Hkv, D), np.asarray(v).reshape(-1, Hkv, D)
+
+    def held_rows(rows):
+        return rows[0].shape[0] // Hkv if preset else rows.shape[0]
+
+    def reference(qr, Kd, Vd, lo, hi):
+        """Attention of the rotated query over logical rows [lo, hi)."""
+        if preset:
+            cut = lambda rows: tuple(a[lo * Hkv:hi * Hkv] for a in rows)
+            return oracle.tq_attention_decode_preset(qr[0], cut(Kd), cut(Vd), preset, Hkv, hi - lo, threads=4)
+        return oracle.gqa_f32(qr, Kd[lo:hi], Vd[lo:hi], causal=False)[0]
+
+    worst = 0.0
+    for s_ in range(14):                                   # the ring (48 slots) wraps after 8 steps
+        q, k, v = normal_f16(rng, (1, 1, Hq, D)), normal_f16(rng, (1, 1, Hkv, D)), normal_f16(rng, (1, 1, Hkv, D))
+        out = torch.full((1, 1, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+        cache.decode_step(dev(torch, q), dev(torch, k), dev(torch, v), out, Hq, sp)
+        torch.cuda.synchronize()
+        Kd, Vd = decoded()                                  # logical order: the newest rows last
+        held = held_rows(Kd)
+        n = min(window, held)
+        qr = oracle.rope_neox(q[0], ctx + s_, theta)
+        want = reference(qr, Kd, Vd, held - n, held)
+        worst = max(worst, max_rel_err(out.cpu().numpy()[0, 0], want))
+    assert cache.total_written(0, 0) == ctx + 14
+    # a windowed chunk: the 12 newest rows as queries
+    S, total = 12, ctx + 14
+    qc = normal_f16(rng, (S, Hq, D))
+    outp = torch.full((S, Hq, D), float("nan"), dtype=torch.float32, device="cuda")
+    cache.attention_prefill(0, 0, dev(torch, qc), outp, Hq, S, sp)
+    torch.cuda.synchronize()
+    Kd, Vd = decoded()
+    held = held_rows(Kd)
+    for r in range(S):
+        end = held - (S - 1 - r)                           # rows visible to query row r
+        n = min(window, end)
+        qr = oracle.rope_neox(qc[r][None], total - S + r, theta)
+        want = reference(qr, Kd, Vd, end - n, end)
+        worst = max(worst, max_rel_err(outp.cpu().numpy()[r], want))
+    print("%s rows, sliding window %d: worst element-wise relative error %.2e" % (precision, window, worst))
+    assert worst < TOL
+    assert cache.device_status() == 0
 
 
 @pytest.mark.parametrize("layout,page_size,Hq,Hkv,ctx,S,window", [
