@@ -175,7 +175,8 @@ struct er_kv {
     bool q8 = false;              // q8_0 rows: int8 part in the K / V slabs, four fp16 scales per row in the side slabs
     bool outlier = false;         // balanced / aggressive TurboQuant rows: codes + mask + signs + two norms in one block per row
     OutlierFormat ofmt{};
-    float* d_outlier_partial = nullptr;   // split partials of the outlier decode kernel
+    float* d_outlier_partial = nullptr;   // split partials of the SIMT decode kernel
+    float* d_prefill_partial = nullptr;   // partial rows of the tcgen05 prefill kernel's split tail tiles
     size_t outlier_partial_floats = 0;
     uint8_t* k_slab = nullptr;
     uint8_t* v_slab = nullptr;
@@ -547,7 +548,7 @@ void er_kv_destroy(er_kv* kv) {
     cudaFree(kv->k_slab); cudaFree(kv->v_slab); cudaFree(kv->kn_slab); cudaFree(kv->vn_slab);
     cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
     cudaFree(kv->d_head_norm[0]); cudaFree(kv->d_head_norm[1]);
-    cudaFree(kv->d_stage); cudaFree(kv->d_outlier_partial);
+    cudaFree(kv->d_stage); cudaFree(kv->d_outlier_partial); cudaFree(kv->d_prefill_partial);
     if (kv->h_status) cudaFreeHost(kv->h_status);
     cudaGetLastError();
     delete kv;
@@ -1613,6 +1614,15 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
         pp.v_lo_layer = reinterpret_cast<const uint8_t*>(evl);
         pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
         pp.seq = 0;
+    }
+    {   // scratch that lets the tcgen05 kernel cut the tail of its grid along the keys
+        const size_t want = prefill_split_partial_floats(kv->num_sms);
+        if (kv->d_prefill_partial == nullptr && cudaMalloc(&kv->d_prefill_partial, want * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            kv->d_prefill_partial = nullptr;     // the kernel runs unsplit
+        }
+        pp.split_partial = kv->d_prefill_partial;
+        pp.split_partial_floats = kv->d_prefill_partial ? want : 0;
     }
     pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
     pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);

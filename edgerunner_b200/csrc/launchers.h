@@ -30,6 +30,8 @@ int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cuda
 // behind p.k_layer; status: device word that receives kStatusTimeout if a bounded wait gives up.  kNotBuilt when the
 // shape or the layout is not covered (the caller then uses launch_prefill_f16).
 int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream);
+// Floats of scratch (PrefillParams::split_partial) that let the tcgen05 kernel cut the tail of its grid along the keys.
+size_t prefill_split_partial_floats(int num_sms);
 
 // One query token against ring rows (start + i) % capacity, i < count, of token-major fp16 K/V [capacity][kv heads][head_dim];
 // any even head_dim <= 512, any GQA group (decode_generic.cu).  scratch: nsplit x heads x (head_dim + 2) floats at most

@@ -47,6 +47,13 @@ struct PrefillParams {
     float rope_scaling;
     int apply_rope;          // NeoX-rotate Q at position q_offset + row
     InvFreqTable inv_freq;
+    // tcgen05 kernel only: CTA tiles (query tile x kv head) with linear index >= split_from are each run by split_parts CTAs
+    // that share the tile's key range and leave (max, sum, unnormalised row) partials in split_partial
+    // [tile - split_from][part][128 rows][132]; a merge launch combines them.  The launcher fills these in (the tail of the grid
+    // that would occupy only part of the SMs is cut along the keys); split_partial == nullptr turns it off.
+    float* split_partial;
+    size_t split_partial_floats;
+    int split_from, split_parts;
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {

@@ -2,6 +2,8 @@
 // prefill_umma_kernel (GQA groups 1, 2, 4, 8; optional second K operand).
 #include "prefill_umma.cuh"
 
+#include <algorithm>
+
 #include "launchers.h"
 #include "tmap.h"
 
@@ -47,8 +49,28 @@ int um_launch(const UmmaPrefillParams& up, int num_kv_heads, cudaStream_t stream
         configured_device = device;
     }
     constexpr int rows_per_cta = kUmRows / GROUP;
-    dim3 grid((up.base.seq_len + rows_per_cta - 1) / rows_per_cta, num_kv_heads);
-    prefill_umma_kernel<GROUP, KSPLIT><<<grid, kUmThreads, kSmem, stream>>>(up);
+    const int tiles = ((up.base.seq_len + rows_per_cta - 1) / rows_per_cta) * num_kv_heads;
+    // One CTA per SM at a time: a grid of `tiles` equal CTAs runs in ceil(tiles / SMs) rounds, the last one on `rest` SMs only.
+    // Those last tiles are cut along the keys into `parts` CTAs each (their partial rows merged by a second launch), so the
+    // tail round takes 1 / parts of a tile's time: 512 tiles on 148 SMs = 3 rounds + 68 tiles x 2 halves instead of 4 rounds.
+    UmmaPrefillParams launch = up;
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    int rest = sms > 0 ? tiles % sms : 0, parts = 1;
+    if (launch.base.split_partial != nullptr && rest > 0) {
+        parts = std::min(4, sms / rest);
+        while (parts > 1 && static_cast<size_t>(rest) * parts * kUmRows * kUmPartialStride > launch.base.split_partial_floats) --parts;
+    }
+    if (parts > 1) {
+        launch.base.split_from = tiles - rest;
+        launch.base.split_parts = parts;
+    } else {
+        launch.base.split_partial = nullptr;
+        rest = 0;
+    }
+    const int ctas = tiles - rest + rest * parts;
+    prefill_umma_kernel<GROUP, KSPLIT><<<ctas, kUmThreads, kSmem, stream>>>(launch);
+    if (parts > 1) prefill_umma_merge_kernel<GROUP><<<(rest * kUmRows + 7) / 8, 256, 0, stream>>>(launch.base, rest);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -57,6 +79,11 @@ int um_launch_group(const UmmaPrefillParams& up, int num_kv_heads, cudaStream_t 
     return up.base.k_lo_layer != nullptr ? um_launch<GROUP, true>(up, num_kv_heads, stream) : um_launch<GROUP, false>(up, num_kv_heads, stream);
 }
 }  // namespace
+
+size_t prefill_split_partial_floats(int num_sms) {
+    // at most (SMs - 1) tail tiles x parts <= SMs CTAs of partial rows
+    return static_cast<size_t>(std::max(num_sms, 1)) * kUmRows * kUmPartialStride;
+}
 
 int launch_prefill_umma(int group, const PrefillParams& p, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream) {
     if (status == nullptr) return kNotBuilt;

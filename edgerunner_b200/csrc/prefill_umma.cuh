@@ -38,6 +38,7 @@
 namespace er {
 
 constexpr int kUmRows = 128;          // M rows per CTA
+constexpr int kUmPartialStride = 132; // floats per row of a split tile's partial: max, sum, pad, pad, 128 columns
 __host__ __device__ constexpr int um_tile(bool ksplit) { return ksplit ? 64 : 128; }   // tokens per K/V tile
 constexpr int kUmThreads = 352;
 __host__ __device__ constexpr int um_kv_region(bool ksplit) { return um_tile(ksplit) * 128; }   // tile tokens x 64 halves
@@ -181,9 +182,18 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + kNumBars) + 1;
     float* xchg = reinterpret_cast<float*>(sgen + kStages * kStageBytes + 256);   // maxima [2 tile parities][2 halves][128 rows], then denominators [2][128]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kv_head = blockIdx.y;
     constexpr int kQRowsPerCta = kUmRows / GROUP;
-    const int q0 = blockIdx.x * kQRowsPerCta;
+    // linear CTA index -> (tile = query tile x kv head, part of the tile's key range)
+    int tile_id = static_cast<int>(blockIdx.x), part = 0, nparts = 1;
+    if (p.split_partial != nullptr && tile_id >= p.split_from) {
+        const int r = tile_id - p.split_from;
+        tile_id = p.split_from + r / p.split_parts;
+        part = r % p.split_parts;
+        nparts = p.split_parts;
+    }
+    const int q_tiles = (p.seq_len + kQRowsPerCta - 1) / kQRowsPerCta;
+    const int kv_head = tile_id / q_tiles;
+    const int q0 = (tile_id % q_tiles) * kQRowsPerCta;
 
     int kv_len = p.kv_len;
     if (p.kv_len_ptr != nullptr) {
@@ -193,7 +203,13 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     const int q_offset = p.q_offset_from_end ? kv_len - p.seq_len : p.q_offset;
     const int q_last = min(q0 + kQRowsPerCta, p.seq_len) - 1;
     const int kv_hi = p.causal ? min(kv_len, q_last + q_offset + 1) : kv_len;
-    const int num_tiles = (kv_hi + kUmTile - 1) / kUmTile;
+    const int total_tiles = (kv_hi + kUmTile - 1) / kUmTile;
+    int tile_begin = 0, num_tiles = total_tiles;     // this CTA's key tiles: [tile_begin, tile_begin + num_tiles)
+    if (nparts > 1) {
+        const int per = (total_tiles + nparts - 1) / nparts;
+        tile_begin = min(total_tiles, part * per);
+        num_tiles = min(total_tiles, tile_begin + per) - tile_begin;
+    }
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
@@ -218,7 +234,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 const int st = tile % kStages;
                 if (tile >= kStages) mbar_wait(bar_gen + kBarKvEmpty + st, ((tile / kStages) - 1) & 1, abort_flag, up.status);
                 if (*abort_flag) break;
-                const int t0 = tile * kUmTile;
+                const int t0 = (tile_begin + tile) * kUmTile;
                 const uint32_t stage = sbase + st * kStageBytes;
                 // rows past the cache length are not fetched (their pages may not exist); the consumers clear V there
                 int nbox = 0;
@@ -378,7 +394,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         const uint32_t tmem_o = tmem + kUmColO + 64u * h + lane_base;   // this thread's 64 columns of the O row
         const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
         for (int j = 0; j < num_tiles; ++j) {
-            const int t0 = j * kUmTile + kHalfCols * h, b = j % kUmSBufs, xb = j & 1;
+            const int t0 = (tile_begin + j) * kUmTile + kHalfCols * h, b = j % kUmSBufs, xb = j & 1;
             const uint32_t tmem_s = tmem + kUmColS + static_cast<uint32_t>(kUmTile) * b + lane_base;
             mbar_wait(bar_gen + kBarSFull + b, (j / kUmSBufs) & 1, abort_flag, up.status);
             tc_fence_after();
@@ -432,10 +448,10 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                 }
             }
             // the last tile: V rows past the cache length were not fetched; clear them (0 * stale bits must not be NaN)
-            if (j * kUmTile + kUmTile > kv_len) {
+            if ((tile_begin + j) * kUmTile + kUmTile > kv_len) {
                 mbar_wait(bar_gen + kBarKvFull + j % kStages, (j / kStages) & 1, abort_flag, up.status);
                 uint8_t* vst = sgen + (j % kStages) * kStageBytes + kOffV;
-                const int first = kv_len - j * kUmTile;
+                const int first = kv_len - (tile_begin + j) * kUmTile;
                 for (int idx = tid; idx < (kUmTile - first) * 16; idx += 256) {
                     const int row = first + idx / 16, part = idx % 16;    // 2 regions x 8 chunks
                     *reinterpret_cast<uint4*>(vst + (part >> 3) * kUmKvRegion + row * 128 + (part & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -477,8 +493,12 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         xchg[512 + h * 128 + m] = l_run;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const float lsum = l_run + xchg[512 + (h ^ 1) * 128 + m];
-        const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-        float* dst = p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim + 64 * h;
+        // a part of a split tile leaves (max, sum, unnormalised row) for the merge launch instead of the finished row
+        const bool partial = nparts > 1;
+        const float inv = partial ? 1.f : (lsum > 0.f ? 1.0f / lsum : 0.f);
+        float* prow = partial ? p.split_partial + (static_cast<int64_t>(static_cast<int>(blockIdx.x) - p.split_from) * kUmRows + m) * kUmPartialStride : nullptr;
+        if (partial && h == 0) { prow[0] = m_run; prow[1] = lsum; }
+        float* dst = partial ? prow + 4 + 64 * h : p.out + (static_cast<int64_t>(row_ok ? qi : 0) * p.num_q_heads + head) * kHeadDim + 64 * h;
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 32) {
             if (num_tiles > 0 && !*abort_flag) {   // the last tile's product
@@ -487,7 +507,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
 #pragma unroll
                 for (int c = 0; c < 32; ++c) o_run[c0 + c] += o[c];
             }
-            if (row_ok) {
+            if (row_ok || partial) {
 #pragma unroll
                 for (int c = 0; c < 32; c += 4)
                     *reinterpret_cast<float4*>(dst + c0 + c) =
@@ -498,6 +518,34 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     tc_fence_before();
     __syncthreads();
     if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+
+// Combines the parts of the split tiles: one warp per (split tile, M row), a lane per 4 dims.
+template <int GROUP>
+__global__ void prefill_umma_merge_kernel(const __grid_constant__ PrefillParams p, int tiles) {
+    const int lane = threadIdx.x & 31;
+    const int64_t job = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (job >= static_cast<int64_t>(tiles) * kUmRows) return;
+    const int t = static_cast<int>(job / kUmRows), m = static_cast<int>(job % kUmRows);
+    constexpr int kQRowsPerCta = kUmRows / GROUP;
+    const int tile_id = p.split_from + t;
+    const int q_tiles = (p.seq_len + kQRowsPerCta - 1) / kQRowsPerCta;
+    const int kv_head = tile_id / q_tiles, qi = (tile_id % q_tiles) * kQRowsPerCta + m / GROUP, head = kv_head * GROUP + m % GROUP;
+    if (qi >= p.seq_len) return;
+    const float* base = p.split_partial + (static_cast<int64_t>(t) * p.split_parts * kUmRows + m) * kUmPartialStride;
+    float M = -INFINITY;
+    for (int s = 0; s < p.split_parts; ++s) M = fmaxf(M, base[static_cast<int64_t>(s) * kUmRows * kUmPartialStride]);
+    float L = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.split_parts; ++s) {
+        const float* ps = base + static_cast<int64_t>(s) * kUmRows * kUmPartialStride;
+        const float wgt = ps[0] == -INFINITY ? 0.f : exp2f(ps[0] - M);
+        L = fmaf(ps[1], wgt, L);
+        const float4 v = *reinterpret_cast<const float4*>(ps + 4 + 4 * lane);
+        a[0] = fmaf(v.x, wgt, a[0]); a[1] = fmaf(v.y, wgt, a[1]); a[2] = fmaf(v.z, wgt, a[2]); a[3] = fmaf(v.w, wgt, a[3]);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    *reinterpret_cast<float4*>(p.out + (static_cast<int64_t>(qi) * p.num_q_heads + head) * kHeadDim + 4 * lane) =
+        make_float4(a[0] * inv, a[1] * inv, a[2] * inv, a[3] * inv);
 }
 
 }  // namespace er
