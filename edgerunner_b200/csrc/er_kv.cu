@@ -175,9 +175,9 @@ struct er_kv {
     bool q8 = false;              // q8_0 rows: int8 part in the K / V slabs, four fp16 scales per row in the side slabs
     bool outlier = false;         // balanced / aggressive TurboQuant rows: codes + mask + signs + two norms in one block per row
     OutlierFormat ofmt{};
-    float* d_outlier_partial = nullptr;   // split partials of the SIMT decode kernel
+    float* d_simt_partial = nullptr;   // split partials of the SIMT decode kernel
     float* d_prefill_partial = nullptr;   // partial rows of the tcgen05 prefill kernel's split tail tiles
-    size_t outlier_partial_floats = 0;
+    size_t simt_partial_floats = 0;
     uint8_t* k_slab = nullptr;
     uint8_t* v_slab = nullptr;
     uint8_t* kn_slab = nullptr;
@@ -548,7 +548,7 @@ void er_kv_destroy(er_kv* kv) {
     cudaFree(kv->k_slab); cudaFree(kv->v_slab); cudaFree(kv->kn_slab); cudaFree(kv->vn_slab);
     cudaFree(kv->d_lengths); cudaFree(kv->d_block_table); cudaFree(kv->d_scratch); cudaFree(kv->d_counters);
     cudaFree(kv->d_head_norm[0]); cudaFree(kv->d_head_norm[1]);
-    cudaFree(kv->d_stage); cudaFree(kv->d_outlier_partial); cudaFree(kv->d_prefill_partial);
+    cudaFree(kv->d_stage); cudaFree(kv->d_simt_partial); cudaFree(kv->d_prefill_partial);
     if (kv->h_status) cudaFreeHost(kv->h_status);
     cudaGetLastError();
     delete kv;
@@ -1255,16 +1255,16 @@ static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, co
     const int items = static_cast<int>(problems) * static_cast<int>(kk->cfg.num_kv_heads);
     int splits = std::max(1, (4 * std::max(kk->num_sms, 1) + items - 1) / items);
     splits = std::min(splits, std::max(1, static_cast<int>((kk->cfg.max_seq_len + 63) / 64)));
-    const size_t need = static_cast<size_t>(items) * splits * group * kOutlierPartialStride;
-    if (kk->outlier_partial_floats < need) {
-        if (kk->d_outlier_partial) cudaFree(kk->d_outlier_partial);
-        kk->d_outlier_partial = nullptr;
-        kk->outlier_partial_floats = 0;
-        if (cudaMalloc(&kk->d_outlier_partial, need * sizeof(float)) != cudaSuccess) {
+    const size_t need = static_cast<size_t>(items) * splits * group * kSimtPartialStride;
+    if (kk->simt_partial_floats < need) {
+        if (kk->d_simt_partial) cudaFree(kk->d_simt_partial);
+        kk->d_simt_partial = nullptr;
+        kk->simt_partial_floats = 0;
+        if (cudaMalloc(&kk->d_simt_partial, need * sizeof(float)) != cudaSuccess) {
             cudaGetLastError();
             return fail(ER_ERR_ALLOCATION_FAILED, "split partials of %zu floats", need);
         }
-        kk->outlier_partial_floats = need;
+        kk->simt_partial_floats = need;
     }
     SimtDecodeParams op{};
     int32_t rc = row_source(kk, false, op.k);
@@ -1278,7 +1278,7 @@ static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, co
     op.scale_log2 = s.softmax_scale * 1.4426950408889634f;
     op.apply_rope = s.apply_rope ? 1 : 0; op.rope_scaling = s.rope_scaling;
     if (op.apply_rope) op.inv_freq = kk->freq(s.rope_theta);
-    op.partial = kk->d_outlier_partial;
+    op.partial = kk->d_simt_partial;
     if (kk->out_heads_total > 0) {
         if (kk->num_peers > 0) return fail(ER_ERR_UNSUPPORTED, "peer outputs are built for the flash-decode kernels");
         if (kk->out_head_offset + num_heads > kk->out_heads_total) return fail(ER_ERR_SHAPE, "output sharding: heads exceed %u", kk->out_heads_total);

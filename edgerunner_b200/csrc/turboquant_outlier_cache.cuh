@@ -143,34 +143,90 @@ struct RowSource {
     KVAddressing addr;
 };
 
-// The lane's four coordinates of row `slot` of (layer, seq, kv head), scaled by the row's norm / block scale.
-__device__ __forceinline__ void read_row_lane4(const RowSource& s, int layer, int seq, int head, int slot, int lane, float e[4]) {
+// A row on its way through a warp: the raw words a lane fetched (issued early, used one token later).
+struct RowRegs {
+    uint32_t w0, w1;   // fp16: the lane's 8 bytes; q8_0: its int8 word; TurboQuant: word `lane` of the row (coalesced), shared by shuffles
+    float side;        // q8_0: the block's scale; TurboQuant fixed presets: the row's norm
+};
+
+// Issues the loads of row `slot` of (layer, seq, kv head); nothing here depends on loaded data except the block-table entry.
+__device__ __forceinline__ RowRegs load_row(const RowSource& s, int layer, int seq, int head, int slot, int lane) {
+    RowRegs r;
+    r.w0 = r.w1 = 0u;
+    r.side = 0.f;
     const int64_t ridx = row_index(s.addr, seq, head, slot);
     const uint8_t* rows = s.rows + static_cast<int64_t>(layer) * s.layer_stride_bytes;
     if (s.format == kRowsF16) {
         const uint2 w = *reinterpret_cast<const uint2*>(rows + ridx * kRowBytesF16 + 8 * lane);
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-        e[0] = a.x; e[1] = a.y; e[2] = b.x; e[3] = b.y;
+        r.w0 = w.x; r.w1 = w.y;
     } else if (s.format == kRowsQ8) {
-        const uint32_t word = reinterpret_cast<const uint32_t*>(rows + ridx * kQ8RowBytes)[q8_word_slot(lane)];
+        r.w0 = reinterpret_cast<const uint32_t*>(rows + ridx * kQ8RowBytes)[q8_word_slot(lane)];
         const uint8_t* side = s.side + static_cast<int64_t>(layer) * s.side_layer_stride_bytes;
-        const float sc = __half2float(reinterpret_cast<const __half*>(side + ridx * kQ8ScaleBytes)[lane >> 3]);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) e[c] = sc * static_cast<float>(static_cast<int8_t>((word >> (8 * c)) & 0xFF));
+        r.side = __half2float(reinterpret_cast<const __half*>(side + ridx * kQ8ScaleBytes)[lane >> 3]);
     } else if (s.format == kRowsTurbo) {
         const int words = (kHeadDim * s.bits + 31) / 32;
-        const uint32_t* w = reinterpret_cast<const uint32_t*>(rows + ridx * (words * 4));
+        if (lane < words) r.w0 = reinterpret_cast<const uint32_t*>(rows + ridx * (words * 4))[lane];
         const uint8_t* side = s.side + static_cast<int64_t>(layer) * s.side_layer_stride_bytes;
-        const float norm = s.norm_fp16 ? __half2float(reinterpret_cast<const __half*>(side)[ridx]) : reinterpret_cast<const float*>(side)[ridx];
-        // 4 * bits <= 16 bits at bit 4 * bits * lane: a piece never leaves the row's words
-        const int off = 4 * s.bits * lane, w0 = off >> 5, sh = off & 31;
-        uint32_t piece = w[w0] >> sh;
-        if (sh + 4 * s.bits > 32) piece |= w[w0 + 1] << (32 - sh);
-        const float* cent = tq_centroids_rt(s.bits);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) e[c] = norm * cent[(piece >> (s.bits * c)) & ((1u << s.bits) - 1u)];
+        r.side = s.norm_fp16 ? __half2float(reinterpret_cast<const __half*>(side)[ridx]) : reinterpret_cast<const float*>(side)[ridx];
     } else {
-        tq_outlier_lane_values(reinterpret_cast<const uint32_t*>(rows + ridx * (s.ofmt.row_words * 4)), s.ofmt, lane, s.res_coef, true, e);
+        if (lane < s.ofmt.row_words) r.w0 = reinterpret_cast<const uint32_t*>(rows + ridx * (s.ofmt.row_words * 4))[lane];
+    }
+    return r;
+}
+
+// `width` bits at bit `offset` of a row whose word i sits in lane i's `w` (all lanes call; offset may differ per lane).
+__device__ __forceinline__ uint32_t warp_row_bits(uint32_t w, int offset, int width) {
+    const int w0 = offset >> 5, sh = offset & 31;
+    const uint32_t lo = __shfl_sync(0xffffffffu, w, w0), hi = __shfl_sync(0xffffffffu, w, (w0 + 1) & 31);
+    const uint32_t v = sh == 0 ? lo : ((lo >> sh) | (hi << (32 - sh)));
+    return v & ((1u << width) - 1u);
+}
+
+// The lane's four coordinates of the row, scaled by the row's norm / block scale.  All 32 lanes call (shuffles inside).
+// `tables`: the four codebooks in shared memory, [bits - 2][code] (divergent indices serialise on the constant cache).
+__device__ __forceinline__ void decode_row_lane4(const RowSource& s, const RowRegs& r, int lane, const float (*tables)[32], float e[4]) {
+    if (s.format == kRowsF16) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.w0)), b = __half22float2(*reinterpret_cast<const __half2*>(&r.w1));
+        e[0] = a.x; e[1] = a.y; e[2] = b.x; e[3] = b.y;
+    } else if (s.format == kRowsQ8) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) e[c] = r.side * static_cast<float>(static_cast<int8_t>((r.w0 >> (8 * c)) & 0xFF));
+    } else if (s.format == kRowsTurbo) {
+        const uint32_t piece = warp_row_bits(r.w0, 4 * s.bits * lane, 4 * s.bits);
+        const float* cent = tables[s.bits - 2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) e[c] = r.side * cent[(piece >> (s.bits * c)) & ((1u << s.bits) - 1u)];
+    } else {
+        // [codes: wpr][mask 4][signs 4][rowNorm][residualNorm]: the same arithmetic as tq_outlier_lane_values on shuffled words
+        const OutlierFormat& f = s.ofmt;
+        const int mw = lane >> 3, msh = 4 * (lane & 7);
+        int before = 0;
+        uint32_t mine = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t mi = __shfl_sync(0xffffffffu, r.w0, f.wpr + i);
+            before += i < mw ? __popc(mi) : 0;
+            mine = i == mw ? mi : mine;
+        }
+        before += __popc(mine & ((1u << msh) - 1u));
+        const uint32_t nib = (mine >> msh) & 15u;
+        const uint32_t sgn = (__shfl_sync(0xffffffffu, r.w0, f.wpr + 4 + mw) >> msh) & 15u;
+        const float row_norm = __uint_as_float(__shfl_sync(0xffffffffu, r.w0, f.wpr + 8));
+        const float res_norm = __uint_as_float(__shfl_sync(0xffffffffu, r.w0, f.wpr + 9));
+        const float res = s.res_coef != 0.f ? s.res_coef * res_norm : 0.f;
+        const uint32_t piece = warp_row_bits(r.w0, 4 * f.rb * lane, 4 * f.rb);
+        const int side_w = f.hb - f.rb;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const bool high = (nib >> c) & 1u;
+            // every lane takes part in the shuffles; a lane without a high-precision code here reads (and drops) the bits at its rank
+            const uint32_t hi_bits = warp_row_bits(r.w0, kHeadDim * f.rb + (before < f.high_count ? before : 0) * side_w, side_w);
+            uint32_t code = (piece >> (f.rb * c)) & ((1u << f.rb) - 1u);
+            if (high) { code |= hi_bits << f.rb; ++before; }
+            float v = tables[(high ? f.hb : f.rb) - 2][code];
+            v = fmaf(res, ((sgn >> c) & 1u) ? 1.f : -1.f, v);
+            e[c] = v * row_norm;
+        }
     }
 }
 
@@ -194,17 +250,23 @@ struct SimtDecodeParams {
     int out_heads_total, out_head_offset;
 };
 
-constexpr int kOutlierDecodeWarps = 8;
-constexpr int kOutlierPartialStride = 132;
+constexpr int kSimtDecodeWarps = 8;
+constexpr int kSimtPartialStride = 132;
 
 // grid (splits, kv heads, (layer, sequence) pairs x query rows); every warp walks tokens split_begin + warp, + 8, ...
 // Scores live in the keys' space (rotated for TurboQuant keys: the query is transformed once), outputs in the values' space
 // (one inverse transform at the end for TurboQuant values).
+// the per-token chain of shuffles and lookups is latency-bound: resident warps are what hides it
 template <int GROUP>
-__global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(const __grid_constant__ SimtDecodeParams p) {
+__global__ void __launch_bounds__(kSimtDecodeWarps * 32, GROUP <= 2 ? 4 : (GROUP == 4 ? 2 : 1)) simt_decode_kernel(const __grid_constant__ SimtDecodeParams p) {
     __shared__ __align__(16) float s_q[GROUP][kHeadDim];
-    __shared__ float s_ml[kOutlierDecodeWarps][GROUP][2];
-    __shared__ __align__(16) float s_acc[kOutlierDecodeWarps][GROUP][kHeadDim];
+    __shared__ float s_ml[kSimtDecodeWarps][GROUP][2];
+    __shared__ __align__(16) float s_acc[kSimtDecodeWarps][GROUP][kHeadDim];
+    __shared__ float s_cent[4][32];
+    if (threadIdx.x < 128) {
+        const int bits = 2 + (threadIdx.x >> 5), code = threadIdx.x & 31;
+        s_cent[bits - 2][code] = code < (1 << bits) ? tq_centroids_rt(bits)[code] : 0.f;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, head = blockIdx.y;
     const int problem = blockIdx.z, pair = problem / p.rows_per_pair, qrow = problem % p.rows_per_pair;
@@ -217,7 +279,7 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(c
     const int kv_len = visible < 0 ? 0 : (visible < cap ? visible : cap);
     const uint32_t q_pos = static_cast<uint32_t>(p.q_pos0 >= 0 ? p.q_pos0 + qrow : (visible > 0 ? visible - 1 : 0));
     // ---- the group's query rows: [NeoX RoPE ->] [randomizedHadamard ->] scaled for exp2 ----
-    for (int g = warp; g < GROUP; g += kOutlierDecodeWarps) {
+    for (int g = warp; g < GROUP; g += kSimtDecodeWarps) {
         const float4 x = *reinterpret_cast<const float4*>(p.q + (static_cast<int64_t>(problem) * p.num_q_heads + head * GROUP + g) * kHeadDim + 4 * lane);
         float a[4] = {x.x, x.y, x.z, x.w};
         if (p.apply_rope) {
@@ -248,18 +310,30 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(c
     float m[GROUP], l[GROUP], acc[GROUP][4];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
-    for (int i = t_begin + warp; i < t_end; i += kOutlierDecodeWarps) {
-        const int t = (first_pos + i) % cap;
+    // the next token's words are on their way while this token is decoded and used
+    RowRegs nk{}, nv{};
+    if (t_begin + warp < t_end) {
+        const int t = (first_pos + t_begin + warp) % cap;
+        nk = load_row(p.k, layer, seq, head, t, lane);
+        nv = load_row(p.v, layer, seq, head, t, lane);
+    }
+    for (int i = t_begin + warp; i < t_end; i += kSimtDecodeWarps) {
+        const RowRegs ck = nk, cv = nv;
+        if (i + kSimtDecodeWarps < t_end) {
+            const int t = (first_pos + i + kSimtDecodeWarps) % cap;
+            nk = load_row(p.k, layer, seq, head, t, lane);
+            nv = load_row(p.v, layer, seq, head, t, lane);
+        }
         float ek[4], ev[4];
-        read_row_lane4(p.k, layer, seq, head, t, lane, ek);
-        read_row_lane4(p.v, layer, seq, head, t, lane, ev);
+        decode_row_lane4(p.k, ck, lane, s_cent, ek);
+        decode_row_lane4(p.v, cv, lane, s_cent, ev);
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             float s = fmaf(qr[g][3], ek[3], fmaf(qr[g][2], ek[2], fmaf(qr[g][1], ek[1], qr[g][0] * ek[0])));
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             const float mn = fmaxf(m[g], s);
-            const float corr = exp2f(m[g] - mn), pr = exp2f(s - mn);   // exp2f(-inf) = 0 on the first token
+            const float corr = fast_exp2(m[g] - mn), pr = fast_exp2(s - mn);   // ex2(-inf) = 0 on the first token
             l[g] = fmaf(l[g], corr, pr);
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[g][c] = fmaf(acc[g][c], corr, pr * ev[c]);
@@ -274,19 +348,19 @@ __global__ void __launch_bounds__(kOutlierDecodeWarps * 32) simt_decode_kernel(c
     }
     __syncthreads();
     const int item = problem * hkv + head;
-    for (int idx = threadIdx.x; idx < GROUP * kHeadDim; idx += kOutlierDecodeWarps * 32) {
+    for (int idx = threadIdx.x; idx < GROUP * kHeadDim; idx += kSimtDecodeWarps * 32) {
         const int g = idx >> 7, d = idx & 127;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kOutlierDecodeWarps; ++w) M = fmaxf(M, s_ml[w][g][0]);
+        for (int w = 0; w < kSimtDecodeWarps; ++w) M = fmaxf(M, s_ml[w][g][0]);
         float L = 0.f, A = 0.f;
 #pragma unroll
-        for (int w = 0; w < kOutlierDecodeWarps; ++w) {
+        for (int w = 0; w < kSimtDecodeWarps; ++w) {
             const float wgt = s_ml[w][g][0] == -INFINITY ? 0.f : exp2f(s_ml[w][g][0] - M);
             L = fmaf(s_ml[w][g][1], wgt, L);
             A = fmaf(s_acc[w][g][d], wgt, A);
         }
-        float* dst = p.partial + ((static_cast<int64_t>(item) * p.splits + split) * GROUP + g) * kOutlierPartialStride;
+        float* dst = p.partial + ((static_cast<int64_t>(item) * p.splits + split) * GROUP + g) * kSimtPartialStride;
         if (d == 0) { dst[0] = M; dst[1] = L; }
         dst[4 + d] = A;
     }
@@ -301,12 +375,12 @@ __global__ void simt_decode_merge_kernel(const __grid_constant__ SimtDecodeParam
     const int item = static_cast<int>(job / GROUP), g = static_cast<int>(job % GROUP);
     const int hkv = p.k.addr.num_kv_heads;
     const int problem = item / hkv, head = item % hkv;
-    const float* base = p.partial + (static_cast<int64_t>(item) * p.splits * GROUP + g) * kOutlierPartialStride;
+    const float* base = p.partial + (static_cast<int64_t>(item) * p.splits * GROUP + g) * kSimtPartialStride;
     float M = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, base[static_cast<int64_t>(s) * GROUP * kOutlierPartialStride]);
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, base[static_cast<int64_t>(s) * GROUP * kSimtPartialStride]);
     float L = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < p.splits; ++s) {
-        const float* ps = base + static_cast<int64_t>(s) * GROUP * kOutlierPartialStride;
+        const float* ps = base + static_cast<int64_t>(s) * GROUP * kSimtPartialStride;
         const float wgt = ps[0] == -INFINITY ? 0.f : exp2f(ps[0] - M);
         L = fmaf(ps[1], wgt, L);
         const float4 v = *reinterpret_cast<const float4*>(ps + 4 + 4 * lane);
@@ -327,7 +401,7 @@ inline int launch_simt_decode(int group, const SimtDecodeParams& p, int pairs, c
     switch (group) {
 #define ER_SIMT_CASE(G)                                                                   \
     case G:                                                                               \
-        simt_decode_kernel<G><<<grid, kOutlierDecodeWarps * 32, 0, stream>>>(p);          \
+        simt_decode_kernel<G><<<grid, kSimtDecodeWarps * 32, 0, stream>>>(p);          \
         simt_decode_merge_kernel<G><<<merge_blocks, 256, 0, stream>>>(p, items);          \
         break;
         ER_SIMT_CASE(1) ER_SIMT_CASE(2) ER_SIMT_CASE(4) ER_SIMT_CASE(8)
