@@ -608,7 +608,7 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
             hout_np = hout.numpy()
 
             def host_step(i):
-                dec.step_host(hq[i], hk[i], hv[i], hout, sp, stream=stream)
+                dec.step_host(hq[i], hk[i], hv[i], hout if dec.exchange != "p2p" else None, sp, stream=stream)
             entry = ("HeadShardedDecoder.step_host: pinned host q/k/v slices in (pulled by the decode kernel), exchange on the device, "
                      "every rank's own heads [layers, batch, heads / N, 128] out to pinned host memory")
         e2e_regions = []
@@ -623,7 +623,7 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
             t0 = time.perf_counter()
             for s in range(K):
                 host_step((W + s) % pool)
-                checksum += float(hout_np[0, 0, 0, 0])       # the host reads the step's result
+                checksum += float(hout_np[0, 0, 0, 0]) if (dec is None or dec.host_rows is None) else float(dec.host_rows[0, 0, 0, 0])   # the host reads the step's result
             e1.record(stream)
             cx.barrier()
             wall_ms = (time.perf_counter() - t0) * 1e3

@@ -199,7 +199,7 @@ struct er_kv {
     uint32_t out_heads_total = 0;            // er_kv_set_output_sharding: 0 = outputs are [layers][batch][num_heads][128]
     uint32_t out_head_offset = 0;
     uint32_t num_peers = 0;
-    float* peer_out[7] = {};
+    float* peer_out[8] = {};
     uint32_t probe_wait_limit_us = 0;        // er_kv_debug_wait_probe: patience of the next decode launches' waits
     int probe_withhold_tiles = 0;
     int* h_status = nullptr;                 // pinned, device-mapped host words: [0] the device status copied by er_kv_decode_step_host;
@@ -1870,13 +1870,13 @@ int32_t er_kv_device_status(er_kv* kv) {
 
 int32_t er_kv_set_output_sharding(er_kv* kv, uint32_t heads_total, uint32_t head_offset, float* const* peer_outputs, uint32_t num_peers) {
     if (!kv) return fail(ER_ERR_INVALID_ARGUMENT, "null cache");
-    if (num_peers > 7 || (num_peers > 0 && (!peer_outputs || heads_total == 0))) return fail(ER_ERR_INVALID_ARGUMENT, "at most 7 peers, and peers need heads_total > 0");
+    if (num_peers > 8 || (num_peers > 0 && (!peer_outputs || heads_total == 0))) return fail(ER_ERR_INVALID_ARGUMENT, "at most 8 peer buffers, and peers need heads_total > 0");
     if (kv->cfg.precision == ER_KV_FLOAT32 && heads_total > 0) return fail(ER_ERR_UNSUPPORTED, "output sharding is built for the flash-decode kernels (fp16, q8_0, TurboQuant rows)");
     for (uint32_t r = 0; r < num_peers; ++r)
         if (!peer_outputs[r] || (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u)) return fail(ER_ERR_INVALID_ARGUMENT, "peer output %u is null or not 16-byte aligned", r);
     std::lock_guard<std::mutex> lock(kv->mu);
     kv->out_heads_total = heads_total; kv->out_head_offset = heads_total ? head_offset : 0; kv->num_peers = heads_total ? num_peers : 0;
-    for (uint32_t r = 0; r < 7; ++r) kv->peer_out[r] = r < kv->num_peers ? peer_outputs[r] : nullptr;
+    for (uint32_t r = 0; r < 8; ++r) kv->peer_out[r] = r < kv->num_peers ? peer_outputs[r] : nullptr;
     return ER_OK;
 }
 

@@ -67,12 +67,12 @@ struct DecodeParams {
     int withhold_tiles;
     // kv-head sharding across GPUs: this launch computes num_q_heads of out_heads_total query heads (0 = not sharded) and
     // writes its rows at head offset out_head_offset of a [pair][out_heads_total][128] buffer -- its own (`out`) and the
-    // same buffer on num_peers other GPUs (peer_out: their mapped addresses), so that every GPU ends the step holding all
+    // same buffer at up to 8 more addresses (peer_out: the other GPUs' mapped buffers; a host-buffer step adds this GPU's own device buffer while `out` is host memory), so that every GPU ends the step holding all
     // heads without a separate all-gather.  Plain stores to peer memory; nothing is ever read from a peer.
     int out_heads_total;
     int out_head_offset;
     int num_peers;
-    float* peer_out[7];
+    float* peer_out[8];
     float scale_log2;             // softmax scale * log2(e)
     float rope_scaling;
     int apply_rope;

@@ -94,6 +94,7 @@ class HeadShardedDecoder:
         self.num_heads, self.world, self.rank, self.group = num_heads, world, rank, group
         self.shard = HeadShard(num_heads, num_kv_heads, world, rank)
         self._own_ptr, self._opened = None, []
+        self._host_full, self._with_self, self.host_rows = None, None, None
         self.exchange = "none" if world == 1 else exchange
         dev = torch.device("cuda", torch.cuda.current_device())
         nfull = layers * batch * num_heads * 128
@@ -163,10 +164,33 @@ class HeadShardedDecoder:
 
     def step_host(self, hq_local, hk_local, hv_local, hout_local, params, stream=None):
         """The same step from pinned host memory: this rank's q / k / v slices come straight out of `hq_local`, `hk_local`,
-        `hv_local` (the decode kernel pulls the rows itself on float16 caches), the exchange runs, and the rank's own heads
-        `[layers, batch, local_heads, 128]` are copied to the pinned `hout_local` -- the ranks' host buffers together hold the
-        step's result once.  Returns after the stream has finished the step."""
+        `hv_local` (the decode kernel pulls the rows itself on float16 caches), the exchange runs on the device, and the rank's
+        own heads `[layers, batch, local_heads, 128]` land in the pinned `hout_local` -- the ranks' host buffers together hold
+        the step's result once (`hout_local` may be None: `self.host_rows` then names the rows where they are).  Returns the device
+        tensor of all heads (valid on the stream after the exchange).
+
+        p2p exchange: the launch writes its rows to a pinned full-width host buffer (`out`), to its own device buffer and to the
+        peers' (all as "peer" addresses), and reports to a host word, so the call returns as soon as the rank's own rows are in
+        host memory -- no device-to-host copy, no stream synchronisation; the 4-byte all-reduce that orders the peers' stores
+        stays on the stream for the device-side consumers."""
         hl = self.shard.local_heads
+        if self.exchange == "p2p":
+            import ctypes as C
+            from ._lib import check, lib
+            if self._host_full is None:
+                self._host_full = torch.empty((self.layers, self.batch, self.num_heads, 128), dtype=torch.float32).pin_memory()
+                ptrs = [self._peer_array[i] for i in range(self._num_peers)] + [self._own_ptr]
+                self._with_self = (C.c_void_p * len(ptrs))(*ptrs)
+            check(lib().er_kv_set_output_sharding(self.cache.handle, self.num_heads, self.shard.q_begin, self._with_self, self._num_peers + 1))
+            try:
+                self.cache.decode_step_host(hq_local, hk_local, hv_local, self._host_full, hl, params, stream=stream)
+            finally:
+                self._set_sharding(True)
+            dist.all_reduce(self._flag, group=self.group)
+            self.host_rows = self._host_full[:, :, self.shard.q_begin:self.shard.q_end]     # the rank's heads, in place
+            if hout_local is not None:
+                hout_local.copy_(self.host_rows)      # host to host, for callers that want them contiguous
+            return self.full
         target = self.out_local if self.exchange == "nccl" else self.full
         self.cache.decode_step_host(hq_local, hk_local, hv_local, target, hl, params, stream=stream)
         if self.exchange == "nccl":
@@ -176,10 +200,9 @@ class HeadShardedDecoder:
                                                 stream_ptr(stream)))
             hout_local.copy_(self.out_local, non_blocking=True)
         else:
-            if self.exchange == "p2p":
-                dist.all_reduce(self._flag, group=self.group)
-            hout_local.copy_(self.full[:, :, self.shard.q_begin:self.shard.q_end], non_blocking=True)
+            hout_local.copy_(self.full, non_blocking=True)
         (stream if stream is not None and not isinstance(stream, int) else torch.cuda.current_stream()).synchronize()
+        self.host_rows = hout_local
         return self.full
 
     def set_peer_stores(self, enabled):

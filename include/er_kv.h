@@ -414,7 +414,8 @@ int32_t er_kv_import_pages(er_kv* kv, const int32_t* page_ids, uint32_t count, c
  *
  * (1) Fused: er_kv_set_output_sharding makes every decode launch of the cache write its finished rows straight into a
  *     [layers][batch][heads_total][128] buffer at head offset `head_offset` -- the `out` argument of the call -- and into
- *     the same buffer of up to 7 peer GPUs (`peer_outputs`: addresses obtained with er_peer_buffer_open), with ordinary
+ *     the same buffer at up to 8 more addresses (`peer_outputs`: the other GPUs' buffers obtained with er_peer_buffer_open -- and,
+ *     when the call's `out` is pinned host memory, this GPU's own device buffer), with ordinary
  *     stores from the kernel's merge epilogue.  When every rank's launch has completed (order that with any barrier,
  *     e.g. a 4-byte all-reduce enqueued behind the step) each GPU holds all heads.  Nothing is read from a peer.
  *     heads_total == 0 turns it off.
