@@ -64,7 +64,7 @@ class NormFormat(enum.IntEnum):
 def step_params(rope_theta=10000.0, rope_scaling=1.0, softmax_scale=0.0, apply_rope=True, q_norm_weight=None,
                 k_norm_weight=None, rms_eps=1e-6, norm_weight_layer_stride=0, sliding_window=0):
     """q_norm_weight / k_norm_weight: device float tensors (or raw pointers) of headDim weights per layer; the caller keeps
-    them alive while the parameters are in use.  sliding_window > 0: decode attends to the newest rows only (fp16 caches)."""
+    them alive while the parameters are in use.  sliding_window > 0: every query row attends to the newest rows only."""
     p = er_step_params()
     p.rope_theta, p.rope_scaling, p.softmax_scale, p.apply_rope = rope_theta, rope_scaling, softmax_scale, int(apply_rope)
     p.q_norm_weight, p.k_norm_weight = ptr(q_norm_weight), ptr(k_norm_weight)

@@ -1441,3 +1441,65 @@ def test_seeded_random_windowed_operator_shapes(er, oracle, torch):
             assert not got.any()
         else:
             assert max_rel_err(got, want) < TOL, (Hkv, group, D, cap, st, cnt)
+
+
+def test_full_size_shapes_constant_value_rows(er, torch):
+    """A size-independent property at BASELINE's full sequence sizes (no CPU reference finishes there): when every V row of a
+    kv head is the same vector, attention returns that vector whatever the keys and the scores are (the probabilities sum to
+    one).  Configuration 3's full batch (64 sequences, contexts U[1024, 16384], fp16 rows in 16-token pages behind a random
+    block table, 32 / 8 heads; one of its 32 layers) and configuration 4's full context (131072 tokens, turbo4 / turbo4 in
+    64-token pages; one layer, one sequence) -- the decode step, and for configuration 4 also a 256-row prefill chunk."""
+    D = 128
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2024)
+    # ---- configuration 3 ----
+    B, Hq, Hkv, ps = 64, 32, 8, 16
+    rng = rng_for(33)
+    lens = [int(x) for x in rng.integers(1024, 16385, size=B)]
+    pages = sum((n + 1 + ps - 1) // ps for n in lens)
+    cache = er.KVCache(max(lens) + 16, 1, Hkv, D, er.Precision.float16, max_batch=B, layout=er.Layout.paged, page_size=ps, num_pages=pages)
+    alloc = er.BlockTableAllocator(pages, ps, free_order=rng.permutation(pages))
+    sp = er.step_params(rope_theta=5e5)
+    pattern = torch.randn((Hkv, D), generator=g, device="cuda").half().float()
+    for b, n in enumerate(lens):
+        cache.set_block_table(b, alloc.ensure(b, n + 1))
+        cache.write_rows(0, b, 0, n, torch.randn((n, Hkv, D), generator=g, device="cuda"), pattern.expand(n, Hkv, D).contiguous(), sp)
+    q = torch.randn((1, B, Hq, D), generator=g, device="cuda")
+    k = torch.randn((1, B, Hkv, D), generator=g, device="cuda")
+    out = torch.full((1, B, Hq, D), float("nan"), device="cuda")
+    cache.decode_step(q, k, pattern.expand(1, B, Hkv, D).contiguous(), out, Hq, sp)
+    torch.cuda.synchronize()
+    assert cache.device_status() == 0
+    want = pattern.repeat_interleave(Hq // Hkv, dim=0).expand(B, Hq, D)
+    err = float((out[0] - want).abs().max() / want.abs().max())
+    print("configuration 3, full batch: constant-V error %.2e of the largest value" % err)
+    assert err < 1e-5           # fp32 rounding of the hi + lo products; the bound of the path is 2e-3
+    cache.close()
+    # ---- configuration 4 ----
+    Hq, Hkv, ps, ctx = 32, 8, 64, 131072
+    T = ctx + 64
+    cache = er.KVCache(T, 1, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=4, norm_format=er.NormFormat.float16,
+                       layout=er.Layout.paged, page_size=ps, num_pages=T // ps)
+    cache.set_block_table(0, rng.permutation(T // ps))
+    sp = er.step_params(rope_theta=1e6)
+    pattern = torch.randn((Hkv, D), generator=g, device="cuda").half().float()
+    for s0 in range(0, ctx, 16384):
+        cache.write_rows(0, 0, s0, 16384, torch.randn((16384, Hkv, D), generator=g, device="cuda"), pattern.expand(16384, Hkv, D).contiguous(), sp)
+    one = er.KVCache(16, 1, Hkv, D, er.Precision.turboquantV2, key_type=4, value_type=4, norm_format=er.NormFormat.float16)
+    one.write_rows(0, 0, 0, 1, pattern[None].contiguous(), pattern[None].contiguous(), er.step_params(apply_rope=0))
+    decoded = torch.as_tensor(np.asarray(one.retrieve_decoded_turboquant(0)[1]).reshape(Hkv, D)).cuda()     # what a stored pattern row decodes to
+    want = decoded.repeat_interleave(Hq // Hkv, dim=0)
+    q = torch.randn((1, 1, Hq, D), generator=g, device="cuda")
+    out = torch.full((1, 1, Hq, D), float("nan"), device="cuda")
+    cache.decode_step(q, torch.randn((1, 1, Hkv, D), generator=g, device="cuda"), pattern[None, None].contiguous(), out, Hq, sp)
+    S = 256
+    qc = torch.randn((S, Hq, D), generator=g, device="cuda")
+    outp = torch.full((S, Hq, D), float("nan"), device="cuda")
+    cache.attention_prefill(0, 0, qc, outp, Hq, S, sp)
+    torch.cuda.synchronize()
+    assert cache.device_status() == 0 and cache.total_written(0, 0) == ctx + 1
+    scale = float(want.abs().max())
+    e_dec = float((out[0, 0] - want).abs().max()) / scale
+    e_pre = float((outp - want[None]).abs().max()) / scale
+    print("configuration 4, 131072 tokens: constant-V error %.2e (decode), %.2e (prefill chunk) of the largest value" % (e_dec, e_pre))
+    assert e_dec < 1e-5 and e_pre < 1e-5
