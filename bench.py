@@ -43,7 +43,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode_kv_append_attention_tokens_per_s"
 WORKLOADS = {
-    # BASELINE.json configs[1]
+    # benchmark contract, configuration [1]
     "cfg1": dict(name="cfg1: Qwen3-0.6B shape, 28 layers, batch 1, fp16 KV, context 4096, 1 token appended per step",
                  layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="head_major", theta=1.0e6),
     "cfg1_per_layer": dict(name="cfg1 with one call per layer (28 launches per step: how a model that interleaves its own projections calls the path)",
@@ -51,9 +51,9 @@ WORKLOADS = {
     "cfg1_token_major": dict(name="cfg1 with the reference's token-major [slot][kvHead][dim] ring layout",
                              layers=28, batch=1, heads=16, kv_heads=8, ctx=4096, precision="float16", layout="token_major",
                              theta=1.0e6),
-    "cfg1_long": dict(name="cfg1 shape at context 32768 (asymptotic kernel bandwidth; not a BASELINE configuration)",
+    "cfg1_long": dict(name="cfg1 shape at context 32768 (asymptotic kernel bandwidth; not one of the contract's configurations)",
                       layers=28, batch=1, heads=16, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=1.0e6),
-    # BASELINE.json configs[2]
+    # benchmark contract, configuration [2]
     "cfg2": dict(name="cfg2: Qwen3-0.6B shape, 28 layers, batch 8, TurboQuant turbo4 K / turbo3 V, fp16 norms, context 32768",
                  layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3, norm="float16",
                  layout="head_major", theta=1.0e6, outliers=True),
@@ -70,25 +70,25 @@ WORKLOADS = {
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",
                          layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3,
                          norm="float16", layout="head_major", theta=1.0e6, outliers=True),
-    # BASELINE.json configs[3]: the largest configuration that fits one GPU (73 GB of cache) -- the default workload
+    # benchmark contract, configuration [3]: the largest configuration that fits one GPU (73 GB of cache) -- the default workload
     "cfg3": dict(name="cfg3: Llama-3.1-8B shape, 32 layers, batch 64, fp16 KV in 16-token pages, context U[1024,16384]",
                  layers=32, batch=64, heads=32, kv_heads=8, ctx=16384, ragged=(1024, 16384), precision="float16", layout="paged",
                  page_size=16, theta=5.0e5),
     "cfg3_contiguous": dict(name="cfg3 heads (32 q / 8 kv) on contiguous head-major rows, 8 layers, batch 8, context 32768 "
-                                 "(separates the page gather from the kernel; not a BASELINE configuration)",
+                                 "(separates the page gather from the kernel; not one of the contract's configurations)",
                             layers=8, batch=8, heads=32, kv_heads=8, ctx=32768, precision="float16", layout="head_major", theta=5.0e5),
-    # BASELINE.json configs[4] as a whole job (run_cfg4): prefill chunk over all layers, then 128 decode steps
+    # benchmark contract, configuration [4] as a whole job (run_cfg4): prefill chunk over all layers, then 128 decode steps
     "cfg4": dict(name="cfg4: Qwen3-4B shape, 36 layers, context 131072, TurboQuant turbo4 K / turbo4 V in 64-token pages; one 2048-token "
                       "prefill chunk per sequence, then 128 decode steps",
                  layers=36, batch=16, heads=32, kv_heads=8, ctx=131072, chunk=2048, decode_steps=128, precision="turboquant", kbits=4, vbits=4,
                  norm="float16", layout="paged", page_size=64, theta=1.0e6),
-    # BASELINE.json configs[4], decode leg on one GPU: 2 of the 16 sequences with all heads (an 8-GPU run gives each pair of
+    # benchmark contract, configuration [4], decode leg on one GPU: 2 of the 16 sequences with all heads (an 8-GPU run gives each pair of
     # GPUs 4 sequences and each GPU half of the heads: the same 10 GB of codes per GPU)
     "cfg4_decode_slice": dict(name="cfg4 decode, one GPU's share: Qwen3-4B shape, 36 layers, 2 of the 16 sequences at context 131072, "
                                    "TurboQuant turbo4 K / turbo4 V, fp16 norms, 64-token pages",
                               layers=36, batch=2, heads=32, kv_heads=8, ctx=131072, precision="turboquant", kbits=4, vbits=4,
                               norm="float16", layout="paged", page_size=64, theta=1.0e6),
-    # BASELINE.json configs[4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
+    # benchmark contract, configuration [4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
     # already in the cache (Qwen3-4B heads, TurboQuant turbo4/turbo4 rows in 64-token pages); tensor-core bound
     "cfg4_prefill": dict(name="cfg4 prefill chunk: Qwen3-4B heads, 2048 query rows at the end of a 131072-token context, "
                               "turbo4/turbo4 in 64-token pages, one layer, one sequence per step",
@@ -827,7 +827,7 @@ def run_prefill(args, w):
 
 
 def run_cfg4(args):
-    """BASELINE configs[4]: Qwen3-4B shape (36 layers, 32 q / 8 kv heads), TurboQuant turbo4 K / turbo4 V rows with fp16 norms in
+    """benchmark contract, configuration [4]: Qwen3-4B shape (36 layers, 32 q / 8 kv heads), TurboQuant turbo4 K / turbo4 V rows with fp16 norms in
     64-token pages, sequences at context 131072: ONE chunked-prefill step that appends 2048 tokens per sequence (causal,
     tensor-core kernel, every layer), then 128 decode steps.  GPUs are split by sequence x kv-head group: pairs of GPUs
     share 4 sequences and hold 4 kv heads each (outputs exchanged inside the pair); one GPU alone runs 2 sequences with all

@@ -1,6 +1,6 @@
 """Generates tests/golden/config0_expected.npz: the CPU oracle's result for benchmark configuration 0.
 
-Configuration 0 (BASELINE.json): single Qwen3-0.6B-shaped layer, batch 1, 16 query heads, 8 kv heads (group 2),
+Configuration 0 of the benchmark contract: single Qwen3-0.6B-shaped layer, batch 1, 16 query heads, 8 kv heads (group 2),
 head_dim 128; contiguous fp16 cache pre-filled with 512 tokens, append 1 token; Q/K/V i.i.d. N(0,1) from seed 0
 (numpy PCG64, float32 draws in the order Q, K, V) cast to fp16; NeoX RoPE theta 1e6 at positions 0..512; softmax
 scale 1/sqrt(128); fp32 accumulate; output fp32 [16,128].

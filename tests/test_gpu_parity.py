@@ -747,7 +747,7 @@ def test_turboquant_host_append_and_decoded_retrieve(er, oracle):
     assert np.array_equal(dk, wk) and np.array_equal(dv, wv)
 
 
-# --------------------------------------------------------------------------------------------- full BASELINE sizes
+# --------------------------------------------------------------------------------------------- the contract's full sizes
 
 def test_config1_full_size_first_and_last_layers(er, oracle, torch):
     """Configuration 1 at its full size (28 independent layers, context 4096, 16 q / 8 kv heads): two consecutive
@@ -1444,7 +1444,7 @@ def test_seeded_random_windowed_operator_shapes(er, oracle, torch):
 
 
 def test_full_size_shapes_constant_value_rows(er, torch):
-    """A size-independent property at BASELINE's full sequence sizes (no CPU reference finishes there): when every V row of a
+    """A size-independent property at the benchmark contract's full sequence sizes (no CPU reference finishes there): when every V row of a
     kv head is the same vector, attention returns that vector whatever the keys and the scores are (the probabilities sum to
     one).  Configuration 3's full batch (64 sequences, contexts U[1024, 16384], fp16 rows in 16-token pages behind a random
     block table, 32 / 8 heads; one of its 32 layers) and configuration 4's full context (131072 tokens, turbo4 / turbo4 in
