@@ -137,8 +137,7 @@ int32_t decode_status(int rc, int group, int kbits, int vbits) {
 // the mma.sync kernel; force_legacy (er_kv_config.prefill_kernel == ER_PREFILL_KERNEL_MMA_SYNC) always takes the latter.
 int launch_prefill(int group, const PrefillParams& pp, uint64_t outer_extent, int num_kv_heads, int* status, cudaStream_t stream,
                    bool force_legacy = false) {
-    // windowed chunks (short key ranges by construction) stay on the mma.sync kernel, which carries the window mask
-    if (!force_legacy && pp.window <= 0 && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
+    if (!force_legacy && status != nullptr && static_cast<int64_t>(pp.seq_len) * group >= 128) {
         const int rc = launch_prefill_umma(group, pp, outer_extent, num_kv_heads, status, stream);
         if (rc != kNotBuilt) return rc;
     }

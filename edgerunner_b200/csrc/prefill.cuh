@@ -41,7 +41,7 @@ struct PrefillParams {
     int q_offset;            // absolute position of query row 0
     int causal;
     int window;              // > 0: query row at position P also ignores keys before P - window + 1 (sliding-window layers;
-                             // Gemma4GPUKVCache.attentionRange); the mma.sync kernel only
+                             // Gemma4GPUKVCache.attentionRange)
     int num_q_heads;
     float scale_log2;
     float rope_scaling;

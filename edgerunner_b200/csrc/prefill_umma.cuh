@@ -204,11 +204,14 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
     const int q_last = min(q0 + kQRowsPerCta, p.seq_len) - 1;
     const int kv_hi = p.causal ? min(kv_len, q_last + q_offset + 1) : kv_len;
     const int total_tiles = (kv_hi + kUmTile - 1) / kUmTile;
-    int tile_begin = 0, num_tiles = total_tiles;     // this CTA's key tiles: [tile_begin, tile_begin + num_tiles)
+    // sliding window: the CTA's first query row is the one that looks furthest back; tiles before its window are skipped
+    const int first_tile = p.window > 0 ? max(0, q_offset + q0 - p.window + 1) / kUmTile : 0;
+    int tile_begin = min(first_tile, total_tiles), num_tiles = total_tiles - tile_begin;     // this CTA's key tiles: [tile_begin, tile_begin + num_tiles)
     if (nparts > 1) {
-        const int per = (total_tiles + nparts - 1) / nparts;
-        tile_begin = min(total_tiles, part * per);
-        num_tiles = min(total_tiles, tile_begin + per) - tile_begin;
+        const int per = (num_tiles + nparts - 1) / nparts;
+        const int b0 = min(num_tiles, part * per);
+        num_tiles = min(num_tiles, b0 + per) - b0;
+        tile_begin += b0;
     }
 
     if (tid == 0) {
@@ -393,6 +396,7 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
         for (int c = 0; c < 64; ++c) o_run[c] = 0.f;
         const uint32_t tmem_o = tmem + kUmColO + 64u * h + lane_base;   // this thread's 64 columns of the O row
         const int limit = min(kv_len - 1, p.causal ? qpos : kv_len - 1);   // last visible token of this row
+        const int lower = p.window > 0 ? qpos - p.window + 1 : 0;          // first one (sliding-window layers)
         for (int j = 0; j < num_tiles; ++j) {
             const int t0 = (tile_begin + j) * kUmTile + kHalfCols * h, b = j % kUmSBufs, xb = j & 1;
             const uint32_t tmem_s = tmem + kUmColS + static_cast<uint32_t>(kUmTile) * b + lane_base;
@@ -410,9 +414,9 @@ __global__ void __launch_bounds__(kUmThreads, 1) prefill_umma_kernel(const __gri
                     if (kHalfCols == 64) s[(32 + c) % kHalfCols] = __uint_as_float(r1[c]);
                 }
             }
-            if (t0 + kHalfCols - 1 > limit) {
+            if (t0 + kHalfCols - 1 > limit || t0 < lower) {
 #pragma unroll
-                for (int c = 0; c < kHalfCols; ++c) s[c] = (t0 + c <= limit) ? s[c] : -INFINITY;
+                for (int c = 0; c < kHalfCols; ++c) s[c] = (t0 + c <= limit && t0 + c >= lower) ? s[c] : -INFINITY;
             }
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll

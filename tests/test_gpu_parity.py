@@ -1369,6 +1369,7 @@ def test_sliding_window_on_compressed_caches(er, oracle, torch, precision, kw):
     ("paged", 32, 16, 4, 50, 130, 100),          # window longer than the context of the first rows
     ("token_major", 0, 8, 8, 0, 77, 1),          # every row sees only itself
     ("head_major", 0, 32, 4, 700, 40, 5000),     # window wider than everything: plain causal attention
+    ("paged", 64, 16, 8, 3000, 512, 700),        # tcgen05 kernel: several leading 128-token tiles skipped per CTA, split tail
 ])
 def test_sliding_window_prefill(er, oracle, torch, layout, page_size, Hq, Hkv, ctx, S, window):
     """er_kv_attention_prefill with er_step_params.sliding_window: query row at position P sees keys
