@@ -107,6 +107,10 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
     using Base = TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
     static_assert(GROUP <= 8, "one n-tile of heads");
     static constexpr int kKPairs = 1 << (2 * KBITS);
+    // Up to four heads leave half of the n-tile's eight columns free: the hi parts of the queries (and of the probabilities)
+    // take columns 0..3 and the lo parts columns 4..7, so ONE mma multiplies an A fragment by both; the two column halves
+    // are added across lanes c and c ^ 2 (scores: per unit; outputs: when the accumulators are folded or published).
+    static constexpr bool kPacked = GROUP <= 4;
     // Lookup tables, one column per lane (no bank conflicts), 8-byte entries:
     //   keys    [code pairs (dims d, d + 1 of a token)][32 lanes]: half2 (hi parts of the two centroids), half2 (lo parts)
     //   values  3-bit: [code pairs][32 lanes]: half2 (hi, lo) of dim d, half2 (hi, lo) of dim d + 1 -- the two A registers of an
@@ -134,7 +138,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
     __device__ __forceinline__ static float* fin_ptr(uint8_t* extra) { return window_ptr(extra, plan(extra).rows + GROUP * kHeadDim * 4); }
 
     struct State {
-        uint32_t qh[8][2], ql[8][2];   // B fragments of the rotated queries per k-step: fp16 hi and lo parts
+        uint32_t qh[8][2], ql[8][2];   // B fragments of the rotated queries per k-step: fp16 hi and lo parts (packed: qh holds both)
         float m[2], l[2];              // heads 2c, 2c + 1
         float acc[8][4];               // O^T fragments: [m-tile][(row g | row g + 8) x (head 2c | 2c + 1)]
         uint32_t lut_k, lut_v;         // this lane's column of the tables: table address | lane << 3
@@ -146,8 +150,18 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         }
-        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) const {
+        // packed columns: V . P_hi (lanes c < 2) + V . P_lo (lanes c >= 2) of the same heads
+        __device__ __forceinline__ void join_halves() {
+            if constexpr (kPacked) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[t][e] += __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
+            }
+        }
+        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) {
             const int g = lane >> 2, c = lane & 3;
+            join_halves();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -163,6 +177,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             }
         }
         __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
+            join_halves();
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, 1.f, 1.f, [](int t, int g, int second) { return 16 * g + 2 * t + second; });
         }
     };
@@ -206,13 +221,21 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (g < GROUP) t = *reinterpret_cast<const float4*>(qrot + g * kHeadDim + 32 * c + 4 * s);
+            const int head = kPacked ? (g & 3) : g;   // packed: column g carries head g % 4, hi part below column 4
+            if (head < GROUP) t = *reinterpret_cast<const float4*>(qrot + head * kHeadDim + 32 * c + 4 * s);
             const __half2 h01 = __floats2half2_rn(t.x, t.y), h23 = __floats2half2_rn(t.z, t.w);
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            st.qh[s][0] = *reinterpret_cast<const uint32_t*>(&h01);
-            st.qh[s][1] = *reinterpret_cast<const uint32_t*>(&h23);
-            st.ql[s][0] = pack_half2(t.x - f01.x, t.y - f01.y);
-            st.ql[s][1] = pack_half2(t.z - f23.x, t.w - f23.y);
+            const uint32_t hi0 = *reinterpret_cast<const uint32_t*>(&h01), hi1 = *reinterpret_cast<const uint32_t*>(&h23);
+            const uint32_t lo0 = pack_half2(t.x - f01.x, t.y - f01.y), lo1 = pack_half2(t.z - f23.x, t.w - f23.y);
+            if constexpr (kPacked) {
+                st.qh[s][0] = g < 4 ? hi0 : lo0;
+                st.qh[s][1] = g < 4 ? hi1 : lo1;
+            } else {
+                st.qh[s][0] = hi0;
+                st.qh[s][1] = hi1;
+                st.ql[s][0] = lo0;
+                st.ql[s][1] = lo1;
+            }
         }
         st.reset();
     }
@@ -243,7 +266,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             lds_u32x2(key_entry<2 * S + 1>(k0, st.lut_k), a2, e2);
             lds_u32x2(key_entry<2 * S + 1>(k1, st.lut_k), a3, e3);
             mma_m16n8k16(s, a0, a1, a2, a3, st.qh[S][0], st.qh[S][1]);
-            mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
+            if constexpr (!kPacked) mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
             mma_m16n8k16(s, e0, e1, e2, e3, st.qh[S][0], st.qh[S][1]);
             score_steps<S + 1>(s, k0, k1, st);
         }
@@ -288,7 +311,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                 value_pair<T>(st.lut_v, vlo[2 * j], vhi[2 * j], a0, a1);
                 value_pair<T>(st.lut_v, vlo[2 * j + 1], vhi[2 * j + 1], a2, a3);
                 mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bh[2 * j], bh[2 * j + 1]);
-                mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bl[2 * j], bl[2 * j + 1]);
+                if constexpr (!kPacked) mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bl[2 * j], bl[2 * j + 1]);
             }
             value_tiles<T + 1>(st, vlo, vhi, bh, bl);
         }
@@ -332,6 +355,10 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
 
         float s[4] = {0.f, 0.f, 0.f, 0.f};   // (token tk0 | tk0 + 8) x (head 2c | 2c + 1)
         score_steps<0>(s, k0, k1, st);
+        if constexpr (kPacked) {   // columns 2c, 2c + 1 and their partners four columns on: (Kh + Kl) . qh + (Kh + Kl) . ql
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+        }
         s[0] = ok0 ? (kn0 * s[0]) * sc : -INFINITY;
         s[1] = ok0 ? (kn0 * s[1]) * sc : -INFINITY;
         s[2] = ok1 ? (kn1 * s[2]) * sc : -INFINITY;
@@ -368,13 +395,21 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         const float w0 = p0 * vn0, w1 = p1 * vn0, w2 = p2 * vn1, w3 = p3 * vn1;
         const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
         const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const uint32_t x0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h01));
-        const uint32_t x1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
-        const uint32_t y0 = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
-        const uint32_t y1 = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
-        const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
-        const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
-        value_tiles<0>(st, vlo, vhi, bh, bl);
+        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+        if constexpr (kPacked) {
+            // lanes c and c ^ 2 hold the same probabilities: the first pair supplies the hi parts (columns 0..3), the second the lo parts
+            const uint32_t x0 = movmatrix_trans(c < 2 ? hi01 : lo01);
+            const uint32_t x1 = movmatrix_trans(c < 2 ? hi23 : lo23);
+            const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
+            value_tiles<0>(st, vlo, vhi, bh, bh);
+        } else {
+            const uint32_t x0 = movmatrix_trans(hi01), x1 = movmatrix_trans(hi23);
+            const uint32_t y0 = movmatrix_trans(lo01), y1 = movmatrix_trans(lo23);
+            const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
+            const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
+            value_tiles<0>(st, vlo, vhi, bh, bl);
+        }
     }
 };
 
