@@ -25,9 +25,10 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
     using Base = DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
     static_assert(GROUP <= 8, "one n-tile of heads");
     static constexpr float kProbScale = 4096.f, kInvProbScale = 1.f / 4096.f;
+    static constexpr bool kPacked = GROUP <= 4;   // hi parts in columns 0..3 of the n-tile, lo parts in 4..7 (see Q8MmaPolicy)
 
     struct State {
-        uint32_t qh[8][2], ql[8][2];   // B fragments of the queries per k-step: fp16 hi and lo parts
+        uint32_t qh[8][2], ql[8][2];   // B fragments of the queries per k-step: fp16 hi and lo parts (packed: qh holds both)
         float m[2], l[2];              // heads 2c, 2c + 1
         float acc[8][4];               // O^T fragments: [m-tile][(row g | row g + 8) x (head 2c | 2c + 1)]
         __device__ __forceinline__ void reset() {
@@ -38,9 +39,18 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         }
+        __device__ __forceinline__ void join_halves() {   // packed columns: V . p_hi (lanes c < 2) + V . p_lo (lanes c >= 2)
+            if constexpr (kPacked) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[t][e] += __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
+            }
+        }
         // m-tile t = 2j + u: row n -> dim 32j + 8(n/2) + 4u + n%2, row n + 8 -> that + 2
-        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) const {
+        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) {
             const int g = lane >> 2, c = lane & 3;
+            join_halves();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -59,6 +69,7 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
             }
         }
         __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
+            join_halves();
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, 1.f, kProbScale,
                                   [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
         }
@@ -70,13 +81,14 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane,
                                   int layer) {
         const int g = lane >> 2, c = lane & 3;
+        const int head = kPacked ? (g & 3) : g;   // packed: column g carries head g % 4, its hi part below column 4
         const float* qw = p.q_norm_w ? p.q_norm_w + static_cast<int64_t>(layer) * p.norm_stride : nullptr;
         float rs = 1.f;
         if (qw != nullptr) {
 #pragma unroll
             for (int h = 0; h < GROUP; ++h) {
                 const float r = head_rms_scale<COHERENT>(qrow + h * kHeadDim, p.rms_eps, lane);
-                if (h == g) rs = r;
+                if (h == head) rs = r;
             }
         }
 #pragma unroll
@@ -84,11 +96,11 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
             float x[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] = 0.f;
-            if (g < GROUP) {
+            if (head < GROUP) {
                 const int d0 = 32 * b + 8 * c;
                 auto load8 = [&](int d, float (&out)[8]) {
-                    const float4 lo4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d));
-                    const float4 hi4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d + 4));
+                    const float4 lo4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + head * kHeadDim + d));
+                    const float4 hi4 = ld_step_row<COHERENT>(reinterpret_cast<const float4*>(qrow + head * kHeadDim + d + 4));
                     out[0] = lo4.x; out[1] = lo4.y; out[2] = lo4.z; out[3] = lo4.w;
                     out[4] = hi4.x; out[5] = hi4.y; out[6] = hi4.z; out[7] = hi4.w;
                     if (qw != nullptr) {
@@ -117,8 +129,13 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
                     const float a0 = x[4 * u + 2 * half], a1 = x[4 * u + 2 * half + 1];
                     const __half2 hh = __floats2half2_rn(a0, a1);
                     const float2 hf = __half22float2(hh);
-                    st.qh[2 * b + u][half] = *reinterpret_cast<const uint32_t*>(&hh);
-                    st.ql[2 * b + u][half] = pack_half2(a0 - hf.x, a1 - hf.y);
+                    const uint32_t hi = *reinterpret_cast<const uint32_t*>(&hh), lo = pack_half2(a0 - hf.x, a1 - hf.y);
+                    if constexpr (kPacked) {
+                        st.qh[2 * b + u][half] = g < 4 ? hi : lo;
+                    } else {
+                        st.qh[2 * b + u][half] = hi;
+                        st.ql[2 * b + u][half] = lo;
+                    }
                 }
         }
         st.reset();
@@ -145,8 +162,12 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.qh[2 * j + u][0], st.qh[2 * j + u][1]);
-                mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.ql[2 * j + u][0], st.ql[2 * j + u][1]);
+                if constexpr (!kPacked) mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.ql[2 * j + u][0], st.ql[2 * j + u][1]);
             }
+        }
+        if constexpr (kPacked) {   // columns 2c, 2c + 1 (K . q_hi) and their partners four columns on (K . q_lo)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
         }
         // rows at or past nvalid were never copied (stale shared memory, possibly NaN patterns): the select discards them
         s[0] = ok0 ? s[0] * p.scale_log2 : -INFINITY;
@@ -183,10 +204,16 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
         const float w0 = p0 * kProbScale, w1 = p1 * kProbScale, w2 = p2 * kProbScale, w3 = p3 * kProbScale;
         const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
         const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h01));
-        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
-        const uint32_t b0l = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
-        const uint32_t b1l = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
+        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+        // packed: lanes c and c ^ 2 hold the same probabilities; the first pair supplies the hi columns, the second the lo columns
+        const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
+        const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
+        uint32_t b0l = 0, b1l = 0;
+        if constexpr (!kPacked) {
+            b0l = movmatrix_trans(lo01);
+            b1l = movmatrix_trans(lo23);
+        }
         const bool partial = nvalid < kUnitTokens;   // warp-uniform
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -207,7 +234,7 @@ struct DenseMmaPolicy : DensePolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES> 
                 const uint32_t a2 = movmatrix_trans(v1[2 * u]);
                 const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
                 mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
-                mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
+                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
             }
         }
     }

@@ -53,9 +53,12 @@ struct Q8MmaPolicy {
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
 
     static constexpr float kProbScale = 64.f, kInvProbScale = 1.f / 64.f;
+    // Up to four heads: the hi parts of queries and probabilities take columns 0..3 of the n-tile and the lo parts columns
+    // 4..7, so one mma multiplies an A fragment by both; the column halves are added across lanes c and c ^ 2.
+    static constexpr bool kPacked = GROUP <= 4;
 
     struct State {
-        uint32_t qh[8][2], ql[8][2];   // B fragments of the (rotated) queries per k-step: fp16 hi and lo parts
+        uint32_t qh[8][2], ql[8][2];   // B fragments of the (rotated) queries per k-step: fp16 hi and lo parts (packed: qh holds both)
         float m[2], l[2];              // heads 2c, 2c + 1
         float acc[8][4];               // O^T fragments: [m-tile][(row g | row g + 8) x (head 2c | 2c + 1)]
         __device__ __forceinline__ void reset() {
@@ -66,9 +69,18 @@ struct Q8MmaPolicy {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         }
+        __device__ __forceinline__ void join_halves() {   // packed columns: V . p_hi (lanes c < 2) + V . p_lo (lanes c >= 2)
+            if constexpr (kPacked) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[t][e] += __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
+            }
+        }
         // m-tile t = 2b + u of block b: row n -> dim 32b + 8(n/2) + 4u + n%2, row n + 8 -> that + 2
-        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) const {
+        __device__ __forceinline__ void publish(float* ml, float* accs, int lane) {
             const int g = lane >> 2, c = lane & 3;
+            join_halves();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -87,6 +99,7 @@ struct Q8MmaPolicy {
             }
         }
         __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
+            join_halves();
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, kInvProbScale, 1.f,
                                   [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
         }
@@ -137,21 +150,22 @@ struct Q8MmaPolicy {
     // label 2c + 8 + e -> dim 32b + 8c + 4u + 2 + e; thread (g, c) holds head g.
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane, int) {
         const int g = lane >> 2, c = lane & 3;
+        const int head = kPacked ? (g & 3) : g;   // packed: column g carries head g % 4, its hi part below column 4
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             float x[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] = 0.f;
-            if (g < GROUP) {
+            if (head < GROUP) {
                 const int d0 = 32 * b + 8 * c;
-                const float4 lo4 = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d0));
-                const float4 hi4 = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + d0 + 4));
+                const float4 lo4 = __ldg(reinterpret_cast<const float4*>(qrow + head * kHeadDim + d0));
+                const float4 hi4 = __ldg(reinterpret_cast<const float4*>(qrow + head * kHeadDim + d0 + 4));
                 x[0] = lo4.x; x[1] = lo4.y; x[2] = lo4.z; x[3] = lo4.w; x[4] = hi4.x; x[5] = hi4.y; x[6] = hi4.z; x[7] = hi4.w;
                 if (p.apply_rope) {
                     // partner of dim d is d +- 64: blocks b and b ^ 2, same offset inside the block
                     const int dp = d0 ^ 64;
-                    const float4 plo = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + dp));
-                    const float4 phi = __ldg(reinterpret_cast<const float4*>(qrow + g * kHeadDim + dp + 4));
+                    const float4 plo = __ldg(reinterpret_cast<const float4*>(qrow + head * kHeadDim + dp));
+                    const float4 phi = __ldg(reinterpret_cast<const float4*>(qrow + head * kHeadDim + dp + 4));
                     const float y[8] = {plo.x, plo.y, plo.z, plo.w, phi.x, phi.y, phi.z, phi.w};
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
@@ -169,8 +183,13 @@ struct Q8MmaPolicy {
                     const float a0 = x[4 * u + 2 * half], a1 = x[4 * u + 2 * half + 1];
                     const __half2 hh = __floats2half2_rn(a0, a1);
                     const float2 hf = __half22float2(hh);
-                    st.qh[2 * b + u][half] = *reinterpret_cast<const uint32_t*>(&hh);
-                    st.ql[2 * b + u][half] = pack_half2(a0 - hf.x, a1 - hf.y);
+                    const uint32_t hi = *reinterpret_cast<const uint32_t*>(&hh), lo = pack_half2(a0 - hf.x, a1 - hf.y);
+                    if constexpr (kPacked) {
+                        st.qh[2 * b + u][half] = g < 4 ? hi : lo;
+                    } else {
+                        st.qh[2 * b + u][half] = hi;
+                        st.ql[2 * b + u][half] = lo;
+                    }
                 }
         }
         st.reset();
@@ -204,7 +223,7 @@ struct Q8MmaPolicy {
                     const uint32_t a0 = q8_pair_to_half2<0>(w0), a1 = q8_pair_to_half2<0>(w1);
                     const uint32_t a2 = q8_pair_to_half2<1>(w0), a3 = q8_pair_to_half2<1>(w1);
                     mma_m16n8k16(sb[b], a0, a1, a2, a3, st.qh[2 * b + u][0], st.qh[2 * b + u][1]);
-                    mma_m16n8k16(sb[b], a0, a1, a2, a3, st.ql[2 * b + u][0], st.ql[2 * b + u][1]);
+                    if constexpr (!kPacked) mma_m16n8k16(sb[b], a0, a1, a2, a3, st.ql[2 * b + u][0], st.ql[2 * b + u][1]);
                 }
             }
         }
@@ -229,6 +248,10 @@ struct Q8MmaPolicy {
         s[1] = ks0[0] * sb[0][1] + ks0[1] * sb[1][1] + ks0[2] * sb[2][1] + ks0[3] * sb[3][1];
         s[2] = ks1[0] * sb[0][2] + ks1[1] * sb[1][2] + ks1[2] * sb[2][2] + ks1[3] * sb[3][2];
         s[3] = ks1[0] * sb[0][3] + ks1[1] * sb[1][3] + ks1[2] * sb[2][3] + ks1[3] * sb[3][3];
+        if constexpr (kPacked) {   // columns 2c, 2c + 1 (K . q_hi) and their partners four columns on (K . q_lo)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+        }
         s[0] = ok0 ? s[0] * p.scale_log2 : -INFINITY;
         s[1] = ok0 ? s[1] * p.scale_log2 : -INFINITY;
         s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
@@ -268,10 +291,16 @@ struct Q8MmaPolicy {
             const float w0 = p0 * vs0[b], w1 = p1 * vs0[b], w2 = p2 * vs1[b], w3 = p3 * vs1[b];
             const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h01));
-            const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h23));
-            const uint32_t b0l = movmatrix_trans(pack_half2(w0 - f01.x, w1 - f01.y));
-            const uint32_t b1l = movmatrix_trans(pack_half2(w2 - f23.x, w3 - f23.y));
+            const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+            const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+            // packed: lanes c and c ^ 2 hold the same probabilities; the first pair supplies the hi columns, the second the lo columns
+            const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
+            const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
+            uint32_t b0l = 0, b1l = 0;
+            if constexpr (!kPacked) {
+                b0l = movmatrix_trans(lo01);
+                b1l = movmatrix_trans(lo23);
+            }
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 // rows at or past nvalid were never copied: their bytes are stale but finite after conversion, and p = 0
@@ -281,7 +310,7 @@ struct Q8MmaPolicy {
                 const uint32_t a2 = movmatrix_trans(q8_pair_to_half2<0>(x1));
                 const uint32_t a3 = movmatrix_trans(q8_pair_to_half2<1>(x1));
                 mma_m16n8k16(st.acc[2 * b + u], a0, a1, a2, a3, b0, b1);
-                mma_m16n8k16(st.acc[2 * b + u], a0, a1, a2, a3, b0l, b1l);
+                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * b + u], a0, a1, a2, a3, b0l, b1l);
             }
         }
     }
