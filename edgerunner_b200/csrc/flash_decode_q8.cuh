@@ -69,18 +69,23 @@ struct Q8MmaPolicy {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         }
-        __device__ __forceinline__ void join_halves() {   // packed columns: V . p_hi (lanes c < 2) + V . p_lo (lanes c >= 2)
+        __device__ __forceinline__ void gather() {   // packed columns: V . p_hi (lanes c < 2) + V . p_lo (lanes c >= 2)
             if constexpr (kPacked) {
 #pragma unroll
                 for (int t = 0; t < 8; ++t)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[t][e] += __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
             }
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {   // denominators: per-lane partial sums over the lane's tokens
+                l[0] += __shfl_xor_sync(0xffffffffu, l[0], off);
+                l[1] += __shfl_xor_sync(0xffffffffu, l[1], off);
+            }
         }
         // m-tile t = 2b + u of block b: row n -> dim 32b + 8(n/2) + 4u + n%2, row n + 8 -> that + 2
         __device__ __forceinline__ void publish(float* ml, float* accs, int lane) {
             const int g = lane >> 2, c = lane & 3;
-            join_halves();
+            gather();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -99,7 +104,7 @@ struct Q8MmaPolicy {
             }
         }
         __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
-            join_halves();
+            gather();
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, kInvProbScale, 1.f,
                                   [](int t, int g, int second) { return 32 * (t >> 1) + 8 * (g >> 1) + 4 * (t & 1) + (g & 1) + 2 * second; });
         }
@@ -257,31 +262,32 @@ struct Q8MmaPolicy {
         s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
         s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
 
+        // The running maxima change only when some token of the unit exceeds them (always in a fresh state: token 0 of a unit
+        // is valid, its score finite): the cross-lane maximum and the rescale run only then.  The denominators stay per-lane
+        // partial sums (every lane applies the same corrections); State::gather adds them up when the state is read.
         float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+        float m0 = st.m[0], m1 = st.m[1];
+        if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
 #pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-        }
-        const float m0 = fmaxf(st.m[0], mx0), m1 = fmaxf(st.m[1], mx1);   // finite: token 0 of the unit is valid
-        const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
-        const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
-        float sum0 = p0 + p2, sum1 = p1 + p3;
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
-            sum1 += __shfl_xor_sync(0xffffffffu, sum1, off);
-        }
-        st.l[0] = fmaf(st.l[0], corr0, sum0);
-        st.l[1] = fmaf(st.l[1], corr1, sum1);
-        st.m[0] = m0;
-        st.m[1] = m1;
-        if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            m0 = fmaxf(m0, mx0);
+            m1 = fmaxf(m1, mx1);
+            const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
+            st.l[0] *= corr0;
+            st.l[1] *= corr1;
+            st.m[0] = m0;
+            st.m[1] = m1;
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
                 st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
             }
         }
+        const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
+        st.l[0] += p0 + p2;
+        st.l[1] += p1 + p3;
         // ---- outputs, block by block: B = (p * vScale[block]) as fp16 hi + lo, A = transposed int8 pairs ----
         uint32_t v0[8], v1[8];
         load_row(vrow, v0);

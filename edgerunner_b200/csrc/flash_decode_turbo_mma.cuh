@@ -151,17 +151,22 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
                 for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         }
         // packed columns: V . P_hi (lanes c < 2) + V . P_lo (lanes c >= 2) of the same heads
-        __device__ __forceinline__ void join_halves() {
+        __device__ __forceinline__ void gather() {
             if constexpr (kPacked) {
 #pragma unroll
                 for (int t = 0; t < 8; ++t)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[t][e] += __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
             }
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {   // denominators: per-lane partial sums over the lane's tokens
+                l[0] += __shfl_xor_sync(0xffffffffu, l[0], off);
+                l[1] += __shfl_xor_sync(0xffffffffu, l[1], off);
+            }
         }
         __device__ __forceinline__ void publish(float* ml, float* accs, int lane) {
             const int g = lane >> 2, c = lane & 3;
-            join_halves();
+            gather();
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = 2 * c + e;
@@ -177,7 +182,7 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             }
         }
         __device__ __forceinline__ void fold(float* ml, float* accs, int lane, bool first) {
-            join_halves();
+            gather();
             mma_state_fold<GROUP>(m, l, acc, ml, accs, lane, first, 1.f, 1.f, [](int t, int g, int second) { return 16 * g + 2 * t + second; });
         }
     };
@@ -266,9 +271,27 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
             lds_u32x2(key_entry<2 * S + 1>(k0, st.lut_k), a2, e2);
             lds_u32x2(key_entry<2 * S + 1>(k1, st.lut_k), a3, e3);
             mma_m16n8k16(s, a0, a1, a2, a3, st.qh[S][0], st.qh[S][1]);
-            if constexpr (!kPacked) mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
+            mma_m16n8k16(s, a0, a1, a2, a3, st.ql[S][0], st.ql[S][1]);
             mma_m16n8k16(s, e0, e1, e2, e3, st.qh[S][0], st.qh[S][1]);
             score_steps<S + 1>(s, k0, k1, st);
+        }
+    }
+
+    // Packed form (kPacked).  Rows g + 8 of the A fragment carry the LO parts of the token whose hi parts sit in row g, so the
+    // two registers a table read returns (hi pair, lo pair) are two adjacent A registers as they come, and an mma covers 8
+    // tokens: sa takes tokens 0..7 of the unit, sb tokens 8..15; row g of an accumulator holds Kh . q, row g + 8 Kl . q.
+    template <int S>
+    __device__ __forceinline__ static void score_steps_packed(float (&sa)[4], float (&sb)[4], const uint32_t (&k0)[KBITS],
+                                                              const uint32_t (&k1)[KBITS], const State& st) {
+        if constexpr (S < 8) {
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            lds_u32x2(key_entry<2 * S>(k0, st.lut_k), a0, a1);
+            lds_u32x2(key_entry<2 * S + 1>(k0, st.lut_k), a2, a3);
+            lds_u32x2(key_entry<2 * S>(k1, st.lut_k), b0, b1);
+            lds_u32x2(key_entry<2 * S + 1>(k1, st.lut_k), b2, b3);
+            mma_m16n8k16(sa, a0, a1, a2, a3, st.qh[S][0], st.qh[S][1]);
+            mma_m16n8k16(sb, b0, b1, b2, b3, st.qh[S][0], st.qh[S][1]);
+            score_steps_packed<S + 1>(sa, sb, k0, k1, st);
         }
     }
 
@@ -354,41 +377,49 @@ struct TurboMmaPolicy : TurboStaging<GROUP, KBITS, VBITS, UNITS_PER_TILE, WARP_G
         const float sc = p.scale_log2 * inv_sk;
 
         float s[4] = {0.f, 0.f, 0.f, 0.f};   // (token tk0 | tk0 + 8) x (head 2c | 2c + 1)
-        score_steps<0>(s, k0, k1, st);
-        if constexpr (kPacked) {   // columns 2c, 2c + 1 and their partners four columns on: (Kh + Kl) . qh + (Kh + Kl) . ql
+        if constexpr (kPacked) {
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+            score_steps_packed<0>(sa, sb, k0, k1, st);
+            s[0] = sa[0] + sa[2];   // Kh . q + Kl . q of token g
+            s[1] = sa[1] + sa[3];
+            s[2] = sb[0] + sb[2];   // of token g + 8
+            s[3] = sb[1] + sb[3];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+            for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);   // columns 2c, 2c + 1 (q hi) + their partners four on (q lo)
+        } else {
+            score_steps<0>(s, k0, k1, st);
         }
         s[0] = ok0 ? (kn0 * s[0]) * sc : -INFINITY;
         s[1] = ok0 ? (kn0 * s[1]) * sc : -INFINITY;
         s[2] = ok1 ? (kn1 * s[2]) * sc : -INFINITY;
         s[3] = ok1 ? (kn1 * s[3]) * sc : -INFINITY;
 
+        // The running maxima change only when some token of the unit exceeds them (always in a fresh state: token 0 of a unit
+        // is valid, its score finite): the cross-lane maximum and the rescale run only then.  The denominators stay per-lane
+        // partial sums (every lane applies the same corrections); State::gather adds them up when the state is read.
         float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+        float m0 = st.m[0], m1 = st.m[1];
+        if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
 #pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-        }
-        const float m0 = fmaxf(st.m[0], mx0), m1 = fmaxf(st.m[1], mx1);   // finite: token 0 of the unit (S row 0) is valid
-        const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
-        const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
-        float sum0 = p0 + p2, sum1 = p1 + p3;
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
-            sum1 += __shfl_xor_sync(0xffffffffu, sum1, off);
-        }
-        st.l[0] = fmaf(st.l[0], corr0, sum0);
-        st.l[1] = fmaf(st.l[1], corr1, sum1);
-        st.m[0] = m0;
-        st.m[1] = m1;
-        if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            m0 = fmaxf(m0, mx0);
+            m1 = fmaxf(m1, mx1);
+            const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
+            st.l[0] *= corr0;
+            st.l[1] *= corr1;
+            st.m[0] = m0;
+            st.m[1] = m1;
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
                 st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
             }
         }
+        const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
+        st.l[0] += p0 + p2;
+        st.l[1] += p1 + p3;
         // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed: thread (g', c') receives head g' of tokens 2c', 2c' + 1
         // and, from the rows g + 8, of 2c' + 8, 2c' + 9; each value is duplicated on the two
         // contraction labels that carry the hi and the lo half of a centroid
