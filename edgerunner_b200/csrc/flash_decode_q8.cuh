@@ -8,6 +8,9 @@
 // keep fp32 accuracy with the queries and the scaled probabilities entering as fp16 hi + lo pairs.  p * vScale is small
 // (vScale = maxAbs / 127, p ~ 1 / context): it is carried times 64 so that its lo part stays a normal fp16 number
 // (64 * vScale <= 65504 for every scale an fp16-sourced row can have), and the outputs are divided by 64 when published.
+// With up to four heads per kv head (kPacked) the hi parts sit in columns 0..3 of the n-tile and the lo parts in columns
+// 4..7, so one mma multiplies an A fragment by both; scores add the two column halves across lanes c and c ^ 2, outputs
+// when the state is folded or published.
 // Thread (g = lane / 4, c = lane % 4) reads tokens g and g + 8 of the warp's 16-token unit and, of every 32-element
 // block, the 8 bytes [8c, 8c + 8) -- adjacent in the cached row (q8_word_slot: 32 bytes at 32c, two 16-byte reads
 // that the warp's lanes spread over all banks; the plain element order made eight rows collide on the same banks and cost

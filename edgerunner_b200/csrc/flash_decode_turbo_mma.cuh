@@ -8,7 +8,11 @@
 // Scores.  Thread (g = lane / 4, c = lane % 4) reads, of the two tokens behind S rows g and g + 8, the 32 consecutive codes
 // [32c, 32c + 32) (4 * bits bytes).  A lookup of a code PAIR (two adjacent dims of one token) returns the A-fragment
 // registers directly (hi parts, lo parts); k-step s: label 2c + e -> dim 32c + 4s + e, label 2c + 8 + e -> dim
-// 32c + 4s + 2 + e (e = 0, 1).  Queries enter as fp16 hi + lo B fragments: S = Kh.qh + Kh.ql + Kl.qh.
+// 32c + 4s + 2 + e (e = 0, 1).  Queries enter as fp16 hi + lo B fragments: S = Kh.qh + Kh.ql + Kl.qh (8 heads per kv head).
+// Up to 4 heads per kv head (kPacked) the hi parts of the queries take columns 0..3 of the n-tile and the lo parts columns
+// 4..7, and rows g + 8 of the A fragment carry the lo parts of the token in row g: the two registers a table read returns
+// are adjacent A registers as they come, an mma covers 8 tokens x 16 dims x (hi, lo) of both operands, and
+// S = (Kh + Kl).(qh + ql) is the sum of an accumulator's rows g and g + 8 and of columns n and n + 4 (lanes c and c ^ 2).
 //
 // Outputs.  The contraction runs over tokens, and a code stream never yields two tokens of one dim.  So the value table is
 // indexed by a SINGLE code and returns half2(hi, lo) of its centroid: the two halves sit on adjacent contraction labels
@@ -16,6 +20,8 @@
 // fp32-accurate values: O^T += [Vh | Vl] . [p ; p].  Thread (g, c) owns dims [16g, 16g + 16) (m-tile mt: row g -> dim
 // 16g + 2mt, row g + 8 -> dim 16g + 2mt + 1) of tokens 2c, 2c + 1, 2c + 8, 2c + 9, a contiguous 2 * bits bytes per token: the
 // tokens movmatrix.trans of the S fragment (rows g, g + 8) hands thread (g', c') -- rows 2c', 2c' + 1 and 2c' + 8, 2c' + 9.
+// The probabilities enter as hi + lo too: two B fragments (8 heads), or one with the hi parts in columns 0..3 and the lo
+// parts in columns 4..7 (kPacked; the two column halves of O^T are added when the state is folded or published).
 //
 // Queries, probabilities and all centroids therefore carry ~22 significant bits (fp16 hi + lo), which keeps the outputs
 // within the element-wise 2e-3 bound of the fp32 CPU statement.  Tables hold sigma * centroid with a per-codebook sigma
