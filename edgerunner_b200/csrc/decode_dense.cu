@@ -7,12 +7,18 @@ namespace er {
 
 using Dense4 = DenseMmaPolicy<4, 11, 1, 2>;
 using Dense8 = DenseMmaPolicy<8, 10, 1, 2>;
+constexpr int kDenseMmaMinSlots = 16384;   // group 2: rings at least this long take the tensor-core policy
 
 int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
     switch (group) {
         case 1: return launch_decode_policy<DensePolicy<1, 6, 2, 4>>(p, grid, stream);
-        // 12 consumer warps in two groups over 96-token tiles, 4 stages: best of the measured shapes on B200
-        case 2: return launch_decode_policy<DensePolicy<2, 6, 2, 4>>(p, grid, stream);
+        // Group 2: 12 consumer warps in two groups over 96-token tiles, 4 stages (best of the measured shapes on B200).
+        // The scalar policy is ahead on short rings (cfg1 shape, 4352 slots: 82.5 against 83.3 us per step) because its state
+        // is cheaper to set up and publish per visit; on long rings the tensor-core policy needs fewer instructions per byte
+        // and keeps a higher clock under the power cap (context 32768: 6.9 against 6.4 TB/s).  The ring capacity decides.
+        case 2:
+            if (p.addr.max_seq_len >= kDenseMmaMinSlots) return launch_decode_policy<DenseMmaPolicy<2, 6, 2, 4>>(p, grid, stream);
+            return launch_decode_policy<DensePolicy<2, 6, 2, 4>>(p, grid, stream);
         // groups 4 and 8 run both contractions on the tensor cores (the lane-owns-dims form needs 512 FMAs per lane and unit
         // for 4 heads and 128 query registers for 8): 11 consumer warps + producer keep the 168-register budget (warps
         // are allocated in fours); one group over 176-token tiles, 2 stages
@@ -25,7 +31,7 @@ int launch_decode_dense(int group, const DecodeParams& p, int grid, cudaStream_t
 int decode_dense_tile_tokens(int group) {
     switch (group) {
         case 1: return DensePolicy<1, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
-        case 2: return DensePolicy<2, 6, 2, 4>::kUnitsPerTile * kUnitTokens;
+        case 2: return DensePolicy<2, 6, 2, 4>::kUnitsPerTile * kUnitTokens;   // both policies of this group
         case 4: return Dense4::kUnitsPerTile * kUnitTokens;
         case 8: return Dense8::kUnitsPerTile * kUnitTokens;
         default: return 0;

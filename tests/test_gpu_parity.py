@@ -354,6 +354,17 @@ def test_group8_and_group4_tensor_core_policy(er, oracle, torch, layout, page_si
         _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=16, Hkv=4, ctx=3, steps=20, seed=42, page_size=page_size, decode_kernel=dk)
 
 
+@pytest.mark.parametrize("layout,page_size", [("head_major", 0), ("token_major", 0), ("paged", 16)])
+def test_group2_tensor_core_policy_on_long_rings(er, oracle, torch, layout, page_size):
+    """GQA group 2 takes the tensor-core policy in the persistent kernel when the ring holds 16384 tokens or more (the scalar
+    policy below that): ragged batches, several steps, every layout, contexts from a single row to several tiles."""
+    lay = getattr(er.Layout, layout)
+    _run_dense_config(er, oracle, torch, lay, L=2, B=3, Hq=16, Hkv=8, ctx=1100, steps=3, seed=50, page_size=page_size, ragged=True,
+                      max_seq_len=16384, decode_kernel=1)
+    _run_dense_config(er, oracle, torch, lay, L=1, B=2, Hq=4, Hkv=2, ctx=1, steps=19, seed=51, page_size=page_size, max_seq_len=16400,
+                      decode_kernel=1)
+
+
 @pytest.mark.parametrize("kernel,dk", KERNELS)
 def test_group1_and_tiny_contexts(er, oracle, torch, kernel, dk):
     _run_dense_config(er, oracle, torch, er.Layout.head_major, L=1, B=3, Hq=4, Hkv=4, ctx=40, steps=2, seed=5, ragged=True, decode_kernel=dk)
