@@ -88,6 +88,9 @@ WORKLOADS = {
                                    "TurboQuant turbo4 K / turbo4 V, fp16 norms, 64-token pages",
                               layers=36, batch=2, heads=32, kv_heads=8, ctx=131072, precision="turboquant", kbits=4, vbits=4,
                               norm="float16", layout="paged", page_size=64, theta=1.0e6),
+    "cfg4_decode_4layers": dict(name="cfg4 decode shape with 4 of its 36 layers and 2 sequences (about 1.1 GB on the device: profiler captures)",
+                                layers=4, batch=2, heads=32, kv_heads=8, ctx=131072, precision="turboquant", kbits=4, vbits=4,
+                                norm="float16", layout="paged", page_size=64, theta=1.0e6),
     # benchmark contract, configuration [4], its prefill leg: one 2048-token chunk of one sequence and one layer against the context
     # already in the cache (Qwen3-4B heads, TurboQuant turbo4/turbo4 rows in 64-token pages); tensor-core bound
     "cfg4_prefill": dict(name="cfg4 prefill chunk: Qwen3-4B heads, 2048 query rows at the end of a 131072-token context, "

@@ -7,13 +7,15 @@ namespace er {
 
 template <int KB, int VB>
 static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
-    // one group of 15 consumer warps over 240-token tiles, 3 stages: the fastest of the measured shapes for group 2 (3.55 ms
-    // per cfg2 step; two alternating groups of 7 warps 3.90, one group of 11 warps 3.98).  Group 4 keeps its merge buffers
-    // within shared memory with 11 warps, group 8 with 11 warps and 2 stages.
+    // one group of 15 consumer warps over 240-token tiles: the fastest of the measured shapes (group 2, cfg2: two alternating
+    // groups of 7 warps +7 %, one group of 11 warps +9 %).  Groups 1 and 2 run 3 stages; group 4 keeps its merge buffers and
+    // the 64 KB-aligned table within shared memory with 2 stages (cfg4 decode: 4.43 ms per step against 4.68 ms with 11 warps
+    // and 3 stages: the kernel is bound by shared-memory reads, and resident warps are what keeps that pipe busy); group 8
+    // (unpacked query fragments: 168 registers) stays at 11 warps and 2 stages.
     switch (group) {
         case 1: return launch_decode_policy<TurboMmaPolicy<1, KB, VB, 15, 1, 3>>(p, grid, stream);
         case 2: return launch_decode_policy<TurboMmaPolicy<2, KB, VB, 15, 1, 3>>(p, grid, stream);
-        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 11, 1, 3>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboMmaPolicy<4, KB, VB, 15, 1, 2>>(p, grid, stream);
         case 8: return launch_decode_policy<TurboMmaPolicy<8, KB, VB, 11, 1, 2>>(p, grid, stream);
         default: return kNotBuilt;
     }
