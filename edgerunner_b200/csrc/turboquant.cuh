@@ -264,7 +264,11 @@ struct TurboExpandParams {
 template <int BITS>
 __global__ void tq_expand_rows_f16_kernel(const __grid_constant__ TurboExpandParams p) {
     constexpr int kWords = tq_code_words(BITS);
-    const float* cent = tq_centroids<BITS>();
+    // the codebook in shared memory: its entries lie in distinct banks, so a warp's 32 different codes cost one access
+    // (the same reads from constant memory serialise, one pass per distinct code)
+    __shared__ float cent[1 << BITS];
+    if (threadIdx.x < (1 << BITS)) cent[threadIdx.x] = tq_centroids<BITS>()[threadIdx.x];
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     int len = *p.len_ptr;
     len = len < p.addr.max_seq_len ? len : p.addr.max_seq_len;
