@@ -1515,3 +1515,43 @@ def test_full_size_shapes_constant_value_rows(er, torch):
     e_pre = float((outp - want[None]).abs().max()) / scale
     print("configuration 4, 131072 tokens: constant-V error %.2e (decode), %.2e (prefill chunk) of the largest value" % (e_dec, e_pre))
     assert e_dec < 1e-5 and e_pre < 1e-5
+
+
+@pytest.mark.parametrize("precision,kbits,vbits", [("float16", 0, 0), ("q8_0", 0, 0), ("turboquantV2", 4, 3), ("turboquantV2", 4, 4)])
+def test_constant_value_rows_over_long_visits(er, torch, precision, kbits, vbits):
+    """The same size-independent property (constant V rows of a kv head come back unchanged) on launches large enough that every
+    consumer warp of a CTA walks more than 32 units of one visit -- the tensor-core policies then fold their accumulators into
+    the merge buffer several times (per-lane denominators gathered, packed column halves joined) before the visit is published.
+    Group 2 on head-major rings of 32832 slots: fp16 rows take the tensor-core policy there too."""
+    D, Hq, Hkv, B, L, ctx = 128, 16, 8, 4, 2, 32768
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77)
+    prec = getattr(er.Precision, precision)
+    kw = dict(key_type=kbits, value_type=vbits, norm_format=er.NormFormat.float16) if precision == "turboquantV2" else {}
+    cache = er.KVCache(ctx + 64, L, Hkv, D, prec, max_batch=B, **kw)
+    sp = er.step_params(rope_theta=1e6)
+    pattern = torch.randn((Hkv, D), generator=g, device="cuda").half().float()
+    for l in range(L):
+        for b in range(B):
+            for s0 in range(0, ctx, 16384):
+                cache.write_rows(l, b, s0, 16384, torch.randn((16384, Hkv, D), generator=g, device="cuda"),
+                                 pattern.expand(16384, Hkv, D).contiguous(), sp)
+    # what a stored pattern row reads back as in this format
+    one = er.KVCache(16, 1, Hkv, D, prec, **kw)
+    one.write_rows(0, 0, 0, 1, pattern[None].contiguous(), pattern[None].contiguous(), er.step_params(apply_rope=0))
+    if precision == "float16":
+        stored = pattern
+    elif precision == "q8_0":
+        stored = torch.as_tensor(np.asarray(one.retrieve_decoded_q8_0(0)[1]).reshape(Hkv, D)).cuda()
+    else:
+        stored = torch.as_tensor(np.asarray(one.retrieve_decoded_turboquant(0)[1]).reshape(Hkv, D)).cuda()
+    want = stored.repeat_interleave(Hq // Hkv, dim=0)
+    q = torch.randn((L, B, Hq, D), generator=g, device="cuda")
+    k = torch.randn((L, B, Hkv, D), generator=g, device="cuda")
+    out = torch.full((L, B, Hq, D), float("nan"), device="cuda")
+    cache.decode_step(q, k, pattern.expand(L, B, Hkv, D).contiguous(), out, Hq, sp)
+    torch.cuda.synchronize()
+    assert cache.device_status() == 0
+    err = float((out - want).abs().max() / want.abs().max())
+    print("%s K%d/V%d, %d token-heads per launch: constant-V error %.2e of the largest value" % (precision, kbits, vbits, L * B * Hkv * ctx, err))
+    assert err < 1e-5
