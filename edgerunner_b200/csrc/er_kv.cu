@@ -437,7 +437,7 @@ int32_t er_kv_create(const er_kv_config* c, er_kv** out) {
         default: return fail(ER_ERR_INVALID_ARGUMENT, "unknown precision %u", c->precision);
     }
     if (c->prefill_kernel > ER_PREFILL_KERNEL_MMA_SYNC) return fail(ER_ERR_INVALID_ARGUMENT, "unknown prefill_kernel %u", c->prefill_kernel);
-    if (c->decode_kernel > ER_DECODE_KERNEL_SLIM) return fail(ER_ERR_INVALID_ARGUMENT, "unknown decode_kernel %u", c->decode_kernel);
+    if (c->decode_kernel > ER_DECODE_KERNEL_SIMT) return fail(ER_ERR_INVALID_ARGUMENT, "unknown decode_kernel %u", c->decode_kernel);
     if (er_device_count() <= 0) return fail(ER_ERR_CUDA, "no CUDA device: this backend has no CPU fallback");
     er_kv* kv = new er_kv();
     kv->cfg = *c;
@@ -1293,7 +1293,8 @@ static int32_t simt_attention(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, co
 // float16 caches: launches over a small amount of rows (one layer of a small batch) skip the persistent kernel
 static bool uses_slim_kernel(const er_kv* kv, uint32_t layers) {
     const uint64_t capacity_bytes = static_cast<uint64_t>(layers) * kv->cfg.max_batch * kv->cfg.num_kv_heads * kv->cfg.max_seq_len * 2 * kRowBytesF16;
-    return kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM || (kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO && capacity_bytes <= (128ull << 20));
+    const bool automatic = kv->cfg.decode_kernel == ER_DECODE_KERNEL_AUTO || kv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT;
+    return kv->cfg.decode_kernel == ER_DECODE_KERNEL_SLIM || (automatic && capacity_bytes <= (128ull << 20));
 }
 
 static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads, uint32_t pending,
@@ -1330,7 +1331,9 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
     // 2-bit TurboQuant rows run on the SIMT kernel
     // (no tensor-core policy is built for them), and sliding windows over q8_0 / TurboQuant rows (a window start that is not a
     // multiple of 8 tokens breaks the 16-byte alignment the bulk copies of the side arrays need)
-    if (kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
+    // (balanced / aggressive rows with up to four heads per kv head have a tensor-core policy, OutlierMmaPolicy)
+    const bool outlier_simt = kv->outlier && (group > 4 || kv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT);
+    if (outlier_simt || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
         (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)) {
         const int32_t src = simt_attention(kv, kv, lb, le, q, out, num_heads, pending, 1, -1, -1, s, stream);
         if (src != ER_OK) return src;
@@ -1381,7 +1384,11 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         p.window = static_cast<int>(std::min<uint32_t>(s.sliding_window, 0x7fffffffu));
         p.wait_limit_us = kv->probe_wait_limit_us; p.withhold_tiles = kv->probe_withhold_tiles;
         p.scratch = kv->d_scratch; p.done_counter = kv->d_counters; p.status = kv->d_counters + 1; p.item_counters = kv->d_counters + 16;
-        if (kv->turbo)
+        if (kv->outlier) {
+            p.k_res_coef = kQjlScale * kv->cfg.key_residual_scale;
+            p.v_res_coef = kQjlScale * kv->cfg.value_residual_scale;
+            rc = decode_status(launch_decode_outlier(group, kv->ofmt.rb, kv->ofmt.hb, p, kv->num_sms, stream), group, kv->ofmt.rb, kv->ofmt.rb);
+        } else if (kv->turbo)
             rc = decode_status(launch_decode_turbo(group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type), p, kv->num_sms, stream),
                                group, static_cast<int>(kv->cfg.key_type), static_cast<int>(kv->cfg.value_type));
         else if (kv->q8)

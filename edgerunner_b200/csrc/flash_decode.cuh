@@ -74,6 +74,7 @@ struct DecodeParams {
     int num_peers;
     float* peer_out[8];
     float scale_log2;             // softmax scale * log2(e)
+    float k_res_coef, v_res_coef; // balanced / aggressive TurboQuant rows: sqrt(pi / 2) * residual scale of each side
     float rope_scaling;
     int apply_rope;
     // fp16 policy only: per-head RMS norm of Q and of the fused-append K row before RoPE (fused_qk_norm_rope_neox,

@@ -24,6 +24,8 @@ int decode_slim_splits(int group, int items, int max_units, int num_sms, size_t 
 int launch_decode_slim(int group, const DecodeParams& p, int splits, cudaStream_t stream);
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 int launch_decode_q8(int group, const DecodeParams& p, int grid, cudaStream_t stream);
+// balanced (3 / 5 bits) and aggressive (2 / 3 bits) TurboQuant rows, groups 1, 2, 4 (decode_outlier.cu); kNotBuilt otherwise
+int launch_decode_outlier(int group, int regular_bits, int high_bits, const DecodeParams& p, int grid, cudaStream_t stream);
 struct PrefillParams;
 int launch_prefill_f16(int group, const PrefillParams& p, int num_kv_heads, cudaStream_t stream);
 // tcgen05 version of the same kernel.  outer_extent: pages in the pool (page-major rows) or sequences (token-major rows)

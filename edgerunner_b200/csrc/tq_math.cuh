@@ -23,6 +23,7 @@ __host__ __device__ constexpr int tq_code_words(int bits) { return (kHeadDim * b
 static __constant__ float c_tq_cent2[4] = ER_TQ_CENTROIDS_2BIT;
 static __constant__ float c_tq_cent3[8] = ER_TQ_CENTROIDS_3BIT;
 static __constant__ float c_tq_cent4[16] = ER_TQ_CENTROIDS_4BIT;
+static __constant__ float c_tq_cent5[32] = ER_TQ_CENTROIDS_5BIT;
 static __constant__ uint32_t c_tq_signs1[4] = ER_TQ_SIGNS1_NEGMASK;
 static __constant__ uint32_t c_tq_signs2[4] = ER_TQ_SIGNS2_NEGMASK;
 
@@ -31,6 +32,11 @@ constexpr float kTqForwardScale = 0.08838834764831845f;   // 1/sqrt(Float(128)),
 template <int BITS>
 __device__ __forceinline__ const float* tq_centroids() {
     return BITS == 2 ? c_tq_cent2 : BITS == 3 ? c_tq_cent3 : c_tq_cent4;
+}
+
+// the codebook of a run-time bit width (2 .. 5)
+__device__ __forceinline__ const float* tq_centroids_rt(int bits) {
+    return bits == 2 ? c_tq_cent2 : bits == 3 ? c_tq_cent3 : bits == 4 ? c_tq_cent4 : c_tq_cent5;
 }
 
 // TurboQuantCodebook.code(for:) (TurboQuant.swift:692-697): index of the first threshold strictly greater

@@ -17,15 +17,11 @@
 
 namespace er {
 
-static __constant__ float c_tq_cent5[32] = ER_TQ_CENTROIDS_5BIT;
 static __constant__ float c_tq_thr2[3] = ER_TQ_THRESHOLDS_2BIT;
 static __constant__ float c_tq_thr3[7] = ER_TQ_THRESHOLDS_3BIT;
 static __constant__ float c_tq_thr4[15] = ER_TQ_THRESHOLDS_4BIT;
 static __constant__ float c_tq_thr5[31] = ER_TQ_THRESHOLDS_5BIT;
 
-__device__ __forceinline__ const float* tq_centroids_rt(int bits) {
-    return bits == 2 ? c_tq_cent2 : bits == 3 ? c_tq_cent3 : bits == 4 ? c_tq_cent4 : c_tq_cent5;
-}
 // TurboQuantCodebook.code(for:) with a run-time bit width: number of thresholds t with !(value < t).
 __device__ __forceinline__ uint32_t tq_code_for_rt(float v, int bits) {
     const float* thr = bits == 2 ? c_tq_thr2 : bits == 3 ? c_tq_thr3 : bits == 4 ? c_tq_thr4 : c_tq_thr5;

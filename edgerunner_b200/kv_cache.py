@@ -92,7 +92,7 @@ class KVCache:
         cfg.norm_format, cfg.max_batch, cfg.layout = int(norm_format), max_batch, int(layout)
         cfg.page_size, cfg.num_pages = page_size, num_pages
         cfg.prefill_kernel = int(prefill_kernel)     # 0 = automatic, 1 = always the mma.sync kernel (A/B measurements)
-        cfg.decode_kernel = int(decode_kernel)       # float16 caches: 0 = automatic, 1 = persistent kernel, 2 = slim kernel
+        cfg.decode_kernel = int(decode_kernel)       # float16 caches: 0 = automatic, 1 = persistent kernel, 2 = slim kernel; 3 = SIMT kernel for balanced / aggressive caches
         self._h = C.c_void_p()
         self._destroy = lib().er_kv_destroy      # held by the object: close() may run while the interpreter shuts down
         check(lib().er_kv_create(C.byref(cfg), C.byref(self._h)))

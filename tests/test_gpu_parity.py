@@ -1517,7 +1517,8 @@ def test_full_size_shapes_constant_value_rows(er, torch):
     assert e_dec < 1e-5 and e_pre < 1e-5
 
 
-@pytest.mark.parametrize("precision,kbits,vbits", [("float16", 0, 0), ("q8_0", 0, 0), ("turboquantV2", 4, 3), ("turboquantV2", 4, 4)])
+@pytest.mark.parametrize("precision,kbits,vbits", [("float16", 0, 0), ("q8_0", 0, 0), ("turboquantV2", 4, 3), ("turboquantV2", 4, 4),
+                                                   ("turboQuantBalanced", 0, 0), ("turboQuantAggressive", 0, 0)])
 def test_constant_value_rows_over_long_visits(er, torch, precision, kbits, vbits):
     """The same size-independent property (constant V rows of a kv head come back unchanged) on launches large enough that every
     consumer warp of a CTA walks more than 32 units of one visit -- the tensor-core policies then fold their accumulators into
@@ -1555,3 +1556,48 @@ def test_constant_value_rows_over_long_visits(er, torch, precision, kbits, vbits
     err = float((out - want).abs().max() / want.abs().max())
     print("%s K%d/V%d, %d token-heads per launch: constant-V error %.2e of the largest value" % (precision, kbits, vbits, L * B * Hkv * ctx, err))
     assert err < 1e-5
+
+
+@pytest.mark.parametrize("preset", ["turboQuantBalanced", "turboQuantAggressive"])
+@pytest.mark.parametrize("Hq,Hkv,layout", [(16, 8, "head_major"), (32, 8, "paged"), (4, 4, "head_major")])
+def test_outlier_presets_tensor_core_policy_against_simt_kernel(er, torch, preset, Hq, Hkv, layout):
+    """Balanced / aggressive rows at contexts of several tiles, residual terms of both sides on: the tensor-core policy of the
+    persistent kernel against the SIMT kernel on the same rows (both are held to the CPU restatement at small sizes by
+    test_outlier_preset_caches; er_kv_config.decode_kernel picks the kernel)."""
+    D, L, B = 128, 2, 3
+    lens = [2900, 517, 1]
+    T = 3008
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    kw = {}
+    if layout == "paged":
+        ps = 64
+        pages = (T // ps) * B
+        kw = dict(layout=er.Layout.paged, page_size=ps, num_pages=pages)
+    outs = []
+    fill = [(torch.randn((n, Hkv, D), generator=g, device="cuda"), torch.randn((n, Hkv, D), generator=g, device="cuda")) for n in lens]
+    q = torch.randn((L, B, Hq, D), generator=g, device="cuda")
+    k = torch.randn((L, B, Hkv, D), generator=g, device="cuda")
+    v = torch.randn((L, B, Hkv, D), generator=g, device="cuda")
+    sp = er.step_params(rope_theta=THETA_QWEN3)
+    for dk in (0, 3):
+        cache = er.KVCache(T, L, Hkv, D, getattr(er.Precision, preset), max_batch=B, key_residual_scale=1.0 / 64,
+                           value_residual_scale=1.0 / 128, decode_kernel=dk, **kw)
+        if layout == "paged":
+            perm = np.random.default_rng(3).permutation(pages)
+            for b in range(B):
+                cache.set_block_table(b, perm[b * (T // ps):(b + 1) * (T // ps)])
+        for l in range(L):
+            for b, n in enumerate(lens):
+                cache.write_rows(l, b, 0, n, fill[b][0], fill[b][1], sp)
+        out = torch.full((L, B, Hq, D), float("nan"), device="cuda")
+        for _ in range(2):   # two steps: the second one sees the row the first one appended
+            cache.decode_step(q, k, v, out, Hq, sp)
+        torch.cuda.synchronize()
+        assert cache.device_status() == 0
+        outs.append(out.cpu().numpy())
+        cache.close()
+    for l in range(L):
+        for b in range(B):
+            assert attention_err(outs[0][l, b], outs[1][l, b]) < 3e-5
+            assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
