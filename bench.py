@@ -67,6 +67,19 @@ WORKLOADS = {
                          page_size=16, theta=5.0e5),
     "cfg1_q8_4layers": dict(name="cfg1 shape with a q8_0 KV cache at context 32768, batch 8, 4 of the 28 layers (profiler captures)",
                             layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="q8_0", layout="head_major", theta=1.0e6),
+    # third next-tier row of the scope table: balanced / aggressive rows (32 high-precision channels, QJL signs) on the cfg2 shape
+    "cfg2_balanced": dict(name="cfg2 shape with balanced TurboQuant rows (3 / 5 bits, 96-byte rows), residual terms on",
+                          layers=28, batch=8, heads=16, kv_heads=8, ctx=32768, precision="balanced", residual_scale=1.0 / 128,
+                          layout="head_major", theta=1.0e6, outliers=True),
+    "cfg2_balanced_4layers": dict(name="cfg2 shape with balanced TurboQuant rows, 4 of its 28 layers (profiler captures)",
+                                  layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="balanced", residual_scale=1.0 / 128,
+                                  layout="head_major", theta=1.0e6, outliers=True),
+    "cfg2_balanced_4layers_simt": dict(name="cfg2 shape with balanced TurboQuant rows, 4 of its 28 layers, on the SIMT kernel",
+                                       layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="balanced", residual_scale=1.0 / 128,
+                                       decode_kernel=3, layout="head_major", theta=1.0e6, outliers=True),
+    "cfg2_aggressive_4layers": dict(name="cfg2 shape with aggressive TurboQuant rows (2 / 3 bits, 80-byte rows), 4 of its 28 layers",
+                                    layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="aggressive", residual_scale=1.0 / 128,
+                                    layout="head_major", theta=1.0e6, outliers=True),
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",
                          layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3,
                          norm="float16", layout="head_major", theta=1.0e6, outliers=True),
@@ -161,6 +174,9 @@ def row_bytes(w):
         return 2 * D * 2
     if w["precision"] == "q8_0":
         return 2 * (D // 32) * 34
+    if w["precision"] in ("balanced", "aggressive"):
+        # codes + side bits, mask 16 B, signs 16 B, two float norms, padded to 16 bytes: 96 / 80 bytes per row and side
+        return 2 * (96 if w["precision"] == "balanced" else 80)
     nb = 2 if w.get("norm", "float32") == "float16" else 4
     return (D * w["kbits"] + 31) // 32 * 4 + (D * w["vbits"] + 31) // 32 * 4 + 2 * nb
 
@@ -347,6 +363,10 @@ def build_cache(er, torch, w, lens, extra_tokens):
         cache = er.KVCache(cap, L, Hkv, D, er.Precision.float16, max_batch=B, layout=layout, **kw)
     elif w["precision"] == "q8_0":
         cache = er.KVCache(cap, L, Hkv, D, er.Precision.q8_0, max_batch=B, layout=layout, **kw)
+    elif w["precision"] in ("balanced", "aggressive"):
+        prec = er.Precision.turboQuantBalanced if w["precision"] == "balanced" else er.Precision.turboQuantAggressive
+        cache = er.KVCache(cap, L, Hkv, D, prec, max_batch=B, layout=layout, key_residual_scale=w.get("residual_scale", 0.0),
+                           value_residual_scale=w.get("residual_scale", 0.0), decode_kernel=w.get("decode_kernel", 0), **kw)
     else:
         nf = er.NormFormat.float16 if w.get("norm") == "float16" else er.NormFormat.float32
         cache = er.KVCache(cap, L, Hkv, D, er.Precision.turboquantV2, key_type=w["kbits"], value_type=w["vbits"], norm_format=nf,
@@ -546,7 +566,7 @@ def measure_decode(cx, args, w_full, lens, K, W, repeats, shard_heads, extras=()
     # fp16 rows: the timed region is K launches of the one fused kernel (plus K re-layout launches behind an NCCL all-gather)
     fused_single_launch = launches == K or (sharded and dec.exchange == "nccl" and w["precision"] == "float16" and launches == 2 * K)
     t_append = 0.0
-    kernel_name = "flash_decode_kernel"
+    kernel_name = "simt_decode_kernel" if w.get("decode_kernel") == 3 else "flash_decode_kernel"
     if w.get("per_layer") and launches == K * L:
         # one fused launch per layer: the region's time over its K * L launches
         t_attn, attn_bytes, timed_as = ms_compute / (K * L), bytes_region / (K * L), "the K x layers launches of the timed region, back to back on one stream"
@@ -738,7 +758,7 @@ def run_ours(args, w, lens):
                       "e2e": r.get("e2e"), "gpu_launches": r["gpu_launches"], **({"per_layer_launch": r["per_layer_launch"]} if "per_layer_launch" in r else {})}
 
     cpu = None
-    if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and not args.only_device_leg:
+    if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and not args.only_device_leg and w["precision"] not in ("balanced", "aggressive"):
         r = cpu_reference_leg(w, lens, args.cpu_seconds)
         cpu = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
 
