@@ -21,11 +21,14 @@ static int launch_group(int group, const DecodeParams& p, int grid, cudaStream_t
     }
 }
 
+int launch_decode_turbo_2bit(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);   // decode_turbo2.cu
+
 int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, int grid, cudaStream_t stream) {
     if (kbits == 4 && vbits == 4) return launch_group<4, 4>(group, p, grid, stream);
     if (kbits == 4 && vbits == 3) return launch_group<4, 3>(group, p, grid, stream);
     if (kbits == 3 && vbits == 3) return launch_group<3, 3>(group, p, grid, stream);
     if (kbits == 3 && vbits == 4) return launch_group<3, 4>(group, p, grid, stream);
+    if (kbits == 2 || vbits == 2) return launch_decode_turbo_2bit(group, kbits, vbits, p, grid, stream);
     return kNotBuilt;
 }
 

@@ -128,7 +128,7 @@ int32_t decode_status(int rc, int group, int kbits, int vbits) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (rc == 0) return ER_OK;
     if (rc == kNotBuilt)
-        return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4, 8 and presets turbo3/turbo4 are",
+        return fail(ER_ERR_UNSUPPORTED, "decode kernel for GQA group %d (key bits %d, value bits %d) is not built; groups 1, 2, 4, 8 and presets turbo2/turbo3/turbo4 are",
                     group, kbits, vbits);
     return fail(ER_ERR_CUDA, "flash_decode_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
 }
@@ -1327,14 +1327,13 @@ static int32_t attention_locked(er_kv* kv, uint32_t lb, uint32_t le, const float
         return ER_OK;
     }
     const int group = static_cast<int>(num_heads / kv->cfg.num_kv_heads);
-    // balanced / aggressive rows (the general form of gqa_attention_turboquant_decode, Shaders/TurboQuant.metal:1794-2001) and
-    // 2-bit TurboQuant rows run on the SIMT kernel
-    // (no tensor-core policy is built for them), and sliding windows over q8_0 / TurboQuant rows (a window start that is not a
-    // multiple of 8 tokens breaks the 16-byte alignment the bulk copies of the side arrays need)
-    // (balanced / aggressive rows with up to four heads per kv head have a tensor-core policy, OutlierMmaPolicy)
+    // The SIMT kernel serves: balanced / aggressive rows (the general form of gqa_attention_turboquant_decode,
+    // Shaders/TurboQuant.metal:1794-2001) with eight heads per kv head (OutlierMmaPolicy packs hi and lo parts into one n-tile:
+    // up to four), sliding windows over q8_0 / TurboQuant rows (a window start that is not a multiple of 8 tokens breaks the
+    // 16-byte alignment the bulk copies of the side arrays need), and TurboQuant caches created with ER_DECODE_KERNEL_SIMT.
     const bool outlier_simt = kv->outlier && (group > 4 || kv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT);
-    if (outlier_simt || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
-        (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)) {
+    const bool turbo_simt = kv->turbo && kv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT;
+    if (outlier_simt || turbo_simt || (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16)) {
         const int32_t src = simt_attention(kv, kv, lb, le, q, out, num_heads, pending, 1, -1, -1, s, stream);
         if (src != ER_OK) return src;
         if (advance != 0) {
@@ -1672,7 +1671,7 @@ int32_t er_kv_decode_step(er_kv* kv, uint32_t lb, uint32_t le, const float* q, c
     if ((rc = step_defaults(kv, sp, s)) != ER_OK) return rc;
     if ((rc = check_device(kv)) != ER_OK) return rc;
     const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kv->cfg.max_batch);
-    const bool simt_rows = kv->outlier || (kv->turbo && (kv->cfg.key_type == ER_TQ_TURBO2 || kv->cfg.value_type == ER_TQ_TURBO2)) ||
+    const bool simt_rows = kv->outlier || (kv->turbo && kv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT) ||
                            (s.sliding_window > 0 && kv->cfg.precision != ER_KV_FLOAT16 && kv->cfg.precision != ER_KV_FLOAT32);
     const bool one_launch = le - lb <= layers_per_launch || kv->cfg.precision == ER_KV_FLOAT32 || simt_rows;
     // fp16 rows: the attention kernel appends the new row itself (one launch per step).  TurboQuant rows are

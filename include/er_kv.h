@@ -122,8 +122,8 @@ enum { ER_PREFILL_KERNEL_AUTO = 0, ER_PREFILL_KERNEL_MMA_SYNC = 1 };
  * (Sources/EdgeRunner/Models/LlamaLanguageModel.swift:3867-3881): a few MB of rows per call.  AUTO runs such small calls
  * (capacity of the addressed rows up to 128 MB, GQA group 1/2/4, no sliding window) on a kernel without a staging
  * pipeline, and everything else on the persistent stream-K kernel; PERSISTENT / SLIM force one of them where its shape
- * rules allow (parity tests run both).  SIMT: balanced / aggressive TurboQuant caches run their decode attention on the plain
- * SIMT kernel instead of the tensor-core policy of the persistent kernel (the same A/B use; other caches: as AUTO). */
+ * rules allow (parity tests run both).  SIMT: TurboQuant caches (fixed presets, balanced, aggressive) run their decode attention
+ * on the plain SIMT kernel instead of the tensor-core policies of the persistent kernel (the same A/B use; other caches: as AUTO). */
 enum { ER_DECODE_KERNEL_AUTO = 0, ER_DECODE_KERNEL_PERSISTENT = 1, ER_DECODE_KERNEL_SLIM = 2, ER_DECODE_KERNEL_SIMT = 3 };
 
 typedef struct {
@@ -140,7 +140,7 @@ typedef struct {
     uint32_t page_size;     /* tokens per page, multiple of 16 (PAGED only) */
     uint32_t num_pages;     /* pages in the shared pool (PAGED only) */
     uint32_t prefill_kernel; /* ER_PREFILL_KERNEL_*: which chunked-prefill kernel er_kv_attention_prefill may use */
-    uint32_t decode_kernel;  /* ER_DECODE_KERNEL_*: float16 caches; SIMT: balanced / aggressive caches */
+    uint32_t decode_kernel;  /* ER_DECODE_KERNEL_*: float16 caches; SIMT: TurboQuant caches */
     float key_residual_scale;   /* BALANCED / AGGRESSIVE: weight of the QJL residual term of the scores (0 = off, the contract) */
     float value_residual_scale; /* ... and of the outputs; also the residualWeight of decoded value rows */
 } er_kv_config;

@@ -709,11 +709,19 @@ def test_outlier_preset_caches(er, oracle, torch, preset, Hq, Hkv, layout, scale
     assert wp < TOL, wp
 
 
-@pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4), (4, 2), (2, 3), (2, 2)])      # 2-bit sides: the SIMT kernel
+@pytest.mark.parametrize("kbits,vbits", [(4, 3), (4, 4), (3, 3), (3, 4), (4, 2), (3, 2), (2, 2), (2, 3), (2, 4)])
 def test_turboquant_decode_presets(er, oracle, torch, kbits, vbits):
+    """Every pair of the fixed presets turbo2 / turbo3 / turbo4 on the tensor-core policy of the persistent kernel."""
     w = _run_turbo_config(er, oracle, torch, L=2, B=1, Hq=16, Hkv=8, ctx=333, steps=2, seed=40 + kbits * 4 + vbits, kbits=kbits,
                           vbits=vbits, norm_format=er.NormFormat.float32, layout=er.Layout.head_major)
     print("turbo K%d/V%d max rel err %.3e" % (kbits, vbits, w))
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 8), (32, 8), (16, 2)])
+def test_turboquant_two_bit_values_other_groups(er, oracle, torch, Hq, Hkv):
+    """turbo4 keys with turbo2 values (the value type of the reference's boundary modes) for 1, 4 and 8 heads per kv head, paged."""
+    _run_turbo_config(er, oracle, torch, L=1, B=2, Hq=Hq, Hkv=Hkv, ctx=500, steps=2, seed=90 + Hq, kbits=4, vbits=2,
+                      norm_format=er.NormFormat.float16, layout=er.Layout.paged, page_size=32, ragged=True)
 
 
 def test_turboquant_config2_shape_compact_norms(er, oracle, torch):
