@@ -123,20 +123,23 @@ struct OutlierMmaPolicy {
     }
 
     // ---- per-channel lookups ----
-    // Running view of a row's side stream: bit 0 of `lo` is the first side bit of the next high-precision channel.
+    // Running view of a row's side stream over at most 16 channels (32 side bits): bit 0 of `lo` is the first side bit of the
+    // next high-precision channel.  `rank` = high-precision channels of the row before the view's first channel.
     struct SideBits {
-        uint32_t lo, hi;
+        uint32_t lo;
         __device__ __forceinline__ void start(uint32_t s0, uint32_t s1, int rank) {
             const int sh = rank * kSideW;   // 0 .. 32 kSideW
             if constexpr (kSideW == 1) {
                 lo = sh >= 32 ? 0u : s0 >> sh;
-                hi = 0u;
             } else {
-                if (sh >= 64) { lo = 0u; hi = 0u; }
-                else if (sh >= 32) { lo = s1 >> (sh - 32); hi = 0u; }
-                else { lo = __funnelshift_r(s0, s1, sh); hi = s1 >> sh; }
+                lo = sh >= 64 ? 0u : (sh >= 32 ? s1 >> (sh - 32) : __funnelshift_r(s0, s1, sh));
             }
         }
+    };
+    // What a 32-channel span needs to restart its view at channel 16.
+    struct SideSource {
+        uint32_t s0, s1;
+        int rank;
     };
 
     // Shared-window address of the table entry of channel J of a span whose regular codes start at bit 0 of w[]; channels
@@ -151,13 +154,9 @@ struct OutlierMmaPolicy {
         else v = w[word] << (7 - sh);
         uint32_t addr = (v & cm) | lut;
         if ((mask_bits >> J) & 1u) {
-            addr |= ((side.lo & ((1u << kSideW) - 1u)) << (RB + 7)) | (1u << (HB + 7));
-            if constexpr (kSideW == 1) {
-                side.lo >>= 1;
-            } else {
-                side.lo = __funnelshift_r(side.lo, side.hi, kSideW);
-                side.hi >>= kSideW;
-            }
+            // mask bit at index bit HB = RB + kSideW, side bits below it: one and-or, one shift-add
+            addr += ((side.lo & ((1u << kSideW) - 1u)) | (1u << kSideW)) << (RB + 7);
+            side.lo >>= kSideW;
         }
         return addr;
     }
@@ -180,7 +179,8 @@ struct OutlierMmaPolicy {
     // The span's bookkeeping words of one cached row: mask bits of the span, the side stream positioned at the span's first
     // high-precision channel, sign bits of the span.  HALF = false: the 32 channels of mask word `w`; true: its half `h`.
     template <bool HALF>
-    __device__ __forceinline__ static void span_words(uint32_t row, int w, int h, uint32_t& mask_bits, SideBits& side, uint32_t& signs) {
+    __device__ __forceinline__ static void span_words(uint32_t row, int w, int h, uint32_t& mask_bits, SideBits& side, uint32_t& signs,
+                                                      SideSource* src = nullptr) {
         int rank = 0;
         uint32_t mine = 0u;
 #pragma unroll
@@ -200,14 +200,19 @@ struct OutlierMmaPolicy {
         const uint32_t s0 = lds_u32_stage(row + kOffSide * 4);
         const uint32_t s1 = kSideW == 2 ? lds_u32_stage(row + (kOffSide + 1) * 4) : 0u;
         side.start(s0, s1, rank);
+        if (src != nullptr) { src->s0 = s0; src->s1 = s1; src->rank = rank; }
     }
 
     // Score k-step S for tokens g (sa) and g + 8 (sb): channels 4S .. 4S + 3 of the thread's 32; ss = SIGN . q of both tokens.
     template <int S>
     __device__ __forceinline__ static void score_steps(float (&sa)[4], float (&sb)[4], float (&ss)[4], const uint32_t (&ka)[RB],
                                                        const uint32_t (&kb)[RB], uint32_t ma, uint32_t mb, SideBits& da, SideBits& db,
-                                                       uint32_t ga, uint32_t gb, const State& st) {
+                                                       const SideSource& ra, const SideSource& rb, uint32_t ga, uint32_t gb, const State& st) {
         if constexpr (S < 8) {
+            if constexpr (S == 4) {   // channel 16: a view holds the side bits of 16 channels
+                da.start(ra.s0, ra.s1, ra.rank + __popc(ma & 0xFFFFu));
+                db.start(rb.s0, rb.s1, rb.rank + __popc(mb & 0xFFFFu));
+            }
             const uint32_t ea0 = lds_u32(entry_addr<4 * S>(ka, ma, da, st.lut_k)), ea1 = lds_u32(entry_addr<4 * S + 1>(ka, ma, da, st.lut_k));
             const uint32_t ea2 = lds_u32(entry_addr<4 * S + 2>(ka, ma, da, st.lut_k)), ea3 = lds_u32(entry_addr<4 * S + 3>(ka, ma, da, st.lut_k));
             const uint32_t eb0 = lds_u32(entry_addr<4 * S>(kb, mb, db, st.lut_k)), eb1 = lds_u32(entry_addr<4 * S + 1>(kb, mb, db, st.lut_k));
@@ -219,7 +224,7 @@ struct OutlierMmaPolicy {
                          __byte_perm(eb2, eb3, 0x7632), st.qh[S][0], st.qh[S][1]);
             mma_m16n8k16(ss, sign_pair(ga >> (4 * S)), sign_pair(gb >> (4 * S)), sign_pair(ga >> (4 * S + 2)), sign_pair(gb >> (4 * S + 2)),
                          st.qh[S][0], st.qh[S][1]);
-            score_steps<S + 1>(sa, sb, ss, ka, kb, ma, mb, da, db, ga, gb, st);
+            score_steps<S + 1>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
         }
     }
 
@@ -264,15 +269,16 @@ struct OutlierMmaPolicy {
         {
             uint32_t ka[RB], kb[RB], ma, mb, ga, gb;
             SideBits da, db;
+            SideSource ra, rb;
 #pragma unroll
             for (int i = 0; i < RB; ++i) {
                 ka[i] = lds_u32_stage(krow_a + (c * RB + i) * 4);
                 kb[i] = lds_u32_stage(krow_b + (c * RB + i) * 4);
             }
-            span_words<false>(krow_a, c, 0, ma, da, ga);
-            span_words<false>(krow_b, c, 0, mb, db, gb);
+            span_words<false>(krow_a, c, 0, ma, da, ga, &ra);
+            span_words<false>(krow_b, c, 0, mb, db, gb, &rb);
             float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f}, ss[4] = {0.f, 0.f, 0.f, 0.f};
-            score_steps<0>(sa, sb, ss, ka, kb, ma, mb, da, db, ga, gb, st);
+            score_steps<0>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
             s[0] = fmaf(kr0, ss[0], sa[0] + sa[2]);   // (Ch + Cl) . q + rho * SIGN . q of token g
             s[1] = fmaf(kr0, ss[1], sa[1] + sa[3]);
             s[2] = fmaf(kr1, ss[2], sb[0] + sb[2]);   // of token g + 8
