@@ -48,7 +48,9 @@ struct OutlierMmaPolicy {
     static constexpr int kSideBytes = kTileTokens * kRowBytes;     // K rows, then V rows
     static constexpr int kStageBytes = 2 * kSideBytes;
     static constexpr int kTableBytes = (2 << HB) * 128;            // [mask bit][code][32 lanes] half2 (hi, lo)
-    static constexpr int kExtraBytes = 2 * kTableBytes + 2 * GROUP * kHeadDim * 4;
+    // sign fragments: [4 sign bits][32 lanes] two registers of +-1 halves, one table per contraction (their bit orders differ)
+    static constexpr int kSignTableBytes = 16 * 256;
+    static constexpr int kExtraBytes = 2 * kTableBytes + 2 * kSignTableBytes + 2 * GROUP * kHeadDim * 4;
     static constexpr bool kRotated = true;
     static constexpr bool kFusedAppend = false;                    // rows are written by tq_outlier_append_kernel
     static constexpr int kFoldUnits = 32;
@@ -57,10 +59,17 @@ struct OutlierMmaPolicy {
     __device__ __forceinline__ static uint32_t table_addr(const uint8_t* extra) {
         return (smem_u32(extra) + kTableBytes - 1) & ~static_cast<uint32_t>(kTableBytes - 1);
     }
+    // the two sign tables follow the centroid table (whose size is a multiple of theirs, so they are aligned to their size)
+    __device__ __forceinline__ static uint32_t sign_table_addr(const uint8_t* extra) { return table_addr(extra) + kTableBytes; }
     __device__ __forceinline__ static float* rows_ptr(uint8_t* extra) {
-        return reinterpret_cast<float*>(extra + (table_addr(extra) + kTableBytes - smem_u32(extra)));
+        return reinterpret_cast<float*>(extra + (sign_table_addr(extra) + 2 * kSignTableBytes - smem_u32(extra)));
     }
     __device__ __forceinline__ static float* fin_ptr(uint8_t* extra) { return rows_ptr(extra) + GROUP * kHeadDim; }
+
+    // bits 0 and 1 of `bits` -> half2 (+-1, +-1): a set bit is +1 (TurboQuant.swift:1158: sign bit ? 1 : -1)
+    __device__ __forceinline__ static uint32_t sign_pair(uint32_t bits) {
+        return 0xBC00BC00u ^ ((bits & 1u) << 15) ^ ((bits & 2u) << 30);
+    }
 
     __device__ static bool init_extra(uint8_t* extra, int tid, int) {
         const uint32_t table = table_addr(extra);
@@ -69,6 +78,16 @@ struct OutlierMmaPolicy {
             const float cv = high ? tq_centroids_rt(HB)[code] : (code < (1 << RB) ? tq_centroids_rt(RB)[code] : 0.f);
             const float hi = __half2float(__float2half_rn(cv));
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + 4 * e), "r"(pack_half2(hi, cv - hi)) : "memory");
+        }
+        // index i = x | y << 2 (two sign bits of each of two tokens).  Scores: registers (pair of x, pair of y) -- two adjacent
+        // channels of token x, of token y.  Outputs: (bit 0 of x and y, bit 1 of x and y) -- one channel of both tokens each.
+        const uint32_t signs = sign_table_addr(extra);
+        for (int e = tid; e < 16 * 32; e += kThreads) {
+            const uint32_t i = e >> 5, x = i & 3u, y = i >> 2;
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(signs + 8 * e), "r"(sign_pair(x)), "r"(sign_pair(y)) : "memory");
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(signs + kSignTableBytes + 8 * e), "r"(sign_pair((x & 1u) | ((y & 1u) << 1))),
+                         "r"(sign_pair((x >> 1) | (y & 2u)))
+                         : "memory");
         }
         return true;
     }
@@ -107,8 +126,8 @@ struct OutlierMmaPolicy {
                                   int warp, int lane, int) {
         float* qrot = rows_ptr(extra);
         TS::rotate_queries(p, qrot, qrow, cs, warp, lane);
-        st.lut_k = table_addr(extra) | (lane << 2);
-        st.lut_v = st.lut_k;
+        st.lut_k = table_addr(extra) | (lane << 2);           // centroid table, 4-byte entries
+        st.lut_v = sign_table_addr(extra) | (lane << 3);      // sign tables, 8-byte entries: scores, then outputs
         const int g = lane >> 2, c = lane & 3;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
@@ -161,14 +180,13 @@ struct OutlierMmaPolicy {
         return addr;
     }
 
-    // bits 0 and 1 of `bits` -> half2 (+-1, +-1): a set bit is +1 (TurboQuant.swift:1158: sign bit ? 1 : -1)
-    __device__ __forceinline__ static uint32_t sign_pair(uint32_t bits) {
-        return 0xBC00BC00u ^ ((bits & 1u) << 15) ^ ((bits & 2u) << 30);
-    }
-    // bit B of x (low half) and bit B of y (high half) -> half2 (+-1, +-1)
+    // Two registers of +-1 halves for sign bits [B, B + 2) of x and of y (see init_extra for the two register orders).
     template <int B>
-    __device__ __forceinline__ static uint32_t sign_two(uint32_t x, uint32_t y) {
-        return 0xBC00BC00u ^ (((x >> B) & 1u) << 15) ^ (((y >> B) & 1u) << 31);
+    __device__ __forceinline__ static void sign_regs(uint32_t lut, uint32_t x, uint32_t y, uint32_t& r0, uint32_t& r1) {
+        uint32_t ix, iy;   // (bits of x) << 8 | (bits of y) << 10
+        if constexpr (B >= 8) ix = x >> (B - 8); else ix = x << (8 - B);
+        if constexpr (B >= 10) iy = y >> (B - 10); else iy = y << (10 - B);
+        lds_u32x2(lut + ((ix & 0x300u) | (iy & 0xC00u)), r0, r1);   // the table is aligned to 2 KB at least, not to its 4 KB: add
     }
     __device__ __forceinline__ static float lds_f32(uint32_t addr) {
         float v;
@@ -222,8 +240,10 @@ struct OutlierMmaPolicy {
                          __byte_perm(ea2, ea3, 0x7632), st.qh[S][0], st.qh[S][1]);
             mma_m16n8k16(sb, __byte_perm(eb0, eb1, 0x5410), __byte_perm(eb0, eb1, 0x7632), __byte_perm(eb2, eb3, 0x5410),
                          __byte_perm(eb2, eb3, 0x7632), st.qh[S][0], st.qh[S][1]);
-            mma_m16n8k16(ss, sign_pair(ga >> (4 * S)), sign_pair(gb >> (4 * S)), sign_pair(ga >> (4 * S + 2)), sign_pair(gb >> (4 * S + 2)),
-                         st.qh[S][0], st.qh[S][1]);
+            uint32_t g0, g1, g2, g3;   // (token g, token g + 8) x channels (4S, 4S + 1 | 4S + 2, 4S + 3)
+            sign_regs<4 * S>(st.lut_v, ga, gb, g0, g1);
+            sign_regs<4 * S + 2>(st.lut_v, ga, gb, g2, g3);
+            mma_m16n8k16(ss, g0, g1, g2, g3, st.qh[S][0], st.qh[S][1]);
             score_steps<S + 1>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
         }
     }
@@ -237,14 +257,16 @@ struct OutlierMmaPolicy {
         if constexpr (T < 8) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                const uint32_t a0 = lds_u32(entry_addr<2 * T>(vw[2 * j], vm[2 * j], vd[2 * j], st.lut_v));
-                const uint32_t a1 = lds_u32(entry_addr<2 * T + 1>(vw[2 * j], vm[2 * j], vd[2 * j], st.lut_v));
-                const uint32_t a2 = lds_u32(entry_addr<2 * T>(vw[2 * j + 1], vm[2 * j + 1], vd[2 * j + 1], st.lut_v));
-                const uint32_t a3 = lds_u32(entry_addr<2 * T + 1>(vw[2 * j + 1], vm[2 * j + 1], vd[2 * j + 1], st.lut_v));
+                const uint32_t a0 = lds_u32(entry_addr<2 * T>(vw[2 * j], vm[2 * j], vd[2 * j], st.lut_k));
+                const uint32_t a1 = lds_u32(entry_addr<2 * T + 1>(vw[2 * j], vm[2 * j], vd[2 * j], st.lut_k));
+                const uint32_t a2 = lds_u32(entry_addr<2 * T>(vw[2 * j + 1], vm[2 * j + 1], vd[2 * j + 1], st.lut_k));
+                const uint32_t a3 = lds_u32(entry_addr<2 * T + 1>(vw[2 * j + 1], vm[2 * j + 1], vd[2 * j + 1], st.lut_k));
                 mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bh[2 * j], bh[2 * j + 1]);
             }
-            mma_m16n8k16(st.acc[T], sign_two<2 * T>(vg[0], vg[1]), sign_two<2 * T + 1>(vg[0], vg[1]), sign_two<2 * T>(vg[2], vg[3]),
-                         sign_two<2 * T + 1>(vg[2], vg[3]), bs0, bs1);
+            uint32_t g0, g1, g2, g3;   // (channel 2T, channel 2T + 1) x tokens (2c, 2c + 1 | 2c + 8, 2c + 9)
+            sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[0], vg[1], g0, g1);
+            sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[2], vg[3], g2, g3);
+            mma_m16n8k16(st.acc[T], g0, g1, g2, g3, bs0, bs1);
             value_tiles<T + 1>(st, vw, vm, vd, vg, bh, bs0, bs1);
         }
     }
