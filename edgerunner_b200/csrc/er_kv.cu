@@ -1450,6 +1450,51 @@ static int32_t check_pair(const er_kv* kk, const er_kv* vv) {
     return ER_OK;
 }
 
+// q8_0 keys with TurboQuant values of a fixed preset run the persistent kernel (Q8KTurboVPolicy); every other pair, sliding windows,
+// sharded outputs and caches created with ER_DECODE_KERNEL_SIMT run the SIMT kernel.
+static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32_t num_heads, const er_step_params& s) {
+    if (!kk->q8 || !vv->turbo || kk->cfg.head_dim != kHeadDim || vv->cfg.head_dim != kHeadDim) return false;
+    if (s.sliding_window != 0 || kk->out_heads_total > 0) return false;
+    if (kk->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT || vv->cfg.decode_kernel == ER_DECODE_KERNEL_SIMT) return false;
+    if (num_heads == 0 || num_heads % kk->cfg.num_kv_heads != 0) return false;
+    const uint32_t group = num_heads / kk->cfg.num_kv_heads;
+    return group == 1 || group == 2 || group == 4 || group == 8;
+}
+
+// kk->mu is held by the caller; positions, scratch and counters are the key cache's.
+static int32_t pair_attention_tensor_core(er_kv* kk, er_kv* vv, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads,
+                                          uint32_t pending, const er_step_params& s, cudaStream_t stream) {
+    const int group = static_cast<int>(num_heads / kk->cfg.num_kv_heads);
+    const uint32_t layers_per_launch = std::max<uint32_t>(1, kMaxPairs / kk->cfg.max_batch);
+    if (kk->cfg.max_batch > static_cast<uint32_t>(kMaxPairs)) return fail(ER_ERR_UNSUPPORTED, "max_batch %u > %d", kk->cfg.max_batch, kMaxPairs);
+    for (uint32_t l0 = lb; l0 < le; l0 += layers_per_launch) {
+        const uint32_t l1 = std::min(le, l0 + layers_per_launch);
+        const size_t off = static_cast<size_t>(l0 - lb) * kk->cfg.max_batch * num_heads * kHeadDim;
+        DecodeParams p{};
+        p.q = q + off; p.out = out + off;
+        p.k_base = kk->k_slab; p.k_layer_stride_bytes = kk->k_layer_stride;
+        p.kn_base = kk->kn_slab; p.n_layer_stride_bytes = kk->n_layer_stride;
+        p.v_base = vv->v_slab; p.v_layer_stride_bytes = vv->v_layer_stride;
+        p.vn_base = vv->vn_slab; p.vn_layer_stride_bytes = vv->n_layer_stride;
+        p.norm_fp16 = vv->norm_bytes == 2;
+        p.lengths = kk->d_lengths; p.layer_begin = static_cast<int>(l0); p.num_layers = static_cast<int>(l1 - l0);
+        p.batch = static_cast<int>(kk->cfg.max_batch); p.num_q_heads = static_cast<int>(num_heads);
+        p.pending = static_cast<int>(pending);
+        p.trace = nullptr;
+        p.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+        p.apply_rope = s.apply_rope ? 1 : 0; p.rope_scaling = s.rope_scaling;
+        if (p.apply_rope) p.inv_freq = kk->freq(s.rope_theta);
+        p.addr = kk->addressing();
+        p.addr_v = vv->addressing();
+        p.wait_limit_us = kk->probe_wait_limit_us; p.withhold_tiles = kk->probe_withhold_tiles;
+        p.scratch = kk->d_scratch; p.done_counter = kk->d_counters; p.status = kk->d_counters + 1; p.item_counters = kk->d_counters + 16;
+        const int32_t rc = decode_status(launch_decode_q8k_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 8,
+                                         static_cast<int>(vv->cfg.value_type));
+        if (rc != ER_OK) return rc;
+    }
+    return ER_OK;
+}
+
 int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32_t lb, uint32_t le, const float* q, float* out, uint32_t num_heads,
                                     uint32_t pending, const er_step_params* sp, void* stream) {
     if (!key_cache || !value_cache || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
@@ -1463,6 +1508,8 @@ int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32
                          static_cast<size_t>(key_cache->cfg.max_batch) * num_heads, s.q_norm_weight, lb, s, static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(key_cache->mu);
+    if (pair_has_tensor_core_policy(key_cache, value_cache, num_heads, s))
+        return pair_attention_tensor_core(key_cache, value_cache, lb, le, q, out, num_heads, pending ? 1 : 0, s, static_cast<cudaStream_t>(stream));
     return simt_attention(key_cache, value_cache, lb, le, q, out, num_heads, pending ? 1 : 0, 1, -1, -1, s, static_cast<cudaStream_t>(stream));
 }
 

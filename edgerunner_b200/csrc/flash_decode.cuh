@@ -84,6 +84,10 @@ struct DecodeParams {
     int norm_stride;
     float rms_eps;
     KVAddressing addr;
+    // Layers whose keys and values live in two caches (different row formats): the value cache's addressing and the layer
+    // stride of its side array; k_* / kn_* / addr / lengths then describe the key cache, v_* / vn_* the value cache.
+    KVAddressing addr_v;
+    int64_t vn_layer_stride_bytes;
     float* scratch;               // [gridDim.x][2][GROUP][130]
     int* item_counters;           // [pairs * kv heads], zero between launches
     int* done_counter;            // zero between launches
@@ -246,6 +250,37 @@ __device__ __forceinline__ void mma_state_fold(float (&m)[2], float (&l)[2], flo
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
     __syncwarp();
+}
+
+// One unit's step of the online softmax of the tensor-core policies: s = the thread's four scores (token g | g + 8) x (head 2c |
+// 2c + 1) in the log2 domain (-inf where masked; token 0 of a unit is always valid), pr = their probabilities against the
+// (possibly grown) running maxima.  The cross-lane maximum and the rescale of the accumulators run only when some score exceeds
+// a running maximum; the denominators stay per-lane partial sums until the state is read (State::gather).
+template <class ST>
+__device__ __forceinline__ void mma_softmax_step(ST& st, const float (&s)[4], float (&pr)[4]) {
+    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+    float m0 = st.m[0], m1 = st.m[1];
+    if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        m0 = fmaxf(m0, mx0);
+        m1 = fmaxf(m1, mx1);
+        const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
+        st.l[0] *= corr0;
+        st.l[1] *= corr1;
+        st.m[0] = m0;
+        st.m[1] = m1;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
+        }
+    }
+    pr[0] = fast_exp2(s[0] - m0); pr[1] = fast_exp2(s[1] - m1); pr[2] = fast_exp2(s[2] - m0); pr[3] = fast_exp2(s[3] - m1);
+    st.l[0] += pr[0] + pr[2];
+    st.l[1] += pr[1] + pr[3];
 }
 
 template <int GROUP, int UNITS_PER_TILE = 8, int WARP_GROUPS = 1, int STAGES = 3>

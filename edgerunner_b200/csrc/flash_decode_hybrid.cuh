@@ -1,0 +1,132 @@
+// Layers whose keys are q8_0 rows and whose values are TurboQuant rows of a fixed preset (gqa_attention_q8k_turboquant_decode,
+// Shaders/TurboQuant.metal:1651-1792; chosen per layer by TurboQuantV2Contract, TurboQuant.swift:432-488: earlyQ8KeyLayers,
+// a q8_0 key cache type) in the persistent flash-decode kernel.  The two sides live in two caches of the same geometry, so
+// DecodeParams names two addressings: k_* / kn_* / addr / lengths describe the key cache, v_* / vn_* / addr_v the value cache.
+//
+// Scores are Q8MmaPolicy's (queries in their own space, int8 exact in fp16, one accumulator per 32-element block), outputs
+// are TurboMmaPolicy's (value centroids looked up as fp16 hi + lo pairs, accumulated in the rotated space, one inverse
+// transform after the merge); the fragment layouts of the two policies meet in the score fragment (token g | g + 8) x
+// (head 2c | 2c + 1), which both use.  Stage = K int8 rows | K block scales | V codes | V norms.
+#pragma once
+
+#include "flash_decode_q8.cuh"
+
+namespace er {
+
+template <int GROUP, int VBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
+struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
+    using TM = TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;   // tables, value lookups, state, output transform
+    using Q8 = Q8MmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;                    // query fragments, scores
+    using State = typename TM::State;
+    static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
+    static constexpr int kVW = tq_code_words(VBITS);
+    static constexpr int kOffKs = kTileTokens * 128;
+    static constexpr int kOffVc = kOffKs + kTileTokens * 8;
+    static constexpr int kOffVn = kOffVc + kTileTokens * kVW * 4;
+    static constexpr int kStageBytes = kOffVn + kTileTokens * 4;
+    static_assert(TM::kPacked == Q8::kPacked, "both sides pack the hi and lo parts of their B operands the same way");
+
+    template <class WAIT>
+    __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
+                                      int t0, int ntok, int lane, int /*ring start: fp16 rows only*/, WAIT&& wait_free) {
+        const int nb = p.norm_fp16 ? 2 : 4;
+        const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
+        const uint8_t* ks = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
+        const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        const uint8_t* vn = p.vn_base + static_cast<int64_t>(layer) * p.vn_layer_stride_bytes;
+        // page segments of the tile in each cache (a head-major cache is one page per sequence)
+        const int kps = p.addr.page_size, vps = p.addr_v.page_size;
+        const int kfirst = t0 / kps, kseg = (t0 + ntok - 1) / kps - kfirst + 1;
+        const int vfirst = t0 / vps, vseg = (t0 + ntok - 1) / vps - vfirst + 1;
+        wait_free();
+        if (lane == 0) {   // side copies are rounded up to 16 bytes per page segment
+            uint32_t bytes = static_cast<uint32_t>(ntok) * (128u + kVW * 4u);
+            for (int i = 0; i < kseg; ++i) {
+                const int tb = max(t0, (kfirst + i) * kps), te = min(t0 + ntok, (kfirst + i + 1) * kps);
+                bytes += (static_cast<uint32_t>(te - tb) * 8u + 15u) & ~15u;
+            }
+            for (int i = 0; i < vseg; ++i) {
+                const int tb = max(t0, (vfirst + i) * vps), te = min(t0 + ntok, (vfirst + i + 1) * vps);
+                bytes += (static_cast<uint32_t>(te - tb) * nb + 15u) & ~15u;
+            }
+            mbar_arrive_expect_tx(bar, bytes);
+        }
+        __syncwarp();
+        for (int c = lane; c < 2 * (kseg + vseg); c += 32) {
+            const bool value_side = c >= 2 * kseg;
+            const int i = value_side ? c - 2 * kseg : c, kind = i & 1, sgi = i >> 1;
+            const int ps = value_side ? vps : kps, first = value_side ? vfirst : kfirst;
+            const int tb = max(t0, (first + sgi) * ps), te = min(t0 + ntok, (first + sgi + 1) * ps);
+            const uint32_t rows = static_cast<uint32_t>(te - tb);
+            const int64_t row = row_index(value_side ? p.addr_v : p.addr, seq, head, tb);
+            if (!value_side) {
+                if (kind == 0) bulk_g2s(stage + (tb - t0) * 128, kc + row * 128, rows * 128, bar);
+                else bulk_g2s(stage + kOffKs + (tb - t0) * 8, ks + row * 8, (rows * 8 + 15u) & ~15u, bar);
+            } else {
+                if (kind == 0) bulk_g2s(stage + kOffVc + (tb - t0) * kVW * 4, vc + row * (kVW * 4), rows * kVW * 4, bar);
+                else bulk_g2s(stage + kOffVn + (tb - t0) * nb, vn + row * nb, (rows * nb + 15u) & ~15u, bar);
+            }
+        }
+    }
+
+    // queries stay in their own space (q8_0 keys are not rotated); the tables are the value side's
+    __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t* extra, int, int lane, int) {
+        const TurboSmemPlan pl = TM::plan(extra);
+        st.lut_k = pl.lut_k | (lane << 3);
+        st.lut_v = pl.lut_v | (lane << 3);
+        Q8::load_q_fragments(p, st, qrow, cs, lane);
+    }
+
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
+                                        const uint8_t*, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        const uint32_t sbase = smem_u32(stage);
+        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        // value codes: dims [16g, 16g + 16) of tokens 2c, 2c + 1, 2c + 8, 2c + 9 (TurboMmaPolicy's value layout), read ahead of the scores
+        uint32_t vlo[4], vhi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t row = sbase + kOffVc + (unit * kUnitTokens + 2 * c + (j & 1) + 8 * (j >> 1)) * kVW * 4;
+            if constexpr (VBITS == 4) {
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(vlo[j]), "=r"(vhi[j]) : "r"(row + 8 * g) : "memory");
+            } else if constexpr (VBITS == 3) {
+                const uint32_t w = row + ((3 * g) >> 1) * 4;
+                const uint32_t wa = lds_u32_stage(w), wb = lds_u32_stage(w + 4);
+                const uint32_t sh = (g & 1) * 16;
+                vlo[j] = __funnelshift_r(wa, wb, sh);
+                vhi[j] = wb >> sh;
+            } else {
+                vlo[j] = lds_u32_stage(row + 4 * g);
+                vhi[j] = 0;
+            }
+        }
+        const int r0 = unit * kUnitTokens + g;
+        constexpr float inv_sv = 1.f / tq_fp16_scale<VBITS>();
+        const float vn0 = ok0 ? TM::load_norm(stage + kOffVn, r0, p.norm_fp16) * inv_sv : 0.f;
+        const float vn1 = ok1 ? TM::load_norm(stage + kOffVn, r0 + 8, p.norm_fp16) * inv_sv : 0.f;
+
+        float s[4], pr[4];
+        Q8::unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        mma_softmax_step(st, s, pr);
+
+        // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed and duplicated on the (hi, lo) labels of a centroid
+        const float w0 = pr[0] * vn0, w1 = pr[1] * vn0, w2 = pr[2] * vn1, w3 = pr[3] * vn1;
+        const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+        if constexpr (TM::kPacked) {
+            const uint32_t x0 = movmatrix_trans(c < 2 ? hi01 : lo01), x1 = movmatrix_trans(c < 2 ? hi23 : lo23);
+            const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
+            TM::template value_tiles<0>(st, vlo, vhi, bh, bh);
+        } else {
+            const uint32_t x0 = movmatrix_trans(hi01), x1 = movmatrix_trans(hi23);
+            const uint32_t y0 = movmatrix_trans(lo01), y1 = movmatrix_trans(lo23);
+            const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
+            const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
+            TM::template value_tiles<0>(st, vlo, vhi, bh, bl);
+        }
+    }
+};
+
+}  // namespace er

@@ -157,6 +157,11 @@ struct Q8MmaPolicy {
     // Q row (NeoX-rotated when asked) -> B fragments.  k-step 2b + u of block b: label 2c + e -> dim 32b + 8c + 4u + e,
     // label 2c + 8 + e -> dim 32b + 8c + 4u + 2 + e; thread (g, c) holds head g.
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane, int) {
+        load_q_fragments(p, st, qrow, cs, lane);
+    }
+    // ST: any state with qh / ql fragments and reset() (the policies of layers with q8_0 keys and other values share this)
+    template <class ST>
+    __device__ static void load_q_fragments(const DecodeParams& p, ST& st, const float* qrow, const float2* cs, int lane) {
         const int g = lane >> 2, c = lane & 3;
         const int head = kPacked ? (g & 3) : g;   // packed: column g carries head g % 4, its hi part below column 4
 #pragma unroll
@@ -203,24 +208,35 @@ struct Q8MmaPolicy {
         st.reset();
     }
 
-    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
-                                        const uint8_t*, int lane) {
-        const int g = lane >> 2, c = lane & 3;
-        const uint32_t sbase = smem_u32(stage);
-        const int r0 = unit * kUnitTokens + g;
-        const uint32_t krow = sbase + r0 * 128 + 32 * c, vrow = sbase + kOffV + r0 * 128 + 32 * c;
-        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
-        auto load_row = [](uint32_t addr, uint32_t (&w)[8]) {   // words 2b, 2b + 1 = this thread's 8 bytes of block b
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr + 16) : "memory");
-        };
+    // words 2b, 2b + 1 = the thread's 8 bytes of block b of a cached row
+    __device__ __forceinline__ static void load_row_words(uint32_t addr, uint32_t (&w)[8]) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr) : "memory");
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr + 16) : "memory");
+    }
+    // a row's four block scales (fp16), zeros for a row that was never copied
+    __device__ __forceinline__ static void load_scales4(uint32_t addr, float (&out)[4], bool ok) {
+        uint32_t w[2];
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr) : "memory");
+        const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&w[0]));
+        const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&w[1]));
+        out[0] = ok ? f01.x : 0.f; out[1] = ok ? f01.y : 0.f; out[2] = ok ? f23.x : 0.f; out[3] = ok ? f23.y : 0.f;
+    }
 
-        // ---- scores: one accumulator per 32-element block ----
-        float sb[4][4];
+    // Scores of one unit, s = (token g | g + 8) x (head 2c | 2c + 1) in the log2 domain, -inf for rows at or past nvalid.
+    // krows / kscales: shared-window addresses of the tile's int8 rows (128 B per row) and block scales (8 B per row).
+    // ST: any state with the query fragments load_q_fragments wrote.
+    template <class ST>
+    __device__ __forceinline__ static void unit_scores(const DecodeParams& p, uint32_t krows, uint32_t kscales, int unit, int nvalid,
+                                                       const ST& st, int lane, float (&s)[4]) {
+        const int g = lane >> 2, c = lane & 3;
+        const int r0 = unit * kUnitTokens + g;
+        const uint32_t krow = krows + r0 * 128 + 32 * c;
+        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        float sb[4][4];   // one accumulator per 32-element block
         {
             uint32_t k0[8], k1[8];
-            load_row(krow, k0);
-            load_row(krow + 8 * 128, k1);
+            load_row_words(krow, k0);
+            load_row_words(krow + 8 * 128, k1);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
 #pragma unroll
@@ -235,23 +251,9 @@ struct Q8MmaPolicy {
                 }
             }
         }
-        float ks0[4], ks1[4], vs0[4], vs1[4];
-        {
-            uint32_t w[2];
-            auto load4 = [&](uint32_t addr, float (&out)[4], bool ok) {
-                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr) : "memory");
-                const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&w[0]));
-                const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&w[1]));
-                out[0] = ok ? f01.x : 0.f; out[1] = ok ? f01.y : 0.f; out[2] = ok ? f23.x : 0.f; out[3] = ok ? f23.y : 0.f;
-            };
-            load4(sbase + kOffKs + r0 * 8, ks0, ok0);
-            load4(sbase + kOffKs + (r0 + 8) * 8, ks1, ok1);
-            load4(sbase + kOffVs + r0 * 8, vs0, ok0);
-            load4(sbase + kOffVs + (r0 + 8) * 8, vs1, ok1);
-#pragma unroll
-            for (int b = 0; b < 4; ++b) { vs0[b] *= kProbScale; vs1[b] *= kProbScale; }
-        }
-        float s[4];   // (token g | g + 8) x (head 2c | 2c + 1)
+        float ks0[4], ks1[4];
+        load_scales4(kscales + r0 * 8, ks0, ok0);
+        load_scales4(kscales + (r0 + 8) * 8, ks1, ok1);
         s[0] = ks0[0] * sb[0][0] + ks0[1] * sb[1][0] + ks0[2] * sb[2][0] + ks0[3] * sb[3][0];
         s[1] = ks0[0] * sb[0][1] + ks0[1] * sb[1][1] + ks0[2] * sb[2][1] + ks0[3] * sb[3][1];
         s[2] = ks1[0] * sb[0][2] + ks1[1] * sb[1][2] + ks1[2] * sb[2][2] + ks1[3] * sb[3][2];
@@ -264,6 +266,22 @@ struct Q8MmaPolicy {
         s[1] = ok0 ? s[1] * p.scale_log2 : -INFINITY;
         s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
         s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
+    }
+
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
+                                        const uint8_t*, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        const uint32_t sbase = smem_u32(stage);
+        const int r0 = unit * kUnitTokens + g;
+        const uint32_t vrow = sbase + kOffV + r0 * 128 + 32 * c;
+        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        float s[4];   // (token g | g + 8) x (head 2c | 2c + 1)
+        unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        float vs0[4], vs1[4];
+        load_scales4(sbase + kOffVs + r0 * 8, vs0, ok0);
+        load_scales4(sbase + kOffVs + (r0 + 8) * 8, vs1, ok1);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) { vs0[b] *= kProbScale; vs1[b] *= kProbScale; }
 
         // The running maxima change only when some token of the unit exceeds them (always in a fresh state: token 0 of a unit
         // is valid, its score finite): the cross-lane maximum and the rescale run only then.  The denominators stay per-lane
@@ -293,8 +311,8 @@ struct Q8MmaPolicy {
         st.l[1] += p1 + p3;
         // ---- outputs, block by block: B = (p * vScale[block]) as fp16 hi + lo, A = transposed int8 pairs ----
         uint32_t v0[8], v1[8];
-        load_row(vrow, v0);
-        load_row(vrow + 8 * 128, v1);
+        load_row_words(vrow, v0);
+        load_row_words(vrow + 8 * 128, v1);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const float w0 = p0 * vs0[b], w1 = p1 * vs0[b], w2 = p2 * vs1[b], w3 = p3 * vs1[b];

@@ -35,6 +35,7 @@ struct TurboStaging {
     static constexpr bool kRotated = true;
     static constexpr bool kFusedAppend = false;   // rows are quantised by the separate append kernel
     static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
+    static_assert(UNITS_PER_TILE * WARP_GROUPS >= GROUP, "one consumer warp per query head rotates it and transforms its output back");
     __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
                                          const float2*, int) {}
     template <class WAIT>

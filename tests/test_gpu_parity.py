@@ -1609,3 +1609,58 @@ def test_outlier_presets_tensor_core_policy_against_simt_kernel(er, torch, prese
         for b in range(B):
             assert attention_err(outs[0][l, b], outs[1][l, b]) < 3e-5
             assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
+
+
+@pytest.mark.parametrize("vbits", [2, 3, 4])
+@pytest.mark.parametrize("Hq,Hkv,layout", [(16, 8, "head_major"), (32, 8, "paged"), (4, 4, "head_major"), (16, 2, "paged")])
+def test_q8_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(er, torch, vbits, Hq, Hkv, layout):
+    """Layers with q8_0 keys and TurboQuant values (gqa_attention_q8k_turboquant_decode; two caches): the tensor-core policy of
+    the persistent kernel against the SIMT kernel on the same rows, contexts of several tiles, ragged, head-major and paged,
+    groups 1 / 2 / 4 / 8, an appended row pending (both kernels are held to fp32 attention over the decoded rows at small
+    sizes by test_mixed_family_layers_through_pair_caches; er_kv_config.decode_kernel picks the kernel)."""
+    D, L, B = 128, 2, 3
+    lens = [2900, 517, 1]
+    T = 3008
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    fill = [(torch.randn((n, Hkv, D), generator=g, device="cuda"), torch.randn((n, Hkv, D), generator=g, device="cuda")) for n in lens]
+    q = torch.randn((L, B, Hq, D), generator=g, device="cuda")
+    k = torch.randn((L, B, Hkv, D), generator=g, device="cuda")
+    v = torch.randn((L, B, Hkv, D), generator=g, device="cuda")
+    sp = er.step_params(rope_theta=THETA_QWEN3)
+    outs = []
+    for dk in (0, 3):
+        kw = {}
+        if layout == "paged":
+            ps = 64
+            pages = (T // ps) * B
+            kw = dict(layout=er.Layout.paged, page_size=ps, num_pages=pages)
+        kc = er.KVCache(T, L, Hkv, D, er.Precision.q8_0, max_batch=B, decode_kernel=dk, **kw)
+        # the value cache's pages are laid out on their own (another permutation of another pool)
+        vc = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=vbits, value_type=vbits, norm_format=er.NormFormat.float16,
+                        max_batch=B, decode_kernel=dk, **kw)
+        if layout == "paged":
+            for cache, seed in ((kc, 3), (vc, 4)):
+                perm = np.random.default_rng(seed).permutation(pages)
+                for b in range(B):
+                    cache.set_block_table(b, perm[b * (T // ps):(b + 1) * (T // ps)])
+        for cache in (kc, vc):
+            for l in range(L):
+                for b, n in enumerate(lens):
+                    cache.write_rows(l, b, 0, n, fill[b][0], fill[b][1], sp)
+        out = torch.full((L, B, Hq, D), float("nan"), device="cuda")
+        for _ in range(2):   # two steps: the second one sees the row the first one appended
+            kc.append_rope_kv(k, v, sp)
+            vc.append_rope_kv(k, v, sp)
+            kc.attention_decode_with_values_of(vc, q, out, Hq, sp, pending=1)
+            kc.advance(1)
+            vc.advance(1)
+        torch.cuda.synchronize()
+        assert kc.device_status() == 0 and vc.device_status() == 0
+        outs.append(out.cpu().numpy())
+        kc.close()
+        vc.close()
+    for l in range(L):
+        for b in range(B):
+            assert attention_err(outs[0][l, b], outs[1][l, b]) < 3e-5
+            assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
