@@ -1,4 +1,4 @@
-// Instantiations of the persistent flash-decode kernel for layers with q8_0 keys and TurboQuant values (two caches).
+// Instantiations of the persistent flash-decode kernel for layers whose keys and values use different row formats (two caches).
 #include "flash_decode_hybrid.cuh"
 #include "launchers.h"
 
@@ -23,6 +23,30 @@ int launch_decode_q8k_turbov(int group, int vbits, const DecodeParams& p, int gr
     if (vbits == 4) return launch_group<4>(group, p, grid, stream);
     if (vbits == 3) return launch_group<3>(group, p, grid, stream);
     if (vbits == 2) return launch_group<2>(group, p, grid, stream);
+    return kNotBuilt;
+}
+
+// TurboQuant keys with float16 values: a 256-byte value row per token leaves room for two stages; with 4-bit keys (64 KB table on
+// a 64 KB boundary) the tiles shrink to 128 tokens, and eight heads per kv head do not fit beside that table (kNotBuilt: the caller
+// keeps such layers on the SIMT kernel).
+template <int KB>
+static int launch_dense_values(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
+    constexpr int kUnits = KB == 4 ? 8 : 11;
+    switch (group) {
+        case 1: return launch_decode_policy<TurboKDenseVPolicy<1, KB, kUnits, 1, 2>>(p, grid, stream);
+        case 2: return launch_decode_policy<TurboKDenseVPolicy<2, KB, kUnits, 1, 2>>(p, grid, stream);
+        case 4: return launch_decode_policy<TurboKDenseVPolicy<4, KB, kUnits, 1, 2>>(p, grid, stream);
+        case 8:
+            if constexpr (KB == 4) return kNotBuilt;
+            else return launch_decode_policy<TurboKDenseVPolicy<8, KB, kUnits, 1, 2>>(p, grid, stream);
+        default: return kNotBuilt;
+    }
+}
+
+int launch_decode_turbok_densev(int group, int kbits, const DecodeParams& p, int grid, cudaStream_t stream) {
+    if (kbits == 4) return launch_dense_values<4>(group, p, grid, stream);
+    if (kbits == 3) return launch_dense_values<3>(group, p, grid, stream);
+    if (kbits == 2) return launch_dense_values<2>(group, p, grid, stream);
     return kNotBuilt;
 }
 

@@ -1,7 +1,11 @@
-// Layers whose keys are q8_0 rows and whose values are TurboQuant rows of a fixed preset (gqa_attention_q8k_turboquant_decode,
-// Shaders/TurboQuant.metal:1651-1792; chosen per layer by TurboQuantV2Contract, TurboQuant.swift:432-488: earlyQ8KeyLayers,
-// a q8_0 key cache type) in the persistent flash-decode kernel.  The two sides live in two caches of the same geometry, so
-// DecodeParams names two addressings: k_* / kn_* / addr / lengths describe the key cache, v_* / vn_* / addr_v the value cache.
+// Layers whose keys and values use different row formats (chosen per layer by TurboQuantV2Contract, TurboQuant.swift:432-488) in
+// the persistent flash-decode kernel.  The two sides live in two caches of the same geometry, so DecodeParams names two
+// addressings: k_* / kn_* / addr / lengths describe the key cache, v_* / vn_* / addr_v the value cache.  Each policy here joins
+// the score half of one single-format policy to the output half of another; the halves meet in the score fragment
+// (token g | g + 8) x (head 2c | 2c + 1), which all of them use.
+//
+// Q8KTurboVPolicy: q8_0 keys, TurboQuant values of a fixed preset (gqa_attention_q8k_turboquant_decode,
+// Shaders/TurboQuant.metal:1651-1792: earlyQ8KeyLayers, a q8_0 key cache type).
 //
 // Scores are Q8MmaPolicy's (queries in their own space, int8 exact in fp16, one accumulator per 32-element block), outputs
 // are TurboMmaPolicy's (value centroids looked up as fp16 hi + lo pairs, accumulated in the rotated space, one inverse
@@ -9,7 +13,7 @@
 // (head 2c | 2c + 1), which both use.  Stage = K int8 rows | K block scales | V codes | V norms.
 #pragma once
 
-#include "flash_decode_q8.cuh"
+#include "flash_decode_dense_mma.cuh"   // includes the q8_0 and TurboQuant policies
 
 namespace er {
 
@@ -125,6 +129,184 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
             const uint32_t bh[4] = {__byte_perm(x0, x0, 0x1010), __byte_perm(x0, x0, 0x3232), __byte_perm(x1, x1, 0x1010), __byte_perm(x1, x1, 0x3232)};
             const uint32_t bl[4] = {__byte_perm(y0, y0, 0x1010), __byte_perm(y0, y0, 0x3232), __byte_perm(y1, y1, 0x1010), __byte_perm(y1, y1, 0x3232)};
             TM::template value_tiles<0>(st, vlo, vhi, bh, bl);
+        }
+    }
+};
+
+// TurboKDenseVPolicy: TurboQuant keys of a fixed preset, float16 values (gqa_attention_turboquant_decode_f16v,
+// Shaders/TurboQuant.metal:2003-2239).  Scores are TurboMmaPolicy's (rotated queries, key centroids looked up as fp16 hi + lo
+// pairs), outputs are DenseMmaPolicy's (value rows as they lie, through movmatrix, probabilities carried times 4096) in the
+// values' own space: no output transform.  Stage = K codes | K norms | V float16 rows.
+template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
+struct TurboKDenseVPolicy {
+    using TM = TurboMmaPolicy<GROUP, KBITS, KBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;   // key table, score fragments, query rotation
+    using DM = DenseMmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;                  // output fragment order, state
+    struct State : DM::State {
+        uint32_t lut_k;   // this lane's column of the key table
+    };
+    static constexpr int kGroup = GROUP;
+    static constexpr int kUnitsPerTile = UNITS_PER_TILE;
+    static constexpr int kWarpGroups = WARP_GROUPS;
+    static constexpr int kStages = STAGES;
+    static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
+    static constexpr int kThreads = (UNITS_PER_TILE * WARP_GROUPS + 1) * 32;
+    static constexpr int kKW = tq_code_words(KBITS);
+    static constexpr int kOffKn = kTileTokens * kKW * 4;
+    static constexpr int kOffV = kOffKn + kTileTokens * 4;
+    static constexpr int kStageBytes = kOffV + kTileTokens * kRowBytesF16;
+    static constexpr int kExtraBytes = -1;          // the key table sits on a 64 KB boundary of the shared window (TurboSmemPlan)
+    static constexpr bool kRotated = false;         // outputs are in the values' space
+    static constexpr bool kFusedAppend = false;
+    static constexpr int kFoldUnits = 32;
+    static constexpr bool kPacked = TM::kPacked;
+    static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
+
+    __device__ static float* fin_ptr(uint8_t*) { return nullptr; }
+    __device__ static bool init_extra(uint8_t* extra, int tid, int smem_bytes_after_extra) { return TM::init_extra(extra, tid, smem_bytes_after_extra); }
+    __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
+                                         const float2*, int) {}
+    __device__ static void store_out(const DecodeParams&, int64_t, const float*, int, int) {}
+
+    template <class WAIT>
+    __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
+                                      int t0, int ntok, int lane, int /*ring start: fp16 caches only*/, WAIT&& wait_free) {
+        const int nb = p.norm_fp16 ? 2 : 4;
+        const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
+        const uint8_t* kn = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
+        const uint8_t* vr = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        const int kps = p.addr.page_size, vps = p.addr_v.page_size;
+        const int kfirst = t0 / kps, kseg = (t0 + ntok - 1) / kps - kfirst + 1;
+        const int vfirst = t0 / vps, vseg = (t0 + ntok - 1) / vps - vfirst + 1;
+        wait_free();
+        if (lane == 0) {   // norm copies are rounded up to 16 bytes per page segment
+            uint32_t bytes = static_cast<uint32_t>(ntok) * (kKW * 4u + kRowBytesF16);
+            for (int i = 0; i < kseg; ++i) {
+                const int tb = max(t0, (kfirst + i) * kps), te = min(t0 + ntok, (kfirst + i + 1) * kps);
+                bytes += (static_cast<uint32_t>(te - tb) * nb + 15u) & ~15u;
+            }
+            mbar_arrive_expect_tx(bar, bytes);
+        }
+        __syncwarp();
+        for (int c = lane; c < 2 * kseg + vseg; c += 32) {
+            if (c < 2 * kseg) {
+                const int kind = c & 1, sgi = c >> 1;
+                const int tb = max(t0, (kfirst + sgi) * kps), te = min(t0 + ntok, (kfirst + sgi + 1) * kps);
+                const uint32_t rows = static_cast<uint32_t>(te - tb);
+                const int64_t row = row_index(p.addr, seq, head, tb);
+                if (kind == 0) bulk_g2s(stage + (tb - t0) * kKW * 4, kc + row * (kKW * 4), rows * kKW * 4, bar);
+                else bulk_g2s(stage + kOffKn + (tb - t0) * nb, kn + row * nb, (rows * nb + 15u) & ~15u, bar);
+            } else {
+                const int sgi = c - 2 * kseg;
+                const int tb = max(t0, (vfirst + sgi) * vps), te = min(t0 + ntok, (vfirst + sgi + 1) * vps);
+                const int64_t row = row_index(p.addr_v, seq, head, tb);
+                bulk_g2s(stage + kOffV + (tb - t0) * kRowBytesF16, vr + row * kRowBytesF16, static_cast<uint32_t>(te - tb) * kRowBytesF16, bar);
+            }
+        }
+    }
+
+    // Rotated queries -> B fragments in TurboMmaPolicy's order (k-step s: label 2c + e -> dim 32c + 4s + e, 2c + 8 + e -> + 2)
+    __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t* extra, int warp, int lane, int) {
+        const TurboSmemPlan pl = TM::plan(extra);
+        float* qrot = TM::window_ptr(extra, pl.rows);
+        TM::rotate_queries(p, qrot, qrow, cs, warp, lane);
+        st.lut_k = pl.lut_k | (lane << 3);
+        const int g = lane >> 2, c = lane & 3;
+        const int head = kPacked ? (g & 3) : g;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (head < GROUP) t = *reinterpret_cast<const float4*>(qrot + head * kHeadDim + 32 * c + 4 * s);
+            const __half2 h01 = __floats2half2_rn(t.x, t.y), h23 = __floats2half2_rn(t.z, t.w);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const uint32_t hi0 = *reinterpret_cast<const uint32_t*>(&h01), hi1 = *reinterpret_cast<const uint32_t*>(&h23);
+            const uint32_t lo0 = pack_half2(t.x - f01.x, t.y - f01.y), lo1 = pack_half2(t.z - f23.x, t.w - f23.y);
+            if constexpr (kPacked) {
+                st.qh[s][0] = g < 4 ? hi0 : lo0;
+                st.qh[s][1] = g < 4 ? hi1 : lo1;
+            } else {
+                st.qh[s][0] = hi0; st.qh[s][1] = hi1;
+                st.ql[s][0] = lo0; st.ql[s][1] = lo1;
+            }
+        }
+        st.reset();
+    }
+
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
+                                        const uint8_t*, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        const uint32_t sbase = smem_u32(stage);
+        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        const int r0 = unit * kUnitTokens + g;
+        // ---- scores (TurboMmaPolicy): the thread's 32 codes of tokens g and g + 8 ----
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t kc = sbase + (r0 * kKW + c * KBITS) * 4;
+            uint32_t k0[KBITS], k1[KBITS];
+            load_code_chunk<KBITS>(kc, k0);
+            load_code_chunk<KBITS>(kc + 32 * kKW, k1);
+            typename TM::State ts;   // the score steps read the query fragments and the table column only
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                ts.qh[i][0] = st.qh[i][0]; ts.qh[i][1] = st.qh[i][1];
+                if constexpr (!kPacked) { ts.ql[i][0] = st.ql[i][0]; ts.ql[i][1] = st.ql[i][1]; }
+            }
+            ts.lut_k = st.lut_k;
+            if constexpr (kPacked) {
+                float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+                TM::template score_steps_packed<0>(sa, sb, k0, k1, ts);
+                s[0] = sa[0] + sa[2]; s[1] = sa[1] + sa[3]; s[2] = sb[0] + sb[2]; s[3] = sb[1] + sb[3];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+            } else {
+                TM::template score_steps<0>(s, k0, k1, ts);
+            }
+            const float kn0 = ok0 ? TM::load_norm(stage + kOffKn, r0, p.norm_fp16) : 0.f;
+            const float kn1 = ok1 ? TM::load_norm(stage + kOffKn, r0 + 8, p.norm_fp16) : 0.f;
+            const float sc = p.scale_log2 * (1.f / tq_fp16_scale<KBITS>());
+            s[0] = ok0 ? (kn0 * s[0]) * sc : -INFINITY;
+            s[1] = ok0 ? (kn0 * s[1]) * sc : -INFINITY;
+            s[2] = ok1 ? (kn1 * s[2]) * sc : -INFINITY;
+            s[3] = ok1 ? (kn1 * s[3]) * sc : -INFINITY;
+        }
+        float pr[4];
+        mma_softmax_step(st, s, pr);
+
+        // ---- outputs (DenseMmaPolicy): B = 4096 p as fp16 hi + lo, A = transposed value blocks ----
+        const float w0 = pr[0] * DM::kProbScale, w1 = pr[1] * DM::kProbScale, w2 = pr[2] * DM::kProbScale, w3 = pr[3] * DM::kProbScale;
+        const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+        const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
+        const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
+        uint32_t b0l = 0, b1l = 0;
+        if constexpr (!kPacked) {
+            b0l = movmatrix_trans(lo01);
+            b1l = movmatrix_trans(lo23);
+        }
+        const uint32_t vrow = sbase + kOffV + r0 * kRowBytesF16 + 16 * c;
+        const bool partial = nvalid < kUnitTokens;   // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t v0[4], v1[4];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0[0]), "=r"(v0[1]), "=r"(v0[2]), "=r"(v0[3]) : "r"(vrow + 64 * j) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1[0]), "=r"(v1[1]), "=r"(v1[2]), "=r"(v1[3]) : "r"(vrow + 64 * j + 8 * kRowBytesF16) : "memory");
+            if (partial) {   // 0 x NaN would poison the accumulators: stale rows become zeros
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v0[e] = ok0 ? v0[e] : 0u;
+                    v1[e] = ok1 ? v1[e] : 0u;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t a0 = movmatrix_trans(v0[2 * u]);
+                const uint32_t a1 = movmatrix_trans(v0[2 * u + 1]);
+                const uint32_t a2 = movmatrix_trans(v1[2 * u]);
+                const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
+                mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
+                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
+            }
         }
     }
 };

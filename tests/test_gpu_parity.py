@@ -1611,13 +1611,10 @@ def test_outlier_presets_tensor_core_policy_against_simt_kernel(er, torch, prese
             assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
 
 
-@pytest.mark.parametrize("vbits", [2, 3, 4])
-@pytest.mark.parametrize("Hq,Hkv,layout", [(16, 8, "head_major"), (32, 8, "paged"), (4, 4, "head_major"), (16, 2, "paged")])
-def test_q8_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(er, torch, vbits, Hq, Hkv, layout):
-    """Layers with q8_0 keys and TurboQuant values (gqa_attention_q8k_turboquant_decode; two caches): the tensor-core policy of
-    the persistent kernel against the SIMT kernel on the same rows, contexts of several tiles, ragged, head-major and paged,
-    groups 1 / 2 / 4 / 8, an appended row pending (both kernels are held to fp32 attention over the decoded rows at small
-    sizes by test_mixed_family_layers_through_pair_caches; er_kv_config.decode_kernel picks the kernel)."""
+def _pair_kernels_agree(er, torch, make_key_cache, make_value_cache, Hq, Hkv, layout):
+    """Decode attention over a key cache and a value cache of different row formats: the tensor-core policy of the persistent
+    kernel (decode_kernel 0) against the SIMT kernel (3) on the same rows -- contexts of several tiles, ragged, an appended row
+    pending; paged caches lay their pages out independently of each other."""
     D, L, B = 128, 2, 3
     lens = [2900, 517, 1]
     T = 3008
@@ -1630,15 +1627,13 @@ def test_q8_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(e
     sp = er.step_params(rope_theta=THETA_QWEN3)
     outs = []
     for dk in (0, 3):
-        kw = {}
+        kw = dict(max_batch=B, decode_kernel=dk)
         if layout == "paged":
             ps = 64
             pages = (T // ps) * B
-            kw = dict(layout=er.Layout.paged, page_size=ps, num_pages=pages)
-        kc = er.KVCache(T, L, Hkv, D, er.Precision.q8_0, max_batch=B, decode_kernel=dk, **kw)
-        # the value cache's pages are laid out on their own (another permutation of another pool)
-        vc = er.KVCache(T, L, Hkv, D, er.Precision.turboquantV2, key_type=vbits, value_type=vbits, norm_format=er.NormFormat.float16,
-                        max_batch=B, decode_kernel=dk, **kw)
+            kw.update(layout=er.Layout.paged, page_size=ps, num_pages=pages)
+        kc = make_key_cache(T, L, Hkv, D, **kw)
+        vc = make_value_cache(T, L, Hkv, D, **kw)
         if layout == "paged":
             for cache, seed in ((kc, 3), (vc, 4)):
                 perm = np.random.default_rng(seed).permutation(pages)
@@ -1664,3 +1659,30 @@ def test_q8_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(e
         for b in range(B):
             assert attention_err(outs[0][l, b], outs[1][l, b]) < 3e-5
             assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
+
+
+PAIR_SHAPES = [(16, 8, "head_major"), (32, 8, "paged"), (4, 4, "head_major"), (16, 2, "paged")]      # groups 2, 4, 1, 8
+
+
+@pytest.mark.parametrize("vbits", [2, 3, 4])
+@pytest.mark.parametrize("Hq,Hkv,layout", PAIR_SHAPES)
+def test_q8_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(er, torch, vbits, Hq, Hkv, layout):
+    """gqa_attention_q8k_turboquant_decode's layers (both kernels are held to fp32 attention over the decoded rows at small sizes
+    by test_mixed_family_layers_through_pair_caches; er_kv_config.decode_kernel picks the kernel)."""
+    _pair_kernels_agree(er, torch,
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.q8_0, **kw),
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.turboquantV2, key_type=vbits, value_type=vbits,
+                                                               norm_format=er.NormFormat.float16, **kw),
+                        Hq, Hkv, layout)
+
+
+@pytest.mark.parametrize("kbits", [2, 3, 4])
+@pytest.mark.parametrize("Hq,Hkv,layout", PAIR_SHAPES)
+def test_turboquant_keys_with_float16_values_tensor_core_policy_against_simt_kernel(er, torch, kbits, Hq, Hkv, layout):
+    """gqa_attention_turboquant_decode_f16v's layers (4-bit keys with eight heads per kv head stay on the SIMT kernel)."""
+    _pair_kernels_agree(er, torch,
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.turboquantV2, key_type=kbits, value_type=kbits,
+                                                               norm_format=er.NormFormat.float32, **kw),
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.float16,
+                                                               **{**kw, "layout": kw.get("layout", er.Layout.head_major)}),
+                        Hq, Hkv, layout)
