@@ -1450,8 +1450,8 @@ static int32_t check_pair(const er_kv* kk, const er_kv* vv) {
     return ER_OK;
 }
 
-// q8_0 keys with TurboQuant values of a fixed preset (Q8KTurboVPolicy) and TurboQuant keys of a fixed preset with float16 values
-// (TurboKDenseVPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
+// q8_0 keys with TurboQuant values of a fixed preset (Q8KTurboVPolicy) and TurboQuant keys of a fixed preset with float16 or q8_0
+// values (TurboKeysPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
 // ER_DECODE_KERNEL_SIMT run the SIMT kernel.
 static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32_t num_heads, const er_step_params& s) {
     if (kk->cfg.head_dim != kHeadDim || vv->cfg.head_dim != kHeadDim) return false;
@@ -1462,6 +1462,7 @@ static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32
     if (group != 1 && group != 2 && group != 4 && group != 8) return false;
     if (kk->q8 && vv->turbo) return true;
     if (kk->turbo && vv->cfg.precision == ER_KV_FLOAT16 && !vv->token_major) return !(kk->cfg.key_type == ER_TQ_TURBO4 && group == 8);
+    if (kk->turbo && vv->q8) return true;
     return false;
 }
 
@@ -1494,6 +1495,8 @@ static int32_t pair_attention_tensor_core(er_kv* kk, er_kv* vv, uint32_t lb, uin
         p.scratch = kk->d_scratch; p.done_counter = kk->d_counters; p.status = kk->d_counters + 1; p.item_counters = kk->d_counters + 16;
         const int32_t rc = kk->q8 ? decode_status(launch_decode_q8k_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 8,
                                                   static_cast<int>(vv->cfg.value_type))
+                         : vv->q8 ? decode_status(launch_decode_turbok_q8v(group, static_cast<int>(kk->cfg.key_type), p, kk->num_sms, stream), group,
+                                                  static_cast<int>(kk->cfg.key_type), 8)
                                   : decode_status(launch_decode_turbok_densev(group, static_cast<int>(kk->cfg.key_type), p, kk->num_sms, stream), group,
                                                   static_cast<int>(kk->cfg.key_type), 16);
         if (rc != ER_OK) return rc;

@@ -13,6 +13,8 @@
 // (head 2c | 2c + 1), which both use.  Stage = K int8 rows | K block scales | V codes | V norms.
 #pragma once
 
+#include <type_traits>
+
 #include "flash_decode_dense_mma.cuh"   // includes the q8_0 and TurboQuant policies
 
 namespace er {
@@ -133,15 +135,18 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
     }
 };
 
-// TurboKDenseVPolicy: TurboQuant keys of a fixed preset, float16 values (gqa_attention_turboquant_decode_f16v,
-// Shaders/TurboQuant.metal:2003-2239).  Scores are TurboMmaPolicy's (rotated queries, key centroids looked up as fp16 hi + lo
-// pairs), outputs are DenseMmaPolicy's (value rows as they lie, through movmatrix, probabilities carried times 4096) in the
-// values' own space: no output transform.  Stage = K codes | K norms | V float16 rows.
-template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
-struct TurboKDenseVPolicy {
+// TurboKeysPolicy: TurboQuant keys of a fixed preset with float16 values (gqa_attention_turboquant_decode_f16v,
+// Shaders/TurboQuant.metal:2003-2239) or q8_0 values (the boundary layers of TurboQuantAdaptiveMode.boundaryQ8).  Scores are
+// TurboMmaPolicy's (rotated queries, key centroids looked up as fp16 hi + lo pairs); outputs are DenseMmaPolicy's (value rows as
+// they lie, through movmatrix, probabilities carried times 4096) or Q8MmaPolicy's (int8 pairs, probabilities times the block
+// scales), in the values' own space: no output transform.  Stage = K codes | K norms | V rows [| V block scales].
+template <int GROUP, int KBITS, bool Q8_VALUES, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
+struct TurboKeysPolicy {
     using TM = TurboMmaPolicy<GROUP, KBITS, KBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;   // key table, score fragments, query rotation
-    using DM = DenseMmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;                  // output fragment order, state
-    struct State : DM::State {
+    using DM = DenseMmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+    using Q8 = Q8MmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+    using VState = std::conditional_t<Q8_VALUES, typename Q8::State, typename DM::State>;   // the value side's accumulator order
+    struct State : VState {
         uint32_t lut_k;   // this lane's column of the key table
     };
     static constexpr int kGroup = GROUP;
@@ -151,9 +156,11 @@ struct TurboKDenseVPolicy {
     static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
     static constexpr int kThreads = (UNITS_PER_TILE * WARP_GROUPS + 1) * 32;
     static constexpr int kKW = tq_code_words(KBITS);
+    static constexpr int kVRowBytes = Q8_VALUES ? 128 : kRowBytesF16;
     static constexpr int kOffKn = kTileTokens * kKW * 4;
     static constexpr int kOffV = kOffKn + kTileTokens * 4;
-    static constexpr int kStageBytes = kOffV + kTileTokens * kRowBytesF16;
+    static constexpr int kOffVs = kOffV + kTileTokens * kVRowBytes;
+    static constexpr int kStageBytes = kOffVs + (Q8_VALUES ? kTileTokens * 8 : 0);
     static constexpr int kExtraBytes = -1;          // the key table sits on a 64 KB boundary of the shared window (TurboSmemPlan)
     static constexpr bool kRotated = false;         // outputs are in the values' space
     static constexpr bool kFusedAppend = false;
@@ -174,32 +181,39 @@ struct TurboKDenseVPolicy {
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
         const uint8_t* kn = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
         const uint8_t* vr = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        const uint8_t* vs = Q8_VALUES ? p.vn_base + static_cast<int64_t>(layer) * p.vn_layer_stride_bytes : nullptr;
         const int kps = p.addr.page_size, vps = p.addr_v.page_size;
         const int kfirst = t0 / kps, kseg = (t0 + ntok - 1) / kps - kfirst + 1;
         const int vfirst = t0 / vps, vseg = (t0 + ntok - 1) / vps - vfirst + 1;
         wait_free();
-        if (lane == 0) {   // norm copies are rounded up to 16 bytes per page segment
-            uint32_t bytes = static_cast<uint32_t>(ntok) * (kKW * 4u + kRowBytesF16);
+        if (lane == 0) {   // side copies are rounded up to 16 bytes per page segment
+            uint32_t bytes = static_cast<uint32_t>(ntok) * (kKW * 4u + kVRowBytes);
             for (int i = 0; i < kseg; ++i) {
                 const int tb = max(t0, (kfirst + i) * kps), te = min(t0 + ntok, (kfirst + i + 1) * kps);
                 bytes += (static_cast<uint32_t>(te - tb) * nb + 15u) & ~15u;
             }
+            if constexpr (Q8_VALUES) {
+                for (int i = 0; i < vseg; ++i) {
+                    const int tb = max(t0, (vfirst + i) * vps), te = min(t0 + ntok, (vfirst + i + 1) * vps);
+                    bytes += (static_cast<uint32_t>(te - tb) * 8u + 15u) & ~15u;
+                }
+            }
             mbar_arrive_expect_tx(bar, bytes);
         }
         __syncwarp();
-        for (int c = lane; c < 2 * kseg + vseg; c += 32) {
-            if (c < 2 * kseg) {
-                const int kind = c & 1, sgi = c >> 1;
-                const int tb = max(t0, (kfirst + sgi) * kps), te = min(t0 + ntok, (kfirst + sgi + 1) * kps);
-                const uint32_t rows = static_cast<uint32_t>(te - tb);
-                const int64_t row = row_index(p.addr, seq, head, tb);
+        for (int c = lane; c < 2 * (kseg + vseg); c += 32) {
+            const bool value_side = c >= 2 * kseg;
+            const int i = value_side ? c - 2 * kseg : c, kind = i & 1, sgi = i >> 1;
+            const int ps = value_side ? vps : kps, first = value_side ? vfirst : kfirst;
+            const int tb = max(t0, (first + sgi) * ps), te = min(t0 + ntok, (first + sgi + 1) * ps);
+            const uint32_t rows = static_cast<uint32_t>(te - tb);
+            const int64_t row = row_index(value_side ? p.addr_v : p.addr, seq, head, tb);
+            if (!value_side) {
                 if (kind == 0) bulk_g2s(stage + (tb - t0) * kKW * 4, kc + row * (kKW * 4), rows * kKW * 4, bar);
                 else bulk_g2s(stage + kOffKn + (tb - t0) * nb, kn + row * nb, (rows * nb + 15u) & ~15u, bar);
             } else {
-                const int sgi = c - 2 * kseg;
-                const int tb = max(t0, (vfirst + sgi) * vps), te = min(t0 + ntok, (vfirst + sgi + 1) * vps);
-                const int64_t row = row_index(p.addr_v, seq, head, tb);
-                bulk_g2s(stage + kOffV + (tb - t0) * kRowBytesF16, vr + row * kRowBytesF16, static_cast<uint32_t>(te - tb) * kRowBytesF16, bar);
+                if (kind == 0) bulk_g2s(stage + kOffV + (tb - t0) * kVRowBytes, vr + row * kVRowBytes, rows * kVRowBytes, bar);
+                else if constexpr (Q8_VALUES) bulk_g2s(stage + kOffVs + (tb - t0) * 8, vs + row * 8, (rows * 8 + 15u) & ~15u, bar);
             }
         }
     }
@@ -229,6 +243,48 @@ struct TurboKDenseVPolicy {
             }
         }
         st.reset();
+    }
+
+    // DenseMmaPolicy's output block: B = 4096 p as fp16 hi + lo, A = transposed value blocks of the 256-byte rows at `vrows`.
+    __device__ __forceinline__ static void dense_unit_values(State& st, uint32_t vrows, int unit, int nvalid, const float (&pr)[4], int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+        const float w0 = pr[0] * DM::kProbScale, w1 = pr[1] * DM::kProbScale, w2 = pr[2] * DM::kProbScale, w3 = pr[3] * DM::kProbScale;
+        const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+        const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
+        const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
+        uint32_t b0l = 0, b1l = 0;
+        if constexpr (!kPacked) {
+            b0l = movmatrix_trans(lo01);
+            b1l = movmatrix_trans(lo23);
+        }
+        const uint32_t vrow = vrows + (unit * kUnitTokens + g) * kRowBytesF16 + 16 * c;
+        const bool partial = nvalid < kUnitTokens;   // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t v0[4], v1[4];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0[0]), "=r"(v0[1]), "=r"(v0[2]), "=r"(v0[3]) : "r"(vrow + 64 * j) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1[0]), "=r"(v1[1]), "=r"(v1[2]), "=r"(v1[3]) : "r"(vrow + 64 * j + 8 * kRowBytesF16) : "memory");
+            if (partial) {   // 0 x NaN would poison the accumulators: stale rows become zeros
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v0[e] = ok0 ? v0[e] : 0u;
+                    v1[e] = ok1 ? v1[e] : 0u;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t a0 = movmatrix_trans(v0[2 * u]);
+                const uint32_t a1 = movmatrix_trans(v0[2 * u + 1]);
+                const uint32_t a2 = movmatrix_trans(v1[2 * u]);
+                const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
+                mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
+                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
+            }
+        }
     }
 
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
@@ -270,45 +326,14 @@ struct TurboKDenseVPolicy {
         }
         float pr[4];
         mma_softmax_step(st, s, pr);
-
-        // ---- outputs (DenseMmaPolicy): B = 4096 p as fp16 hi + lo, A = transposed value blocks ----
-        const float w0 = pr[0] * DM::kProbScale, w1 = pr[1] * DM::kProbScale, w2 = pr[2] * DM::kProbScale, w3 = pr[3] * DM::kProbScale;
-        const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
-        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
-        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
-        const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
-        const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
-        uint32_t b0l = 0, b1l = 0;
-        if constexpr (!kPacked) {
-            b0l = movmatrix_trans(lo01);
-            b1l = movmatrix_trans(lo23);
-        }
-        const uint32_t vrow = sbase + kOffV + r0 * kRowBytesF16 + 16 * c;
-        const bool partial = nvalid < kUnitTokens;   // warp-uniform
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint32_t v0[4], v1[4];
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0[0]), "=r"(v0[1]), "=r"(v0[2]), "=r"(v0[3]) : "r"(vrow + 64 * j) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1[0]), "=r"(v1[1]), "=r"(v1[2]), "=r"(v1[3]) : "r"(vrow + 64 * j + 8 * kRowBytesF16) : "memory");
-            if (partial) {   // 0 x NaN would poison the accumulators: stale rows become zeros
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    v0[e] = ok0 ? v0[e] : 0u;
-                    v1[e] = ok1 ? v1[e] : 0u;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const uint32_t a0 = movmatrix_trans(v0[2 * u]);
-                const uint32_t a1 = movmatrix_trans(v0[2 * u + 1]);
-                const uint32_t a2 = movmatrix_trans(v1[2 * u]);
-                const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
-                mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
-                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
-            }
-        }
+        if constexpr (Q8_VALUES) Q8::unit_values(st, sbase + kOffV, sbase + kOffVs, unit, nvalid, pr, lane);
+        else dense_unit_values(st, sbase + kOffV, unit, nvalid, pr, lane);
     }
 };
+
+template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
+using TurboKDenseVPolicy = TurboKeysPolicy<GROUP, KBITS, false, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
+using TurboKQ8VPolicy = TurboKeysPolicy<GROUP, KBITS, true, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
 
 }  // namespace er

@@ -268,54 +268,26 @@ struct Q8MmaPolicy {
         s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
     }
 
-    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
-                                        const uint8_t*, int lane) {
+    // Outputs of one unit: O^T += V8^T . (p * vScale[block])^T block by block, B = (p * vScale) as fp16 hi + lo, A = transposed int8
+    // pairs.  vrows / vscales: shared-window addresses of the tile's int8 value rows and block scales; pr = the probabilities of
+    // (token g | g + 8) x (head 2c | 2c + 1).  ST: any state with this policy's accumulator order (State::publish).
+    template <class ST>
+    __device__ __forceinline__ static void unit_values(ST& st, uint32_t vrows, uint32_t vscales, int unit, int nvalid, const float (&pr)[4], int lane) {
         const int g = lane >> 2, c = lane & 3;
-        const uint32_t sbase = smem_u32(stage);
         const int r0 = unit * kUnitTokens + g;
-        const uint32_t vrow = sbase + kOffV + r0 * 128 + 32 * c;
+        const uint32_t vrow = vrows + r0 * 128 + 32 * c;
         const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
-        float s[4];   // (token g | g + 8) x (head 2c | 2c + 1)
-        unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
         float vs0[4], vs1[4];
-        load_scales4(sbase + kOffVs + r0 * 8, vs0, ok0);
-        load_scales4(sbase + kOffVs + (r0 + 8) * 8, vs1, ok1);
+        load_scales4(vscales + r0 * 8, vs0, ok0);
+        load_scales4(vscales + (r0 + 8) * 8, vs1, ok1);
 #pragma unroll
         for (int b = 0; b < 4; ++b) { vs0[b] *= kProbScale; vs1[b] *= kProbScale; }
-
-        // The running maxima change only when some token of the unit exceeds them (always in a fresh state: token 0 of a unit
-        // is valid, its score finite): the cross-lane maximum and the rescale run only then.  The denominators stay per-lane
-        // partial sums (every lane applies the same corrections); State::gather adds them up when the state is read.
-        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
-        float m0 = st.m[0], m1 = st.m[1];
-        if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
-#pragma unroll
-            for (int off = 4; off < 32; off <<= 1) {
-                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-            }
-            m0 = fmaxf(m0, mx0);
-            m1 = fmaxf(m1, mx1);
-            const float corr0 = fast_exp2(st.m[0] - m0), corr1 = fast_exp2(st.m[1] - m1);
-            st.l[0] *= corr0;
-            st.l[1] *= corr1;
-            st.m[0] = m0;
-            st.m[1] = m1;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                st.acc[t][0] *= corr0; st.acc[t][1] *= corr1; st.acc[t][2] *= corr0; st.acc[t][3] *= corr1;
-            }
-        }
-        const float p0 = fast_exp2(s[0] - m0), p1 = fast_exp2(s[1] - m1), p2 = fast_exp2(s[2] - m0), p3 = fast_exp2(s[3] - m1);
-        st.l[0] += p0 + p2;
-        st.l[1] += p1 + p3;
-        // ---- outputs, block by block: B = (p * vScale[block]) as fp16 hi + lo, A = transposed int8 pairs ----
         uint32_t v0[8], v1[8];
         load_row_words(vrow, v0);
         load_row_words(vrow + 8 * 128, v1);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const float w0 = p0 * vs0[b], w1 = p1 * vs0[b], w2 = p2 * vs1[b], w3 = p3 * vs1[b];
+            const float w0 = pr[0] * vs0[b], w1 = pr[1] * vs0[b], w2 = pr[2] * vs1[b], w3 = pr[3] * vs1[b];
             const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
             const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
@@ -340,6 +312,15 @@ struct Q8MmaPolicy {
                 if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * b + u], a0, a1, a2, a3, b0l, b1l);
             }
         }
+    }
+
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
+                                        const uint8_t*, int lane) {
+        const uint32_t sbase = smem_u32(stage);
+        float s[4], pr[4];
+        unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        mma_softmax_step(st, s, pr);
+        unit_values(st, sbase + kOffV, sbase + kOffVs, unit, nvalid, pr, lane);
     }
 };
 

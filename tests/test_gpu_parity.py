@@ -1686,3 +1686,14 @@ def test_turboquant_keys_with_float16_values_tensor_core_policy_against_simt_ker
                         lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.float16,
                                                                **{**kw, "layout": kw.get("layout", er.Layout.head_major)}),
                         Hq, Hkv, layout)
+
+
+@pytest.mark.parametrize("kbits", [2, 3, 4])
+@pytest.mark.parametrize("Hq,Hkv,layout", PAIR_SHAPES)
+def test_turboquant_keys_with_q8_values_tensor_core_policy_against_simt_kernel(er, torch, kbits, Hq, Hkv, layout):
+    """TurboQuant keys with q8_0 values: the boundary layers of TurboQuantAdaptiveMode.boundaryQ8."""
+    _pair_kernels_agree(er, torch,
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.turboquantV2, key_type=kbits, value_type=kbits,
+                                                               norm_format=er.NormFormat.float16, **kw),
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.q8_0, **kw),
+                        Hq, Hkv, layout)
