@@ -26,6 +26,28 @@ int launch_decode_q8k_turbov(int group, int vbits, const DecodeParams& p, int gr
     return kNotBuilt;
 }
 
+// float16 keys with TurboQuant values: the bytes per token of TurboQuant keys with float16 values below, so those shapes.
+template <int VB>
+static int launch_dense_keys(int group, const DecodeParams& p, int grid, cudaStream_t stream) {
+    constexpr int kUnits = VB == 4 ? 8 : 11;
+    switch (group) {
+        case 1: return launch_decode_policy<DenseKTurboVPolicy<1, VB, kUnits, 1, 2>>(p, grid, stream);
+        case 2: return launch_decode_policy<DenseKTurboVPolicy<2, VB, kUnits, 1, 2>>(p, grid, stream);
+        case 4: return launch_decode_policy<DenseKTurboVPolicy<4, VB, kUnits, 1, 2>>(p, grid, stream);
+        case 8:
+            if constexpr (VB == 4) return kNotBuilt;
+            else return launch_decode_policy<DenseKTurboVPolicy<8, VB, kUnits, 1, 2>>(p, grid, stream);
+        default: return kNotBuilt;
+    }
+}
+
+int launch_decode_densek_turbov(int group, int vbits, const DecodeParams& p, int grid, cudaStream_t stream) {
+    if (vbits == 4) return launch_dense_keys<4>(group, p, grid, stream);
+    if (vbits == 3) return launch_dense_keys<3>(group, p, grid, stream);
+    if (vbits == 2) return launch_dense_keys<2>(group, p, grid, stream);
+    return kNotBuilt;
+}
+
 // TurboQuant keys with float16 values: a 256-byte value row per token leaves room for two stages; with 4-bit keys (64 KB table on
 // a 64 KB boundary) the tiles shrink to 128 tokens, and eight heads per kv head do not fit beside that table (kNotBuilt: the caller
 // keeps such layers on the SIMT kernel).

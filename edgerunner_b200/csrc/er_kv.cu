@@ -1450,8 +1450,8 @@ static int32_t check_pair(const er_kv* kk, const er_kv* vv) {
     return ER_OK;
 }
 
-// q8_0 keys with TurboQuant values of a fixed preset (Q8KTurboVPolicy) and TurboQuant keys of a fixed preset with float16 or q8_0
-// values (TurboKeysPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
+// q8_0 or float16 keys with TurboQuant values of a fixed preset (TurboValuesPolicy) and TurboQuant keys of a fixed preset with
+// float16 or q8_0 values (TurboKeysPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
 // ER_DECODE_KERNEL_SIMT run the SIMT kernel.
 static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32_t num_heads, const er_step_params& s) {
     if (kk->cfg.head_dim != kHeadDim || vv->cfg.head_dim != kHeadDim) return false;
@@ -1463,6 +1463,7 @@ static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32
     if (kk->q8 && vv->turbo) return true;
     if (kk->turbo && vv->cfg.precision == ER_KV_FLOAT16 && !vv->token_major) return !(kk->cfg.key_type == ER_TQ_TURBO4 && group == 8);
     if (kk->turbo && vv->q8) return true;
+    if (kk->cfg.precision == ER_KV_FLOAT16 && !kk->token_major && vv->turbo) return !(vv->cfg.value_type == ER_TQ_TURBO4 && group == 8);
     return false;
 }
 
@@ -1481,7 +1482,7 @@ static int32_t pair_attention_tensor_core(er_kv* kk, er_kv* vv, uint32_t lb, uin
         p.kn_base = kk->kn_slab; p.n_layer_stride_bytes = kk->n_layer_stride;
         p.v_base = vv->v_slab; p.v_layer_stride_bytes = vv->v_layer_stride;
         p.vn_base = vv->vn_slab; p.vn_layer_stride_bytes = vv->n_layer_stride;
-        p.norm_fp16 = (kk->q8 ? vv->norm_bytes : kk->norm_bytes) == 2;   // the TurboQuant side's stored norms
+        p.norm_fp16 = (kk->turbo ? kk->norm_bytes : vv->norm_bytes) == 2;   // the TurboQuant side's stored norms
         p.lengths = kk->d_lengths; p.layer_begin = static_cast<int>(l0); p.num_layers = static_cast<int>(l1 - l0);
         p.batch = static_cast<int>(kk->cfg.max_batch); p.num_q_heads = static_cast<int>(num_heads);
         p.pending = static_cast<int>(pending);
@@ -1495,6 +1496,8 @@ static int32_t pair_attention_tensor_core(er_kv* kk, er_kv* vv, uint32_t lb, uin
         p.scratch = kk->d_scratch; p.done_counter = kk->d_counters; p.status = kk->d_counters + 1; p.item_counters = kk->d_counters + 16;
         const int32_t rc = kk->q8 ? decode_status(launch_decode_q8k_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 8,
                                                   static_cast<int>(vv->cfg.value_type))
+                         : !kk->turbo ? decode_status(launch_decode_densek_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 16,
+                                                      static_cast<int>(vv->cfg.value_type))
                          : vv->q8 ? decode_status(launch_decode_turbok_q8v(group, static_cast<int>(kk->cfg.key_type), p, kk->num_sms, stream), group,
                                                   static_cast<int>(kk->cfg.key_type), 8)
                                   : decode_status(launch_decode_turbok_densev(group, static_cast<int>(kk->cfg.key_type), p, kk->num_sms, stream), group,

@@ -4,13 +4,14 @@
 // the score half of one single-format policy to the output half of another; the halves meet in the score fragment
 // (token g | g + 8) x (head 2c | 2c + 1), which all of them use.
 //
-// Q8KTurboVPolicy: q8_0 keys, TurboQuant values of a fixed preset (gqa_attention_q8k_turboquant_decode,
-// Shaders/TurboQuant.metal:1651-1792: earlyQ8KeyLayers, a q8_0 key cache type).
+// TurboValuesPolicy: TurboQuant values of a fixed preset with q8_0 keys (gqa_attention_q8k_turboquant_decode,
+// Shaders/TurboQuant.metal:1651-1792: earlyQ8KeyLayers, a q8_0 key cache type) or float16 keys (a dense key cache type).
 //
-// Scores are Q8MmaPolicy's (queries in their own space, int8 exact in fp16, one accumulator per 32-element block), outputs
+// Scores are Q8MmaPolicy's (queries in their own space, int8 exact in fp16, one accumulator per 32-element block) or
+// DenseMmaPolicy's (the float16 rows as they lie), outputs
 // are TurboMmaPolicy's (value centroids looked up as fp16 hi + lo pairs, accumulated in the rotated space, one inverse
 // transform after the merge); the fragment layouts of the two policies meet in the score fragment (token g | g + 8) x
-// (head 2c | 2c + 1), which both use.  Stage = K int8 rows | K block scales | V codes | V norms.
+// (head 2c | 2c + 1), which both use.  Stage = K rows [| K block scales] | V codes | V norms.
 #pragma once
 
 #include <type_traits>
@@ -19,15 +20,16 @@
 
 namespace er {
 
-template <int GROUP, int VBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
-struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
+template <int GROUP, int VBITS, bool Q8_KEYS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
+struct TurboValuesPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
     using TM = TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;   // tables, value lookups, state, output transform
     using Q8 = Q8MmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;                    // query fragments, scores
     using State = typename TM::State;
     static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
     static constexpr int kVW = tq_code_words(VBITS);
-    static constexpr int kOffKs = kTileTokens * 128;
-    static constexpr int kOffVc = kOffKs + kTileTokens * 8;
+    static constexpr int kKRowBytes = Q8_KEYS ? 128 : kRowBytesF16;
+    static constexpr int kOffKs = kTileTokens * kKRowBytes;                           // q8_0 keys: the rows' block scales
+    static constexpr int kOffVc = kOffKs + (Q8_KEYS ? kTileTokens * 8 : 0);
     static constexpr int kOffVn = kOffVc + kTileTokens * kVW * 4;
     static constexpr int kStageBytes = kOffVn + kTileTokens * 4;
     static_assert(TM::kPacked == Q8::kPacked, "both sides pack the hi and lo parts of their B operands the same way");
@@ -37,7 +39,7 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
                                       int t0, int ntok, int lane, int /*ring start: fp16 rows only*/, WAIT&& wait_free) {
         const int nb = p.norm_fp16 ? 2 : 4;
         const uint8_t* kc = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
-        const uint8_t* ks = p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes;
+        const uint8_t* ks = Q8_KEYS ? p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes : nullptr;
         const uint8_t* vc = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
         const uint8_t* vn = p.vn_base + static_cast<int64_t>(layer) * p.vn_layer_stride_bytes;
         // page segments of the tile in each cache (a head-major cache is one page per sequence)
@@ -46,10 +48,12 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
         const int vfirst = t0 / vps, vseg = (t0 + ntok - 1) / vps - vfirst + 1;
         wait_free();
         if (lane == 0) {   // side copies are rounded up to 16 bytes per page segment
-            uint32_t bytes = static_cast<uint32_t>(ntok) * (128u + kVW * 4u);
-            for (int i = 0; i < kseg; ++i) {
-                const int tb = max(t0, (kfirst + i) * kps), te = min(t0 + ntok, (kfirst + i + 1) * kps);
-                bytes += (static_cast<uint32_t>(te - tb) * 8u + 15u) & ~15u;
+            uint32_t bytes = static_cast<uint32_t>(ntok) * (kKRowBytes + kVW * 4u);
+            if constexpr (Q8_KEYS) {
+                for (int i = 0; i < kseg; ++i) {
+                    const int tb = max(t0, (kfirst + i) * kps), te = min(t0 + ntok, (kfirst + i + 1) * kps);
+                    bytes += (static_cast<uint32_t>(te - tb) * 8u + 15u) & ~15u;
+                }
             }
             for (int i = 0; i < vseg; ++i) {
                 const int tb = max(t0, (vfirst + i) * vps), te = min(t0 + ntok, (vfirst + i + 1) * vps);
@@ -66,8 +70,8 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
             const uint32_t rows = static_cast<uint32_t>(te - tb);
             const int64_t row = row_index(value_side ? p.addr_v : p.addr, seq, head, tb);
             if (!value_side) {
-                if (kind == 0) bulk_g2s(stage + (tb - t0) * 128, kc + row * 128, rows * 128, bar);
-                else bulk_g2s(stage + kOffKs + (tb - t0) * 8, ks + row * 8, (rows * 8 + 15u) & ~15u, bar);
+                if (kind == 0) bulk_g2s(stage + (tb - t0) * kKRowBytes, kc + row * kKRowBytes, rows * kKRowBytes, bar);
+                else if constexpr (Q8_KEYS) bulk_g2s(stage + kOffKs + (tb - t0) * 8, ks + row * 8, (rows * 8 + 15u) & ~15u, bar);
             } else {
                 if (kind == 0) bulk_g2s(stage + kOffVc + (tb - t0) * kVW * 4, vc + row * (kVW * 4), rows * kVW * 4, bar);
                 else bulk_g2s(stage + kOffVn + (tb - t0) * nb, vn + row * nb, (rows * nb + 15u) & ~15u, bar);
@@ -75,7 +79,8 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
         }
     }
 
-    // queries stay in their own space (q8_0 keys are not rotated); the tables are the value side's
+    // queries stay in their own space (q8_0 and float16 keys are not rotated; both key policies use the same fragment order); the
+    // tables are the value side's
     __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t* extra, int, int lane, int) {
         const TurboSmemPlan pl = TM::plan(extra);
         st.lut_k = pl.lut_k | (lane << 3);
@@ -112,7 +117,33 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
         const float vn1 = ok1 ? TM::load_norm(stage + kOffVn, r0 + 8, p.norm_fp16) * inv_sv : 0.f;
 
         float s[4], pr[4];
-        Q8::unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        if constexpr (Q8_KEYS) {
+            Q8::unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        } else {
+            // DenseMmaPolicy's score block: the key rows are the A operands as they lie (16-byte chunks 4j + c of tokens g and g + 8)
+            const uint32_t krow = sbase + r0 * kRowBytesF16 + 16 * c;
+            s[0] = s[1] = s[2] = s[3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t k0[4], k1[4];
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k0[0]), "=r"(k0[1]), "=r"(k0[2]), "=r"(k0[3]) : "r"(krow + 64 * j) : "memory");
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k1[0]), "=r"(k1[1]), "=r"(k1[2]), "=r"(k1[3]) : "r"(krow + 64 * j + 8 * kRowBytesF16) : "memory");
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.qh[2 * j + u][0], st.qh[2 * j + u][1]);
+                    if constexpr (!TM::kPacked) mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.ql[2 * j + u][0], st.ql[2 * j + u][1]);
+                }
+            }
+            if constexpr (TM::kPacked) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+            }
+            // rows at or past nvalid were never copied (stale shared memory, possibly NaN patterns): the select discards them
+            s[0] = ok0 ? s[0] * p.scale_log2 : -INFINITY;
+            s[1] = ok0 ? s[1] * p.scale_log2 : -INFINITY;
+            s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
+            s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
+        }
         mma_softmax_step(st, s, pr);
 
         // (p_t * vNorm_t)[token][head] as fp16 hi + lo parts, transposed and duplicated on the (hi, lo) labels of a centroid
@@ -134,6 +165,11 @@ struct Q8KTurboVPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WAR
         }
     }
 };
+
+template <int GROUP, int VBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
+using Q8KTurboVPolicy = TurboValuesPolicy<GROUP, VBITS, true, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+template <int GROUP, int VBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
+using DenseKTurboVPolicy = TurboValuesPolicy<GROUP, VBITS, false, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
 
 // TurboKeysPolicy: TurboQuant keys of a fixed preset with float16 values (gqa_attention_turboquant_decode_f16v,
 // Shaders/TurboQuant.metal:2003-2239) or q8_0 values (the boundary layers of TurboQuantAdaptiveMode.boundaryQ8).  Scores are

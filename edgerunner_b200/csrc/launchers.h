@@ -26,6 +26,8 @@ int launch_decode_turbo(int group, int kbits, int vbits, const DecodeParams& p, 
 int launch_decode_q8(int group, const DecodeParams& p, int grid, cudaStream_t stream);
 // q8_0 keys (p.k_*, p.kn_*, p.addr) with TurboQuant values of a fixed preset (p.v_*, p.vn_*, p.addr_v): two caches (decode_hybrid.cu)
 int launch_decode_q8k_turbov(int group, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
+// float16 keys (head-major or paged rows) with TurboQuant values of a fixed preset; kNotBuilt for 4-bit values with eight heads per kv head
+int launch_decode_densek_turbov(int group, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 // TurboQuant keys of a fixed preset with float16 values (head-major or paged rows); kNotBuilt for 4-bit keys with eight heads per kv head
 int launch_decode_turbok_densev(int group, int kbits, const DecodeParams& p, int grid, cudaStream_t stream);
 // TurboQuant keys of a fixed preset with q8_0 values (p.v_* rows, p.vn_* block scales)

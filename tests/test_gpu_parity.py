@@ -1697,3 +1697,16 @@ def test_turboquant_keys_with_q8_values_tensor_core_policy_against_simt_kernel(e
                                                                norm_format=er.NormFormat.float16, **kw),
                         lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.q8_0, **kw),
                         Hq, Hkv, layout)
+
+
+@pytest.mark.parametrize("vbits", [2, 3, 4])
+@pytest.mark.parametrize("Hq,Hkv,layout", PAIR_SHAPES)
+def test_float16_keys_with_turboquant_values_tensor_core_policy_against_simt_kernel(er, torch, vbits, Hq, Hkv, layout):
+    """float16 keys with TurboQuant values (a dense key cache type in TurboQuantV2Contract; 4-bit values with eight heads per kv
+    head stay on the SIMT kernel)."""
+    _pair_kernels_agree(er, torch,
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.float16,
+                                                               **{**kw, "layout": kw.get("layout", er.Layout.head_major)}),
+                        lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.turboquantV2, key_type=vbits, value_type=vbits,
+                                                               norm_format=er.NormFormat.float32, **kw),
+                        Hq, Hkv, layout)
