@@ -167,6 +167,31 @@ __global__ void gather_rows_kernel(const uint8_t* base, uint8_t* dst, KVAddressi
     }
 }
 
+// Rows [0, *len) of (seq, every kv head) of a float16 cache (head-major or paged) as head-major [kv head][slot][128] rows, and zeros
+// as their second operand: the form the chunked-prefill kernels read expanded rows in (layers whose two sides use different formats).
+struct F16ExpandParams {
+    const uint8_t* rows;
+    uint8_t* out;
+    uint8_t* out_lo;
+    KVAddressing addr;
+    const int32_t* len_ptr;
+    int seq, out_stride_rows;
+};
+
+__global__ void __launch_bounds__(256) f16_expand_rows_kernel(const __grid_constant__ F16ExpandParams p) {
+    const int lane = threadIdx.x & 31;
+    int len = *p.len_ptr;
+    len = len < p.addr.max_seq_len ? len : p.addr.max_seq_len;
+    const int64_t total = static_cast<int64_t>(len) * p.addr.num_kv_heads;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < total; row += static_cast<int64_t>(gridDim.x) * 8) {
+        const int h = static_cast<int>(row / len), t = static_cast<int>(row % len);
+        const int64_t ridx = row_index(p.addr, p.seq, h, t);
+        const int64_t dst = (static_cast<int64_t>(h) * p.out_stride_rows + t) * 256;
+        reinterpret_cast<uint2*>(p.out + dst)[lane] = reinterpret_cast<const uint2*>(p.rows + ridx * 256)[lane];
+        reinterpret_cast<uint2*>(p.out_lo + dst)[lane] = make_uint2(0u, 0u);
+    }
+}
+
 // rope_neox_f32 / rope_neox_f32_to_f16 as stand-alone operators (Shaders/RoPE.metal:57-93, 498-531),
 // any even head_dim up to 512, partial rotary factor honoured.  inv_freq[pair] =
 // 1.0f / powr(theta, float(2*pair)/float(headDim)) is tabulated by the host.

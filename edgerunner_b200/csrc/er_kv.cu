@@ -1525,6 +1525,117 @@ int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32
     return simt_attention(key_cache, value_cache, lb, le, q, out, num_heads, pending ? 1 : 0, 1, -1, -1, s, static_cast<cudaStream_t>(stream));
 }
 
+// One side of a (layer, sequence) as fp16 hi + lo rows, head-major [kv head][tpad][128], for the chunked-prefill kernels: what the
+// single-cache prefill does for its own two sides, for a side taken from either cache of a pair.
+static int32_t expand_side_for_prefill(er_kv* src, bool is_v, uint32_t layer, uint32_t seq, const int32_t* len_ptr, __half* dst, __half* dst_lo,
+                                       int tpad, cudaStream_t cs) {
+    const uint8_t* rows = (is_v ? src->v_slab : src->k_slab) + layer * (is_v ? src->v_layer_stride : src->k_layer_stride);
+    const int64_t max_rows = static_cast<int64_t>(src->cfg.max_seq_len) * src->cfg.num_kv_heads;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((max_rows + 7) / 8, 16384));
+    if (src->outlier) {
+        OutlierExpandParams ep{};
+        ep.rows = rows; ep.out = dst; ep.out_lo = dst_lo; ep.fmt = src->ofmt; ep.addr = src->addressing(); ep.len_ptr = len_ptr;
+        ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
+        ep.res_coef = kQjlScale * (is_v ? src->cfg.value_residual_scale : src->cfg.key_residual_scale);
+        tq_outlier_expand_rows_kernel<<<blocks, 256, 0, cs>>>(ep);
+        return check_launch("tq_outlier_expand_rows_kernel");
+    }
+    if (src->turbo) {
+        TurboExpandParams ep{};
+        ep.codes = rows; ep.norms = (is_v ? src->vn_slab : src->kn_slab) + layer * src->n_layer_stride;
+        ep.out = dst; ep.out_lo = dst_lo; ep.addr = src->addressing(); ep.len_ptr = len_ptr;
+        ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad; ep.norm_fp16 = src->norm_bytes == 2;
+        return launch_turbo_expand_rows(ep, static_cast<int>(is_v ? src->cfg.value_type : src->cfg.key_type), static_cast<int>(max_rows), cs, check_launch);
+    }
+    if (src->q8) {
+        Q8ExpandParams ep{};
+        ep.rows = rows; ep.scales = (is_v ? src->vn_slab : src->kn_slab) + layer * src->n_layer_stride;
+        ep.out = dst; ep.out_lo = dst_lo; ep.addr = src->addressing(); ep.len_ptr = len_ptr;
+        ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
+        q8_expand_rows_f16_kernel<<<blocks, 256, 0, cs>>>(ep);
+        return check_launch("q8_expand_rows_f16_kernel");
+    }
+    F16ExpandParams ep{};
+    ep.rows = rows; ep.out = reinterpret_cast<uint8_t*>(dst); ep.out_lo = reinterpret_cast<uint8_t*>(dst_lo); ep.addr = src->addressing();
+    ep.len_ptr = len_ptr; ep.seq = static_cast<int>(seq); ep.out_stride_rows = tpad;
+    f16_expand_rows_kernel<<<blocks, 256, 0, cs>>>(ep);
+    return check_launch("f16_expand_rows_kernel");
+}
+
+static bool prefill_side_is_expandable(const er_kv* c) {
+    return c->cfg.head_dim == kHeadDim && (c->turbo || c->outlier || c->q8 || (c->cfg.precision == ER_KV_FLOAT16 && !c->token_major));
+}
+
+// Chunked prefill of a layer whose two sides live in two caches, on the tensor-core prefill kernels: both sides expanded to fp16
+// hi + lo rows in the key cache's scratch (scores in the keys' space, outputs transformed back from the values' space).
+// kk->mu is held by the caller.
+static int32_t pair_prefill_tensor_core(er_kv* kk, er_kv* vv, uint32_t layer, uint32_t seq, const float* q, float* out, uint32_t num_heads,
+                                        uint32_t seq_len, uint32_t q_offset, er_step_params s, cudaStream_t cs) {
+    const int tpad = (static_cast<int>(kk->cfg.max_seq_len) + 15) & ~15;
+    const size_t rows_bytes = static_cast<size_t>(kk->cfg.num_kv_heads) * tpad * kHeadDim * 2;
+    const int n_qrows = static_cast<int>(seq_len * num_heads);
+    const size_t q_bytes = static_cast<size_t>(n_qrows) * kHeadDim * 4;
+    int32_t rc = ensure_stage(kk, 4 * rows_bytes + q_bytes + 256);
+    if (rc != ER_OK) return rc;
+    __half* ek = reinterpret_cast<__half*>(kk->d_stage);
+    __half* ev = reinterpret_cast<__half*>(kk->d_stage + rows_bytes);
+    __half* ekl = reinterpret_cast<__half*>(kk->d_stage + 2 * rows_bytes);
+    __half* evl = reinterpret_cast<__half*>(kk->d_stage + 3 * rows_bytes);
+    float* qrot = reinterpret_cast<float*>(kk->d_stage + 4 * rows_bytes);
+    const int32_t* len_ptr = kk->d_lengths + static_cast<size_t>(layer) * kk->cfg.max_batch + seq;
+    if ((rc = expand_side_for_prefill(kk, false, layer, seq, len_ptr, ek, ekl, tpad, cs)) != ER_OK) return rc;
+    if ((rc = expand_side_for_prefill(vv, true, layer, seq, len_ptr, ev, evl, tpad, cs)) != ER_OK) return rc;
+    PrefillParams pp{};
+    pp.q = q; pp.out = out;
+    if (kk->turbo || kk->outlier) {   // rotated keys: [RoPE ->] randomizedHadamard on the queries
+        TurboRotateParams rp{};
+        rp.in = q; rp.out = qrot; rp.rows = n_qrows; rp.heads = static_cast<int>(num_heads); rp.inverse = 0;
+        rp.apply_rope = s.apply_rope ? 1 : 0; rp.rope_scaling = s.rope_scaling;
+        if (rp.apply_rope) rp.inv_freq = kk->freq(s.rope_theta);
+        rp.pos_from_len = q_offset == UINT32_MAX ? 1 : 0; rp.pos0 = q_offset == UINT32_MAX ? 0u : q_offset;
+        rp.seq_len = static_cast<int>(seq_len); rp.len_ptr = len_ptr; rp.max_len = static_cast<int>(kk->cfg.max_seq_len);
+        tq_rotate_rows_kernel<<<std::min((n_qrows + 7) / 8, 4096), 256, 0, cs>>>(rp);
+        if ((rc = check_launch("tq_rotate_rows_kernel")) != ER_OK) return rc;
+        pp.q = qrot;
+        s.apply_rope = 0;
+    }
+    pp.k_layer = reinterpret_cast<const uint8_t*>(ek); pp.v_layer = reinterpret_cast<const uint8_t*>(ev);
+    pp.k_lo_layer = reinterpret_cast<const uint8_t*>(ekl); pp.v_lo_layer = reinterpret_cast<const uint8_t*>(evl);
+    pp.addr = kk->addressing();
+    pp.addr.token_major = 0; pp.addr.pages_per_seq = 0; pp.addr.page_size = tpad; pp.addr.block_table = nullptr;
+    pp.seq = 0; pp.seq_len = static_cast<int>(seq_len);
+    pp.kv_len_ptr = len_ptr;
+    {
+        const size_t want = prefill_split_partial_floats(kk->num_sms);
+        if (kk->d_prefill_partial == nullptr && cudaMalloc(&kk->d_prefill_partial, want * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            kk->d_prefill_partial = nullptr;     // the kernel runs unsplit
+        }
+        pp.split_partial = kk->d_prefill_partial;
+        pp.split_partial_floats = kk->d_prefill_partial ? want : 0;
+    }
+    pp.q_offset_from_end = q_offset == UINT32_MAX ? 1 : 0;
+    pp.q_offset = static_cast<int>(q_offset == UINT32_MAX ? 0 : q_offset);
+    pp.causal = 1;
+    pp.window = 0;
+    pp.num_q_heads = static_cast<int>(num_heads);
+    pp.scale_log2 = s.softmax_scale * 1.4426950408889634f;
+    pp.apply_rope = s.apply_rope ? 1 : 0; pp.rope_scaling = s.rope_scaling;
+    if (pp.apply_rope) pp.inv_freq = kk->freq(s.rope_theta);
+    const int rcl = launch_prefill(static_cast<int>(num_heads / kk->cfg.num_kv_heads), pp, 1u, static_cast<int>(kk->cfg.num_kv_heads), kk->d_counters + 1, cs,
+                                   kk->cfg.prefill_kernel == ER_PREFILL_KERNEL_MMA_SYNC);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rcl == -1) return fail(ER_ERR_UNSUPPORTED, "prefill kernel is built for GQA groups 1, 2, 4, 8");
+    if (rcl != 0) return fail(ER_ERR_CUDA, "prefill_f16_kernel: %s", cudaGetErrorString(static_cast<cudaError_t>(rcl)));
+    if (vv->turbo || vv->outlier) {   // rotated values: outputs back to the original space
+        TurboRotateParams rp{};
+        rp.in = out; rp.out = out; rp.rows = n_qrows; rp.heads = static_cast<int>(num_heads); rp.inverse = 1;
+        tq_rotate_rows_kernel<<<std::min((n_qrows + 7) / 8, 4096), 256, 0, cs>>>(rp);
+        if ((rc = check_launch("tq_rotate_rows_kernel")) != ER_OK) return rc;
+    }
+    return ER_OK;
+}
+
 int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer, uint32_t seq, const float* q, float* out,
                                      uint32_t num_heads, uint32_t seq_len, uint32_t q_offset, const er_step_params* sp, void* stream) {
     if (!key_cache || !value_cache || !q || !out) return fail(ER_ERR_INVALID_ARGUMENT, "null argument");
@@ -1549,6 +1660,11 @@ int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint3
         if (static_cast<int64_t>(q_offset) + seq_len != total)
             return fail(ER_ERR_UNSUPPORTED, "pair prefill: the chunk [%u, %u) must end at the sequence's %d rows", q_offset, q_offset + seq_len, total);
     }
+    const uint32_t group = num_heads / std::max<uint32_t>(key_cache->cfg.num_kv_heads, 1);
+    if (s.sliding_window == 0 && key_cache->out_heads_total == 0 && num_heads % key_cache->cfg.num_kv_heads == 0 &&
+        (group == 1 || group == 2 || group == 4 || group == 8) && prefill_side_is_expandable(key_cache) && prefill_side_is_expandable(value_cache) &&
+        key_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT && value_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT)
+        return pair_prefill_tensor_core(key_cache, value_cache, layer, seq, q, out, num_heads, seq_len, q_offset, s, static_cast<cudaStream_t>(stream));
     return simt_attention(key_cache, value_cache, layer, layer + 1, q, out, num_heads, 0, static_cast<int>(seq_len), q_pos0, static_cast<int>(seq), s,
                           static_cast<cudaStream_t>(stream));
 }

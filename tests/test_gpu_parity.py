@@ -1614,7 +1614,8 @@ def test_outlier_presets_tensor_core_policy_against_simt_kernel(er, torch, prese
 def _pair_kernels_agree(er, torch, make_key_cache, make_value_cache, Hq, Hkv, layout):
     """Decode attention over a key cache and a value cache of different row formats: the tensor-core policy of the persistent
     kernel (decode_kernel 0) against the SIMT kernel (3) on the same rows -- contexts of several tiles, ragged, an appended row
-    pending; paged caches lay their pages out independently of each other."""
+    pending; paged caches lay their pages out independently of each other.  Then two prefill chunks the same way (the
+    tensor-core prefill kernels on rows expanded from both caches against the SIMT kernel)."""
     D, L, B = 128, 2, 3
     lens = [2900, 517, 1]
     T = 3008
@@ -1650,15 +1651,26 @@ def _pair_kernels_agree(er, torch, make_key_cache, make_value_cache, Hq, Hkv, la
             kc.attention_decode_with_values_of(vc, q, out, Hq, sp, pending=1)
             kc.advance(1)
             vc.advance(1)
+        # a chunk of 150 query rows at the end of the longest sequence and one of 9 rows at the end of the second (causal)
+        chunks = []
+        for b_, S in ((0, 150), (1, 9)):
+            qc = torch.randn((S, Hq, D), generator=torch.Generator(device="cuda").manual_seed(100 + b_), device="cuda")
+            oc = torch.full((S, Hq, D), float("nan"), device="cuda")
+            kc.attention_prefill_with_values_of(vc, 1, b_, qc, oc, Hq, S, sp)
+            chunks.append(oc)
         torch.cuda.synchronize()
         assert kc.device_status() == 0 and vc.device_status() == 0
-        outs.append(out.cpu().numpy())
+        outs.append([out.cpu().numpy()] + [c_.cpu().numpy() for c_ in chunks])
         kc.close()
         vc.close()
     for l in range(L):
         for b in range(B):
-            assert attention_err(outs[0][l, b], outs[1][l, b]) < 3e-5
-            assert max_rel_err(outs[0][l, b], outs[1][l, b]) < TOL
+            assert attention_err(outs[0][0][l, b], outs[1][0][l, b]) < 3e-5
+            assert max_rel_err(outs[0][0][l, b], outs[1][0][l, b]) < TOL
+    for i in (1, 2):     # prefill chunks: the tensor-core prefill kernels on rows expanded from both caches against the SIMT kernel
+        for r in range(outs[0][i].shape[0]):
+            assert attention_err(outs[0][i][r], outs[1][i][r]) < 3e-5
+            assert max_rel_err(outs[0][i][r], outs[1][i][r]) < TOL
 
 
 PAIR_SHAPES = [(16, 8, "head_major"), (32, 8, "paged"), (4, 4, "head_major"), (16, 2, "paged")]      # groups 2, 4, 1, 8
