@@ -1451,7 +1451,7 @@ static int32_t check_pair(const er_kv* kk, const er_kv* vv) {
 }
 
 // q8_0 or float16 keys with TurboQuant values of a fixed preset (TurboValuesPolicy) and TurboQuant keys of a fixed preset with
-// float16 or q8_0 values (TurboKeysPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
+// float16 or q8_0 values (TurboKeysPolicy) and q8_0 with float16 rows (PlainPairPolicy) run the persistent kernel; every other pair, sliding windows, sharded outputs and caches created with
 // ER_DECODE_KERNEL_SIMT run the SIMT kernel.
 static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32_t num_heads, const er_step_params& s) {
     if (kk->cfg.head_dim != kHeadDim || vv->cfg.head_dim != kHeadDim) return false;
@@ -1464,6 +1464,8 @@ static bool pair_has_tensor_core_policy(const er_kv* kk, const er_kv* vv, uint32
     if (kk->turbo && vv->cfg.precision == ER_KV_FLOAT16 && !vv->token_major) return !(kk->cfg.key_type == ER_TQ_TURBO4 && group == 8);
     if (kk->turbo && vv->q8) return true;
     if (kk->cfg.precision == ER_KV_FLOAT16 && !kk->token_major && vv->turbo) return !(vv->cfg.value_type == ER_TQ_TURBO4 && group == 8);
+    if (kk->q8 && vv->cfg.precision == ER_KV_FLOAT16 && !vv->token_major) return true;
+    if (kk->cfg.precision == ER_KV_FLOAT16 && !kk->token_major && vv->q8) return true;
     return false;
 }
 
@@ -1494,7 +1496,9 @@ static int32_t pair_attention_tensor_core(er_kv* kk, er_kv* vv, uint32_t lb, uin
         p.addr_v = vv->addressing();
         p.wait_limit_us = kk->probe_wait_limit_us; p.withhold_tiles = kk->probe_withhold_tiles;
         p.scratch = kk->d_scratch; p.done_counter = kk->d_counters; p.status = kk->d_counters + 1; p.item_counters = kk->d_counters + 16;
-        const int32_t rc = kk->q8 ? decode_status(launch_decode_q8k_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 8,
+        const bool plain = !kk->turbo && !vv->turbo;   // q8_0 with float16 rows
+        const int32_t rc = plain ? decode_status(launch_decode_q8_dense_pair(group, kk->q8 ? 1 : 0, p, kk->num_sms, stream), group, kk->q8 ? 8 : 16, kk->q8 ? 16 : 8)
+                         : kk->q8 ? decode_status(launch_decode_q8k_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 8,
                                                   static_cast<int>(vv->cfg.value_type))
                          : !kk->turbo ? decode_status(launch_decode_densek_turbov(group, static_cast<int>(vv->cfg.value_type), p, kk->num_sms, stream), group, 16,
                                                       static_cast<int>(vv->cfg.value_type))

@@ -20,6 +20,81 @@
 
 namespace er {
 
+// DenseMmaPolicy's score block for any state with its query fragments: the float16 key rows at `krows` (256 bytes each) are the A
+// operands as they lie (16-byte chunks 4j + c of tokens g and g + 8).  s = (token g | g + 8) x (head 2c | 2c + 1), log2 domain.
+template <bool PACKED, class ST>
+__device__ __forceinline__ void dense_unit_scores(const DecodeParams& p, uint32_t krows, int unit, int nvalid, const ST& st, int lane, float (&s)[4]) {
+    const int g = lane >> 2, c = lane & 3;
+    const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+    const uint32_t krow = krows + (unit * kUnitTokens + g) * kRowBytesF16 + 16 * c;
+    s[0] = s[1] = s[2] = s[3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t k0[4], k1[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k0[0]), "=r"(k0[1]), "=r"(k0[2]), "=r"(k0[3]) : "r"(krow + 64 * j) : "memory");
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k1[0]), "=r"(k1[1]), "=r"(k1[2]), "=r"(k1[3]) : "r"(krow + 64 * j + 8 * kRowBytesF16) : "memory");
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.qh[2 * j + u][0], st.qh[2 * j + u][1]);
+            if constexpr (!PACKED) mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.ql[2 * j + u][0], st.ql[2 * j + u][1]);
+        }
+    }
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
+    }
+    // rows at or past nvalid were never copied (stale shared memory, possibly NaN patterns): the select discards them
+    s[0] = ok0 ? s[0] * p.scale_log2 : -INFINITY;
+    s[1] = ok0 ? s[1] * p.scale_log2 : -INFINITY;
+    s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
+    s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
+}
+
+// DenseMmaPolicy's output block for any state with its accumulator order: B = 4096 p as fp16 hi + lo, A = transposed value blocks
+// of the 256-byte rows at `vrows`.
+template <bool PACKED, class ST>
+__device__ __forceinline__ void dense_unit_values(ST& st, uint32_t vrows, int unit, int nvalid, const float (&pr)[4], int lane) {
+    constexpr float kProbScale = 4096.f;   // DenseMmaPolicy::kProbScale: State::publish divides it out
+    const int g = lane >> 2, c = lane & 3;
+    const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+    const float w0 = pr[0] * kProbScale, w1 = pr[1] * kProbScale, w2 = pr[2] * kProbScale, w3 = pr[3] * kProbScale;
+    const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
+    const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
+    const uint32_t b0 = movmatrix_trans(PACKED && c >= 2 ? lo01 : hi01);
+    const uint32_t b1 = movmatrix_trans(PACKED && c >= 2 ? lo23 : hi23);
+    uint32_t b0l = 0, b1l = 0;
+    if constexpr (!PACKED) {
+        b0l = movmatrix_trans(lo01);
+        b1l = movmatrix_trans(lo23);
+    }
+    const uint32_t vrow = vrows + (unit * kUnitTokens + g) * kRowBytesF16 + 16 * c;
+    const bool partial = nvalid < kUnitTokens;   // warp-uniform
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t v0[4], v1[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0[0]), "=r"(v0[1]), "=r"(v0[2]), "=r"(v0[3]) : "r"(vrow + 64 * j) : "memory");
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1[0]), "=r"(v1[1]), "=r"(v1[2]), "=r"(v1[3]) : "r"(vrow + 64 * j + 8 * kRowBytesF16) : "memory");
+        if (partial) {   // 0 x NaN would poison the accumulators: stale rows become zeros
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                v0[e] = ok0 ? v0[e] : 0u;
+                v1[e] = ok1 ? v1[e] : 0u;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const uint32_t a0 = movmatrix_trans(v0[2 * u]);
+            const uint32_t a1 = movmatrix_trans(v0[2 * u + 1]);
+            const uint32_t a2 = movmatrix_trans(v1[2 * u]);
+            const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
+            mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
+            if constexpr (!PACKED) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
+        }
+    }
+}
+
 template <int GROUP, int VBITS, bool Q8_KEYS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
 struct TurboValuesPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES> {
     using TM = TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, WARP_GROUPS, STAGES>;   // tables, value lookups, state, output transform
@@ -120,29 +195,7 @@ struct TurboValuesPolicy : TurboMmaPolicy<GROUP, VBITS, VBITS, UNITS_PER_TILE, W
         if constexpr (Q8_KEYS) {
             Q8::unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
         } else {
-            // DenseMmaPolicy's score block: the key rows are the A operands as they lie (16-byte chunks 4j + c of tokens g and g + 8)
-            const uint32_t krow = sbase + r0 * kRowBytesF16 + 16 * c;
-            s[0] = s[1] = s[2] = s[3] = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t k0[4], k1[4];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k0[0]), "=r"(k0[1]), "=r"(k0[2]), "=r"(k0[3]) : "r"(krow + 64 * j) : "memory");
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k1[0]), "=r"(k1[1]), "=r"(k1[2]), "=r"(k1[3]) : "r"(krow + 64 * j + 8 * kRowBytesF16) : "memory");
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.qh[2 * j + u][0], st.qh[2 * j + u][1]);
-                    if constexpr (!TM::kPacked) mma_m16n8k16(s, k0[2 * u], k1[2 * u], k0[2 * u + 1], k1[2 * u + 1], st.ql[2 * j + u][0], st.ql[2 * j + u][1]);
-                }
-            }
-            if constexpr (TM::kPacked) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 2);
-            }
-            // rows at or past nvalid were never copied (stale shared memory, possibly NaN patterns): the select discards them
-            s[0] = ok0 ? s[0] * p.scale_log2 : -INFINITY;
-            s[1] = ok0 ? s[1] * p.scale_log2 : -INFINITY;
-            s[2] = ok1 ? s[2] * p.scale_log2 : -INFINITY;
-            s[3] = ok1 ? s[3] * p.scale_log2 : -INFINITY;
+            dense_unit_scores<TM::kPacked>(p, sbase, unit, nvalid, st, lane, s);
         }
         mma_softmax_step(st, s, pr);
 
@@ -281,48 +334,6 @@ struct TurboKeysPolicy {
         st.reset();
     }
 
-    // DenseMmaPolicy's output block: B = 4096 p as fp16 hi + lo, A = transposed value blocks of the 256-byte rows at `vrows`.
-    __device__ __forceinline__ static void dense_unit_values(State& st, uint32_t vrows, int unit, int nvalid, const float (&pr)[4], int lane) {
-        const int g = lane >> 2, c = lane & 3;
-        const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
-        const float w0 = pr[0] * DM::kProbScale, w1 = pr[1] * DM::kProbScale, w2 = pr[2] * DM::kProbScale, w3 = pr[3] * DM::kProbScale;
-        const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
-        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const uint32_t hi01 = *reinterpret_cast<const uint32_t*>(&h01), hi23 = *reinterpret_cast<const uint32_t*>(&h23);
-        const uint32_t lo01 = pack_half2(w0 - f01.x, w1 - f01.y), lo23 = pack_half2(w2 - f23.x, w3 - f23.y);
-        const uint32_t b0 = movmatrix_trans(kPacked && c >= 2 ? lo01 : hi01);
-        const uint32_t b1 = movmatrix_trans(kPacked && c >= 2 ? lo23 : hi23);
-        uint32_t b0l = 0, b1l = 0;
-        if constexpr (!kPacked) {
-            b0l = movmatrix_trans(lo01);
-            b1l = movmatrix_trans(lo23);
-        }
-        const uint32_t vrow = vrows + (unit * kUnitTokens + g) * kRowBytesF16 + 16 * c;
-        const bool partial = nvalid < kUnitTokens;   // warp-uniform
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint32_t v0[4], v1[4];
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0[0]), "=r"(v0[1]), "=r"(v0[2]), "=r"(v0[3]) : "r"(vrow + 64 * j) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1[0]), "=r"(v1[1]), "=r"(v1[2]), "=r"(v1[3]) : "r"(vrow + 64 * j + 8 * kRowBytesF16) : "memory");
-            if (partial) {   // 0 x NaN would poison the accumulators: stale rows become zeros
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    v0[e] = ok0 ? v0[e] : 0u;
-                    v1[e] = ok1 ? v1[e] : 0u;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const uint32_t a0 = movmatrix_trans(v0[2 * u]);
-                const uint32_t a1 = movmatrix_trans(v0[2 * u + 1]);
-                const uint32_t a2 = movmatrix_trans(v1[2 * u]);
-                const uint32_t a3 = movmatrix_trans(v1[2 * u + 1]);
-                mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0, b1);
-                if constexpr (!kPacked) mma_m16n8k16(st.acc[2 * j + u], a0, a1, a2, a3, b0l, b1l);
-            }
-        }
-    }
-
     __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
                                         const uint8_t*, int lane) {
         const int g = lane >> 2, c = lane & 3;
@@ -363,7 +374,7 @@ struct TurboKeysPolicy {
         float pr[4];
         mma_softmax_step(st, s, pr);
         if constexpr (Q8_VALUES) Q8::unit_values(st, sbase + kOffV, sbase + kOffVs, unit, nvalid, pr, lane);
-        else dense_unit_values(st, sbase + kOffV, unit, nvalid, pr, lane);
+        else dense_unit_values<kPacked>(st, sbase + kOffV, unit, nvalid, pr, lane);
     }
 };
 
@@ -371,5 +382,92 @@ template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, in
 using TurboKDenseVPolicy = TurboKeysPolicy<GROUP, KBITS, false, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
 template <int GROUP, int KBITS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 3>
 using TurboKQ8VPolicy = TurboKeysPolicy<GROUP, KBITS, true, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+
+// PlainPairPolicy: q8_0 keys with float16 values or float16 keys with q8_0 values -- neither side is rotated and neither needs a
+// table; Q8MmaPolicy and DenseMmaPolicy share one query fragment order and one accumulator order.
+// Stage = K rows [| K block scales] | V rows [| V block scales].
+template <int GROUP, bool Q8_KEYS, int UNITS_PER_TILE = 11, int WARP_GROUPS = 1, int STAGES = 2>
+struct PlainPairPolicy {
+    static constexpr bool Q8_VALUES = !Q8_KEYS;
+    using DM = DenseMmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+    using Q8 = Q8MmaPolicy<GROUP, UNITS_PER_TILE, WARP_GROUPS, STAGES>;
+    using State = std::conditional_t<Q8_VALUES, typename Q8::State, typename DM::State>;   // the value side's probability scale
+    static constexpr int kGroup = GROUP;
+    static constexpr int kUnitsPerTile = UNITS_PER_TILE;
+    static constexpr int kWarpGroups = WARP_GROUPS;
+    static constexpr int kStages = STAGES;
+    static constexpr int kTileTokens = UNITS_PER_TILE * kUnitTokens;
+    static constexpr int kThreads = (UNITS_PER_TILE * WARP_GROUPS + 1) * 32;
+    static constexpr int kKRowBytes = Q8_KEYS ? 128 : kRowBytesF16, kVRowBytes = Q8_VALUES ? 128 : kRowBytesF16;
+    static constexpr int kOffKs = kTileTokens * kKRowBytes;
+    static constexpr int kOffV = kOffKs + (Q8_KEYS ? kTileTokens * 8 : 0);
+    static constexpr int kOffVs = kOffV + kTileTokens * kVRowBytes;
+    static constexpr int kStageBytes = kOffVs + (Q8_VALUES ? kTileTokens * 8 : 0);
+    static constexpr int kExtraBytes = 0;
+    static constexpr bool kRotated = false;
+    static constexpr bool kFusedAppend = false;
+    static constexpr int kFoldUnits = 32;
+    static constexpr bool kPacked = Q8::kPacked;
+    static_assert(STAGES % WARP_GROUPS == 0, "STAGES must be a multiple of WARP_GROUPS");
+
+    __device__ static float* fin_ptr(uint8_t*) { return nullptr; }
+    __device__ static bool init_extra(uint8_t*, int, int) { return true; }
+    __device__ static void patch_new_row(const DecodeParams&, uint8_t*, int, int, int, int, int, int, const float*, const float*,
+                                         const float2*, int) {}
+    __device__ static void store_out(const DecodeParams&, int64_t, const float*, int, int) {}
+
+    template <class WAIT>
+    __device__ static void issue_tile(const DecodeParams& p, uint8_t* stage, uint64_t* bar, int layer, int seq, int head,
+                                      int t0, int ntok, int lane, int /*ring start: fp16 caches only*/, WAIT&& wait_free) {
+        const uint8_t* kr = p.k_base + static_cast<int64_t>(layer) * p.k_layer_stride_bytes;
+        const uint8_t* ks = Q8_KEYS ? p.kn_base + static_cast<int64_t>(layer) * p.n_layer_stride_bytes : nullptr;
+        const uint8_t* vr = p.v_base + static_cast<int64_t>(layer) * p.v_layer_stride_bytes;
+        const uint8_t* vs = Q8_VALUES ? p.vn_base + static_cast<int64_t>(layer) * p.vn_layer_stride_bytes : nullptr;
+        const int kps = p.addr.page_size, vps = p.addr_v.page_size;
+        const int kfirst = t0 / kps, kseg = (t0 + ntok - 1) / kps - kfirst + 1;
+        const int vfirst = t0 / vps, vseg = (t0 + ntok - 1) / vps - vfirst + 1;
+        wait_free();
+        if (lane == 0) {   // scale copies are rounded up to 16 bytes per page segment of the q8_0 side
+            uint32_t bytes = static_cast<uint32_t>(ntok) * (kKRowBytes + kVRowBytes);
+            const int ps = Q8_KEYS ? kps : vps, first = Q8_KEYS ? kfirst : vfirst, nseg = Q8_KEYS ? kseg : vseg;
+            for (int i = 0; i < nseg; ++i) {
+                const int tb = max(t0, (first + i) * ps), te = min(t0 + ntok, (first + i + 1) * ps);
+                bytes += (static_cast<uint32_t>(te - tb) * 8u + 15u) & ~15u;
+            }
+            mbar_arrive_expect_tx(bar, bytes);
+        }
+        __syncwarp();
+        for (int c = lane; c < 2 * (kseg + vseg); c += 32) {
+            const bool value_side = c >= 2 * kseg;
+            const int i = value_side ? c - 2 * kseg : c, kind = i & 1, sgi = i >> 1;
+            const int ps = value_side ? vps : kps, first = value_side ? vfirst : kfirst;
+            const int tb = max(t0, (first + sgi) * ps), te = min(t0 + ntok, (first + sgi + 1) * ps);
+            const uint32_t rows = static_cast<uint32_t>(te - tb);
+            const int64_t row = row_index(value_side ? p.addr_v : p.addr, seq, head, tb);
+            if (!value_side) {
+                if (kind == 0) bulk_g2s(stage + (tb - t0) * kKRowBytes, kr + row * kKRowBytes, rows * kKRowBytes, bar);
+                else if constexpr (Q8_KEYS) bulk_g2s(stage + kOffKs + (tb - t0) * 8, ks + row * 8, (rows * 8 + 15u) & ~15u, bar);
+            } else {
+                if (kind == 0) bulk_g2s(stage + kOffV + (tb - t0) * kVRowBytes, vr + row * kVRowBytes, rows * kVRowBytes, bar);
+                else if constexpr (Q8_VALUES) bulk_g2s(stage + kOffVs + (tb - t0) * 8, vs + row * 8, (rows * 8 + 15u) & ~15u, bar);
+            }
+        }
+    }
+
+    __device__ static void load_q(const DecodeParams& p, State& st, const float* qrow, const float2* cs, uint8_t*, int, int lane, int) {
+        Q8::load_q_fragments(p, st, qrow, cs, lane);
+    }
+
+    __device__ static void process_unit(const DecodeParams& p, const uint8_t* stage, int unit, int nvalid, State& st, float*,
+                                        const uint8_t*, int lane) {
+        const uint32_t sbase = smem_u32(stage);
+        float s[4], pr[4];
+        if constexpr (Q8_KEYS) Q8::unit_scores(p, sbase, sbase + kOffKs, unit, nvalid, st, lane, s);
+        else dense_unit_scores<kPacked>(p, sbase, unit, nvalid, st, lane, s);
+        mma_softmax_step(st, s, pr);
+        if constexpr (Q8_VALUES) Q8::unit_values(st, sbase + kOffV, sbase + kOffVs, unit, nvalid, pr, lane);
+        else dense_unit_values<kPacked>(st, sbase + kOffV, unit, nvalid, pr, lane);
+    }
+};
 
 }  // namespace er

@@ -30,6 +30,8 @@ int launch_decode_q8k_turbov(int group, int vbits, const DecodeParams& p, int gr
 int launch_decode_densek_turbov(int group, int vbits, const DecodeParams& p, int grid, cudaStream_t stream);
 // TurboQuant keys of a fixed preset with float16 values (head-major or paged rows); kNotBuilt for 4-bit keys with eight heads per kv head
 int launch_decode_turbok_densev(int group, int kbits, const DecodeParams& p, int grid, cudaStream_t stream);
+// q8_0 keys with float16 values (q8_keys != 0) or float16 keys with q8_0 values
+int launch_decode_q8_dense_pair(int group, int q8_keys, const DecodeParams& p, int grid, cudaStream_t stream);
 // TurboQuant keys of a fixed preset with q8_0 values (p.v_* rows, p.vn_* block scales)
 int launch_decode_turbok_q8v(int group, int kbits, const DecodeParams& p, int grid, cudaStream_t stream);
 // balanced (3 / 5 bits) and aggressive (2 / 3 bits) TurboQuant rows, groups 1, 2, 4 (decode_outlier.cu); kNotBuilt otherwise

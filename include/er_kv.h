@@ -363,8 +363,8 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
  * in two caches of the same geometry (max_seq_len, max_batch, num_kv_heads, num_layers): append the step's rows to both
  * (er_kv_append_rope_kv), run attention with the K rows of `key_cache` and the V rows of `value_cache`, advance both.  Any
  * pair of float16 (head-major / paged), q8_0 and TurboQuant caches (all presets) is accepted; positions are the key cache's.
- * Decode runs on the tensor cores for q8_0 or float16 keys with fixed-preset TurboQuant values and for fixed-preset TurboQuant
- * keys with float16 or q8_0 values (GQA groups 1, 2, 4, 8; no sliding window); the prefill form expands both sides to fp16 rows and
+ * Decode runs on the tensor cores for every pair of float16 (head-major / paged), q8_0 and fixed-preset TurboQuant caches (GQA
+ * groups 1, 2, 4, 8; no sliding window); the prefill form expands both sides to fp16 rows and
  * runs the tensor-core prefill kernel for any pair; a plain SIMT kernel serves the other decode pairs and sliding windows (correct, not
  * tuned).  With a sliding window the prefill form takes a chunk that ends at the newest row. */
 int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer_begin, uint32_t layer_end, const float* q,

@@ -1722,3 +1722,12 @@ def test_float16_keys_with_turboquant_values_tensor_core_policy_against_simt_ker
                         lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.turboquantV2, key_type=vbits, value_type=vbits,
                                                                norm_format=er.NormFormat.float32, **kw),
                         Hq, Hkv, layout)
+
+
+@pytest.mark.parametrize("q8_keys", [True, False])
+@pytest.mark.parametrize("Hq,Hkv,layout", PAIR_SHAPES)
+def test_q8_with_float16_rows_tensor_core_policy_against_simt_kernel(er, torch, q8_keys, Hq, Hkv, layout):
+    """q8_0 keys with float16 values and float16 keys with q8_0 values."""
+    q8 = lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.q8_0, **kw)
+    f16 = lambda T, L, Hkv_, D, **kw: er.KVCache(T, L, Hkv_, D, er.Precision.float16, **{**kw, "layout": kw.get("layout", er.Layout.head_major)})
+    _pair_kernels_agree(er, torch, q8 if q8_keys else f16, f16 if q8_keys else q8, Hq, Hkv, layout)
