@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "liber_kv.so")
-SOURCES = ["er_kv.cu", "decode_dense.cu", "decode_turbo.cu", "decode_q8.cu", "no_alloc.cu", "prefill.cu", "prefill_umma.cu", "decode_generic.cu", "attention_f32.cu", "decode_slim.cu", "decode_outlier.cu", "decode_turbo2.cu", "decode_hybrid.cu"]
+SOURCES = ["er_kv.cu", "decode_dense.cu", "decode_turbo.cu", "decode_q8.cu", "no_alloc.cu", "prefill.cu", "prefill_umma.cu", "decode_generic.cu", "attention_f32.cu", "decode_slim.cu", "decode_outlier.cu", "decode_turbo2.cu", "decode_hybrid.cu", "decode_hybrid_keys.cu", "decode_hybrid_plain.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
