@@ -80,6 +80,12 @@ WORKLOADS = {
     "cfg2_aggressive_4layers": dict(name="cfg2 shape with aggressive TurboQuant rows (2 / 3 bits, 80-byte rows), 4 of its 28 layers",
                                     layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="aggressive", residual_scale=1.0 / 128,
                                     layout="head_major", theta=1.0e6, outliers=True),
+    # layers whose keys and values use different row formats (two caches): the cfg2 shape with 4 layers, decode attention only
+    **{"pair_%s_%s%s" % (k_, v_, "_simt" if simt_ else ""): dict(
+        name="cfg2 shape, 4 layers: %s keys with %s values in two caches, decode attention%s" % (k_, v_, " on the SIMT kernel" if simt_ else ""),
+        layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, keys=k_, values=v_, simt=simt_, theta=1.0e6)
+       for k_, v_ in (("q8_0", "turbo3"), ("turbo3", "q8_0"), ("turbo4", "float16"), ("float16", "turbo3"), ("q8_0", "float16"))
+       for simt_ in (False, True)},
     "cfg2_4layers": dict(name="cfg2 shape with 4 of its 28 layers (about 1 GB on the device: the size profiler captures use)",
                          layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="turboquant", kbits=4, vbits=3,
                          norm="float16", layout="head_major", theta=1.0e6, outliers=True),
@@ -849,6 +855,70 @@ def run_prefill(args, w):
         "gpu_launches": int(er.lib().er_kernel_launch_count() - launches0), "clocks": clocks}))
 
 
+PAIR_SIDES = {   # cache arguments and cached bytes per (token, kv head) of one side
+    "float16": (lambda er: dict(precision=er.Precision.float16, layout=er.Layout.head_major), 256),
+    "q8_0": (lambda er: dict(precision=er.Precision.q8_0), 136),
+    "turbo2": (lambda er: dict(precision=er.Precision.turboquantV2, key_type=2, value_type=2, norm_format=er.NormFormat.float16), 34),
+    "turbo3": (lambda er: dict(precision=er.Precision.turboquantV2, key_type=3, value_type=3, norm_format=er.NormFormat.float16), 50),
+    "turbo4": (lambda er: dict(precision=er.Precision.turboquantV2, key_type=4, value_type=4, norm_format=er.NormFormat.float16), 66),
+}
+
+
+def run_pair(args, w):
+    """Decode attention of layers whose keys and values live in two caches of different row formats (er_kv_attention_decode_pair):
+    step = one attention launch over all layers and sequences of the workload, rows resident; achieved = the cached bytes of the
+    key side of one cache and the value side of the other, per launch, over CUDA-event time."""
+    import torch
+    import edgerunner_b200 as er
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    L, B, H, Hkv, ctx = w["layers"], w["batch"], w["heads"], w["kv_heads"], w["ctx"]
+    (kargs, kbytes), (vargs, vbytes) = PAIR_SIDES[w["keys"]], PAIR_SIDES[w["values"]]
+    dk = 3 if w.get("simt") else 0
+    mk = lambda side: er.KVCache(ctx + 64, L, Hkv, D, side(er).pop("precision"), max_batch=B, decode_kernel=dk,
+                                 **{k_: v_ for k_, v_ in side(er).items() if k_ != "precision"})
+    kc, vc = mk(kargs), mk(vargs)
+    sp = er.step_params(rope_theta=w["theta"])
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for cache in (kc, vc):
+        for l in range(L):
+            for b in range(B):
+                for s0 in range(0, ctx, 8192):
+                    n = min(8192, ctx - s0)
+                    cache.write_rows(l, b, s0, n, torch.randn((n, Hkv, D), device="cuda", generator=g).half().float(),
+                                     torch.randn((n, Hkv, D), device="cuda", generator=g).half().float(), sp)
+    q = torch.randn((L, B, H, D), device="cuda", generator=g).half().float()
+    out = torch.empty_like(q)
+    K, W = args.steps, max(args.warmup, 0)
+    for _ in range(W):
+        kc.attention_decode_with_values_of(vc, q, out, H, sp)
+    torch.cuda.synchronize()
+    launches0 = er.lib().er_kernel_launch_count()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        kc.attention_decode_with_values_of(vc, q, out, H, sp)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    assert kc.device_status() == 0
+    ms = e0.elapsed_time(e1) / K
+    nbytes = L * B * Hkv * ctx * (kbytes + vbytes) + 2 * L * B * H * D * 4
+    peak, peak_src = measured_peaks()
+    achieved = nbytes / ms / 1e6
+    print(json.dumps({
+        "metric": "decode_attention_launches_per_s", "value": round(1e3 / ms, 2), "unit": "launches/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "layers": L, "batch": B, "q_heads": H, "kv_heads": Hkv, "context": ctx, "keys": w["keys"],
+                   "values": w["values"], "kernel": "simt_decode_kernel" if dk else "flash_decode_kernel"},
+        "roofline": {"bound": "hbm", "kernel": "simt_decode_kernel" if dk else "flash_decode_kernel", "achieved": round(achieved, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": int(nbytes)},
+        "gpu_launches": int(er.lib().er_kernel_launch_count() - launches0), "clocks": clocks}))
+
+
 def run_cfg4(args):
     """benchmark contract, configuration [4]: Qwen3-4B shape (36 layers, 32 q / 8 kv heads), TurboQuant turbo4 K / turbo4 V rows with fp16 norms in
     64-token pages, sequences at context 131072: ONE chunked-prefill step that appends 2048 tokens per sequence (causal,
@@ -987,11 +1057,11 @@ def main():
             return
         run_cfg4(args)
         return
-    if w.get("prefill"):
+    if w.get("prefill") or w.get("keys"):
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "the prefill workloads are measured on the GPU path only"}))
+            print(json.dumps({"impl": "reference", "unavailable": "the prefill and cache-pair workloads are measured on the GPU path only"}))
             return
-        run_prefill(args, w)
+        (run_prefill if w.get("prefill") else run_pair)(args, w)
         return
     lens = sequence_lengths(w)
     if args.impl == "reference":
