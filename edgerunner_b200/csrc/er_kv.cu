@@ -1655,6 +1655,13 @@ int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint3
                          static_cast<cudaStream_t>(stream));
     if (rc != ER_OK) return rc;
     std::lock_guard<std::mutex> lock(key_cache->mu);
+    {   // the tensor-core prefill kernels take a chunk anywhere in the sequence
+        const uint32_t group = num_heads / std::max<uint32_t>(key_cache->cfg.num_kv_heads, 1);
+        if (s.sliding_window == 0 && key_cache->out_heads_total == 0 && num_heads % key_cache->cfg.num_kv_heads == 0 &&
+            (group == 1 || group == 2 || group == 4 || group == 8) && prefill_side_is_expandable(key_cache) && prefill_side_is_expandable(value_cache) &&
+            key_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT && value_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT)
+            return pair_prefill_tensor_core(key_cache, value_cache, layer, seq, q, out, num_heads, seq_len, q_offset, s, static_cast<cudaStream_t>(stream));
+    }
     // query row r sits at position q_offset + r (UINT32_MAX: the chunk's rows are the newest rows) and sees the keys up to it
     const int q_pos0 = q_offset == UINT32_MAX ? -1 : static_cast<int>(q_offset);
     if (q_pos0 >= 0) {
@@ -1664,11 +1671,6 @@ int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint3
         if (static_cast<int64_t>(q_offset) + seq_len != total)
             return fail(ER_ERR_UNSUPPORTED, "pair prefill: the chunk [%u, %u) must end at the sequence's %d rows", q_offset, q_offset + seq_len, total);
     }
-    const uint32_t group = num_heads / std::max<uint32_t>(key_cache->cfg.num_kv_heads, 1);
-    if (s.sliding_window == 0 && key_cache->out_heads_total == 0 && num_heads % key_cache->cfg.num_kv_heads == 0 &&
-        (group == 1 || group == 2 || group == 4 || group == 8) && prefill_side_is_expandable(key_cache) && prefill_side_is_expandable(value_cache) &&
-        key_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT && value_cache->cfg.decode_kernel != ER_DECODE_KERNEL_SIMT)
-        return pair_prefill_tensor_core(key_cache, value_cache, layer, seq, q, out, num_heads, seq_len, q_offset, s, static_cast<cudaStream_t>(stream));
     return simt_attention(key_cache, value_cache, layer, layer + 1, q, out, num_heads, 0, static_cast<int>(seq_len), q_pos0, static_cast<int>(seq), s,
                           static_cast<cudaStream_t>(stream));
 }

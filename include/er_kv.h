@@ -366,7 +366,7 @@ int32_t er_kv_attention_prefill(er_kv* kv, uint32_t layer, uint32_t seq, const f
  * Decode runs on the tensor cores for every pair of float16 (head-major / paged), q8_0 and fixed-preset TurboQuant caches (GQA
  * groups 1, 2, 4, 8; no sliding window); the prefill form expands both sides to fp16 rows and
  * runs the tensor-core prefill kernel for any pair; a plain SIMT kernel serves the other decode pairs and sliding windows (correct, not
- * tuned).  With a sliding window the prefill form takes a chunk that ends at the newest row. */
+ * tuned).  On the SIMT kernel (sliding windows, ER_DECODE_KERNEL_SIMT) the prefill form takes a chunk that ends at the newest row. */
 int32_t er_kv_attention_decode_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer_begin, uint32_t layer_end, const float* q,
                                     float* out, uint32_t num_heads, uint32_t pending, const er_step_params* params, void* stream);
 int32_t er_kv_attention_prefill_pair(er_kv* key_cache, er_kv* value_cache, uint32_t layer, uint32_t seq, const float* q, float* out,

@@ -462,6 +462,17 @@ def test_mixed_family_layers_through_pair_caches(er, torch, oracle, contract_kw,
         want = oracle.gqa_f32(qr, Kd[:n - S + r + 1], Vd[:n - S + r + 1], causal=False)[0]
         floor = 1e-3 * np.abs(want).max()
         worst = max(worst, float(np.max(np.abs(gp[r] - want) / np.maximum(np.abs(want), floor))))
+    # the same rows as a chunk in the middle of the sequence (positions 20 .. 35): later rows stay invisible
+    off = 20
+    outm = torch.full((S, Hq, D), float("nan"), device="cuda")
+    pc.attention_prefill(0, 0, torch.as_tensor(qc).cuda(), outm, Hq, S, sp, q_offset=off)
+    torch.cuda.synchronize()
+    gm = outm.cpu().numpy()
+    for r in range(S):
+        qr = oracle.rope_neox(qc[r][None], off + r, theta)
+        want = oracle.gqa_f32(qr, Kd[:off + r + 1], Vd[:off + r + 1], causal=False)[0]
+        floor = 1e-3 * np.abs(want).max()
+        worst = max(worst, float(np.max(np.abs(gm[r] - want) / np.maximum(np.abs(want), floor))))
     print("%s keys / %s values: worst element-wise relative error %.2e" % (layer_pair[0], layer_pair[1], worst))
     assert worst < 2e-3
     assert kc.device_status() == 0 and vc.device_status() == 0
