@@ -204,3 +204,24 @@ def test_policy_cache_pairs_for_mixed_family_layers():
     assert cache_arguments("q8_0", "turbo3") is None and cache_arguments("turbo3", "dense") is None      # two caches, one per side
     c = er.TurboQuantLayerContract(early_q8_key_layers=1)
     assert (c.key_cache_type_for(0, 4), c.value_cache_type_for(0, 4)) == ("q8_0", "turbo3")
+
+
+def test_bench_workload_table_is_consistent():
+    """Every workload of bench.py names a format the script can build and account bytes for (no GPU involved: the table only)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.DEFAULT_WORKLOAD in bench.WORKLOADS
+    for name, w in bench.WORKLOADS.items():
+        assert w["name"] and w["heads"] % w["kv_heads"] == 0, name
+        if "keys" in w:                                    # cache pairs
+            assert w["keys"] in bench.PAIR_SIDES and w["values"] in bench.PAIR_SIDES and w["keys"] != w["values"], name
+            continue
+        assert w["precision"] in ("float16", "q8_0", "turboquant", "balanced", "aggressive"), name
+        if w["precision"] == "turboquant":
+            assert w["kbits"] in (2, 3, 4) and w["vbits"] in (2, 3, 4), name
+        assert bench.row_bytes(w) in (512, 272, 192, 160) or w["precision"] == "turboquant", name
+        if w.get("layout") == "paged":
+            assert w["page_size"] % 16 == 0, name
