@@ -77,6 +77,9 @@ WORKLOADS = {
     "cfg2_balanced_4layers_simt": dict(name="cfg2 shape with balanced TurboQuant rows, 4 of its 28 layers, on the SIMT kernel",
                                        layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="balanced", residual_scale=1.0 / 128,
                                        decode_kernel=3, layout="head_major", theta=1.0e6, outliers=True),
+    "cfg2_balanced_4layers_contract": dict(name="cfg2 shape with balanced TurboQuant rows, 4 of its 28 layers, residual scales 0 (the reference's contract)",
+                                           layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="balanced", residual_scale=0.0,
+                                           layout="head_major", theta=1.0e6, outliers=True),
     "cfg2_aggressive_4layers": dict(name="cfg2 shape with aggressive TurboQuant rows (2 / 3 bits, 80-byte rows), 4 of its 28 layers",
                                     layers=4, batch=8, heads=16, kv_heads=8, ctx=32768, precision="aggressive", residual_scale=1.0 / 128,
                                     layout="head_major", theta=1.0e6, outliers=True),

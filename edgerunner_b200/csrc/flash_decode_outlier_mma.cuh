@@ -221,8 +221,9 @@ struct OutlierMmaPolicy {
         if (src != nullptr) { src->s0 = s0; src->s1 = s1; src->rank = rank; }
     }
 
-    // Score k-step S for tokens g (sa) and g + 8 (sb): channels 4S .. 4S + 3 of the thread's 32; ss = SIGN . q of both tokens.
-    template <int S>
+    // Score k-step S for tokens g (sa) and g + 8 (sb): channels 4S .. 4S + 3 of the thread's 32; ss = SIGN . q of both tokens
+    // (SIGNS = false: the residual scale of the keys is 0, the reference's contract, and the sign products are left out).
+    template <int S, bool SIGNS>
     __device__ __forceinline__ static void score_steps(float (&sa)[4], float (&sb)[4], float (&ss)[4], const uint32_t (&ka)[RB],
                                                        const uint32_t (&kb)[RB], uint32_t ma, uint32_t mb, SideBits& da, SideBits& db,
                                                        const SideSource& ra, const SideSource& rb, uint32_t ga, uint32_t gb, const State& st) {
@@ -240,18 +241,20 @@ struct OutlierMmaPolicy {
                          __byte_perm(ea2, ea3, 0x7632), st.qh[S][0], st.qh[S][1]);
             mma_m16n8k16(sb, __byte_perm(eb0, eb1, 0x5410), __byte_perm(eb0, eb1, 0x7632), __byte_perm(eb2, eb3, 0x5410),
                          __byte_perm(eb2, eb3, 0x7632), st.qh[S][0], st.qh[S][1]);
-            uint32_t g0, g1, g2, g3;   // (token g, token g + 8) x channels (4S, 4S + 1 | 4S + 2, 4S + 3)
-            sign_regs<4 * S>(st.lut_v, ga, gb, g0, g1);
-            sign_regs<4 * S + 2>(st.lut_v, ga, gb, g2, g3);
-            mma_m16n8k16(ss, g0, g1, g2, g3, st.qh[S][0], st.qh[S][1]);
-            score_steps<S + 1>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
+            if constexpr (SIGNS) {
+                uint32_t g0, g1, g2, g3;   // (token g, token g + 8) x channels (4S, 4S + 1 | 4S + 2, 4S + 3)
+                sign_regs<4 * S>(st.lut_v, ga, gb, g0, g1);
+                sign_regs<4 * S + 2>(st.lut_v, ga, gb, g2, g3);
+                mma_m16n8k16(ss, g0, g1, g2, g3, st.qh[S][0], st.qh[S][1]);
+            }
+            score_steps<S + 1, SIGNS>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
         }
     }
 
     static constexpr int kVWords = RB == 2 ? 1 : 2;   // 16 channels of RB bits
     // Output m-tile T (dims 16g + 2T in row g, 16g + 2T + 1 in row g + 8): centroids of the thread's four tokens against the
     // duplicated probabilities, signs of all four against the (token pair) sign weights.
-    template <int T>
+    template <int T, bool SIGNS>
     __device__ __forceinline__ static void value_tiles(State& st, const uint32_t (&vw)[4][kVWords], const uint32_t (&vm)[4], SideBits (&vd)[4],
                                                        const uint32_t (&vg)[4], const uint32_t (&bh)[4], uint32_t bs0, uint32_t bs1) {
         if constexpr (T < 8) {
@@ -263,11 +266,13 @@ struct OutlierMmaPolicy {
                 const uint32_t a3 = lds_u32(entry_addr<2 * T + 1>(vw[2 * j + 1], vm[2 * j + 1], vd[2 * j + 1], st.lut_k));
                 mma_m16n8k16(st.acc[T], a0, a1, a2, a3, bh[2 * j], bh[2 * j + 1]);
             }
-            uint32_t g0, g1, g2, g3;   // (channel 2T, channel 2T + 1) x tokens (2c, 2c + 1 | 2c + 8, 2c + 9)
-            sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[0], vg[1], g0, g1);
-            sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[2], vg[3], g2, g3);
-            mma_m16n8k16(st.acc[T], g0, g1, g2, g3, bs0, bs1);
-            value_tiles<T + 1>(st, vw, vm, vd, vg, bh, bs0, bs1);
+            if constexpr (SIGNS) {
+                uint32_t g0, g1, g2, g3;   // (channel 2T, channel 2T + 1) x tokens (2c, 2c + 1 | 2c + 8, 2c + 9)
+                sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[0], vg[1], g0, g1);
+                sign_regs<2 * T>(st.lut_v + kSignTableBytes, vg[2], vg[3], g2, g3);
+                mma_m16n8k16(st.acc[T], g0, g1, g2, g3, bs0, bs1);
+            }
+            value_tiles<T + 1, SIGNS>(st, vw, vm, vd, vg, bh, bs0, bs1);
         }
     }
 
@@ -300,7 +305,8 @@ struct OutlierMmaPolicy {
             span_words<false>(krow_a, c, 0, ma, da, ga, &ra);
             span_words<false>(krow_b, c, 0, mb, db, gb, &rb);
             float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f}, ss[4] = {0.f, 0.f, 0.f, 0.f};
-            score_steps<0>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
+            if (p.k_res_coef != 0.f) score_steps<0, true>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);   // launch-uniform
+            else score_steps<0, false>(sa, sb, ss, ka, kb, ma, mb, da, db, ra, rb, ga, gb, st);
             s[0] = fmaf(kr0, ss[0], sa[0] + sa[2]);   // (Ch + Cl) . q + rho * SIGN . q of token g
             s[1] = fmaf(kr0, ss[1], sa[1] + sa[3]);
             s[2] = fmaf(kr1, ss[2], sb[0] + sb[2]);   // of token g + 8
@@ -368,7 +374,8 @@ struct OutlierMmaPolicy {
             }
             span_words<true>(row, g >> 1, g & 1, vm[j], vd[j], vg[j]);
         }
-        value_tiles<0>(st, vw, vm, vd, vg, bh, bs0, bs1);
+        if (p.v_res_coef != 0.f) value_tiles<0, true>(st, vw, vm, vd, vg, bh, bs0, bs1);   // launch-uniform
+        else value_tiles<0, false>(st, vw, vm, vd, vg, bh, bs0, bs1);
     }
 };
 
