@@ -13,7 +13,8 @@
 // bit, and the side bits at the channel's rank, kept in a running shift of the side stream -- and one 4-byte read of the
 // unified table [mask bit][code] returns half2 (hi, lo) of the centroid; two reads are re-paired with two prmt for a score
 // fragment, and are output fragments as they come.  Signs are exact in fp16, so SIGN . q and SIGN^T . p are plain 16-token
-// mma with fragments built from the sign bits.
+// mma whose +-1 fragments come from two 16-entry tables indexed by four sign bits; a side whose residual scale is 0 (the
+// reference's contract) leaves its sign products out.
 //
 // Thread (g = lane / 4, c = lane % 4): scores -- tokens g and g + 8, channels [32c, 32c + 32) = mask word c, sign word c and
 // RB code words; outputs -- tokens 2c, 2c + 1, 2c + 8, 2c + 9, channels [16g, 16g + 16) = one half of mask word g / 2.
